@@ -1,0 +1,99 @@
+"""Device-timed micro-benchmarks of the hot kernels with achieved-vs-roofline fractions.
+
+Counterpart of the reference's ``kernels/bench/bench_gemv.cu`` / ``bench_w4h.cu`` / ``bench_read.cu``.  Every number
+is taken with CUDA events on the launching stream after warm-up; the L2 is flushed between timed launches by writing
+a buffer larger than L2 (256 MiB).  Roofline denominators come from ``MEASURED_PEAKS.json`` when present.
+
+    python -m agens_engine_b200.bench_kernels gemv [--m 1] [--small]
+    python -m agens_engine_b200.bench_kernels attn
+    python -m agens_engine_b200.bench_kernels gemm
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from . import _lib
+from .ops import linear as L
+
+
+def peaks() -> dict:
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+class L2Flusher:
+    def __init__(self, dev):
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def time_cuda(fn, iters=20, warmup=5, flush=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) * 1e3)
+    ts.sort()
+    return ts[len(ts) // 2], ts[0]
+
+
+def bench_gemv(args):
+    dev = "cuda:0"
+    pk = peaks()
+    flush = L2Flusher(dev)
+    ws = L.GemvWorkspace(dev, floats=16 << 20)
+    shapes = [("qkv", 10240, 5120), ("o", 5120, 8192), ("gate_up", 51200, 5120), ("down", 5120, 25600),
+              ("lm_head", 151936, 5120)]
+    if args.small:
+        shapes = [("gate_up", 51200, 5120)]
+    rows = []
+    for name, n, k in shapes:
+        for bits in ([4] if name == "lm_head" else [2, 3, 4]):
+            for rb in (2, 4):
+                ks_list = sorted({1, L.choose_ks(n, k, rb), L.choose_ks(n, k, rb, 2400)})
+                for ks in ks_list:
+                    lin = L.WqLinear.random(n, k, bits, 128, dev, seed=1, rb=rb, ks=ks)
+                    x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
+                    out = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+                    fn = lambda: L.gemv(lin, x, ws, out=out)
+                    med, best = time_cuda(fn, flush=flush)
+                    nbytes = lin.wq.numel() + lin.sz.numel() * 2
+                    gbs = nbytes / med / 1e3
+                    rows.append(dict(name=name, n=n, k=k, bits=bits, rb=rb, ks=ks, m=args.m, us=round(med, 2),
+                                     best_us=round(best, 2), gbs=round(gbs, 1), frac=round(gbs / pk["hbm_gbs"], 3)))
+                    print(json.dumps(rows[-1]), flush=True)
+    print(json.dumps({"peaks": pk}))
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemv", "attn", "gemm"])
+    ap.add_argument("--m", type=int, default=1)
+    ap.add_argument("--small", action="store_true")
+    args = ap.parse_args(argv)
+    if args.what == "gemv":
+        bench_gemv(args)
+    else:
+        raise SystemExit(f"{args.what}: not available yet")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,46 @@
+"""Launchers of the paged attention kernels (``csrc/kernels/sm100/attn_decode.cu``, ``attn_prefill.cu``)."""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import AttnDecodeArgs, check, current_stream, ptr
+
+PAGE = 16
+
+
+def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tensor, grp_tok0: torch.Tensor,
+                grp_cnt: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, hq: int, hkv: int, hd: int,
+                split_keys: int, max_splits: int, part_o: Optional[torch.Tensor] = None,
+                part_ml: Optional[torch.Tensor] = None, tree_mask: Optional[torch.Tensor] = None,
+                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q: bf16 [n_tok, hq*hd] (RoPE applied); kv_pool: bf16 [pages, 2, hkv, 16, hd].  Returns bf16 [n_tok, hq*hd]."""
+    lib = _lib.cuda_lib()
+    n_tok = q.shape[0]
+    dev = q.device
+    if part_o is None:
+        part_o = torch.empty(n_tok, hq, max_splits, hd, dtype=torch.float32, device=dev)
+        part_ml = torch.empty(n_tok, hq, max_splits, 2, dtype=torch.float32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
+    out = torch.empty(n_tok, hq * hd, dtype=torch.bfloat16, device=dev)
+    a = AttnDecodeArgs()
+    a.q, a.ldq = ptr(q), q.stride(0)
+    a.kv_pool, a.n_pages = ptr(kv_pool), kv_pool.shape[0]
+    a.block_table, a.bt_ld = ptr(block_table), block_table.stride(0)
+    a.grp_tok0, a.grp_cnt, a.n_groups = ptr(grp_tok0), ptr(grp_cnt), grp_tok0.numel()
+    a.tok_pos, a.tok_seq = ptr(tok_pos), ptr(tok_seq)
+    a.tree_mask = ptr(tree_mask)
+    a.hq, a.hkv = hq, hkv
+    a.split_keys, a.max_splits = split_keys, max_splits
+    a.scale_log2 = (1.0 / math.sqrt(hd)) * math.log2(math.e)
+    a.part_o, a.part_ml = ptr(part_o), ptr(part_ml)
+    a.out, a.ldo = ptr(out), out.stride(0)
+    a.n_tok = n_tok
+    a.status = ptr(status)
+    with torch.cuda.device(dev):
+        check(lib.b2_attn_decode(C.byref(a), hd, current_stream()), "b2_attn_decode")
+    return out

@@ -1,0 +1,170 @@
+"""Quantised linears on the GPU: FM weight holder + GEMV launcher (decode / verify / small batch).
+
+Python here only assembles argument blocks; the arithmetic is in ``csrc/kernels/sm100/wq_gemv.cu``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import (EPI_ARGMAX, EPI_F32, EPI_RESID, EPI_STORE, EPI_SWIGLU, EPI_TP_RESID, PRO_NORM, PRO_PLAIN, WqGemvArgs,
+                    check, current_stream, ptr)
+from ..utils import quant
+
+SS_LD = 64   # token stride of partial-sum-of-squares / argmax-partial buffers
+
+
+def fm_bytes(n: int, k: int, bits: int) -> int:
+    return (n // 16) * (k // quant.chunk_k(bits)) * quant.record_bytes(bits)
+
+
+def choose_ks(n: int, k: int, rb: int, target_ctas: int = 1184) -> int:
+    """k-split of a linear: a function of the shape only (never of the token count), so per-row arithmetic stays
+    batch invariant.  Picks the smallest divisor-friendly split that yields about ``target_ctas`` CTAs."""
+    nu = k // 128
+    npanels = (n // 16 + rb - 1) // rb
+    best = 1
+    for ks in (1, 2, 4, 5, 8, 10, 16, 20, 25, 32, 40, 50):
+        if nu % (4 * ks) and nu >= 4 * ks:
+            continue
+        if nu < 4 * ks:
+            break
+        best = ks
+        if npanels * ks >= target_ctas:
+            break
+    return best
+
+
+@dataclasses.dataclass
+class WqLinear:
+    """One quantised linear in kernel (FM) layout on a CUDA device."""
+    n: int
+    k: int
+    bits: int
+    group: int
+    wq: torch.Tensor            # uint8 [fm_bytes]
+    sz: torch.Tensor            # fp16 [n/16, k/group, 16, 2]
+    rb: int = 2
+    ks: int = 1
+
+    @staticmethod
+    def from_quant(ql: quant.QuantLinear, device, rb: Optional[int] = None, ks: Optional[int] = None) -> "WqLinear":
+        wq, sz = quant.pack_fm(ql)
+        rb = rb or (4 if ql.n >= 16384 else 2)
+        ks = ks or choose_ks(ql.n, ql.k, rb)
+        return WqLinear(ql.n, ql.k, ql.bits, ql.group, wq.reshape(-1).to(device), sz.to(device), rb, ks)
+
+    @staticmethod
+    def random(n: int, k: int, bits: int, group: int, device, seed: int, stddev: float = 0.02,
+               rb: Optional[int] = None, ks: Optional[int] = None) -> "WqLinear":
+        """Random-init N(0, stddev) weights quantised on the device directly into FM form."""
+        lib = _lib.cuda_lib()
+        wq = torch.empty(fm_bytes(n, k, bits), dtype=torch.uint8, device=device)
+        sz = torch.empty(n // 16, k // group, 16, 2, dtype=torch.float16, device=device)
+        with torch.cuda.device(device):
+            check(lib.b2_wq_random(ptr(wq), ptr(sz), n, k, bits, group, stddev, seed, current_stream()), "b2_wq_random")
+        rb = rb or (4 if n >= 16384 else 2)
+        ks = ks or choose_ks(n, k, rb)
+        return WqLinear(n, k, bits, group, wq, sz, rb, ks)
+
+    @staticmethod
+    def from_checkpoint(packed: torch.Tensor, scale: torch.Tensor, zero: Optional[torch.Tensor], n: int, k: int,
+                        bits: int, group: int, device, rb: Optional[int] = None, ks: Optional[int] = None) -> "WqLinear":
+        """Checkpoint container (bit stream + scales [+ zero points]) -> FM, repacked on the device."""
+        lib = _lib.cuda_lib()
+        packed = packed.to(device).contiguous()
+        scale = scale.to(device).contiguous()
+        zero = None if zero is None else zero.to(device=device, dtype=torch.float16).contiguous()
+        wq = torch.empty(fm_bytes(n, k, bits), dtype=torch.uint8, device=device)
+        sz = torch.empty(n // 16, k // group, 16, 2, dtype=torch.float16, device=device)
+        is_bf16 = 1 if scale.dtype == torch.bfloat16 else 0
+        if not is_bf16 and scale.dtype != torch.float16:
+            scale = scale.to(torch.float16)
+        with torch.cuda.device(device):
+            check(lib.b2_wq_repack(ptr(packed), ptr(scale), is_bf16, ptr(zero), n, k, bits, group, ptr(wq), ptr(sz),
+                                   current_stream()), "b2_wq_repack")
+        rb = rb or (4 if n >= 16384 else 2)
+        ks = ks or choose_ks(n, k, rb)
+        return WqLinear(n, k, bits, group, wq, sz, rb, ks)
+
+    def n_panels(self) -> int:
+        return (self.n // 16 + self.rb - 1) // self.rb
+
+    def dequant(self) -> torch.Tensor:
+        """bf16 [n, k] on the device (kernel path)."""
+        lib = _lib.cuda_lib()
+        out = torch.empty(self.n, self.k, dtype=torch.bfloat16, device=self.wq.device)
+        with torch.cuda.device(out.device):
+            check(lib.b2_wq_dequant(ptr(self.wq), ptr(self.sz), self.n, self.k, self.bits, self.group, ptr(out), self.k,
+                                    current_stream()), "b2_wq_dequant")
+        return out
+
+    def dequant_cpu(self) -> torch.Tensor:
+        """fp32 [n, k] computed on the CPU from the FM bytes (independent of every kernel)."""
+        ql = quant.unpack_fm(self.wq.cpu().reshape(self.n // 16, -1, quant.record_bytes(self.bits)), self.sz.cpu(),
+                             self.bits, self.n, self.k, self.group)
+        return ql.dequant()
+
+
+class GemvWorkspace:
+    """Split-k scratch and self-resetting panel counters shared by the GEMV launches of one stream."""
+
+    def __init__(self, device, floats: int = 4 << 20, panels: int = 1 << 16):
+        self.scratch = torch.empty(floats, dtype=torch.float32, device=device)
+        self.counters = torch.zeros(panels, dtype=torch.int32, device=device)
+
+
+def gemv(lin: WqLinear, x: torch.Tensor, ws: Optional[GemvWorkspace] = None, *, epi: int = EPI_STORE,
+         pro: int = PRO_PLAIN, ss_in: Optional[torch.Tensor] = None, ss_parts: int = 0,
+         norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6, resid: Optional[torch.Tensor] = None,
+         out: Optional[torch.Tensor] = None, ss_out: Optional[torch.Tensor] = None,
+         amax_val: Optional[torch.Tensor] = None, amax_idx: Optional[torch.Tensor] = None, n_valid: Optional[int] = None,
+         yf: Optional[torch.Tensor] = None, tp: Optional[_lib.TpPush] = None):
+    """Launch one GEMV on the current stream.  ``x``: bf16 ``[m, k]`` (``h`` when ``pro == PRO_NORM``)."""
+    lib = _lib.cuda_lib()
+    m = x.shape[0]
+    assert x.dtype == torch.bfloat16 and x.shape[1] == lin.k and x.stride(1) == 1
+    dev = x.device
+    a = WqGemvArgs()
+    a.wq, a.sz = ptr(lin.wq), ptr(lin.sz)
+    a.n, a.k, a.m = lin.n, lin.k, m
+    a.bits, a.group, a.rb, a.ks = lin.bits, lin.group, lin.rb, lin.ks
+    a.pro = pro
+    a.x, a.ldx = ptr(x), x.stride(0)
+    a.ss_in, a.ss_parts, a.ss_ld = ptr(ss_in), ss_parts, SS_LD
+    a.norm_w, a.eps = ptr(norm_w), eps
+    a.epi = epi
+    if epi in (EPI_STORE, EPI_RESID, EPI_TP_RESID):
+        if out is None:
+            out = torch.empty(m, lin.n, dtype=torch.bfloat16, device=dev)
+        a.y, a.ldy = ptr(out), out.stride(0)
+    elif epi == EPI_SWIGLU:
+        if out is None:
+            out = torch.empty(m, lin.n // 2, dtype=torch.bfloat16, device=dev)
+        a.y, a.ldy = ptr(out), out.stride(0)
+    elif epi == EPI_F32:
+        if out is None:
+            out = torch.empty(m, lin.n, dtype=torch.float32, device=dev)
+        a.yf, a.ldy = ptr(out), out.stride(0)
+    elif epi == EPI_ARGMAX:
+        a.amax_val, a.amax_idx = ptr(amax_val), ptr(amax_idx)
+        a.n_valid = lin.n if n_valid is None else n_valid
+        if yf is not None:
+            a.yf, a.ldy = ptr(yf), yf.stride(0)
+    if resid is not None:
+        a.resid, a.ldr = ptr(resid), resid.stride(0)
+    a.ss_out = ptr(ss_out)
+    if lin.ks > 1:
+        assert ws is not None
+        need = lib.b2_wq_gemv_scratch_floats(lin.n, lin.rb, lin.ks, m)
+        assert need <= ws.scratch.numel() and lin.n_panels() <= ws.counters.numel()
+        a.scratch, a.counters = ptr(ws.scratch), ptr(ws.counters)
+    if tp is not None:
+        a.tp = tp
+    with torch.cuda.device(dev):
+        check(lib.b2_wq_gemv(C.byref(a), current_stream()), "b2_wq_gemv")
+    return out
