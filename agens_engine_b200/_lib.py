@@ -63,6 +63,7 @@ def host_lib() -> C.CDLL:
 # structure mirrors
 # ---------------------------------------------------------------------------------------------------------------
 K_MAX_TP = 8
+K_MAX_KS = 64
 
 
 class TpPush(C.Structure):
@@ -81,7 +82,7 @@ class WqGemvArgs(C.Structure):
         ("wq", C.c_void_p), ("sz", C.c_void_p),
         ("n", C.c_int), ("k", C.c_int), ("m", C.c_int),
         ("bits", C.c_int), ("group", C.c_int),
-        ("rb", C.c_int), ("ks", C.c_int),
+        ("ks", C.c_int),
         ("pro", C.c_int),
         ("x", C.c_void_p), ("ldx", C.c_long),
         ("ss_in", C.c_void_p), ("ss_parts", C.c_int), ("ss_ld", C.c_int),
@@ -93,6 +94,8 @@ class WqGemvArgs(C.Structure):
         ("yf", C.c_void_p),
         ("amax_val", C.c_void_p), ("amax_idx", C.c_void_p), ("n_valid", C.c_int),
         ("scratch", C.c_void_p), ("counters", C.c_void_p),
+        ("tickets", C.c_void_p), ("ticket_parity", C.c_int),
+        ("status", C.c_void_p),
         ("tp", TpPush),
     ]
 
@@ -123,7 +126,7 @@ def _declare(lib: C.CDLL):
     vp, i, l, f = C.c_void_p, C.c_int, C.c_long, C.c_float
     sig = {
         "b2_wq_gemv": ([C.POINTER(WqGemvArgs), vp], i),
-        "b2_wq_gemv_scratch_floats": ([i, i, i, i], l),
+        "b2_wq_gemv_scratch_floats": ([i, i, i], l),
         "b2_wq_dequant": ([vp, vp, i, i, i, i, vp, l, vp], i),
         "b2_wq_repack": ([vp, vp, i, vp, i, i, i, i, vp, vp, vp], i),
         "b2_wq_random": ([vp, vp, i, i, i, i, f, C.c_ulonglong, vp], i),

@@ -22,20 +22,16 @@ def fm_bytes(n: int, k: int, bits: int) -> int:
     return (n // 16) * (k // quant.chunk_k(bits)) * quant.record_bytes(bits)
 
 
-def choose_ks(n: int, k: int, rb: int, target_ctas: int = 1184) -> int:
-    """k-split of a linear: a function of the shape only (never of the token count), so per-row arithmetic stays
-    batch invariant.  Picks the smallest divisor-friendly split that yields about ``target_ctas`` CTAs."""
+def choose_ks(n: int, k: int, slice_k: int = 1024) -> int:
+    """Number of k slices of a linear: a function of the shape only (never of the token count), so per-row
+    arithmetic stays batch invariant.  Slices of about ``slice_k`` inputs keep the staged activations small and give
+    the persistent GEMV thousands of (panel, slice) work items to balance over the SMs."""
     nu = k // 128
-    npanels = (n // 16 + rb - 1) // rb
+    want = max(1, round(k / slice_k))
     best = 1
-    for ks in (1, 2, 4, 5, 8, 10, 16, 20, 25, 32, 40, 50):
-        if nu % (4 * ks) and nu >= 4 * ks:
-            continue
-        if nu < 4 * ks:
-            break
-        best = ks
-        if npanels * ks >= target_ctas:
-            break
+    for ks in range(1, min(nu, _lib.K_MAX_KS) + 1):
+        if nu % ks == 0 and abs(ks - want) < abs(best - want):
+            best = ks
     return best
 
 
@@ -48,32 +44,29 @@ class WqLinear:
     group: int
     wq: torch.Tensor            # uint8 [fm_bytes]
     sz: torch.Tensor            # fp16 [n/16, k/group, 16, 2]
-    rb: int = 2
     ks: int = 1
 
     @staticmethod
-    def from_quant(ql: quant.QuantLinear, device, rb: Optional[int] = None, ks: Optional[int] = None) -> "WqLinear":
+    def from_quant(ql: quant.QuantLinear, device, ks: Optional[int] = None) -> "WqLinear":
         wq, sz = quant.pack_fm(ql)
-        rb = rb or (4 if ql.n >= 16384 else 2)
-        ks = ks or choose_ks(ql.n, ql.k, rb)
-        return WqLinear(ql.n, ql.k, ql.bits, ql.group, wq.reshape(-1).to(device), sz.to(device), rb, ks)
+        ks = ks or choose_ks(ql.n, ql.k)
+        return WqLinear(ql.n, ql.k, ql.bits, ql.group, wq.reshape(-1).to(device), sz.to(device), ks)
 
     @staticmethod
     def random(n: int, k: int, bits: int, group: int, device, seed: int, stddev: float = 0.02,
-               rb: Optional[int] = None, ks: Optional[int] = None) -> "WqLinear":
+               ks: Optional[int] = None) -> "WqLinear":
         """Random-init N(0, stddev) weights quantised on the device directly into FM form."""
         lib = _lib.cuda_lib()
         wq = torch.empty(fm_bytes(n, k, bits), dtype=torch.uint8, device=device)
         sz = torch.empty(n // 16, k // group, 16, 2, dtype=torch.float16, device=device)
         with torch.cuda.device(device):
             check(lib.b2_wq_random(ptr(wq), ptr(sz), n, k, bits, group, stddev, seed, current_stream()), "b2_wq_random")
-        rb = rb or (4 if n >= 16384 else 2)
-        ks = ks or choose_ks(n, k, rb)
-        return WqLinear(n, k, bits, group, wq, sz, rb, ks)
+        ks = ks or choose_ks(n, k)
+        return WqLinear(n, k, bits, group, wq, sz, ks)
 
     @staticmethod
     def from_checkpoint(packed: torch.Tensor, scale: torch.Tensor, zero: Optional[torch.Tensor], n: int, k: int,
-                        bits: int, group: int, device, rb: Optional[int] = None, ks: Optional[int] = None) -> "WqLinear":
+                        bits: int, group: int, device, ks: Optional[int] = None) -> "WqLinear":
         """Checkpoint container (bit stream + scales [+ zero points]) -> FM, repacked on the device."""
         lib = _lib.cuda_lib()
         packed = packed.to(device).contiguous()
@@ -87,12 +80,11 @@ class WqLinear:
         with torch.cuda.device(device):
             check(lib.b2_wq_repack(ptr(packed), ptr(scale), is_bf16, ptr(zero), n, k, bits, group, ptr(wq), ptr(sz),
                                    current_stream()), "b2_wq_repack")
-        rb = rb or (4 if n >= 16384 else 2)
-        ks = ks or choose_ks(n, k, rb)
-        return WqLinear(n, k, bits, group, wq, sz, rb, ks)
+        ks = ks or choose_ks(n, k)
+        return WqLinear(n, k, bits, group, wq, sz, ks)
 
     def n_panels(self) -> int:
-        return (self.n // 16 + self.rb - 1) // self.rb
+        return (self.n // 16 + 1) // 2
 
     def dequant(self) -> torch.Tensor:
         """bf16 [n, k] on the device (kernel path)."""
@@ -111,14 +103,22 @@ class WqLinear:
 
 
 class GemvWorkspace:
-    """Split-k scratch and self-resetting panel counters shared by the GEMV launches of one stream."""
+    """Split-k scratch, self-resetting panel counters and the two alternating sets of work tickets shared by the
+    GEMV launches of one stream."""
 
     def __init__(self, device, floats: int = 4 << 20, panels: int = 1 << 16):
         self.scratch = torch.empty(floats, dtype=torch.float32, device=device)
         self.counters = torch.zeros(panels, dtype=torch.int32, device=device)
+        self.tickets = torch.zeros(2 * (_lib.K_MAX_KS + 1), dtype=torch.int32, device=device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.parity = 0
+
+    def next_parity(self) -> int:
+        self.parity ^= 1
+        return self.parity
 
 
-def gemv(lin: WqLinear, x: torch.Tensor, ws: Optional[GemvWorkspace] = None, *, epi: int = EPI_STORE,
+def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STORE,
          pro: int = PRO_PLAIN, ss_in: Optional[torch.Tensor] = None, ss_parts: int = 0,
          norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6, resid: Optional[torch.Tensor] = None,
          out: Optional[torch.Tensor] = None, ss_out: Optional[torch.Tensor] = None,
@@ -132,7 +132,7 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: Optional[GemvWorkspace] = None, *, 
     a = WqGemvArgs()
     a.wq, a.sz = ptr(lin.wq), ptr(lin.sz)
     a.n, a.k, a.m = lin.n, lin.k, m
-    a.bits, a.group, a.rb, a.ks = lin.bits, lin.group, lin.rb, lin.ks
+    a.bits, a.group, a.ks = lin.bits, lin.group, lin.ks
     a.pro = pro
     a.x, a.ldx = ptr(x), x.stride(0)
     a.ss_in, a.ss_parts, a.ss_ld = ptr(ss_in), ss_parts, SS_LD
@@ -159,10 +159,11 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: Optional[GemvWorkspace] = None, *, 
         a.resid, a.ldr = ptr(resid), resid.stride(0)
     a.ss_out = ptr(ss_out)
     if lin.ks > 1:
-        assert ws is not None
-        need = lib.b2_wq_gemv_scratch_floats(lin.n, lin.rb, lin.ks, m)
+        need = lib.b2_wq_gemv_scratch_floats(lin.n, lin.ks, m)
         assert need <= ws.scratch.numel() and lin.n_panels() <= ws.counters.numel()
         a.scratch, a.counters = ptr(ws.scratch), ptr(ws.counters)
+    a.tickets, a.ticket_parity = ptr(ws.tickets), ws.next_parity()
+    a.status = ptr(ws.status)
     if tp is not None:
         a.tp = tp
     with torch.cuda.device(dev):

@@ -35,21 +35,62 @@ struct WFrag {
   uint32_t sz[GPB][2];      // half2 (scale, zero) for rows g and g+8
 };
 
+// Shared-memory ring of one warp.  A stage holds kBps consecutive 128-k batches of RB row blocks, brought in by
+// cp.async.bulk copies (one per row block for the weights, one for the scale/zero pairs) that complete on the
+// stage's mbarrier.  Every warp runs its own ring, so the CTA never synchronises inside the k loop.
+constexpr int kBps = 2;     // batches per stage
+constexpr int kStages = 3;  // ring depth
+
+template <int BITS, int GROUP, int RB>
+struct Ring {
+  static constexpr int RPB = 128 / Fmt<BITS>::CK;
+  static constexpr int GPB = 128 / GROUP;
+  static constexpr int W_BATCH = RPB * Fmt<BITS>::REC;     // weight bytes of one batch of one row block
+  static constexpr int SZ_BATCH = GPB * 64;                 // scale/zero bytes of one batch of one row block
+  static constexpr int W_BYTES = kBps * W_BATCH;
+  static constexpr int SZ_BYTES = kBps * SZ_BATCH;
+  static constexpr int STAGE = RB * (W_BYTES + SZ_BYTES);
+};
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after about two seconds and reports failure instead of hanging the GPU.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (globaltimer_ns() - t0 > 2000000000ull) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
 template <int BITS, int GROUP>
-__device__ __forceinline__ void load_frag(WFrag<BITS, GROUP>& f, const uint8_t* wq, const __half2* sz, int rb, int nch,
-                                          int ng, int kb /* batch index = k/128 */, int lane) {
+__device__ __forceinline__ void load_frag_smem(WFrag<BITS, GROUP>& f, const uint8_t* wrec, const uint8_t* szrec, int lane) {
   constexpr int REC = Fmt<BITS>::REC;
   constexpr int RPB = WFrag<BITS, GROUP>::RPB;
   constexpr int GPB = WFrag<BITS, GROUP>::GPB;
-  const uint8_t* p = wq + ((size_t)rb * nch + (size_t)kb * RPB) * REC;
 #pragma unroll
-  for (int i = 0; i < RPB; ++i) f.lo[i] = ld_nc_v4(p + (size_t)i * REC + lane * 16);
-  if (BITS == 3) f.hi = ld_nc_v2(p + 512 + lane * 8);
-  const uint32_t* s = reinterpret_cast<const uint32_t*>(sz) + ((size_t)rb * ng + (size_t)kb * GPB) * 16 + (lane >> 2);
+  for (int i = 0; i < RPB; ++i) f.lo[i] = *reinterpret_cast<const uint4*>(wrec + i * REC + lane * 16);
+  if (BITS == 3) f.hi = *reinterpret_cast<const uint2*>(wrec + 512 + lane * 8);
 #pragma unroll
   for (int g = 0; g < GPB; ++g) {
-    f.sz[g][0] = ld_nc_u32(s + g * 16);
-    f.sz[g][1] = ld_nc_u32(s + g * 16 + 8);
+    f.sz[g][0] = *reinterpret_cast<const uint32_t*>(szrec + g * 64 + (lane >> 2) * 4);
+    f.sz[g][1] = *reinterpret_cast<const uint32_t*>(szrec + g * 64 + 32 + (lane >> 2) * 4);
   }
 }
 
@@ -112,55 +153,93 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v))
 
 }  // namespace
 
-template <int BITS, int GROUP, int RB, int NT>
+constexpr int kRB = 2;   // row blocks per panel: 32 rows, one row per lane in the epilogue
+
+// Persistent kernel.  CTA c works on k slice (c % ks) of every panel; its four warps pull panels of that slice from
+// a ticket counter, so a warp item is (panel of 32 rows, k slice) and nothing inside the k loop synchronises the
+// CTA.  The activation slice is staged once per CTA.  Partial results of the ks slices of a panel meet in
+// scratch memory; the warp that arrives last sums them in slice order and runs the epilogue.
+template <int BITS, int GROUP, int NT>
 __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs a) {
   constexpr int CK = Fmt<BITS>::CK;
   constexpr int GPB = 128 / GROUP;
-  constexpr int PK = NT == 1 ? 512 : (NT == 2 ? 256 : 128);   // k positions staged per piece
-  constexpr int XST = PK + 16;                                 // halfs per staged token row (bank spread)
-  constexpr int ROWS = RB * 16;
+  constexpr int RB = kRB;
   constexpr int MP = NT * 8;
-  constexpr int NGP = PK / GROUP;
+  using R = Ring<BITS, GROUP, RB>;
 
-  extern __shared__ __align__(16) uint8_t smem_raw[];
+  extern __shared__ __align__(128) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int m = a.m;
-  // carve shared memory
-  float* inv_rms = reinterpret_cast<float*>(smem_raw);                       // [MP]
-  float* red = inv_rms + MP;                                                 // [4][MP][ROWS]
-  uint8_t* wbase = reinterpret_cast<uint8_t*>(red + 4 * MP * ROWS);
-  const int xs_bytes = m * XST * 2;
-  const int per_warp = xs_bytes + NGP * MP * 8;
-  __half* xs = reinterpret_cast<__half*>(wbase + (size_t)warp * per_warp);   // [m][XST]
-  float2* gsum = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(xs) + xs_bytes);   // [NGP][MP]
-
   const int nrb = a.n >> 4;
+  const int npanels = (nrb + RB - 1) / RB;
   const int nch = a.k / CK;
   const int ng = a.k / GROUP;
-  const int panel = blockIdx.x;
-  const int rb0 = panel * RB;
-
-  // k range of this warp in 128-k batches (depends on k and ks only)
   const int nu = a.k >> 7;
-  const int nsub = 4 * a.ks;
-  const int sub = blockIdx.y * 4 + warp;
-  const int u0 = (int)(((long)nu * sub) / nsub);
-  const int u1 = (int)(((long)nu * (sub + 1)) / nsub);
-  const int nb = u1 - u0;
+  const int ks = a.ks;
+  const int slice = blockIdx.x % ks;
+  const int u0 = (int)(((long)nu * slice) / ks);
+  const int u1 = (int)(((long)nu * (slice + 1)) / ks);
+  const int nb = u1 - u0;                       // 128-k batches of this CTA's slice
+  const int nst = (nb + kBps - 1) / kBps;       // ring stages per item
+  const int nb_max = (nu + ks - 1) / ks;
+  const int XST = nb_max * 128 + 16;            // halfs per staged token row (row pitch = 32 B mod 128 B)
 
-  WFrag<BITS, GROUP> cur[RB], nxt[RB];
-  int rbs[RB];
+  // shared memory: [4 rings][mbarriers][inv_rms][4 x fin][xs][gsum]
+  uint8_t* ring = smem_raw + (size_t)warp * kStages * R::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)4 * kStages * R::STAGE) + warp * kStages;
+  float* inv_rms = reinterpret_cast<float*>(smem_raw + (size_t)4 * kStages * R::STAGE + 4 * kStages * 8);
+  float* fin = inv_rms + MP + (size_t)warp * MP * 32;                        // [MP][32] per warp
+  __half* xs = reinterpret_cast<__half*>(inv_rms + MP + 4 * MP * 32);        // [m][XST]
+  float2* gsum = reinterpret_cast<float2*>(xs + (size_t)m * XST);            // [nb_max * GPB][MP]
+
+  const uint32_t ring_u = smem_u32(ring);
+  const uint32_t bars_u = smem_u32(bars);
+  unsigned* tickets = a.tickets + (size_t)a.ticket_parity * (kMaxKs + 1);
+
+  // ---- producer state (lane 0): panels cur / nxt / nx2 and a cursor (which item, which stage) ----
+  unsigned t_cur = 0, t_nxt = 0, t_nx2 = 0;
+  if (lane == 0) {
 #pragma unroll
-  for (int r = 0; r < RB; ++r) rbs[r] = min(rb0 + r, nrb - 1);   // tail panel: duplicate the last block, ignore it later
-  // Weights do not depend on the previous kernel: start streaming before the dependency wait.
-  if (nb > 0) {
-#pragma unroll
-    for (int r = 0; r < RB; ++r) load_frag<BITS, GROUP>(cur[r], a.wq, a.sz, rbs[r], nch, ng, u0, lane);
+    for (int i = 0; i < kStages; ++i) mbar_init(bars_u + i * 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    t_cur = atomicAdd(tickets + slice, 1u);
+    t_nxt = atomicAdd(tickets + slice, 1u);
+    t_nx2 = atomicAdd(tickets + slice, 1u);
   }
+  unsigned prod = 0, cons = 0;     // stages issued / consumed by this warp since kernel start
+  int p_which = 0, p_st = 0;       // producer cursor: item (0 = cur, 1 = nxt) and stage inside it
+  auto issue_one = [&]() -> bool { // lane 0 only; returns false when nothing can be issued now
+    if (p_which > 1) return false;
+    const unsigned panel = p_which == 0 ? t_cur : t_nxt;
+    if (panel >= (unsigned)npanels) return false;
+    const int slot = prod % kStages;
+    const int b0 = p_st * kBps;
+    const int nbs = min(kBps, nb - b0);
+    const uint32_t bar = bars_u + slot * 8;
+    mbar_expect_tx(bar, (uint32_t)(RB * nbs * (R::W_BATCH + R::SZ_BATCH)));
+    const uint32_t dst = ring_u + slot * R::STAGE;
+#pragma unroll
+    for (int r = 0; r < RB; ++r) {
+      const int rb = min((int)panel * RB + r, nrb - 1);   // tail panel: duplicate the last block, ignored later
+      const uint8_t* wsrc = a.wq + ((size_t)rb * nch + (size_t)(u0 + b0) * R::RPB) * Fmt<BITS>::REC;
+      bulk_g2s(dst + r * R::W_BYTES, wsrc, (uint32_t)(nbs * R::W_BATCH), bar);
+      const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(a.sz) + ((size_t)rb * ng + (size_t)(u0 + b0) * GPB) * 64;
+      bulk_g2s(dst + RB * R::W_BYTES + r * R::SZ_BYTES, ssrc, (uint32_t)(nbs * R::SZ_BATCH), bar);
+    }
+    ++prod;
+    if (++p_st == nst) { p_st = 0; ++p_which; }
+    return true;
+  };
+  // Weights do not depend on the previous kernel: start streaming before the dependency wait.
+  if (lane == 0 && nb > 0) {
+    while (prod - cons < (unsigned)kStages && issue_one()) { }
+  }
+  __syncwarp();
   pdl_wait();
   pdl_launch_dependents();   // the next kernel may start prefetching its weights while this one runs
 
+  // ---- stage the activation slice of this CTA: fp16(x / c) and the per-group sums ----
   if (a.pro == PRO_NORM) {
     for (int tok = warp; tok < m; tok += 4) {
       float s = 0.f;
@@ -168,317 +247,348 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
       s = warp_sum(s);
       if (lane == 0) inv_rms[tok] = rsqrtf(s / (float)a.k + a.eps);
     }
+    __syncthreads();
+  }
+  {
+    const int nvec = nb * 16;
+    const int k0 = u0 * 128;
+    for (int tok = 0; tok < m; ++tok) {
+      for (int v0 = 0; v0 < nvec; v0 += kGemvThreads) {
+        const int v = v0 + threadIdx.x;
+        const bool act = v < nvec;
+        float ssum = 0.f, xsum = 0.f;
+        if (act) {
+          const int k = k0 + v * 8;
+          const uint4 raw = *reinterpret_cast<const uint4*>(a.x + (size_t)tok * a.ldx + k);
+          const bf16* xb = reinterpret_cast<const bf16*>(&raw);
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(xb[i]);
+          if (a.pro == PRO_NORM) {
+            const uint4 wr = *reinterpret_cast<const uint4*>(a.norm_w + k);
+            const bf16* wb = reinterpret_cast<const bf16*>(&wr);
+            const float ir = inv_rms[tok];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[i] = bf16_round(f[i] * ir * __bfloat162float(wb[i]));
+          }
+          __align__(16) __half h[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float cinv, c;
+            slot_scale<BITS>((v * 8 + i) & 127, cinv, c);
+            h[i] = __float2half_rn(f[i] * cinv);
+            const float hf = __half2float(h[i]);
+            ssum += hf;
+            xsum += hf * c;
+          }
+          *reinterpret_cast<uint4*>(xs + (size_t)tok * XST + v * 8) = *reinterpret_cast<const uint4*>(h);
+        }
+        // reduce over the GROUP/8 lanes that cover one group (fixed xor tree)
+#pragma unroll
+        for (int o = GROUP / 16; o > 0; o >>= 1) {
+          ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+          xsum += __shfl_xor_sync(0xffffffffu, xsum, o);
+        }
+        if (act && (lane % (GROUP / 8)) == 0) gsum[((v * 8) / GROUP) * MP + tok] = make_float2(1024.f * ssum, xsum);
+      }
+    }
   }
   __syncthreads();
 
-  float y[RB][NT][4];
+  unsigned cur = __shfl_sync(0xffffffffu, t_cur, 0);
+  bool failed = false;
+  while (cur < (unsigned)npanels && nb > 0 && !failed) {
+    float y[RB][NT][4];
 #pragma unroll
-  for (int r = 0; r < RB; ++r)
+    for (int r = 0; r < RB; ++r)
 #pragma unroll
-    for (int n = 0; n < NT; ++n)
+      for (int n = 0; n < NT; ++n)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) y[r][n][i] = 0.f;
+        for (int i = 0; i < 4; ++i) y[r][n][i] = 0.f;
 
-  for (int b = 0; b < nb; ++b) {
-    const int kb = u0 + b;
-    if (b + 1 < nb) {
+    for (int st = 0; st < nst; ++st) {
+      const int slot = cons % kStages;
+      if (!mbar_wait_bounded(bars_u + slot * 8, (cons / kStages) & 1u)) {
+        if (a.status) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
+        failed = true;
+        break;
+      }
+      const int nbs = min(kBps, nb - st * kBps);
+#pragma unroll 1
+      for (int bb = 0; bb < nbs; ++bb) {
+        const int b = st * kBps + bb;
+        WFrag<BITS, GROUP> cf[RB];
 #pragma unroll
-      for (int r = 0; r < RB; ++r) load_frag<BITS, GROUP>(nxt[r], a.wq, a.sz, rbs[r], nch, ng, kb + 1, lane);
-    }
-    const int pofs = (b * 128) % PK;
-    if (pofs == 0) {
-      // ---- stage the next piece of x for this warp: fp16(x / c) and the per-group sums ----
-      __syncwarp();
-      const int len = min(PK, (nb - b) * 128);
-      const int k0 = kb * 128;
-      const int nvec = len >> 3;
-      for (int tok = 0; tok < m; ++tok) {
-        for (int v0 = 0; v0 < nvec; v0 += 32) {
-          const int v = v0 + lane;
-          const bool act = v < nvec;
-          float ssum = 0.f, xsum = 0.f;
-          if (act) {
-            const int k = k0 + v * 8;
-            const uint4 raw = *reinterpret_cast<const uint4*>(a.x + (size_t)tok * a.ldx + k);
-            const bf16* xb = reinterpret_cast<const bf16*>(&raw);
-            float f[8];
+        for (int r = 0; r < RB; ++r)
+          load_frag_smem<BITS, GROUP>(cf[r], ring + slot * R::STAGE + r * R::W_BYTES + bb * R::W_BATCH,
+                                      ring + slot * R::STAGE + RB * R::W_BYTES + r * R::SZ_BYTES + bb * R::SZ_BATCH, lane);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(xb[i]);
-            if (a.pro == PRO_NORM) {
-              const uint4 wr = *reinterpret_cast<const uint4*>(a.norm_w + k);
-              const bf16* wb = reinterpret_cast<const bf16*>(&wr);
-              const float ir = inv_rms[tok];
+        for (int gg = 0; gg < GPB; ++gg) {
+          float acc[RB][NT][4];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = bf16_round(f[i] * ir * __bfloat162float(wb[i]));
+          for (int r = 0; r < RB; ++r)
+#pragma unroll
+            for (int n = 0; n < NT; ++n)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) acc[r][n][i] = 0.f;
+#pragma unroll
+          for (int s8 = 0; s8 < 8 / GPB; ++s8) {
+            const int s = gg * (8 / GPB) + s8;
+            uint32_t bf[NT][2];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+              bf[n][0] = 0u; bf[n][1] = 0u;
+              const int tok = n * 8 + g;
+              if (tok < m) {
+                const uint2 v = *reinterpret_cast<const uint2*>(xs + (size_t)tok * XST + b * 128 + s * 16 + t * 4);
+                bf[n][0] = v.x; bf[n][1] = v.y;
+              }
             }
-            __align__(16) __half h[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              float cinv, c;
-              slot_scale<BITS>((v * 8 + i) & 127, cinv, c);
-              h[i] = __float2half_rn(f[i] * cinv);
-              const float hf = __half2float(h[i]);
-              ssum += hf;
-              xsum += hf * c;
+            for (int r = 0; r < RB; ++r) {
+              uint32_t af[4];
+              extract<BITS, GROUP>(cf[r], s, af);
+#pragma unroll
+              for (int n = 0; n < NT; ++n) mma_f16_16816(acc[r][n], af, bf[n][0], bf[n][1]);
             }
-            *reinterpret_cast<uint4*>(xs + (size_t)tok * XST + v * 8) = *reinterpret_cast<const uint4*>(h);
           }
-          // reduce over the GROUP/8 lanes that cover one group (fixed xor tree)
+          // y += scale * (acc - 1024*sum(xs) - zero*sum(x))
+          const int gi = b * GPB + gg;
 #pragma unroll
-          for (int o = GROUP / 16; o > 0; o >>= 1) {
-            ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
-            xsum += __shfl_xor_sync(0xffffffffu, xsum, o);
+          for (int n = 0; n < NT; ++n) {
+            const float2 q0 = gsum[gi * MP + n * 8 + 2 * t];
+            const float2 q1 = gsum[gi * MP + n * 8 + 2 * t + 1];
+#pragma unroll
+            for (int r = 0; r < RB; ++r) {
+              const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&cf[r].sz[gg][0]));
+              const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&cf[r].sz[gg][1]));
+              y[r][n][0] += s0.x * (acc[r][n][0] - q0.x - s0.y * q0.y);
+              y[r][n][1] += s0.x * (acc[r][n][1] - q1.x - s0.y * q1.y);
+              y[r][n][2] += s1.x * (acc[r][n][2] - q0.x - s1.y * q0.y);
+              y[r][n][3] += s1.x * (acc[r][n][3] - q1.x - s1.y * q1.y);
+            }
           }
-          if (act && (lane % (GROUP / 8)) == 0) gsum[((v * 8) / GROUP) * MP + tok] = make_float2(1024.f * ssum, xsum);
         }
       }
+      // the slot is free again: keep the ring full (the cursor may already be in the next item)
       __syncwarp();
-    }
-    // ---- one 128-k batch ----
-#pragma unroll
-    for (int gg = 0; gg < GPB; ++gg) {
-      float acc[RB][NT][4];
-#pragma unroll
-      for (int r = 0; r < RB; ++r)
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) acc[r][n][i] = 0.f;
-#pragma unroll
-      for (int s8 = 0; s8 < 8 / GPB; ++s8) {
-        const int s = gg * (8 / GPB) + s8;
-        uint32_t bf[NT][2];
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          bf[n][0] = 0u; bf[n][1] = 0u;
-          const int tok = n * 8 + g;
-          if (tok < m) {
-            const uint2 v = *reinterpret_cast<const uint2*>(xs + (size_t)tok * XST + pofs + s * 16 + t * 4);
-            bf[n][0] = v.x; bf[n][1] = v.y;
-          }
-        }
-#pragma unroll
-        for (int r = 0; r < RB; ++r) {
-          uint32_t af[4];
-          extract<BITS, GROUP>(cur[r], s, af);
-#pragma unroll
-          for (int n = 0; n < NT; ++n) mma_f16_16816(acc[r][n], af, bf[n][0], bf[n][1]);
-        }
+      ++cons;
+      if (lane == 0) {
+        while (prod - cons < (unsigned)kStages && issue_one()) { }
       }
-      // y += scale * (acc - 1024*sum(xs) - zero*sum(x))
-      const int gi = (pofs / GROUP) + gg;
+    }
+    if (failed) break;
+
+    // ---- item done: fragment layout -> one row per lane ----
+    const int panel = (int)cur;
+    const int n0 = panel * 32;
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < RB; ++r)
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
-        const float2 q0 = gsum[gi * MP + n * 8 + 2 * t];
-        const float2 q1 = gsum[gi * MP + n * 8 + 2 * t + 1];
+        const int tok = n * 8 + 2 * t;
+        fin[(size_t)tok * 32 + r * 16 + g] = y[r][n][0];
+        fin[(size_t)(tok + 1) * 32 + r * 16 + g] = y[r][n][1];
+        fin[(size_t)tok * 32 + r * 16 + g + 8] = y[r][n][2];
+        fin[(size_t)(tok + 1) * 32 + r * 16 + g + 8] = y[r][n][3];
+      }
+    __syncwarp();
+    float v[MP];
 #pragma unroll
-        for (int r = 0; r < RB; ++r) {
-          const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&cur[r].sz[gg][0]));
-          const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&cur[r].sz[gg][1]));
-          y[r][n][0] += s0.x * (acc[r][n][0] - q0.x - s0.y * q0.y);
-          y[r][n][1] += s0.x * (acc[r][n][1] - q1.x - s0.y * q1.y);
-          y[r][n][2] += s1.x * (acc[r][n][2] - q0.x - s1.y * q0.y);
-          y[r][n][3] += s1.x * (acc[r][n][3] - q1.x - s1.y * q1.y);
+    for (int tok = 0; tok < MP; ++tok) v[tok] = tok < m ? fin[tok * 32 + lane] : 0.f;
+    bool do_epi = true;
+    if (ks > 1) {
+      float* sp = a.scratch + ((size_t)panel * ks) * (size_t)(m * 32);
+#pragma unroll
+      for (int tok = 0; tok < MP; ++tok)
+        if (tok < m) sp[(size_t)slice * (m * 32) + tok * 32 + lane] = v[tok];
+      __threadfence();
+      __syncwarp();
+      unsigned prev = 0;
+      if (lane == 0) prev = atomicInc(a.counters + panel, (unsigned)ks - 1u);
+      prev = __shfl_sync(0xffffffffu, prev, 0);
+      do_epi = prev == (unsigned)ks - 1u;
+      if (do_epi) {
+        __threadfence();
+#pragma unroll
+        for (int tok = 0; tok < MP; ++tok) {
+          if (tok < m) {
+            float s = 0.f;
+            for (int j = 0; j < ks; ++j) s += __ldcg(sp + (size_t)j * (m * 32) + tok * 32 + lane);
+            v[tok] = s;
+          }
         }
       }
     }
-    if (b + 1 < nb) {
+    const int row = n0 + lane;
+    const bool row_ok = row < a.n;
+    if (do_epi) {
+      if (a.epi == EPI_TP_RESID) {
+        // ---- push all-reduce of this panel: every rank writes its partial into every inbox, then sums its own
+        //      inbox in rank order once no sentinel is left ----
+        const TpPush& tp = a.tp;
+        if (row_ok) {
+          if (!tp.skip_push) {
+            for (int dst = 0; dst < tp.size; ++dst) {
+              float* pb = tp.inbox[dst] + tp.slot_off + (size_t)tp.rank * tp.slot_stride + row;
 #pragma unroll
-      for (int r = 0; r < RB; ++r) cur[r] = nxt[r];
+              for (int tok = 0; tok < MP; ++tok)
+                if (tok < m) {
+                  const float val = v[tok] + 0.f;   // -0.0 -> +0.0: the sentinel never travels as data
+                  asm volatile("st.volatile.global.f32 [%0], %1;" ::"l"(pb + (size_t)tok * a.n), "f"(val) : "memory");
+                }
+            }
+          }
+          const float* mine = tp.inbox[tp.rank] + tp.slot_off + row;
+          const uint64_t t_start = globaltimer_ns();
+#pragma unroll
+          for (int tok = 0; tok < MP; ++tok) {
+            if (tok < m) {
+              float s = 0.f;
+              for (int src = 0; src < tp.size; ++src) {
+                const float* pp = mine + (size_t)src * tp.slot_stride + (size_t)tok * a.n;
+                float val;
+                unsigned spins = 0;
+                bool ok;
+                while (true) {
+                  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(val) : "l"(pp) : "memory");
+                  ok = __float_as_uint(val) != 0x80000000u;
+                  if (ok) break;
+                  if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > tp.timeout_ns) break;
+                }
+                if (!ok) { atomicExch(tp.status, (int)B2_ERR_TIMEOUT); val = 0.f; }
+                s += val;
+              }
+              v[tok] = s;
+            }
+          }
+          if (tp.clear_off >= 0) {   // re-arm the slot that no rank writes before its next use
+            float* clr = tp.inbox[tp.rank] + tp.clear_off + row;
+            const float neg0 = __uint_as_float(0x80000000u);
+            for (int src = 0; src < tp.size; ++src)
+#pragma unroll
+              for (int tok = 0; tok < MP; ++tok)
+                if (tok < m) clr[(size_t)src * tp.slot_stride + (size_t)tok * a.n] = neg0;
+          }
+        }
+      }
+      if (a.epi == EPI_STORE) {
+#pragma unroll
+        for (int tok = 0; tok < MP; ++tok)
+          if (tok < m && row_ok) a.y[(size_t)tok * a.ldy + row] = __float2bfloat16_rn(v[tok]);
+      } else if (a.epi == EPI_F32) {
+#pragma unroll
+        for (int tok = 0; tok < MP; ++tok)
+          if (tok < m && row_ok) a.yf[(size_t)tok * a.ldy + row] = v[tok];
+      } else if (a.epi == EPI_RESID || a.epi == EPI_TP_RESID) {
+#pragma unroll
+        for (int tok = 0; tok < MP; ++tok) {
+          if (tok < m) {
+            float sq = 0.f;
+            if (row_ok) {
+              const bf16 hb = __float2bfloat16_rn(v[tok] + __bfloat162float(a.resid[(size_t)tok * a.ldr + row]));
+              a.y[(size_t)tok * a.ldy + row] = hb;
+              const float hf = __bfloat162float(hb);
+              sq = hf * hf;
+            }
+            sq = warp_sum(sq);
+            if (lane == 0 && a.ss_out) a.ss_out[(size_t)panel * a.ss_ld + tok] = sq;
+          }
+        }
+      } else if (a.epi == EPI_SWIGLU) {
+        // lanes 0-7 / 16-23 hold gate rows, lanes 8-15 / 24-31 the matching up rows
+#pragma unroll
+        for (int tok = 0; tok < MP; ++tok) {
+          if (tok < m) {
+            const float up = __shfl_down_sync(0xffffffffu, v[tok], 8);
+            if ((lane & 8) == 0 && row_ok) {
+              const float gt = bf16_round(v[tok]);
+              a.y[(size_t)tok * a.ldy + (size_t)panel * 16 + (lane >> 4) * 8 + (lane & 7)] =
+                  __float2bfloat16_rn(silu_f(gt) * bf16_round(up));
+            }
+          }
+        }
+      } else if (a.epi == EPI_ARGMAX) {
+#pragma unroll
+        for (int tok = 0; tok < MP; ++tok) {
+          if (tok < m) {
+            if (a.yf && row_ok) a.yf[(size_t)tok * a.ldy + row] = v[tok];
+            float best = (row_ok && row < a.n_valid) ? v[tok] : -INFINITY;
+            int bi = (row_ok && row < a.n_valid) ? row : 0x7fffffff;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+              const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+              if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+            }
+            if (lane == 0) {
+              a.amax_val[(size_t)panel * a.ss_ld + tok] = best;
+              a.amax_idx[(size_t)panel * a.ss_ld + tok] = bi;
+            }
+          }
+        }
+      }
     }
-  }
-  // tokens >= m were staged as zeros only implicitly (their B fragments were zero): gsum of those tokens is
-  // uninitialised, so their y is garbage and is never read below.
-
-  // ---- cross-warp reduction in warp order ----
-#pragma unroll
-  for (int r = 0; r < RB; ++r)
-#pragma unroll
-    for (int n = 0; n < NT; ++n) {
-      const int tok = n * 8 + 2 * t;
-      float* base = red + ((size_t)warp * MP) * ROWS + r * 16 + g;
-      base[(size_t)tok * ROWS] = y[r][n][0];
-      base[(size_t)(tok + 1) * ROWS] = y[r][n][1];
-      base[(size_t)tok * ROWS + 8] = y[r][n][2];
-      base[(size_t)(tok + 1) * ROWS + 8] = y[r][n][3];
+    // ---- next item ----
+    if (lane == 0) {
+      t_cur = t_nxt; t_nxt = t_nx2;
+      t_nx2 = atomicAdd(tickets + slice, 1u);
+      --p_which;
+      while (prod - cons < (unsigned)kStages && issue_one()) { }
     }
-  __syncthreads();
-  float* fin = red;   // [tok][ROWS], reuses warp 0's slab after the sum
-  {
-    float v[(MP * ROWS + kGemvThreads - 1) / kGemvThreads];
-    int c = 0;
-    for (int idx = threadIdx.x; idx < m * ROWS; idx += kGemvThreads, ++c)
-      v[c] = ((red[idx] + red[MP * ROWS + idx]) + red[2 * MP * ROWS + idx]) + red[3 * MP * ROWS + idx];
-    __syncthreads();
-    c = 0;
-    for (int idx = threadIdx.x; idx < m * ROWS; idx += kGemvThreads, ++c) fin[idx] = v[c];
+    cur = __shfl_sync(0xffffffffu, t_cur, 0);
   }
-  __syncthreads();
-
-  // ---- split-k across CTAs: partials to scratch, the last CTA of the panel sums them in slice order ----
-  if (a.ks > 1) {
-    float* sp = a.scratch + ((size_t)panel * a.ks) * (size_t)(m * ROWS);
-    for (int idx = threadIdx.x; idx < m * ROWS; idx += kGemvThreads) sp[(size_t)blockIdx.y * (m * ROWS) + idx] = fin[idx];
+  if (failed) {
+    // Give copies still in flight a bounded chance to land before the CTA's shared memory is released.
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) { }
+  }
+  // ---- the last warp of the grid to leave re-arms the ticket counters for the next launch on this parity ----
+  __syncwarp();
+  if (lane == 0) {
     __threadfence();
-    __syncthreads();
-    __shared__ int s_last;
-    if (threadIdx.x == 0) {
-      const unsigned prev = atomicInc(a.counters + panel, (unsigned)a.ks - 1u);
-      s_last = (prev == (unsigned)a.ks - 1u);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    for (int idx = threadIdx.x; idx < m * ROWS; idx += kGemvThreads) {
-      float s = 0.f;
-      for (int j = 0; j < a.ks; ++j) s += __ldcg(sp + (size_t)j * (m * ROWS) + idx);
-      fin[idx] = s;
-    }
-    __syncthreads();
-  }
-
-  const int n0 = panel * ROWS;
-
-  // ---- tensor-parallel push all-reduce of this panel ----
-  if (a.epi == EPI_TP_RESID) {
-    const TpPush& tp = a.tp;
-    const int nvec = (m * ROWS) >> 2;
-    if (!tp.skip_push) {
-      for (int idx = threadIdx.x; idx < nvec * tp.size; idx += kGemvThreads) {
-        const int dst = idx / nvec, e = (idx - dst * nvec) << 2;
-        const int tok = e / ROWS, row = e - tok * ROWS;
-        if (n0 + row >= a.n) continue;
-        float4 v = *reinterpret_cast<const float4*>(fin + e);
-        v.x += 0.f; v.y += 0.f; v.z += 0.f; v.w += 0.f;   // -0.0 -> +0.0: the sentinel never travels as data
-        float* p = tp.inbox[dst] + tp.slot_off + (size_t)tp.rank * tp.slot_stride + (size_t)tok * a.n + n0 + row;
-        asm volatile("st.volatile.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w)
-                     : "memory");
-      }
-    }
-    __syncthreads();
-    const float* mine = tp.inbox[tp.rank] + tp.slot_off;
-    const uint64_t t_start = globaltimer_ns();
-    for (int idx = threadIdx.x; idx < nvec; idx += kGemvThreads) {
-      const int e = idx << 2;
-      const int tok = e / ROWS, row = e - tok * ROWS;
-      if (n0 + row >= a.n) continue;
-      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int src = 0; src < tp.size; ++src) {
-        const float* p = mine + (size_t)src * tp.slot_stride + (size_t)tok * a.n + n0 + row;
-        float4 v;
-        unsigned spins = 0;
-        bool ok = false;
-        while (true) {
-          asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-                       : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
-          ok = (__float_as_uint(v.x) != 0x80000000u) & (__float_as_uint(v.y) != 0x80000000u) &
-               (__float_as_uint(v.z) != 0x80000000u) & (__float_as_uint(v.w) != 0x80000000u);
-          if (ok) break;
-          if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > tp.timeout_ns) break;
-        }
-        if (!ok) {
-          atomicExch(tp.status, (int)B2_ERR_TIMEOUT);
-          v = make_float4(0.f, 0.f, 0.f, 0.f);
-        }
-        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-      }
-      *reinterpret_cast<float4*>(fin + e) = s;
-    }
-    // re-arm the slot that no rank writes before its next use
-    if (tp.clear_off >= 0) {
-      float* clr = tp.inbox[tp.rank] + tp.clear_off;
-      const float neg0 = __uint_as_float(0x80000000u);
-      for (int idx = threadIdx.x; idx < nvec * tp.size; idx += kGemvThreads) {
-        const int src = idx / nvec, e = (idx - src * nvec) << 2;
-        const int tok = e / ROWS, row = e - tok * ROWS;
-        if (n0 + row >= a.n) continue;
-        *reinterpret_cast<float4*>(clr + (size_t)src * tp.slot_stride + (size_t)tok * a.n + n0 + row) =
-            make_float4(neg0, neg0, neg0, neg0);
-      }
-    }
-    __syncthreads();
-  }
-
-  // ---- epilogues ----
-  if (a.epi == EPI_STORE) {
-    for (int idx = threadIdx.x; idx < m * ROWS; idx += kGemvThreads) {
-      const int tok = idx / ROWS, row = idx - tok * ROWS;
-      if (n0 + row < a.n) a.y[(size_t)tok * a.ldy + n0 + row] = __float2bfloat16_rn(fin[idx]);
-    }
-  } else if (a.epi == EPI_F32) {
-    for (int idx = threadIdx.x; idx < m * ROWS; idx += kGemvThreads) {
-      const int tok = idx / ROWS, row = idx - tok * ROWS;
-      if (n0 + row < a.n) a.yf[(size_t)tok * a.ldy + n0 + row] = fin[idx];
-    }
-  } else if (a.epi == EPI_RESID || a.epi == EPI_TP_RESID) {
-    for (int tok = warp; tok < m; tok += 4) {
-      float sq = 0.f;
-#pragma unroll
-      for (int row = lane; row < ROWS; row += 32) {
-        if (n0 + row < a.n) {
-          const float v = fin[tok * ROWS + row] + __bfloat162float(a.resid[(size_t)tok * a.ldr + n0 + row]);
-          const bf16 hb = __float2bfloat16_rn(v);
-          a.y[(size_t)tok * a.ldy + n0 + row] = hb;
-          const float hf = __bfloat162float(hb);
-          sq += hf * hf;
-        }
-      }
-      sq = warp_sum(sq);
-      if (lane == 0 && a.ss_out) a.ss_out[(size_t)panel * a.ss_ld + tok] = sq;
-    }
-  } else if (a.epi == EPI_SWIGLU) {
-    constexpr int HR = ROWS / 2;
-    for (int idx = threadIdx.x; idx < m * HR; idx += kGemvThreads) {
-      const int tok = idx / HR, j = idx - tok * HR;
-      const int blk = j >> 3, r = j & 7;
-      if (n0 + blk * 16 < a.n) {
-        const float gate = bf16_round(fin[tok * ROWS + blk * 16 + r]);
-        const float up = bf16_round(fin[tok * ROWS + blk * 16 + 8 + r]);
-        a.y[(size_t)tok * a.ldy + (size_t)panel * HR + j] = __float2bfloat16_rn(silu_f(gate) * up);
-      }
-    }
-  } else if (a.epi == EPI_ARGMAX) {
-    for (int tok = warp; tok < m; tok += 4) {
-      float best = -INFINITY;
-      int bi = 0x7fffffff;
-#pragma unroll
-      for (int row = lane; row < ROWS; row += 32) {
-        const int ni = n0 + row;
-        if (ni < a.n) {
-          const float v = fin[tok * ROWS + row];
-          if (a.yf) a.yf[(size_t)tok * a.ldy + ni] = v;
-          if (ni < a.n_valid && (v > best || (v == best && ni < bi))) { best = v; bi = ni; }
-        }
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-      }
-      if (lane == 0) {
-        a.amax_val[(size_t)panel * a.ss_ld + tok] = best;
-        a.amax_idx[(size_t)panel * a.ss_ld + tok] = bi;
-      }
+    const unsigned total = gridDim.x * 4u;
+    if (atomicAdd(tickets + kMaxKs, 1u) == total - 1u) {
+      for (int i = 0; i < ks; ++i) tickets[i] = 0u;
+      tickets[kMaxKs] = 0u;
+      __threadfence();
     }
   }
 }
 
-template <int BITS, int GROUP, int RB, int NT>
+template <int BITS, int GROUP, int NT>
 static int launch_one(const WqGemvArgs& a, cudaStream_t st) {
-  constexpr int PK = NT == 1 ? 512 : (NT == 2 ? 256 : 128);
-  constexpr int XST = PK + 16, ROWS = RB * 16, MP = NT * 8, NGP = PK / GROUP;
-  const size_t smem = (size_t)MP * 4 + (size_t)4 * MP * ROWS * 4 + 4 * ((size_t)a.m * XST * 2 + (size_t)NGP * MP * 8);
-  auto kern = wq_gemv_kernel<BITS, GROUP, RB, NT>;
+  constexpr int MP = NT * 8;
+  using R = Ring<BITS, GROUP, kRB>;
+  const int nu = a.k / 128;
+  const int nb_max = (nu + a.ks - 1) / a.ks;
+  const int xst = nb_max * 128 + 16;
+  const size_t smem = (size_t)4 * kStages * R::STAGE + 4 * kStages * 8 + (size_t)MP * 4 + (size_t)4 * MP * 32 * 4 +
+                      (size_t)a.m * xst * 2 + (size_t)nb_max * (128 / GROUP) * MP * 8;
+  if (smem > 220 * 1024) return B2_ERR_ARG;
+  auto kern = wq_gemv_kernel<BITS, GROUP, NT>;
   static bool attr_set = false;   // one flag per instantiation
+  static int sm_count = 0;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return B2_ERR_LAUNCH;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) return B2_ERR_LAUNCH;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     attr_set = true;
   }
+  int occ = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kGemvThreads, smem) != cudaSuccess || occ < 1) return B2_ERR_LAUNCH;
   const int nrb = a.n / 16;
-  const int npanels = (nrb + RB - 1) / RB;
+  const int npanels = (nrb + kRB - 1) / kRB;
+  // persistent grid: a multiple of ks, at most what fits on the device, at most one warp per item
+  long want = (long)sm_count * occ;
+  const long items = (long)npanels * a.ks;
+  if (want * 4 > items) want = (items + 3) / 4;
+  long grid = (want / a.ks) * a.ks;
+  if (grid < a.ks) grid = a.ks;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(npanels, a.ks, 1);
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
   cfg.blockDim = dim3(kGemvThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
@@ -493,11 +603,9 @@ static int launch_one(const WqGemvArgs& a, cudaStream_t st) {
 template <int BITS, int GROUP>
 static int launch_bg(const WqGemvArgs& a, cudaStream_t st) {
   const int nt = (a.m + 7) / 8;
-  if (a.rb == 4 && nt == 1) return launch_one<BITS, GROUP, 4, 1>(a, st);
-  if (a.rb == 4 && nt == 2) return launch_one<BITS, GROUP, 4, 2>(a, st);
-  if (a.rb == 2 && nt == 1) return launch_one<BITS, GROUP, 2, 1>(a, st);
-  if (a.rb == 2 && nt == 2) return launch_one<BITS, GROUP, 2, 2>(a, st);
-  if (a.rb == 2 && nt <= 4) return launch_one<BITS, GROUP, 2, 4>(a, st);
+  if (nt == 1) return launch_one<BITS, GROUP, 1>(a, st);
+  if (nt == 2) return launch_one<BITS, GROUP, 2>(a, st);
+  if (nt <= 4) return launch_one<BITS, GROUP, 4>(a, st);
   return B2_ERR_ARG;
 }
 
@@ -505,24 +613,23 @@ static int launch_bg(const WqGemvArgs& a, cudaStream_t st) {
 
 using namespace b2;
 
-B2_API long b2_wq_gemv_scratch_floats(int n, int rb, int ks, int m) {
+B2_API long b2_wq_gemv_scratch_floats(int n, int ks, int m) {
   if (ks <= 1) return 0;
-  const long npanels = (n / 16 + rb - 1) / rb;
-  return npanels * ks * (long)m * rb * 16;
+  const long npanels = (n / 16 + kRB - 1) / kRB;
+  return npanels * ks * (long)m * 32;
 }
 
 // Launches the GEMV described by *args on `stream`.  Returns a b2::Status; nothing is launched on B2_ERR_ARG.
 B2_API int b2_wq_gemv(const WqGemvArgs* args, cudaStream_t stream) {
-  WqGemvArgs a = *args;
+  const WqGemvArgs& a = *args;
   if (a.n <= 0 || a.k <= 0 || a.m <= 0 || a.m > 32) return B2_ERR_ARG;
-  if (a.n % 16 || a.k % 128 || a.ks < 1) return B2_ERR_ARG;
+  if (a.n % 16 || a.k % 128 || a.ks < 1 || a.ks > kMaxKs || a.ks > a.k / 128) return B2_ERR_ARG;
   if (a.group != 64 && a.group != 128) return B2_ERR_ARG;
-  if (a.rb != 2 && a.rb != 4) return B2_ERR_ARG;
-  if (a.m > 16 && a.rb != 2) return B2_ERR_ARG;   // 17..32 tokens only with 32-row panels (register budget)
+  if (!a.tickets || (a.ticket_parity != 0 && a.ticket_parity != 1)) return B2_ERR_ARG;
   if (a.ks > 1 && (!a.scratch || !a.counters)) return B2_ERR_ARG;
   if (a.epi == EPI_SWIGLU && (a.n % 32)) return B2_ERR_ARG;
   if ((a.ldx % 8) || (reinterpret_cast<uintptr_t>(a.x) & 15)) return B2_ERR_ARG;
-  if (a.epi == EPI_TP_RESID && ((a.n % 4) || a.tp.size < 1 || a.tp.size > kMaxTp)) return B2_ERR_ARG;
+  if (a.epi == EPI_TP_RESID && (a.tp.size < 1 || a.tp.size > kMaxTp)) return B2_ERR_ARG;
   switch (a.bits * 1000 + a.group) {
     case 4128: return launch_bg<4, 128>(a, stream);
     case 4064: return launch_bg<4, 64>(a, stream);

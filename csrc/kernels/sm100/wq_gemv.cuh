@@ -19,6 +19,7 @@ enum GemvEpi : int {
 
 constexpr int kGemvThreads = 128;       // 4 warps per CTA, the warps split the CTA's k range
 constexpr int kMaxTp = 8;
+constexpr int kMaxKs = 64;            // most k slices a linear may be cut into
 
 struct TpPush {
   // Lamport-style inboxes: inbox[r] is rank r's inbox region as mapped in this process (own region included).
@@ -38,8 +39,7 @@ struct WqGemvArgs {
   const __half2* sz;     // [n/16][k/group][16] (scale, zero)
   int n, k, m;
   int bits, group;
-  int rb;                // row blocks (of 16 rows) per panel: 2 or 4
-  int ks;                // CTAs along k per panel
+  int ks;                // k slices (a function of the linear's shape only)
   int pro;
   const bf16* x; long ldx;
   const float* ss_in; int ss_parts; int ss_ld;
@@ -50,7 +50,9 @@ struct WqGemvArgs {
   float* ss_out;
   float* yf;
   float* amax_val; int* amax_idx; int n_valid;   // EPI_ARGMAX: rows >= n_valid never win
-  float* scratch; unsigned* counters;
+  float* scratch; unsigned* counters;   // split-k partials [panel][ks][m][32] and self-resetting panel counters
+  unsigned* tickets; int ticket_parity;  // 2 x (kMaxKs + 1) work counters; consecutive launches alternate parity
+  int* status;           // device status word (B2_ERR_TIMEOUT when a bounded wait ran out)
   TpPush tp;
 };
 
@@ -58,7 +60,7 @@ struct WqGemvArgs {
 
 // Host entry points (C ABI).
 B2_API int b2_wq_gemv(const b2::WqGemvArgs* args, cudaStream_t stream);
-B2_API long b2_wq_gemv_scratch_floats(int n, int rb, int ks, int m);
+B2_API long b2_wq_gemv_scratch_floats(int n, int ks, int m);
 B2_API int b2_wq_dequant(const uint8_t* wq, const __half2* sz, int n, int k, int bits, int group, bf16* out, long ldo,
                          cudaStream_t stream);
 B2_API int b2_wq_repack(const int32_t* packed, const void* scale, int scale_is_bf16, const __half* zero, int n, int k,

@@ -124,6 +124,6 @@ def test_rmsnorm_embed_swiglu():
     assert torch.allclose(ss[:3], (h.float() ** 2).sum(-1), rtol=1e-5)
     gu = torch.randn(n, 512).to(torch.bfloat16).to(DEV)
     act = basic.swiglu_interleaved(gu)
-    g = gu.reshape(n, 16, 2, 8)[:, :, 0].reshape(n, 128).float()
-    u = gu.reshape(n, 16, 2, 8)[:, :, 1].reshape(n, 128).float()
+    g = gu.reshape(n, 32, 2, 8)[:, :, 0].reshape(n, 256).float()
+    u = gu.reshape(n, 32, 2, 8)[:, :, 1].reshape(n, 256).float()
     assert (act.float() - torch.nn.functional.silu(g) * u).abs().max() < 0.03

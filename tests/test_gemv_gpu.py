@@ -11,11 +11,11 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-def _mk(n, k, bits, group, seed=0, rb=None, ks=None):
+def _mk(n, k, bits, group, seed=0, ks=None):
     torch.manual_seed(seed)
     w = torch.randn(n, k) * 0.02
     ql = quant.quantize(w, bits, group)
-    return ql, L.WqLinear.from_quant(ql, DEV, rb=rb, ks=ks)
+    return ql, L.WqLinear.from_quant(ql, DEV, ks=ks)
 
 
 def _ref(ql, x):
@@ -24,12 +24,12 @@ def _ref(ql, x):
 
 @pytest.mark.parametrize("bits", [2, 3, 4])
 @pytest.mark.parametrize("group", [64, 128])
-@pytest.mark.parametrize("rb,ks", [(2, 1), (4, 1), (2, 2)])
-def test_gemv_matches_fp64(bits, group, rb, ks):
+@pytest.mark.parametrize("ks", [1, 2, 8])
+def test_gemv_matches_fp64(bits, group, ks):
     n, k = 160, 1024
-    ql, lin = _mk(n, k, bits, group, rb=rb, ks=ks)
+    ql, lin = _mk(n, k, bits, group, ks=ks)
     ws = L.GemvWorkspace(DEV)
-    for m in (1, 3, 8):
+    for m in (1, 3, 8, 13, 32):
         x = (torch.randn(m, k) * 1.5).to(torch.bfloat16).to(DEV)
         y = L.gemv(lin, x, ws, epi=_lib.EPI_F32)
         ref = _ref(ql, x)
@@ -63,7 +63,7 @@ def test_device_repack_matches_cpu_pack(bits, sym):
 def test_rows_do_not_depend_on_batch():
     """Batch invariance: a token's output bits are the same at m = 1, inside m = 8 and inside m = 16."""
     for bits in (2, 3, 4):
-        ql, lin = _mk(128, 2048, bits, 128, seed=bits, rb=2, ks=2)
+        ql, lin = _mk(128, 2048, bits, 128, seed=bits, ks=2)
         ws = L.GemvWorkspace(DEV)
         x = torch.randn(16, 2048).to(torch.bfloat16).to(DEV)
         y16 = L.gemv(lin, x, ws, epi=_lib.EPI_F32)
@@ -71,12 +71,13 @@ def test_rows_do_not_depend_on_batch():
         y1 = L.gemv(lin, x[5:6].contiguous(), ws, epi=_lib.EPI_F32)
         assert torch.equal(y16[:8], y8)
         assert torch.equal(y16[5:6], y1)
-        lin4 = L.WqLinear(lin.n, lin.k, lin.bits, lin.group, lin.wq, lin.sz, rb=4, ks=2)
-        assert torch.equal(L.gemv(lin4, x[:8].contiguous(), ws, epi=_lib.EPI_F32), y8)
+        x32 = torch.cat([x, x], 0)
+        y32 = L.gemv(lin, x32, ws, epi=_lib.EPI_F32)
+        assert torch.equal(y32[:16], y16) and torch.equal(y32[16:], y16)
 
 
 def test_gemv_is_deterministic():
-    ql, lin = _mk(256, 4096, 3, 128, seed=9, rb=2, ks=4)
+    ql, lin = _mk(256, 4096, 3, 128, seed=9, ks=4)
     ws = L.GemvWorkspace(DEV)
     x = torch.randn(4, 4096).to(torch.bfloat16).to(DEV)
     y0 = L.gemv(lin, x, ws, epi=_lib.EPI_F32)
@@ -88,7 +89,7 @@ def test_norm_prologue_and_residual_epilogue():
     torch.manual_seed(11)
     d, n = 1024, 256
     ql, lin = _mk(n, d, 4, 128, seed=1)
-    qlo, lino = _mk(d, n, 4, 128, seed=2, rb=2, ks=1)
+    qlo, lino = _mk(d, n, 4, 128, seed=2, ks=1)
     ws = L.GemvWorkspace(DEV)
     m = 3
     h = torch.randn(m, d).to(torch.bfloat16).to(DEV)
@@ -119,9 +120,9 @@ def test_swiglu_epilogue():
     gate = torch.randn(f, d) * 0.05
     up = torch.randn(f, d) * 0.05
     ql = quant.quantize(quant.interleave_gate_up(gate, up), 4, 128)
-    lin = L.WqLinear.from_quant(ql, DEV, rb=2, ks=1)
+    lin = L.WqLinear.from_quant(ql, DEV, ks=2)
     x = torch.randn(m, d).to(torch.bfloat16).to(DEV)
-    act = L.gemv(lin, x, None, epi=_lib.EPI_SWIGLU)
+    act = L.gemv(lin, x, L.GemvWorkspace(DEV), epi=_lib.EPI_SWIGLU)
     wd = ql.dequant().reshape(f // 8, 16, d)
     g = (x.float().cpu() @ wd[:, :8].reshape(f, d).t()).to(torch.bfloat16).float()
     u = (x.float().cpu() @ wd[:, 8:].reshape(f, d).t()).to(torch.bfloat16).float()
@@ -133,12 +134,12 @@ def test_argmax_epilogue():
     from agens_engine_b200.ops import basic
     torch.manual_seed(13)
     n, d, m = 1000 * 16, 512, 4
-    ql, lin = _mk(n, d, 4, 128, seed=4, rb=4, ks=1)
+    ql, lin = _mk(n, d, 4, 128, seed=4, ks=2)
     x = torch.randn(m, d).to(torch.bfloat16).to(DEV)
     val = torch.empty(lin.n_panels(), L.SS_LD, dtype=torch.float32, device=DEV)
     idx = torch.empty(lin.n_panels(), L.SS_LD, dtype=torch.int32, device=DEV)
     logits = torch.empty(m, n, dtype=torch.float32, device=DEV)
-    L.gemv(lin, x, None, epi=_lib.EPI_ARGMAX, amax_val=val, amax_idx=idx, n_valid=n - 100, yf=logits)
+    L.gemv(lin, x, L.GemvWorkspace(DEV), epi=_lib.EPI_ARGMAX, amax_val=val, amax_idx=idx, n_valid=n - 100, yf=logits)
     ids = basic.argmax_final(val, idx, lin.n_panels(), m, L.SS_LD)
     assert torch.equal(ids.long().cpu(), logits[:, : n - 100].argmax(-1).cpu())
     assert torch.equal(basic.argmax_rows(logits, n - 100).long().cpu(), logits[:, : n - 100].argmax(-1).cpu())
