@@ -1,0 +1,374 @@
+"""Engine-backed dense GQA decoder: weights in kernel layout, paged KV, chunked prefill, graph-captured decode.
+
+This is the model-runtime layer (reference: ``kernels/m1/m1_model.cu`` ``run_model`` :2815-2967 and ``layer``
+:2544-2596, the page allocator :1694-1716 and the decode graphs :3071-3140) restated for the dense family.
+A decode step is five fused launches per layer -- qkv GEMV (RMSNorm folded into its prologue), RoPE + KV store,
+paged attention (+ merge), o_proj GEMV (residual add + next norm statistic in its epilogue), gate/up GEMV (norm
+prologue, SwiGLU epilogue), down GEMV (residual epilogue) -- captured once per batch size into a CUDA graph whose
+only per-step input is the token produced by the previous step, handled on the device.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import _lib
+from .._lib import EPI_ARGMAX, EPI_F32, EPI_RESID, EPI_STORE, EPI_SWIGLU, PRO_NORM, PRO_PLAIN, check, current_stream, ptr
+from ..ops import attention as A
+from ..ops import basic
+from ..ops import linear as L
+from .config import LINEARS, ModelConfig
+
+M_GEMV = 32          # most token rows the GEMV family takes in one launch
+
+
+class PagePool:
+    """Free-list page allocator over the paged KV pool (16-token pages, reference: alloc_row m1_model.cu:1694)."""
+
+    def __init__(self, n_pages: int):
+        self.free = list(range(n_pages - 1, -1, -1))
+        self.n_pages = n_pages
+
+    def alloc(self) -> int:
+        if not self.free:
+            raise RuntimeError("KV pool exhausted")
+        return self.free.pop()
+
+    def release(self, pages):
+        self.free.extend(pages)
+
+
+class DenseModel:
+    def __init__(self, cfg: ModelConfig, device="cuda:0", max_seqs: int = 1, max_ctx: int = 4096,
+                 n_pages: Optional[int] = None, split_keys: int = 64, prefill_chunk: int = 256):
+        self.cfg, self.dev = cfg, torch.device(device)
+        self.max_seqs, self.max_ctx, self.split_keys = max_seqs, max_ctx, split_keys
+        self.prefill_chunk = prefill_chunk
+        self.pages_per_seq = (max_ctx + cfg.page_size - 1) // cfg.page_size
+        self.n_pages = n_pages or self.pages_per_seq * max_seqs
+        self.max_splits = (max_ctx + split_keys - 1) // split_keys
+        self.layers: List[Dict[str, object]] = []
+        self.embed = None
+        self.final_norm = None
+        self.lm_head: Optional[L.WqLinear] = None
+        self.pool = PagePool(self.n_pages)
+        self.seq_pages: Dict[int, List[int]] = {}
+        self.seq_len_host: Dict[int, int] = {}
+        self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self._alloc_buffers()
+
+    # ------------------------------------------------------------------------------------------------ weights
+    @staticmethod
+    def from_oracle(ow, device="cuda:0", **kw) -> "DenseModel":
+        m = DenseModel(ow.cfg, device, **kw)
+        for l, lay in enumerate(ow.layers):
+            d = {lin: L.WqLinear.from_quant(ow.quant[f"{l}.{lin}"], m.dev) for lin in LINEARS}
+            d["ln1"], d["ln2"] = lay["ln1"].to(m.dev), lay["ln2"].to(m.dev)
+            m.layers.append(d)
+        m.embed = ow.embed.to(m.dev)
+        m.final_norm = ow.final_norm.to(m.dev)
+        m.lm_head = L.WqLinear.from_quant(ow.quant["lm_head"], m.dev)
+        return m.finalize()
+
+    @staticmethod
+    def random_init(cfg: ModelConfig, device="cuda:0", seed: int = 0, **kw) -> "DenseModel":
+        """Random-init weights of the named architecture, quantised on the device (no host copy of 32B weights)."""
+        m = DenseModel(cfg, device, **kw)
+        shapes = cfg.linear_shapes()
+        g = torch.Generator(device=m.dev).manual_seed(seed)
+        for l in range(cfg.n_layers):
+            d = {}
+            for i, lin in enumerate(LINEARS):
+                n, k = shapes[lin]
+                d[lin] = L.WqLinear.random(n, k, cfg.bits_of(l, lin), cfg.group, m.dev, seed=seed * 1000003 + l * 8 + i)
+            d["ln1"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
+            d["ln2"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
+            m.layers.append(d)
+        m.embed = (torch.randn(cfg.vocab, cfg.d_model, device=m.dev, generator=g) * 0.02).to(torch.bfloat16)
+        m.final_norm = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
+        m.lm_head = L.WqLinear.random(cfg.vocab, cfg.d_model, cfg.lm_head_bits, cfg.group, m.dev, seed=seed * 1000003 + 999983)
+        return m.finalize()
+
+    def weight_bytes(self) -> int:
+        t = self.embed.numel() * 2 + self.lm_head.wq.numel() + self.lm_head.sz.numel() * 2
+        for d in self.layers:
+            for lin in LINEARS:
+                t += d[lin].wq.numel() + d[lin].sz.numel() * 2
+        return t
+
+    # ------------------------------------------------------------------------------------------------ buffers
+    def _alloc_buffers(self):
+        cfg, dev = self.cfg, self.dev
+        i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
+        bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
+        M = M_GEMV
+        self.kv = [torch.zeros(self.n_pages, 2, cfg.n_kv_heads, cfg.page_size, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+                   for _ in range(cfg.n_layers)]
+        self.block_table = torch.full((self.max_seqs, self.pages_per_seq), -1, dtype=torch.int32, device=dev)
+        self.seq_len = i32(self.max_seqs)
+        self.ids, self.last_ids, self.out_ids = i32(M), i32(M), i32(M)
+        self.tok_pos, self.tok_seq, self.grp_tok0, self.grp_cnt = i32(M), i32(M), i32(M), i32(M)
+        self.h_a, self.h_b = bf(M, cfg.d_model), bf(M, cfg.d_model)
+        parts = max(cfg.d_model // 32, 1)
+        self.ss_a = torch.zeros(parts, L.SS_LD, dtype=torch.float32, device=dev)
+        self.ss_b = torch.zeros(parts, L.SS_LD, dtype=torch.float32, device=dev)
+        self.qkv = bf(M, cfg.q_dim + 2 * cfg.kv_dim)
+        self.q = bf(M, cfg.q_dim)
+        self.attn = bf(M, cfg.q_dim)
+        self.act = bf(M, cfg.ffn)
+        self.part_o = torch.empty(M, cfg.n_heads, self.max_splits, cfg.head_dim, dtype=torch.float32, device=dev)
+        self.part_ml = torch.empty(M, cfg.n_heads, self.max_splits, 2, dtype=torch.float32, device=dev)
+        lm_panels = (cfg.vocab // 16 + 1) // 2
+        self.amax_val = torch.empty(lm_panels, L.SS_LD, dtype=torch.float32, device=dev)
+        self.amax_idx = torch.empty(lm_panels, L.SS_LD, dtype=torch.int32, device=dev)
+        self.logits = torch.empty(M, cfg.vocab, dtype=torch.float32, device=dev)
+        self.status = i32(1)
+        self.inv_freq = basic.rope_inv_freq(cfg.head_dim, cfg.rope_theta, dev)
+        self.ws = L.GemvWorkspace(dev, floats=max(4 << 20, 2 * cfg.d_model * 64 * M), panels=max(1 << 16, lm_panels))
+        self._deq_tmp = None
+
+    def finalize(self):
+        """Size the split-k workspace from the loaded linears (call once after the weights are in place)."""
+        lib = _lib.cuda_lib()
+        lins = [self.lm_head] + [d[lin] for d in self.layers[:1] for lin in LINEARS]
+        need = max(lib.b2_wq_gemv_scratch_floats(x.n, x.ks, M_GEMV) for x in lins)
+        panels = max(x.n_panels() for x in lins)
+        self.ws = L.GemvWorkspace(self.dev, floats=max(need, 1 << 16), panels=max(panels, 1 << 10))
+        return self
+
+    # ------------------------------------------------------------------------------------------------ sessions
+    def new_seq(self, seq: int):
+        assert 0 <= seq < self.max_seqs and seq not in self.seq_pages
+        self.seq_pages[seq] = []
+        self.seq_len_host[seq] = 0
+        self.seq_len[seq] = 0
+
+    def free_seq(self, seq: int):
+        self.pool.release(self.seq_pages.pop(seq))
+        self.seq_len_host.pop(seq)
+        self.block_table[seq].fill_(-1)
+
+    def reserve(self, seq: int, n_tokens: int):
+        """Make sure pages exist for the first ``n_tokens`` positions of ``seq`` (rows grow lazily, as in the
+        reference's KV admission, serve.rs:343-410)."""
+        pages = self.seq_pages[seq]
+        need = (n_tokens + self.cfg.page_size - 1) // self.cfg.page_size
+        if need > self.pages_per_seq:
+            raise RuntimeError("context length exceeds max_ctx")
+        if need > len(pages):
+            new = [self.pool.alloc() for _ in range(need - len(pages))]
+            self.block_table[seq, len(pages):need] = torch.tensor(new, dtype=torch.int32, device=self.dev)
+            pages.extend(new)
+
+    def truncate(self, seq: int, n_tokens: int):
+        """Roll a sequence back to ``n_tokens`` (rejected speculative rows); pages past the end are released."""
+        self.seq_len_host[seq] = n_tokens
+        self.seq_len[seq] = n_tokens
+        keep = (n_tokens + self.cfg.page_size - 1) // self.cfg.page_size
+        pages = self.seq_pages[seq]
+        if keep < len(pages):
+            self.pool.release(pages[keep:])
+            self.block_table[seq, keep:len(pages)] = -1
+            del pages[keep:]
+
+    # ------------------------------------------------------------------------------------------------ small-m forward
+    def _layers_small(self, m: int, n_groups: int):
+        """Layers of one step for m <= 32 token rows already described by tok_pos / tok_seq / grp_*; h_a and ss_a
+        hold the embedded tokens.  Every launch goes to the current stream (capturable)."""
+        cfg, ws = self.cfg, self.ws
+        h_a, h_b = self.h_a[:m], self.h_b[:m]
+        parts_a = 1
+        for li, d in enumerate(self.layers):
+            L.gemv(d["qkv"], h_a, ws, pro=PRO_NORM, ss_in=self.ss_a, ss_parts=parts_a, norm_w=d["ln1"], eps=cfg.rms_eps,
+                   out=self.qkv[:m])
+            basic.rope_kvstore(self.qkv[:m], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, self.tok_pos,
+                               self.tok_seq, self.block_table, self.kv[li], self.q[:m], status=self.status)
+            A.attn_decode(self.q[:m], self.kv[li], self.block_table, self.grp_tok0[:n_groups], self.grp_cnt[:n_groups],
+                          self.tok_pos, self.tok_seq, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.split_keys,
+                          self.max_splits, part_o=self.part_o, part_ml=self.part_ml, status=self.status, out=self.attn[:m])
+            L.gemv(d["o"], self.attn[:m], ws, epi=EPI_RESID, resid=h_a, out=h_b, ss_out=self.ss_b)
+            L.gemv(d["gate_up"], h_b, ws, pro=PRO_NORM, ss_in=self.ss_b, ss_parts=d["o"].n_panels(), norm_w=d["ln2"],
+                   eps=cfg.rms_eps, epi=EPI_SWIGLU, out=self.act[:m])
+            L.gemv(d["down"], self.act[:m], ws, epi=EPI_RESID, resid=h_b, out=h_a, ss_out=self.ss_a)
+            parts_a = d["down"].n_panels()
+        return parts_a
+
+    def _head_small(self, m: int, parts_a: int, want_logits: bool):
+        cfg = self.cfg
+        L.gemv(self.lm_head, self.h_a[:m], self.ws, pro=PRO_NORM, ss_in=self.ss_a, ss_parts=parts_a, norm_w=self.final_norm,
+               eps=cfg.rms_eps, epi=EPI_ARGMAX, amax_val=self.amax_val, amax_idx=self.amax_idx,
+               n_valid=cfg.vocab_valid or cfg.vocab, yf=self.logits[:m] if want_logits else None)
+        lib = _lib.cuda_lib()
+        check(lib.b2_argmax_final(ptr(self.amax_val), ptr(self.amax_idx), self.lm_head.n_panels(), L.SS_LD, m,
+                                  ptr(self.out_ids), 0, current_stream()), "b2_argmax_final")
+
+    def forward_rows(self, ids: List[int], seqs: List[int], want_logits: bool = False):
+        """Eager step over explicit rows: ``ids[i]`` is appended to sequence ``seqs[i]`` (rows of one sequence must be
+        adjacent: they form a verify group).  Returns the argmax token of every row (and fp32 logits on request)."""
+        m = len(ids)
+        assert 1 <= m <= M_GEMV
+        pos, g0, gc = [], [], []
+        nxt = dict(self.seq_len_host)
+        for i, s in enumerate(seqs):
+            if i == 0 or seqs[i - 1] != s:
+                g0.append(i); gc.append(0)
+            gc[-1] += 1
+            assert gc[-1] <= 8
+            pos.append(nxt[s]); nxt[s] += 1
+        for s, n in nxt.items():
+            self.reserve(s, n)
+        t = lambda x: torch.tensor(x, dtype=torch.int32, device=self.dev)
+        self.ids[:m] = t(ids); self.tok_pos[:m] = t(pos); self.tok_seq[:m] = t(seqs)
+        self.grp_tok0[:len(g0)] = t(g0); self.grp_cnt[:len(g0)] = t(gc)
+        basic.embed(self.ids[:m], self.embed, self.ss_a, status=self.status, out=self.h_a[:m])
+        parts = self._layers_small(m, len(g0))
+        self._head_small(m, parts, want_logits)
+        for s, n in nxt.items():
+            self.seq_len_host[s] = n
+            self.seq_len[s] = n
+        return self.out_ids[:m].clone(), (self.logits[:m].clone() if want_logits else None)
+
+    # ------------------------------------------------------------------------------------------------ prefill
+    def _linear_big(self, lin: L.WqLinear, x: torch.Tensor) -> torch.Tensor:
+        """bf16 [T, n] = x @ dequant(W)^T for T > 32 rows."""
+        from ..ops import gemm as G
+        return G.wq_linear(lin, x, self)
+
+    def prefill(self, seq: int, ids: torch.Tensor, want_logits: bool = False):
+        """Chunked prefill of ``ids`` (1-D int tensor) appended to ``seq``; returns the greedy next token (int)."""
+        cfg = self.cfg
+        ids = ids.to(device=self.dev, dtype=torch.int32)
+        T = ids.numel()
+        start = self.seq_len_host[seq]
+        self.reserve(seq, start + T)
+        last = None
+        for c0 in range(0, T, self.prefill_chunk):
+            c1 = min(T, c0 + self.prefill_chunk)
+            last = self._prefill_chunk(seq, ids[c0:c1], start + c0, final=(c1 == T), want_logits=want_logits)
+            self.seq_len_host[seq] = start + c1
+            self.seq_len[seq] = start + c1
+        return last
+
+    def _prefill_chunk(self, seq: int, ids: torch.Tensor, pos0: int, final: bool, want_logits: bool):
+        cfg, dev = self.cfg, self.dev
+        T = ids.numel()
+        if T <= 8:
+            out, logits = self.forward_rows(ids.tolist(), [seq] * T, want_logits)
+            # forward_rows advanced the host length itself; undo so prefill() owns the bookkeeping
+            return (int(out[-1]), logits[-1] if logits is not None else None) if final else None
+        from ..ops import gemm as G
+        pos = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=dev)
+        seqv = torch.full((T,), seq, dtype=torch.int32, device=dev)
+        h = basic.embed(ids, self.embed, None, status=self.status)
+        q = torch.empty(T, cfg.q_dim, dtype=torch.bfloat16, device=dev)
+        delta = None
+        for li, d in enumerate(self.layers):
+            if delta is None:
+                x = basic.rmsnorm(h, d["ln1"], cfg.rms_eps)
+            else:
+                x, h = basic.rmsnorm(delta, d["ln1"], cfg.rms_eps, resid=h)
+            qkv = self._linear_big(d["qkv"], x)
+            basic.rope_kvstore(qkv, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, pos, seqv, self.block_table,
+                               self.kv[li], q, status=self.status)
+            a = A.attn_prefill(q, self.kv[li], self.block_table, seq, pos0, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
+                               status=self.status)
+            o = self._linear_big(d["o"], a)
+            x, h = basic.rmsnorm(o, d["ln2"], cfg.rms_eps, resid=h)
+            gu = self._linear_big(d["gate_up"], x)
+            act = basic.swiglu_interleaved(gu)
+            delta = self._linear_big(d["down"], act)
+        if not final:
+            return None
+        hl = (h[-1:].float() + delta[-1:].float()).to(torch.bfloat16)
+        self.h_a[:1] = hl
+        basic.sumsq(self.h_a[:1], self.ss_a)
+        self._head_small(1, 1, want_logits)
+        return int(self.out_ids[0]), (self.logits[0].clone() if want_logits else None)
+
+    # ------------------------------------------------------------------------------------------------ decode
+    def _decode_body(self, seqs: List[int]):
+        """One decode step for ``seqs`` (one row each): the token of the previous step is the input."""
+        m = len(seqs)
+        lib = _lib.cuda_lib()
+        check(lib.b2_decode_step_prep(m, ptr(self.last_ids), ptr(self.ids), ptr(self.seq_len), ptr(self.tok_pos),
+                                      ptr(self.tok_seq), ptr(self._slot_seq), current_stream()), "b2_decode_step_prep")
+        basic.embed(self.ids[:m], self.embed, self.ss_a, status=self.status, out=self.h_a[:m])
+        parts = self._layers_small(m, m)
+        self._head_small(m, parts, False)
+        self.last_ids[:m].copy_(self.out_ids[:m])
+
+    def decode_setup(self, seqs: List[int], first_tokens: List[int], n_steps: int):
+        """Prepare device state for ``n_steps`` graph-replayed decode steps of ``seqs``."""
+        m = len(seqs)
+        t = lambda x: torch.tensor(x, dtype=torch.int32, device=self.dev)
+        self._slot_seq = t(seqs)
+        self.last_ids[:m] = t(first_tokens)
+        self.grp_tok0[:m] = torch.arange(m, dtype=torch.int32, device=self.dev)
+        self.grp_cnt[:m] = 1
+        for s in seqs:
+            self.reserve(s, self.seq_len_host[s] + n_steps)
+        self._decode_seqs = list(seqs)
+
+    def decode_graph(self) -> torch.cuda.CUDAGraph:
+        key = tuple(self._decode_seqs)
+        g = self._graphs.get(key)
+        if g is None:
+            # warm-up on a side stream (lazy module loads, attribute calls), restoring the state it advanced
+            saved = (self.seq_len.clone(), self.last_ids.clone())
+            st = torch.cuda.Stream(device=self.dev)
+            st.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(st):
+                self._decode_body(self._decode_seqs)
+            torch.cuda.current_stream(self.dev).wait_stream(st)
+            torch.cuda.synchronize(self.dev)
+            self.seq_len.copy_(saved[0]); self.last_ids.copy_(saved[1])
+            self.ws.parity = 0
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                self._decode_body(self._decode_seqs)
+            self.seq_len.copy_(saved[0]); self.last_ids.copy_(saved[1])
+            self._graphs[key] = g
+        return g
+
+    def decode_steps(self, n_steps: int, collect: bool = True) -> Optional[torch.Tensor]:
+        """Replay the decode graph ``n_steps`` times; returns the produced tokens ``[n_steps, batch]``."""
+        g = self.decode_graph()
+        m = len(self._decode_seqs)
+        outs = torch.empty(n_steps, m, dtype=torch.int32, device=self.dev) if collect else None
+        for i in range(n_steps):
+            g.replay()
+            if collect:
+                outs[i].copy_(self.out_ids[:m])
+        for s in self._decode_seqs:
+            self.seq_len_host[s] += n_steps
+        return outs
+
+    def generate_greedy(self, seq: int, prompt: torch.Tensor, n_new: int) -> torch.Tensor:
+        """Prefill ``prompt`` into ``seq`` and decode ``n_new`` tokens greedily; returns them as a CPU tensor."""
+        first, _ = self.prefill(seq, prompt)
+        if n_new == 1:
+            return torch.tensor([first])
+        self.decode_setup([seq], [first], n_new - 1)
+        outs = self.decode_steps(n_new - 1)
+        torch.cuda.synchronize(self.dev)
+        st = int(self.status.item())
+        if st != 0 or int(self.ws.status.item()) != 0:
+            raise _lib.B2Error("decode", st or int(self.ws.status.item()))
+        return torch.cat([torch.tensor([first]), outs[:, 0].cpu().long()])
+
+    def step_host(self, tok_in: torch.Tensor, tok_out: torch.Tensor):
+        """Public step API: feed this step's input tokens from pinned host memory, run one decode step for the
+        sequences given to :meth:`decode_setup`, read the produced tokens back to pinned host memory."""
+        m = len(self._decode_seqs)
+        self.last_ids[:m].copy_(tok_in, non_blocking=True)
+        self.decode_graph().replay()
+        tok_out.copy_(self.out_ids[:m], non_blocking=True)
+        torch.cuda.current_stream(self.dev).synchronize()
+        for s in self._decode_seqs:
+            self.seq_len_host[s] += 1
+
+    def launches_per_step(self, batch: int = 1) -> int:
+        """Kernels of this package launched by one decode step (prep, embed, 7 per layer, lm_head, argmax)."""
+        return 2 + 7 * self.cfg.n_layers + 2

@@ -17,7 +17,7 @@ def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tenso
                 grp_cnt: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, hq: int, hkv: int, hd: int,
                 split_keys: int, max_splits: int, part_o: Optional[torch.Tensor] = None,
                 part_ml: Optional[torch.Tensor] = None, tree_mask: Optional[torch.Tensor] = None,
-                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q: bf16 [n_tok, hq*hd] (RoPE applied); kv_pool: bf16 [pages, 2, hkv, 16, hd].  Returns bf16 [n_tok, hq*hd]."""
     lib = _lib.cuda_lib()
     n_tok = q.shape[0]
@@ -26,7 +26,8 @@ def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tenso
         part_o = torch.empty(n_tok, hq, max_splits, hd, dtype=torch.float32, device=dev)
         part_ml = torch.empty(n_tok, hq, max_splits, 2, dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev) if status is None else status
-    out = torch.empty(n_tok, hq * hd, dtype=torch.bfloat16, device=dev)
+    if out is None:
+        out = torch.empty(n_tok, hq * hd, dtype=torch.bfloat16, device=dev)
     a = AttnDecodeArgs()
     a.q, a.ldq = ptr(q), q.stride(0)
     a.kv_pool, a.n_pages = ptr(kv_pool), kv_pool.shape[0]
@@ -44,3 +45,17 @@ def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tenso
     with torch.cuda.device(dev):
         check(lib.b2_attn_decode(C.byref(a), hd, current_stream()), "b2_attn_decode")
     return out
+
+
+def attn_prefill(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tensor, seq: int, pos0: int, hq: int,
+                 hkv: int, hd: int, status: Optional[torch.Tensor] = None, split_keys: int = 256) -> torch.Tensor:
+    """Causal attention of a prefill chunk (``q``: bf16 ``[T, hq*hd]`` at positions ``pos0 .. pos0+T-1`` of ``seq``)
+    over the paged KV cache, which already holds the chunk's own K/V."""
+    dev = q.device
+    T = q.shape[0]
+    pos = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=dev)
+    seqv = torch.full((T,), seq, dtype=torch.int32, device=dev)
+    g0 = torch.arange(0, T, 8, dtype=torch.int32, device=dev)
+    gc = torch.clamp(T - g0, max=8).to(torch.int32)
+    max_splits = (pos0 + T + split_keys - 1) // split_keys
+    return attn_decode(q, kv_pool, block_table, g0, gc, pos, seqv, hq, hkv, hd, split_keys, max_splits, status=status)

@@ -15,13 +15,13 @@ def _status(dev) -> torch.Tensor:
 
 def embed(ids: torch.Tensor, table: torch.Tensor, ss: Optional[torch.Tensor] = None,
           sub_rows: Optional[torch.Tensor] = None, sub_index: Optional[torch.Tensor] = None,
-          status: Optional[torch.Tensor] = None) -> torch.Tensor:
+          status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     lib = _lib.cuda_lib()
     n, d = ids.numel(), table.shape[1]
-    h = torch.empty(n, d, dtype=torch.bfloat16, device=table.device)
+    h = torch.empty(n, d, dtype=torch.bfloat16, device=table.device) if out is None else out
     status = _status(table.device) if status is None else status
     with torch.cuda.device(table.device):
-        check(lib.b2_embed(ptr(ids), n, ptr(table), d, table.shape[0], ptr(sub_rows), ptr(sub_index), ptr(h), d, ptr(ss),
+        check(lib.b2_embed(ptr(ids), n, ptr(table), d, table.shape[0], ptr(sub_rows), ptr(sub_index), ptr(h), h.stride(0), ptr(ss),
                            ptr(status), current_stream()), "b2_embed")
     return h
 

@@ -86,10 +86,11 @@ class WqLinear:
     def n_panels(self) -> int:
         return (self.n // 16 + 1) // 2
 
-    def dequant(self) -> torch.Tensor:
+    def dequant(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """bf16 [n, k] on the device (kernel path)."""
         lib = _lib.cuda_lib()
-        out = torch.empty(self.n, self.k, dtype=torch.bfloat16, device=self.wq.device)
+        if out is None:
+            out = torch.empty(self.n, self.k, dtype=torch.bfloat16, device=self.wq.device)
         with torch.cuda.device(out.device):
             check(lib.b2_wq_dequant(ptr(self.wq), ptr(self.sz), self.n, self.k, self.bits, self.group, ptr(out), self.k,
                                     current_stream()), "b2_wq_dequant")
