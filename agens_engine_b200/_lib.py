@@ -79,10 +79,10 @@ class TpPush(C.Structure):
 
 class WqGemvArgs(C.Structure):
     _fields_ = [
-        ("wq", C.c_void_p), ("sz", C.c_void_p),
+        ("wq", C.c_void_p),
         ("n", C.c_int), ("k", C.c_int), ("m", C.c_int),
         ("bits", C.c_int), ("group", C.c_int),
-        ("ks", C.c_int),
+        ("ks", C.c_int), ("rb", C.c_int),
         ("pro", C.c_int),
         ("x", C.c_void_p), ("ldx", C.c_long),
         ("ss_in", C.c_void_p), ("ss_parts", C.c_int), ("ss_ld", C.c_int),
@@ -94,8 +94,8 @@ class WqGemvArgs(C.Structure):
         ("yf", C.c_void_p),
         ("amax_val", C.c_void_p), ("amax_idx", C.c_void_p), ("n_valid", C.c_int),
         ("scratch", C.c_void_p), ("counters", C.c_void_p),
-        ("tickets", C.c_void_p), ("ticket_parity", C.c_int),
         ("status", C.c_void_p),
+        ("debug", C.c_int),
         ("tp", TpPush),
     ]
 
@@ -127,9 +127,10 @@ def _declare(lib: C.CDLL):
     sig = {
         "b2_wq_gemv": ([C.POINTER(WqGemvArgs), vp], i),
         "b2_wq_gemv_scratch_floats": ([i, i, i], l),
-        "b2_wq_dequant": ([vp, vp, i, i, i, i, vp, l, vp], i),
-        "b2_wq_repack": ([vp, vp, i, vp, i, i, i, i, vp, vp, vp], i),
-        "b2_wq_random": ([vp, vp, i, i, i, i, f, C.c_ulonglong, vp], i),
+        "b2_wq_bytes": ([i, i, i, i], l),
+        "b2_wq_dequant": ([vp, i, i, i, i, vp, l, vp], i),
+        "b2_wq_repack": ([vp, vp, i, vp, i, i, i, i, vp, vp], i),
+        "b2_wq_random": ([vp, i, i, i, i, f, C.c_ulonglong, vp], i),
         "b2_embed": ([vp, i, vp, i, i, vp, vp, vp, l, vp, vp, vp], i),
         "b2_rmsnorm": ([vp, l, vp, l, vp, l, vp, f, i, i, vp, l, vp], i),
         "b2_sumsq": ([vp, l, i, i, vp, vp], i),

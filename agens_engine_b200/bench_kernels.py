@@ -93,12 +93,12 @@ def bench_gemv(args):
     for name, n, k in shapes:
         for bits in ([4] if name == "lm_head" else [2, 3, 4]):
             for _ in (0,):
-                ks_list = sorted({L.choose_ks(n, k), L.choose_ks(n, k, 2560), L.choose_ks(n, k, 512)})
+                ks_list = sorted({L.choose_ks(n, k), L.choose_ks(n, k, 2560), L.choose_ks(n, k, 512), L.choose_ks(n, k, 640)})
                 for ks in ks_list:
                     lin = L.WqLinear.random(n, k, bits, 128, dev, seed=1, ks=ks)
-                    nbytes = lin.wq.numel() + lin.sz.numel() * 2
+                    nbytes = lin.nbytes()
                     ncopy = max(2, min(24, (512 << 20) // nbytes + 1))   # rotate over > 512 MiB of weights: L2 stays cold
-                    lins = [lin] + [L.WqLinear(n, k, bits, 128, lin.wq.clone(), lin.sz.clone(), ks)
+                    lins = [lin] + [L.WqLinear(n, k, bits, 128, lin.wq.clone(), ks, lin.rb)
                                     for _ in range(ncopy - 1)]
                     x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
                     out = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)

@@ -92,10 +92,10 @@ class DenseModel:
         return m.finalize()
 
     def weight_bytes(self) -> int:
-        t = self.embed.numel() * 2 + self.lm_head.wq.numel() + self.lm_head.sz.numel() * 2
+        t = self.embed.numel() * 2 + self.lm_head.nbytes()
         for d in self.layers:
             for lin in LINEARS:
-                t += d[lin].wq.numel() + d[lin].sz.numel() * 2
+                t += d[lin].nbytes()
         return t
 
     # ------------------------------------------------------------------------------------------------ buffers
@@ -120,7 +120,7 @@ class DenseModel:
         self.act = bf(M, cfg.ffn)
         self.part_o = torch.empty(M, cfg.n_heads, self.max_splits, cfg.head_dim, dtype=torch.float32, device=dev)
         self.part_ml = torch.empty(M, cfg.n_heads, self.max_splits, 2, dtype=torch.float32, device=dev)
-        lm_panels = (cfg.vocab // 16 + 1) // 2
+        lm_panels = cfg.vocab // 32
         self.amax_val = torch.empty(lm_panels, L.SS_LD, dtype=torch.float32, device=dev)
         self.amax_idx = torch.empty(lm_panels, L.SS_LD, dtype=torch.int32, device=dev)
         self.logits = torch.empty(M, cfg.vocab, dtype=torch.float32, device=dev)
@@ -324,7 +324,6 @@ class DenseModel:
             torch.cuda.current_stream(self.dev).wait_stream(st)
             torch.cuda.synchronize(self.dev)
             self.seq_len.copy_(saved[0]); self.last_ids.copy_(saved[1])
-            self.ws.parity = 0
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g, stream=st):
                 self._decode_body(self._decode_seqs)

@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import ctypes as C
 import dataclasses
+import os
 from typing import Optional
 
 import torch
@@ -18,8 +19,15 @@ from ..utils import quant
 SS_LD = 64   # token stride of partial-sum-of-squares / argmax-partial buffers
 
 
-def fm_bytes(n: int, k: int, bits: int) -> int:
-    return (n // 16) * (k // quant.chunk_k(bits)) * quant.record_bytes(bits)
+def fm_bytes(n: int, k: int, bits: int, group: int) -> int:
+    return (n // 32) * (k // 128) * quant.block_bytes(bits, group)
+
+
+def choose_rb(n: int) -> int:
+    """Row blocks per warp item: 64-row items when the matrix has enough rows to keep every warp busy."""
+    if os.environ.get("B200E_GEMV_RB"):
+        return int(os.environ["B200E_GEMV_RB"])
+    return 4 if n >= 16384 else 2
 
 
 def choose_ks(n: int, k: int, slice_k: int = 1024) -> int:
@@ -42,27 +50,26 @@ class WqLinear:
     k: int
     bits: int
     group: int
-    wq: torch.Tensor            # uint8 [fm_bytes]
-    sz: torch.Tensor            # fp16 [n/16, k/group, 16, 2]
+    wq: torch.Tensor            # uint8 [fm_bytes]: (32-row panel, 128-k batch) blocks, scales inside
     ks: int = 1
+    rb: int = 2
 
     @staticmethod
     def from_quant(ql: quant.QuantLinear, device, ks: Optional[int] = None) -> "WqLinear":
-        wq, sz = quant.pack_fm(ql)
+        wq = quant.pack_fm(ql)
         ks = ks or choose_ks(ql.n, ql.k)
-        return WqLinear(ql.n, ql.k, ql.bits, ql.group, wq.reshape(-1).to(device), sz.to(device), ks)
+        return WqLinear(ql.n, ql.k, ql.bits, ql.group, wq.reshape(-1).to(device), ks, choose_rb(ql.n))
 
     @staticmethod
     def random(n: int, k: int, bits: int, group: int, device, seed: int, stddev: float = 0.02,
                ks: Optional[int] = None) -> "WqLinear":
         """Random-init N(0, stddev) weights quantised on the device directly into FM form."""
         lib = _lib.cuda_lib()
-        wq = torch.empty(fm_bytes(n, k, bits), dtype=torch.uint8, device=device)
-        sz = torch.empty(n // 16, k // group, 16, 2, dtype=torch.float16, device=device)
+        wq = torch.empty(fm_bytes(n, k, bits, group), dtype=torch.uint8, device=device)
         with torch.cuda.device(device):
-            check(lib.b2_wq_random(ptr(wq), ptr(sz), n, k, bits, group, stddev, seed, current_stream()), "b2_wq_random")
+            check(lib.b2_wq_random(ptr(wq), n, k, bits, group, stddev, seed, current_stream()), "b2_wq_random")
         ks = ks or choose_ks(n, k)
-        return WqLinear(n, k, bits, group, wq, sz, ks)
+        return WqLinear(n, k, bits, group, wq, ks, choose_rb(n))
 
     @staticmethod
     def from_checkpoint(packed: torch.Tensor, scale: torch.Tensor, zero: Optional[torch.Tensor], n: int, k: int,
@@ -72,19 +79,21 @@ class WqLinear:
         packed = packed.to(device).contiguous()
         scale = scale.to(device).contiguous()
         zero = None if zero is None else zero.to(device=device, dtype=torch.float16).contiguous()
-        wq = torch.empty(fm_bytes(n, k, bits), dtype=torch.uint8, device=device)
-        sz = torch.empty(n // 16, k // group, 16, 2, dtype=torch.float16, device=device)
+        wq = torch.empty(fm_bytes(n, k, bits, group), dtype=torch.uint8, device=device)
         is_bf16 = 1 if scale.dtype == torch.bfloat16 else 0
         if not is_bf16 and scale.dtype != torch.float16:
             scale = scale.to(torch.float16)
         with torch.cuda.device(device):
-            check(lib.b2_wq_repack(ptr(packed), ptr(scale), is_bf16, ptr(zero), n, k, bits, group, ptr(wq), ptr(sz),
+            check(lib.b2_wq_repack(ptr(packed), ptr(scale), is_bf16, ptr(zero), n, k, bits, group, ptr(wq),
                                    current_stream()), "b2_wq_repack")
         ks = ks or choose_ks(n, k)
-        return WqLinear(n, k, bits, group, wq, sz, ks)
+        return WqLinear(n, k, bits, group, wq, ks, choose_rb(n))
 
     def n_panels(self) -> int:
-        return (self.n // 16 + 1) // 2
+        return self.n // 32
+
+    def nbytes(self) -> int:
+        return self.wq.numel()
 
     def dequant(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """bf16 [n, k] on the device (kernel path)."""
@@ -92,31 +101,23 @@ class WqLinear:
         if out is None:
             out = torch.empty(self.n, self.k, dtype=torch.bfloat16, device=self.wq.device)
         with torch.cuda.device(out.device):
-            check(lib.b2_wq_dequant(ptr(self.wq), ptr(self.sz), self.n, self.k, self.bits, self.group, ptr(out), self.k,
+            check(lib.b2_wq_dequant(ptr(self.wq), self.n, self.k, self.bits, self.group, ptr(out), self.k,
                                     current_stream()), "b2_wq_dequant")
         return out
 
     def dequant_cpu(self) -> torch.Tensor:
         """fp32 [n, k] computed on the CPU from the FM bytes (independent of every kernel)."""
-        ql = quant.unpack_fm(self.wq.cpu().reshape(self.n // 16, -1, quant.record_bytes(self.bits)), self.sz.cpu(),
-                             self.bits, self.n, self.k, self.group)
+        ql = quant.unpack_fm(self.wq.cpu(), self.bits, self.n, self.k, self.group)
         return ql.dequant()
 
 
 class GemvWorkspace:
-    """Split-k scratch, self-resetting panel counters and the two alternating sets of work tickets shared by the
-    GEMV launches of one stream."""
+    """Split-k scratch, self-resetting item counters and the status word shared by the GEMV launches of one stream."""
 
     def __init__(self, device, floats: int = 4 << 20, panels: int = 1 << 16):
         self.scratch = torch.empty(floats, dtype=torch.float32, device=device)
         self.counters = torch.zeros(panels, dtype=torch.int32, device=device)
-        self.tickets = torch.zeros(2 * (_lib.K_MAX_KS + 1), dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.parity = 0
-
-    def next_parity(self) -> int:
-        self.parity ^= 1
-        return self.parity
 
 
 def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STORE,
@@ -131,9 +132,9 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
     assert x.dtype == torch.bfloat16 and x.shape[1] == lin.k and x.stride(1) == 1
     dev = x.device
     a = WqGemvArgs()
-    a.wq, a.sz = ptr(lin.wq), ptr(lin.sz)
+    a.wq = ptr(lin.wq)
     a.n, a.k, a.m = lin.n, lin.k, m
-    a.bits, a.group, a.ks = lin.bits, lin.group, lin.ks
+    a.bits, a.group, a.ks, a.rb = lin.bits, lin.group, lin.ks, (lin.rb if m <= 16 else 2)
     a.pro = pro
     a.x, a.ldx = ptr(x), x.stride(0)
     a.ss_in, a.ss_parts, a.ss_ld = ptr(ss_in), ss_parts, SS_LD
@@ -163,8 +164,8 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
         need = lib.b2_wq_gemv_scratch_floats(lin.n, lin.ks, m)
         assert need <= ws.scratch.numel() and lin.n_panels() <= ws.counters.numel()
         a.scratch, a.counters = ptr(ws.scratch), ptr(ws.counters)
-    a.tickets, a.ticket_parity = ptr(ws.tickets), ws.next_parity()
     a.status = ptr(ws.status)
+    a.debug = int(os.environ.get("B200E_GEMV_DEBUG", "0"))
     if tp is not None:
         a.tp = tp
     with torch.cuda.device(dev):

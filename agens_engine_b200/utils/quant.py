@@ -10,7 +10,10 @@ Two layouts exist for one quantised linear ``W[n, k]``:
   ``[n, k/group]`` in code units.  ``w = scale * (code - zero)``; symmetric tensors use ``zero = 2**(bits-1)``.
 
 * **FM (fragment-major) kernel layout**, consumed by ``csrc/kernels/sm100/wq_gemv.cu``.  Rows are cut into blocks
-  of 16, k into chunks (64 codes for 4 bits, 128 for 2 and 3 bits).  One chunk of one row block is a record of
+  of 16, k into chunks (64 codes for 4 bits, 128 for 2 and 3 bits).  The tensor is stored panel-major: for every
+  panel of 32 rows and every batch of 128 k one contiguous block holds the records of its two row blocks followed by
+  their (scale, zero) pairs, so one bulk copy brings everything a warp needs for that tile.  One chunk of one row
+  block is a record of
   ``32 lanes x 16 B`` (plus ``32 x 8 B`` of high bits for 3-bit tensors) in which lane ``(g, t)`` (``g = lane >> 2``,
   ``t = lane & 3``) finds exactly the codes of rows ``g`` and ``g + 8`` that its ``mma.m16n8k16`` A fragments need,
   positioned so that a single ``lop3`` turns two codes into two fp16 numbers ``1024 + c * code``.  The power of two
@@ -20,7 +23,7 @@ Two layouts exist for one quantised linear ``W[n, k]``:
 from __future__ import annotations
 
 import dataclasses
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 
@@ -176,11 +179,20 @@ def slot_scales(bits: int) -> torch.Tensor:
     return out
 
 
-def pack_fm(ql: QuantLinear) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Checkpoint codes -> FM layout.  Returns ``(wq uint8 [n/16, k/CK, record_bytes], sz fp16 [n/16, k/group, 16, 2])``."""
+def w_batch_bytes(bits: int) -> int:
+    """Weight bytes of one 128-k batch of one 16-row block."""
+    return (128 // chunk_k(bits)) * record_bytes(bits)
+
+
+def block_bytes(bits: int, group: int) -> int:
+    """Bytes of one (32-row panel, 128-k batch) block: two row blocks of records + their (scale, zero) pairs."""
+    return 2 * w_batch_bytes(bits) + 2 * (128 // group) * 64
+
+
+def _records(ql: QuantLinear) -> torch.Tensor:
+    """uint8 [n/16, k/CK, record_bytes]: the per-(row block, chunk) records."""
     n, k, bits = ql.n, ql.k, ql.bits
     ck = chunk_k(bits)
-    assert n % 16 == 0 and k % ck == 0 and k % ql.group == 0
     nrb, nch = n // 16, k // ck
     codes = ql.codes.to(torch.int64).cpu().reshape(nrb, 16, nch, ck // 16, 4, 4)   # rb, row, chunk, step, t, slot
     lanes_g = torch.arange(32) >> 2
@@ -206,20 +218,39 @@ def pack_fm(ql: QuantLinear) -> Tuple[torch.Tensor, torch.Tensor]:
     for w in rec:                                                 # [nrb, nch, 32, W] -> bytes little endian
         w8 = torch.stack([(w >> (8 * b)) & 0xFF for b in range(4)], dim=-1).to(torch.uint8)
         flat.append(w8.reshape(nrb, nch, -1))
-    wq = torch.cat(flat, dim=-1).contiguous()
-    assert wq.shape[-1] == record_bytes(bits)
-    ng = k // ql.group
-    s = ql.scale.cpu().reshape(nrb, 16, ng).permute(0, 2, 1)
-    z = ql.zero.cpu().reshape(nrb, 16, ng).permute(0, 2, 1)
-    sz = torch.stack([s, z], dim=-1).to(torch.float16).contiguous()   # [nrb, ng, 16, 2]
-    return wq, sz
+    out = torch.cat(flat, dim=-1).contiguous()
+    assert out.shape[-1] == record_bytes(bits)
+    return out
 
 
-def unpack_fm(wq: torch.Tensor, sz: torch.Tensor, bits: int, n: int, k: int, group: int) -> QuantLinear:
+def pack_fm(ql: QuantLinear) -> torch.Tensor:
+    """Checkpoint codes -> FM layout: uint8 ``[n/32, k/128, block_bytes]``."""
+    n, k, bits, group = ql.n, ql.k, ql.bits, ql.group
+    assert n % 32 == 0 and k % 128 == 0 and k % group == 0
+    rec = _records(ql)                                            # [n/16, k/CK, REC]
+    rpb = 128 // chunk_k(bits)
+    npan, nbat = n // 32, k // 128
+    w = rec.reshape(npan, 2, nbat, rpb * record_bytes(bits)).permute(0, 2, 1, 3).reshape(npan, nbat, -1)
+    gpb = 128 // group
+    sz = torch.stack([ql.scale.cpu(), ql.zero.cpu()], dim=-1).to(torch.float16)        # [n, ng, 2]
+    sz = sz.reshape(npan, 2, 16, nbat, gpb, 2).permute(0, 3, 1, 4, 2, 5).contiguous()  # pan, bat, rb, g, row, (s,z)
+    szb = sz.view(torch.uint8).reshape(npan, nbat, 2 * gpb * 64)
+    out = torch.cat([w, szb], dim=-1).contiguous()
+    assert out.shape[-1] == block_bytes(bits, group)
+    return out
+
+
+def unpack_fm(wq: torch.Tensor, bits: int, n: int, k: int, group: int) -> QuantLinear:
     """Inverse of :func:`pack_fm` (used by tests and by the dequant oracle)."""
     ck = chunk_k(bits)
+    rpb, gpb = 128 // ck, 128 // group
+    npan, nbat = n // 32, k // 128
+    blk = wq.cpu().reshape(npan, nbat, block_bytes(bits, group))
+    wb = 2 * w_batch_bytes(bits)
+    rec = blk[:, :, :wb].reshape(npan, nbat, 2, rpb, record_bytes(bits)).permute(0, 2, 1, 3, 4)
+    rec = rec.reshape(n // 16, k // ck, record_bytes(bits))
     nrb, nch = n // 16, k // ck
-    b = wq.cpu().to(torch.int64).reshape(nrb, nch, -1)
+    b = rec.to(torch.int64)
     lo = b[:, :, :512].reshape(nrb, nch, 32, 4, 4)
     words = sum(lo[..., i] << (8 * i) for i in range(4))          # [nrb, nch, 32, 4]
     codes = torch.zeros(nrb, 16, nch, ck // 16, 4, 4, dtype=torch.int64)
@@ -238,11 +269,10 @@ def unpack_fm(wq: torch.Tensor, sz: torch.Tensor, bits: int, n: int, k: int, gro
             rows = lanes_g + 8 * row_half
             v = ((hi[:, :, :, hword] >> bit) & 1) << 2
             codes[:, rows, :, step, lanes_t, slot] |= v.permute(2, 0, 1)
-    ng = k // group
-    s = sz[..., 0].cpu().permute(0, 2, 1).reshape(n, ng)
-    z = sz[..., 1].cpu().permute(0, 2, 1).reshape(n, ng)
+    szb = blk[:, :, wb:].contiguous().view(torch.float16).reshape(npan, nbat, 2, gpb, 16, 2)
+    sz = szb.permute(0, 2, 4, 1, 3, 5).reshape(n, k // group, 2)
     return QuantLinear(n=n, k=k, bits=bits, group=group, codes=codes.reshape(n, k).to(torch.uint8),
-                       scale=s.contiguous(), zero=z.contiguous())
+                       scale=sz[..., 0].contiguous(), zero=sz[..., 1].contiguous())
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:

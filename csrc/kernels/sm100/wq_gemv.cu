@@ -35,21 +35,18 @@ struct WFrag {
   uint32_t sz[GPB][2];      // half2 (scale, zero) for rows g and g+8
 };
 
-// Shared-memory ring of one warp.  A stage holds kBps consecutive 128-k batches of RB row blocks, brought in by
-// cp.async.bulk copies (one per row block for the weights, one for the scale/zero pairs) that complete on the
-// stage's mbarrier.  Every warp runs its own ring, so the CTA never synchronises inside the k loop.
-constexpr int kBps = 2;     // batches per stage
-constexpr int kStages = 3;  // ring depth
-
+// Geometry of the FM buffer and of a warp's shared-memory ring.  The buffer is a grid of blocks, one per (32-row
+// panel, 128-k batch): [2 row blocks x records][2 row blocks x groups x 16 rows x (scale, zero)].  A ring stage holds
+// the RB/2 blocks of one batch of a warp item and is filled by RB/2 cp.async.bulk copies that complete on the
+// stage's mbarrier.  Every warp runs its own ring, so nothing inside the k loop synchronises the CTA.
 template <int BITS, int GROUP, int RB>
 struct Ring {
   static constexpr int RPB = 128 / Fmt<BITS>::CK;
   static constexpr int GPB = 128 / GROUP;
   static constexpr int W_BATCH = RPB * Fmt<BITS>::REC;     // weight bytes of one batch of one row block
-  static constexpr int SZ_BATCH = GPB * 64;                 // scale/zero bytes of one batch of one row block
-  static constexpr int W_BYTES = kBps * W_BATCH;
-  static constexpr int SZ_BYTES = kBps * SZ_BATCH;
-  static constexpr int STAGE = RB * (W_BYTES + SZ_BYTES);
+  static constexpr int BLK = 2 * W_BATCH + 2 * GPB * 64;    // one (panel, batch) block
+  static constexpr int STAGE = (RB / 2) * BLK;
+  static constexpr int NST = BITS == 4 ? 3 : (BITS == 3 ? 4 : 5);   // ring depth: about 13 KB in flight per warp
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -153,87 +150,77 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v))
 
 }  // namespace
 
-constexpr int kRB = 2;   // row blocks per panel: 32 rows, one row per lane in the epilogue
 
-// Persistent kernel.  CTA c works on k slice (c % ks) of every panel; its four warps pull panels of that slice from
-// a ticket counter, so a warp item is (panel of 32 rows, k slice) and nothing inside the k loop synchronises the
-// CTA.  The activation slice is staged once per CTA.  Partial results of the ks slices of a panel meet in
-// scratch memory; the warp that arrives last sums them in slice order and runs the epilogue.
-template <int BITS, int GROUP, int NT>
+// Persistent kernel.  CTA c works on k slice (c % ks) of every item; its eight warps pull items of that slice from
+// a ticket counter.  A warp item is (16*RB rows, k slice); the activation slice is staged once per CTA; partial
+// results of the ks slices of an item meet in scratch memory, and the warp that arrives last sums them in slice
+// order and runs the epilogue with one or two rows per lane.
+template <int BITS, int GROUP, int RB, int NT>
 __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs a) {
-  constexpr int CK = Fmt<BITS>::CK;
   constexpr int GPB = 128 / GROUP;
-  constexpr int RB = kRB;
   constexpr int MP = NT * 8;
+  constexpr int ROWS = RB * 16;
+  constexpr int RPL = RB / 2;                   // rows per lane in the epilogue
   using R = Ring<BITS, GROUP, RB>;
+  constexpr int NST = R::NST;
 
   extern __shared__ __align__(128) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int m = a.m;
-  const int nrb = a.n >> 4;
-  const int npanels = (nrb + RB - 1) / RB;
-  const int nch = a.k / CK;
-  const int ng = a.k / GROUP;
-  const int nu = a.k >> 7;
+  const int npan = a.n >> 5;                    // 32-row panels of the FM buffer
+  const int nitems = (npan + RPL - 1) / RPL;
+  const int nbat = a.k >> 7;
   const int ks = a.ks;
   const int slice = blockIdx.x % ks;
-  const int u0 = (int)(((long)nu * slice) / ks);
-  const int u1 = (int)(((long)nu * (slice + 1)) / ks);
-  const int nb = u1 - u0;                       // 128-k batches of this CTA's slice
-  const int nst = (nb + kBps - 1) / kBps;       // ring stages per item
-  const int nb_max = (nu + ks - 1) / ks;
+  const int u0 = (int)(((long)nbat * slice) / ks);
+  const int u1 = (int)(((long)nbat * (slice + 1)) / ks);
+  const int nb = u1 - u0;                       // 128-k batches of this CTA's slice = ring stages per item
+  const int nb_max = (nbat + ks - 1) / ks;
   const int XST = nb_max * 128 + 16;            // halfs per staged token row (row pitch = 32 B mod 128 B)
 
-  // shared memory: [4 rings][mbarriers][inv_rms][4 x fin][xs][gsum]
-  uint8_t* ring = smem_raw + (size_t)warp * kStages * R::STAGE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)4 * kStages * R::STAGE) + warp * kStages;
-  float* inv_rms = reinterpret_cast<float*>(smem_raw + (size_t)4 * kStages * R::STAGE + 4 * kStages * 8);
-  float* fin = inv_rms + MP + (size_t)warp * MP * 32;                        // [MP][32] per warp
-  __half* xs = reinterpret_cast<__half*>(inv_rms + MP + 4 * MP * 32);        // [m][XST]
-  float2* gsum = reinterpret_cast<float2*>(xs + (size_t)m * XST);            // [nb_max * GPB][MP]
+  // shared memory: [8 rings][mbarriers][inv_rms][8 x fin][xs][gsum]
+  uint8_t* ring = smem_raw + (size_t)warp * NST * R::STAGE;
+  uint8_t* after = smem_raw + (size_t)kGemvWarps * NST * R::STAGE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after) + warp * NST;
+  float* inv_rms = reinterpret_cast<float*>(after + kGemvWarps * NST * 8);
+  float* fin = inv_rms + 32 + (size_t)warp * m * ROWS;                                   // [m][ROWS] per warp
+  __half* xs = reinterpret_cast<__half*>(inv_rms + 32 + (size_t)kGemvWarps * m * ROWS);   // [m][XST]
+  float2* gsum = reinterpret_cast<float2*>(xs + (size_t)m * XST);                         // [nb_max * GPB][MP]
 
   const uint32_t ring_u = smem_u32(ring);
   const uint32_t bars_u = smem_u32(bars);
-  unsigned* tickets = a.tickets + (size_t)a.ticket_parity * (kMaxKs + 1);
+  // Static schedule: the warps of the CTAs that share a slice take items round robin.  Items are equal in size and
+  // the launcher sizes the grid so that every warp gets the same number of them (give or take one).
+  const int wstride = (gridDim.x / ks) * kGemvWarps;
+  const int wfirst = (blockIdx.x / ks) * kGemvWarps + warp;
 
-  // ---- producer state (lane 0): panels cur / nxt / nx2 and a cursor (which item, which stage) ----
-  unsigned t_cur = 0, t_nxt = 0, t_nx2 = 0;
   if (lane == 0) {
 #pragma unroll
-    for (int i = 0; i < kStages; ++i) mbar_init(bars_u + i * 8, 1);
+    for (int i = 0; i < NST; ++i) mbar_init(bars_u + i * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    t_cur = atomicAdd(tickets + slice, 1u);
-    t_nxt = atomicAdd(tickets + slice, 1u);
-    t_nx2 = atomicAdd(tickets + slice, 1u);
   }
   unsigned prod = 0, cons = 0;     // stages issued / consumed by this warp since kernel start
-  int p_which = 0, p_st = 0;       // producer cursor: item (0 = cur, 1 = nxt) and stage inside it
-  auto issue_one = [&]() -> bool { // lane 0 only; returns false when nothing can be issued now
-    if (p_which > 1) return false;
-    const unsigned panel = p_which == 0 ? t_cur : t_nxt;
-    if (panel >= (unsigned)npanels) return false;
-    const int slot = prod % kStages;
-    const int b0 = p_st * kBps;
-    const int nbs = min(kBps, nb - b0);
+  int p_item = wfirst, p_b = 0;    // producer cursor: item and batch inside it (may run ahead into the next item)
+  auto issue_one = [&]() -> bool { // lane 0 only; returns false when nothing is left to issue
+    const int item = p_item;
+    if (item >= nitems) return false;
+    const int slot = prod % NST;
     const uint32_t bar = bars_u + slot * 8;
-    mbar_expect_tx(bar, (uint32_t)(RB * nbs * (R::W_BATCH + R::SZ_BATCH)));
+    mbar_expect_tx(bar, (uint32_t)R::STAGE);
     const uint32_t dst = ring_u + slot * R::STAGE;
 #pragma unroll
-    for (int r = 0; r < RB; ++r) {
-      const int rb = min((int)panel * RB + r, nrb - 1);   // tail panel: duplicate the last block, ignored later
-      const uint8_t* wsrc = a.wq + ((size_t)rb * nch + (size_t)(u0 + b0) * R::RPB) * Fmt<BITS>::REC;
-      bulk_g2s(dst + r * R::W_BYTES, wsrc, (uint32_t)(nbs * R::W_BATCH), bar);
-      const uint8_t* ssrc = reinterpret_cast<const uint8_t*>(a.sz) + ((size_t)rb * ng + (size_t)(u0 + b0) * GPB) * 64;
-      bulk_g2s(dst + RB * R::W_BYTES + r * R::SZ_BYTES, ssrc, (uint32_t)(nbs * R::SZ_BATCH), bar);
+    for (int pi = 0; pi < RPL; ++pi) {
+      const int pan = min(item * RPL + pi, npan - 1);   // tail item: duplicate the last panel, ignored later
+      bulk_g2s(dst + pi * R::BLK, a.wq + ((size_t)pan * nbat + (u0 + p_b)) * R::BLK, (uint32_t)R::BLK, bar);
     }
     ++prod;
-    if (++p_st == nst) { p_st = 0; ++p_which; }
+    if (++p_b == nb) { p_b = 0; p_item += wstride; }
     return true;
   };
   // Weights do not depend on the previous kernel: start streaming before the dependency wait.
   if (lane == 0 && nb > 0) {
-    while (prod - cons < (unsigned)kStages && issue_one()) { }
+    while (prod - cons < (unsigned)NST && issue_one()) { }
   }
   __syncwarp();
   pdl_wait();
@@ -241,7 +228,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
 
   // ---- stage the activation slice of this CTA: fp16(x / c) and the per-group sums ----
   if (a.pro == PRO_NORM) {
-    for (int tok = warp; tok < m; tok += 4) {
+    for (int tok = warp; tok < m; tok += kGemvWarps) {
       float s = 0.f;
       for (int p = lane; p < a.ss_parts; p += 32) s += a.ss_in[(size_t)p * a.ss_ld + tok];
       s = warp_sum(s);
@@ -295,9 +282,8 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
   }
   __syncthreads();
 
-  unsigned cur = __shfl_sync(0xffffffffu, t_cur, 0);
   bool failed = false;
-  while (cur < (unsigned)npanels && nb > 0 && !failed) {
+  for (int cur = wfirst; cur < nitems && nb > 0 && !failed; cur += wstride) {
     float y[RB][NT][4];
 #pragma unroll
     for (int r = 0; r < RB; ++r)
@@ -306,67 +292,78 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
 #pragma unroll
         for (int i = 0; i < 4; ++i) y[r][n][i] = 0.f;
 
-    for (int st = 0; st < nst; ++st) {
-      const int slot = cons % kStages;
-      if (!mbar_wait_bounded(bars_u + slot * 8, (cons / kStages) & 1u)) {
+#pragma unroll 1
+    for (int b = 0; b < nb; ++b) {
+      const int slot = cons % NST;
+      if (!mbar_wait_bounded(bars_u + slot * 8, (cons / NST) & 1u)) {
         if (a.status) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
         failed = true;
         break;
       }
-      const int nbs = min(kBps, nb - st * kBps);
-#pragma unroll 1
-      for (int bb = 0; bb < nbs; ++bb) {
-        const int b = st * kBps + bb;
-        WFrag<BITS, GROUP> cf[RB];
+      const uint8_t* stg = ring + slot * R::STAGE;
+      if (a.debug == 1) {   // measurement aid: stream the weights, skip the arithmetic
+        y[0][0][0] += (float)stg[lane];
+        __syncwarp();
+        ++cons;
+        if (lane == 0) {
+          while (prod - cons < (unsigned)NST && issue_one()) { }
+        }
+        continue;
+      }
+      WFrag<BITS, GROUP> cf[RB];
 #pragma unroll
-        for (int r = 0; r < RB; ++r)
-          load_frag_smem<BITS, GROUP>(cf[r], ring + slot * R::STAGE + r * R::W_BYTES + bb * R::W_BATCH,
-                                      ring + slot * R::STAGE + RB * R::W_BYTES + r * R::SZ_BYTES + bb * R::SZ_BATCH, lane);
+      for (int r = 0; r < RB; ++r)
+        load_frag_smem<BITS, GROUP>(cf[r], stg + (r >> 1) * R::BLK + (r & 1) * R::W_BATCH,
+                                    stg + (r >> 1) * R::BLK + 2 * R::W_BATCH + (r & 1) * GPB * 64, lane);
+      const __half* xrow = xs + b * 128 + t * 4;
 #pragma unroll
-        for (int gg = 0; gg < GPB; ++gg) {
-          float acc[RB][NT][4];
+      for (int gg = 0; gg < GPB; ++gg) {
+        // accumulators start at -1024 * sum(x / c) of the group, so the mma result is sum(code * x) directly
+        const int gi = b * GPB + gg;
+        float2 q0[NT], q1[NT];
+        float acc[RB][NT][4];
 #pragma unroll
-          for (int r = 0; r < RB; ++r)
+        for (int n = 0; n < NT; ++n) {
+          q0[n] = gsum[gi * MP + n * 8 + 2 * t];
+          q1[n] = gsum[gi * MP + n * 8 + 2 * t + 1];
 #pragma unroll
-            for (int n = 0; n < NT; ++n)
-#pragma unroll
-              for (int i = 0; i < 4; ++i) acc[r][n][i] = 0.f;
-#pragma unroll
-          for (int s8 = 0; s8 < 8 / GPB; ++s8) {
-            const int s = gg * (8 / GPB) + s8;
-            uint32_t bf[NT][2];
-#pragma unroll
-            for (int n = 0; n < NT; ++n) {
-              bf[n][0] = 0u; bf[n][1] = 0u;
-              const int tok = n * 8 + g;
-              if (tok < m) {
-                const uint2 v = *reinterpret_cast<const uint2*>(xs + (size_t)tok * XST + b * 128 + s * 16 + t * 4);
-                bf[n][0] = v.x; bf[n][1] = v.y;
-              }
-            }
-#pragma unroll
-            for (int r = 0; r < RB; ++r) {
-              uint32_t af[4];
-              extract<BITS, GROUP>(cf[r], s, af);
-#pragma unroll
-              for (int n = 0; n < NT; ++n) mma_f16_16816(acc[r][n], af, bf[n][0], bf[n][1]);
-            }
+          for (int r = 0; r < RB; ++r) {
+            acc[r][n][0] = -q0[n].x; acc[r][n][1] = -q1[n].x;
+            acc[r][n][2] = -q0[n].x; acc[r][n][3] = -q1[n].x;
           }
-          // y += scale * (acc - 1024*sum(xs) - zero*sum(x))
-          const int gi = b * GPB + gg;
+        }
+#pragma unroll
+        for (int s8 = 0; s8 < 8 / GPB; ++s8) {
+          const int s = gg * (8 / GPB) + s8;
+          uint32_t bf[NT][2];
 #pragma unroll
           for (int n = 0; n < NT; ++n) {
-            const float2 q0 = gsum[gi * MP + n * 8 + 2 * t];
-            const float2 q1 = gsum[gi * MP + n * 8 + 2 * t + 1];
-#pragma unroll
-            for (int r = 0; r < RB; ++r) {
-              const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&cf[r].sz[gg][0]));
-              const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&cf[r].sz[gg][1]));
-              y[r][n][0] += s0.x * (acc[r][n][0] - q0.x - s0.y * q0.y);
-              y[r][n][1] += s0.x * (acc[r][n][1] - q1.x - s0.y * q1.y);
-              y[r][n][2] += s1.x * (acc[r][n][2] - q0.x - s1.y * q0.y);
-              y[r][n][3] += s1.x * (acc[r][n][3] - q1.x - s1.y * q1.y);
+            bf[n][0] = 0u; bf[n][1] = 0u;
+            const int tok = n * 8 + g;
+            if (tok < m) {
+              const uint2 v = *reinterpret_cast<const uint2*>(xrow + (size_t)tok * XST + s * 16);
+              bf[n][0] = v.x; bf[n][1] = v.y;
             }
+          }
+#pragma unroll
+          for (int r = 0; r < RB; ++r) {
+            uint32_t af[4];
+            extract<BITS, GROUP>(cf[r], s, af);
+#pragma unroll
+            for (int n = 0; n < NT; ++n) mma_f16_16816(acc[r][n], af, bf[n][0], bf[n][1]);
+          }
+        }
+        // y += scale * (acc - zero * sum(x))
+#pragma unroll
+        for (int r = 0; r < RB; ++r) {
+          const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&cf[r].sz[gg][0]));
+          const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&cf[r].sz[gg][1]));
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+            y[r][n][0] = fmaf(s0.x, fmaf(-s0.y, q0[n].y, acc[r][n][0]), y[r][n][0]);
+            y[r][n][1] = fmaf(s0.x, fmaf(-s0.y, q1[n].y, acc[r][n][1]), y[r][n][1]);
+            y[r][n][2] = fmaf(s1.x, fmaf(-s1.y, q0[n].y, acc[r][n][2]), y[r][n][2]);
+            y[r][n][3] = fmaf(s1.x, fmaf(-s1.y, q1[n].y, acc[r][n][3]), y[r][n][3]);
           }
         }
       }
@@ -374,200 +371,195 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
       __syncwarp();
       ++cons;
       if (lane == 0) {
-        while (prod - cons < (unsigned)kStages && issue_one()) { }
+        while (prod - cons < (unsigned)NST && issue_one()) { }
       }
     }
     if (failed) break;
 
-    // ---- item done: fragment layout -> one row per lane ----
-    const int panel = (int)cur;
-    const int n0 = panel * 32;
+    // ---- item done: fragment layout -> RPL rows per lane (row = lane + 32 j) ----
+    const int item = cur;
+    const int n0 = item * ROWS;
     __syncwarp();
 #pragma unroll
     for (int r = 0; r < RB; ++r)
 #pragma unroll
       for (int n = 0; n < NT; ++n) {
         const int tok = n * 8 + 2 * t;
-        fin[(size_t)tok * 32 + r * 16 + g] = y[r][n][0];
-        fin[(size_t)(tok + 1) * 32 + r * 16 + g] = y[r][n][1];
-        fin[(size_t)tok * 32 + r * 16 + g + 8] = y[r][n][2];
-        fin[(size_t)(tok + 1) * 32 + r * 16 + g + 8] = y[r][n][3];
+        if (tok < m) {
+          fin[(size_t)tok * ROWS + r * 16 + g] = y[r][n][0];
+          fin[(size_t)tok * ROWS + r * 16 + g + 8] = y[r][n][2];
+        }
+        if (tok + 1 < m) {
+          fin[(size_t)(tok + 1) * ROWS + r * 16 + g] = y[r][n][1];
+          fin[(size_t)(tok + 1) * ROWS + r * 16 + g + 8] = y[r][n][3];
+        }
       }
     __syncwarp();
-    float v[MP];
+    float v[RPL][MP];
 #pragma unroll
-    for (int tok = 0; tok < MP; ++tok) v[tok] = tok < m ? fin[tok * 32 + lane] : 0.f;
+    for (int j = 0; j < RPL; ++j)
+#pragma unroll
+      for (int tok = 0; tok < MP; ++tok) v[j][tok] = tok < m ? fin[tok * ROWS + j * 32 + lane] : 0.f;
     bool do_epi = true;
     if (ks > 1) {
-      float* sp = a.scratch + ((size_t)panel * ks) * (size_t)(m * 32);
+      float* sp = a.scratch + ((size_t)item * ks) * (size_t)(m * ROWS);
 #pragma unroll
-      for (int tok = 0; tok < MP; ++tok)
-        if (tok < m) sp[(size_t)slice * (m * 32) + tok * 32 + lane] = v[tok];
+      for (int j = 0; j < RPL; ++j)
+#pragma unroll
+        for (int tok = 0; tok < MP; ++tok)
+          if (tok < m) sp[(size_t)slice * (m * ROWS) + tok * ROWS + j * 32 + lane] = v[j][tok];
       __threadfence();
       __syncwarp();
       unsigned prev = 0;
-      if (lane == 0) prev = atomicInc(a.counters + panel, (unsigned)ks - 1u);
+      if (lane == 0) prev = atomicInc(a.counters + item, (unsigned)ks - 1u);
       prev = __shfl_sync(0xffffffffu, prev, 0);
       do_epi = prev == (unsigned)ks - 1u;
       if (do_epi) {
         __threadfence();
 #pragma unroll
-        for (int tok = 0; tok < MP; ++tok) {
-          if (tok < m) {
-            float s = 0.f;
-            for (int j = 0; j < ks; ++j) s += __ldcg(sp + (size_t)j * (m * 32) + tok * 32 + lane);
-            v[tok] = s;
-          }
-        }
-      }
-    }
-    const int row = n0 + lane;
-    const bool row_ok = row < a.n;
-    if (do_epi) {
-      if (a.epi == EPI_TP_RESID) {
-        // ---- push all-reduce of this panel: every rank writes its partial into every inbox, then sums its own
-        //      inbox in rank order once no sentinel is left ----
-        const TpPush& tp = a.tp;
-        if (row_ok) {
-          if (!tp.skip_push) {
-            for (int dst = 0; dst < tp.size; ++dst) {
-              float* pb = tp.inbox[dst] + tp.slot_off + (size_t)tp.rank * tp.slot_stride + row;
-#pragma unroll
-              for (int tok = 0; tok < MP; ++tok)
-                if (tok < m) {
-                  const float val = v[tok] + 0.f;   // -0.0 -> +0.0: the sentinel never travels as data
-                  asm volatile("st.volatile.global.f32 [%0], %1;" ::"l"(pb + (size_t)tok * a.n), "f"(val) : "memory");
-                }
-            }
-          }
-          const float* mine = tp.inbox[tp.rank] + tp.slot_off + row;
-          const uint64_t t_start = globaltimer_ns();
+        for (int j = 0; j < RPL; ++j)
 #pragma unroll
           for (int tok = 0; tok < MP; ++tok) {
             if (tok < m) {
               float s = 0.f;
-              for (int src = 0; src < tp.size; ++src) {
-                const float* pp = mine + (size_t)src * tp.slot_stride + (size_t)tok * a.n;
-                float val;
-                unsigned spins = 0;
-                bool ok;
-                while (true) {
-                  asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(val) : "l"(pp) : "memory");
-                  ok = __float_as_uint(val) != 0x80000000u;
-                  if (ok) break;
-                  if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > tp.timeout_ns) break;
-                }
-                if (!ok) { atomicExch(tp.status, (int)B2_ERR_TIMEOUT); val = 0.f; }
-                s += val;
+              for (int sl = 0; sl < ks; ++sl) s += __ldcg(sp + (size_t)sl * (m * ROWS) + tok * ROWS + j * 32 + lane);
+              v[j][tok] = s;
+            }
+          }
+      }
+    }
+    if (do_epi) {
+#pragma unroll
+      for (int j = 0; j < RPL; ++j) {
+        const int row = n0 + j * 32 + lane;
+        const bool row_ok = row < a.n;
+        const int part = item * RPL + j;            // 32-row panel index: partial statistics are per panel
+        if (a.epi == EPI_TP_RESID) {
+          // push all-reduce of this panel: every rank writes its partial into every inbox, then sums its own inbox
+          // in rank order once no sentinel is left
+          const TpPush& tp = a.tp;
+          if (row_ok) {
+            if (!tp.skip_push) {
+              for (int dst = 0; dst < tp.size; ++dst) {
+                float* pb = tp.inbox[dst] + tp.slot_off + (size_t)tp.rank * tp.slot_stride + row;
+#pragma unroll
+                for (int tok = 0; tok < MP; ++tok)
+                  if (tok < m) {
+                    const float val = v[j][tok] + 0.f;   // -0.0 -> +0.0: the sentinel never travels as data
+                    asm volatile("st.volatile.global.f32 [%0], %1;" ::"l"(pb + (size_t)tok * a.n), "f"(val) : "memory");
+                  }
               }
-              v[tok] = s;
             }
-          }
-          if (tp.clear_off >= 0) {   // re-arm the slot that no rank writes before its next use
-            float* clr = tp.inbox[tp.rank] + tp.clear_off + row;
-            const float neg0 = __uint_as_float(0x80000000u);
-            for (int src = 0; src < tp.size; ++src)
+            const float* mine = tp.inbox[tp.rank] + tp.slot_off + row;
+            const uint64_t t_start = globaltimer_ns();
 #pragma unroll
-              for (int tok = 0; tok < MP; ++tok)
-                if (tok < m) clr[(size_t)src * tp.slot_stride + (size_t)tok * a.n] = neg0;
-          }
-        }
-      }
-      if (a.epi == EPI_STORE) {
-#pragma unroll
-        for (int tok = 0; tok < MP; ++tok)
-          if (tok < m && row_ok) a.y[(size_t)tok * a.ldy + row] = __float2bfloat16_rn(v[tok]);
-      } else if (a.epi == EPI_F32) {
-#pragma unroll
-        for (int tok = 0; tok < MP; ++tok)
-          if (tok < m && row_ok) a.yf[(size_t)tok * a.ldy + row] = v[tok];
-      } else if (a.epi == EPI_RESID || a.epi == EPI_TP_RESID) {
-#pragma unroll
-        for (int tok = 0; tok < MP; ++tok) {
-          if (tok < m) {
-            float sq = 0.f;
-            if (row_ok) {
-              const bf16 hb = __float2bfloat16_rn(v[tok] + __bfloat162float(a.resid[(size_t)tok * a.ldr + row]));
-              a.y[(size_t)tok * a.ldy + row] = hb;
-              const float hf = __bfloat162float(hb);
-              sq = hf * hf;
+            for (int tok = 0; tok < MP; ++tok) {
+              if (tok < m) {
+                float s = 0.f;
+                for (int src = 0; src < tp.size; ++src) {
+                  const float* pp = mine + (size_t)src * tp.slot_stride + (size_t)tok * a.n;
+                  float val;
+                  unsigned spins = 0;
+                  bool ok;
+                  while (true) {
+                    asm volatile("ld.volatile.global.f32 %0, [%1];" : "=f"(val) : "l"(pp) : "memory");
+                    ok = __float_as_uint(val) != 0x80000000u;
+                    if (ok) break;
+                    if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > tp.timeout_ns) break;
+                  }
+                  if (!ok) { atomicExch(tp.status, (int)B2_ERR_TIMEOUT); val = 0.f; }
+                  s += val;
+                }
+                v[j][tok] = s;
+              }
             }
-            sq = warp_sum(sq);
-            if (lane == 0 && a.ss_out) a.ss_out[(size_t)panel * a.ss_ld + tok] = sq;
-          }
-        }
-      } else if (a.epi == EPI_SWIGLU) {
-        // lanes 0-7 / 16-23 hold gate rows, lanes 8-15 / 24-31 the matching up rows
+            if (tp.clear_off >= 0) {   // re-arm the slot that no rank writes before its next use
+              float* clr = tp.inbox[tp.rank] + tp.clear_off + row;
+              const float neg0 = __uint_as_float(0x80000000u);
+              for (int src = 0; src < tp.size; ++src)
 #pragma unroll
-        for (int tok = 0; tok < MP; ++tok) {
-          if (tok < m) {
-            const float up = __shfl_down_sync(0xffffffffu, v[tok], 8);
-            if ((lane & 8) == 0 && row_ok) {
-              const float gt = bf16_round(v[tok]);
-              a.y[(size_t)tok * a.ldy + (size_t)panel * 16 + (lane >> 4) * 8 + (lane & 7)] =
-                  __float2bfloat16_rn(silu_f(gt) * bf16_round(up));
+                for (int tok = 0; tok < MP; ++tok)
+                  if (tok < m) clr[(size_t)src * tp.slot_stride + (size_t)tok * a.n] = neg0;
             }
           }
         }
-      } else if (a.epi == EPI_ARGMAX) {
+        if (a.epi == EPI_STORE) {
 #pragma unroll
-        for (int tok = 0; tok < MP; ++tok) {
-          if (tok < m) {
-            if (a.yf && row_ok) a.yf[(size_t)tok * a.ldy + row] = v[tok];
-            float best = (row_ok && row < a.n_valid) ? v[tok] : -INFINITY;
-            int bi = (row_ok && row < a.n_valid) ? row : 0x7fffffff;
+          for (int tok = 0; tok < MP; ++tok)
+            if (tok < m && row_ok) a.y[(size_t)tok * a.ldy + row] = __float2bfloat16_rn(v[j][tok]);
+        } else if (a.epi == EPI_F32) {
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-              const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-              const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-              if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+          for (int tok = 0; tok < MP; ++tok)
+            if (tok < m && row_ok) a.yf[(size_t)tok * a.ldy + row] = v[j][tok];
+        } else if (a.epi == EPI_RESID || a.epi == EPI_TP_RESID) {
+#pragma unroll
+          for (int tok = 0; tok < MP; ++tok) {
+            if (tok < m) {
+              float sq = 0.f;
+              if (row_ok) {
+                const bf16 hb = __float2bfloat16_rn(v[j][tok] + __bfloat162float(a.resid[(size_t)tok * a.ldr + row]));
+                a.y[(size_t)tok * a.ldy + row] = hb;
+                const float hf = __bfloat162float(hb);
+                sq = hf * hf;
+              }
+              sq = warp_sum(sq);
+              if (lane == 0 && a.ss_out && part < npan) a.ss_out[(size_t)part * a.ss_ld + tok] = sq;
             }
-            if (lane == 0) {
-              a.amax_val[(size_t)panel * a.ss_ld + tok] = best;
-              a.amax_idx[(size_t)panel * a.ss_ld + tok] = bi;
+          }
+        } else if (a.epi == EPI_SWIGLU) {
+          // lanes 0-7 / 16-23 hold gate rows, lanes 8-15 / 24-31 the matching up rows
+#pragma unroll
+          for (int tok = 0; tok < MP; ++tok) {
+            if (tok < m) {
+              const float up = __shfl_down_sync(0xffffffffu, v[j][tok], 8);
+              if ((lane & 8) == 0 && row_ok) {
+                const float gt = bf16_round(v[j][tok]);
+                a.y[(size_t)tok * a.ldy + (size_t)part * 16 + (lane >> 4) * 8 + (lane & 7)] =
+                    __float2bfloat16_rn(silu_f(gt) * bf16_round(up));
+              }
+            }
+          }
+        } else if (a.epi == EPI_ARGMAX) {
+#pragma unroll
+          for (int tok = 0; tok < MP; ++tok) {
+            if (tok < m) {
+              if (a.yf && row_ok) a.yf[(size_t)tok * a.ldy + row] = v[j][tok];
+              float best = (row_ok && row < a.n_valid) ? v[j][tok] : -INFINITY;
+              int bi = (row_ok && row < a.n_valid) ? row : 0x7fffffff;
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+              }
+              if (lane == 0 && part < npan) {
+                a.amax_val[(size_t)part * a.ss_ld + tok] = best;
+                a.amax_idx[(size_t)part * a.ss_ld + tok] = bi;
+              }
             }
           }
         }
       }
     }
-    // ---- next item ----
-    if (lane == 0) {
-      t_cur = t_nxt; t_nxt = t_nx2;
-      t_nx2 = atomicAdd(tickets + slice, 1u);
-      --p_which;
-      while (prod - cons < (unsigned)kStages && issue_one()) { }
-    }
-    cur = __shfl_sync(0xffffffffu, t_cur, 0);
   }
   if (failed) {
     // Give copies still in flight a bounded chance to land before the CTA's shared memory is released.
     const uint64_t t0 = globaltimer_ns();
     while (globaltimer_ns() - t0 < 2000000ull) { }
   }
-  // ---- the last warp of the grid to leave re-arms the ticket counters for the next launch on this parity ----
-  __syncwarp();
-  if (lane == 0) {
-    __threadfence();
-    const unsigned total = gridDim.x * 4u;
-    if (atomicAdd(tickets + kMaxKs, 1u) == total - 1u) {
-      for (int i = 0; i < ks; ++i) tickets[i] = 0u;
-      tickets[kMaxKs] = 0u;
-      __threadfence();
-    }
-  }
 }
 
-template <int BITS, int GROUP, int NT>
+template <int BITS, int GROUP, int RB, int NT>
 static int launch_one(const WqGemvArgs& a, cudaStream_t st) {
   constexpr int MP = NT * 8;
-  using R = Ring<BITS, GROUP, kRB>;
-  const int nu = a.k / 128;
-  const int nb_max = (nu + a.ks - 1) / a.ks;
+  using R = Ring<BITS, GROUP, RB>;
+  const int nbat = a.k / 128;
+  const int nb_max = (nbat + a.ks - 1) / a.ks;
   const int xst = nb_max * 128 + 16;
-  const size_t smem = (size_t)4 * kStages * R::STAGE + 4 * kStages * 8 + (size_t)MP * 4 + (size_t)4 * MP * 32 * 4 +
-                      (size_t)a.m * xst * 2 + (size_t)nb_max * (128 / GROUP) * MP * 8;
+  const size_t smem = (size_t)kGemvWarps * R::NST * R::STAGE + kGemvWarps * R::NST * 8 + 32 * 4 +
+                      (size_t)kGemvWarps * a.m * RB * 16 * 4 + (size_t)a.m * xst * 2 + (size_t)nb_max * (128 / GROUP) * MP * 8;
   if (smem > 220 * 1024) return B2_ERR_ARG;
-  auto kern = wq_gemv_kernel<BITS, GROUP, NT>;
+  auto kern = wq_gemv_kernel<BITS, GROUP, RB, NT>;
   static bool attr_set = false;   // one flag per instantiation
   static int sm_count = 0;
   if (!attr_set) {
@@ -579,14 +571,13 @@ static int launch_one(const WqGemvArgs& a, cudaStream_t st) {
   }
   int occ = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kGemvThreads, smem) != cudaSuccess || occ < 1) return B2_ERR_LAUNCH;
-  const int nrb = a.n / 16;
-  const int npanels = (nrb + kRB - 1) / kRB;
-  // persistent grid: a multiple of ks, at most what fits on the device, at most one warp per item
-  long want = (long)sm_count * occ;
-  const long items = (long)npanels * a.ks;
-  if (want * 4 > items) want = (items + 3) / 4;
-  long grid = (want / a.ks) * a.ks;
-  if (grid < a.ks) grid = a.ks;
+  const int npan = a.n / 32;
+  const int nitems = (npan + RB / 2 - 1) / (RB / 2);
+  // persistent grid of (CTAs per slice) x ks CTAs: every SM carries the same number of CTAs
+  long cps = ((long)sm_count * occ) / a.ks;
+  if (cps < 1) cps = 1;
+  if (cps * kGemvWarps > nitems) cps = (nitems + kGemvWarps - 1) / kGemvWarps;   // never more warps than items
+  const long grid = cps * a.ks;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
   cfg.blockDim = dim3(kGemvThreads, 1, 1);
@@ -603,9 +594,11 @@ static int launch_one(const WqGemvArgs& a, cudaStream_t st) {
 template <int BITS, int GROUP>
 static int launch_bg(const WqGemvArgs& a, cudaStream_t st) {
   const int nt = (a.m + 7) / 8;
-  if (nt == 1) return launch_one<BITS, GROUP, 1>(a, st);
-  if (nt == 2) return launch_one<BITS, GROUP, 2>(a, st);
-  if (nt <= 4) return launch_one<BITS, GROUP, 4>(a, st);
+  if (a.rb == 4 && nt == 1) return launch_one<BITS, GROUP, 4, 1>(a, st);
+  if (a.rb == 4 && nt == 2) return launch_one<BITS, GROUP, 4, 2>(a, st);
+  if (nt == 1) return launch_one<BITS, GROUP, 2, 1>(a, st);
+  if (nt == 2) return launch_one<BITS, GROUP, 2, 2>(a, st);
+  if (nt <= 4) return launch_one<BITS, GROUP, 2, 4>(a, st);
   return B2_ERR_ARG;
 }
 
@@ -613,21 +606,22 @@ static int launch_bg(const WqGemvArgs& a, cudaStream_t st) {
 
 using namespace b2;
 
+// Scratch floats for split-k: [item][ks][m][rows per item] = n * ks * m for any rb.
 B2_API long b2_wq_gemv_scratch_floats(int n, int ks, int m) {
   if (ks <= 1) return 0;
-  const long npanels = (n / 16 + kRB - 1) / kRB;
-  return npanels * ks * (long)m * 32;
+  return ((long)n + 63) / 64 * 64 * ks * m;
 }
 
 // Launches the GEMV described by *args on `stream`.  Returns a b2::Status; nothing is launched on B2_ERR_ARG.
+// Rows 17..32 tokens always use 32-row items (register budget), whatever args->rb says; per-row results do not
+// depend on rb, because the k range and summation order of a row are fixed by (k, ks) alone.
 B2_API int b2_wq_gemv(const WqGemvArgs* args, cudaStream_t stream) {
   const WqGemvArgs& a = *args;
   if (a.n <= 0 || a.k <= 0 || a.m <= 0 || a.m > 32) return B2_ERR_ARG;
-  if (a.n % 16 || a.k % 128 || a.ks < 1 || a.ks > kMaxKs || a.ks > a.k / 128) return B2_ERR_ARG;
+  if (a.n % 32 || a.k % 128 || a.ks < 1 || a.ks > kMaxKs || a.ks > a.k / 128) return B2_ERR_ARG;
   if (a.group != 64 && a.group != 128) return B2_ERR_ARG;
-  if (!a.tickets || (a.ticket_parity != 0 && a.ticket_parity != 1)) return B2_ERR_ARG;
+  if (a.rb != 2 && a.rb != 4) return B2_ERR_ARG;
   if (a.ks > 1 && (!a.scratch || !a.counters)) return B2_ERR_ARG;
-  if (a.epi == EPI_SWIGLU && (a.n % 32)) return B2_ERR_ARG;
   if ((a.ldx % 8) || (reinterpret_cast<uintptr_t>(a.x) & 15)) return B2_ERR_ARG;
   if (a.epi == EPI_TP_RESID && (a.tp.size < 1 || a.tp.size > kMaxTp)) return B2_ERR_ARG;
   switch (a.bits * 1000 + a.group) {

@@ -17,7 +17,8 @@ enum GemvEpi : int {
   EPI_TP_RESID = 5,   // tensor parallel: push the partial to every peer, sum all ranks in rank order, then EPI_RESID
 };
 
-constexpr int kGemvThreads = 128;       // 4 warps per CTA, the warps split the CTA's k range
+constexpr int kGemvWarps = 8;
+constexpr int kGemvThreads = kGemvWarps * 32;
 constexpr int kMaxTp = 8;
 constexpr int kMaxKs = 64;            // most k slices a linear may be cut into
 
@@ -35,11 +36,11 @@ struct TpPush {
 };
 
 struct WqGemvArgs {
-  const uint8_t* wq;     // FM records [n/16][k/CK][REC]
-  const __half2* sz;     // [n/16][k/group][16] (scale, zero)
+  const uint8_t* wq;     // FM blocks [n/32][k/128][2 x records | 2 x groups x 16 x (scale, zero)]
   int n, k, m;
   int bits, group;
   int ks;                // k slices (a function of the linear's shape only)
+  int rb;                // row blocks per warp item: 2 (32 rows) or 4 (64 rows)
   int pro;
   const bf16* x; long ldx;
   const float* ss_in; int ss_parts; int ss_ld;
@@ -50,9 +51,9 @@ struct WqGemvArgs {
   float* ss_out;
   float* yf;
   float* amax_val; int* amax_idx; int n_valid;   // EPI_ARGMAX: rows >= n_valid never win
-  float* scratch; unsigned* counters;   // split-k partials [panel][ks][m][32] and self-resetting panel counters
-  unsigned* tickets; int ticket_parity;  // 2 x (kMaxKs + 1) work counters; consecutive launches alternate parity
+  float* scratch; unsigned* counters;   // split-k partials [item][ks][m][16*rb] and self-resetting panel counters
   int* status;           // device status word (B2_ERR_TIMEOUT when a bounded wait ran out)
+  int debug;             // 0 normal; 1 = stream weights without arithmetic (bandwidth probe, results meaningless)
   TpPush tp;
 };
 
@@ -61,9 +62,10 @@ struct WqGemvArgs {
 // Host entry points (C ABI).
 B2_API int b2_wq_gemv(const b2::WqGemvArgs* args, cudaStream_t stream);
 B2_API long b2_wq_gemv_scratch_floats(int n, int ks, int m);
-B2_API int b2_wq_dequant(const uint8_t* wq, const __half2* sz, int n, int k, int bits, int group, bf16* out, long ldo,
-                         cudaStream_t stream);
+B2_API int b2_wq_gemv_parts(int n, int rb);
+B2_API long b2_wq_bytes(int n, int k, int bits, int group);
+B2_API int b2_wq_dequant(const uint8_t* wq, int n, int k, int bits, int group, bf16* out, long ldo, cudaStream_t stream);
 B2_API int b2_wq_repack(const int32_t* packed, const void* scale, int scale_is_bf16, const __half* zero, int n, int k,
-                        int bits, int group, uint8_t* wq, __half2* sz, cudaStream_t stream);
-B2_API int b2_wq_random(uint8_t* wq, __half2* sz, int n, int k, int bits, int group, float stddev,
-                        unsigned long long seed, cudaStream_t stream);
+                        int bits, int group, uint8_t* wq, cudaStream_t stream);
+B2_API int b2_wq_random(uint8_t* wq, int n, int k, int bits, int group, float stddev, unsigned long long seed,
+                        cudaStream_t stream);

@@ -49,15 +49,13 @@ def test_dequant_kernel_matches_cpu(bits):
 @pytest.mark.parametrize("sym", [False, True])
 def test_device_repack_matches_cpu_pack(bits, sym):
     torch.manual_seed(5)
-    n, k, group = 48, 512, 64
+    n, k, group = 64, 512, 64
     w = torch.randn(n, k) * 0.02
     ql = quant.quantize(w, bits, group, symmetric=sym, scale_dtype=torch.bfloat16 if sym else torch.float16)
     packed = quant.pack_stream(ql.codes, bits)
     lin = L.WqLinear.from_checkpoint(packed, ql.scale.to(torch.bfloat16) if sym else ql.scale,
                                      None if sym else ql.zero, n, k, bits, group, DEV)
-    wq_cpu, sz_cpu = quant.pack_fm(ql)
-    assert torch.equal(lin.wq.cpu(), wq_cpu.reshape(-1))
-    assert torch.equal(lin.sz.cpu(), sz_cpu)
+    assert torch.equal(lin.wq.cpu(), quant.pack_fm(ql).reshape(-1))
 
 
 def test_rows_do_not_depend_on_batch():
@@ -71,6 +69,8 @@ def test_rows_do_not_depend_on_batch():
         y1 = L.gemv(lin, x[5:6].contiguous(), ws, epi=_lib.EPI_F32)
         assert torch.equal(y16[:8], y8)
         assert torch.equal(y16[5:6], y1)
+        lin4 = L.WqLinear(lin.n, lin.k, lin.bits, lin.group, lin.wq, lin.ks, rb=4)
+        assert torch.equal(L.gemv(lin4, x[:8].contiguous(), ws, epi=_lib.EPI_F32), y8)
         x32 = torch.cat([x, x], 0)
         y32 = L.gemv(lin, x32, ws, epi=_lib.EPI_F32)
         assert torch.equal(y32[:16], y16) and torch.equal(y32[16:], y16)

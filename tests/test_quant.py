@@ -39,26 +39,25 @@ def test_stream_w4_matches_reference_nibble_order():
 @pytest.mark.parametrize("group", [64, 128])
 def test_fm_roundtrip(bits, group):
     torch.manual_seed(7)
-    w = torch.randn(48, 384) * 0.02
+    w = torch.randn(64, 384) * 0.02
     ql = quant.quantize(w, bits, group)
-    wq, sz = quant.pack_fm(ql)
-    assert wq.shape == (3, 384 // quant.chunk_k(bits), quant.record_bytes(bits))
-    back = quant.unpack_fm(wq, sz, bits, 48, 384, group)
+    wq = quant.pack_fm(ql)
+    assert wq.shape == (2, 3, quant.block_bytes(bits, group))
+    back = quant.unpack_fm(wq, bits, 64, 384, group)
     assert torch.equal(back.codes, ql.codes)
     assert torch.equal(back.scale, ql.scale) and torch.equal(back.zero, ql.zero)
 
 
 def test_fm_every_bit_used_once():
     for bits in (2, 3, 4):
-        n, k = 16, quant.chunk_k(bits)
-        total = torch.zeros(quant.record_bytes(bits) * 8, dtype=torch.int32)
+        n, k = 32, 128
+        total = torch.zeros(quant.block_bytes(bits, 64) * 8, dtype=torch.int32)
         for r in range(0, n, 5):
             for c in range(0, k, 7):
                 codes = torch.zeros(n, k, dtype=torch.uint8)
                 codes[r, c] = (1 << bits) - 1
-                ql = quant.QuantLinear(n, k, bits, 64, codes, torch.ones(n, k // 64).half(), torch.zeros(n, k // 64).half())
-                wq, _ = quant.pack_fm(ql)
-                b = wq.reshape(-1)
+                ql = quant.QuantLinear(n, k, bits, 64, codes, torch.zeros(n, k // 64).half(), torch.zeros(n, k // 64).half())
+                b = quant.pack_fm(ql).reshape(-1)
                 setbits = sum(bin(int(x)).count("1") for x in b.tolist())
                 assert setbits == bits
                 idx = torch.nonzero(b).reshape(-1)
