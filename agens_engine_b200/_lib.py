@@ -83,6 +83,7 @@ class WqGemvArgs(C.Structure):
         ("n", C.c_int), ("k", C.c_int), ("m", C.c_int),
         ("bits", C.c_int), ("group", C.c_int),
         ("ks", C.c_int), ("rb", C.c_int),
+        ("vworkers", C.c_int), ("fmax", C.c_int),
         ("pro", C.c_int),
         ("x", C.c_void_p), ("ldx", C.c_long),
         ("ss_in", C.c_void_p), ("ss_parts", C.c_int), ("ss_ld", C.c_int),
@@ -126,7 +127,9 @@ def _declare(lib: C.CDLL):
     vp, i, l, f = C.c_void_p, C.c_int, C.c_long, C.c_float
     sig = {
         "b2_wq_gemv": ([C.POINTER(WqGemvArgs), vp], i),
-        "b2_wq_gemv_scratch_floats": ([i, i, i], l),
+        "b2_wq_gemv_scratch_floats": ([i, i, i, i, i], l),
+        "b2_wq_gemv_vworkers": ([i, i, i, i], i),
+        "b2_wq_gemv_fmax": ([i, i, i, i], i),
         "b2_wq_bytes": ([i, i, i, i], l),
         "b2_wq_dequant": ([vp, i, i, i, i, vp, l, vp], i),
         "b2_wq_repack": ([vp, vp, i, vp, i, i, i, i, vp, vp], i),
@@ -142,6 +145,7 @@ def _declare(lib: C.CDLL):
         "b2_fill_u32": ([vp, C.c_uint32, l, vp], i),
         "b2_attn_decode": ([C.POINTER(AttnDecodeArgs), i, vp], i),
         "b2_attn_decode_smem_bytes": ([i], i),
+        "b2_gemm_bf16": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp, vp], i),
     }
     for name, (args, res) in sig.items():
         if hasattr(lib, name):

@@ -93,7 +93,7 @@ def bench_gemv(args):
     for name, n, k in shapes:
         for bits in ([4] if name == "lm_head" else [2, 3, 4]):
             for _ in (0,):
-                ks_list = sorted({L.choose_ks(n, k), L.choose_ks(n, k, 2560), L.choose_ks(n, k, 512), L.choose_ks(n, k, 640)})
+                ks_list = sorted({1, L.choose_ks(n, k), L.choose_ks(n, k, 1280), L.choose_ks(n, k, 5120)})
                 for ks in ks_list:
                     lin = L.WqLinear.random(n, k, bits, 128, dev, seed=1, ks=ks)
                     nbytes = lin.nbytes()

@@ -133,7 +133,7 @@ class DenseModel:
         """Size the split-k workspace from the loaded linears (call once after the weights are in place)."""
         lib = _lib.cuda_lib()
         lins = [self.lm_head] + [d[lin] for d in self.layers[:1] for lin in LINEARS]
-        need = max(lib.b2_wq_gemv_scratch_floats(x.n, x.ks, M_GEMV) for x in lins)
+        need = max(lib.b2_wq_gemv_scratch_floats(x.n, x.k, x.ks, r, M_GEMV) for x in lins for r in (2, x.rb))
         panels = max(x.n_panels() for x in lins)
         self.ws = L.GemvWorkspace(self.dev, floats=max(need, 1 << 16), panels=max(panels, 1 << 10))
         return self

@@ -30,7 +30,7 @@ def choose_rb(n: int) -> int:
     return 4 if n >= 16384 else 2
 
 
-def choose_ks(n: int, k: int, slice_k: int = 1024) -> int:
+def choose_ks(n: int, k: int, slice_k: int = 2560) -> int:
     """Number of k slices of a linear: a function of the shape only (never of the token count), so per-row
     arithmetic stays batch invariant.  Slices of about ``slice_k`` inputs keep the staged activations small and give
     the persistent GEMV thousands of (panel, slice) work items to balance over the SMs."""
@@ -160,10 +160,12 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
     if resid is not None:
         a.resid, a.ldr = ptr(resid), resid.stride(0)
     a.ss_out = ptr(ss_out)
-    if lin.ks > 1:
-        need = lib.b2_wq_gemv_scratch_floats(lin.n, lin.ks, m)
-        assert need <= ws.scratch.numel() and lin.n_panels() <= ws.counters.numel()
-        a.scratch, a.counters = ptr(ws.scratch), ptr(ws.counters)
+    a.vworkers = lib.b2_wq_gemv_vworkers(lin.n, lin.k, lin.ks, a.rb)
+    a.fmax = lib.b2_wq_gemv_fmax(lin.n, lin.k, lin.ks, a.rb)
+    need = lib.b2_wq_gemv_scratch_floats(lin.n, lin.k, lin.ks, a.rb, m)
+    if need > ws.scratch.numel() or lin.n_panels() > ws.counters.numel():
+        raise RuntimeError(f"GEMV workspace too small: need {need} floats, {lin.n_panels()} counters")
+    a.scratch, a.counters = ptr(ws.scratch), ptr(ws.counters)
     a.status = ptr(ws.status)
     a.debug = int(os.environ.get("B200E_GEMV_DEBUG", "0"))
     if tp is not None:

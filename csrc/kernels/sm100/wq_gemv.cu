@@ -46,7 +46,7 @@ struct Ring {
   static constexpr int W_BATCH = RPB * Fmt<BITS>::REC;     // weight bytes of one batch of one row block
   static constexpr int BLK = 2 * W_BATCH + 2 * GPB * 64;    // one (panel, batch) block
   static constexpr int STAGE = (RB / 2) * BLK;
-  static constexpr int NST = BITS == 4 ? 3 : (BITS == 3 ? 4 : 5);   // ring depth: about 13 KB in flight per warp
+  static constexpr int NST = (BITS == 4 ? 2 : (BITS == 3 ? 3 : 4)) * (RB == 2 ? 2 : 1);   // about 9 KB in flight per warp
 };
 
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
@@ -190,10 +190,15 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
 
   const uint32_t ring_u = smem_u32(ring);
   const uint32_t bars_u = smem_u32(bars);
-  // Static schedule: the warps of the CTAs that share a slice take items round robin.  Items are equal in size and
-  // the launcher sizes the grid so that every warp gets the same number of them (give or take one).
+  // Static, balanced schedule.  The (item, batch) units of a slice are laid out item-major and cut into V equal
+  // contiguous ranges, one per virtual worker; V depends on the linear's shape only, so the cut points -- and with
+  // them every summation order -- never depend on the token count or on how many CTAs are resident.  The warps of the
+  // CTAs that share a slice take virtual workers round robin (normally exactly one each).
   const int wstride = (gridDim.x / ks) * kGemvWarps;
   const int wfirst = (blockIdx.x / ks) * kGemvWarps + warp;
+  const int V = a.vworkers;
+  const unsigned U = (unsigned)nitems * (unsigned)nb;          // host checks U * V < 2^32
+  auto range_lo = [&](int v) -> unsigned { return ((unsigned)v * U) / (unsigned)V; };
 
   if (lane == 0) {
 #pragma unroll
@@ -201,23 +206,35 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   unsigned prod = 0, cons = 0;     // stages issued / consumed by this warp since kernel start
-  int p_item = wfirst, p_b = 0;    // producer cursor: item and batch inside it (may run ahead into the next item)
+  // producer cursor (lane 0): virtual worker, next unit and end of its range; item / batch of the next unit
+  int p_v = wfirst;
+  unsigned p_u = 0, p_end = 0;
+  int p_item = 0, p_b = 0;
+  auto p_load = [&]() {            // position the cursor on the first non-empty worker at or after p_v
+    while (p_v < V) {
+      p_u = range_lo(p_v); p_end = range_lo(p_v + 1);
+      if (p_u < p_end) { p_item = (int)(p_u / (unsigned)nb); p_b = (int)(p_u - (unsigned)p_item * (unsigned)nb); return; }
+      p_v += wstride;
+    }
+  };
   auto issue_one = [&]() -> bool { // lane 0 only; returns false when nothing is left to issue
-    const int item = p_item;
-    if (item >= nitems) return false;
+    if (p_v >= V) return false;
     const int slot = prod % NST;
     const uint32_t bar = bars_u + slot * 8;
     mbar_expect_tx(bar, (uint32_t)R::STAGE);
     const uint32_t dst = ring_u + slot * R::STAGE;
 #pragma unroll
     for (int pi = 0; pi < RPL; ++pi) {
-      const int pan = min(item * RPL + pi, npan - 1);   // tail item: duplicate the last panel, ignored later
+      const int pan = min(p_item * RPL + pi, npan - 1);   // tail item: duplicate the last panel, ignored later
       bulk_g2s(dst + pi * R::BLK, a.wq + ((size_t)pan * nbat + (u0 + p_b)) * R::BLK, (uint32_t)R::BLK, bar);
     }
     ++prod;
-    if (++p_b == nb) { p_b = 0; p_item += wstride; }
+    ++p_u;
+    if (++p_b == nb) { p_b = 0; ++p_item; }
+    if (p_u == p_end) { p_v += wstride; p_load(); }
     return true;
   };
+  if (lane == 0 && nb > 0) p_load();
   // Weights do not depend on the previous kernel: start streaming before the dependency wait.
   if (lane == 0 && nb > 0) {
     while (prod - cons < (unsigned)NST && issue_one()) { }
@@ -229,8 +246,18 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
   // ---- stage the activation slice of this CTA: fp16(x / c) and the per-group sums ----
   if (a.pro == PRO_NORM) {
     for (int tok = warp; tok < m; tok += kGemvWarps) {
+      // partial sums are fetched eight at a time so that their latencies overlap; the order of the adds is fixed
       float s = 0.f;
-      for (int p = lane; p < a.ss_parts; p += 32) s += a.ss_in[(size_t)p * a.ss_ld + tok];
+      for (int p0 = lane; p0 < a.ss_parts; p0 += 256) {
+        float pv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int p = p0 + 32 * i;
+          pv[i] = p < a.ss_parts ? a.ss_in[(size_t)p * a.ss_ld + tok] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += pv[i];
+      }
       s = warp_sum(s);
       if (lane == 0) inv_rms[tok] = rsqrtf(s / (float)a.k + a.eps);
     }
@@ -283,7 +310,15 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
   __syncthreads();
 
   bool failed = false;
-  for (int cur = wfirst; cur < nitems && nb > 0 && !failed; cur += wstride) {
+  for (int vw = wfirst; vw < V && nb > 0 && !failed; vw += wstride) {
+   unsigned u = range_lo(vw);
+   const unsigned u_end = range_lo(vw + 1);
+   while (u < u_end && !failed) {
+    // one fragment: the batches [b_lo, b_hi) of one item that fall into this worker's range
+    const int cur = (int)(u / (unsigned)nb);
+    const int b_lo = (int)(u - (unsigned)cur * (unsigned)nb);
+    const int b_hi = min(nb, b_lo + (int)(u_end - u));
+    u += (unsigned)(b_hi - b_lo);
     float y[RB][NT][4];
 #pragma unroll
     for (int r = 0; r < RB; ++r)
@@ -293,7 +328,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
         for (int i = 0; i < 4; ++i) y[r][n][i] = 0.f;
 
 #pragma unroll 1
-    for (int b = 0; b < nb; ++b) {
+    for (int b = b_lo; b < b_hi; ++b) {
       const int slot = cons % NST;
       if (!mbar_wait_bounded(bars_u + slot * 8, (cons / NST) & 1u)) {
         if (a.status) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
@@ -400,20 +435,33 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
     for (int j = 0; j < RPL; ++j)
 #pragma unroll
       for (int tok = 0; tok < MP; ++tok) v[j][tok] = tok < m ? fin[tok * ROWS + j * 32 + lane] : 0.f;
+    // Fragments of this item: workers v_first .. v_last of every slice.  Partials meet in scratch memory
+    // [item][slice][fragment]; the last arriver sums them in (slice, fragment) order.
+    const unsigned i_lo = (unsigned)cur * (unsigned)nb, i_hi = i_lo + (unsigned)nb - 1u;   // first / last unit of the item
+    int v_first = (int)((i_lo * (unsigned)V) / U);
+    while (range_lo(v_first + 1) <= i_lo) ++v_first;
+    while (range_lo(v_first) > i_lo) --v_first;
+    int v_last = (int)((i_hi * (unsigned)V) / U);
+    while (range_lo(v_last + 1) <= i_hi) ++v_last;
+    while (range_lo(v_last) > i_hi) --v_last;
+    const int nfrag = v_last - v_first + 1;
+    const int nparts = nfrag * ks;
     bool do_epi = true;
-    if (ks > 1) {
-      float* sp = a.scratch + ((size_t)item * ks) * (size_t)(m * ROWS);
+    if (nparts > 1) {
+      const size_t fsz = (size_t)(m * ROWS);
+      float* sp = a.scratch + ((size_t)item * ks) * a.fmax * fsz;
+      float* mine = sp + ((size_t)slice * a.fmax + (vw - v_first)) * fsz;
 #pragma unroll
       for (int j = 0; j < RPL; ++j)
 #pragma unroll
         for (int tok = 0; tok < MP; ++tok)
-          if (tok < m) sp[(size_t)slice * (m * ROWS) + tok * ROWS + j * 32 + lane] = v[j][tok];
+          if (tok < m) mine[tok * ROWS + j * 32 + lane] = v[j][tok];
       __threadfence();
       __syncwarp();
       unsigned prev = 0;
-      if (lane == 0) prev = atomicInc(a.counters + item, (unsigned)ks - 1u);
+      if (lane == 0) prev = atomicInc(a.counters + item, (unsigned)nparts - 1u);
       prev = __shfl_sync(0xffffffffu, prev, 0);
-      do_epi = prev == (unsigned)ks - 1u;
+      do_epi = prev == (unsigned)nparts - 1u;
       if (do_epi) {
         __threadfence();
 #pragma unroll
@@ -421,8 +469,19 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
 #pragma unroll
           for (int tok = 0; tok < MP; ++tok) {
             if (tok < m) {
+              // (slice, fragment) order; eight loads in flight at a time
               float s = 0.f;
-              for (int sl = 0; sl < ks; ++sl) s += __ldcg(sp + (size_t)sl * (m * ROWS) + tok * ROWS + j * 32 + lane);
+              for (int p0 = 0; p0 < nparts; p0 += 8) {
+                float pv[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                  const int pidx = p0 + i;
+                  const int sl = pidx / nfrag, f = pidx - sl * nfrag;
+                  pv[i] = pidx < nparts ? __ldcg(sp + ((size_t)sl * a.fmax + f) * fsz + tok * ROWS + j * 32 + lane) : 0.f;
+                }
+#pragma unroll
+                for (int i = 0; i < 8; ++i) s += pv[i];
+              }
               v[j][tok] = s;
             }
           }
@@ -541,6 +600,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
         }
       }
     }
+   }
   }
   if (failed) {
     // Give copies still in flight a bounded chance to land before the CTA's shared memory is released.
@@ -576,7 +636,8 @@ static int launch_one(const WqGemvArgs& a, cudaStream_t st) {
   // persistent grid of (CTAs per slice) x ks CTAs: every SM carries the same number of CTAs
   long cps = ((long)sm_count * occ) / a.ks;
   if (cps < 1) cps = 1;
-  if (cps * kGemvWarps > nitems) cps = (nitems + kGemvWarps - 1) / kGemvWarps;   // never more warps than items
+  const long vcps = (a.vworkers + kGemvWarps - 1) / kGemvWarps;
+  if (cps > vcps) cps = vcps;                                                     // never more warps than workers
   const long grid = cps * a.ks;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
@@ -606,10 +667,29 @@ static int launch_bg(const WqGemvArgs& a, cudaStream_t st) {
 
 using namespace b2;
 
-// Scratch floats for split-k: [item][ks][m][rows per item] = n * ks * m for any rb.
-B2_API long b2_wq_gemv_scratch_floats(int n, int ks, int m) {
-  if (ks <= 1) return 0;
-  return ((long)n + 63) / 64 * 64 * ks * m;
+// Virtual workers per slice and the most fragments an item can be cut into, both functions of the shape only.
+// kVirtualCtas is the resident-CTA count the schedule is laid out for (2 per SM on a 148-SM part).
+static const int kVirtualCtas = 296;
+B2_API int b2_wq_gemv_vworkers(int n, int k, int ks, int rb) {
+  const long nitems = (n / 32 + rb / 2 - 1) / (rb / 2);
+  const long U = nitems * (k / 128 / ks);
+  long V = (long)(kVirtualCtas / ks) * kGemvWarps;
+  if (V < 1) V = 1;
+  if (V > U) V = U;
+  return (int)V;
+}
+B2_API int b2_wq_gemv_fmax(int n, int k, int ks, int rb) {
+  const long nitems = (n / 32 + rb / 2 - 1) / (rb / 2);
+  const long nb = k / 128 / ks;
+  const long U = nitems * nb;
+  const long V = b2_wq_gemv_vworkers(n, k, ks, rb);
+  const long per = U / V;                       // every worker owns per or per + 1 units
+  return (int)((nb + per - 1) / per + 1);
+}
+// Scratch floats for the split partials: [item][ks][fmax][m][rows per item].
+B2_API long b2_wq_gemv_scratch_floats(int n, int k, int ks, int rb, int m) {
+  const long nitems = (n / 32 + rb / 2 - 1) / (rb / 2);
+  return nitems * ks * b2_wq_gemv_fmax(n, k, ks, rb) * (long)m * rb * 16;
 }
 
 // Launches the GEMV described by *args on `stream`.  Returns a b2::Status; nothing is launched on B2_ERR_ARG.
@@ -621,7 +701,10 @@ B2_API int b2_wq_gemv(const WqGemvArgs* args, cudaStream_t stream) {
   if (a.n % 32 || a.k % 128 || a.ks < 1 || a.ks > kMaxKs || a.ks > a.k / 128) return B2_ERR_ARG;
   if (a.group != 64 && a.group != 128) return B2_ERR_ARG;
   if (a.rb != 2 && a.rb != 4) return B2_ERR_ARG;
-  if (a.ks > 1 && (!a.scratch || !a.counters)) return B2_ERR_ARG;
+  if (!a.scratch || !a.counters) return B2_ERR_ARG;
+  if (a.k / 128 % a.ks) return B2_ERR_ARG;
+  if ((double)a.vworkers * (double)(a.n / 32) * (double)(a.k / 128 / a.ks) >= 4.0e9) return B2_ERR_ARG;   // 32-bit schedule arithmetic
+  if (a.vworkers != b2_wq_gemv_vworkers(a.n, a.k, a.ks, a.rb) || a.fmax != b2_wq_gemv_fmax(a.n, a.k, a.ks, a.rb)) return B2_ERR_ARG;
   if ((a.ldx % 8) || (reinterpret_cast<uintptr_t>(a.x) & 15)) return B2_ERR_ARG;
   if (a.epi == EPI_TP_RESID && (a.tp.size < 1 || a.tp.size > kMaxTp)) return B2_ERR_ARG;
   switch (a.bits * 1000 + a.group) {

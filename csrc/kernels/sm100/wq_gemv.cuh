@@ -41,6 +41,7 @@ struct WqGemvArgs {
   int bits, group;
   int ks;                // k slices (a function of the linear's shape only)
   int rb;                // row blocks per warp item: 2 (32 rows) or 4 (64 rows)
+  int vworkers, fmax;    // b2_wq_gemv_vworkers / b2_wq_gemv_fmax of (n, k, ks, rb)
   int pro;
   const bf16* x; long ldx;
   const float* ss_in; int ss_parts; int ss_ld;
@@ -61,8 +62,9 @@ struct WqGemvArgs {
 
 // Host entry points (C ABI).
 B2_API int b2_wq_gemv(const b2::WqGemvArgs* args, cudaStream_t stream);
-B2_API long b2_wq_gemv_scratch_floats(int n, int ks, int m);
-B2_API int b2_wq_gemv_parts(int n, int rb);
+B2_API int b2_wq_gemv_vworkers(int n, int k, int ks, int rb);
+B2_API int b2_wq_gemv_fmax(int n, int k, int ks, int rb);
+B2_API long b2_wq_gemv_scratch_floats(int n, int k, int ks, int rb, int m);
 B2_API long b2_wq_bytes(int n, int k, int bits, int group);
 B2_API int b2_wq_dequant(const uint8_t* wq, int n, int k, int bits, int group, bf16* out, long ldo, cudaStream_t stream);
 B2_API int b2_wq_repack(const int32_t* packed, const void* scale, int scale_is_bf16, const __half* zero, int n, int k,
