@@ -133,6 +133,27 @@ def profile_gemv(args):
     print("profile_gemv done")
 
 
+def bench_gemm(args):
+    """tcgen05 GEMM vs the library GEMM (torch.matmul -> cuBLAS) on the prefill shapes of the 32B model."""
+    from .ops import gemm as G
+    dev = "cuda:0"
+    pk = peaks()
+    flush = L2Flusher(dev)
+    shapes = [("qkv", 10240, 5120), ("o", 5120, 8192), ("gate_up", 51200, 5120), ("down", 5120, 25600)]
+    for M in ([2048] if args.small else [512, 2048, 8192]):
+        for name, n, k in shapes:
+            a = torch.randn(M, k, device=dev).to(torch.bfloat16)
+            b = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+            out = torch.empty(M, n, dtype=torch.bfloat16, device=dev)
+            ours, _ = time_cuda(lambda: G.gemm_bf16(a, b, out=out), iters=10, warmup=3, flush=flush)
+            lib, _ = time_cuda(lambda: torch.matmul(a, b.t(), out=out), iters=10, warmup=3, flush=flush)
+            fl = 2.0 * M * n * k
+            print(json.dumps(dict(name=name, M=M, n=n, k=k, ours_us=round(ours, 1), cublas_us=round(lib, 1),
+                                  ours_tflops=round(fl / ours / 1e6, 1), cublas_tflops=round(fl / lib / 1e6, 1),
+                                  frac_of_measured_peak=round(fl / ours / 1e6 / pk["bf16_tflops"], 3))), flush=True)
+    print(json.dumps({"peaks": pk, "timing": "CUDA events, median of 10, L2 flushed between launches"}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv"])
@@ -145,6 +166,8 @@ def main(argv=None):
         bench_gemv(args)
     elif args.what == "profile_gemv":
         profile_gemv(args)
+    elif args.what == "gemm":
+        bench_gemm(args)
     else:
         raise SystemExit(f"{args.what}: not available yet")
 

@@ -260,7 +260,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
   }
 }
 
-// Combine the splits of every (token, q head) in split order.
+// Combine the splits of every (token, q head) in split order.  One warp per (token, head); the scalar pass over the
+// (max, sum) pairs runs lane-parallel, the accumulation over splits keeps eight loads in flight and adds in order.
 template <int HD>
 __global__ void attn_merge_kernel(const AttnDecodeArgs a) {
   pdl_wait();
@@ -271,21 +272,33 @@ __global__ void attn_merge_kernel(const AttnDecodeArgs a) {
   const int tok = wid / a.hq, head = wid - tok * a.hq;
   const int ns = (a.tok_pos[tok] + a.split_keys) / a.split_keys;   // ceil((pos + 1) / split_keys)
   const float* po = a.part_o + ((size_t)tok * a.hq + head) * a.max_splits * HD;
-  const float* pm = a.part_ml + ((size_t)tok * a.hq + head) * a.max_splits * 2;
+  const float2* pm = reinterpret_cast<const float2*>(a.part_ml + ((size_t)tok * a.hq + head) * a.max_splits * 2);
   float M = -INFINITY;
-  for (int s = 0; s < ns; ++s) M = fmaxf(M, pm[2 * s]);
+  for (int s = lane; s < ns; s += 32) M = fmaxf(M, pm[s].x);
+  M = warp_max(M);
   constexpr int PER = HD / 32;
   float acc[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) acc[i] = 0.f;
   float L = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float m = pm[2 * s];
-    if (m == -INFINITY) continue;
-    const float w = exp2f(m - M);
-    L += pm[2 * s + 1] * w;
+  for (int s0 = 0; s0 < ns; s0 += 8) {
+    float2 ml[8];
+    float pv[8][PER];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) acc[i] += po[(size_t)s * HD + lane * PER + i] * w;
+    for (int j = 0; j < 8; ++j) {
+      const int s = s0 + j;
+      ml[j] = s < ns ? pm[s] : make_float2(-INFINITY, 0.f);
+#pragma unroll
+      for (int i = 0; i < PER; ++i) pv[j][i] = s < ns ? po[(size_t)s * HD + lane * PER + i] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (ml[j].x == -INFINITY) continue;
+      const float w = exp2f(ml[j].x - M);
+      L += ml[j].y * w;
+#pragma unroll
+      for (int i = 0; i < PER; ++i) acc[i] += pv[j][i] * w;
+    }
   }
   const float inv = L > 0.f ? 1.f / L : 0.f;
   bf16* out = a.out + (size_t)tok * a.ldo + (size_t)head * HD + lane * PER;

@@ -182,10 +182,18 @@ __global__ void argmax_final_kernel(const float* __restrict__ val, const int* __
   const int tok = blockIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int p = threadIdx.x; p < parts; p += blockDim.x) {
-    const float v = val[(size_t)p * ld + tok];
-    const int i = idx[(size_t)p * ld + tok];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  for (int p0 = threadIdx.x; p0 < parts; p0 += blockDim.x * 8) {   // eight loads in flight per thread
+    float pv[8];
+    int pi[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int p = p0 + j * blockDim.x;
+      pv[j] = p < parts ? val[(size_t)p * ld + tok] : -INFINITY;
+      pi[j] = p < parts ? idx[(size_t)p * ld + tok] : 0x7fffffff;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (pv[j] > best || (pv[j] == best && pi[j] < bi)) { best = pv[j]; bi = pi[j]; }
   }
   __shared__ float sv[32];
   __shared__ int si[32];
@@ -306,7 +314,7 @@ B2_API int b2_swiglu_interleaved(const bf16* gu, long ldg, int n_tok, int f, bf1
 B2_API int b2_argmax_final(const float* val, const int* idx, int parts, int ld, int n_tok, int* out_ids, float* out_val,
                            cudaStream_t st) {
   if (n_tok <= 0 || parts <= 0) return B2_ERR_ARG;
-  return launch_pdl(argmax_final_kernel, dim3(n_tok), dim3(256), 0, st, val, idx, parts, ld, out_ids, out_val);
+  return launch_pdl(argmax_final_kernel, dim3(n_tok), dim3(1024), 0, st, val, idx, parts, ld, out_ids, out_val);
 }
 
 B2_API int b2_argmax_rows(const float* logits, long ld, int n_tok, int n_valid, int* out_ids, cudaStream_t st) {
