@@ -77,6 +77,17 @@ class TpPush(C.Structure):
     ]
 
 
+class CommArgs(C.Structure):
+    _fields_ = [
+        ("inbox", C.c_void_p * K_MAX_TP),
+        ("rank", C.c_int), ("size", C.c_int),
+        ("slot_off", C.c_long), ("clear_off", C.c_long), ("slot_stride", C.c_long),
+        ("status", C.c_void_p),
+        ("timeout_ns", C.c_ulonglong),
+        ("skip_push", C.c_int),
+    ]
+
+
 class WqGemvArgs(C.Structure):
     _fields_ = [
         ("wq", C.c_void_p),
@@ -145,6 +156,16 @@ def _declare(lib: C.CDLL):
         "b2_fill_u32": ([vp, C.c_uint32, l, vp], i),
         "b2_attn_decode": ([C.POINTER(AttnDecodeArgs), i, vp], i),
         "b2_attn_decode_smem_bytes": ([i], i),
+        "b2_ipc_alloc": ([C.c_size_t, C.POINTER(vp), C.c_char_p], i),
+        "b2_ipc_open": ([C.c_char_p, C.POINTER(vp)], i),
+        "b2_ipc_close": ([vp], i),
+        "b2_ipc_free": ([vp], i),
+        "b2_can_access_peer": ([i, i], i),
+        "b2_comm_all_reduce": ([C.POINTER(CommArgs), vp, vp, l, vp, vp, vp], i),
+        "b2_comm_all_gather": ([C.POINTER(CommArgs), vp, l, vp, vp], i),
+        "b2_comm_reduce_scatter": ([C.POINTER(CommArgs), vp, l, vp, vp], i),
+        "b2_comm_barrier": ([C.POINTER(CommArgs), vp], i),
+        "b2_comm_argmax_combine": ([C.POINTER(CommArgs), vp, vp, i, vp, vp, vp], i),
         "b2_gemm_bf16": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp, vp], i),
     }
     for name, (args, res) in sig.items():

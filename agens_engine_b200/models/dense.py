@@ -42,8 +42,10 @@ class PagePool:
 
 class DenseModel:
     def __init__(self, cfg: ModelConfig, device="cuda:0", max_seqs: int = 1, max_ctx: int = 4096,
-                 n_pages: Optional[int] = None, split_keys: int = 64, prefill_chunk: int = 256):
+                 n_pages: Optional[int] = None, split_keys: int = 64, prefill_chunk: int = 256,
+                 lm_rows: Optional[int] = None):
         self.cfg, self.dev = cfg, torch.device(device)
+        self.lm_rows = lm_rows or cfg.vocab          # rows of the (possibly vocab-sharded, padded) lm_head
         self.max_seqs, self.max_ctx, self.split_keys = max_seqs, max_ctx, split_keys
         self.prefill_chunk = prefill_chunk
         self.pages_per_seq = (max_ctx + cfg.page_size - 1) // cfg.page_size
@@ -120,10 +122,11 @@ class DenseModel:
         self.act = bf(M, cfg.ffn)
         self.part_o = torch.empty(M, cfg.n_heads, self.max_splits, cfg.head_dim, dtype=torch.float32, device=dev)
         self.part_ml = torch.empty(M, cfg.n_heads, self.max_splits, 2, dtype=torch.float32, device=dev)
-        lm_panels = cfg.vocab // 32
+        lm_panels = (self.lm_rows + 31) // 32
         self.amax_val = torch.empty(lm_panels, L.SS_LD, dtype=torch.float32, device=dev)
         self.amax_idx = torch.empty(lm_panels, L.SS_LD, dtype=torch.int32, device=dev)
-        self.logits = torch.empty(M, cfg.vocab, dtype=torch.float32, device=dev)
+        self.logits = torch.empty(M, self.lm_rows, dtype=torch.float32, device=dev)
+        self.out_val = torch.empty(M, dtype=torch.float32, device=dev)
         self.status = i32(1)
         self.inv_freq = basic.rope_inv_freq(cfg.head_dim, cfg.rope_theta, dev)
         self.ws = L.GemvWorkspace(dev, floats=max(4 << 20, 2 * cfg.d_model * 64 * M), panels=max(1 << 16, lm_panels))
@@ -188,21 +191,37 @@ class DenseModel:
             A.attn_decode(self.q[:m], self.kv[li], self.block_table, self.grp_tok0[:n_groups], self.grp_cnt[:n_groups],
                           self.tok_pos, self.tok_seq, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.split_keys,
                           self.max_splits, part_o=self.part_o, part_ml=self.part_ml, status=self.status, out=self.attn[:m])
-            L.gemv(d["o"], self.attn[:m], ws, epi=EPI_RESID, resid=h_a, out=h_b, ss_out=self.ss_b)
-            L.gemv(d["gate_up"], h_b, ws, pro=PRO_NORM, ss_in=self.ss_b, ss_parts=d["o"].n_panels(), norm_w=d["ln2"],
+            parts_b = self._row_parallel(d["o"], self.attn[:m], h_a, h_b, self.ss_b, 2 * li)
+            L.gemv(d["gate_up"], h_b, ws, pro=PRO_NORM, ss_in=self.ss_b, ss_parts=parts_b, norm_w=d["ln2"],
                    eps=cfg.rms_eps, epi=EPI_SWIGLU, out=self.act[:m])
-            L.gemv(d["down"], self.act[:m], ws, epi=EPI_RESID, resid=h_b, out=h_a, ss_out=self.ss_a)
-            parts_a = d["down"].n_panels()
+            parts_a = self._row_parallel(d["down"], self.act[:m], h_b, h_a, self.ss_a, 2 * li + 1)
         return parts_a
+
+    def _row_parallel(self, lin, x, resid, out, ss_out, site: int):
+        """Row-parallel linear + residual add + next-norm statistics (one GPU: nothing to reduce).  Returns the
+        number of partial sums of squares it left in ``ss_out``."""
+        L.gemv(lin, x, self.ws, epi=EPI_RESID, resid=resid, out=out, ss_out=ss_out)
+        return lin.n_panels()
+
+    def _reduce_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """Sum of a row-parallel partial over the tensor-parallel ranks (prefill path); identity on one GPU."""
+        return x
 
     def _head_small(self, m: int, parts_a: int, want_logits: bool):
         cfg = self.cfg
         L.gemv(self.lm_head, self.h_a[:m], self.ws, pro=PRO_NORM, ss_in=self.ss_a, ss_parts=parts_a, norm_w=self.final_norm,
                eps=cfg.rms_eps, epi=EPI_ARGMAX, amax_val=self.amax_val, amax_idx=self.amax_idx,
-               n_valid=cfg.vocab_valid or cfg.vocab, yf=self.logits[:m] if want_logits else None)
+               n_valid=self._lm_valid(), yf=self.logits[:m] if want_logits else None)
         lib = _lib.cuda_lib()
         check(lib.b2_argmax_final(ptr(self.amax_val), ptr(self.amax_idx), self.lm_head.n_panels(), L.SS_LD, m,
-                                  ptr(self.out_ids), 0, current_stream()), "b2_argmax_final")
+                                  ptr(self.out_ids), ptr(self.out_val), current_stream()), "b2_argmax_final")
+        self._combine_argmax(m)
+
+    def _lm_valid(self) -> int:
+        return self.cfg.vocab_valid or self.cfg.vocab
+
+    def _combine_argmax(self, m: int):
+        """Vocab-parallel models merge the per-rank winners here; nothing to do on one GPU."""
 
     def forward_rows(self, ids: List[int], seqs: List[int], want_logits: bool = False):
         """Eager step over explicit rows: ``ids[i]`` is appended to sequence ``seqs[i]`` (rows of one sequence must be
@@ -274,11 +293,11 @@ class DenseModel:
                                self.kv[li], q, status=self.status)
             a = A.attn_prefill(q, self.kv[li], self.block_table, seq, pos0, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
                                status=self.status)
-            o = self._linear_big(d["o"], a)
+            o = self._reduce_rows(self._linear_big(d["o"], a))
             x, h = basic.rmsnorm(o, d["ln2"], cfg.rms_eps, resid=h)
             gu = self._linear_big(d["gate_up"], x)
             act = basic.swiglu_interleaved(gu)
-            delta = self._linear_big(d["down"], act)
+            delta = self._reduce_rows(self._linear_big(d["down"], act))
         if not final:
             return None
         hl = (h[-1:].float() + delta[-1:].float()).to(torch.bfloat16)

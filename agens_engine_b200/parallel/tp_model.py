@@ -1,0 +1,153 @@
+"""Tensor-parallel dense decoder: one process per GPU, weights sharded, collectives fused into the kernels.
+
+Sharding (reference rules: ``crates/agens-cli/src/m1.rs:41-98``): q/k/v and gate/up are column parallel (heads and FFN
+features split), o_proj and down_proj are row parallel, the lm_head is vocab parallel, embeddings and norms are
+replicated.  On the decode path the two row-parallel linears of a layer run as ONE kernel each: the GEMV epilogue
+pushes its partial into every rank's inbox over NVLink, sums all ranks in rank order, adds the residual and leaves the
+next norm's statistics (``EPI_TP_RESID`` in ``wq_gemv.cu``) -- no NCCL call and no separate all-reduce launch.  The
+lm_head produces per-rank (value, index) winners that are exchanged and merged by ``b2_comm_argmax_combine``.
+Prefill chunks use NCCL all-reduce on the row-parallel outputs (the baseline path) for now.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _lib
+from .._lib import EPI_TP_RESID, check, current_stream, ptr
+from ..models.config import LINEARS, ModelConfig
+from ..models.dense import M_GEMV, DenseModel
+from ..ops import linear as L
+from ..utils import quant
+from .symm import SymmetricInbox
+
+
+def local_config(cfg: ModelConfig, world: int) -> ModelConfig:
+    assert cfg.n_heads % world == 0 and cfg.n_kv_heads % world == 0 and cfg.ffn % (world * 128) == 0
+    return dataclasses.replace(cfg, name=f"{cfg.name}/tp{world}", n_heads=cfg.n_heads // world,
+                               n_kv_heads=cfg.n_kv_heads // world, ffn=cfg.ffn // world)
+
+
+def _pad32(n: int) -> int:
+    return (n + 31) // 32 * 32
+
+
+class TpDenseModel(DenseModel):
+    def __init__(self, cfg: ModelConfig, device, rank: int, world: int, use_nccl_decode: bool = False, **kw):
+        self.full_cfg, self.rank, self.world = cfg, rank, world
+        self.vocab_shard = (cfg.vocab + world - 1) // world
+        self.use_nccl_decode = use_nccl_decode
+        super().__init__(local_config(cfg, world), device, lm_rows=_pad32(self.vocab_shard), **kw)
+        n_sites = 2 * cfg.n_layers + 1
+        self.inbox = SymmetricInbox(rank, world, M_GEMV * cfg.d_model, n_sites, self.dev)
+        self.n_sites = n_sites
+        self.idx_off = torch.full((M_GEMV,), rank * self.vocab_shard, dtype=torch.int32, device=self.dev)
+        self.skip_push_site = -1     # test hook: the call site whose push this rank drops
+
+    # ------------------------------------------------------------------------------------------------ weights
+    @staticmethod
+    def random_init(cfg: ModelConfig, device, seed: int, rank: int, world: int, **kw) -> "TpDenseModel":
+        m = TpDenseModel(cfg, device, rank, world, **kw)
+        lc = m.cfg
+        shapes = lc.linear_shapes()
+        g = torch.Generator(device=m.dev).manual_seed(seed)     # replicated tensors: same seed on every rank
+        for l in range(cfg.n_layers):
+            d = {}
+            for i, lin in enumerate(LINEARS):
+                n, k = shapes[lin]
+                d[lin] = L.WqLinear.random(n, k, cfg.bits_of(l, lin), cfg.group, m.dev,
+                                           seed=(seed * 1000003 + l * 8 + i) * 64 + rank)
+            d["ln1"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
+            d["ln2"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
+            m.layers.append(d)
+        m.embed = (torch.randn(cfg.vocab, cfg.d_model, device=m.dev, generator=g) * 0.02).to(torch.bfloat16)
+        m.final_norm = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
+        m.lm_head = L.WqLinear.random(m.lm_rows, cfg.d_model, cfg.lm_head_bits, cfg.group, m.dev,
+                                      seed=(seed * 1000003 + 999983) * 64 + rank)
+        return m.finalize()
+
+    @staticmethod
+    def from_oracle(ow, device, rank: int, world: int, **kw) -> "TpDenseModel":
+        """Shard a full set of oracle weights (tests: TP-N logits against TP1)."""
+        cfg = ow.cfg
+        m = TpDenseModel(cfg, device, rank, world, **kw)
+        hd = cfg.head_dim
+        hq, hkv, f = cfg.n_heads // world, cfg.n_kv_heads // world, cfg.ffn // world
+
+        def rows(ql, idx):
+            return quant.QuantLinear(len(idx), ql.k, ql.bits, ql.group, ql.codes[idx], ql.scale[idx], ql.zero[idx])
+
+        def cols(ql, k0, k1):
+            g0, g1 = k0 // ql.group, k1 // ql.group
+            return quant.QuantLinear(ql.n, k1 - k0, ql.bits, ql.group, ql.codes[:, k0:k1].contiguous(),
+                                     ql.scale[:, g0:g1].contiguous(), ql.zero[:, g0:g1].contiguous())
+
+        for l, lay in enumerate(ow.layers):
+            q = ow.quant
+            qi = torch.arange(rank * hq * hd, (rank + 1) * hq * hd)
+            ki = cfg.q_dim + torch.arange(rank * hkv * hd, (rank + 1) * hkv * hd)
+            vi = cfg.q_dim + cfg.kv_dim + torch.arange(rank * hkv * hd, (rank + 1) * hkv * hd)
+            d = {"qkv": L.WqLinear.from_quant(rows(q[f"{l}.qkv"], torch.cat([qi, ki, vi])), m.dev),
+                 "o": L.WqLinear.from_quant(cols(q[f"{l}.o"], rank * hq * hd, (rank + 1) * hq * hd), m.dev),
+                 # merged gate_up rows come in blocks of 16 (8 gate + 8 up) per 8 features
+                 "gate_up": L.WqLinear.from_quant(rows(q[f"{l}.gate_up"], torch.arange(rank * 2 * f, (rank + 1) * 2 * f)), m.dev),
+                 "down": L.WqLinear.from_quant(cols(q[f"{l}.down"], rank * f, (rank + 1) * f), m.dev),
+                 "ln1": lay["ln1"].to(m.dev), "ln2": lay["ln2"].to(m.dev)}
+            m.layers.append(d)
+        m.embed = ow.embed.to(m.dev)
+        m.final_norm = ow.final_norm.to(m.dev)
+        ql = ow.quant["lm_head"]
+        lo, hi = rank * m.vocab_shard, min(cfg.vocab, (rank + 1) * m.vocab_shard)
+        idx = torch.arange(lo, hi)
+        pad = m.lm_rows - (hi - lo)
+        sh = rows(ql, idx)
+        if pad:
+            sh = quant.QuantLinear(m.lm_rows, ql.k, ql.bits, ql.group,
+                                   torch.cat([sh.codes, torch.zeros(pad, ql.k, dtype=torch.uint8)]),
+                                   torch.cat([sh.scale, torch.zeros(pad, ql.k // ql.group, dtype=torch.float16)]),
+                                   torch.cat([sh.zero, torch.zeros(pad, ql.k // ql.group, dtype=torch.float16)]))
+        m.lm_head = L.WqLinear.from_quant(sh, m.dev)
+        return m.finalize()
+
+    # ------------------------------------------------------------------------------------------------ collectives
+    def _row_parallel(self, lin, x, resid, out, ss_out, site: int):
+        if self.use_nccl_decode:
+            # baseline: library all-reduce between an unfused GEMV and a separate add + statistics pass
+            part = L.gemv(lin, x, self.ws, epi=_lib.EPI_F32)
+            dist.all_reduce(part)
+            out.copy_((part + resid.float()).to(torch.bfloat16))
+            from ..ops import basic
+            basic.sumsq(out, ss_out)
+            return 1
+        prev = (site - 1) % self.n_sites
+        tp = self.inbox.tp_push(site, prev, skip_push=(site == self.skip_push_site))
+        L.gemv(lin, x, self.ws, epi=EPI_TP_RESID, resid=resid, out=out, ss_out=ss_out, tp=tp)
+        return lin.n_panels()
+
+    def _reduce_rows(self, x: torch.Tensor) -> torch.Tensor:
+        y = x.float()
+        dist.all_reduce(y)
+        return y.to(torch.bfloat16)
+
+    def _lm_valid(self) -> int:
+        valid = self.full_cfg.vocab_valid or self.full_cfg.vocab
+        lo = self.rank * self.vocab_shard
+        return max(0, min(self.vocab_shard, valid - lo))
+
+    def _combine_argmax(self, m: int):
+        lib = _lib.cuda_lib()
+        self.out_ids[:m].add_(self.idx_off[:m])
+        site = self.n_sites - 1
+        a = self.inbox.comm_args(site, site - 1, skip_push=(site == self.skip_push_site))
+        check(lib.b2_comm_argmax_combine(C.byref(a), ptr(self.out_val), ptr(self.out_ids), m, ptr(self.out_ids), 0,
+                                         current_stream()), "b2_comm_argmax_combine")
+
+    def weight_bytes(self) -> int:
+        return super().weight_bytes()
+
+    def launches_per_step(self, batch: int = 1) -> int:
+        return super().launches_per_step(batch) + 1

@@ -1,0 +1,101 @@
+"""Worker of the multi-GPU tests (launched by tests/test_tp_gpu.py through torch.distributed.run, one rank per GPU)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from agens_engine_b200 import _lib  # noqa: E402
+from agens_engine_b200.models import config as C  # noqa: E402
+from agens_engine_b200.models import oracle as O  # noqa: E402
+from agens_engine_b200.models.dense import DenseModel  # noqa: E402
+from agens_engine_b200.parallel.comm import NcclComm, PushComm  # noqa: E402
+from agens_engine_b200.parallel.symm import SymmetricInbox  # noqa: E402
+from agens_engine_b200.parallel.tp_model import TpDenseModel  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    dist.init_process_group("nccl", device_id=torch.device(dev))
+    what = sys.argv[1]
+    if what == "collectives":
+        inbox = SymmetricInbox(rank, world, 1 << 16, 3, dev, timeout_s=1.0)
+        pc, nc = PushComm(inbox), NcclComm()
+        torch.manual_seed(rank)
+        for it in range(7):                       # more calls than slots: exercises the re-arm rotation
+            x = torch.randn(4096 * (1 + it % 3), device=dev)
+            a, b = pc.all_reduce(x), nc.all_reduce(x)
+            assert torch.allclose(a, b, rtol=1e-6, atol=1e-6), (it, (a - b).abs().max())
+            ga = [torch.empty_like(a) for _ in range(world)]
+            dist.all_gather(ga, a)
+            assert all(torch.equal(ga[0], g) for g in ga)       # rank-ordered sums: identical bits on every rank
+            xb = x.to(torch.bfloat16)
+            assert torch.allclose(pc.all_reduce(xb, out_dtype=torch.float32), nc.all_reduce(xb, out_dtype=torch.float32), atol=1e-5)
+        x = torch.randn(1024, device=dev)
+        assert torch.equal(pc.all_gather(x), nc.all_gather(x))
+        y = torch.randn(world, 2048, device=dev)
+        assert torch.allclose(pc.reduce_scatter(y), nc.reduce_scatter(y), rtol=1e-6, atol=1e-6)
+        pc.barrier()
+        torch.cuda.synchronize()
+        inbox.check_status()
+        # a lost message: the last rank drops its push; every rank's bounded wait runs out and reports, nothing hangs
+        inbox.timeout_ns = int(0.2e9)
+        out = pc.all_reduce(torch.ones(64, device=dev), skip_push=(rank == world - 1))
+        torch.cuda.synchronize()
+        assert int(inbox.status.item()) == _lib.B2_ERR_TIMEOUT
+        try:
+            inbox.check_status("all_reduce")
+            raise AssertionError("expected a timeout error")
+        except _lib.B2Error as e:
+            assert e.code == _lib.B2_ERR_TIMEOUT
+        # recovery: re-arm, agree on the host, carry on
+        dist.barrier()
+        inbox.rearm_all()
+        torch.cuda.synchronize()
+        dist.barrier()
+        pc2 = PushComm(inbox)
+        inbox.timeout_ns = int(1e9)
+        z = pc2.all_reduce(torch.full((64,), float(rank + 1), device=dev))
+        torch.cuda.synchronize()
+        assert torch.equal(z, torch.full((64,), float(world * (world + 1) // 2), device=dev))
+        inbox.check_status()
+        inbox.close()
+    elif what == "model":
+        cfg = C.oracle_tiny()
+        if cfg.n_kv_heads % world:
+            cfg.n_kv_heads = world * max(1, cfg.n_kv_heads // world)
+        ow = O.random_weights(cfg, seed=0)
+        torch.manual_seed(0)
+        prompt = torch.randint(0, cfg.vocab, (48,))
+        m = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=1, max_ctx=256)
+        m.new_seq(0)
+        toks = m.generate_greedy(0, prompt, 16)
+        m.inbox.check_status("tp decode")
+        ref = None
+        if rank == 0:
+            r = DenseModel.from_oracle(ow, dev, max_seqs=1, max_ctx=256)
+            r.new_seq(0)
+            ref = r.generate_greedy(0, prompt, 16)
+            agree = sum(int(a == b) for a, b in zip(toks.tolist(), ref.tolist()))
+            assert agree >= 14, (toks.tolist(), ref.tolist())
+        allt = [None] * world
+        dist.all_gather_object(allt, toks.tolist())
+        assert all(t == allt[0] for t in allt)          # every rank produced the same tokens
+        # fused path vs the NCCL baseline path: same tokens
+        b = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=1, max_ctx=256, use_nccl_decode=True)
+        b.new_seq(0)
+        tb = b.generate_greedy(0, prompt, 16)
+        agree = sum(int(x == y) for x, y in zip(toks.tolist(), tb.tolist()))
+        assert agree >= 14, (toks.tolist(), tb.tolist())
+        m.inbox.close(); b.inbox.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    print(f"rank {rank}: {what} ok")
+
+
+if __name__ == "__main__":
+    main()
