@@ -81,7 +81,7 @@ class CommArgs(C.Structure):
     _fields_ = [
         ("inbox", C.c_void_p * K_MAX_TP),
         ("rank", C.c_int), ("size", C.c_int),
-        ("slot_off", C.c_long), ("clear_off", C.c_long), ("slot_stride", C.c_long),
+        ("slot_off", C.c_long), ("clear_off", C.c_long), ("clear_n", C.c_long), ("slot_stride", C.c_long),
         ("status", C.c_void_p),
         ("timeout_ns", C.c_ulonglong),
         ("skip_push", C.c_int),

@@ -19,20 +19,22 @@ class PushComm:
     before it.  Not graph-safe by itself (the rotation is host state); graph-captured steps use fixed call-site slots."""
 
     def __init__(self, inbox: SymmetricInbox, first_slot: int = 0):
-        self.inbox, self.first, self.calls = inbox, first_slot, 0
+        self.inbox, self.first, self.calls, self.prev_n = inbox, first_slot, 0, 0
 
-    def _args(self, skip_push=False):
+    def _args(self, n: int, skip_push=False):
         cur = self.first + self.calls % 3
         prev = self.first + (self.calls - 1) % 3
         self.calls += 1
-        return self.inbox.comm_args(cur, prev, skip_push)
+        a = self.inbox.comm_args(cur, prev, skip_push, clear_n=self.prev_n)
+        self.prev_n = n
+        return a
 
     def all_reduce(self, x: torch.Tensor, out_dtype=None, skip_push: bool = False) -> torch.Tensor:
         lib = _lib.cuda_lib()
         n = x.numel()
         assert x.is_contiguous() and n % 4 == 0 and n <= self.inbox.slot_stride
         out = torch.empty_like(x, dtype=out_dtype or x.dtype)
-        a = self._args(skip_push)
+        a = self._args(n, skip_push)
         f32 = x.dtype == torch.float32
         with torch.cuda.device(x.device):
             check(lib.b2_comm_all_reduce(C.byref(a), ptr(x) if f32 else 0, 0 if f32 else ptr(x), n,
@@ -45,7 +47,7 @@ class PushComm:
         n = x.numel()
         assert x.dtype == torch.float32 and x.is_contiguous() and n % 4 == 0 and n <= self.inbox.slot_stride
         out = torch.empty(self.inbox.world, *x.shape, dtype=torch.float32, device=x.device)
-        a = self._args()
+        a = self._args(n)
         with torch.cuda.device(x.device):
             check(lib.b2_comm_all_gather(C.byref(a), ptr(x), n, ptr(out), current_stream()), "all_gather")
         return out
@@ -57,14 +59,14 @@ class PushComm:
         n = x.numel() // w
         assert n % 4 == 0 and n <= self.inbox.slot_stride
         out = torch.empty(x.shape[1:], dtype=torch.float32, device=x.device)
-        a = self._args()
+        a = self._args(n)
         with torch.cuda.device(x.device):
             check(lib.b2_comm_reduce_scatter(C.byref(a), ptr(x), n, ptr(out), current_stream()), "reduce_scatter")
         return out
 
     def barrier(self):
         lib = _lib.cuda_lib()
-        a = self._args()
+        a = self._args(4)
         with torch.cuda.device(self.inbox.device):
             check(lib.b2_comm_barrier(C.byref(a), current_stream()), "barrier")
 

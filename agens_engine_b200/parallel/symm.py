@@ -72,9 +72,13 @@ class SymmetricInbox:
         a.skip_push = 1 if skip_push else 0
         return a
 
-    def comm_args(self, slot: int, clear_slot: Optional[int] = None, skip_push: bool = False) -> CommArgs:
+    def comm_args(self, slot: int, clear_slot: Optional[int] = None, skip_push: bool = False,
+                  clear_n: Optional[int] = None) -> CommArgs:
+        """``clear_n``: floats per source rank that the earlier user of ``clear_slot`` wrote (default: whole slot)."""
         assert 0 <= slot < self.n_slots
-        return self._fill(CommArgs(), slot, clear_slot, skip_push)
+        a = self._fill(CommArgs(), slot, clear_slot, skip_push)
+        a.clear_n = self.slot_stride if clear_n is None else (clear_n + 3) // 4 * 4
+        return a
 
     def tp_push(self, slot: int, clear_slot: Optional[int] = None, skip_push: bool = False) -> TpPush:
         assert 0 <= slot < self.n_slots
@@ -93,13 +97,17 @@ class SymmetricInbox:
             check(lib.b2_fill_u32(self._own.value, SENTINEL, self.slot_floats * self.n_slots, _lib.current_stream()),
                   "b2_fill_u32")
 
-    def close(self):
+    def close(self, group=None):
+        """Unmap the peers' regions, wait until every rank has done so, then free the own region (an exporter must
+        not free memory that an importer still maps)."""
         lib = _lib.cuda_lib()
         with torch.cuda.device(self.device):
             torch.cuda.synchronize(self.device)
             for p in self._opened:
                 lib.b2_ipc_close(p)
             self._opened = []
+            if self.world > 1 and dist.is_initialized():
+                dist.barrier(group=group)
             if self._own:
                 lib.b2_ipc_free(self._own)
                 self._own = None

@@ -141,8 +141,18 @@ class TpDenseModel(DenseModel):
     def _combine_argmax(self, m: int):
         lib = _lib.cuda_lib()
         self.out_ids[:m].add_(self.idx_off[:m])
+        if self.use_nccl_decode:
+            # baseline: library all-gather of the per-rank winners, merged with framework ops
+            vals = torch.empty(self.world, m, dtype=torch.float32, device=self.dev)
+            ids = torch.empty(self.world, m, dtype=torch.int32, device=self.dev)
+            dist.all_gather_into_tensor(vals, self.out_val[:m].contiguous())
+            dist.all_gather_into_tensor(ids, self.out_ids[:m].contiguous())
+            best = vals.max(dim=0, keepdim=True).values
+            cand = torch.where(vals == best, ids, torch.full_like(ids, 0x7fffffff))
+            self.out_ids[:m].copy_(cand.min(dim=0).values)
+            return
         site = self.n_sites - 1
-        a = self.inbox.comm_args(site, site - 1, skip_push=(site == self.skip_push_site))
+        a = self.inbox.comm_args(site, site - 1, skip_push=(site == self.skip_push_site), clear_n=m * self.cfg.d_model)
         check(lib.b2_comm_argmax_combine(C.byref(a), ptr(self.out_val), ptr(self.out_ids), m, ptr(self.out_ids), 0,
                                          current_stream()), "b2_comm_argmax_combine")
 

@@ -183,6 +183,10 @@ def main():
             out["invalid"] = "debug run with fewer layers than the named config"
         print(json.dumps(out))
     if world > 1:
+        torch.cuda.synchronize()
+        model._graphs.clear()
+        model.inbox.close()
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

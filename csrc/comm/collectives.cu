@@ -46,6 +46,16 @@ __device__ __forceinline__ void clear_unit(float* p) {
   *reinterpret_cast<float4*>(p) = make_float4(n0, n0, n0, n0);
 }
 
+// Re-arm the slot that no rank writes before its next use, over the extent the earlier call used (grid-stride).
+__device__ __forceinline__ void rearm(const CommArgs& a) {
+  if (a.clear_off < 0) return;
+  const long nvec = a.clear_n >> 2;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long)gridDim.x * blockDim.x) {
+    float* clr = a.inbox[a.rank] + a.clear_off + (i << 2);
+    for (int src = 0; src < a.size; ++src) clear_unit(clr + (long)src * a.slot_stride);
+  }
+}
+
 // mode 0: all-reduce (n elements, every rank ends with the rank-ordered sum)
 // mode 1: all-gather (n elements per rank, out[src * n + e])
 // mode 2: reduce-scatter (input size * n elements; rank r ends with the sum of chunk r)
@@ -93,12 +103,8 @@ __global__ void push_collective_kernel(const CommArgs a, const float* __restrict
         *reinterpret_cast<uint2*>(out_bf16 + e) = *reinterpret_cast<const uint2*>(o);
       }
     }
-    // ---- re-arm the slot that no rank writes before its next use ----
-    if (a.clear_off >= 0) {
-      float* clr = a.inbox[a.rank] + a.clear_off + e;
-      for (int src = 0; src < a.size; ++src) clear_unit(clr + (long)src * a.slot_stride);
-    }
   }
+  rearm(a);
   if (timed_out) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
 }
 
@@ -109,6 +115,7 @@ __global__ void argmax_combine_kernel(const CommArgs a, const float* __restrict_
   pdl_wait();
   pdl_launch_dependents();
   const int tok = blockIdx.x * blockDim.x + threadIdx.x;
+  rearm(a);
   if (tok >= n_tok) return;
   const uint64_t t_start = globaltimer_ns();
   const long e = (long)tok * 4;
@@ -128,10 +135,6 @@ __global__ void argmax_combine_kernel(const CommArgs a, const float* __restrict_
   }
   out_idx[tok] = bi;
   if (out_val) out_val[tok] = best;
-  if (a.clear_off >= 0) {
-    float* clr = a.inbox[a.rank] + a.clear_off + e;
-    for (int src = 0; src < a.size; ++src) clear_unit(clr + (long)src * a.slot_stride);
-  }
   if (timed_out) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
 }
 
@@ -148,7 +151,8 @@ int launch_pdl_c(void (*kern)(KArgs...), dim3 grid, dim3 block, cudaStream_t st,
 
 bool args_ok(const CommArgs* a, long n) {
   return a && a->size >= 1 && a->size <= kCommMaxRanks && a->rank >= 0 && a->rank < a->size && n > 0 && (n % 4) == 0 &&
-         n <= a->slot_stride && (a->slot_off % 4) == 0 && (a->slot_stride % 4) == 0 && a->status;
+         n <= a->slot_stride && (a->slot_off % 4) == 0 && (a->slot_stride % 4) == 0 && a->status &&
+         (a->clear_off < 0 || (a->clear_n >= 0 && a->clear_n <= a->slot_stride && (a->clear_n % 4) == 0));
 }
 int grid_of(long nvec) {
   long b = (nvec + 255) / 256;
@@ -201,5 +205,9 @@ B2_API int b2_comm_barrier(const CommArgs* a, cudaStream_t st) {
 B2_API int b2_comm_argmax_combine(const CommArgs* a, const float* val, const int* idx, int n_tok, int* out_idx, float* out_val,
                                   cudaStream_t st) {
   if (!a || n_tok <= 0 || (long)n_tok * 4 > a->slot_stride || !a->status) return B2_ERR_ARG;
-  return launch_pdl_c(argmax_combine_kernel, dim3((n_tok + 63) / 64), dim3(64), st, *a, val, idx, n_tok, out_idx, out_val);
+  if (a->clear_off >= 0 && (a->clear_n < 0 || a->clear_n > a->slot_stride || (a->clear_n % 4))) return B2_ERR_ARG;
+  long blocks = (n_tok + 255) / 256;
+  const long cb = a->clear_off >= 0 ? (a->clear_n / 4 + 255) / 256 : 0;
+  if (cb > blocks) blocks = cb > 64 ? 64 : cb;
+  return launch_pdl_c(argmax_combine_kernel, dim3((unsigned)blocks), dim3(256), st, *a, val, idx, n_tok, out_idx, out_val);
 }

@@ -13,6 +13,7 @@ struct CommArgs {
   int rank, size;
   long slot_off;                 // float offset of this call's slot inside every region
   long clear_off;                // slot to re-arm with the sentinel (no rank writes it before its next use), -1: none
+  long clear_n;                  // floats per source rank to re-arm there (the extent the earlier call used)
   long slot_stride;              // floats per source rank inside a slot
   int* status;                   // device status word: B2_ERR_TIMEOUT when a wait ran out
   unsigned long long timeout_ns;

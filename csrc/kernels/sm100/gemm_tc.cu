@@ -5,7 +5,7 @@
 // kernels/m1/m1_model.cu:1875-1895).
 //
 // One CTA computes a 128 x 256 tile.  Warp 0 feeds a 4-stage shared-memory ring with TMA (cp.async.bulk.tensor, 128-byte
-// swizzle, no multicast); one elected thread of warp 1 issues tcgen05.mma (M 128, N 256, K 16 per instruction, operands
+// swizzle, every CTA loads its own tiles); one elected thread of warp 1 issues tcgen05.mma (M 128, N 256, K 16 per instruction, operands
 // read through shared-memory descriptors, accumulator = 256 TMEM columns) and commits stage releases and the final
 // "accumulator ready" arrival to mbarriers; warps 2..5 read the accumulator back with tcgen05.ld (each warp owns the
 // 32 TMEM lanes its warp id modulo 4 selects), add the optional residual, convert and store.

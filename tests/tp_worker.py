@@ -75,6 +75,7 @@ def main():
         m.new_seq(0)
         toks = m.generate_greedy(0, prompt, 16)
         m.inbox.check_status("tp decode")
+        print(f"rank {rank}: fused decode done", flush=True)
         ref = None
         if rank == 0:
             r = DenseModel.from_oracle(ow, dev, max_seqs=1, max_ctx=256)
@@ -88,10 +89,16 @@ def main():
         # fused path vs the NCCL baseline path: same tokens
         b = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=1, max_ctx=256, use_nccl_decode=True)
         b.new_seq(0)
+        print(f"rank {rank}: baseline model built", flush=True)
         tb = b.generate_greedy(0, prompt, 16)
+        print(f"rank {rank}: baseline decode done", flush=True)
         agree = sum(int(x == y) for x, y in zip(toks.tolist(), tb.tolist()))
         assert agree >= 14, (toks.tolist(), tb.tolist())
+        torch.cuda.synchronize()
+        print(f"rank {rank}: closing", flush=True)
+        m._graphs.clear(); b._graphs.clear()
         m.inbox.close(); b.inbox.close()
+        print(f"rank {rank}: closed", flush=True)
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: {what} ok")
