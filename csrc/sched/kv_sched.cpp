@@ -1,0 +1,324 @@
+// Host-side KV bookkeeping and scheduling policy: refcounted page allocator with fork, banker's-algorithm admission,
+// eviction order, SRPT chunk scheduling, copy-from-context drafter and the hash-chained prefix cache.
+//
+// Reference behaviour restated here: alloc_row / own_partial_page / fork (kernels/m1/m1_model.cu:1694-1716, 4526-4585,
+// 4869), KvPolicy + kv_safe + victim + prefill order (crates/agens-cli/src/serve.rs:343-422, 616-639), Lookup
+// (crates/agens-cli/src/lookup.rs:107-201) and PrefixCache (crates/agens-cli/src/prefix.rs).  Pages hold 16 tokens
+// here (the reference allocates single rows), so fork shares whole pages and copies at most one partial page.
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <list>
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#define B2H_API extern "C" __attribute__((visibility("default")))
+
+namespace b2 {
+
+// ------------------------------------------------------------------------------------------------ page allocator
+class PageAllocator {
+ public:
+  PageAllocator(int n_pages, int page_size) : page_size_(page_size), ref_(n_pages, 0) {
+    for (int i = n_pages - 1; i >= 0; --i) free_.push_back(i);
+  }
+  int free_pages() const { return (int)free_.size(); }
+  int n_pages() const { return (int)ref_.size(); }
+  int new_seq() { int id = next_id_++; seqs_[id] = Seq(); return id; }
+  bool has(int s) const { return seqs_.count(s) != 0; }
+  int seq_len(int s) const { return seqs_.at(s).len; }
+  // Grow `s` to hold n_tokens; returns number of pages newly taken, -1 if the pool cannot serve it (nothing changes).
+  int reserve(int s, int n_tokens) {
+    Seq& q = seqs_.at(s);
+    const int need = (n_tokens + page_size_ - 1) / page_size_;
+    const int extra = need - (int)q.pages.size();
+    if (extra <= 0) return 0;
+    if (extra > (int)free_.size()) return -1;
+    for (int i = 0; i < extra; ++i) { int p = free_.back(); free_.pop_back(); ref_[p] = 1; q.pages.push_back(p); }
+    return extra;
+  }
+  void set_len(int s, int n) { seqs_.at(s).len = n; }
+  // Drop everything past n_tokens (rejected speculative rows); returns pages released.
+  int truncate(int s, int n_tokens) {
+    Seq& q = seqs_.at(s);
+    q.len = std::min(q.len, n_tokens);
+    const int keep = (n_tokens + page_size_ - 1) / page_size_;
+    int rel = 0;
+    while ((int)q.pages.size() > keep) { rel += unref(q.pages.back()); q.pages.pop_back(); }
+    return rel;
+  }
+  // Fork: the child shares all full pages; a partial last page must be copied by the caller into the page returned in
+  // *copy_dst (source page in *copy_src), -1 when no copy is needed.  Returns the child id, -1 when no page is free.
+  int fork(int s, int* copy_src, int* copy_dst) {
+    const Seq& q = seqs_.at(s);
+    *copy_src = *copy_dst = -1;
+    const bool partial = q.len % page_size_ != 0;
+    if (partial && free_.empty()) return -1;
+    const int id = next_id_++;
+    Seq c;
+    c.len = q.len;
+    const int used = (q.len + page_size_ - 1) / page_size_;
+    for (int i = 0; i < used; ++i) {
+      if (i == used - 1 && partial) {
+        int p = free_.back(); free_.pop_back(); ref_[p] = 1;
+        *copy_src = q.pages[i]; *copy_dst = p;
+        c.pages.push_back(p);
+      } else { ++ref_[q.pages[i]]; c.pages.push_back(q.pages[i]); }
+    }
+    seqs_[id] = c;
+    return id;
+  }
+  int free_seq(int s) {
+    auto it = seqs_.find(s);
+    if (it == seqs_.end()) return 0;
+    int rel = 0;
+    for (int p : it->second.pages) rel += unref(p);
+    seqs_.erase(it);
+    return rel;
+  }
+  const std::vector<int>& pages(int s) const { return seqs_.at(s).pages; }
+  int refcount(int page) const { return ref_[page]; }
+  // Pages only this sequence holds (what freeing it would give back).
+  int exclusive_pages(int s) const { int n = 0; for (int p : seqs_.at(s).pages) n += ref_[p] == 1; return n; }
+ private:
+  struct Seq { std::vector<int> pages; int len = 0; };
+  int unref(int p) { if (--ref_[p] == 0) { free_.push_back(p); return 1; } return 0; }
+  int page_size_;
+  std::vector<int> ref_, free_;
+  std::unordered_map<int, Seq> seqs_;
+  int next_id_ = 0;
+};
+
+// ------------------------------------------------------------------------------------------------ banker's check
+// `avail` rows are free or reclaimable; item i may still take need[i] rows and gives back hold[i] when it finishes.
+// Safe iff some order lets every item finish: visit by need ascending (ties by hold), as with one resource class.
+static bool kv_safe(long avail, std::vector<std::pair<long, long>> items) {
+  std::sort(items.begin(), items.end());
+  for (auto& it : items) { if (it.first > avail) return false; avail += it.second; }
+  return true;
+}
+
+// Eviction classes in the order they are given up (serve.rs:616-639): unreferenced prefix snapshots (LRU), idle
+// conversations past the hold window (LRU), recently idle (most recent first), conversations with a queued turn
+// (most recent first).  Candidates: (kind 0 snapshot / 1 conversation, id, idle seconds, queued flag).
+struct EvictCand { int kind; long long id; double idle_s; int queued; };
+static int pick_victim(const EvictCand* c, int n, double hold_s, bool allow_protected) {
+  int best = -1;
+  auto cls = [&](const EvictCand& e) { return e.kind == 0 ? 0 : (e.queued ? 3 : (e.idle_s >= hold_s ? 1 : 2)); };
+  for (int i = 0; i < n; ++i) {
+    const int ci = cls(c[i]);
+    if (ci >= 2 && !allow_protected) continue;
+    if (best < 0) { best = i; continue; }
+    const int cb = cls(c[best]);
+    if (ci != cb) { if (ci < cb) best = i; continue; }
+    // classes 0,1: least recently used first; classes 2,3: most recently used first
+    if (ci <= 1 ? c[i].idle_s > c[best].idle_s : c[i].idle_s < c[best].idle_s) best = i;
+  }
+  return best;
+}
+
+// Which prefilling request gets the next chunk: shortest remaining prompt first, every `fair`-th chunk to the oldest.
+static int pick_prefill(const long* remaining, const double* age_s, int n, long chunk_index, int fair, int srpt) {
+  if (n <= 0) return -1;
+  int best = 0;
+  const bool oldest = !srpt || (fair > 0 && chunk_index % fair == fair - 1);
+  for (int i = 1; i < n; ++i) {
+    if (oldest ? age_s[i] > age_s[best] : (remaining[i] < remaining[best] || (remaining[i] == remaining[best] && age_s[i] > age_s[best]))) best = i;
+  }
+  return best;
+}
+
+// ------------------------------------------------------------------------------------------------ copy-from-context drafter
+class CopyLookup {
+ public:
+  static constexpr int kMaxDraft = 7, kCandidates = 24, kMaxMatch = 64, kBuckets = 6;
+  CopyLookup() {
+    const double prior[kBuckets] = {0.6, 1.0, 1.8, 2.6, 3.6, 4.6};
+    for (int i = 0; i < kBuckets; ++i) lk_[i] = {prior[i], 4.0};
+    dr_ = {2.0, 4.0};
+  }
+  void extend(const int* toks, int n) { hist_.insert(hist_.end(), toks, toks + n); }
+  void truncate(int n) { if (n < (int)hist_.size()) { hist_.resize(n); reindex(); } }
+  int size() const { return (int)hist_.size(); }
+  // Proposes up to 7 tokens that followed the longest earlier occurrence of the current suffix.  Returns the count
+  // (0 = use the other draft source); *match_len receives the matched suffix length.
+  int propose(int* out, int* match_len, bool copy_only) {
+    index_up_to((int)hist_.size() - 1);
+    pending_lookup_ = false;
+    const int n = (int)hist_.size();
+    if (n < 3) return 0;
+    const uint64_t key = bigram(hist_[n - 2], hist_[n - 1]);
+    auto it = idx_.find(key);
+    if (it == idx_.end()) return 0;
+    const std::vector<int>& pos = it->second;
+    int best_len = 0, best_p = -1, seen = 0;
+    for (int i = (int)pos.size() - 1; i >= 0 && seen < kCandidates; --i, ++seen) {
+      const int p = pos[i];              // bigram ends at p (p < n - 1)
+      int m = 2;
+      while (m < kMaxMatch && p - m >= 0 && hist_[p - m] == hist_[n - 1 - m]) ++m;
+      if (m > best_len && p + 1 < n) { best_len = m; best_p = p; }
+    }
+    if (best_p < 0) return 0;
+    const int b = bucket(best_len);
+    if (!copy_only && lk_[b].v <= dr_.v) return 0;           // the other source is expected to do better
+    int cnt = 0;
+    for (int q = best_p + 1; q < n && cnt < kMaxDraft; ++q) out[cnt++] = hist_[q];
+    *match_len = best_len;
+    pending_lookup_ = cnt > 0;
+    pending_bucket_ = b;
+    return cnt;
+  }
+  // Outcome of the verified step: `accepted` drafts were kept.
+  void record(int accepted) {
+    Mean& m = pending_lookup_ ? lk_[pending_bucket_] : dr_;
+    m.n += 1.0;
+    const double w = std::max(1.0 / m.n, 0.03);
+    m.v += w * (accepted - m.v);
+    pending_lookup_ = false;
+  }
+  double mean_lookup(int b) const { return lk_[b].v; }
+  double mean_drafter() const { return dr_.v; }
+ private:
+  struct Mean { double v, n; };
+  static uint64_t bigram(int a, int b) { return ((uint64_t)(uint32_t)a << 32) | (uint32_t)b; }
+  static int bucket(int m) { const int th[kBuckets] = {2, 3, 4, 6, 10, 16}; int b = 0; for (int i = 0; i < kBuckets; ++i) if (m >= th[i]) b = i; return b; }
+  void index_up_to(int end) {   // positions p in [1, end): bigram (p-1, p); the last position is the query itself
+    for (int p = std::max(indexed_, 1); p < end; ++p) idx_[bigram(hist_[p - 1], hist_[p])].push_back(p);
+    indexed_ = std::max(indexed_, end);
+  }
+  void reindex() { idx_.clear(); indexed_ = 0; }
+  std::vector<int> hist_;
+  std::unordered_map<uint64_t, std::vector<int>> idx_;
+  int indexed_ = 0;
+  Mean lk_[kBuckets], dr_;
+  bool pending_lookup_ = false;
+  int pending_bucket_ = 0;
+};
+
+// ------------------------------------------------------------------------------------------------ prefix cache
+// Snapshots at chunk boundaries keyed by a hash chain over token ids (and image keys); lookup returns the longest
+// cached prefix; insertion evicts least recently used entries that nobody references to stay inside the byte budget.
+class PrefixCache {
+ public:
+  explicit PrefixCache(long long budget_bytes, int chunk) : budget_(budget_bytes), chunk_(chunk) {}
+  static uint64_t mix(uint64_t h, uint64_t v) {
+    h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2);
+    h *= 0xff51afd7ed558ccdull;
+    return h ^ (h >> 33);
+  }
+  // Hash of the first n tokens, chained chunk by chunk so that equal prefixes give equal keys.
+  uint64_t key_of(const int* toks, int n, uint64_t salt) const {
+    uint64_t h = 0x243f6a8885a308d3ull ^ salt;
+    for (int i = 0; i < n; ++i) h = mix(h, (uint32_t)toks[i]);
+    return mix(h, (uint64_t)n);
+  }
+  // Longest cached prefix of toks that ends on a chunk boundary; returns its length (0 = none) and snapshot handle.
+  int lookup(const int* toks, int n, uint64_t salt, long long* handle) {
+    int best = 0;
+    uint64_t h = 0x243f6a8885a308d3ull ^ salt;
+    for (int i = 0; i < n; ++i) {
+      h = mix(h, (uint32_t)toks[i]);
+      if ((i + 1) % chunk_ == 0) {
+        auto it = map_.find(mix(h, (uint64_t)(i + 1)));
+        if (it != map_.end()) { best = i + 1; *handle = it->second->handle; touch(it->second); }
+      }
+    }
+    return best;
+  }
+  // Registers a snapshot of `bytes` for the first n tokens (n a multiple of the chunk).  Evicted handles are written
+  // to `evicted` (caller frees their device/host memory); returns their count, -1 if the snapshot cannot fit.
+  int insert(const int* toks, int n, uint64_t salt, long long handle, long long bytes, long long* evicted, int max_evicted) {
+    if (n % chunk_ != 0 || bytes > budget_) return -1;
+    const uint64_t k = key_of(toks, n, salt);
+    if (map_.count(k)) return 0;
+    int ne = 0;
+    while (used_ + bytes > budget_) {
+      auto victim = lru_.end();
+      for (auto it = lru_.begin(); it != lru_.end(); ++it) if (it->refs == 0) { victim = it; break; }
+      if (victim == lru_.end() || ne >= max_evicted) return -1;
+      evicted[ne++] = victim->handle;
+      used_ -= victim->bytes;
+      map_.erase(victim->key);
+      lru_.erase(victim);
+    }
+    lru_.push_back(Entry{k, handle, bytes, 0});
+    map_[k] = std::prev(lru_.end());
+    used_ += bytes;
+    return ne;
+  }
+  void ref(long long handle, int delta) { for (auto& e : lru_) if (e.handle == handle) e.refs += delta; }
+  long long used() const { return used_; }
+  int entries() const { return (int)lru_.size(); }
+  // Oldest unreferenced entry (eviction candidate of class 0), -1 if none.
+  long long evict_lru() {
+    for (auto it = lru_.begin(); it != lru_.end(); ++it)
+      if (it->refs == 0) { long long h = it->handle; used_ -= it->bytes; map_.erase(it->key); lru_.erase(it); return h; }
+    return -1;
+  }
+ private:
+  struct Entry { uint64_t key; long long handle, bytes; int refs; };
+  void touch(std::list<Entry>::iterator it) { lru_.splice(lru_.end(), lru_, it); }
+  long long budget_, used_ = 0;
+  int chunk_;
+  std::list<Entry> lru_;
+  std::unordered_map<uint64_t, std::list<Entry>::iterator> map_;
+};
+
+}  // namespace b2
+
+using namespace b2;
+
+// ---- C ABI ----
+B2H_API void* b2h_pages_new(int n_pages, int page_size) { return new PageAllocator(n_pages, page_size); }
+B2H_API void b2h_pages_free(void* a) { delete static_cast<PageAllocator*>(a); }
+B2H_API int b2h_pages_free_count(void* a) { return static_cast<PageAllocator*>(a)->free_pages(); }
+B2H_API int b2h_pages_new_seq(void* a) { return static_cast<PageAllocator*>(a)->new_seq(); }
+B2H_API int b2h_pages_reserve(void* a, int s, int n_tokens) { return static_cast<PageAllocator*>(a)->reserve(s, n_tokens); }
+B2H_API void b2h_pages_set_len(void* a, int s, int n) { static_cast<PageAllocator*>(a)->set_len(s, n); }
+B2H_API int b2h_pages_len(void* a, int s) { return static_cast<PageAllocator*>(a)->seq_len(s); }
+B2H_API int b2h_pages_truncate(void* a, int s, int n) { return static_cast<PageAllocator*>(a)->truncate(s, n); }
+B2H_API int b2h_pages_fork(void* a, int s, int* src, int* dst) { return static_cast<PageAllocator*>(a)->fork(s, src, dst); }
+B2H_API int b2h_pages_free_seq(void* a, int s) { return static_cast<PageAllocator*>(a)->free_seq(s); }
+B2H_API int b2h_pages_exclusive(void* a, int s) { return static_cast<PageAllocator*>(a)->exclusive_pages(s); }
+B2H_API int b2h_pages_refcount(void* a, int page) { return static_cast<PageAllocator*>(a)->refcount(page); }
+B2H_API int b2h_pages_list(void* a, int s, int* out, int cap) {
+  const auto& p = static_cast<PageAllocator*>(a)->pages(s);
+  const int n = std::min<int>((int)p.size(), cap);
+  std::memcpy(out, p.data(), sizeof(int) * n);
+  return (int)p.size();
+}
+
+B2H_API int b2h_kv_safe(long avail, const long* need, const long* hold, int n) {
+  std::vector<std::pair<long, long>> items;
+  for (int i = 0; i < n; ++i) items.emplace_back(need[i], hold[i]);
+  return kv_safe(avail, items) ? 1 : 0;
+}
+B2H_API int b2h_pick_victim(const int* kind, const long long* id, const double* idle_s, const int* queued, int n, double hold_s,
+                            int allow_protected) {
+  std::vector<EvictCand> c(n);
+  for (int i = 0; i < n; ++i) c[i] = EvictCand{kind[i], id[i], idle_s[i], queued[i]};
+  return pick_victim(c.data(), n, hold_s, allow_protected != 0);
+}
+B2H_API int b2h_pick_prefill(const long* remaining, const double* age_s, int n, long chunk_index, int fair, int srpt) {
+  return pick_prefill(remaining, age_s, n, chunk_index, fair, srpt);
+}
+
+B2H_API void* b2h_lookup_new() { return new CopyLookup(); }
+B2H_API void b2h_lookup_free(void* l) { delete static_cast<CopyLookup*>(l); }
+B2H_API void b2h_lookup_extend(void* l, const int* toks, int n) { static_cast<CopyLookup*>(l)->extend(toks, n); }
+B2H_API void b2h_lookup_truncate(void* l, int n) { static_cast<CopyLookup*>(l)->truncate(n); }
+B2H_API int b2h_lookup_propose(void* l, int* out, int* match_len, int copy_only) { return static_cast<CopyLookup*>(l)->propose(out, match_len, copy_only != 0); }
+B2H_API void b2h_lookup_record(void* l, int accepted) { static_cast<CopyLookup*>(l)->record(accepted); }
+B2H_API double b2h_lookup_mean(void* l, int bucket) { return bucket < 0 ? static_cast<CopyLookup*>(l)->mean_drafter() : static_cast<CopyLookup*>(l)->mean_lookup(bucket); }
+
+B2H_API void* b2h_prefix_new(long long budget_bytes, int chunk) { return new PrefixCache(budget_bytes, chunk); }
+B2H_API void b2h_prefix_free(void* p) { delete static_cast<PrefixCache*>(p); }
+B2H_API int b2h_prefix_lookup(void* p, const int* toks, int n, unsigned long long salt, long long* handle) { return static_cast<PrefixCache*>(p)->lookup(toks, n, salt, handle); }
+B2H_API int b2h_prefix_insert(void* p, const int* toks, int n, unsigned long long salt, long long handle, long long bytes, long long* evicted, int max_evicted) {
+  return static_cast<PrefixCache*>(p)->insert(toks, n, salt, handle, bytes, evicted, max_evicted);
+}
+B2H_API void b2h_prefix_ref(void* p, long long handle, int delta) { static_cast<PrefixCache*>(p)->ref(handle, delta); }
+B2H_API long long b2h_prefix_used(void* p) { return static_cast<PrefixCache*>(p)->used(); }
+B2H_API long long b2h_prefix_evict_lru(void* p) { return static_cast<PrefixCache*>(p)->evict_lru(); }
