@@ -1,0 +1,97 @@
+"""Checkpoint container tests on the CPU (model: the reference's toy 4-layer checkpoint tests,
+crates/agens-core/src/weights.rs:311-453: format detection, bad shapes, SHA sums, shard index cross-check)."""
+import json
+import os
+
+import pytest
+import torch
+
+from agens_engine_b200.models import config as C
+from agens_engine_b200.models import oracle as O
+from agens_engine_b200.utils import checkpoint as K
+from agens_engine_b200.utils import quant
+
+
+@pytest.fixture(scope="module")
+def ckpt(tmp_path_factory):
+    d = str(tmp_path_factory.mktemp("ckpt"))
+    ow = O.random_weights(C.oracle_tiny(), seed=1)
+    K.save_oracle(d, ow, shards=3)
+    return d, ow
+
+
+def test_safetensors_roundtrip(tmp_path):
+    p = str(tmp_path / "x.safetensors")
+    t = {"a": torch.arange(12, dtype=torch.int32).reshape(3, 4), "b": torch.randn(5).to(torch.bfloat16), "e": torch.zeros(0, 3)}
+    K.write_safetensors(p, t)
+    f = K.SafeTensorsFile(p)
+    assert set(f.keys()) == {"a", "b", "e"}
+    assert torch.equal(f.tensor("a"), t["a"]) and torch.equal(f.tensor("b"), t["b"]) and f.tensor("e").shape == (0, 3)
+    with pytest.raises(IOError):
+        K.SafeTensorsFile(str(tmp_path / "missing.safetensors"))
+    open(p, "r+b").write(b"\xff" * 8)
+    with pytest.raises(IOError):
+        K.SafeTensorsFile(p)
+
+
+def test_validate_detects_formats(ckpt):
+    d, ow = ckpt
+    rep = K.validate(d)
+    assert rep["ok"], rep["errors"]
+    assert rep["shards"] == 3
+    f = rep["linears"]
+    assert f["model.layers.0.self_attn.q_proj"] == {"format": "wq", "bits": 4, "group": 64, "asymmetric": True, "scale_dtype": "F16"}
+    assert f["model.layers.1.self_attn.o_proj"]["bits"] == 2 and f["model.layers.1.mlp.down_proj"]["bits"] == 3
+    info = K.inspect(d)
+    assert info["linear_formats"] == {"w4g64a": 8, "w2g64a": 4, "w3g64a": 3}
+
+
+def test_sha256_verify_and_tamper(ckpt, tmp_path):
+    d, _ = ckpt
+    r = K.verify(d)
+    assert r["files"] == 4 and r["ok"] == 4 and r["bad"] == []
+    import hashlib
+    fn = os.path.join(d, "config.json")
+    assert K.sha256_file(fn) == hashlib.sha256(open(fn, "rb").read()).hexdigest()
+    import shutil
+    d2 = str(tmp_path / "t")
+    shutil.copytree(d, d2)
+    with open(os.path.join(d2, "config.json"), "a") as f:
+        f.write(" ")
+    r2 = K.verify(d2)
+    assert r2["ok"] == 3 and r2["bad"][0]["file"] == "config.json"
+
+
+def test_validate_reports_bad_shapes_and_index(ckpt, tmp_path):
+    d, ow = ckpt
+    import shutil
+    d2 = str(tmp_path / "bad")
+    shutil.copytree(d, d2)
+    cfg = json.load(open(os.path.join(d2, "config.json")))
+    cfg["intermediate_size"] = 640
+    json.dump(cfg, open(os.path.join(d2, "config.json"), "w"))
+    rep = K.validate(d2)
+    assert not rep["ok"] and any("mlp.gate_proj" in e for e in rep["errors"])
+    d3 = str(tmp_path / "idx")
+    shutil.copytree(d, d3)
+    idx = json.load(open(os.path.join(d3, "model.safetensors.index.json")))
+    idx["weight_map"]["model.layers.9.ghost.weight"] = "model-00001-of-00003.safetensors"
+    json.dump(idx, open(os.path.join(d3, "model.safetensors.index.json"), "w"))
+    rep3 = K.validate(d3)
+    assert not rep3["ok"] and any("ghost" in e for e in rep3["errors"])
+
+
+def test_symmetric_reference_container(tmp_path):
+    """The reference's own container: int4 nibbles (code = q + 8), bf16 scales, symmetric, no zero-point tensor."""
+    cfg = C.oracle_tiny()
+    cfg.bits = {}
+    ow = O.random_weights(cfg, seed=2, symmetric=True)
+    d = str(tmp_path / "sym")
+    K.save_oracle(d, ow, symmetric=True)
+    rep = K.validate(d)
+    assert rep["ok"], rep["errors"]
+    assert rep["linears"]["lm_head"] == {"format": "wq", "bits": 4, "group": 64, "asymmetric": False, "scale_dtype": "BF16"}
+    f = K.SafeTensorsFile(os.path.join(d, "model.safetensors"))
+    packed = f.tensor("model.layers.0.self_attn.o_proj.weight_packed")
+    codes = quant.unpack_stream(packed, 4, cfg.q_dim)
+    assert torch.equal(codes, ow.quant["0.o"].codes)
