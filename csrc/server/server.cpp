@@ -1,0 +1,681 @@
+// OpenAI-compatible HTTP front end: /health, /health_generate, /metrics, /v1/models, /v1/models/{name},
+// /v1/chat/completions, /v1/completions with SSE streaming, stop strings, incremental detokenisation, reasoning and
+// tool-call parsing, usage accounting and cancellation when the client goes away.
+//
+// Reference: crates/agens-server/src/{server.rs:90-99, openai.rs:244-385 & 742-835, engine.rs, sampling.rs:104-205,
+// backend.rs:1-64}.  The engine is reached through a Backend: generate() returns at once and the engine pushes each
+// step's accepted ids (one or several with speculation) into the request's stream; the server owns stop strings,
+// text, parsing and usage.  MockBackend replays a scripted id list in fixed steps, as the reference's test backend.
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <cstdio>
+#include <cstring>
+#include <ctime>
+#include <deque>
+#include <fstream>
+#include <functional>
+#include <memory>
+#include <mutex>
+#include <random>
+#include <sstream>
+#include <thread>
+
+#include "text.hpp"
+
+#define B2H_API extern "C" __attribute__((visibility("default")))
+
+namespace b2 {
+
+// ------------------------------------------------------------------------------------------------ backend
+struct TokenStream {
+  std::mutex mu;
+  std::condition_variable cv;
+  std::deque<std::vector<int>> q;
+  bool finished = false, cancelled = false;
+  std::string error;
+  void push(const int* ids, int n, bool fin, const char* err = nullptr) {
+    std::lock_guard<std::mutex> l(mu);
+    if (n > 0) q.emplace_back(ids, ids + n);
+    if (fin) finished = true;
+    if (err) { error = err; finished = true; }
+    cv.notify_all();
+  }
+  // false when the stream is finished and drained
+  bool pop(std::vector<int>& out) {
+    std::unique_lock<std::mutex> l(mu);
+    cv.wait(l, [&] { return !q.empty() || finished; });
+    if (q.empty()) return false;
+    out = std::move(q.front());
+    q.pop_front();
+    return true;
+  }
+  void cancel() { std::lock_guard<std::mutex> l(mu); cancelled = true; }
+  bool is_cancelled() { std::lock_guard<std::mutex> l(mu); return cancelled; }
+};
+
+struct GenRequest { long long id; std::vector<int> prompt; Json sampling; std::string session_id; Json images; };
+
+class Backend {
+ public:
+  virtual ~Backend() {}
+  virtual void generate(const GenRequest& r, std::shared_ptr<TokenStream> s) = 0;
+  virtual bool supports_images() const { return false; }
+  virtual int context_length() const { return 262144; }
+};
+
+class MockBackend : public Backend {
+ public:
+  std::vector<int> script;
+  int step = 1;
+  bool images = false;
+  std::mutex mu;
+  std::vector<GenRequest> calls;
+  void generate(const GenRequest& r, std::shared_ptr<TokenStream> s) override {
+    { std::lock_guard<std::mutex> l(mu); calls.push_back(r); }
+    const long long maxn = r.sampling.get_int("max_new_tokens", 1 << 30);
+    std::vector<int> out = script;
+    if ((long long)out.size() > maxn) out.resize((size_t)maxn);
+    std::thread([out, s, st = step]() {
+      for (size_t i = 0; i < out.size(); i += st) {
+        if (s->is_cancelled()) break;
+        const int n = (int)std::min<size_t>(st, out.size() - i);
+        s->push(out.data() + i, n, false);
+      }
+      s->push(nullptr, 0, true);
+    }).detach();
+  }
+  bool supports_images() const override { return images; }
+};
+
+typedef void (*GenerateFn)(void* user, long long req_id, const int* prompt, int n_prompt, const char* sampling_json, const char* session_id);
+
+class CallbackBackend : public Backend {
+ public:
+  GenerateFn fn = nullptr;
+  void* user = nullptr;
+  int ctx = 262144;
+  std::mutex mu;
+  std::map<long long, std::shared_ptr<TokenStream>> streams;
+  void generate(const GenRequest& r, std::shared_ptr<TokenStream> s) override {
+    { std::lock_guard<std::mutex> l(mu); streams[r.id] = s; }
+    fn(user, r.id, r.prompt.data(), (int)r.prompt.size(), r.sampling.dump().c_str(), r.session_id.c_str());
+  }
+  std::shared_ptr<TokenStream> find(long long id) { std::lock_guard<std::mutex> l(mu); auto it = streams.find(id); return it == streams.end() ? nullptr : it->second; }
+  void drop(long long id) { std::lock_guard<std::mutex> l(mu); streams.erase(id); }
+  int context_length() const override { return ctx; }
+};
+
+// ------------------------------------------------------------------------------------------------ server state
+struct HttpResponse { int status = 200; std::string content_type = "application/json", body; bool sse = false; };
+
+struct Server {
+  Tokenizer tok;
+  bool has_tok = false;
+  std::string model_name = "b200-engine";
+  Json gen_defaults = Json::object();      // generation_config.json: temperature, top_k, top_p
+  std::vector<int> eos_ids;
+  long long max_tokens_default = 32768;
+  std::shared_ptr<Backend> backend;
+  std::atomic<long long> next_req{1}, n_requests{0}, n_prompt_tokens{0}, n_completion_tokens{0}, n_errors{0};
+  int listen_fd = -1;
+  std::thread accept_thread;
+  std::atomic<bool> stopping{false};
+};
+
+static std::string hex_id(int n) {
+  static std::mt19937_64 rng{std::random_device{}()};
+  static std::mutex mu;
+  std::lock_guard<std::mutex> l(mu);
+  static const char* d = "0123456789abcdef";
+  std::string s;
+  for (int i = 0; i < n; ++i) s.push_back(d[rng() & 15]);
+  return s;
+}
+
+static HttpResponse error_response(int status, const std::string& msg, const std::string& type = "invalid_request_error") {
+  Json e = Json::object(), o = Json::object();
+  e.set("message", msg); e.set("type", type); e.set("param", Json()); e.set("code", status);
+  o.set("error", e);
+  HttpResponse r; r.status = status; r.body = o.dump();
+  return r;
+}
+
+// Sampling parameters of a request: defaults, then the request's fields, validated (sampling.rs:132-205).
+static std::string build_sampling(const Server& sv, const Json& body, bool chat, Json& out) {
+  out = Json::object();
+  double temperature = chat ? sv.gen_defaults.get_double("temperature", 1.0) : 1.0;
+  double top_p = chat ? sv.gen_defaults.get_double("top_p", 1.0) : 1.0;
+  long long top_k = chat ? sv.gen_defaults.get_int("top_k", -1) : -1;
+  auto num = [&](const char* k, double& v) -> bool { if (auto p = body.find(k); p && !p->is_null()) { if (!p->is_number()) return false; v = p->as_double(); } return true; };
+  double min_p = 0, pres = 0, freq = 0, rep = 1;
+  if (!num("temperature", temperature) || !num("top_p", top_p) || !num("min_p", min_p) || !num("presence_penalty", pres) ||
+      !num("frequency_penalty", freq) || !num("repetition_penalty", rep)) return "sampling parameters must be numbers";
+  if (auto p = body.find("top_k"); p && p->is_number()) top_k = p->as_int();
+  if (temperature < 0) return "temperature must be non-negative, got " + Json(temperature).dump();
+  if (top_p <= 0 || top_p > 1) return "top_p must be in (0, 1], got " + Json(top_p).dump();
+  if (min_p < 0 || min_p > 1) return "min_p must be in [0, 1], got " + Json(min_p).dump();
+  if (top_k < -1 || top_k == 0) return "top_k must be -1 (disable) or at least 1, got " + std::to_string(top_k);
+  if (freq < -2 || freq > 2) return "frequency_penalty must be in [-2, 2], got " + Json(freq).dump();
+  if (pres < -2 || pres > 2) return "presence_penalty must be in [-2, 2], got " + Json(pres).dump();
+  if (rep <= 0 || rep > 2) return "repetition_penalty must be in (0, 2], got " + Json(rep).dump();
+  if (temperature < 1e-6) { temperature = 1.0; top_k = 1; }     // greedy is expressed as top_k = 1
+  long long max_new = sv.max_tokens_default;
+  if (auto p = body.find("max_completion_tokens"); p && p->is_number()) max_new = p->as_int();
+  else if (auto q = body.find("max_tokens"); q && q->is_number()) max_new = q->as_int();
+  if (max_new < 0) return "max_tokens must be at least 0, got " + std::to_string(max_new);
+  const long long min_new = body.get_int("min_tokens", 0);
+  if (min_new > max_new) return "min_tokens must not exceed max_tokens";
+  out.set("temperature", temperature); out.set("top_p", top_p); out.set("top_k", top_k); out.set("min_p", min_p);
+  out.set("presence_penalty", pres); out.set("frequency_penalty", freq); out.set("repetition_penalty", rep);
+  out.set("max_new_tokens", max_new); out.set("min_new_tokens", min_new);
+  if (auto p = body.find("seed"); p && p->is_number()) out.set("seed", p->as_int());
+  if (auto p = body.find("logit_bias"); p && p->is_object()) out.set("logit_bias", *p);
+  Json stops = Json::array();
+  if (!body.get_bool("ignore_eos", false)) for (int e : sv.eos_ids) stops.push_back(e);
+  if (auto p = body.find("stop_token_ids"); p && p->is_array()) for (auto& v : p->items()) stops.push_back(v.as_int());
+  out.set("stop_token_ids", stops);
+  out.set("ignore_eos", body.get_bool("ignore_eos", false));
+  // ids beyond the tokenizer (padding rows of the embedding) are never produced
+  if (sv.has_tok) out.set("vocab_valid", sv.tok.size());
+  return "";
+}
+
+static std::string reject_unsupported(const Json& body, bool chat) {
+  for (const char* k : {"response_format", "regex", "ebnf", "json_schema", "stop_regex", "input_ids", "custom_logit_processor"})
+    if (auto p = body.find(k); p && !p->is_null()) return std::string(k) + " is not supported";
+  if (body.get_int("n", 1) > 1) return "n > 1 is not supported";
+  if (auto p = body.find("logprobs"); p && ((p->is_bool() && p->as_bool()) || (p->is_number() && p->as_int() > 0))) return "logprobs is not supported";
+  if (!chat) {
+    if (body.get_bool("echo", false)) return "echo is not supported";
+    if (auto p = body.find("suffix"); p && !p->is_null()) return "suffix is not supported";
+  }
+  return "";
+}
+
+// Earliest position at which any stop string begins, or npos; `hold` receives how many trailing bytes might still
+// grow into a stop string and must not be emitted yet.
+static size_t find_stop(const std::string& text, const std::vector<std::string>& stops, size_t& hold) {
+  size_t best = std::string::npos;
+  hold = 0;
+  for (auto& s : stops) {
+    if (s.empty()) continue;
+    const size_t p = text.find(s);
+    if (p != std::string::npos) best = std::min(best, p);
+    const size_t m = std::min(text.size(), s.size() - 1);
+    for (size_t k = m; k > 0; --k) if (text.compare(text.size() - k, k, s, 0, k) == 0) { hold = std::max(hold, k); break; }
+  }
+  return best;
+}
+
+struct Emit { std::function<void(const std::string&)> write; std::function<bool()> alive; };
+
+// Runs one generation to completion.  Streaming responses are written through `emit` as SSE events; the complete
+// response body (JSON or the concatenated event stream) is returned as well.
+static HttpResponse run_generation(Server& sv, const Json& body, bool chat, const std::vector<int>& prompt_ids, const Json& sampling,
+                                   bool starts_in_reasoning, const std::string& session_id, Emit* emit) {
+  const bool stream = body.get_bool("stream", false);
+  const bool include_usage = body.find("stream_options") && body.at("stream_options").get_bool("include_usage", false);
+  const bool separate_reasoning = body.get_bool("separate_reasoning", true);
+  const bool stream_reasoning = body.get_bool("stream_reasoning", true);
+  const bool skip_special = body.get_bool("skip_special_tokens", true);
+  const bool no_stop_trim = body.get_bool("no_stop_trim", false);
+  const Json tools = body.find("tools") && body.at("tools").is_array() && body.get_string("tool_choice", "auto") != "none" ? body.at("tools") : Json::array();
+  std::vector<std::string> stops;
+  if (auto p = body.find("stop")) { if (p->is_string()) stops.push_back(p->as_string()); else if (p->is_array()) for (auto& s : p->items()) if (s.is_string()) stops.push_back(s.as_string()); }
+  std::vector<int> stop_ids;
+  for (auto& v : sampling.at("stop_token_ids").items()) stop_ids.push_back((int)v.as_int());
+  const long long max_new = sampling.get_int("max_new_tokens", sv.max_tokens_default);
+
+  GenRequest req;
+  req.id = sv.next_req++;
+  req.prompt = prompt_ids;
+  req.sampling = sampling;
+  req.session_id = session_id;
+  auto ts = std::make_shared<TokenStream>();
+  sv.n_requests++;
+  sv.n_prompt_tokens += (long long)prompt_ids.size();
+  if (max_new > 0) sv.backend->generate(req, ts); else ts->push(nullptr, 0, true);
+
+  const std::string id = (chat ? "chatcmpl-" : "cmpl-") + hex_id(24);
+  const long long created = (long long)std::time(nullptr);
+  Detokenizer detok(&sv.tok, skip_special);
+  ReasoningParser rp(starts_in_reasoning, stream_reasoning);
+  ToolStreamParser tp(tools);
+  std::string text_all, content_all, reasoning_all, sse_all, pending_text;
+  std::vector<ToolCall> calls;
+  long long n_out = 0, n_reasoning_tokens = 0;
+  std::string finish = "length";
+  bool in_reasoning_tokens = starts_in_reasoning;
+
+  auto send = [&](const Json& chunk) {
+    const std::string ev = "data: " + chunk.dump() + "\n\n";
+    sse_all += ev;
+    if (emit) emit->write(ev);
+  };
+  auto base_chunk = [&]() {
+    Json c = Json::object();
+    c.set("id", id); c.set("object", chat ? "chat.completion.chunk" : "text_completion"); c.set("created", created); c.set("model", sv.model_name);
+    return c;
+  };
+  auto delta_chunk = [&](const std::string& content, const std::string& reasoning, const Json& tool_delta, const Json& fin) {
+    Json c = base_chunk(), ch = Json::object();
+    ch.set("index", 0);
+    if (chat) {
+      Json d = Json::object();
+      if (!content.empty()) d.set("content", content);
+      if (!reasoning.empty()) d.set("reasoning_content", reasoning);
+      if (!tool_delta.is_null()) d.set("tool_calls", tool_delta);
+      ch.set("delta", d);
+    } else ch.set("text", content);
+    ch.set("finish_reason", fin);
+    Json arr = Json::array(); arr.push_back(ch);
+    c.set("choices", arr);
+    return c;
+  };
+  if (stream && chat) {
+    Json c = base_chunk(), ch = Json::object(), d = Json::object();
+    d.set("role", "assistant"); d.set("content", "");
+    ch.set("index", 0); ch.set("delta", d); ch.set("finish_reason", Json());
+    Json arr = Json::array(); arr.push_back(ch); c.set("choices", arr);
+    send(c);
+  }
+  // text -> (reasoning, content, tool calls) -> client
+  auto process_text = [&](const std::string& piece, bool last) {
+    ReasoningParser::Out ro;
+    if (chat && separate_reasoning) { ro = rp.push(piece); if (last) { auto f = rp.finish(); ro.content += f.content; ro.reasoning += f.reasoning; } }
+    else ro.content = piece;
+    reasoning_all += ro.reasoning;
+    ToolParse t;
+    if (chat && tools.size()) { t = tp.push(ro.content); if (last) { auto f = tp.finish(); t.content += f.content; for (auto& c : f.calls) t.calls.push_back(c); } }
+    else t.content = ro.content;
+    content_all += t.content;
+    Json tool_delta;
+    if (!t.calls.empty()) {
+      tool_delta = Json::array();
+      for (auto& c : t.calls) {
+        Json tc = Json::object(), fn = Json::object();
+        tc.set("index", (long long)calls.size()); tc.set("id", "call_" + hex_id(24)); tc.set("type", "function");
+        fn.set("name", c.name); fn.set("arguments", c.arguments_json);
+        tc.set("function", fn);
+        tool_delta.push_back(tc);
+        calls.push_back(c);
+      }
+    }
+    if (stream && (!t.content.empty() || !ro.reasoning.empty() || !tool_delta.is_null())) send(delta_chunk(t.content, ro.reasoning, tool_delta, Json()));
+  };
+
+  std::vector<int> step_ids;
+  bool done = false;
+  while (!done && ts->pop(step_ids)) {
+    for (int tkn : step_ids) {
+      if (n_out >= max_new) { done = true; break; }
+      ++n_out;
+      const bool is_stop_id = std::find(stop_ids.begin(), stop_ids.end(), tkn) != stop_ids.end() && n_out > sampling.get_int("min_new_tokens", 0);
+      if (is_stop_id) { finish = "stop"; done = true; break; }
+      if (in_reasoning_tokens) ++n_reasoning_tokens;
+      std::string piece = detok.push({tkn});
+      text_all += piece;
+      if (in_reasoning_tokens && text_all.find("</think>") != std::string::npos) in_reasoning_tokens = false;
+      pending_text += piece;
+      size_t hold = 0;
+      const size_t sp = find_stop(pending_text, stops, hold);
+      if (sp != std::string::npos) {
+        std::string upto = pending_text.substr(0, sp);
+        if (no_stop_trim) for (auto& s : stops) if (pending_text.compare(sp, s.size(), s) == 0) { upto += s; break; }
+        process_text(upto, false);
+        pending_text.clear();
+        finish = "stop"; done = true; break;
+      }
+      const std::string ready = pending_text.substr(0, pending_text.size() - hold);
+      pending_text.erase(0, ready.size());
+      if (!ready.empty()) process_text(ready, false);
+      if (n_out >= max_new) { done = true; break; }
+    }
+    if (emit && !emit->alive()) { ts->cancel(); done = true; finish = "abort"; }
+  }
+  ts->cancel();     // the engine stops at its next step once the receiver is gone
+  if (auto cb = dynamic_cast<CallbackBackend*>(sv.backend.get())) cb->drop(req.id);
+  if (!ts->error.empty()) { sv.n_errors++; return error_response(500, ts->error, "internal_error"); }
+  { std::string tail = detok.finish(); if (finish != "stop") pending_text += tail; }
+  process_text(finish == "stop" ? std::string() : pending_text, true);
+  if (!calls.empty()) finish = "tool_calls";
+  sv.n_completion_tokens += n_out;
+
+  Json usage = Json::object();
+  usage.set("prompt_tokens", (long long)prompt_ids.size()); usage.set("completion_tokens", n_out);
+  usage.set("total_tokens", (long long)prompt_ids.size() + n_out);
+  Json det = Json::object(); det.set("reasoning_tokens", n_reasoning_tokens); usage.set("completion_tokens_details", det);
+
+  HttpResponse resp;
+  if (stream) {
+    send(delta_chunk("", "", Json(), Json(finish)));
+    if (include_usage) { Json c = base_chunk(); c.set("choices", Json::array()); c.set("usage", usage); send(c); }
+    sse_all += "data: [DONE]\n\n";
+    if (emit) emit->write("data: [DONE]\n\n");
+    resp.sse = true; resp.content_type = "text/event-stream"; resp.body = sse_all;
+    return resp;
+  }
+  Json o = Json::object(), ch = Json::object();
+  o.set("id", id); o.set("object", chat ? "chat.completion" : "text_completion"); o.set("created", created); o.set("model", sv.model_name);
+  ch.set("index", 0);
+  if (chat) {
+    Json m = Json::object();
+    m.set("role", "assistant");
+    m.set("content", content_all.empty() && !calls.empty() ? Json() : Json(content_all));
+    m.set("reasoning_content", reasoning_all.empty() ? Json() : Json(reasoning_all));
+    if (!calls.empty()) {
+      Json arr = Json::array();
+      for (auto& c : calls) { Json tc = Json::object(), fn = Json::object(); tc.set("id", "call_" + hex_id(24)); tc.set("type", "function"); fn.set("name", c.name); fn.set("arguments", c.arguments_json); tc.set("function", fn); arr.push_back(tc); }
+      m.set("tool_calls", arr);
+    } else m.set("tool_calls", Json());
+    ch.set("message", m);
+  } else ch.set("text", content_all);
+  ch.set("finish_reason", finish);
+  Json arr = Json::array(); arr.push_back(ch);
+  o.set("choices", arr); o.set("usage", usage);
+  resp.body = o.dump();
+  return resp;
+}
+
+static HttpResponse handle_chat(Server& sv, const Json& body, const std::string& session_hdr, Emit* emit) {
+  if (!body.is_object()) return error_response(400, "request body must be a JSON object");
+  if (std::string e = reject_unsupported(body, true); !e.empty()) return error_response(400, e);
+  const Json* ms = body.find("messages");
+  if (!ms || !ms->is_array() || ms->size() == 0) return error_response(400, "messages must be a non-empty array");
+  std::vector<ChatMessage> msgs;
+  for (auto& m : ms->items()) {
+    ChatMessage cm;
+    cm.role = m.get_string("role", "");
+    if (cm.role != "system" && cm.role != "user" && cm.role != "assistant" && cm.role != "tool" && cm.role != "developer") return error_response(400, "unknown message role: " + cm.role);
+    if (cm.role == "developer") cm.role = "system";
+    if (auto c = m.find("content")) {
+      if (c->is_string()) cm.content = c->as_string();
+      else if (c->is_array()) {
+        for (auto& part : c->items()) {
+          const std::string type = part.get_string("type", "");
+          if (type == "text") cm.content += part.get_string("text", "");
+          else if (type == "image_url") {
+            if (!sv.backend->supports_images()) return error_response(400, "this model does not accept images");
+            const Json* iu = part.find("image_url");
+            const std::string url = iu ? iu->get_string("url", "") : "";
+            if (url.compare(0, 5, "data:") != 0) return error_response(400, "only base64 data: URLs are accepted for images");
+            cm.content += "<|vision_start|><|image_pad|><|vision_end|>";
+          } else return error_response(400, "unsupported content part type: " + type);
+        }
+      }
+    }
+    cm.reasoning = m.get_string("reasoning_content", "");
+    if (auto tc = m.find("tool_calls")) cm.tool_calls = *tc;
+    msgs.push_back(cm);
+  }
+  bool enable_thinking = true;
+  if (auto k = body.find("chat_template_kwargs"); k && k->is_object()) enable_thinking = k->get_bool("enable_thinking", true);
+  if (body.get_string("reasoning_effort", "") == "none") enable_thinking = false;
+  const bool cont = body.get_bool("continue_final_message", false);
+  const Json tools = body.find("tools") && body.at("tools").is_array() && body.get_string("tool_choice", "auto") != "none" ? body.at("tools") : Json::array();
+  const std::string prompt = render_chatml(msgs, tools, !cont, enable_thinking, cont);
+  Json sampling;
+  if (std::string e = build_sampling(sv, body, true, sampling); !e.empty()) return error_response(400, e);
+  if (auto rb = body.find("reasoning_budget"); rb && rb->is_number()) sampling.set("reasoning_budget", rb->as_int());
+  const std::vector<int> ids = sv.tok.encode(prompt);
+  if ((long long)ids.size() >= sv.backend->context_length()) return error_response(400, "the prompt is longer than the model's context length");
+  const std::string session = !session_hdr.empty() ? session_hdr : body.get_string("session_id", "");
+  return run_generation(sv, body, true, ids, sampling, /*starts_in_reasoning=*/false, session, emit);
+}
+
+static HttpResponse handle_completion(Server& sv, const Json& body, const std::string& session_hdr, Emit* emit) {
+  if (!body.is_object()) return error_response(400, "request body must be a JSON object");
+  if (std::string e = reject_unsupported(body, false); !e.empty()) return error_response(400, e);
+  const Json* p = body.find("prompt");
+  std::vector<int> ids;
+  if (!p) return error_response(400, "prompt is required");
+  if (p->is_string()) ids = sv.tok.encode(p->as_string());
+  else if (p->is_array() && p->size() && (*p)[0].is_int()) for (auto& v : p->items()) ids.push_back((int)v.as_int());
+  else if (p->is_array() && p->size() == 1 && (*p)[0].is_string()) ids = sv.tok.encode((*p)[0].as_string());
+  else return error_response(400, "prompt must be one string or one list of token ids (batched prompts are not supported)");
+  Json sampling;
+  if (std::string e = build_sampling(sv, body, false, sampling); !e.empty()) return error_response(400, e);
+  const std::string session = !session_hdr.empty() ? session_hdr : body.get_string("session_id", "");
+  return run_generation(sv, body, false, ids, sampling, false, session, emit);
+}
+
+static HttpResponse route(Server& sv, const std::string& method, const std::string& path, const std::string& session_hdr,
+                          const std::string& body_text, Emit* emit) {
+  if (method == "GET" && (path == "/health" || path == "/health_generate")) { HttpResponse r; r.content_type = "text/plain"; return r; }
+  if (method == "GET" && path == "/metrics") {
+    HttpResponse r; r.content_type = "text/plain; version=0.0.4";
+    std::ostringstream o;
+    o << "b200e_requests_total " << sv.n_requests << "\nb200e_prompt_tokens_total " << sv.n_prompt_tokens
+      << "\nb200e_completion_tokens_total " << sv.n_completion_tokens << "\nb200e_errors_total " << sv.n_errors << "\n";
+    r.body = o.str();
+    return r;
+  }
+  auto model_card = [&]() { Json m = Json::object(); m.set("id", sv.model_name); m.set("object", "model"); m.set("created", (long long)std::time(nullptr)); m.set("owned_by", "b200-engine"); m.set("max_model_len", sv.backend->context_length()); m.set("engine_version", "0.1.0"); return m; };
+  if (method == "GET" && path == "/v1/models") { Json o = Json::object(), a = Json::array(); a.push_back(model_card()); o.set("object", "list"); o.set("data", a); HttpResponse r; r.body = o.dump(); return r; }
+  if (method == "GET" && path.compare(0, 11, "/v1/models/") == 0) {
+    if (path.substr(11) != sv.model_name) return error_response(404, "model not found: " + path.substr(11), "not_found_error");
+    HttpResponse r; r.body = model_card().dump(); return r;
+  }
+  if (method == "POST" && (path == "/v1/chat/completions" || path == "/v1/completions")) {
+    Json body;
+    try { body = Json::parse(body_text); } catch (const std::exception& e) { return error_response(400, std::string("invalid JSON: ") + e.what()); }
+    return path == "/v1/chat/completions" ? handle_chat(sv, body, session_hdr, emit) : handle_completion(sv, body, session_hdr, emit);
+  }
+  return error_response(404, "no route for " + method + " " + path, "not_found_error");
+}
+
+// ------------------------------------------------------------------------------------------------ HTTP/1.1 over sockets
+static bool send_all(int fd, const std::string& s) {
+  size_t off = 0;
+  while (off < s.size()) { ssize_t n = ::send(fd, s.data() + off, s.size() - off, MSG_NOSIGNAL); if (n <= 0) return false; off += (size_t)n; }
+  return true;
+}
+static const char* status_text(int s) { return s == 200 ? "OK" : s == 400 ? "Bad Request" : s == 404 ? "Not Found" : s == 500 ? "Internal Server Error" : "Error"; }
+
+static void serve_connection(Server* sv, int fd) {
+  std::string buf;
+  char tmp[8192];
+  size_t hdr_end = std::string::npos;
+  while (hdr_end == std::string::npos) {
+    ssize_t n = recv(fd, tmp, sizeof tmp, 0);
+    if (n <= 0) { close(fd); return; }
+    buf.append(tmp, (size_t)n);
+    hdr_end = buf.find("\r\n\r\n");
+    if (buf.size() > (1 << 20)) { close(fd); return; }
+  }
+  std::istringstream hs(buf.substr(0, hdr_end));
+  std::string method, path, ver, line, session;
+  hs >> method >> path >> ver;
+  size_t clen = 0;
+  std::getline(hs, line);
+  while (std::getline(hs, line)) {
+    if (!line.empty() && line.back() == '\r') line.pop_back();
+    const size_t c = line.find(':');
+    if (c == std::string::npos) continue;
+    std::string k = line.substr(0, c), v = line.substr(c + 1);
+    while (!v.empty() && v[0] == ' ') v.erase(0, 1);
+    for (auto& ch : k) ch = (char)tolower(ch);
+    if (k == "content-length") clen = (size_t)std::atoll(v.c_str());
+    if (k == "x-session-id") session = v;
+  }
+  std::string body = buf.substr(hdr_end + 4);
+  while (body.size() < clen) { ssize_t n = recv(fd, tmp, sizeof tmp, 0); if (n <= 0) break; body.append(tmp, (size_t)n); }
+  const size_t q = path.find('?');
+  if (q != std::string::npos) path.resize(q);
+  bool headers_sent = false, alive = true;
+  Emit em;
+  em.write = [&](const std::string& ev) {
+    if (!headers_sent) { alive = send_all(fd, "HTTP/1.1 200 OK\r\nContent-Type: text/event-stream\r\nCache-Control: no-cache\r\nConnection: close\r\n\r\n"); headers_sent = true; }
+    if (alive) alive = send_all(fd, ev);
+  };
+  em.alive = [&]() {
+    if (!alive) return false;
+    char c;
+    const ssize_t n = recv(fd, &c, 1, MSG_PEEK | MSG_DONTWAIT);
+    if (n == 0) alive = false;      // orderly shutdown by the client
+    return alive;
+  };
+  HttpResponse r = route(*sv, method, path, session, body, &em);
+  if (!(r.sse && headers_sent)) {
+    std::ostringstream o;
+    o << "HTTP/1.1 " << r.status << " " << status_text(r.status) << "\r\nContent-Type: " << r.content_type << "\r\nContent-Length: " << r.body.size() << "\r\nConnection: close\r\n\r\n";
+    send_all(fd, o.str() + r.body);
+  }
+  shutdown(fd, SHUT_RDWR);
+  close(fd);
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+static char* dup_cstr(const std::string& s) { char* p = (char*)malloc(s.size() + 1); memcpy(p, s.c_str(), s.size() + 1); return p; }
+
+// config: {"tokenizer_json": path, "model_name", "generation_config": {...}, "eos_token_ids": [..], "max_tokens_default"}
+B2H_API void* b2h_server_new(const char* config_json, char* err, int err_cap) {
+  try {
+    Json c = Json::parse(config_json);
+    auto sv = new Server();
+    if (auto p = c.find("tokenizer_json"); p && p->is_string()) {
+      std::ifstream f(p->as_string());
+      if (!f) throw std::runtime_error("cannot read " + p->as_string());
+      std::stringstream ss; ss << f.rdbuf();
+      sv->tok = Tokenizer::from_json(ss.str());
+      sv->has_tok = true;
+    }
+    sv->model_name = c.get_string("model_name", "b200-engine");
+    if (auto g = c.find("generation_config"); g && g->is_object()) sv->gen_defaults = *g;
+    if (auto e = c.find("eos_token_ids"); e && e->is_array()) for (auto& v : e->items()) sv->eos_ids.push_back((int)v.as_int());
+    sv->max_tokens_default = c.get_int("max_tokens_default", 32768);
+    sv->backend = std::make_shared<MockBackend>();
+    return sv;
+  } catch (const std::exception& e) { if (err) snprintf(err, err_cap, "%s", e.what()); return nullptr; }
+}
+B2H_API void b2h_server_free(void* s) { delete static_cast<Server*>(s); }
+B2H_API void b2h_server_use_mock(void* s, const int* script, int n, int step, int supports_images) {
+  auto m = std::make_shared<MockBackend>();
+  m->script.assign(script, script + n); m->step = std::max(1, step); m->images = supports_images != 0;
+  static_cast<Server*>(s)->backend = m;
+}
+// JSON list of the calls the mock backend received: [{"prompt": [...], "sampling": {...}, "session_id": "..."}]
+B2H_API char* b2h_server_mock_calls(void* s) {
+  auto m = std::dynamic_pointer_cast<MockBackend>(static_cast<Server*>(s)->backend);
+  Json a = Json::array();
+  if (m) { std::lock_guard<std::mutex> l(m->mu); for (auto& c : m->calls) { Json o = Json::object(), p = Json::array(); for (int t : c.prompt) p.push_back(t); o.set("prompt", p); o.set("sampling", c.sampling); o.set("session_id", c.session_id); a.push_back(o); } }
+  return dup_cstr(a.dump());
+}
+B2H_API void b2h_server_use_callback(void* s, GenerateFn fn, void* user, int context_length) {
+  auto b = std::make_shared<CallbackBackend>();
+  b->fn = fn; b->user = user; b->ctx = context_length;
+  static_cast<Server*>(s)->backend = b;
+}
+// Engine side of the callback backend: push a step's tokens / finish / fail; ask whether the client is gone.
+B2H_API int b2h_stream_push(void* s, long long req_id, const int* ids, int n, int finished, const char* error) {
+  auto b = std::dynamic_pointer_cast<CallbackBackend>(static_cast<Server*>(s)->backend);
+  if (!b) return -1;
+  auto ts = b->find(req_id);
+  if (!ts) return -1;
+  ts->push(ids, n, finished != 0, error);
+  return ts->is_cancelled() ? 1 : 0;
+}
+B2H_API int b2h_stream_cancelled(void* s, long long req_id) {
+  auto b = std::dynamic_pointer_cast<CallbackBackend>(static_cast<Server*>(s)->backend);
+  if (!b) return 1;
+  auto ts = b->find(req_id);
+  return !ts || ts->is_cancelled() ? 1 : 0;
+}
+// In-process request (tests, embedding): returns the full body; *status receives the HTTP status.
+B2H_API char* b2h_server_handle(void* s, const char* method, const char* path, const char* session_id, const char* body, int* status) {
+  HttpResponse r = route(*static_cast<Server*>(s), method, path, session_id ? session_id : "", body ? body : "", nullptr);
+  if (status) *status = r.status;
+  return dup_cstr(r.body);
+}
+// Starts listening (port 0 = any free port); returns the bound port or -1.
+B2H_API int b2h_server_start(void* sp, const char* host, int port) {
+  auto sv = static_cast<Server*>(sp);
+  int fd = socket(AF_INET, SOCK_STREAM, 0);
+  if (fd < 0) return -1;
+  int one = 1;
+  setsockopt(fd, SOL_SOCKET, SO_REUSEADDR, &one, sizeof one);
+  sockaddr_in a{};
+  a.sin_family = AF_INET; a.sin_port = htons((uint16_t)port);
+  if (inet_pton(AF_INET, host && *host ? host : "127.0.0.1", &a.sin_addr) != 1) { close(fd); return -1; }
+  if (bind(fd, (sockaddr*)&a, sizeof a) != 0 || listen(fd, 128) != 0) { close(fd); return -1; }
+  socklen_t len = sizeof a;
+  getsockname(fd, (sockaddr*)&a, &len);
+  sv->listen_fd = fd;
+  sv->stopping = false;
+  sv->accept_thread = std::thread([sv]() {
+    while (!sv->stopping) {
+      int c = accept(sv->listen_fd, nullptr, nullptr);
+      if (c < 0) { if (sv->stopping) break; continue; }
+      int one = 1;
+      setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &one, sizeof one);
+      std::thread(serve_connection, sv, c).detach();
+    }
+  });
+  return ntohs(a.sin_port);
+}
+B2H_API void b2h_server_stop(void* sp) {
+  auto sv = static_cast<Server*>(sp);
+  sv->stopping = true;
+  if (sv->listen_fd >= 0) { shutdown(sv->listen_fd, SHUT_RDWR); close(sv->listen_fd); sv->listen_fd = -1; }
+  if (sv->accept_thread.joinable()) sv->accept_thread.join();
+}
+
+// ---- text layer exports (tests, Python-side engine glue) ----
+B2H_API void* b2h_tok_new(const char* tokenizer_json_text, char* err, int cap) {
+  try { return new Tokenizer(Tokenizer::from_json(tokenizer_json_text)); } catch (const std::exception& e) { if (err) snprintf(err, cap, "%s", e.what()); return nullptr; }
+}
+B2H_API void b2h_tok_free(void* t) { delete static_cast<Tokenizer*>(t); }
+B2H_API int b2h_tok_encode(void* t, const char* text, int* out, int cap) {
+  auto ids = static_cast<Tokenizer*>(t)->encode(text);
+  for (int i = 0; i < (int)ids.size() && i < cap; ++i) out[i] = ids[i];
+  return (int)ids.size();
+}
+B2H_API char* b2h_tok_decode(void* t, const int* ids, int n, int skip_special) {
+  return dup_cstr(static_cast<Tokenizer*>(t)->decode(std::vector<int>(ids, ids + n), skip_special != 0));
+}
+B2H_API void* b2h_detok_new(void* t, int skip_special) { return new Detokenizer(static_cast<Tokenizer*>(t), skip_special != 0); }
+B2H_API void b2h_detok_free(void* d) { delete static_cast<Detokenizer*>(d); }
+B2H_API char* b2h_detok_push(void* d, const int* ids, int n) { return dup_cstr(static_cast<Detokenizer*>(d)->push(std::vector<int>(ids, ids + n))); }
+B2H_API char* b2h_detok_finish(void* d) { return dup_cstr(static_cast<Detokenizer*>(d)->finish()); }
+// messages: JSON array of {role, content, reasoning_content?, tool_calls?}
+B2H_API char* b2h_render_chat(const char* messages_json, const char* tools_json, int add_generation_prompt, int enable_thinking, int continue_final) {
+  try {
+    Json ms = Json::parse(messages_json), tools = tools_json && *tools_json ? Json::parse(tools_json) : Json::array();
+    std::vector<ChatMessage> msgs;
+    for (auto& m : ms.items()) { ChatMessage c; c.role = m.get_string("role", ""); c.content = m.get_string("content", ""); c.reasoning = m.get_string("reasoning_content", ""); if (auto t = m.find("tool_calls")) c.tool_calls = *t; msgs.push_back(c); }
+    return dup_cstr(render_chatml(msgs, tools, add_generation_prompt != 0, enable_thinking != 0, continue_final != 0));
+  } catch (const std::exception& e) { return dup_cstr(std::string("ERROR: ") + e.what()); }
+}
+// Parses text in chunks of `chunk` bytes (0 = at once); returns {"content", "reasoning", "tool_calls": [{name, arguments}]}.
+B2H_API char* b2h_parse_output(const char* text, const char* tools_json, int starts_in_reasoning, int chunk) {
+  Json tools = tools_json && *tools_json ? Json::parse(tools_json) : Json::array();
+  std::string t = text, content, reasoning;
+  std::vector<ToolCall> calls;
+  ReasoningParser rp(starts_in_reasoning != 0, true);
+  ToolStreamParser tp(tools);
+  auto feed = [&](const std::string& piece, bool last) {
+    auto ro = rp.push(piece);
+    if (last) { auto f = rp.finish(); ro.content += f.content; ro.reasoning += f.reasoning; }
+    reasoning += ro.reasoning;
+    auto tr = tp.push(ro.content);
+    if (last) { auto f = tp.finish(); tr.content += f.content; for (auto& c : f.calls) tr.calls.push_back(c); }
+    content += tr.content;
+    for (auto& c : tr.calls) calls.push_back(c);
+  };
+  if (chunk <= 0) feed(t, true);
+  else { for (size_t i = 0; i < t.size(); i += (size_t)chunk) feed(t.substr(i, (size_t)chunk), false); feed("", true); }
+  Json o = Json::object(), a = Json::array();
+  for (auto& c : calls) { Json j = Json::object(); j.set("name", c.name); j.set("arguments", c.arguments_json); a.push_back(j); }
+  o.set("content", content); o.set("reasoning", reasoning); o.set("tool_calls", a);
+  return dup_cstr(o.dump());
+}

@@ -1,0 +1,518 @@
+// Text layer of the server.  What each part keeps from the reference (crates/agens-server/src):
+//   tokenizer.rs   byte-level BPE over tokenizer.json with the Qwen2 pre-tokenizer pattern (:21-22), added/special
+//                  tokens matched before pre-tokenisation, skip_special_tokens on decode, and an incremental
+//                  detokenizer that never emits a split UTF-8 sequence.  The pattern is implemented as a hand-written
+//                  scanner (it needs a negative look-ahead); Unicode letter/number classes are approximated by block
+//                  ranges (all scripts above U+00BF count as letters except the listed digit/punctuation/space blocks).
+//   template.rs    here a built-in ChatML renderer instead of a Jinja engine (same observable prompts for the
+//                  ChatML family: roles, tool preamble, think block handling, continue_final_message).
+//   reasoning.rs   think-block splitter, streaming with partial-tag hold-back.
+//   toolcall.rs    tool-call parsing, non-stream and stream, JSON-body and <function=..><parameter=..> wire formats,
+//                  parameter values typed through the tool's JSON schema.
+#include "text.hpp"
+
+#include <algorithm>
+#include <climits>
+#include <cstring>
+
+namespace b2 {
+
+// ------------------------------------------------------------------------------------------------ UTF-8 helpers
+static unsigned decode_cp(const std::string& s, size_t& i) {
+  const unsigned char c = (unsigned char)s[i];
+  unsigned cp; int n;
+  if (c < 0x80) { cp = c; n = 0; }
+  else if ((c & 0xE0) == 0xC0) { cp = c & 0x1F; n = 1; }
+  else if ((c & 0xF0) == 0xE0) { cp = c & 0x0F; n = 2; }
+  else if ((c & 0xF8) == 0xF0) { cp = c & 0x07; n = 3; }
+  else { ++i; return 0xFFFD; }
+  ++i;
+  for (int k = 0; k < n; ++k) {
+    if (i >= s.size() || ((unsigned char)s[i] & 0xC0) != 0x80) return 0xFFFD;
+    cp = (cp << 6) | ((unsigned char)s[i++] & 0x3F);
+  }
+  return cp;
+}
+static void append_cp(std::string& out, unsigned cp) {
+  if (cp < 0x80) out.push_back((char)cp);
+  else if (cp < 0x800) { out.push_back((char)(0xC0 | (cp >> 6))); out.push_back((char)(0x80 | (cp & 0x3F))); }
+  else if (cp < 0x10000) { out.push_back((char)(0xE0 | (cp >> 12))); out.push_back((char)(0x80 | ((cp >> 6) & 0x3F))); out.push_back((char)(0x80 | (cp & 0x3F))); }
+  else { out.push_back((char)(0xF0 | (cp >> 18))); out.push_back((char)(0x80 | ((cp >> 12) & 0x3F))); out.push_back((char)(0x80 | ((cp >> 6) & 0x3F))); out.push_back((char)(0x80 | (cp & 0x3F))); }
+}
+static bool is_space_cp(unsigned c) {
+  return c == ' ' || (c >= 9 && c <= 13) || c == 0x85 || c == 0xA0 || c == 0x1680 || (c >= 0x2000 && c <= 0x200A) || c == 0x2028 ||
+         c == 0x2029 || c == 0x202F || c == 0x205F || c == 0x3000;
+}
+static bool is_number_cp(unsigned c) {
+  if (c < 0x80) return c >= '0' && c <= '9';
+  return c == 0xB2 || c == 0xB3 || c == 0xB9 || (c >= 0xBC && c <= 0xBE) || (c >= 0x660 && c <= 0x669) || (c >= 0x6F0 && c <= 0x6F9) ||
+         (c >= 0x966 && c <= 0x96F) || (c >= 0x9E6 && c <= 0x9EF) || (c >= 0xE50 && c <= 0xE59) || (c >= 0x2070 && c <= 0x2079) ||
+         (c >= 0x2080 && c <= 0x2089) || (c >= 0x2150 && c <= 0x218B) || (c >= 0x2460 && c <= 0x249B) || (c >= 0x3021 && c <= 0x3029) ||
+         (c >= 0xFF10 && c <= 0xFF19);
+}
+static bool is_letter_cp(unsigned c) {
+  if (c < 0x80) return (c >= 'a' && c <= 'z') || (c >= 'A' && c <= 'Z');
+  if (c == 0xAA || c == 0xB5 || c == 0xBA) return true;
+  if (c < 0xC0) return false;
+  if (c == 0xD7 || c == 0xF7) return false;
+  if (is_space_cp(c) || is_number_cp(c)) return false;
+  if ((c >= 0x2000 && c <= 0x206F) || (c >= 0x20A0 && c <= 0x20CF) || (c >= 0x2190 && c <= 0x23FF) || (c >= 0x2500 && c <= 0x27BF) ||
+      (c >= 0x2900 && c <= 0x2BFF) || (c >= 0x3000 && c <= 0x303F) || (c >= 0xFE30 && c <= 0xFE4F) || (c >= 0xFF00 && c <= 0xFF0F) ||
+      (c >= 0xFF1A && c <= 0xFF20) || (c >= 0xFF3B && c <= 0xFF40) || (c >= 0xFF5B && c <= 0xFF65) || (c >= 0x1F000 && c <= 0x1FAFF) ||
+      (c >= 0xE000 && c <= 0xF8FF) || (c >= 0x300 && c <= 0x36F))
+    return false;
+  return true;
+}
+
+// GPT-2 byte <-> printable code point tables
+static const unsigned* byte_to_cp() {
+  static unsigned tab[256];
+  static bool init = false;
+  if (!init) {
+    int n = 0;
+    for (int b = 0; b < 256; ++b) {
+      const bool keep = (b >= '!' && b <= '~') || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF);
+      tab[b] = keep ? (unsigned)b : 256u + (unsigned)(n++);
+    }
+    init = true;
+  }
+  return tab;
+}
+static int cp_to_byte(unsigned cp) {
+  static std::unordered_map<unsigned, int> inv;
+  if (inv.empty()) { const unsigned* t = byte_to_cp(); for (int b = 0; b < 256; ++b) inv[t[b]] = b; }
+  auto it = inv.find(cp);
+  return it == inv.end() ? -1 : it->second;
+}
+
+// ------------------------------------------------------------------------------------------------ tokenizer
+Tokenizer Tokenizer::from_json(const std::string& text) {
+  Tokenizer t;
+  Json j = Json::parse(text);
+  const Json& model = j.at("model");
+  int max_id = -1;
+  for (auto& kv : model.at("vocab").members()) { t.vocab_[kv.first] = (int)kv.second.as_int(); max_id = std::max(max_id, (int)kv.second.as_int()); }
+  if (auto a = j.find("added_tokens"); a && a->is_array())
+    for (auto& e : a->items()) max_id = std::max(max_id, (int)e.at("id").as_int());
+  t.id_to_tok_.assign(max_id + 1, std::string());
+  for (auto& kv : t.vocab_) t.id_to_tok_[kv.second] = kv.first;
+  int rank = 0;
+  for (auto& m : model.at("merges").items()) {
+    std::string key = m.is_string() ? m.as_string() : m[0].as_string() + " " + m[1].as_string();
+    t.merge_rank_[key] = rank++;
+  }
+  if (auto a = j.find("added_tokens"); a && a->is_array()) {
+    for (auto& e : a->items()) {
+      const int id = (int)e.at("id").as_int();
+      const std::string content = e.at("content").as_string();
+      t.added_.emplace_back(content, id);
+      t.id_to_tok_[id] = content;
+      t.is_added_[id] = true;
+      if (e.get_bool("special", false)) t.special_[id] = true;
+    }
+    std::sort(t.added_.begin(), t.added_.end(), [](auto& a, auto& b) { return a.first.size() > b.first.size(); });
+  }
+  return t;
+}
+
+int Tokenizer::token_to_id(const std::string& s) const {
+  for (auto& a : added_) if (a.first == s) return a.second;
+  auto it = vocab_.find(s);
+  return it == vocab_.end() ? -1 : it->second;
+}
+
+std::vector<std::string> Tokenizer::pretokenize(const std::string& text) const {
+  std::vector<unsigned> cp;
+  std::vector<size_t> off;          // byte offset of each code point, plus the end
+  for (size_t i = 0; i < text.size();) { off.push_back(i); cp.push_back(decode_cp(text, i)); }
+  off.push_back(text.size());
+  std::vector<std::string> out;
+  const size_t n = cp.size();
+  auto lower = [](unsigned c) { return c >= 'A' && c <= 'Z' ? c + 32 : c; };
+  size_t i = 0;
+  auto emit = [&](size_t j) { out.push_back(text.substr(off[i], off[j] - off[i])); i = j; };
+  while (i < n) {
+    // 1. contractions
+    if (cp[i] == '\'' && i + 1 < n) {
+      const unsigned a = lower(cp[i + 1]), b = i + 2 < n ? lower(cp[i + 2]) : 0;
+      if ((a == 'r' && b == 'e') || (a == 'v' && b == 'e') || (a == 'l' && b == 'l')) { emit(i + 3); continue; }
+      if (a == 's' || a == 't' || a == 'm' || a == 'd') { emit(i + 2); continue; }
+    }
+    // 2. [^\r\n\p{L}\p{N}]?\p{L}+
+    {
+      size_t j = i;
+      if (!(cp[j] == '\r' || cp[j] == '\n' || is_letter_cp(cp[j]) || is_number_cp(cp[j])) && j + 1 < n && is_letter_cp(cp[j + 1])) ++j;
+      if (is_letter_cp(cp[j])) { while (j < n && is_letter_cp(cp[j])) ++j; emit(j); continue; }
+    }
+    // 3. \p{N}
+    if (is_number_cp(cp[i])) { emit(i + 1); continue; }
+    // 4.  ?[^\s\p{L}\p{N}]+[\r\n]*
+    {
+      size_t j = i;
+      if (cp[j] == ' ' && j + 1 < n) ++j;
+      auto other = [&](unsigned c) { return !is_space_cp(c) && !is_letter_cp(c) && !is_number_cp(c); };
+      if (j < n && other(cp[j])) {
+        while (j < n && other(cp[j])) ++j;
+        while (j < n && (cp[j] == '\r' || cp[j] == '\n')) ++j;
+        emit(j);
+        continue;
+      }
+    }
+    // whitespace alternatives
+    size_t j = i;
+    while (j < n && is_space_cp(cp[j])) ++j;
+    if (j == i) { emit(i + 1); continue; }        // unreachable for valid classes; keeps progress
+    // 5. \s*[\r\n]+ : up to the last newline of the run
+    size_t last_nl = n;
+    for (size_t k = i; k < j; ++k) if (cp[k] == '\r' || cp[k] == '\n') last_nl = k;
+    if (last_nl != n) { emit(last_nl + 1); continue; }
+    // 6. \s+(?!\S) : leave the last space to the following word
+    if (j < n && j - i > 1) { emit(j - 1); continue; }
+    if (j == n) { emit(j); continue; }
+    // 7. \s+
+    emit(j);
+  }
+  return out;
+}
+
+void Tokenizer::bpe(const std::string& piece, std::vector<int>& out) const {
+  // byte-level symbols
+  std::vector<std::string> sym;
+  const unsigned* b2c = byte_to_cp();
+  for (unsigned char c : piece) { std::string s; append_cp(s, b2c[c]); sym.push_back(s); }
+  while (sym.size() > 1) {
+    int best = INT_MAX; size_t at = 0;
+    for (size_t k = 0; k + 1 < sym.size(); ++k) {
+      auto it = merge_rank_.find(sym[k] + " " + sym[k + 1]);
+      if (it != merge_rank_.end() && it->second < best) { best = it->second; at = k; }
+    }
+    if (best == INT_MAX) break;
+    sym[at] += sym[at + 1];
+    sym.erase(sym.begin() + at + 1);
+  }
+  for (auto& s : sym) {
+    auto it = vocab_.find(s);
+    if (it != vocab_.end()) { out.push_back(it->second); continue; }
+    // unknown merged symbol: fall back to its single byte-level characters
+    for (size_t i = 0; i < s.size();) { size_t j = i; decode_cp(s, j); auto b = vocab_.find(s.substr(i, j - i)); if (b != vocab_.end()) out.push_back(b->second); i = j; }
+  }
+}
+
+std::vector<int> Tokenizer::encode(const std::string& text) const {
+  std::vector<int> out;
+  size_t pos = 0, seg = 0;
+  auto flush = [&](size_t end) {
+    if (end > seg) for (auto& p : pretokenize(text.substr(seg, end - seg))) bpe(p, out);
+  };
+  while (pos < text.size()) {
+    bool hit = false;
+    if (!added_.empty()) {
+      for (auto& a : added_) {
+        if (!a.first.empty() && text.compare(pos, a.first.size(), a.first) == 0) {
+          flush(pos);
+          out.push_back(a.second);
+          pos += a.first.size();
+          seg = pos;
+          hit = true;
+          break;
+        }
+      }
+    }
+    if (!hit) ++pos;
+  }
+  flush(text.size());
+  return out;
+}
+
+std::string Tokenizer::token_bytes(int id) const {
+  if (id < 0 || id >= (int)id_to_tok_.size()) return std::string();
+  const std::string& s = id_to_tok_[id];
+  if (is_added_.count(id)) return s;
+  std::string out;
+  for (size_t i = 0; i < s.size();) { const unsigned cp = decode_cp(s, i); const int b = cp_to_byte(cp); if (b >= 0) out.push_back((char)b); else append_cp(out, cp); }
+  return out;
+}
+
+std::string Tokenizer::decode(const std::vector<int>& ids, bool skip_special) const {
+  std::string out;
+  for (int id : ids) { if (skip_special && is_special(id)) continue; out += token_bytes(id); }
+  return out;
+}
+
+// ------------------------------------------------------------------------------------------------ detokenizer
+static size_t complete_utf8_prefix(const std::string& s) {
+  // length of the longest prefix that does not end inside a multi-byte sequence
+  size_t n = s.size();
+  size_t back = 0;
+  while (back < 4 && back < n && ((unsigned char)s[n - 1 - back] & 0xC0) == 0x80) ++back;
+  if (back < n) {
+    const unsigned char lead = (unsigned char)s[n - 1 - back];
+    int need = lead < 0x80 ? 0 : ((lead & 0xE0) == 0xC0 ? 1 : ((lead & 0xF0) == 0xE0 ? 2 : ((lead & 0xF8) == 0xF0 ? 3 : 0)));
+    if ((int)back < need) return n - 1 - back;
+  }
+  return n;
+}
+std::string Detokenizer::push(const std::vector<int>& ids) {
+  for (int id : ids) { if (skip_special_ && tk_->is_special(id)) continue; pending_ += tk_->token_bytes(id); }
+  const size_t k = complete_utf8_prefix(pending_);
+  std::string out = pending_.substr(0, k);
+  pending_.erase(0, k);
+  return out;
+}
+std::string Detokenizer::finish() {
+  std::string out;
+  if (!pending_.empty()) out = "\xEF\xBF\xBD";
+  pending_.clear();
+  return out;
+}
+
+// ------------------------------------------------------------------------------------------------ chat template
+std::string render_chatml(const std::vector<ChatMessage>& msgs, const Json& tools, bool add_generation_prompt,
+                          bool enable_thinking, bool continue_final) {
+  std::string out;
+  size_t first = 0;
+  const bool has_tools = tools.is_array() && tools.size() > 0;
+  if (has_tools) {
+    out += "<|im_start|>system\n";
+    if (!msgs.empty() && msgs[0].role == "system") { out += msgs[0].content + "\n\n"; first = 1; }
+    out += "# Tools\n\nYou may call one or more functions to assist with the user query.\n\nYou are provided with function "
+           "signatures within <tools></tools> XML tags:\n<tools>";
+    for (auto& t : tools.items()) out += "\n" + t.dump_python();
+    out += "\n</tools>\n\nFor each function call, return a json object with function name and arguments within "
+           "<tool_call></tool_call> XML tags:\n<tool_call>\n{\"name\": <function-name>, \"arguments\": <args-json-object>}\n"
+           "</tool_call><|im_end|>\n";
+  } else if (!msgs.empty() && msgs[0].role == "system") {
+    out += "<|im_start|>system\n" + msgs[0].content + "<|im_end|>\n";
+    first = 1;
+  }
+  for (size_t i = first; i < msgs.size(); ++i) {
+    const ChatMessage& m = msgs[i];
+    const bool last = i + 1 == msgs.size();
+    if (m.role == "tool") {
+      const bool prev_tool = i > first && msgs[i - 1].role == "tool";
+      const bool next_tool = !last && msgs[i + 1].role == "tool";
+      if (!prev_tool) out += "<|im_start|>user";
+      out += "\n<tool_response>\n" + m.content + "\n</tool_response>";
+      if (!next_tool) out += "<|im_end|>\n";
+      continue;
+    }
+    out += "<|im_start|>" + m.role + "\n";
+    if (m.role == "assistant") {
+      if (!m.reasoning.empty()) out += "<think>\n" + m.reasoning + "\n</think>\n\n";
+      out += m.content;
+      if (m.tool_calls.is_array())
+        for (auto& tc : m.tool_calls.items()) {
+          const Json* fn = tc.find("function");
+          const Json& f = fn ? *fn : tc;
+          Json args = Json::object();
+          if (auto a = f.find("arguments")) { if (a->is_string()) { try { args = Json::parse(a->as_string()); } catch (...) { args = *a; } } else args = *a; }
+          if (!m.content.empty() || &tc != &m.tool_calls.items()[0]) out += "\n";
+          out += "<tool_call>\n{\"name\": \"" + f.get_string("name", "") + "\", \"arguments\": " + args.dump_python() + "}\n</tool_call>";
+        }
+    } else out += m.content;
+    if (last && continue_final && m.role == "assistant") return out;
+    out += "<|im_end|>\n";
+  }
+  if (add_generation_prompt) {
+    out += "<|im_start|>assistant\n";
+    if (!enable_thinking) out += "<think>\n\n</think>\n\n";
+  }
+  return out;
+}
+
+// ------------------------------------------------------------------------------------------------ reasoning parser
+static size_t partial_suffix(const std::string& s, const std::string& tag) {
+  // longest proper prefix of tag that is a suffix of s
+  const size_t m = std::min(s.size(), tag.size() - 1);
+  for (size_t k = m; k > 0; --k) if (s.compare(s.size() - k, k, tag, 0, k) == 0) return k;
+  return 0;
+}
+ReasoningParser::Out ReasoningParser::parse_all(const std::string& text) const {
+  Out o;
+  std::string t = text;
+  bool in = in_;
+  const size_t op = t.find(open_);
+  if (op != std::string::npos && (in || t.find_first_not_of(" \n\t") == op)) { t.erase(0, op + open_.size()); in = true; }
+  if (!in) { o.content = text; return o; }
+  const size_t cl = t.find(close_);
+  if (cl == std::string::npos) { o.reasoning = t; return o; }
+  o.reasoning = t.substr(0, cl);
+  o.content = t.substr(cl + close_.size());
+  auto trim = [](std::string& s) { size_t a = s.find_first_not_of("\n"); if (a == std::string::npos) { s.clear(); return; } s.erase(0, a); };
+  trim(o.content);
+  while (!o.reasoning.empty() && (o.reasoning.back() == '\n')) o.reasoning.pop_back();
+  while (!o.reasoning.empty() && (o.reasoning.front() == '\n')) o.reasoning.erase(0, 1);
+  return o;
+}
+ReasoningParser::Out ReasoningParser::push(const std::string& delta) {
+  Out o;
+  buf_ += delta;
+  while (true) {
+    if (!in_) {
+      if (!stripped_open_) {
+        const size_t op = buf_.find(open_);
+        if (op != std::string::npos && buf_.find_first_not_of(" \n\t") == op) { buf_.erase(0, op + open_.size()); in_ = true; stripped_open_ = true; continue; }
+        if (partial_suffix(buf_, open_) && buf_.find_first_not_of(" \n\t") != std::string::npos &&
+            buf_.find_first_not_of(" \n\t") + partial_suffix(buf_, open_) == buf_.size()) return o;   // may still become the tag
+      }
+      if (strip_nl_) {       // newlines right after the closing tag belong to the block, whichever chunk brings them
+        size_t a = buf_.find_first_not_of('\n');
+        if (a == std::string::npos) { buf_.clear(); return o; }
+        buf_.erase(0, a);
+        strip_nl_ = false;
+      }
+      o.content += buf_;
+      buf_.clear();
+      return o;
+    }
+    if (!stripped_open_) {   // started inside the block: a leading open tag in the output is dropped
+      const size_t op = buf_.find(open_);
+      if (op == 0) { buf_.erase(0, open_.size()); stripped_open_ = true; continue; }
+      if (!buf_.empty() && partial_suffix(buf_, open_) == buf_.size()) return o;
+      stripped_open_ = true;
+    }
+    const size_t cl = buf_.find(close_);
+    if (cl != std::string::npos) {
+      std::string r = buf_.substr(0, cl);
+      buf_.erase(0, cl + close_.size());
+      in_ = false;
+      if (stream_) o.reasoning += r; else { held_reasoning_ += r; o.reasoning += held_reasoning_; held_reasoning_.clear(); }
+      strip_nl_ = true;
+      stripped_open_ = true;
+      continue;
+    }
+    const size_t keep = partial_suffix(buf_, close_);
+    std::string r = buf_.substr(0, buf_.size() - keep);
+    buf_.erase(0, buf_.size() - keep);
+    if (stream_) o.reasoning += r; else held_reasoning_ += r;
+    return o;
+  }
+}
+ReasoningParser::Out ReasoningParser::finish() {
+  Out o;
+  if (in_) { o.reasoning = held_reasoning_ + buf_; } else o.content = buf_;
+  buf_.clear(); held_reasoning_.clear();
+  return o;
+}
+
+// ------------------------------------------------------------------------------------------------ tool calls
+static const Json* tool_schema(const Json& tools, const std::string& name) {
+  if (!tools.is_array()) return nullptr;
+  for (auto& t : tools.items()) {
+    const Json* f = t.find("function");
+    const Json& fn = f ? *f : t;
+    if (fn.get_string("name", "") == name) return fn.find("parameters");
+  }
+  return nullptr;
+}
+static Json typed_value(const std::string& raw, const Json* schema, const std::string& key) {
+  std::string type = "string";
+  if (schema) if (auto props = schema->find("properties")) if (auto p = props->find(key)) {
+    if (auto t = p->find("type")) { if (t->is_string()) type = t->as_string(); else if (t->is_array() && t->size()) type = (*t)[0].as_string(); }
+    else if (p->contains("enum")) type = "string"; else if (p->contains("properties")) type = "object";
+  }
+  if (type == "string") return Json(raw);
+  try { return Json::parse(raw); } catch (...) {}
+  if (type == "boolean") { if (raw == "True" || raw == "true") return Json(true); if (raw == "False" || raw == "false") return Json(false); }
+  return Json(raw);
+}
+static std::string strip_nl(std::string v) {
+  if (!v.empty() && v[0] == '\n') v.erase(0, 1);
+  if (!v.empty() && v.back() == '\n') v.pop_back();
+  return v;
+}
+static bool parse_function_block(const std::string& body, const Json& tools, ToolCall& out) {
+  // body = NAME>...<parameter=K>V</parameter>...
+  const size_t gt = body.find('>');
+  if (gt == std::string::npos) return false;
+  out.name = body.substr(0, gt);
+  const Json* schema = tool_schema(tools, out.name);
+  Json args = Json::object();
+  size_t pos = gt + 1;
+  while (true) {
+    const size_t p = body.find("<parameter=", pos);
+    if (p == std::string::npos) break;
+    const size_t kend = body.find('>', p);
+    if (kend == std::string::npos) break;
+    const std::string key = body.substr(p + 11, kend - p - 11);
+    size_t vend = body.find("</parameter>", kend);
+    const size_t next = body.find("<parameter=", kend);
+    size_t stop = std::min(vend, next);
+    if (stop == std::string::npos) stop = body.size();
+    args.set(key, typed_value(strip_nl(body.substr(kend + 1, stop - kend - 1)), schema, key));
+    pos = (vend != std::string::npos && vend == stop) ? vend + 12 : stop;
+  }
+  out.arguments_json = args.dump_python();
+  return true;
+}
+ToolParse parse_tool_calls(const std::string& text, const Json& tools) {
+  ToolParse r;
+  size_t pos = 0;
+  while (pos < text.size()) {
+    const size_t a = text.find("<tool_call>", pos), b = text.find("<function=", pos);
+    const size_t s = std::min(a, b);
+    if (s == std::string::npos) { r.content += text.substr(pos); break; }
+    r.content += text.substr(pos, s - pos);
+    if (s == a) {
+      size_t e = text.find("</tool_call>", s);
+      const std::string body = text.substr(s + 11, (e == std::string::npos ? text.size() : e) - s - 11);
+      const size_t fb = body.find("<function=");
+      ToolCall tc;
+      bool ok = false;
+      if (fb != std::string::npos) {
+        size_t fe = body.find("</function>", fb);
+        ok = parse_function_block(body.substr(fb + 10, (fe == std::string::npos ? body.size() : fe) - fb - 10), tools, tc);
+      } else {
+        try {
+          Json j = Json::parse(body);
+          tc.name = j.get_string("name", "");
+          const Json* ar = j.find("arguments");
+          if (!ar) ar = j.find("parameters");
+          tc.arguments_json = ar ? (ar->is_string() ? ar->as_string() : ar->dump_python()) : "{}";
+          ok = !tc.name.empty();
+        } catch (...) { ok = false; }
+      }
+      if (ok) r.calls.push_back(tc); else r.content += text.substr(s, (e == std::string::npos ? text.size() : e + 12) - s);
+      pos = e == std::string::npos ? text.size() : e + 12;
+    } else {
+      size_t e = text.find("</function>", s);
+      ToolCall tc;
+      if (parse_function_block(text.substr(s + 10, (e == std::string::npos ? text.size() : e) - s - 10), tools, tc)) r.calls.push_back(tc);
+      pos = e == std::string::npos ? text.size() : e + 11;
+    }
+  }
+  while (!r.content.empty() && (r.content.back() == '\n' || r.content.back() == ' ')) r.content.pop_back();
+  return r;
+}
+
+ToolParse ToolStreamParser::push(const std::string& delta) {
+  ToolParse out;
+  buf_ += delta;
+  while (true) {
+    const size_t a = buf_.find("<tool_call>"), b = buf_.find("<function=");
+    const size_t s = std::min(a, b);
+    if (s == std::string::npos) {
+      // emit everything except a tail that may still grow into a tag
+      const size_t keep = std::max(partial_suffix(buf_, "<tool_call>"), partial_suffix(buf_, "<function="));
+      out.content += buf_.substr(0, buf_.size() - keep);
+      buf_.erase(0, buf_.size() - keep);
+      return out;
+    }
+    out.content += buf_.substr(0, s);
+    buf_.erase(0, s);
+    const std::string close = (s == a) ? "</tool_call>" : "</function>";
+    const size_t e = buf_.find(close);
+    if (e == std::string::npos) return out;   // the call is still being generated
+    ToolParse one = parse_tool_calls(buf_.substr(0, e + close.size()), tools_);
+    for (auto& c : one.calls) out.calls.push_back(c);
+    out.content += one.content;
+    buf_.erase(0, e + close.size());
+  }
+}
+ToolParse ToolStreamParser::finish() {
+  ToolParse out = parse_tool_calls(buf_, tools_);
+  buf_.clear();
+  return out;
+}
+
+}  // namespace b2

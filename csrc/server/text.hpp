@@ -1,0 +1,87 @@
+// Text layer of the server: byte-level BPE tokenizer (Hugging Face tokenizer.json), incremental detokenizer,
+// chat template, reasoning splitter and tool-call parsers.  See text.cpp for the behaviour each class keeps.
+#pragma once
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../core/json.hpp"
+
+namespace b2 {
+
+class Tokenizer {
+ public:
+  // Loads vocab, merges and added tokens from tokenizer.json text.  Throws std::runtime_error on malformed input.
+  static Tokenizer from_json(const std::string& text);
+  std::vector<int> encode(const std::string& text) const;                  // added/special tokens are matched first
+  std::string decode(const std::vector<int>& ids, bool skip_special) const;
+  std::string token_bytes(int id) const;                                   // raw bytes of one token ("" if unknown)
+  bool is_special(int id) const { return special_.count(id) != 0; }
+  int token_to_id(const std::string& s) const;                             // added tokens and plain vocab entries
+  int size() const { return (int)id_to_tok_.size(); }
+
+ private:
+  std::vector<std::string> pretokenize(const std::string& text) const;
+  void bpe(const std::string& piece, std::vector<int>& out) const;
+  std::unordered_map<std::string, int> vocab_;              // byte-level string -> id
+  std::vector<std::string> id_to_tok_;                      // id -> byte-level string (or added-token text)
+  std::unordered_map<std::string, int> merge_rank_;         // "a b" -> rank
+  std::vector<std::pair<std::string, int>> added_;          // added tokens, longest first
+  std::unordered_map<int, bool> special_;
+  std::unordered_map<int, bool> is_added_;
+};
+
+// Streams text out of a growing id list without ever emitting half a UTF-8 sequence.
+class Detokenizer {
+ public:
+  Detokenizer(const Tokenizer* tk, bool skip_special) : tk_(tk), skip_special_(skip_special) {}
+  std::string push(const std::vector<int>& ids);   // returns the text that became final
+  std::string finish();                            // flushes held-back bytes (invalid tails become U+FFFD)
+ private:
+  const Tokenizer* tk_;
+  bool skip_special_;
+  std::string pending_;
+};
+
+struct ChatMessage { std::string role, content, reasoning; Json tool_calls; std::string tool_call_id; };
+
+// ChatML rendering (the template family of the dense GQA checkpoints): system/user/assistant/tool turns, a tools
+// preamble, generation prompt, optional disabled thinking (empty think block) and continue_final_message.
+std::string render_chatml(const std::vector<ChatMessage>& msgs, const Json& tools, bool add_generation_prompt,
+                          bool enable_thinking, bool continue_final);
+
+// Splits generated text into reasoning and content around <think> ... </think>.
+class ReasoningParser {
+ public:
+  ReasoningParser(bool starts_in_reasoning, bool stream_reasoning, std::string open = "<think>", std::string close = "</think>")
+      : in_(starts_in_reasoning), stream_(stream_reasoning), open_(std::move(open)), close_(std::move(close)) {}
+  struct Out { std::string content, reasoning; };
+  Out parse_all(const std::string& text) const;
+  Out push(const std::string& delta);
+  Out finish();
+ private:
+  bool in_, stream_;
+  std::string open_, close_, buf_, held_reasoning_;
+  bool stripped_open_ = false, strip_nl_ = false;
+};
+
+struct ToolCall { std::string name, arguments_json; };
+
+// Tool calls in either wire format: <tool_call>{"name": .., "arguments": {..}}</tool_call> (JSON body) or
+// <function=NAME><parameter=KEY>VALUE</parameter>...</function> (typed by the tool's JSON schema).
+struct ToolParse { std::string content; std::vector<ToolCall> calls; };
+ToolParse parse_tool_calls(const std::string& text, const Json& tools);
+
+class ToolStreamParser {
+ public:
+  explicit ToolStreamParser(Json tools) : tools_(std::move(tools)) {}
+  // Feeds generated text; returns content that is certainly not part of a call, and calls completed so far.
+  ToolParse push(const std::string& delta);
+  ToolParse finish();
+ private:
+  Json tools_;
+  std::string buf_;
+};
+
+}  // namespace b2

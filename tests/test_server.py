@@ -1,0 +1,193 @@
+"""CPU tests of the server stack with the mock backend (model: crates/agens-server/tests: tokenizer / template /
+parser / request / e2e parity suites and server_basics.rs)."""
+import json
+import socket
+import threading
+
+import pytest
+
+from agens_engine_b200.serve import server as S
+from tests.fixtures import tiny_tokenizer_json
+
+SAMPLES = ["hello world", "the thing and the other thing", "Hello,  world!\n\nNew   paragraph's text isn't  here ",
+           "x=12*345;\n\ty = 'it''s'", "naïve café — ünïcödé 漢字かな 한국어", "tabs\t\tand\r\nCRLF  \n  trailing   ", "   lead",
+           "emoji 🙂 ok", "a" * 50 + " " * 7 + "b", "<|im_start|>user\nhi<|im_end|>\n<think>x</think>", "12 1234 12th"]
+
+
+@pytest.fixture(scope="module")
+def tok_text():
+    return tiny_tokenizer_json()
+
+
+@pytest.fixture(scope="module")
+def tok_path(tmp_path_factory, tok_text):
+    p = tmp_path_factory.mktemp("tok") / "tokenizer.json"
+    p.write_text(tok_text)
+    return str(p)
+
+
+def test_tokenizer_matches_hf_tokenizers(tok_text):
+    tokenizers = pytest.importorskip("tokenizers")
+    ref = tokenizers.Tokenizer.from_str(tok_text)
+    mine = S.Tokenizer(tok_text)
+    for s in SAMPLES:
+        want = ref.encode(s, add_special_tokens=False).ids
+        assert mine.encode(s) == want, s
+        assert mine.decode(want, skip_special=False) == s
+    ids = mine.encode("<|im_start|>the<|im_end|>")
+    assert mine.decode(ids, skip_special=True) == "the"
+
+
+def test_stream_detok_never_splits_utf8(tok_text):
+    mine = S.Tokenizer(tok_text)
+    s = "漢字 🙂 ünï"
+    ids = mine.encode(s)
+    parts = mine.stream_decode(ids, step=1)
+    assert "".join(parts) == s
+    for p in parts:
+        p.encode("utf-8").decode("utf-8")          # every piece is valid on its own
+    cut = mine.stream_decode(ids[:2], step=1)       # ends inside a multi-byte character
+    assert cut[-1] == "�"
+
+
+def test_chat_template():
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    t = S.render_chat(msgs)
+    assert t == "<|im_start|>system\nbe brief<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
+    assert S.render_chat(msgs, enable_thinking=False).endswith("<|im_start|>assistant\n<think>\n\n</think>\n\n")
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {"x": {"type": "integer"}}}}}]
+    tt = S.render_chat(msgs, tools=tools)
+    assert "# Tools" in tt and '"name": "f"' in tt and tt.index("be brief") < tt.index("# Tools")
+    conv = msgs + [{"role": "assistant", "content": "", "tool_calls": [{"function": {"name": "f", "arguments": "{\"x\": 1}"}}]},
+                   {"role": "tool", "content": "42"}]
+    tc = S.render_chat(conv, tools=tools)
+    assert '<tool_call>\n{"name": "f", "arguments": {"x": 1}}\n</tool_call><|im_end|>' in tc
+    assert "<|im_start|>user\n<tool_response>\n42\n</tool_response><|im_end|>" in tc
+    cont = S.render_chat(msgs + [{"role": "assistant", "content": "par"}], add_generation_prompt=False, continue_final=True)
+    assert cont.endswith("<|im_start|>assistant\npar")
+
+
+@pytest.mark.parametrize("chunk", [0, 1, 3, 7])
+def test_reasoning_and_tool_parsers(chunk):
+    tools = [{"type": "function", "function": {"name": "get", "parameters": {"type": "object", "properties": {
+        "n": {"type": "integer"}, "q": {"type": "string"}, "flag": {"type": "boolean"}}}}}]
+    text = '<think>\nlet me see\n</think>\n\nAnswer first.\n<tool_call>\n{"name": "get", "arguments": {"n": 3, "q": "a b"}}\n</tool_call>'
+    r = S.parse_output(text, tools, chunk=chunk)
+    assert r["reasoning"].strip() == "let me see" and r["content"].strip() == "Answer first."
+    assert r["tool_calls"] == [{"name": "get", "arguments": '{"n": 3, "q": "a b"}'}]
+    xml = "ok<function=get>\n<parameter=n>\n5\n</parameter>\n<parameter=q>\nhello\n</parameter>\n<parameter=flag>\ntrue\n</parameter>\n</function>"
+    r2 = S.parse_output(xml, tools, chunk=chunk)
+    assert r2["content"] == "ok" and json.loads(r2["tool_calls"][0]["arguments"]) == {"n": 5, "q": "hello", "flag": True}
+    r3 = S.parse_output("still thinking", starts_in_reasoning=True, chunk=chunk)
+    assert r3 == {"content": "", "reasoning": "still thinking", "tool_calls": []}
+    r4 = S.parse_output("a < b and <thin air", chunk=chunk)
+    assert r4["content"] == "a < b and <thin air" and r4["reasoning"] == ""
+
+
+def _server(tok_path, tok_text, script_text, step=2, **kw):
+    tk = S.Tokenizer(tok_text)
+    sv = S.Server(tok_path, model_name="m", generation_config={"temperature": 1.0, "top_k": 20, "top_p": 0.95},
+                  eos_token_ids=[tk.encode("<|im_end|>")[0]], **kw)
+    sv.use_mock(tk.encode(script_text), step=step)
+    return sv, tk
+
+
+def test_chat_completion_non_stream_defaults_and_usage(tok_path, tok_text):
+    sv, tk = _server(tok_path, tok_text, "<think>hm</think>\n\nhello world<|im_end|>ignored")
+    st, body = sv.handle("POST", "/v1/chat/completions", {"model": "m", "messages": [{"role": "user", "content": "hi"}]}, session_id="abc")
+    assert st == 200, body
+    r = json.loads(body)
+    msg = r["choices"][0]["message"]
+    assert msg["content"] == "hello world" and msg["reasoning_content"] == "hm" and r["choices"][0]["finish_reason"] == "stop"
+    assert r["usage"]["prompt_tokens"] == len(tk.encode(S.render_chat([{"role": "user", "content": "hi"}])))
+    assert r["usage"]["completion_tokens"] == len(tk.encode("<think>hm</think>\n\nhello world")) + 1
+    call = sv.mock_calls()[0]
+    assert call["session_id"] == "abc"                                 # header wins / is forwarded
+    s = call["sampling"]
+    assert s["temperature"] == 1.0 and s["top_k"] == 20 and s["top_p"] == 0.95 and s["max_new_tokens"] == 32768
+    st, body = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "temperature": 0})
+    assert sv.mock_calls()[-1]["sampling"]["top_k"] == 1              # greedy is top_k = 1
+
+
+def test_streaming_sse_stop_string_and_max_tokens(tok_path, tok_text):
+    sv, tk = _server(tok_path, tok_text, "the thing and the other thing", step=3)
+    st, body = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "stream": True,
+                                                           "stop": ["other"], "stream_options": {"include_usage": True}})
+    events = [json.loads(l[6:]) for l in body.split("\n\n") if l.startswith("data: {")]
+    assert body.endswith("data: [DONE]\n\n") and events[0]["choices"][0]["delta"]["role"] == "assistant"
+    text = "".join(e["choices"][0]["delta"].get("content", "") for e in events if e["choices"])
+    assert text == "the thing and the "
+    assert [e for e in events if e["choices"]][-1]["choices"][0]["finish_reason"] == "stop"
+    assert events[-1]["usage"]["completion_tokens"] > 0 and events[-1]["choices"] == []
+    st, body = sv.handle("POST", "/v1/completions", {"prompt": "the", "max_tokens": 2})
+    r = json.loads(body)
+    assert r["choices"][0]["finish_reason"] == "length" and r["usage"]["completion_tokens"] == 2
+    assert r["choices"][0]["text"] == tk.decode(tk.encode("the thing and the other thing")[:2])
+    st, body = sv.handle("POST", "/v1/completions", {"prompt": [1, 2, 3], "max_tokens": 1})
+    assert st == 200 and sv.mock_calls()[-1]["prompt"] == [1, 2, 3]
+
+
+def test_tool_call_response(tok_path, tok_text):
+    sv, _ = _server(tok_path, tok_text, '<tool_call>\n{"name": "f", "arguments": {"x": 1}}\n</tool_call><|im_end|>')
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {"x": {"type": "integer"}}}}}]
+    st, body = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "tools": tools})
+    r = json.loads(body)["choices"][0]
+    assert r["finish_reason"] == "tool_calls" and r["message"]["content"] is None
+    tc = r["message"]["tool_calls"][0]
+    assert tc["function"] == {"name": "f", "arguments": '{"x": 1}'} and tc["id"].startswith("call_") and len(tc["id"]) == 29
+
+
+def test_validation_errors_and_routes(tok_path, tok_text):
+    sv, _ = _server(tok_path, tok_text, "hello")
+    bad = [({"messages": []}, "non-empty"), ({"messages": [{"role": "user", "content": "x"}], "n": 2}, "n > 1"),
+           ({"messages": [{"role": "user", "content": "x"}], "response_format": {"type": "json_object"}}, "response_format"),
+           ({"messages": [{"role": "user", "content": "x"}], "logprobs": True}, "logprobs"),
+           ({"messages": [{"role": "user", "content": "x"}], "temperature": -1}, "temperature"),
+           ({"messages": [{"role": "user", "content": "x"}], "top_p": 0}, "top_p"),
+           ({"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "data:image/png;base64,AA"}}]}]}, "images")]
+    for body, frag in bad:
+        st, text = sv.handle("POST", "/v1/chat/completions", body)
+        assert st == 400 and frag in json.loads(text)["error"]["message"], (body, text)
+    assert sv.handle("POST", "/v1/completions", {"prompt": ["a", "b"]})[0] == 400
+    assert sv.handle("POST", "/v1/completions", {"prompt": "a", "echo": True})[0] == 400
+    assert sv.handle("GET", "/health")[0] == 200 and sv.handle("GET", "/health_generate") == (200, "")
+    st, text = sv.handle("GET", "/v1/models")
+    assert json.loads(text)["data"][0]["id"] == "m"
+    assert sv.handle("GET", "/v1/models/m")[0] == 200 and sv.handle("GET", "/v1/models/zzz")[0] == 404
+    assert "b200e_requests_total" in sv.handle("GET", "/metrics")[1]
+
+
+def test_engine_callback_backend_and_socket(tok_path, tok_text):
+    tk = S.Tokenizer(tok_text)
+    sv = S.Server(tok_path, model_name="m", eos_token_ids=[tk.encode("<|im_end|>")[0]])
+    out = tk.encode("hello world<|im_end|>")
+    seen = {}
+
+    def generate(req_id, prompt, sampling, session):
+        seen["prompt"], seen["sampling"] = prompt, sampling
+        def run():
+            for i in range(0, len(out), 2):
+                if sv.push(req_id, out[i:i + 2]):
+                    break
+            sv.push(req_id, [], finished=True)
+        threading.Thread(target=run).start()
+
+    sv.use_engine(generate, context_length=4096)
+    port = sv.start()
+    body = json.dumps({"messages": [{"role": "user", "content": "hi"}], "stream": True}).encode()
+    s = socket.create_connection(("127.0.0.1", port))
+    s.sendall(b"POST /v1/chat/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\nContent-Length: %d\r\n\r\n" % len(body) + body)
+    data = b""
+    while True:
+        chunk = s.recv(65536)
+        if not chunk:
+            break
+        data += chunk
+    s.close()
+    sv.stop()
+    head, _, payload = data.partition(b"\r\n\r\n")
+    assert b"200 OK" in head and b"text/event-stream" in head
+    events = [json.loads(l[6:]) for l in payload.decode().split("\n\n") if l.startswith("data: {")]
+    text = "".join(e["choices"][0]["delta"].get("content", "") for e in events if e["choices"])
+    assert text == "hello world" and payload.decode().endswith("data: [DONE]\n\n")
+    assert seen["prompt"] == tk.encode(S.render_chat([{"role": "user", "content": "hi"}]))
