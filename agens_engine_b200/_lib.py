@@ -130,6 +130,15 @@ class AttnDecodeArgs(C.Structure):
     ]
 
 
+class SampleArgs(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("ld", C.c_long), ("vocab", C.c_int),
+        ("temperature", C.c_void_p), ("top_k", C.c_void_p), ("top_p", C.c_void_p), ("min_p", C.c_void_p),
+        ("seed", C.c_void_p), ("position", C.c_void_p),
+        ("out", C.c_void_p),
+    ]
+
+
 PRO_PLAIN, PRO_NORM = 0, 1
 EPI_STORE, EPI_RESID, EPI_SWIGLU, EPI_F32, EPI_ARGMAX, EPI_TP_RESID = range(6)
 
@@ -166,6 +175,8 @@ def _declare(lib: C.CDLL):
         "b2_comm_reduce_scatter": ([C.POINTER(CommArgs), vp, l, vp, vp], i),
         "b2_comm_barrier": ([C.POINTER(CommArgs), vp], i),
         "b2_comm_argmax_combine": ([C.POINTER(CommArgs), vp, vp, i, vp, vp, vp], i),
+        "b2_sample_rows": ([C.POINTER(SampleArgs), i, vp], i),
+        "b2_spec_accept": ([vp, vp, vp, vp, i, vp, vp, i, vp], i),
         "b2_gemm_bf16": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp, vp], i),
     }
     for name, (args, res) in sig.items():

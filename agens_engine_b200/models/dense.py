@@ -59,6 +59,7 @@ class DenseModel:
         self.seq_pages: Dict[int, List[int]] = {}
         self.seq_len_host: Dict[int, int] = {}
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
+        self.row_graphs = False                        # forward_rows replays a per-shape CUDA graph when set
         self._alloc_buffers()
 
     # ------------------------------------------------------------------------------------------------ weights
@@ -241,13 +242,37 @@ class DenseModel:
         t = lambda x: torch.tensor(x, dtype=torch.int32, device=self.dev)
         self.ids[:m] = t(ids); self.tok_pos[:m] = t(pos); self.tok_seq[:m] = t(seqs)
         self.grp_tok0[:len(g0)] = t(g0); self.grp_cnt[:len(g0)] = t(gc)
-        basic.embed(self.ids[:m], self.embed, self.ss_a, status=self.status, out=self.h_a[:m])
-        parts = self._layers_small(m, len(g0))
-        self._head_small(m, parts, want_logits)
+        if self.row_graphs:
+            self._rows_graph(m, len(g0), want_logits).replay()
+        else:
+            self._rows_body(m, len(g0), want_logits)
         for s, n in nxt.items():
             self.seq_len_host[s] = n
             self.seq_len[s] = n
         return self.out_ids[:m].clone(), (self.logits[:m].clone() if want_logits else None)
+
+    def _rows_body(self, m: int, n_groups: int, want_logits: bool):
+        basic.embed(self.ids[:m], self.embed, self.ss_a, status=self.status, out=self.h_a[:m])
+        parts = self._layers_small(m, n_groups)
+        self._head_small(m, parts, want_logits)
+
+    def _rows_graph(self, m: int, n_groups: int, want_logits: bool) -> torch.cuda.CUDAGraph:
+        """CUDA graph of one eager-shaped step (rows, groups and positions are read from device buffers, so one graph
+        serves every step of the same shape: verify blocks, drafter steps, mixed batches)."""
+        key = ("rows", m, n_groups, want_logits)
+        g = self._graphs.get(key)
+        if g is None:
+            st = torch.cuda.Stream(device=self.dev)
+            st.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(st):
+                self._rows_body(m, n_groups, want_logits)          # warm-up: the step is idempotent on its buffers
+            torch.cuda.current_stream(self.dev).wait_stream(st)
+            torch.cuda.synchronize(self.dev)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                self._rows_body(m, n_groups, want_logits)
+            self._graphs[key] = g
+        return g
 
     # ------------------------------------------------------------------------------------------------ prefill
     def _linear_big(self, lin: L.WqLinear, x: torch.Tensor) -> torch.Tensor:

@@ -1,0 +1,83 @@
+"""Multi-token-prediction (MTP) head: one extra decoder layer of the target's shape that shares its embedding and
+lm_head and drafts from the target's own hidden state.
+
+Input of MTP position ``i`` is ``fc([norm_e(E[t_{i+1}]) ; norm_h(h_i)])`` where ``h_i`` is the target's last-layer
+residual stream at position ``i`` and ``t_{i+1}`` the token that follows; the layer's output goes through the shared
+final norm and lm_head and predicts ``t_{i+2}``.  Deeper drafts feed the layer's own output back as ``h``.
+Reference: ``crates/agens-dense/src/lib.rs:4305`` (``mtp_draft``, ``mtp_absorb``) and the MTP weights handled by
+``tools/volundr_mtp_export.py``.
+"""
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from ..ops import basic
+from ..ops import linear as L
+from .._lib import EPI_STORE
+from .config import ModelConfig, scaled
+from .dense import DenseModel, M_GEMV
+
+
+class MtpHead(DenseModel):
+    """One-layer model with its own paged KV; ``embed``, ``final_norm`` weights for the head and ``lm_head`` are the
+    target's tensors (shared, not copied)."""
+
+    def __init__(self, target: DenseModel, **kw):
+        cfg = scaled(target.cfg, 1)
+        kw.setdefault("max_seqs", target.max_seqs)
+        kw.setdefault("max_ctx", target.max_ctx)
+        kw.setdefault("split_keys", target.split_keys)
+        super().__init__(cfg, target.dev, lm_rows=target.lm_rows, **kw)
+        self.embed, self.lm_head = target.embed, target.lm_head
+        self.final_norm = target.final_norm
+        self.fc: Optional[L.WqLinear] = None
+        self.norm_e = self.norm_h = None
+        self.cat = torch.zeros(M_GEMV, 2 * cfg.d_model, dtype=torch.bfloat16, device=self.dev)
+        self.hid_in = torch.zeros(M_GEMV, cfg.d_model, dtype=torch.bfloat16, device=self.dev)
+
+    @staticmethod
+    def random_init_for(target: DenseModel, seed: int = 7, **kw) -> "MtpHead":
+        m = MtpHead(target, **kw)
+        cfg, dev = m.cfg, m.dev
+        g = torch.Generator(device=dev).manual_seed(seed)
+        shapes = cfg.linear_shapes()
+        d = {}
+        for i, (lin, (n, k)) in enumerate(shapes.items()):
+            d[lin] = L.WqLinear.random(n, k, 4, cfg.group, dev, seed=seed * 7919 + i)
+        d["ln1"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=dev, generator=g)).to(torch.bfloat16)
+        d["ln2"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=dev, generator=g)).to(torch.bfloat16)
+        m.layers.append(d)
+        m.fc = L.WqLinear.random(cfg.d_model, 2 * cfg.d_model, 4, cfg.group, dev, seed=seed * 7919 + 100)
+        m.norm_e = (1.0 + 0.05 * torch.randn(cfg.d_model, device=dev, generator=g)).to(torch.bfloat16)
+        m.norm_h = (1.0 + 0.05 * torch.randn(cfg.d_model, device=dev, generator=g)).to(torch.bfloat16)
+        return m.finalize()
+
+    def finalize(self):
+        super().finalize()
+        if self.fc is not None:
+            from .. import _lib
+            need = _lib.cuda_lib().b2_wq_gemv_scratch_floats(self.fc.n, self.fc.k, self.fc.ks, 2, M_GEMV)
+            if need > self.ws.scratch.numel():
+                self.ws = L.GemvWorkspace(self.dev, floats=need, panels=max(self.ws.counters.numel(), 1 << 10))
+        return self
+
+    def _rows_body(self, m: int, n_groups: int, want_logits: bool):
+        cfg = self.cfg
+        d = cfg.d_model
+        e = basic.embed(self.ids[:m], self.embed, None, status=self.status)
+        self.cat[:m, :d] = basic.rmsnorm(e, self.norm_e, cfg.rms_eps)
+        self.cat[:m, d:] = basic.rmsnorm(self.hid_in[:m], self.norm_h, cfg.rms_eps)
+        L.gemv(self.fc, self.cat[:m], self.ws, epi=EPI_STORE, out=self.h_a[:m])
+        basic.sumsq(self.h_a[:m], self.ss_a)
+        parts = self._layers_small(m, n_groups)
+        self._head_small(m, parts, want_logits)
+
+    def forward_mtp(self, ids: List[int], hidden: torch.Tensor, seqs: List[int]):
+        """Rows ``(ids[i], hidden[i])`` appended to ``seqs[i]``; returns the drafted token of every row.  The layer's
+        output hidden state of every row stays in ``self.h_a``."""
+        m = len(ids)
+        self.hid_in[:m].copy_(hidden[:m])
+        out, _ = self.forward_rows(ids, seqs)
+        return out

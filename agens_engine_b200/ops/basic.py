@@ -92,3 +92,32 @@ def argmax_rows(logits: torch.Tensor, n_valid: Optional[int] = None) -> torch.Te
         check(lib.b2_argmax_rows(ptr(logits), logits.stride(0), logits.shape[0], n_valid or logits.shape[1], ptr(out),
                                  current_stream()), "b2_argmax_rows")
     return out
+
+
+def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional[torch.Tensor], top_p: Optional[torch.Tensor],
+                min_p: Optional[torch.Tensor], seed: torch.Tensor, position: torch.Tensor, n_valid: Optional[int] = None,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of fp32 ``logits``: the inverse CDF of the filtered distribution at the Philox uniform of
+    ``(seed[row], position[row])``.  ``temperature`` fp32, ``top_k`` int32, ``top_p``/``min_p`` fp32, ``seed`` int64
+    (bit pattern of a uint64), ``position`` int32; a row with ``temperature <= 0`` is greedy."""
+    lib = _lib.cuda_lib()
+    rows = logits.shape[0]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device) if out is None else out
+    a = _lib.SampleArgs(ptr(logits), logits.stride(0), n_valid or logits.shape[1], ptr(temperature), ptr(top_k), ptr(top_p),
+                        ptr(min_p), ptr(seed), ptr(position), ptr(out))
+    with torch.cuda.device(logits.device):
+        check(lib.b2_sample_rows(a, rows, current_stream()), "b2_sample_rows")
+    return out
+
+
+def spec_accept(ids: torch.Tensor, target: torch.Tensor, row0: torch.Tensor, cnt: torch.Tensor, max_block: int):
+    """Longest-prefix acceptance of verify blocks; returns ``(n_emitted [blocks], emitted [blocks, max_block])``."""
+    lib = _lib.cuda_lib()
+    nb = row0.numel()
+    n_emit = torch.empty(nb, dtype=torch.int32, device=ids.device)
+    emitted = torch.zeros(nb, max_block, dtype=torch.int32, device=ids.device)
+    with torch.cuda.device(ids.device):
+        check(lib.b2_spec_accept(ptr(ids), ptr(target), ptr(row0), ptr(cnt), nb, ptr(n_emit), ptr(emitted), max_block,
+                                 current_stream()), "b2_spec_accept")
+    return n_emit, emitted

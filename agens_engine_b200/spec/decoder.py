@@ -1,0 +1,267 @@
+"""Speculative decoding: draft sources, verify blocks and acceptance.
+
+A step of a sequence builds a verify block ``[t, d_1 .. d_n]`` (``t`` = the last emitted token, ``d_j`` drafts),
+runs it through the target as one group of rows, lets the target name its own token after every row (argmax, or the
+positional sample of ``ops.basic.sample_rows``) and accepts draft ``d_{j+1}`` iff it equals the target's token after
+row ``j``.  The emitted tokens are therefore exactly what plain decoding would have produced, greedy or sampled
+(the sampler's draw depends only on seed, position and logits).  Rejected rows are rolled back by truncating the
+sequence; their KV entries are overwritten by the next block.
+
+Draft sources, in the reference's cascade order (``crates/agens-dense/src/lib.rs:4191-4349``): copy-lookup over the
+sequence's own tokens, the MTP head, the companion drafter model.  Acceptance: ``kernels/m1/m1_model.cu:476-579``.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.dense import DenseModel
+from ..models.mtp import MtpHead
+from ..ops import basic
+
+MAX_BLOCK = 8          # rows of one verify group (bonus + 7 drafts)
+
+
+class DraftSource:
+    """Interface of a draft source for one sequence slot."""
+    name = "none"
+
+    def begin(self, seq: int, prompt: Sequence[int]):
+        pass
+
+    def propose(self, seq: int, history: Sequence[int], max_n: int) -> List[int]:
+        """Drafts continuing ``history`` (whose last element is the next input token)."""
+        return []
+
+    def feedback(self, seq: int, n_proposed: int, n_accepted: int):
+        pass
+
+    def end(self, seq: int):
+        pass
+
+
+class CopyLookupSource(DraftSource):
+    """Drafts by copying what followed the longest earlier occurrence of the current suffix (host side, C++)."""
+    name = "copy"
+
+    def __init__(self):
+        from ..serve import host
+        self._host = host
+        self.tables: Dict[int, object] = {}
+        self.fed: Dict[int, int] = {}
+
+    def begin(self, seq, prompt):
+        self.tables[seq] = self._host.CopyLookup()
+        self.fed[seq] = 0
+
+    def propose(self, seq, history, max_n):
+        t = self.tables[seq]
+        if self.fed[seq] > len(history):
+            t.truncate(len(history)); self.fed[seq] = len(history)
+        if self.fed[seq] < len(history):
+            t.extend(list(history[self.fed[seq]:])); self.fed[seq] = len(history)
+        drafts, _ = t.propose()
+        return drafts[:max_n]
+
+    def feedback(self, seq, n_proposed, n_accepted):
+        if n_proposed:
+            self.tables[seq].record(n_accepted)
+
+    def end(self, seq):
+        self.tables.pop(seq, None); self.fed.pop(seq, None)
+
+
+class ModelSource(DraftSource):
+    """A small model of the same vocabulary drafting greedily with its own paged KV."""
+    name = "drafter"
+
+    def __init__(self, drafter: DenseModel, depth: int = 4):
+        self.m, self.depth = drafter, depth
+
+    def begin(self, seq, prompt):
+        self.m.new_seq(seq)
+        if len(prompt) > 1:
+            self.m.prefill(seq, torch.tensor(list(prompt[:-1]), dtype=torch.int32))
+
+    def propose(self, seq, history, max_n):
+        m = self.m
+        have = m.seq_len_host[seq]
+        if have > len(history) - 1:                     # rows fed for drafts that were then rejected
+            m.truncate(seq, len(history) - 1); have = len(history) - 1
+        missing = list(history[have:])                  # always ends with the next input token
+        out = None
+        for c in range(0, len(missing), MAX_BLOCK):
+            rows = missing[c:c + MAX_BLOCK]
+            out, _ = m.forward_rows(rows, [seq] * len(rows))
+        drafts = [int(out[-1])]
+        while len(drafts) < min(max_n, self.depth):
+            out, _ = m.forward_rows([drafts[-1]], [seq])
+            drafts.append(int(out[0]))
+        return drafts
+
+    def end(self, seq):
+        self.m.free_seq(seq)
+
+
+class MtpSource(DraftSource):
+    """Drafts from the target's hidden state through the MTP layer.  Needs the verify step's hidden rows, which the
+    decoder hands over through :meth:`absorb`."""
+    name = "mtp"
+
+    def __init__(self, head: MtpHead, depth: int = 2):
+        self.h, self.depth = head, depth
+        self.pending: Dict[int, tuple] = {}
+
+    def begin(self, seq, prompt):
+        self.h.new_seq(seq)
+
+    def absorb(self, seq: int, tokens_after: Sequence[int], hidden: torch.Tensor):
+        """``hidden[i]`` is the target's state at a committed position and ``tokens_after[i]`` the token that follows
+        it.  Feeds the pairs to the MTP layer; the last row's output is the first draft."""
+        n = len(tokens_after)
+        out = None
+        for c in range(0, n, MAX_BLOCK):
+            e = min(n, c + MAX_BLOCK)
+            out = self.h.forward_mtp(list(tokens_after[c:e]), hidden[c:e], [seq] * (e - c))
+        self.pending[seq] = (int(out[-1]), self.h.h_a[e - c - 1:e - c].clone(), self.h.seq_len_host[seq])
+
+    def propose(self, seq, history, max_n):
+        if seq not in self.pending:
+            return []
+        first, hid, base = self.pending.pop(seq)
+        drafts = [first]
+        while len(drafts) < min(max_n, self.depth):
+            out = self.h.forward_mtp([drafts[-1]], hid, [seq])
+            hid = self.h.h_a[:1].clone()
+            drafts.append(int(out[0]))
+        self.h.truncate(seq, base)                      # recurrent rows are provisional
+        return drafts
+
+    def end(self, seq):
+        self.h.free_seq(seq); self.pending.pop(seq, None)
+
+
+@dataclasses.dataclass
+class SamplingState:
+    temperature: float = 0.0
+    top_k: int = 0
+    top_p: float = 1.0
+    min_p: float = 0.0
+    seed: int = 0
+
+
+@dataclasses.dataclass
+class SpecStats:
+    steps: int = 0
+    proposed: int = 0
+    accepted: int = 0
+    emitted: int = 0
+    by_source: Dict[str, List[int]] = dataclasses.field(default_factory=dict)
+
+    def tokens_per_step(self) -> float:
+        return self.emitted / max(self.steps, 1)
+
+
+class SpecDecoder:
+    """Drives target + draft sources for a set of sequences."""
+
+    def __init__(self, target: DenseModel, sources: Sequence[DraftSource], max_drafts: int = 4):
+        assert 0 <= max_drafts <= MAX_BLOCK - 1
+        self.t, self.sources, self.max_drafts = target, list(sources), max_drafts
+        self.hist: Dict[int, List[int]] = {}
+        self.samp: Dict[int, SamplingState] = {}
+        self.stats = SpecStats()
+        self._mtp = [s for s in self.sources if isinstance(s, MtpSource)]
+
+    # -------------------------------------------------------------------------------------------- sequences
+    def begin(self, seq: int, prompt: Sequence[int], sampling: Optional[SamplingState] = None) -> int:
+        """Prefills ``prompt`` and returns the first generated token."""
+        t = self.t
+        t.new_seq(seq)
+        self.samp[seq] = sampling or SamplingState()
+        sampled = self.samp[seq].temperature > 0
+        first, logits = t.prefill(seq, torch.tensor(list(prompt), dtype=torch.int32), want_logits=sampled)
+        if sampled:
+            first = int(self._sample(logits[None, :], [seq], [len(prompt)])[0])
+        self.hist[seq] = list(prompt) + [first]
+        for s in self.sources:
+            s.begin(seq, self.hist[seq])
+        return first
+
+    def end(self, seq: int):
+        for s in self.sources:
+            s.end(seq)
+        self.t.free_seq(seq)
+        self.hist.pop(seq); self.samp.pop(seq)
+
+    # -------------------------------------------------------------------------------------------- one step
+    def _sample(self, logits: torch.Tensor, seqs: List[int], positions: List[int]) -> torch.Tensor:
+        dev = logits.device
+        st = [self.samp[s] for s in seqs]
+        f = lambda xs: torch.tensor(xs, dtype=torch.float32, device=dev)
+        seed = torch.tensor([x.seed & 0x7FFFFFFFFFFFFFFF for x in st], dtype=torch.int64, device=dev)
+        return basic.sample_rows(logits, f([x.temperature for x in st]),
+                                 torch.tensor([x.top_k for x in st], dtype=torch.int32, device=dev),
+                                 f([x.top_p for x in st]), f([x.min_p for x in st]), seed,
+                                 torch.tensor(positions, dtype=torch.int32, device=dev), n_valid=self.t._lm_valid())
+
+    def step(self, seqs: Sequence[int], forced_drafts: Optional[Dict[int, List[int]]] = None) -> Dict[int, List[int]]:
+        """One verify step for every sequence of ``seqs``; returns the tokens each of them emitted (at least one).
+        ``forced_drafts`` overrides the draft sources (tests: corrupted drafts)."""
+        t = self.t
+        ids, rows_seq, row0, cnt, positions = [], [], [], [], []
+        used: Dict[int, tuple] = {}
+        for s in seqs:
+            h = self.hist[s]
+            drafts: List[int] = []
+            src_used = None
+            if forced_drafts is not None and s in forced_drafts:
+                drafts = list(forced_drafts[s])[:self.max_drafts]
+            else:
+                for src in self.sources:
+                    drafts = src.propose(s, h, self.max_drafts) if self.max_drafts else []
+                    if drafts:
+                        src_used = src
+                        break
+            room = t.max_ctx - t.seq_len_host[s] - 1
+            drafts = drafts[:max(room, 0)]
+            used[s] = (src_used, len(drafts))
+            row0.append(len(ids)); cnt.append(1 + len(drafts))
+            base = t.seq_len_host[s]
+            positions += [base + 1 + j for j in range(1 + len(drafts))]
+            ids += [h[-1]] + drafts
+            rows_seq += [s] * (1 + len(drafts))
+        sampled = any(self.samp[s].temperature > 0 for s in seqs)
+        base_len = {s: t.seq_len_host[s] for s in seqs}
+        out, logits = t.forward_rows(ids, rows_seq, want_logits=sampled)
+        target = self._sample(logits, rows_seq, positions) if sampled else out
+        dev = t.dev
+        ti = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+        n_emit, emitted = basic.spec_accept(ti(ids), target, ti(row0), ti(cnt), MAX_BLOCK)
+        n_emit_h, emitted_h = n_emit.cpu().tolist(), emitted.cpu().tolist()
+        result: Dict[int, List[int]] = {}
+        for b, s in enumerate(seqs):
+            k = n_emit_h[b]
+            toks = emitted_h[b][:k]
+            result[s] = toks
+            t.truncate(s, base_len[s] + k)
+            self.hist[s].extend(toks)
+            src, n_prop = used[s]
+            self.stats.steps += 1; self.stats.proposed += n_prop; self.stats.accepted += k - 1; self.stats.emitted += k
+            if src is not None:
+                src.feedback(s, n_prop, k - 1)
+                st = self.stats.by_source.setdefault(src.name, [0, 0]); st[0] += n_prop; st[1] += k - 1
+            for mtp in self._mtp:
+                # committed positions of this block: rows 0 .. k-1; the token after row j is toks[j]
+                mtp.absorb(s, toks, t.h_a[row0[b]:row0[b] + k])
+        return result
+
+    def generate(self, seq: int, prompt: Sequence[int], n_new: int, sampling: Optional[SamplingState] = None,
+                 eos: Optional[int] = None) -> List[int]:
+        out = [self.begin(seq, prompt, sampling)]
+        while len(out) < n_new and (eos is None or out[-1] != eos):
+            out += self.step([seq])[seq]
+        self.end(seq)
+        return out[:n_new]
