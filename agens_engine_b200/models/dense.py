@@ -24,22 +24,6 @@ from .config import LINEARS, ModelConfig
 M_GEMV = 32          # most token rows the GEMV family takes in one launch
 
 
-class PagePool:
-    """Free-list page allocator over the paged KV pool (16-token pages, reference: alloc_row m1_model.cu:1694)."""
-
-    def __init__(self, n_pages: int):
-        self.free = list(range(n_pages - 1, -1, -1))
-        self.n_pages = n_pages
-
-    def alloc(self) -> int:
-        if not self.free:
-            raise RuntimeError("KV pool exhausted")
-        return self.free.pop()
-
-    def release(self, pages):
-        self.free.extend(pages)
-
-
 class DenseModel:
     def __init__(self, cfg: ModelConfig, device="cuda:0", max_seqs: int = 1, max_ctx: int = 4096,
                  n_pages: Optional[int] = None, split_keys: int = 64, prefill_chunk: int = 256,
@@ -55,8 +39,10 @@ class DenseModel:
         self.embed = None
         self.final_norm = None
         self.lm_head: Optional[L.WqLinear] = None
-        self.pool = PagePool(self.n_pages)
-        self.seq_pages: Dict[int, List[int]] = {}
+        from ..serve import host as _host
+        self.pool = _host.PageAllocator(self.n_pages, cfg.page_size)     # C++ allocator: refcounted pages, fork
+        self._aid: Dict[int, int] = {}                                   # sequence slot -> allocator sequence id
+        self.seq_pages: Dict[int, List[int]] = {}                        # host mirror of each slot's block-table row
         self.seq_len_host: Dict[int, int] = {}
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.row_graphs = False                        # forward_rows replays a per-shape CUDA graph when set
@@ -145,14 +131,19 @@ class DenseModel:
     # ------------------------------------------------------------------------------------------------ sessions
     def new_seq(self, seq: int):
         assert 0 <= seq < self.max_seqs and seq not in self.seq_pages
+        self._aid[seq] = self.pool.new_seq()
         self.seq_pages[seq] = []
         self.seq_len_host[seq] = 0
         self.seq_len[seq] = 0
 
     def free_seq(self, seq: int):
-        self.pool.release(self.seq_pages.pop(seq))
+        self.pool.free_seq(self._aid.pop(seq))
+        self.seq_pages.pop(seq)
         self.seq_len_host.pop(seq)
         self.block_table[seq].fill_(-1)
+
+    def free_pages(self) -> int:
+        return self.pool.free_pages
 
     def reserve(self, seq: int, n_tokens: int):
         """Make sure pages exist for the first ``n_tokens`` positions of ``seq`` (rows grow lazily, as in the
@@ -162,20 +153,71 @@ class DenseModel:
         if need > self.pages_per_seq:
             raise RuntimeError("context length exceeds max_ctx")
         if need > len(pages):
-            new = [self.pool.alloc() for _ in range(need - len(pages))]
+            if self.pool.reserve(self._aid[seq], n_tokens) < 0:
+                raise RuntimeError("KV pool exhausted")
+            new = self.pool.pages(self._aid[seq])[len(pages):]
             self.block_table[seq, len(pages):need] = torch.tensor(new, dtype=torch.int32, device=self.dev)
             pages.extend(new)
 
     def truncate(self, seq: int, n_tokens: int):
-        """Roll a sequence back to ``n_tokens`` (rejected speculative rows); pages past the end are released."""
+        """Roll a sequence back to ``n_tokens`` (rejected speculative rows); pages past the end are released.  A forked
+        sequence must not be rolled back below its fork point (its earlier pages are shared)."""
         self.seq_len_host[seq] = n_tokens
         self.seq_len[seq] = n_tokens
         keep = (n_tokens + self.cfg.page_size - 1) // self.cfg.page_size
         pages = self.seq_pages[seq]
         if keep < len(pages):
-            self.pool.release(pages[keep:])
+            self.pool.truncate(self._aid[seq], n_tokens)
             self.block_table[seq, keep:len(pages)] = -1
             del pages[keep:]
+
+    def fork(self, src: int, dst: int):
+        """``dst`` becomes a copy of ``src`` that shares its full KV pages; only a partial last page is copied
+        (reference: fork_row / COW pages, m1_model.cu:1694-1716 and the beam scheduler of bv_engine.cu)."""
+        assert dst not in self.seq_pages and 0 <= dst < self.max_seqs
+        self.pool.set_len(self._aid[src], self.seq_len_host[src])
+        child, cs, cd = self.pool.fork(self._aid[src])
+        if child < 0:
+            raise RuntimeError("KV pool exhausted")
+        if cs >= 0:
+            for kv in self.kv:
+                kv[cd].copy_(kv[cs])
+        self._aid[dst] = child
+        pages = self.pool.pages(child)
+        self.seq_pages[dst] = list(pages)
+        self.block_table[dst].fill_(-1)
+        if pages:
+            self.block_table[dst, :len(pages)] = torch.tensor(pages, dtype=torch.int32, device=self.dev)
+        self.seq_len_host[dst] = self.seq_len_host[src]
+        self.seq_len[dst] = self.seq_len_host[src]
+
+    def park(self, seq: int) -> Dict[str, object]:
+        """Moves a sequence's KV rows to pinned host memory and frees its slot and pages.  :meth:`unpark` brings it
+        back bit for bit, so a preempted or idle conversation resumes without recomputation (reference: park/unpark of
+        conversations, serve.rs:616-760, and the host KV tier of m1_model.cu:1818-1905)."""
+        n = self.seq_len_host[seq]
+        used = (n + self.cfg.page_size - 1) // self.cfg.page_size
+        idx = torch.tensor(self.seq_pages[seq][:used], dtype=torch.long, device=self.dev)
+        shape = (self.cfg.n_layers, used) + tuple(self.kv[0].shape[1:])
+        host_kv = torch.empty(shape, dtype=torch.bfloat16, pin_memory=True)
+        for l, kv in enumerate(self.kv):
+            host_kv[l].copy_(kv.index_select(0, idx), non_blocking=True)
+        torch.cuda.current_stream(self.dev).synchronize()
+        self.free_seq(seq)
+        return {"len": n, "kv": host_kv}
+
+    def unpark(self, seq: int, blob: Dict[str, object]):
+        """Restores a parked sequence into the (free) slot ``seq``."""
+        self.new_seq(seq)
+        n = int(blob["len"])
+        self.reserve(seq, n)
+        used = (n + self.cfg.page_size - 1) // self.cfg.page_size
+        idx = torch.tensor(self.seq_pages[seq][:used], dtype=torch.long, device=self.dev)
+        host_kv = blob["kv"]
+        for l, kv in enumerate(self.kv):
+            kv.index_copy_(0, idx, host_kv[l].to(self.dev, non_blocking=True))
+        self.seq_len_host[seq] = n
+        self.seq_len[seq] = n
 
     # ------------------------------------------------------------------------------------------------ small-m forward
     def _layers_small(self, m: int, n_groups: int):

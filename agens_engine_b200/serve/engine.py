@@ -1,0 +1,405 @@
+"""Continuous-batching engine loop: admits requests against the KV pool, interleaves prefill chunks with batched decode
+(or speculative verify) steps, samples on the device, applies reasoning budget / think guard, and streams tokens to
+whoever submitted the request.
+
+Plays the role of the reference's continuous loop (``crates/agens-cli/src/serve.rs:860-2770``): admission by the
+banker's check (``kv_safe``), shortest-remaining-prefill first with a fairness turn (``pick_prefill``), eviction of the
+cheapest victim when the pool runs dry (``pick_victim``; the victim is re-queued and recomputed), one rule for sampling
+so that speculation does not change tokens.  The loop itself is a thread of this process; the model calls go to the
+GPU through the engine's kernels.
+"""
+from __future__ import annotations
+
+import dataclasses
+import queue
+import threading
+import time
+from typing import Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from ..models.dense import DenseModel, M_GEMV
+from ..ops import basic
+from ..spec import DraftSource, SamplingState, SpecDecoder
+from . import host
+
+WAITING, PREFILL, DECODE, DONE = range(4)
+
+
+@dataclasses.dataclass
+class Request:
+    rid: int
+    prompt: List[int]
+    sampling: dict
+    session: str = ""
+    state: int = WAITING
+    slot: int = -1
+    done_prompt: int = 0                  # prompt tokens already prefilled
+    out: List[int] = dataclasses.field(default_factory=list)
+    t_submit: float = 0.0
+    t_last: float = 0.0
+    chunk_index: int = 0
+    budget: Optional[host.ReasoningBudget] = None
+    guard: Optional[host.ThinkGuard] = None
+    evictions: int = 0
+    parked: Optional[dict] = None         # KV rows in pinned host memory while preempted
+    parked_hist: Optional[List[int]] = None
+
+    @property
+    def max_new(self) -> int:
+        return int(self.sampling.get("max_new_tokens", 256))
+
+    def state_of_sampling(self) -> SamplingState:
+        s = self.sampling
+        t = float(s.get("temperature", 0.0))
+        k = int(s.get("top_k", 0) or 0)
+        if k == 1:
+            t = 0.0
+        return SamplingState(temperature=t, top_k=max(k, 0), top_p=float(s.get("top_p", 1.0)), min_p=float(s.get("min_p", 0.0)),
+                             seed=int(s.get("seed", self.rid * 0x9E3779B97F4A7C15 + 1)) & 0x7FFFFFFFFFFFFFFF)
+
+    def needs_logit_edits(self) -> bool:
+        s = self.sampling
+        return bool(s.get("logit_bias")) or float(s.get("presence_penalty", 0)) != 0 or float(s.get("frequency_penalty", 0)) != 0 \
+            or float(s.get("repetition_penalty", 1)) != 1
+
+
+@dataclasses.dataclass
+class EngineStats:
+    steps: int = 0
+    prefill_chunks: int = 0
+    tokens_out: int = 0
+    tokens_prefilled: int = 0
+    evictions: int = 0
+    rejected: int = 0
+    peak_batch: int = 0
+
+
+class Engine:
+    """``emit(rid, tokens, finished, error)`` is called from the engine thread with every batch of new tokens; it
+    returns True when the receiver is gone (the request is dropped)."""
+
+    def __init__(self, model: DenseModel, emit: Callable[[int, List[int], bool, Optional[str]], bool],
+                 sources_factory: Optional[Callable[[], Sequence[DraftSource]]] = None, max_drafts: int = 0,
+                 max_batch: Optional[int] = None, think_tokens: Optional[tuple] = None, reserve_ahead: int = 16):
+        self.m, self.emit = model, emit
+        self.max_batch = min(max_batch or model.max_seqs, model.max_seqs, M_GEMV)
+        self.max_drafts = max_drafts
+        self.spec = SpecDecoder(model, list(sources_factory()) if sources_factory else [], max_drafts=max_drafts)
+        self.think = think_tokens                      # (start id, end id) for budget / guard
+        self.reserve_ahead = reserve_ahead
+        self.inbox: "queue.Queue[Request]" = queue.Queue()
+        self.waiting: List[Request] = []
+        self.active: Dict[int, Request] = {}           # slot -> request
+        self.free_slots = list(range(model.max_seqs - 1, -1, -1))
+        self.stats = EngineStats()
+        self._stop = threading.Event()
+        self._thread: Optional[threading.Thread] = None
+        self._rid = 0
+        self._lock = threading.Lock()
+
+    # ------------------------------------------------------------------------------------------------ submission
+    def submit(self, prompt: Sequence[int], sampling: Optional[dict] = None, rid: Optional[int] = None, session: str = "") -> int:
+        with self._lock:
+            if rid is None:
+                self._rid += 1
+                rid = self._rid
+        r = Request(rid, list(prompt), dict(sampling or {}), session, t_submit=time.monotonic())
+        self.inbox.put(r)
+        return rid
+
+    def start(self):
+        self._thread = threading.Thread(target=self.run, name="engine", daemon=True)
+        self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=30)
+
+    def run(self):
+        torch.cuda.set_device(self.m.dev)
+        while not self._stop.is_set():
+            if not self.step():
+                try:
+                    self.waiting.append(self.inbox.get(timeout=0.02))
+                except queue.Empty:
+                    pass
+
+    def idle(self) -> bool:
+        return not self.waiting and not self.active and self.inbox.empty()
+
+    def run_until_idle(self, max_steps: int = 1 << 30):
+        n = 0
+        while not self.idle() and n < max_steps:
+            self.step(); n += 1
+
+    # ------------------------------------------------------------------------------------------------ one iteration
+    def step(self) -> bool:
+        """One scheduler iteration; returns False when there was nothing to do."""
+        while True:
+            try:
+                self.waiting.append(self.inbox.get_nowait())
+            except queue.Empty:
+                break
+        self._admit()
+        did = False
+        pre = [r for r in self.active.values() if r.state == PREFILL]
+        if pre:
+            self._prefill_one(pre); did = True
+        dec = [r for r in self.active.values() if r.state == DECODE]
+        if dec:
+            self._decode(dec); did = True
+        return did
+
+    # ---- admission -----------------------------------------------------------------------------------------------
+    def _pages(self, n_tokens: int) -> int:
+        ps = self.m.cfg.page_size
+        return (n_tokens + ps - 1) // ps
+
+    def _demand(self, r: Request) -> tuple:
+        """(pages it may still take, pages it holds) for the banker's check."""
+        total = self._pages(min(len(r.prompt) + r.max_new + self.max_drafts + 1, self.m.max_ctx))
+        if r.slot < 0 and r.parked is not None:          # needs its parked rows back at once
+            return total, 0
+        held = len(self.m.seq_pages.get(r.slot, ())) if r.slot >= 0 else 0
+        return max(total - held, 0), held
+
+    def _admit(self):
+        keep: List[Request] = []
+        for r in self.waiting:
+            if len(r.prompt) + 1 > self.m.max_ctx or not r.prompt:
+                self.stats.rejected += 1
+                self.emit(r.rid, [], True, "prompt does not fit the context window" if r.prompt else "empty prompt")
+                continue
+            if not self.free_slots or len(self.active) >= self.max_batch:
+                keep.append(r); continue
+            items = [self._demand(a) for a in self.active.values()] + [self._demand(r)]
+            if self.active and not host.kv_safe(self.m.free_pages(), items):
+                keep.append(r); continue
+            if not self.active and self._pages(len(r.prompt) + len(r.out) + 1) > self.m.free_pages():
+                self.stats.rejected += 1
+                self.emit(r.rid, [], True, "prompt does not fit the KV pool")
+                continue
+            if r.parked is not None and self._pages(int(r.parked["len"]) + 1 + self.max_drafts) > self.m.free_pages():
+                keep.append(r); continue
+            r.slot = self.free_slots.pop()
+            self.spec.samp[r.slot] = r.state_of_sampling()
+            if r.parked is not None:                     # preempted earlier: bring its KV rows back and go on decoding
+                self.m.unpark(r.slot, r.parked)
+                self.spec.hist[r.slot] = r.parked_hist
+                for s in self.spec.sources:
+                    s.begin(r.slot, r.parked_hist)
+                r.parked = r.parked_hist = None
+                r.state = DECODE
+                self.active[r.slot] = r
+                continue
+            r.state, r.done_prompt, r.chunk_index = PREFILL, 0, 0
+            self.m.new_seq(r.slot)
+            if self.think and r.sampling.get("reasoning_budget") is not None:
+                r.budget = host.ReasoningBudget(int(r.sampling["reasoning_budget"]), float(r.sampling.get("reasoning_soft", 0.0)),
+                                                r.prompt, self.think[0], self.think[1])
+            if self.think and r.sampling.get("think_guard"):
+                g = r.sampling["think_guard"]
+                r.guard = host.ThinkGuard(int(g.get("n", 64)), int(g.get("k", 4)), int(g.get("w", 2048)), r.prompt, self.think[0],
+                                          self.think[1])
+            self.active[r.slot] = r
+            self.stats.peak_batch = max(self.stats.peak_batch, len(self.active))
+        self.waiting = keep
+
+    # ---- eviction ------------------------------------------------------------------------------------------------
+    def _evict_for(self, needy: Request) -> bool:
+        """Preempts the most recently submitted other sequence and re-queues it at the head of the line (a decoding
+        victim's KV rows wait in pinned host memory and come back bit for bit; a prefilling victim starts over).  False
+        if nobody can go."""
+        others = [r for r in self.active.values() if r is not needy]
+        if not others:
+            return False
+        v = max(others, key=lambda r: (r.t_submit, r.rid))      # last admitted goes first: the least work is lost
+        v.parked = self.m.park(v.slot) if v.state == DECODE else None      # bit-exact resume; a prefilling victim restarts
+        v.parked_hist = self.spec.hist.get(v.slot)
+        self._release(v, keep_kv=v.parked is not None)
+        v.state, v.slot = WAITING, -1
+        if v.parked is None:
+            v.done_prompt = 0
+        v.evictions += 1
+        self.stats.evictions += 1
+        self.waiting.insert(0, v)
+        return True
+
+    def _release(self, r: Request, keep_kv: bool = False):
+        if r.state == DECODE:
+            for s in self.spec.sources:
+                s.end(r.slot)
+        self.spec.hist.pop(r.slot, None)
+        self.spec.samp.pop(r.slot, None)
+        if not keep_kv:                                  # park() has already given the slot's pages back
+            self.m.free_seq(r.slot)
+        self.active.pop(r.slot)
+        self.free_slots.append(r.slot)
+
+    def _with_room(self, r: Request, fn):
+        """Runs ``fn`` and, when the KV pool is exhausted, evicts a victim and retries."""
+        while True:
+            try:
+                return fn()
+            except RuntimeError as e:
+                if "KV pool exhausted" not in str(e) or not self._evict_for(r):
+                    raise
+
+    # ---- prefill -------------------------------------------------------------------------------------------------
+    def _prefill_one(self, pre: List[Request]):
+        now = time.monotonic()
+        i = host.pick_prefill([len(r.prompt) - r.done_prompt for r in pre], [now - r.t_submit for r in pre],
+                              self.stats.prefill_chunks)
+        r = pre[i if 0 <= i < len(pre) else 0]
+        n = min(self.m.prefill_chunk, len(r.prompt) - r.done_prompt)
+        chunk = torch.tensor(r.prompt[r.done_prompt:r.done_prompt + n], dtype=torch.int32)
+        final = r.done_prompt + n == len(r.prompt)
+        sampled = self.spec.samp[r.slot].temperature > 0 or r.needs_logit_edits()
+        try:
+            res = self._with_room(r, lambda: self.m.prefill(r.slot, chunk, want_logits=final and sampled))
+        except RuntimeError as e:
+            self._finish(r, error=str(e)); return
+        r.done_prompt += n
+        r.chunk_index += 1
+        self.stats.prefill_chunks += 1
+        self.stats.tokens_prefilled += n
+        if not final:
+            return
+        tok, logits = res
+        if sampled:
+            logits = logits[None, :]
+            self._edit_logits(logits, [r])
+            tok = int(self.spec._sample(logits, [r.slot], [len(r.prompt)])[0])
+        self.spec.hist[r.slot] = list(r.prompt) + [tok]
+        for s in self.spec.sources:
+            s.begin(r.slot, self.spec.hist[r.slot])
+        r.state = DECODE
+        self._deliver(r, [tok])
+
+    # ---- decode --------------------------------------------------------------------------------------------------
+    def _edit_logits(self, logits: torch.Tensor, rows: List[Request]):
+        """Penalties and logit bias, applied in place on the device rows (reference: sampler.rs penalties)."""
+        for i, r in enumerate(rows):
+            if not r.needs_logit_edits():
+                continue
+            s = r.sampling
+            seen = r.prompt + r.out if float(s.get("repetition_penalty", 1)) != 1 else r.out
+            if seen:
+                ids, counts = torch.unique(torch.tensor(seen, device=logits.device), return_counts=True)
+                rep = float(s.get("repetition_penalty", 1))
+                if rep != 1:
+                    v = logits[i, ids]
+                    logits[i, ids] = torch.where(v > 0, v / rep, v * rep)
+                if r.out:
+                    oid, oc = torch.unique(torch.tensor(r.out, device=logits.device), return_counts=True)
+                    logits[i, oid] -= float(s.get("presence_penalty", 0)) + float(s.get("frequency_penalty", 0)) * oc.float()
+            for k, v in (s.get("logit_bias") or {}).items():
+                if 0 <= int(k) < logits.shape[1]:
+                    logits[i, int(k)] += float(v)
+
+    def _decode(self, dec: List[Request]):
+        dec = dec[:self.max_batch]
+        plain = [r for r in dec if r.needs_logit_edits() or r.budget is not None]
+        if plain:
+            self._decode_plain(plain)
+        fast = [r for r in dec if r not in plain and r.state == DECODE]
+        if not fast:
+            return
+        # verify rows of all sequences must fit one launch
+        per = max(1, min(1 + self.max_drafts, M_GEMV // len(fast)))
+        self.spec.max_drafts = per - 1
+        slots = [r.slot for r in fast]
+        try:
+            res = self._with_room(fast[0], lambda: self.spec.step([s for s in slots if s in self.active and self.active[s].state == DECODE]))
+        except RuntimeError as e:
+            for r in fast:
+                self._finish(r, error=str(e))
+            return
+        self.stats.steps += 1
+        for r in fast:
+            if r.slot in res:
+                self._deliver(r, res[r.slot])
+
+    def _decode_plain(self, rows: List[Request]):
+        """One token per sequence with logit edits / forced tokens (no speculation: the edits depend on every token)."""
+        m = self.m
+        ids = [self.spec.hist[r.slot][-1] for r in rows]
+        slots = [r.slot for r in rows]
+        pos = [m.seq_len_host[s] + 1 for s in slots]
+        try:
+            _, logits = self._with_room(rows[0], lambda: m.forward_rows(ids, slots, want_logits=True))
+        except RuntimeError as e:
+            for r in rows:
+                self._finish(r, error=str(e))
+            return
+        self._edit_logits(logits, rows)
+        forced: Dict[int, int] = {}
+        for i, r in enumerate(rows):
+            if r.budget is not None:
+                act = r.budget.act(len(r.out))
+                if act[0] == "force":
+                    forced[i] = act[1]
+                elif act[0] == "bias":
+                    logits[i, act[1]] += act[2]
+        toks = self.spec._sample(logits, slots, pos).cpu().tolist()
+        self.stats.steps += 1
+        for i, r in enumerate(rows):
+            t = forced.get(i, toks[i])
+            self.spec.hist[r.slot].append(t)
+            self._deliver(r, [t])
+
+    # ---- delivery ------------------------------------------------------------------------------------------------
+    def _deliver(self, r: Request, toks: List[int]):
+        """Hands the step's tokens of ``r`` to the receiver, cutting at a stop token or the length limit.  The sequence
+        history already ends with ``toks``."""
+        stops = set(r.sampling.get("stop_token_ids") or ())
+        min_new = int(r.sampling.get("min_new_tokens", 0))
+        out: List[int] = []
+        finished = False
+        for j, t in enumerate(toks):
+            if r.guard is not None:
+                t2 = r.guard.filter(t)
+                if t2 != t:                                  # the guard closed a runaway think block: continue from its token
+                    self._rewrite_tail(r, len(toks), j, t2)
+                    out.append(t2); r.out.append(t2)
+                    break
+            if r.budget is not None:
+                r.budget.accept(len(r.out), t)
+            out.append(t); r.out.append(t)
+            if (t in stops and len(r.out) >= min_new) or len(r.out) >= r.max_new:
+                finished = True
+                break
+        if self.m.seq_len_host.get(r.slot, 0) + 1 >= self.m.max_ctx:
+            finished = True
+        r.t_last = time.monotonic()
+        self.stats.tokens_out += len(out)
+        gone = self.emit(r.rid, out, finished, None)
+        if finished or gone:
+            self._finish(r, silent=True)
+
+    def _rewrite_tail(self, r: Request, n_step: int, keep: int, tok: int):
+        """Of the ``n_step`` tokens this step appended to the history only the first ``keep`` stay, followed by ``tok``;
+        the KV rows of the dropped tokens are rolled back (every kept row was part of the verify block)."""
+        h = self.spec.hist[r.slot]
+        del h[len(h) - n_step + keep:]
+        for s in self.spec.sources:
+            s.rewind(r.slot, len(h))
+        h.append(tok)
+        self.m.truncate(r.slot, len(h) - 1)
+
+    def _finish(self, r: Request, error: Optional[str] = None, silent: bool = False):
+        if not silent:
+            self.emit(r.rid, [], True, error)
+        if r.slot in self.active:
+            self._release(r)
+        r.state = DONE
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def attach_to_server(engine: Engine, server, context_length: Optional[int] = None):
+    """Makes ``engine`` the backend of an OpenAI front end (:class:`agens_engine_b200.serve.server.Server`)."""
+    engine.emit = lambda rid, toks, fin, err: server.push(rid, toks, fin, err)
+    server.use_engine(lambda rid, prompt, sampling, session: engine.submit(prompt, sampling, rid=rid, session=session),
+                      context_length or engine.m.max_ctx)

@@ -38,6 +38,9 @@ class DraftSource:
     def feedback(self, seq: int, n_proposed: int, n_accepted: int):
         pass
 
+    def rewind(self, seq: int, n_hist: int):
+        """Only the first ``n_hist`` tokens of the history this source has seen are still valid."""
+
     def end(self, seq: int):
         pass
 
@@ -68,6 +71,10 @@ class CopyLookupSource(DraftSource):
     def feedback(self, seq, n_proposed, n_accepted):
         if n_proposed:
             self.tables[seq].record(n_accepted)
+
+    def rewind(self, seq, n_hist):
+        if self.fed.get(seq, 0) > n_hist:
+            self.tables[seq].truncate(n_hist); self.fed[seq] = n_hist
 
     def end(self, seq):
         self.tables.pop(seq, None); self.fed.pop(seq, None)
@@ -101,6 +108,10 @@ class ModelSource(DraftSource):
             drafts.append(int(out[0]))
         return drafts
 
+    def rewind(self, seq, n_hist):
+        if self.m.seq_len_host[seq] > n_hist:
+            self.m.truncate(seq, n_hist)
+
     def end(self, seq):
         self.m.free_seq(seq)
 
@@ -113,9 +124,17 @@ class MtpSource(DraftSource):
     def __init__(self, head: MtpHead, depth: int = 2):
         self.h, self.depth = head, depth
         self.pending: Dict[int, tuple] = {}
+        self.first: Dict[int, int] = {}                 # history index of the token paired with MTP entry 0
 
     def begin(self, seq, prompt):
         self.h.new_seq(seq)
+        self.first[seq] = len(prompt)
+
+    def rewind(self, seq, n_hist):
+        keep = max(n_hist - self.first[seq], 0)         # entry e pairs the hidden state with history token first + e
+        if self.h.seq_len_host[seq] > keep:
+            self.h.truncate(seq, keep)
+            self.pending.pop(seq, None)
 
     def absorb(self, seq: int, tokens_after: Sequence[int], hidden: torch.Tensor):
         """``hidden[i]`` is the target's state at a committed position and ``tokens_after[i]`` the token that follows
@@ -140,7 +159,7 @@ class MtpSource(DraftSource):
         return drafts
 
     def end(self, seq):
-        self.h.free_seq(seq); self.pending.pop(seq, None)
+        self.h.free_seq(seq); self.pending.pop(seq, None); self.first.pop(seq, None)
 
 
 @dataclasses.dataclass

@@ -1,0 +1,123 @@
+"""Engine loop on the GPU: continuous batching gives every request the tokens it gets alone (greedy and seeded
+sampling, with and without speculation), stops at stop ids and length limits, survives KV pressure by preempting, and
+serves the OpenAI front end end to end (reference gates: serve-smoke, batch-e2e; crates/agens-cli/src/serve.rs)."""
+import dataclasses
+import json
+import threading
+
+import pytest
+import torch
+
+from agens_engine_b200.models import config as C
+from agens_engine_b200.models import oracle as O
+from agens_engine_b200.models.dense import DenseModel
+from agens_engine_b200.serve.engine import Engine, attach_to_server
+from agens_engine_b200.spec import CopyLookupSource, ModelSource, SamplingState, SpecDecoder
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def tiny():
+    cfg = C.oracle_tiny()
+    return cfg, O.random_weights(cfg, seed=0)
+
+
+class Collector:
+    def __init__(self):
+        self.toks, self.done, self.err = {}, {}, {}
+
+    def __call__(self, rid, toks, finished, error):
+        self.toks.setdefault(rid, []).extend(toks)
+        if finished:
+            self.done[rid] = True
+        if error:
+            self.err[rid] = error
+        return False
+
+
+def _alone(ow, prompt, n_new, sampling=None):
+    m = DenseModel.from_oracle(ow, max_seqs=1, max_ctx=512, prefill_chunk=128)
+    return SpecDecoder(m, [], max_drafts=0).generate(0, prompt, n_new, sampling)
+
+
+def test_engine_batches_match_single_runs(tiny):
+    cfg, ow = tiny
+    torch.manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (5, 300, 47, 130, 9, 64)]
+    want = [_alone(ow, p, 24) for p in prompts]
+    samp = {"temperature": 0.9, "top_k": 50, "top_p": 0.9, "seed": 99, "max_new_tokens": 24}
+    want_s = _alone(ow, prompts[2], 24, SamplingState(0.9, 50, 0.9, 0.0, 99))
+    for spec in (False, True):
+        m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512, prefill_chunk=128)
+        col = Collector()
+        drafter = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512) if spec else None
+        eng = Engine(m, col, sources_factory=(lambda: [CopyLookupSource(), ModelSource(drafter, 3)]) if spec else None,
+                     max_drafts=3 if spec else 0)
+        rids = [eng.submit(p, {"max_new_tokens": 24}) for p in prompts]
+        rs = eng.submit(prompts[2], samp)
+        eng.run_until_idle(10000)
+        assert eng.idle() and not col.err
+        for rid, w in zip(rids, want):
+            assert col.toks[rid] == w, (spec, rid)
+        assert col.toks[rs] == want_s
+        assert eng.stats.peak_batch == 4 and m.free_pages() == m.n_pages
+        if spec:
+            assert eng.spec.stats.accepted > 0
+
+
+def test_engine_stops_limits_and_pressure(tiny):
+    cfg, ow = tiny
+    torch.manual_seed(12)
+    p = torch.randint(0, cfg.vocab, (40,)).tolist()
+    ref = _alone(ow, p, 48)
+    m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=256, n_pages=14, prefill_chunk=128)          # 224 token rows for everybody
+    col = Collector()
+    eng = Engine(m, col)
+    stop_tok = ref[10]
+    first_stop = ref.index(stop_tok)
+    r1 = eng.submit(p, {"max_new_tokens": 48, "stop_token_ids": [stop_tok]})
+    r2 = eng.submit(p, {"max_new_tokens": 48})
+    r3 = eng.submit(p, {"max_new_tokens": 48})
+    r4 = eng.submit(p + p, {"max_new_tokens": 30})
+    r5 = eng.submit(list(range(300)), {"max_new_tokens": 4})                      # longer than the context window
+    eng.run_until_idle(20000)
+    assert eng.idle()
+    assert col.toks[r1] == ref[:first_stop + 1]
+    assert col.toks[r2] == ref and col.toks[r3] == ref
+    assert col.toks[r4] == _alone(ow, p + p, 30)
+    assert r5 in col.err and col.toks[r5] == []
+    assert m.free_pages() == m.n_pages
+
+
+def test_engine_behind_openai_server(tiny, tmp_path):
+    from agens_engine_b200.serve.server import Server
+    from tests.fixtures import tiny_tokenizer_json
+    cfg, ow = tiny
+    tj = str(tmp_path / "tokenizer.json")
+    open(tj, "w").write(tiny_tokenizer_json())
+    srv = Server(tj, model_name="tiny", eos_token_ids=[])
+    m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512)
+    m.cfg = dataclasses.replace(m.cfg, vocab_valid=256)           # ids the test tokenizer knows
+    eng = Engine(m, lambda *a: False)
+    attach_to_server(eng, srv)
+    eng.start()
+    try:
+        body = {"model": "tiny", "prompt": "hello world and the thing", "max_tokens": 12, "temperature": 0}
+        st, text = srv.handle("POST", "/v1/completions", body)
+        assert st == 200, text
+        a = json.loads(text)
+        assert a["usage"]["completion_tokens"] == 12
+        # the same request concurrently with others gives the same text
+        res = {}
+        def call(i):
+            res[i] = srv.handle("POST", "/v1/completions", dict(body, prompt=body["prompt"] if i == 0 else "in the " * (i + 1)))
+        th = [threading.Thread(target=call, args=(i,)) for i in range(4)]
+        [t.start() for t in th]; [t.join(60) for t in th]
+        assert all(res[i][0] == 200 for i in range(4))
+        assert json.loads(res[0][1])["choices"][0]["text"] == a["choices"][0]["text"]
+        st, text = srv.handle("POST", "/v1/chat/completions", {"model": "tiny", "messages": [{"role": "user", "content": "hello"}],
+                                                              "max_tokens": 8, "temperature": 0.7, "seed": 5})
+        assert st == 200 and json.loads(text)["usage"]["completion_tokens"] == 8
+    finally:
+        eng.stop()
