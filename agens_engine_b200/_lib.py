@@ -109,6 +109,7 @@ class WqGemvArgs(C.Structure):
         ("status", C.c_void_p),
         ("debug", C.c_int),
         ("tp", TpPush),
+        ("trace", C.c_void_p),
     ]
 
 

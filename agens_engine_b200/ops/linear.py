@@ -120,6 +120,9 @@ class GemvWorkspace:
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
 
 
+TRACE_BUFFER = None      # measurement aid: int64 CUDA tensor [CTAs * 8 warps * 8] that receives the kernel's phase stamps
+
+
 def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STORE,
          pro: int = PRO_PLAIN, ss_in: Optional[torch.Tensor] = None, ss_parts: int = 0,
          norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6, resid: Optional[torch.Tensor] = None,
@@ -168,6 +171,7 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
     a.scratch, a.counters = ptr(ws.scratch), ptr(ws.counters)
     a.status = ptr(ws.status)
     a.debug = int(os.environ.get("B200E_GEMV_DEBUG", "0"))
+    a.trace = ptr(TRACE_BUFFER)
     if tp is not None:
         a.tp = tp
     with torch.cuda.device(dev):

@@ -12,6 +12,7 @@
 //     token-identical to plain greedy decoding.
 // Prologue options fold RMSNorm into the activation staging; epilogue options fold the residual add (with the
 // next norm's partial sums of squares), SwiGLU, argmax partials, or the tensor-parallel push all-reduce.
+#include <cstdlib>
 #include "wq_gemv.cuh"
 
 namespace b2 {
@@ -200,6 +201,9 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
   const unsigned U = (unsigned)nitems * (unsigned)nb;          // host checks U * V < 2^32
   auto range_lo = [&](int v) -> unsigned { return ((unsigned)v * U) / (unsigned)V; };
 
+  unsigned long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * kGemvWarps + warp) * 8 : nullptr;
+  auto stamp = [&](int i) { if (tr && lane == 0) tr[i] = globaltimer_ns(); };
+  stamp(0);
   if (lane == 0) {
 #pragma unroll
     for (int i = 0; i < NST; ++i) mbar_init(bars_u + i * 8, 1);
@@ -240,8 +244,10 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
     while (prod - cons < (unsigned)NST && issue_one()) { }
   }
   __syncwarp();
+  stamp(1);
   pdl_wait();
-  pdl_launch_dependents();   // the next kernel may start prefetching its weights while this one runs
+  pdl_launch_dependents();
+  stamp(2);   // the next kernel may start prefetching its weights while this one runs
 
   // ---- stage the activation slice of this CTA: fp16(x / c) and the per-group sums ----
   if (a.pro == PRO_NORM) {
@@ -308,8 +314,10 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
     }
   }
   __syncthreads();
+  stamp(3);
 
   bool failed = false;
+  bool first_wait = true;
   for (int vw = wfirst; vw < V && nb > 0 && !failed; vw += wstride) {
    unsigned u = range_lo(vw);
    const unsigned u_end = range_lo(vw + 1);
@@ -335,6 +343,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
         failed = true;
         break;
       }
+      if (first_wait) { stamp(4); first_wait = false; }
       const uint8_t* stg = ring + slot * R::STAGE;
       if (a.debug == 1) {   // measurement aid: stream the weights, skip the arithmetic
         y[0][0][0] += (float)stg[lane];
@@ -412,6 +421,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
     if (failed) break;
 
     // ---- item done: fragment layout -> RPL rows per lane (row = lane + 32 j) ----
+    stamp(5);
     const int item = cur;
     const int n0 = item * ROWS;
     __syncwarp();
@@ -602,6 +612,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
     }
    }
   }
+  stamp(6);
   if (failed) {
     // Give copies still in flight a bounded chance to land before the CTA's shared memory is released.
     const uint64_t t0 = globaltimer_ns();
@@ -631,6 +642,8 @@ static int launch_one(const WqGemvArgs& a, cudaStream_t st) {
   }
   int occ = 0;
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, kGemvThreads, smem) != cudaSuccess || occ < 1) return B2_ERR_LAUNCH;
+  static const int occ_cap = [] { const char* e = getenv("B200E_GEMV_OCC"); return e ? atoi(e) : 0; }();
+  if (occ_cap > 0 && occ > occ_cap) occ = occ_cap;   // fewer resident CTAs leave room for the next kernel's prefetching CTAs
   const int npan = a.n / 32;
   const int nitems = (npan + RB / 2 - 1) / (RB / 2);
   // persistent grid of (CTAs per slice) x ks CTAs: every SM carries the same number of CTAs

@@ -56,6 +56,7 @@ struct WqGemvArgs {
   int* status;           // device status word (B2_ERR_TIMEOUT when a bounded wait ran out)
   int debug;             // 0 normal; 1 = stream weights without arithmetic (bandwidth probe, results meaningless)
   TpPush tp;
+  unsigned long long* trace;   // measurement aid: [CTA][warp][8] globaltimer stamps of the kernel's phases (null: off)
 };
 
 }  // namespace b2
