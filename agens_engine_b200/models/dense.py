@@ -250,7 +250,9 @@ class DenseModel:
         """Sum of a row-parallel partial over the tensor-parallel ranks (prefill path); identity on one GPU."""
         return x
 
-    def _head_small(self, m: int, parts_a: int, want_logits: bool):
+    def _head_small(self, m: int, parts_a: int, want_logits: bool, standalone: bool = False):
+        """lm_head + argmax of the rows in h_a.  ``standalone``: the call does not follow a pass through the small-m
+        layers (prefill tail); vocab-parallel models then must not rely on the layers' slot re-arming."""
         cfg = self.cfg
         L.gemv(self.lm_head, self.h_a[:m], self.ws, pro=PRO_NORM, ss_in=self.ss_a, ss_parts=parts_a, norm_w=self.final_norm,
                eps=cfg.rms_eps, epi=EPI_ARGMAX, amax_val=self.amax_val, amax_idx=self.amax_idx,
@@ -258,13 +260,20 @@ class DenseModel:
         lib = _lib.cuda_lib()
         check(lib.b2_argmax_final(ptr(self.amax_val), ptr(self.amax_idx), self.lm_head.n_panels(), L.SS_LD, m,
                                   ptr(self.out_ids), ptr(self.out_val), current_stream()), "b2_argmax_final")
-        self._combine_argmax(m)
+        self._combine_argmax(m, standalone)
 
     def _lm_valid(self) -> int:
         return self.cfg.vocab_valid or self.cfg.vocab
 
-    def _combine_argmax(self, m: int):
+    def _combine_argmax(self, m: int, standalone: bool = False):
         """Vocab-parallel models merge the per-rank winners here; nothing to do on one GPU."""
+
+    def _full_logits(self, m: int) -> torch.Tensor:
+        """fp32 logits of the last step's first ``m`` rows over the whole vocabulary (vocab-parallel models gather)."""
+        return self.logits[:m].clone()
+
+    def vocab_valid_full(self) -> int:
+        return self.cfg.vocab_valid or self.cfg.vocab
 
     def forward_rows(self, ids: List[int], seqs: List[int], want_logits: bool = False):
         """Eager step over explicit rows: ``ids[i]`` is appended to sequence ``seqs[i]`` (rows of one sequence must be
@@ -291,7 +300,7 @@ class DenseModel:
         for s, n in nxt.items():
             self.seq_len_host[s] = n
             self.seq_len[s] = n
-        return self.out_ids[:m].clone(), (self.logits[:m].clone() if want_logits else None)
+        return self.out_ids[:m].clone(), (self._full_logits(m) if want_logits else None)
 
     def _rows_body(self, m: int, n_groups: int, want_logits: bool):
         basic.embed(self.ids[:m], self.embed, self.ss_a, status=self.status, out=self.h_a[:m])
@@ -370,8 +379,8 @@ class DenseModel:
         hl = (h[-1:].float() + delta[-1:].float()).to(torch.bfloat16)
         self.h_a[:1] = hl
         basic.sumsq(self.h_a[:1], self.ss_a)
-        self._head_small(1, 1, want_logits)
-        return int(self.out_ids[0]), (self.logits[0].clone() if want_logits else None)
+        self._head_small(1, 1, want_logits, standalone=True)
+        return int(self.out_ids[0]), (self._full_logits(1)[0] if want_logits else None)
 
     # ------------------------------------------------------------------------------------------------ decode
     def _decode_body(self, seqs: List[int]):

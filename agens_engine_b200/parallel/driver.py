@@ -1,0 +1,125 @@
+"""Rank 0 drives, the other ranks follow: every state-changing model call made on rank 0 is first announced to the
+followers, which then make the same call, so that the scheduler (one thread on rank 0) can treat a tensor-parallel
+model like a local one.
+
+Reference: the leader/follower command interpreter of ``crates/agens-cli/src/tp.rs:190-298`` (re-exec per GPU, file
+rendezvous).  Here ranks are ``torch.distributed`` processes; commands travel as pickled tuples over a gloo (CPU) group,
+so that no GPU stream ever blocks on the host protocol; the data path stays in the fused kernels.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+_FORWARDED = ("new_seq", "free_seq", "reserve", "truncate", "fork", "forward_rows", "prefill",
+              "decode_setup", "decode_steps")
+
+
+class TpDriver:
+    """Wraps the rank-0 shard of a tensor-parallel model; attribute reads go to the shard, forwarded calls are
+    broadcast first.  ``park``/``unpark`` keep every rank's KV shard on that rank's host (handles are integers)."""
+
+    def __init__(self, model, ctrl_group):
+        object.__setattr__(self, "_m", model)
+        object.__setattr__(self, "_g", ctrl_group)
+        object.__setattr__(self, "_parked", {})
+        object.__setattr__(self, "_next", 0)
+
+    def __getattr__(self, name):
+        attr = getattr(self._m, name)
+        if name in _FORWARDED and callable(attr):
+            def call(*a, **kw):
+                _send(self._g, (name, _plain(a), _plain(kw)))
+                return attr(*a, **kw)
+            return call
+        return attr
+
+    def __setattr__(self, name, value):
+        setattr(self._m, name, value)
+
+    def park(self, seq: int):
+        h = self._next
+        object.__setattr__(self, "_next", h + 1)
+        _send(self._g, ("park", (seq, h), {}))
+        self._parked[h] = self._m.park(seq)
+        return {"len": self._parked[h]["len"], "handle": h}
+
+    def unpark(self, seq: int, blob):
+        _send(self._g, ("unpark", (seq, blob["handle"]), {}))
+        self._m.unpark(seq, self._parked.pop(blob["handle"]))
+
+    def shutdown(self):
+        _send(self._g, ("stop", (), {}))
+
+
+def _plain(x):
+    """Tensors become lists so that commands stay small and device free."""
+    if isinstance(x, torch.Tensor):
+        return ("__tensor__", x.dtype, x.cpu().tolist())
+    if isinstance(x, (list, tuple)):
+        return type(x)(_plain(v) for v in x)
+    if isinstance(x, dict):
+        return {k: _plain(v) for k, v in x.items()}
+    return x
+
+
+def _revive(x):
+    if isinstance(x, tuple) and len(x) == 3 and x[0] == "__tensor__":
+        return torch.tensor(x[2], dtype=x[1])
+    if isinstance(x, (list, tuple)):
+        return type(x)(_revive(v) for v in x)
+    if isinstance(x, dict):
+        return {k: _revive(v) for k, v in x.items()}
+    return x
+
+
+def _send(group, cmd):
+    dist.broadcast_object_list([cmd], src=0, group=group)
+
+
+def follow(model, ctrl_group) -> int:
+    """Follower loop: executes the leader's calls until it says stop.  Returns the number of calls made."""
+    parked = {}
+    n = 0
+    while True:
+        box = [None]
+        dist.broadcast_object_list(box, src=0, group=ctrl_group)
+        name, a, kw = box[0]
+        if name == "stop":
+            return n
+        a, kw = _revive(a), _revive(kw)
+        if name == "park":
+            parked[a[1]] = model.park(a[0])
+        elif name == "unpark":
+            model.unpark(a[0], parked.pop(a[1]))
+        else:
+            getattr(model, name)(*a, **kw)
+        n += 1
+
+
+def control_group():
+    """A gloo group over all ranks for host-side commands (the default group stays NCCL)."""
+    return dist.new_group(backend="gloo")
+
+
+def launch(argv: Sequence[str], world: int, log_dir: str = ".", port: Optional[int] = None) -> List[subprocess.Popen]:
+    """Starts ranks 1 .. world-1 of this program (same argv) and returns their handles; the caller becomes rank 0 by
+    setting the same environment for itself (``rank_env(0, ...)``).  Logs go to ``tp_rank<r>.log``."""
+    port = port or 29400 + os.getpid() % 500
+    procs = []
+    for r in range(1, world):
+        env = dict(os.environ, **rank_env(r, world, port))
+        log = open(os.path.join(log_dir, f"tp_rank{r}.log"), "w")
+        procs.append(subprocess.Popen([sys.executable] + list(argv), env=env, stdout=log, stderr=subprocess.STDOUT))
+    os.environ.update(rank_env(0, world, port))
+    return procs
+
+
+def rank_env(rank: int, world: int, port: int) -> dict:
+    return {"RANK": str(rank), "LOCAL_RANK": str(rank), "WORLD_SIZE": str(world), "MASTER_ADDR": "127.0.0.1",
+            "MASTER_PORT": str(port), "B200E_TP_CHILD": "1" if rank else "0"}

@@ -47,6 +47,9 @@ class TpDenseModel(DenseModel):
         self.n_sites = n_sites
         self.idx_off = torch.full((M_GEMV,), rank * self.vocab_shard, dtype=torch.int32, device=self.dev)
         self.skip_push_site = -1     # test hook: the call site whose push this rank drops
+        from .comm import PushComm
+        self._gather_inbox = SymmetricInbox(rank, world, 8 * self.lm_rows, 3, self.dev)     # logits / winners exchange
+        self._gather = PushComm(self._gather_inbox)
 
     # ------------------------------------------------------------------------------------------------ weights
     @staticmethod
@@ -138,9 +141,22 @@ class TpDenseModel(DenseModel):
         lo = self.rank * self.vocab_shard
         return max(0, min(self.vocab_shard, valid - lo))
 
-    def _combine_argmax(self, m: int):
+    def _combine_argmax(self, m: int, standalone: bool = False):
         lib = _lib.cuda_lib()
         self.out_ids[:m].add_(self.idx_off[:m])
+        if standalone and not self.use_nccl_decode:
+            # The static argmax slot is re-armed by the first row-parallel site of the next small-m pass; a prefill tail
+            # is not followed by one, so it exchanges the winners through the rotating gather inbox instead.
+            n = (2 * m + 3) // 4 * 4
+            x = torch.zeros(n, dtype=torch.float32, device=self.dev)
+            x[:m] = self.out_val[:m]
+            x[m:2 * m] = self.out_ids[:m].float()                    # ids < 2^24: exact in fp32
+            g = self._gather.all_gather(x)
+            vals, ids = g[:, :m], g[:, m:2 * m].to(torch.int32)
+            best = vals.max(dim=0, keepdim=True).values
+            cand = torch.where(vals == best, ids, torch.full_like(ids, 0x7fffffff))
+            self.out_ids[:m].copy_(cand.min(dim=0).values)
+            return
         if self.use_nccl_decode:
             # baseline: library all-gather of the per-rank winners, merged with framework ops
             vals = torch.empty(self.world, m, dtype=torch.float32, device=self.dev)
@@ -155,6 +171,28 @@ class TpDenseModel(DenseModel):
         a = self.inbox.comm_args(site, site - 1, skip_push=(site == self.skip_push_site), clear_n=m * self.cfg.d_model)
         check(lib.b2_comm_argmax_combine(C.byref(a), ptr(self.out_val), ptr(self.out_ids), m, ptr(self.out_ids), 0,
                                          current_stream()), "b2_comm_argmax_combine")
+
+    def _full_logits(self, m: int) -> torch.Tensor:
+        """All-gather of the vocab shards through the push inbox (own kernel, no library collective): every rank ends
+        up with the same [m, vocab] fp32 logits, so that sampling is replicated and needs no further exchange."""
+        outs = []
+        for r0 in range(0, m, 8):
+            r1 = min(m, r0 + 8)
+            g = self._gather.all_gather(self.logits[r0:r1].contiguous().view(-1))          # [world, rows * lm_rows]
+            g = g.view(self.world, r1 - r0, self.lm_rows)[:, :, :self.vocab_shard]
+            outs.append(g.permute(1, 0, 2).reshape(r1 - r0, self.world * self.vocab_shard)[:, :self.full_cfg.vocab])
+        return torch.cat(outs).contiguous()
+
+    def vocab_valid_full(self) -> int:
+        return self.full_cfg.vocab_valid or self.full_cfg.vocab
+
+    def close(self):
+        """Releases the peer mappings (collective: every rank calls it, with nothing in flight)."""
+        self._graphs.clear()
+        if self._gather_inbox is not None:
+            self._gather_inbox.close()
+            self._gather = self._gather_inbox = None
+        self.inbox.close()
 
     def weight_bytes(self) -> int:
         return super().weight_bytes()

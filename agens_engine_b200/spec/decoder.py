@@ -224,7 +224,7 @@ class SpecDecoder:
         return basic.sample_rows(logits, f([x.temperature for x in st]),
                                  torch.tensor([x.top_k for x in st], dtype=torch.int32, device=dev),
                                  f([x.top_p for x in st]), f([x.min_p for x in st]), seed,
-                                 torch.tensor(positions, dtype=torch.int32, device=dev), n_valid=self.t._lm_valid())
+                                 torch.tensor(positions, dtype=torch.int32, device=dev), n_valid=self.t.vocab_valid_full())
 
     def step(self, seqs: Sequence[int], forced_drafts: Optional[Dict[int, List[int]]] = None) -> Dict[int, List[int]]:
         """One verify step for every sequence of ``seqs``; returns the tokens each of them emitted (at least one).

@@ -184,8 +184,7 @@ def main():
         print(json.dumps(out))
     if world > 1:
         torch.cuda.synchronize()
-        model._graphs.clear()
-        model.inbox.close()
+        model.close()
         dist.barrier()
         dist.destroy_process_group()
     return 0

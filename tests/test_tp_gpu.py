@@ -29,3 +29,7 @@ def test_push_collectives_match_nccl_and_time_out_cleanly():
 
 def test_tp2_model_matches_single_gpu():
     _run("model")
+
+
+def test_tp2_engine_leader_follower_and_sampling():
+    _run("engine")

@@ -97,8 +97,45 @@ def main():
         torch.cuda.synchronize()
         print(f"rank {rank}: closing", flush=True)
         m._graphs.clear(); b._graphs.clear()
-        m.inbox.close(); b.inbox.close()
+        m.close(); b.close()
         print(f"rank {rank}: closed", flush=True)
+    elif what == "engine":
+        # rank 0 schedules, the others follow; batched requests equal their solo runs, greedy and sampled
+        from agens_engine_b200.parallel import driver as D
+        from agens_engine_b200.serve.engine import Engine
+        cfg = C.oracle_tiny()
+        ow = O.random_weights(cfg, seed=0)
+        m = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=4, max_ctx=256, prefill_chunk=128)
+        ctrl = D.control_group()
+        if rank == 0:
+            drv = D.TpDriver(m, ctrl)
+            torch.manual_seed(5)
+            prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (20, 150, 33)]
+            samp = {"max_new_tokens": 12, "temperature": 0.8, "top_k": 30, "seed": 17}
+
+            def serve(reqs):
+                got = {}
+                eng = Engine(drv, lambda rid, t, f, e: got.setdefault(rid, []).extend(t) or False)
+                rids = [eng.submit(p, s) for p, s in reqs]
+                eng.run_until_idle(5000)
+                assert eng.idle()
+                return [got[r] for r in rids]
+
+            reqs = [(p, {"max_new_tokens": 12}) for p in prompts] + [(prompts[0], samp)]
+            together = serve(reqs)
+            alone = [serve([r])[0] for r in reqs]
+            assert together == alone, (together, alone)
+            assert all(len(t) == 12 for t in together) and together[3] != together[0]
+            blob = None
+            drv.new_seq(0); drv.prefill(0, torch.tensor(prompts[0], dtype=torch.int32))
+            blob = drv.park(0); drv.unpark(1, blob); drv.free_seq(1)
+            drv.shutdown()
+        else:
+            D.follow(m, ctrl)
+        torch.cuda.synchronize()
+        m.inbox.check_status("tp engine")
+        dist.barrier()
+        m.close()
     dist.barrier()
     dist.destroy_process_group()
     print(f"rank {rank}: {what} ok")
