@@ -128,6 +128,7 @@ class AttnDecodeArgs(C.Structure):
         ("out", C.c_void_p), ("ldo", C.c_long),
         ("n_tok", C.c_int),
         ("status", C.c_void_p),
+        ("split_lo", C.c_int), ("split_hi", C.c_int), ("phase", C.c_int),
     ]
 
 

@@ -46,6 +46,9 @@ class DenseModel:
         self.seq_len_host: Dict[int, int] = {}
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self.row_graphs = False                        # forward_rows replays a per-shape CUDA graph when set
+        self.tier = None                               # HostKvTier once enable_host_tier() was called
+        self._tiered_groups: Dict[int, tuple] = {}     # this step's sequences with pages on the host
+        self.prefill_split = 256                       # KV split size of prefill attention
         self._alloc_buffers()
 
     # ------------------------------------------------------------------------------------------------ weights
@@ -136,7 +139,16 @@ class DenseModel:
         self.seq_len_host[seq] = 0
         self.seq_len[seq] = 0
 
+    def enable_host_tier(self, window_tokens: int, batch_pages: int = 256):
+        """KV pages older than ``window_tokens`` (rounded up to batches of ``batch_pages`` pages) move to pinned host
+        memory; attention streams them back on a side stream.  Eager steps only (graph replays need resident KV)."""
+        from .kv_tier import HostKvTier
+        self.tier = HostKvTier(self, window_tokens, batch_pages)
+        return self.tier
+
     def free_seq(self, seq: int):
+        if self.tier is not None:
+            self.tier.drop(seq)
         self.pool.free_seq(self._aid.pop(seq))
         self.seq_pages.pop(seq)
         self.seq_len_host.pop(seq)
@@ -231,9 +243,13 @@ class DenseModel:
                    out=self.qkv[:m])
             basic.rope_kvstore(self.qkv[:m], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, self.tok_pos,
                                self.tok_seq, self.block_table, self.kv[li], self.q[:m], status=self.status)
-            A.attn_decode(self.q[:m], self.kv[li], self.block_table, self.grp_tok0[:n_groups], self.grp_cnt[:n_groups],
-                          self.tok_pos, self.tok_seq, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.split_keys,
-                          self.max_splits, part_o=self.part_o, part_ml=self.part_ml, status=self.status, out=self.attn[:m])
+            if self._tiered_groups:
+                self.tier.attend(li, self.q[:m], self.grp_tok0[:n_groups], self.grp_cnt[:n_groups], self.tok_pos, self.tok_seq,
+                                 self._tiered_groups, self.split_keys, self.max_splits, self.part_o, self.part_ml, self.attn[:m])
+            else:
+                A.attn_decode(self.q[:m], self.kv[li], self.block_table, self.grp_tok0[:n_groups], self.grp_cnt[:n_groups],
+                              self.tok_pos, self.tok_seq, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.split_keys,
+                              self.max_splits, part_o=self.part_o, part_ml=self.part_ml, status=self.status, out=self.attn[:m])
             parts_b = self._row_parallel(d["o"], self.attn[:m], h_a, h_b, self.ss_b, 2 * li)
             L.gemv(d["gate_up"], h_b, ws, pro=PRO_NORM, ss_in=self.ss_b, ss_parts=parts_b, norm_w=d["ln2"],
                    eps=cfg.rms_eps, epi=EPI_SWIGLU, out=self.act[:m])
@@ -293,13 +309,24 @@ class DenseModel:
         t = lambda x: torch.tensor(x, dtype=torch.int32, device=self.dev)
         self.ids[:m] = t(ids); self.tok_pos[:m] = t(pos); self.tok_seq[:m] = t(seqs)
         self.grp_tok0[:len(g0)] = t(g0); self.grp_cnt[:len(g0)] = t(gc)
-        if self.row_graphs:
+        self._tiered_groups = {}
+        if self.tier is not None:
+            for gi, i in enumerate(g0):
+                s = seqs[i]
+                if self.tier.n_host_pages(s):
+                    first, cnt = self._tiered_groups.get(s, (gi, 0))
+                    self._tiered_groups[s] = (first, cnt + 1)
+        if self.row_graphs and not self._tiered_groups:
             self._rows_graph(m, len(g0), want_logits).replay()
         else:
             self._rows_body(m, len(g0), want_logits)
+        self._tiered_groups = {}
         for s, n in nxt.items():
             self.seq_len_host[s] = n
             self.seq_len[s] = n
+        if self.tier is not None:
+            for s in set(seqs):
+                self.tier.maybe_offload(s)
         return self.out_ids[:m].clone(), (self._full_logits(m) if want_logits else None)
 
     def _rows_body(self, m: int, n_groups: int, want_logits: bool):
@@ -344,6 +371,8 @@ class DenseModel:
             last = self._prefill_chunk(seq, ids[c0:c1], start + c0, final=(c1 == T), want_logits=want_logits)
             self.seq_len_host[seq] = start + c1
             self.seq_len[seq] = start + c1
+            if self.tier is not None:
+                self.tier.maybe_offload(seq)
         return last
 
     def _prefill_chunk(self, seq: int, ids: torch.Tensor, pos0: int, final: bool, want_logits: bool):
@@ -359,6 +388,13 @@ class DenseModel:
         h = basic.embed(ids, self.embed, None, status=self.status)
         q = torch.empty(T, cfg.q_dim, dtype=torch.bfloat16, device=dev)
         delta = None
+        tiered = self.tier is not None and self.tier.n_host_pages(seq) > 0
+        if tiered:
+            pg0, pgc, _, _ = A.prefill_groups(T, pos0, seq, dev)
+            p_splits = (pos0 + T + self.prefill_split - 1) // self.prefill_split
+            p_o = torch.empty(T, cfg.n_heads, p_splits, cfg.head_dim, dtype=torch.float32, device=dev)
+            p_ml = torch.empty(T, cfg.n_heads, p_splits, 2, dtype=torch.float32, device=dev)
+            p_out = torch.empty(T, cfg.q_dim, dtype=torch.bfloat16, device=dev)
         for li, d in enumerate(self.layers):
             if delta is None:
                 x = basic.rmsnorm(h, d["ln1"], cfg.rms_eps)
@@ -367,8 +403,11 @@ class DenseModel:
             qkv = self._linear_big(d["qkv"], x)
             basic.rope_kvstore(qkv, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, pos, seqv, self.block_table,
                                self.kv[li], q, status=self.status)
-            a = A.attn_prefill(q, self.kv[li], self.block_table, seq, pos0, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
-                               status=self.status)
+            if tiered:
+                a = self.tier.attend(li, q, pg0, pgc, pos, seqv, {seq: (0, pg0.numel())}, self.prefill_split, p_splits, p_o, p_ml, p_out)
+            else:
+                a = A.attn_prefill(q, self.kv[li], self.block_table, seq, pos0, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
+                                   status=self.status, split_keys=self.prefill_split)
             o = self._reduce_rows(self._linear_big(d["o"], a))
             x, h = basic.rmsnorm(o, d["ln2"], cfg.rms_eps, resid=h)
             gu = self._linear_big(d["gate_up"], x)

@@ -17,8 +17,11 @@ def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tenso
                 grp_cnt: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor, hq: int, hkv: int, hd: int,
                 split_keys: int, max_splits: int, part_o: Optional[torch.Tensor] = None,
                 part_ml: Optional[torch.Tensor] = None, tree_mask: Optional[torch.Tensor] = None,
-                status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q: bf16 [n_tok, hq*hd] (RoPE applied); kv_pool: bf16 [pages, 2, hkv, 16, hd].  Returns bf16 [n_tok, hq*hd]."""
+                status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                split_range: Optional[tuple] = None, phase: int = 0) -> torch.Tensor:
+    """q: bf16 [n_tok, hq*hd] (RoPE applied); kv_pool: bf16 [pages, 2, hkv, 16, hd].  Returns bf16 [n_tok, hq*hd].
+    ``split_range=(lo, hi)`` restricts the launch to those KV splits and ``phase`` selects the split kernel (1), the
+    merge (2) or both (0): the pieces of a tiered-KV step."""
     lib = _lib.cuda_lib()
     n_tok = q.shape[0]
     dev = q.device
@@ -42,20 +45,27 @@ def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tenso
     a.out, a.ldo = ptr(out), out.stride(0)
     a.n_tok = n_tok
     a.status = ptr(status)
+    a.split_lo, a.split_hi = split_range if split_range else (0, 0)
+    a.phase = phase
     with torch.cuda.device(dev):
         check(lib.b2_attn_decode(C.byref(a), hd, current_stream()), "b2_attn_decode")
     return out
+
+
+def prefill_groups(T: int, pos0: int, seq: int, dev):
+    """Row groups of a prefill chunk for the split-KV kernel: 8 consecutive rows per group."""
+    pos = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=dev)
+    seqv = torch.full((T,), seq, dtype=torch.int32, device=dev)
+    g0 = torch.arange(0, T, 8, dtype=torch.int32, device=dev)
+    gc = torch.clamp(T - g0, max=8).to(torch.int32)
+    return g0, gc, pos, seqv
 
 
 def attn_prefill(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tensor, seq: int, pos0: int, hq: int,
                  hkv: int, hd: int, status: Optional[torch.Tensor] = None, split_keys: int = 256) -> torch.Tensor:
     """Causal attention of a prefill chunk (``q``: bf16 ``[T, hq*hd]`` at positions ``pos0 .. pos0+T-1`` of ``seq``)
     over the paged KV cache, which already holds the chunk's own K/V."""
-    dev = q.device
     T = q.shape[0]
-    pos = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=dev)
-    seqv = torch.full((T,), seq, dtype=torch.int32, device=dev)
-    g0 = torch.arange(0, T, 8, dtype=torch.int32, device=dev)
-    gc = torch.clamp(T - g0, max=8).to(torch.int32)
+    g0, gc, pos, seqv = prefill_groups(T, pos0, seq, q.device)
     max_splits = (pos0 + T + split_keys - 1) // split_keys
     return attn_decode(q, kv_pool, block_table, g0, gc, pos, seqv, hq, hkv, hd, split_keys, max_splits, status=status)

@@ -30,7 +30,7 @@ def lib() -> C.CDLL:
             "b2h_pages_new_seq": ([vp], i), "b2h_pages_reserve": ([vp, i, i], i), "b2h_pages_set_len": ([vp, i, i], None),
             "b2h_pages_len": ([vp, i], i), "b2h_pages_truncate": ([vp, i, i], i), "b2h_pages_fork": ([vp, i, ip, ip], i),
             "b2h_pages_free_seq": ([vp, i], i), "b2h_pages_exclusive": ([vp, i], i), "b2h_pages_refcount": ([vp, i], i),
-            "b2h_pages_list": ([vp, i, ip, i], i),
+            "b2h_pages_list": ([vp, i, ip, i], i), "b2h_pages_evict_page": ([vp, i, i], i),
             "b2h_kv_safe": ([C.c_long, lp, lp, i], i),
             "b2h_pick_victim": ([ip, llp, dp, ip, i, d, i], i),
             "b2h_pick_prefill": ([lp, dp, i, C.c_long, i, i], i),
@@ -155,6 +155,10 @@ class PageAllocator:
 
     def free_seq(self, s: int) -> int:
         return lib().b2h_pages_free_seq(self._h, s)
+
+    def evict_page(self, s: int, index: int) -> int:
+        """The page at ``index`` moved to the host tier: frees its GPU page and marks the position -2."""
+        return lib().b2h_pages_evict_page(self._h, s, index)
 
     def exclusive(self, s: int) -> int:
         return lib().b2h_pages_exclusive(self._h, s)

@@ -30,6 +30,11 @@ struct AttnDecodeArgs {
   bf16* out; long ldo;                // [n_tok][hq*hd]
   int n_tok;
   int* status;
+  // Tiered KV: a launch may cover only the splits [split_lo, split_hi) (0, 0 = all) and leave the merge to a later
+  // launch (phase bit 0: split kernel, bit 1: merge kernel; 0 = both).  Partial results of several launches -- pages
+  // resident on the GPU, page batches staged from pinned host memory -- land in their own split slots and are merged
+  // once, in split order, so the result is bit-identical to an all-resident run.
+  int split_lo, split_hi, phase;
 };
 
 namespace {
@@ -74,7 +79,9 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
   const int gq = a.hq / a.hkv;
   // decode the work item
   long item = (long)blockIdx.x * 4 + warp;
-  const int split = (int)(item % a.max_splits); item /= a.max_splits;
+  const int s_lo = a.split_hi > 0 ? a.split_lo : 0;
+  const int s_n = a.split_hi > 0 ? a.split_hi - a.split_lo : a.max_splits;
+  const int split = s_lo + (int)(item % s_n); item /= s_n;
   const int mt_max = (8 * gq + 15) / 16;             // tiles needed for the largest group (8 tokens)
   const int mtile = (int)(item % mt_max); item /= mt_max;
   const int kvh = (int)(item % a.hkv); item /= a.hkv;
@@ -108,6 +115,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
   uint8_t* wsm = smem + (size_t)warp * kStages * 2 * PAGE_B;
   const uint32_t wsm_u = smem_u32(wsm);
   const int* bt = a.block_table + (size_t)seq * a.bt_ld;
+  if (bt[k_begin / kPage] == -2) return;   // split lives in the host tier: a staged launch fills its slot
 
   auto issue_page = [&](int pi) {
     const int stage = pi % kStages;
@@ -320,7 +328,10 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* args, int hd, cudaStream_t st) {
   if (hd != 128 && hd != 64) return B2_ERR_ARG;
   const int gq = a.hq / a.hkv;
   const int mt_max = (8 * gq + 15) / 16;
-  const long items = (long)a.n_groups * a.hkv * mt_max * a.max_splits;
+  if (a.split_hi > 0 && (a.split_lo < 0 || a.split_hi <= a.split_lo || a.split_hi > a.max_splits)) return B2_ERR_ARG;
+  const int s_n = a.split_hi > 0 ? a.split_hi - a.split_lo : a.max_splits;
+  const long items = (long)a.n_groups * a.hkv * mt_max * s_n;
+  const bool run_split = a.phase == 0 || (a.phase & 1), run_merge = a.phase == 0 || (a.phase & 2);
   const int grid = (int)((items + 3) / 4);
   const size_t smem = (size_t)b2_attn_decode_smem_bytes(hd);
   cudaLaunchConfig_t cfg = {};
@@ -329,9 +340,10 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* args, int hd, cudaStream_t st) {
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  cudaError_t e;
+  cudaError_t e = cudaSuccess;
   static bool attr128 = false, attr64 = false;
-  if (hd == 128) {
+  if (!run_split) {
+  } else if (hd == 128) {
     if (!attr128) { cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr128 = true; }
     e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, a);
   } else {
@@ -339,6 +351,7 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* args, int hd, cudaStream_t st) {
     e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, a);
   }
   if (e != cudaSuccess) return B2_ERR_LAUNCH;
+  if (!run_merge) return B2_OK;
   cfg.gridDim = dim3((a.n_tok * a.hq + 7) / 8); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0;
   if (hd == 128) e = cudaLaunchKernelEx(&cfg, attn_merge_kernel<128>, a);
   else e = cudaLaunchKernelEx(&cfg, attn_merge_kernel<64>, a);

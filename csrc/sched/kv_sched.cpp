@@ -49,11 +49,22 @@ class PageAllocator {
     while ((int)q.pages.size() > keep) { rel += unref(q.pages.back()); q.pages.pop_back(); }
     return rel;
   }
+  // Host tier: the page at `index` of the sequence moved to host memory; its GPU page goes back to the pool and the
+  // position is marked kHostPage.  Returns 1 if a page was freed.
+  static constexpr int kHostPage = -2;
+  int evict_page(int s, int index) {
+    Seq& q = seqs_.at(s);
+    if (index < 0 || index >= (int)q.pages.size() || q.pages[index] < 0) return 0;
+    const int rel = unref(q.pages[index]);
+    q.pages[index] = kHostPage;
+    return rel;
+  }
   // Fork: the child shares all full pages; a partial last page must be copied by the caller into the page returned in
   // *copy_dst (source page in *copy_src), -1 when no copy is needed.  Returns the child id, -1 when no page is free.
   int fork(int s, int* copy_src, int* copy_dst) {
     const Seq& q = seqs_.at(s);
     *copy_src = *copy_dst = -1;
+    for (int p : q.pages) if (p < 0) return -1;          // sequences with pages in the host tier do not fork
     const bool partial = q.len % page_size_ != 0;
     if (partial && free_.empty()) return -1;
     const int id = next_id_++;
@@ -74,17 +85,17 @@ class PageAllocator {
     auto it = seqs_.find(s);
     if (it == seqs_.end()) return 0;
     int rel = 0;
-    for (int p : it->second.pages) rel += unref(p);
+    for (int p : it->second.pages) rel += unref(p);   // unref ignores host-tier markers
     seqs_.erase(it);
     return rel;
   }
   const std::vector<int>& pages(int s) const { return seqs_.at(s).pages; }
   int refcount(int page) const { return ref_[page]; }
   // Pages only this sequence holds (what freeing it would give back).
-  int exclusive_pages(int s) const { int n = 0; for (int p : seqs_.at(s).pages) n += ref_[p] == 1; return n; }
+  int exclusive_pages(int s) const { int n = 0; for (int p : seqs_.at(s).pages) n += p >= 0 && ref_[p] == 1; return n; }
  private:
   struct Seq { std::vector<int> pages; int len = 0; };
-  int unref(int p) { if (--ref_[p] == 0) { free_.push_back(p); return 1; } return 0; }
+  int unref(int p) { if (p < 0) return 0; if (--ref_[p] == 0) { free_.push_back(p); return 1; } return 0; }
   int page_size_;
   std::vector<int> ref_, free_;
   std::unordered_map<int, Seq> seqs_;
@@ -279,6 +290,7 @@ B2H_API int b2h_pages_reserve(void* a, int s, int n_tokens) { return static_cast
 B2H_API void b2h_pages_set_len(void* a, int s, int n) { static_cast<PageAllocator*>(a)->set_len(s, n); }
 B2H_API int b2h_pages_len(void* a, int s) { return static_cast<PageAllocator*>(a)->seq_len(s); }
 B2H_API int b2h_pages_truncate(void* a, int s, int n) { return static_cast<PageAllocator*>(a)->truncate(s, n); }
+B2H_API int b2h_pages_evict_page(void* a, int s, int index) { return static_cast<PageAllocator*>(a)->evict_page(s, index); }
 B2H_API int b2h_pages_fork(void* a, int s, int* src, int* dst) { return static_cast<PageAllocator*>(a)->fork(s, src, dst); }
 B2H_API int b2h_pages_free_seq(void* a, int s) { return static_cast<PageAllocator*>(a)->free_seq(s); }
 B2H_API int b2h_pages_exclusive(void* a, int s) { return static_cast<PageAllocator*>(a)->exclusive_pages(s); }
