@@ -358,21 +358,35 @@ class DenseModel:
         from ..ops import gemm as G
         return G.wq_linear(lin, x, self)
 
-    def prefill(self, seq: int, ids: torch.Tensor, want_logits: bool = False):
-        """Chunked prefill of ``ids`` (1-D int tensor) appended to ``seq``; returns the greedy next token (int)."""
+    def prefill(self, seq: int, ids: torch.Tensor, want_logits: bool = False, image_rows: Optional[torch.Tensor] = None,
+                image_pad_id: Optional[int] = None):
+        """Chunked prefill of ``ids`` (1-D int tensor) appended to ``seq``; returns the greedy next token (int).
+        ``image_rows`` (bf16 [n, d_model], from the vision encoder) replace the embedding rows of the ``image_pad_id``
+        tokens, in order (reference: m1_model.cu:2821-2834)."""
         cfg = self.cfg
         ids = ids.to(device=self.dev, dtype=torch.int32)
         T = ids.numel()
+        self._sub_rows = self._sub_index = None
+        if image_rows is not None:
+            is_img = ids == image_pad_id
+            assert int(is_img.sum()) == image_rows.shape[0], "image rows do not match the placeholders"
+            self._sub_rows = image_rows.to(self.dev, torch.bfloat16).contiguous()
+            self._sub_index = torch.where(is_img, torch.cumsum(is_img.to(torch.int32), 0, dtype=torch.int32) - 1,
+                                          torch.full_like(ids, -1)).contiguous()
+            assert self.prefill_chunk > 8 and all(min(self.prefill_chunk, T - c0) > 8 for c0 in range(0, T, self.prefill_chunk)), \
+                "chunks with image rows go through the large-m path"
         start = self.seq_len_host[seq]
         self.reserve(seq, start + T)
         last = None
         for c0 in range(0, T, self.prefill_chunk):
             c1 = min(T, c0 + self.prefill_chunk)
+            self._sub_slice = (c0, c1)
             last = self._prefill_chunk(seq, ids[c0:c1], start + c0, final=(c1 == T), want_logits=want_logits)
             self.seq_len_host[seq] = start + c1
             self.seq_len[seq] = start + c1
             if self.tier is not None:
                 self.tier.maybe_offload(seq)
+        self._sub_rows = self._sub_index = None
         return last
 
     def _prefill_chunk(self, seq: int, ids: torch.Tensor, pos0: int, final: bool, want_logits: bool):
@@ -385,7 +399,11 @@ class DenseModel:
         from ..ops import gemm as G
         pos = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=dev)
         seqv = torch.full((T,), seq, dtype=torch.int32, device=dev)
-        h = basic.embed(ids, self.embed, None, status=self.status)
+        sub_i = None
+        if getattr(self, "_sub_index", None) is not None:
+            sub_i = self._sub_index[self._sub_slice[0]:self._sub_slice[1]].contiguous()
+        h = basic.embed(ids, self.embed, None, sub_rows=self._sub_rows if sub_i is not None else None, sub_index=sub_i,
+                        status=self.status)
         q = torch.empty(T, cfg.q_dim, dtype=torch.bfloat16, device=dev)
         delta = None
         tiered = self.tier is not None and self.tier.n_host_pages(seq) > 0

@@ -1,0 +1,166 @@
+"""Image input, host side (bindings of ``csrc/server/vision.cpp``): smart_resize, antialiased bicubic resize +
+normalisation + patch layout, placeholder expansion, multi-axis rotary positions, and a few pure-Python decoders for
+the image containers a request may carry."""
+from __future__ import annotations
+
+import base64
+import ctypes as C
+import hashlib
+import struct
+import zlib
+from typing import List, Sequence, Tuple
+
+import numpy as np
+
+from .. import _lib
+
+PATCH = 16
+MERGE = 2
+FACTOR = PATCH * MERGE
+MIN_PIXELS = 64 * 64
+MAX_PIXELS = 4_194_304
+MAX_IMAGES = 16
+_sig = False
+
+
+def _h():
+    global _sig
+    h = _lib.host_lib()
+    if not _sig:
+        i, ll, vp = C.c_int, C.c_longlong, C.c_void_p
+        ip = C.POINTER(C.c_int)
+        h.b2h_smart_resize.argtypes, h.b2h_smart_resize.restype = [i, i, i, ll, ll, ip, ip], i
+        h.b2h_image_preprocess.argtypes, h.b2h_image_preprocess.restype = [vp, i, i, i, i, i, vp, vp], i
+        h.b2h_ppm_header.argtypes, h.b2h_ppm_header.restype = [vp, C.c_long, ip, ip], i
+        h.b2h_expand_placeholders.argtypes, h.b2h_expand_placeholders.restype = [ip, i, i, ip, i, ip, i], i
+        h.b2h_mrope_positions.argtypes, h.b2h_mrope_positions.restype = [ip, i, i, ip, i, ip], i
+        _sig = True
+    return h
+
+
+def smart_resize(h: int, w: int, factor: int = FACTOR, min_pixels: int = MIN_PIXELS, max_pixels: int = MAX_PIXELS) -> Tuple[int, int]:
+    oh, ow = C.c_int(), C.c_int()
+    if _h().b2h_smart_resize(h, w, factor, min_pixels, max_pixels, C.byref(oh), C.byref(ow)) != 0:
+        raise ValueError("absolute aspect ratio must be smaller than 200")
+    return oh.value, ow.value
+
+
+def preprocess(rgb: np.ndarray, size: Tuple[int, int] = None, want_resized: bool = False):
+    """rgb: uint8 [h, w, 3].  Returns (patches fp32 [gh*gw, 1536] in merge-block order, (gh, gw)[, resized fp32 [3, oh, ow]])."""
+    rgb = np.ascontiguousarray(rgb, dtype=np.uint8)
+    h, w, _ = rgb.shape
+    oh, ow = size or smart_resize(h, w)
+    gh, gw = oh // PATCH, ow // PATCH
+    patches = np.empty((gh * gw, 3 * 2 * PATCH * PATCH), dtype=np.float32)
+    resized = np.empty((3, oh, ow), dtype=np.float32) if want_resized else None
+    rc = _h().b2h_image_preprocess(rgb.ctypes.data, h, w, oh, ow, PATCH, resized.ctypes.data if want_resized else None,
+                                   patches.ctypes.data)
+    if rc != 0:
+        raise ValueError("bad image or target size")
+    return (patches, (gh, gw), resized) if want_resized else (patches, (gh, gw))
+
+
+def expand_placeholders(ids: Sequence[int], pad_id: int, counts: Sequence[int]) -> List[int]:
+    cap = len(ids) + sum(counts)
+    out = (C.c_int * cap)()
+    n = _h().b2h_expand_placeholders((C.c_int * len(ids))(*ids), len(ids), pad_id, (C.c_int * max(len(counts), 1))(*counts),
+                                     len(counts), out, cap)
+    if n < 0:
+        raise ValueError("number of image placeholders does not match the number of images")
+    return list(out[:n])
+
+
+def mrope_positions(ids: Sequence[int], pad_id: int, grids: Sequence[Tuple[int, int]]):
+    """Returns (positions int32 [3, n], next running position); ``grids`` are the merged (gh/2, gw/2) sizes."""
+    n = len(ids)
+    pos = np.zeros((3, n), dtype=np.int32)
+    flat = [v for g in grids for v in g]
+    nxt = _h().b2h_mrope_positions((C.c_int * n)(*ids), n, pad_id, (C.c_int * max(len(flat), 1))(*flat), len(grids),
+                                   pos.ctypes.data_as(C.POINTER(C.c_int)))
+    if nxt < 0:
+        raise ValueError("placeholder runs do not match the image grids")
+    return pos, nxt
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+def decode_image(data: bytes) -> np.ndarray:
+    """uint8 [h, w, 3] from a binary PPM or a non-interlaced 8-bit PNG (RGB, RGBA, grey, grey+alpha, palette); alpha is
+    dropped.  JPEG is not decoded here (no decoder in this build): callers get a clear error."""
+    if data[:2] == b"P6":
+        h, w = C.c_int(), C.c_int()
+        buf = (C.c_ubyte * len(data)).from_buffer_copy(data)
+        off = _h().b2h_ppm_header(buf, len(data), C.byref(h), C.byref(w))
+        if off < 0:
+            raise ValueError("bad PPM")
+        return np.frombuffer(data, dtype=np.uint8, count=h.value * w.value * 3, offset=off).reshape(h.value, w.value, 3).copy()
+    if data[:8] == b"\x89PNG\r\n\x1a\n":
+        return _decode_png(data)
+    if data[:2] == b"\xff\xd8":
+        raise ValueError("JPEG input needs a decoder that this build does not carry; send PNG or PPM")
+    raise ValueError("unknown image format")
+
+
+def _decode_png(data: bytes) -> np.ndarray:
+    p, idat, pal = 8, b"", None
+    w = h = depth = ctype = interlace = 0
+    while p < len(data):
+        n, kind = struct.unpack(">I4s", data[p:p + 8])
+        body = data[p + 8:p + 8 + n]
+        if kind == b"IHDR":
+            w, h, depth, ctype, _, _, interlace = struct.unpack(">IIBBBBB", body)
+        elif kind == b"PLTE":
+            pal = np.frombuffer(body, dtype=np.uint8).reshape(-1, 3)
+        elif kind == b"IDAT":
+            idat += body
+        elif kind == b"IEND":
+            break
+        p += 12 + n
+    if depth != 8 or interlace:
+        raise ValueError("only 8-bit non-interlaced PNG is supported")
+    ch = {0: 1, 2: 3, 3: 1, 4: 2, 6: 4}[ctype]
+    raw = zlib.decompress(idat)
+    stride = w * ch
+    out = np.zeros((h, stride), dtype=np.uint8)
+    prev = np.zeros(stride, dtype=np.int32)
+    for y in range(h):
+        f = raw[y * (stride + 1)]
+        line = np.frombuffer(raw, dtype=np.uint8, count=stride, offset=y * (stride + 1) + 1).astype(np.int32)
+        cur = np.zeros(stride, dtype=np.int32)
+        if f == 0:
+            cur = line
+        elif f == 2:
+            cur = (line + prev) & 255
+        else:
+            for x in range(stride):
+                a = cur[x - ch] if x >= ch else 0
+                b = prev[x]
+                c = prev[x - ch] if x >= ch else 0
+                if f == 1:
+                    pr = a
+                elif f == 3:
+                    pr = (a + b) >> 1
+                else:
+                    pa, pb, pc = abs(b - c), abs(a - c), abs(a + b - 2 * c)
+                    pr = a if pa <= pb and pa <= pc else (b if pb <= pc else c)
+                cur[x] = (line[x] + pr) & 255
+        out[y] = cur
+        prev = cur
+    img = out.reshape(h, w, ch)
+    if ctype == 3:
+        return pal[img[:, :, 0]]
+    if ch == 1 or ch == 2:
+        return np.repeat(img[:, :, :1], 3, axis=2)
+    return img[:, :, :3].copy()
+
+
+def load_url(url: str) -> bytes:
+    """Only ``data:`` URLs are accepted (the server has no outbound network)."""
+    if not url.startswith("data:"):
+        raise ValueError("only data: URLs are supported for images")
+    head, _, payload = url.partition(",")
+    return base64.b64decode(payload) if head.endswith(";base64") else payload.encode()
+
+
+def image_key(data: bytes) -> int:
+    """Prefix-cache salt of an image: the first 8 bytes of its SHA-256."""
+    return int.from_bytes(hashlib.sha256(data).digest()[:8], "little")

@@ -1,0 +1,92 @@
+"""Host image pipeline against torch's antialiased bicubic and hand-worked cases (reference: vision.rs tests :223 and
+the preprocess contract of kernels/oracle/bridge/vision.cpp:234-256)."""
+import base64
+import struct
+import zlib
+
+import numpy as np
+import pytest
+import torch
+import torch.nn.functional as F
+
+from agens_engine_b200.serve import vision as V
+
+
+def test_smart_resize_rules():
+    assert V.smart_resize(480, 640) == (480, 640)
+    assert V.smart_resize(100, 100) == (96, 96)
+    assert V.smart_resize(50, 50) == (64, 64)                 # 48 x 48 would fall below min_pixels: scaled up
+    assert V.smart_resize(16, 16) == (64, 64)
+    h, w = V.smart_resize(4000, 6000)
+    assert h % 32 == 0 and w % 32 == 0 and h * w <= V.MAX_PIXELS and abs(h / w - 4000 / 6000) < 0.02
+    assert V.smart_resize(48, 80) == (64, 64)                 # 1.5 -> 2 and 2.5 -> 2: halves round to even
+    with pytest.raises(ValueError):
+        V.smart_resize(10, 4000)
+
+
+@pytest.mark.parametrize("hw,size", [((97, 131), (64, 96)), ((40, 52), (96, 128)), ((300, 200), (160, 96)), ((64, 64), (64, 64))])
+def test_bicubic_aa_matches_torch_and_patch_layout(hw, size):
+    rng = np.random.default_rng(0)
+    img = rng.integers(0, 256, size=(hw[0], hw[1], 3), dtype=np.uint8)
+    patches, (gh, gw), resized = V.preprocess(img, size, want_resized=True)
+    ref = F.interpolate(torch.from_numpy(img).permute(2, 0, 1)[None].float(), size=size, mode="bicubic", antialias=True,
+                        align_corners=False)[0].numpy()
+    assert np.abs(resized - ref).max() < 2e-3
+    q = (np.rint(np.clip(resized, 0, 255)) - 127.5) / 127.5
+    P = V.PATCH
+    assert patches.shape == (gh * gw, 1536)
+    # row order (gh/2, gw/2, 2, 2); columns (channel, time, py, px) with the frame duplicated in time
+    row = 0
+    for by in range(gh // 2):
+        for bx in range(gw // 2):
+            for iy in range(2):
+                for ix in range(2):
+                    gy, gx = by * 2 + iy, bx * 2 + ix
+                    blk = q[:, gy * P:(gy + 1) * P, gx * P:(gx + 1) * P]
+                    exp = np.stack([blk, blk], 1).reshape(-1)
+                    assert np.array_equal(patches[row], exp.astype(np.float32)), row
+                    row += 1
+
+
+def test_placeholders_positions_and_decoders():
+    PAD = 900
+    ids = [1, 2, PAD, 3, PAD, 4]
+    out = V.expand_placeholders(ids, PAD, [6, 2])
+    assert out == [1, 2] + [PAD] * 6 + [3] + [PAD] * 2 + [4]
+    with pytest.raises(ValueError):
+        V.expand_placeholders(ids, PAD, [6])
+    pos, nxt = V.mrope_positions(out, PAD, [(2, 3), (1, 2)])
+    assert pos[:, :2].tolist() == [[0, 1]] * 3
+    assert pos[0, 2:8].tolist() == [2] * 6 and pos[1, 2:8].tolist() == [2, 2, 2, 3, 3, 3] and pos[2, 2:8].tolist() == [2, 3, 4, 2, 3, 4]
+    assert pos[:, 8].tolist() == [5, 5, 5]                     # text resumes at 2 + max(2, 3)
+    assert pos[0, 9:11].tolist() == [6, 6] and pos[2, 9:11].tolist() == [6, 7]
+    assert pos[:, 11].tolist() == [8, 8, 8] and nxt == 9
+    rng = np.random.default_rng(1)
+    img = rng.integers(0, 256, size=(5, 7, 3), dtype=np.uint8)
+    ppm = b"P6\n# comment\n7 5\n255\n" + img.tobytes()
+    assert np.array_equal(V.decode_image(ppm), img)
+    # PNG with every filter type
+    raw = b""
+    prev = np.zeros(21, dtype=np.int32)
+    for y in range(5):
+        line = img[y].reshape(-1).astype(np.int32)
+        f = y % 5
+        enc = np.zeros(21, dtype=np.int32)
+        for x in range(21):
+            a = line[x - 3] if x >= 3 else 0
+            b, c = prev[x], (prev[x - 3] if x >= 3 else 0)
+            pa, pb, pc = abs(b - c), abs(a - c), abs(a + b - 2 * c)
+            pr = [0, a, b, (a + b) >> 1, a if pa <= pb and pa <= pc else (b if pb <= pc else c)][f]
+            enc[x] = (line[x] - pr) & 255
+        raw += bytes([f]) + enc.astype(np.uint8).tobytes()
+        prev = line
+
+    def chunk(kind, body):
+        return struct.pack(">I", len(body)) + kind + body + struct.pack(">I", zlib.crc32(kind + body))
+
+    png = b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", 7, 5, 8, 2, 0, 0, 0)) + chunk(b"IDAT", zlib.compress(raw)) + chunk(b"IEND", b"")
+    assert np.array_equal(V.decode_image(png), img)
+    url = "data:image/png;base64," + base64.b64encode(png).decode()
+    assert V.load_url(url) == png and V.image_key(png) == V.image_key(png)
+    with pytest.raises(ValueError):
+        V.decode_image(b"\xff\xd8\xff\xe0")
