@@ -132,6 +132,22 @@ class AttnDecodeArgs(C.Structure):
     ]
 
 
+class WqMmArgs(C.Structure):
+    _fields_ = [
+        ("wq", C.c_void_p), ("n", C.c_int), ("k", C.c_int), ("m", C.c_int),
+        ("bits", C.c_int), ("group", C.c_int),
+        ("ks", C.c_int), ("n_pad", C.c_int), ("stages", C.c_int),
+        ("epi", C.c_int),
+        ("y", C.c_void_p), ("ldy", C.c_long),
+        ("resid", C.c_void_p), ("ldr", C.c_long),
+        ("ss_out", C.c_void_p), ("ss_ld", C.c_int),
+        ("yf", C.c_void_p),
+        ("amax_val", C.c_void_p), ("amax_idx", C.c_void_p), ("n_valid", C.c_int),
+        ("scratch", C.c_void_p), ("counters", C.c_void_p),
+        ("status", C.c_void_p),
+    ]
+
+
 class SampleArgs(C.Structure):
     _fields_ = [
         ("logits", C.c_void_p), ("ld", C.c_long), ("vocab", C.c_int),
@@ -177,6 +193,8 @@ def _declare(lib: C.CDLL):
         "b2_comm_reduce_scatter": ([C.POINTER(CommArgs), vp, l, vp, vp], i),
         "b2_comm_barrier": ([C.POINTER(CommArgs), vp], i),
         "b2_comm_argmax_combine": ([C.POINTER(CommArgs), vp, vp, i, vp, vp, vp], i),
+        "b2_wq_mm": ([C.POINTER(WqMmArgs), vp, l, vp, i, i, vp, f, vp, vp], i),
+        "b2_wq_mm_ks": ([i, i], i), "b2_wq_mm_npad": ([i], i), "b2_wq_mm_scratch_floats": ([i, i, i], l),
         "b2_sample_rows": ([C.POINTER(SampleArgs), i, vp], i),
         "b2_spec_accept": ([vp, vp, vp, vp, i, vp, vp, i, vp], i),
         "b2_gemm_bf16": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp, vp], i),

@@ -34,6 +34,7 @@ def choose_ks(n: int, k: int, slice_k: int = 2560) -> int:
     """Number of k slices of a linear: a function of the shape only (never of the token count), so per-row
     arithmetic stays batch invariant.  Slices of about ``slice_k`` inputs keep the staged activations small and give
     the persistent GEMV thousands of (panel, slice) work items to balance over the SMs."""
+    slice_k = int(os.environ.get("B200E_SLICE_K", slice_k))
     nu = k // 128
     want = max(1, round(k / slice_k))
     best = 1
@@ -112,14 +113,26 @@ class WqLinear:
 
 
 class GemvWorkspace:
-    """Split-k scratch, self-resetting item counters and the status word shared by the GEMV launches of one stream."""
+    """Split-k scratch, self-resetting item counters and the status word shared by the GEMV / GEMM launches of one
+    stream, plus the fp16 activation staging buffer of the tensor-core path (grown on first use)."""
 
     def __init__(self, device, floats: int = 4 << 20, panels: int = 1 << 16):
         self.scratch = torch.empty(floats, dtype=torch.float32, device=device)
         self.counters = torch.zeros(panels, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self.x16 = None
+
+    def x16_buffer(self, n_pad: int, k: int) -> torch.Tensor:
+        if self.x16 is None or self.x16.numel() < n_pad * k:
+            self.x16 = torch.empty(max(n_pad * k, 32 * 25600), dtype=torch.float16, device=self.scratch.device)
+        return self.x16
+
+    def ensure_scratch(self, floats: int):
+        if floats > self.scratch.numel():
+            self.scratch = torch.empty(floats, dtype=torch.float32, device=self.scratch.device)
 
 
+MM_MIN_ROWS = int(os.environ.get("B200E_MM_MIN_ROWS", "9"))     # token rows from which the tcgen05 GEMM takes over
 TRACE_BUFFER = None      # measurement aid: int64 CUDA tensor [CTAs * 8 warps * 8] that receives the kernel's phase stamps
 
 
@@ -129,9 +142,13 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
          out: Optional[torch.Tensor] = None, ss_out: Optional[torch.Tensor] = None,
          amax_val: Optional[torch.Tensor] = None, amax_idx: Optional[torch.Tensor] = None, n_valid: Optional[int] = None,
          yf: Optional[torch.Tensor] = None, tp: Optional[_lib.TpPush] = None):
-    """Launch one GEMV on the current stream.  ``x``: bf16 ``[m, k]`` (``h`` when ``pro == PRO_NORM``)."""
+    """Launch one GEMV on the current stream.  ``x``: bf16 ``[m, k]`` (``h`` when ``pro == PRO_NORM``).  More than
+    ``MM_MIN_ROWS - 1`` rows go to the tensor-core GEMM (:func:`mm`), which takes the same arguments."""
     lib = _lib.cuda_lib()
     m = x.shape[0]
+    if m >= MM_MIN_ROWS and tp is None:
+        return mm(lin, x, ws, epi=epi, pro=pro, ss_in=ss_in, ss_parts=ss_parts, norm_w=norm_w, eps=eps, resid=resid, out=out,
+                  ss_out=ss_out, amax_val=amax_val, amax_idx=amax_idx, n_valid=n_valid, yf=yf)
     assert x.dtype == torch.bfloat16 and x.shape[1] == lin.k and x.stride(1) == 1
     dev = x.device
     a = WqGemvArgs()
@@ -176,4 +193,51 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
         a.tp = tp
     with torch.cuda.device(dev):
         check(lib.b2_wq_gemv(C.byref(a), current_stream()), "b2_wq_gemv")
+    return out
+
+
+def mm(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STORE, pro: int = PRO_PLAIN,
+       ss_in: Optional[torch.Tensor] = None, ss_parts: int = 0, norm_w: Optional[torch.Tensor] = None, eps: float = 1e-6,
+       resid: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, ss_out: Optional[torch.Tensor] = None,
+       amax_val: Optional[torch.Tensor] = None, amax_idx: Optional[torch.Tensor] = None, n_valid: Optional[int] = None,
+       yf: Optional[torch.Tensor] = None):
+    """Same contract as :func:`gemv` for 1 .. 256 rows on the tcgen05 tensor cores (``csrc/kernels/sm100/wq_mm.cu``):
+    the weights are dequantised to fp16 tiles inside the kernel, the activations are staged as fp16 by a small prologue
+    kernel that also applies the RMSNorm of ``pro == PRO_NORM``."""
+    lib = _lib.cuda_lib()
+    m = x.shape[0]
+    assert x.dtype == torch.bfloat16 and x.shape[1] == lin.k and x.stride(1) == 1 and 1 <= m <= 256
+    dev = x.device
+    a = _lib.WqMmArgs()
+    a.wq, a.n, a.k, a.m, a.bits, a.group = ptr(lin.wq), lin.n, lin.k, m, lin.bits, lin.group
+    a.epi = epi
+    if epi in (EPI_STORE, EPI_RESID):
+        out = torch.empty(m, lin.n, dtype=torch.bfloat16, device=dev) if out is None else out
+        a.y, a.ldy = ptr(out), out.stride(0)
+    elif epi == EPI_SWIGLU:
+        out = torch.empty(m, lin.n // 2, dtype=torch.bfloat16, device=dev) if out is None else out
+        a.y, a.ldy = ptr(out), out.stride(0)
+    elif epi == EPI_F32:
+        out = torch.empty(m, lin.n, dtype=torch.float32, device=dev) if out is None else out
+        a.yf, a.ldy = ptr(out), out.stride(0)
+    elif epi == EPI_ARGMAX:
+        a.amax_val, a.amax_idx = ptr(amax_val), ptr(amax_idx)
+        a.n_valid = lin.n if n_valid is None else n_valid
+        if yf is not None:
+            a.yf, a.ldy = ptr(yf), yf.stride(0)
+    else:
+        raise ValueError("epilogue not available on the tensor-core path")
+    if resid is not None:
+        a.resid, a.ldr = ptr(resid), resid.stride(0)
+    a.ss_out, a.ss_ld = ptr(ss_out), SS_LD
+    n_pad = lib.b2_wq_mm_npad(m)
+    ws.ensure_scratch(lib.b2_wq_mm_scratch_floats(lin.n, lin.k, n_pad))
+    if (lin.n + 127) // 128 > ws.counters.numel():
+        raise RuntimeError("workspace has too few counters")
+    a.scratch, a.counters, a.status = ptr(ws.scratch), ptr(ws.counters), ptr(ws.status)
+    x16 = ws.x16_buffer(n_pad, lin.k)
+    norm = pro == PRO_NORM
+    with torch.cuda.device(dev):
+        check(lib.b2_wq_mm(C.byref(a), ptr(x), x.stride(0), ptr(ss_in) if norm else 0, ss_parts if norm else 0, SS_LD,
+                           ptr(norm_w) if norm else 0, eps, ptr(x16), current_stream()), "b2_wq_mm")
     return out
