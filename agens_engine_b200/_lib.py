@@ -145,6 +145,7 @@ class WqMmArgs(C.Structure):
         ("amax_val", C.c_void_p), ("amax_idx", C.c_void_p), ("n_valid", C.c_int),
         ("scratch", C.c_void_p), ("counters", C.c_void_p),
         ("status", C.c_void_p),
+        ("dbg", C.c_int),
     ]
 
 

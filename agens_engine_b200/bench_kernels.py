@@ -154,9 +154,86 @@ def bench_gemm(args):
     print(json.dumps({"peaks": pk, "timing": "CUDA events, median of 10, L2 flushed between launches"}))
 
 
+def trace_gemv(args):
+    """Phase stamps of the GEMV on the 32B shapes (m rows), captured inside a CUDA graph of back-to-back launches over
+    rotating weight copies: where the time of one launch goes (start skew, prefetch issue, dependency wait, activation
+    staging, first weights, k loop of the first item, hand-off + epilogue)."""
+    import numpy as np
+    dev = "cuda:0"
+    ws = L.GemvWorkspace(dev, floats=16 << 20)
+    tr = torch.zeros(600 * 8 * 8, dtype=torch.int64, device=dev)
+    L.TRACE_BUFFER = tr
+    shapes = [(10240, 5120), (5120, 8192), (51200, 5120), (5120, 25600)]
+    for n, k in shapes[:1] if args.small else shapes:
+        lin = L.WqLinear.random(n, k, args.bits, 128, dev, seed=1)
+        ncopy = max(4, min(16, (512 << 20) // lin.nbytes() + 1))
+        lins = [L.WqLinear(n, k, args.bits, 128, lin.wq.clone(), lin.ks, lin.rb) for _ in range(ncopy)]
+        x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
+        out = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+
+        def launch_all():
+            for ln in lins:
+                L.gemv(ln, x, ws, out=out)
+
+        med, _ = graph_time_us(launch_all, len(lins))
+        t = tr.cpu().numpy().reshape(-1, 8)
+        t = t[t[:, 0] > 0]
+        base = t[:, 0].min()
+        q = lambda a: [round(float(np.percentile(a, p)) / 1e3, 2) for p in (0, 50, 100)]
+        print(json.dumps(dict(n=n, k=k, bits=args.bits, m=args.m, ks=lin.ks, rb=lin.rb, us_per_launch=round(med, 2), warps=len(t),
+                              start_skew=q(t[:, 0] - base), prefetch_issue=q(t[:, 1] - t[:, 0]), dependency_wait=q(t[:, 2] - t[:, 1]),
+                              activation_staging=q(t[:, 3] - t[:, 2]), first_weights=q(t[:, 4] - t[:, 3]),
+                              k_loop_first_item=q(t[:, 5] - t[:, 3]), handoff_epilogue=q(t[:, 6] - t[:, 5]),
+                              end=q(t[:, 6] - base), unit="us [min, median, max] over warps of the last launch")), flush=True)
+    L.TRACE_BUFFER = None
+
+
+def bench_mm(args):
+    """Mixed-bit tcgen05 GEMM (in-kernel dequantisation) on the 32B shapes for m rows, CUDA-graph timing over rotating
+    weight copies larger than L2."""
+    dev = "cuda:0"
+    pk = peaks()
+    ws = L.GemvWorkspace(dev, floats=16 << 20)
+    lib = _lib.cuda_lib()
+    shapes = [("qkv", 10240, 5120), ("o", 5120, 8192), ("gate_up", 51200, 5120), ("down", 5120, 25600), ("lm_head", 151936, 5120)]
+    for name, n, k in shapes[2:3] if args.small else shapes:
+        for bits in ([4] if name == "lm_head" else [2, 3, 4]):
+            lin = L.WqLinear.random(n, k, bits, 128, dev, seed=1)
+            nb = lin.nbytes()
+            ncopy = max(3, min(12, (512 << 20) // nb + 1))
+            lins = [lin] + [L.WqLinear(n, k, bits, 128, lin.wq.clone(), lin.ks, lin.rb) for _ in range(ncopy - 1)]
+            x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
+            out = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+
+            def launch_all():
+                for ln in lins:
+                    L.mm(ln, x, ws, out=out)
+
+            med, best = graph_time_us(launch_all, len(lins))
+            print(json.dumps(dict(name=name, n=n, k=k, bits=bits, m=args.m, ks=lib.b2_wq_mm_ks(n, k), us=round(med, 1),
+                                  gbs=round(nb / med / 1e3, 0), frac_hbm=round(nb / med / 1e3 / pk["hbm_gbs"], 3),
+                                  tflops=round(2.0 * args.m * n * k / med / 1e6, 1))), flush=True)
+    print(json.dumps({"peaks": pk, "timing": "CUDA graph of back-to-back launches (activation prologue + GEMM) over rotating weight "
+                      "copies (> 512 MiB); median per launch"}))
+
+
+def profile_mm(args):
+    """Three plain launches of the gate/up shape for a profiler capture of a small case."""
+    dev = "cuda:0"
+    ws = L.GemvWorkspace(dev, floats=16 << 20)
+    n, k = 51200, 5120
+    lins = [L.WqLinear.random(n, k, args.bits, 128, dev, seed=i) for i in range(3)]
+    x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
+    out = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+    for ln in lins:
+        L.mm(ln, x, ws, out=out)
+    torch.cuda.synchronize()
+    print("profile_mm done", int(ws.status.item()))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv"])
+    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--ks", type=int, default=0)
     ap.add_argument("--m", type=int, default=1)
@@ -168,6 +245,12 @@ def main(argv=None):
         profile_gemv(args)
     elif args.what == "gemm":
         bench_gemm(args)
+    elif args.what == "trace_gemv":
+        trace_gemv(args)
+    elif args.what == "mm":
+        bench_mm(args)
+    elif args.what == "profile_mm":
+        profile_mm(args)
     else:
         raise SystemExit(f"{args.what}: not available yet")
 

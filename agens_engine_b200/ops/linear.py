@@ -236,6 +236,7 @@ def mm(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STOR
         raise RuntimeError("workspace has too few counters")
     a.scratch, a.counters, a.status = ptr(ws.scratch), ptr(ws.counters), ptr(ws.status)
     x16 = ws.x16_buffer(n_pad, lin.k)
+    a.dbg = int(os.environ.get("B200E_MM_DBG", "0"))
     norm = pro == PRO_NORM
     with torch.cuda.device(dev):
         check(lib.b2_wq_mm(C.byref(a), ptr(x), x.stride(0), ptr(ss_in) if norm else 0, ss_parts if norm else 0, SS_LD,

@@ -5,7 +5,7 @@
 // rows x all tokens x 16 k and the cost of a step hardly depends on the token count.  Per CTA (row tile, k slice):
 //   warp 0      TMA: the fp16 activation tile [tokens][64 k] of every stage (128-byte swizzle, this CTA's own copy)
 //   warp 1      one elected thread issues tcgen05.mma (kind f16, fp32 accumulator in TMEM) and commits stage releases
-//   warps 2..9  dequantisers: each owns a 16-row block; it reads the lane's FM words straight from global memory
+//   warps 2..17 dequantisers (two sets of eight alternating over the stages): each owns a 16-row block; it reads the lane's FM words straight from global memory
 //               (prefetched one stage ahead), turns codes into fp16 weights scale * (code - zero) with two HFMA2 per
 //               pair, and writes them into the stage's A tile in the same swizzled K-major layout TMA would produce
 //   warps 2..5  afterwards read the accumulator with tcgen05.ld and run the epilogue (same variants as the GEMV:
@@ -34,14 +34,16 @@ struct WqMmArgs {
   float* amax_val; int* amax_idx; int n_valid;
   float* scratch; unsigned* counters;
   int* status;
+  int dbg;                    // measurement aid (results meaningless): 1 no weight loads, 2 no proxy fence, 4 no dequant stores, 8 no MMA
 };
 
 namespace {
 
 enum { EPI_STORE = 0, EPI_RESID = 1, EPI_SWIGLU = 2, EPI_F32 = 3, EPI_ARGMAX = 4 };
-constexpr int BM = 128, BKS = 64;
-constexpr int A_STAGE = BM * BKS * 2;            // 16 KB of fp16 weights per stage
-constexpr int kMmThreads = 320;                  // 10 warps
+constexpr int BM = 128, BKS = 64;                // BKS: width of one 128-byte swizzle atom in fp16 elements
+constexpr int A_SUB = BM * BKS * 2;              // 16 KB: 128 rows x 64 k
+constexpr int A_STAGE = 2 * A_SUB;               // a stage covers one 128-k batch: two sub-tiles per operand
+constexpr int kMmThreads = 576;                  // 18 warps: TMA, MMA, 2 x 8 dequantisers
 constexpr int kDequantWarps = 8;
 constexpr uint32_t kMagicH = 0x64006400u;        // two fp16 1024.0
 
@@ -54,18 +56,21 @@ __device__ __forceinline__ void mbar_expect_tx_m(uint32_t bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive_m(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase flips or the hint runs out, so a
+// waiting warp issues few instructions (the tensor-core pipeline shares its issue slots with sixteen busy warps).
 __device__ __forceinline__ bool mbar_try_wait_m(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(1000000u) : "memory");
   return ok != 0;
 }
 __device__ __forceinline__ bool mbar_wait_m(uint32_t bar, uint32_t parity) {      // bounded: about two seconds
   if (mbar_try_wait_m(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
+  unsigned it = 0;
   while (!mbar_try_wait_m(bar, parity)) {
-    if (globaltimer_ns() - t0 > 2000000000ull) return false;
+    if ((++it & 15u) == 0u && globaltimer_ns() - t0 > 2000000000ull) return false;
   }
   return true;
 }
@@ -123,7 +128,7 @@ template <> struct FmtM<4> { static constexpr int CK = 64, REC = 512; };
 template <> struct FmtM<2> { static constexpr int CK = 128, REC = 512; };
 template <> struct FmtM<3> { static constexpr int CK = 128, REC = 768; };
 
-struct RawW { uint4 lo; uint2 hi; uint32_t sz0, sz1; };
+struct RawW { uint4 lo0, lo1; uint2 hi; uint32_t sz[4]; };
 
 }  // namespace
 
@@ -141,14 +146,14 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = a.stages;
-  const int b_stage = a.n_pad * BKS * 2;
+  const int b_sub = a.n_pad * BKS * 2;
+  const int b_stage = 2 * b_sub;
   const int stage_bytes = A_STAGE + b_stage;
   const uint32_t ring = (smem_u32(smem_m) + 1023u) & ~1023u;
   const int tile = blockIdx.x, slice = blockIdx.y;
-  const int nk64 = a.k / BKS;
-  const int kb0 = (int)(((long)nk64 * slice) / a.ks), kb1 = (int)(((long)nk64 * (slice + 1)) / a.ks);
-  const int nkb = kb1 - kb0;
   const int nbat = a.k / 128;
+  const int kb0 = (nbat * slice) / a.ks, kb1 = (nbat * (slice + 1)) / a.ks;      // 128-k batches of this slice
+  const int nkb = kb1 - kb0;
   const int npan = a.n / 32;
   const uint32_t tmem_cols = a.n_pad < 32 ? 32u : (uint32_t)a.n_pad;
 
@@ -176,8 +181,10 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
         const int s = kb % S;
         if (kb >= S && !mbar_wait_m(smem_u32(&empty_bar[s]), ((kb / S) - 1) & 1)) { atomicExch(&s_failed, 1); break; }
         const uint32_t bar = smem_u32(&full_bar[s]);
+        if (a.dbg & 16) { mbar_arrive_m(bar); continue; }
         mbar_expect_tx_m(bar, (uint32_t)b_stage);
-        tma_load_2d_m(ring + s * stage_bytes + A_STAGE, &map_x, (kb0 + kb) * BKS, 0, bar);
+        tma_load_2d_m(ring + s * stage_bytes + A_STAGE, &map_x, (kb0 + kb) * 128, 0, bar);
+        tma_load_2d_m(ring + s * stage_bytes + A_STAGE + b_sub, &map_x, (kb0 + kb) * 128 + BKS, 0, bar);
       }
     }
   } else if (warp == 1) {
@@ -189,16 +196,22 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
         if (!mbar_wait_m(smem_u32(&full_bar[s]), (kb / S) & 1)) { atomicExch(&s_failed, 1); break; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t sa = ring + s * stage_bytes, sb = sa + A_STAGE;
-        const uint64_t da = desc_sw128(sa), db = desc_sw128(sb);
 #pragma unroll
-        for (int k = 0; k < BKS / 16; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | k) ? 1u : 0u);
+        for (int kh = 0; kh < 2; ++kh) {
+          const uint64_t da = desc_sw128(sa + kh * A_SUB), db = desc_sw128(sb + kh * b_sub);
+#pragma unroll
+          for (int k = 0; k < BKS / 16; ++k)
+            if (!(a.dbg & 8)) umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | kh | k) ? 1u : 0u);
+        }
         umma_commit_m(smem_u32(&empty_bar[s]));
       }
       umma_commit_m(smem_u32(&acc_bar));
     }
   } else {
     // ---------------- dequantisers: warp - 2 = 2 * panel + row block ----------------
-    const int dw = warp - 2;
+    // two sets of eight warps alternate over the stages (set = stage parity), so that sixteen warps hide each other's
+    // latencies; inside a set, warp = 2 * panel + row block
+    const int dw = (warp - 2) & 7, kset = (warp - 2) >> 3;
     const int p = dw >> 1, rbk = dw & 1;
     const int g = lane >> 2, t = lane & 3;
     const int pan = tile * 4 + p;
@@ -206,51 +219,67 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
     const uint8_t* pbase = a.wq + (size_t)(pan_ok ? pan : 0) * nbat * BLK;
     auto load_raw = [&](int kb) -> RawW {
       RawW r;
-      const int kg = kb0 + kb;
-      const int ub = kg >> 1, h = kg & 1;
-      const uint8_t* blk = pbase + (size_t)ub * BLK;
-      if (BITS == 4) r.lo = ld_nc_v4(blk + rbk * W_BATCH + h * 512 + lane * 16);
-      else r.lo = ld_nc_v4(blk + rbk * W_BATCH + lane * 16);
-      if (BITS == 3) r.hi = ld_nc_v2(blk + rbk * W_BATCH + 512 + lane * 8); else r.hi = make_uint2(0u, 0u);
-      const int gi = GPB == 2 ? h : 0;
-      const uint8_t* sz = blk + 2 * W_BATCH + rbk * GPB * 64 + gi * 64 + g * 4;
-      r.sz0 = ld_nc_u32(sz);
-      r.sz1 = ld_nc_u32(sz + 32);
+      const uint8_t* blk = pbase + (size_t)(kb0 + kb) * BLK;
+      r.lo1 = make_uint4(0u, 0u, 0u, 0u); r.hi = make_uint2(0u, 0u); r.sz[2] = r.sz[3] = 0u;
+      if (a.dbg & 1) { r.lo0 = r.lo1 = make_uint4(kb, kb, kb, kb); r.sz[0] = r.sz[1] = r.sz[2] = r.sz[3] = 0x3C003C00u; return r; }
+      r.lo0 = ld_nc_v4(blk + rbk * W_BATCH + lane * 16);
+      if (BITS == 4) r.lo1 = ld_nc_v4(blk + rbk * W_BATCH + 512 + lane * 16);
+      if (BITS == 3) r.hi = ld_nc_v2(blk + rbk * W_BATCH + 512 + lane * 8);
+      const uint8_t* sz = blk + 2 * W_BATCH + rbk * GPB * 64 + g * 4;
+#pragma unroll
+      for (int gi = 0; gi < GPB; ++gi) { r.sz[2 * gi] = ld_nc_u32(sz + gi * 64); r.sz[2 * gi + 1] = ld_nc_u32(sz + gi * 64 + 32); }
       return r;
     };
     // tile address pieces of this lane: rows (p*32 + rbk*16 + g) and that + 8
     const uint32_t row_off = (uint32_t)((p * 4 + rbk * 2) * 1024 + g * 128);
-    RawW nxt;
-    if (nkb > 0) nxt = load_raw(0);
+    // the lane's fields of mma step j cover the four consecutive inputs 16 j + 4 t .. + 3 (first pair, second pair)
+    uint32_t joff[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) joff[j] = (uint32_t)((((2 * j + (t >> 1)) ^ g) << 4) + ((t & 1) << 3));
+    // Register ring of raw FM words, kPrefetch stages deep: enough loads in flight per warp to cover DRAM latency.
+    constexpr int kPrefetch = 4;
+    RawW ringw[kPrefetch];
+#pragma unroll
+    for (int i = 0; i < kPrefetch; ++i)
+      if (kset + 2 * i < nkb) ringw[i] = load_raw(kset + 2 * i);
     bool ok = true;
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      const RawW cur = nxt;
-      if (kb + 1 < nkb) nxt = load_raw(kb + 1);
+    for (int ibase = 0; kset + 2 * ibase < nkb && ok; ibase += kPrefetch) {
+#pragma unroll
+     for (int pi = 0; pi < kPrefetch; ++pi) {
+      const int kb = kset + 2 * (ibase + pi);
+      if (kb >= nkb || !ok) break;
+      const RawW cur = ringw[pi];
+      if (kb + 2 * kPrefetch < nkb) ringw[pi] = load_raw(kb + 2 * kPrefetch);
       const int s = kb % S;
       if (kb >= S) {
         if (!mbar_wait_m(smem_u32(&empty_bar[s]), ((kb / S) - 1) & 1)) { atomicExch(&s_failed, 1); ok = false; break; }
       }
-      const int h = (kb0 + kb) & 1;
-      // (scale, -zero * scale) of rows g and g + 8
-      const __half2 z0 = *reinterpret_cast<const __half2*>(&cur.sz0), z1 = *reinterpret_cast<const __half2*>(&cur.sz1);
-      const float s0 = __low2float(z0), s1 = __low2float(z1);
-      const uint32_t sc0 = h2_bits(s0, s0), sc1 = h2_bits(s1, s1);
-      const uint32_t bi0 = h2_bits(-__high2float(z0) * s0, -__high2float(z0) * s0);
-      const uint32_t bi1 = h2_bits(-__high2float(z1) * s1, -__high2float(z1) * s1);
-      const uint32_t sa = ring + s * stage_bytes + row_off;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+      // (scale, scale) and (-zero * scale) x 2 of rows g and g + 8, formed in fp16 (one rounding of the product, as
+      // an fp32 product rounded once would give); a panel past the end of the matrix contributes zeros
+      const int gi = GPB == 2 ? h : 0;
+      const __half2 z0 = *reinterpret_cast<const __half2*>(&cur.sz[2 * gi]), z1 = *reinterpret_cast<const __half2*>(&cur.sz[2 * gi + 1]);
+      const __half2 zero2 = __floats2half2_rn(0.f, 0.f);
+      const __half2 s0h = pan_ok ? __low2half2(z0) : zero2, s1h = pan_ok ? __low2half2(z1) : zero2;
+      const __half2 b0h = __hneg2(__hmul2(__high2half2(z0), s0h)), b1h = __hneg2(__hmul2(__high2half2(z1), s1h));
+      const uint32_t sc0 = *reinterpret_cast<const uint32_t*>(&s0h), sc1 = *reinterpret_cast<const uint32_t*>(&s1h);
+      const uint32_t bi0 = *reinterpret_cast<const uint32_t*>(&b0h), bi1 = *reinterpret_cast<const uint32_t*>(&b1h);
+      const uint32_t sa = ring + s * stage_bytes + h * A_SUB + row_off;
+      const uint4 lo = (BITS == 4 && h) ? cur.lo1 : cur.lo0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         uint32_t r0, r1, r2, r3;
         float ic0, ic1;                       // 1 / c of the two field positions
         if (BITS == 4) {
-          const uint32_t w = j == 0 ? cur.lo.x : (j == 1 ? cur.lo.y : (j == 2 ? cur.lo.z : cur.lo.w));
+          const uint32_t w = j == 0 ? lo.x : (j == 1 ? lo.y : (j == 2 ? lo.z : lo.w));
           const uint32_t w8 = w >> 8;
           r0 = lop3_and_or(w, 0x000F000Fu, kMagicH); r2 = lop3_and_or(w, 0x00F000F0u, kMagicH);
           r1 = lop3_and_or(w8, 0x000F000Fu, kMagicH); r3 = lop3_and_or(w8, 0x00F000F0u, kMagicH);
           ic0 = 1.f; ic1 = 1.f / 16.f;
         } else {
           const int u = 2 * h + (j >> 1);
-          const uint32_t w = u == 0 ? cur.lo.x : (u == 1 ? cur.lo.y : (u == 2 ? cur.lo.z : cur.lo.w));
+          const uint32_t w = u == 0 ? lo.x : (u == 1 ? lo.y : (u == 2 ? lo.z : lo.w));
           const uint32_t w8 = w >> 8;
           const int q0 = 2 * (j & 1);
           const uint32_t m0 = 0x00030003u << (2 * q0), m1 = 0x00030003u << (2 * q0 + 2);
@@ -273,15 +302,17 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
         r2 = hfma2_u(hfma2_u(r2, m1h, a1h), sc0, bi0);
         r1 = hfma2_u(hfma2_u(r1, m0h, a0h), sc1, bi1);
         r3 = hfma2_u(hfma2_u(r3, m1h, a1h), sc1, bi1);
-        if (!pan_ok) { r0 = r1 = r2 = r3 = 0u; }
-        // the lane's fields cover the four consecutive inputs 16 j + 4 t .. + 3 (r0: first pair, r2: second pair)
-        const uint32_t off = (uint32_t)((((2 * j + (t >> 1)) ^ g) << 4) + ((t & 1) << 3));
-        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(sa + off), "r"(r0), "r"(r2) : "memory");
-        asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(sa + 1024u + off), "r"(r1), "r"(r3) : "memory");
+        const uint32_t off = joff[j];
+        if (!(a.dbg & 4)) {
+          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(sa + off), "r"(r0), "r"(r2) : "memory");
+          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(sa + 1024u + off), "r"(r1), "r"(r3) : "memory");
+        }
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
+      }
+      if (!(a.dbg & 2)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive_m(smem_u32(&full_bar[s]));
+     }
     }
 
     // ---------------- epilogue: warps 2..5 own TMEM lanes 32 * (warp % 4) ----------------
@@ -446,12 +477,12 @@ static EncodeTiledFnM encode_fn_m() {
 }
 
 // k slices of a linear for this kernel: a function of the shape only.  Enough CTAs to cover the SMs, slices of at
-// least 512 inputs.
+// least 512 inputs (four 128-k stages).
 B2_API int b2_wq_mm_ks(int n, int k) {
-  const int tiles = (n + BM - 1) / BM, nk64 = k / BKS;
+  const int tiles = (n + BM - 1) / BM, nbat = k / 128;
   int best = 1;
-  for (int ks = 1; ks <= nk64 && ks <= 16; ++ks) {
-    if (nk64 % ks || nk64 / ks < 8) continue;
+  for (int ks = 1; ks <= nbat && ks <= 16; ++ks) {
+    if (nbat % ks || nbat / ks < 4) continue;
     best = ks;
     if (tiles * ks >= 148) break;
   }
@@ -474,7 +505,7 @@ B2_API int b2_wq_mm(const WqMmArgs* args, const bf16* x, long ldx, const float* 
   a.ks = b2_wq_mm_ks(a.n, a.k);
   if ((a.epi == EPI_RESID || a.epi == EPI_ARGMAX) && a.m > a.ss_ld) return B2_ERR_ARG;
   if (a.ks > 1 && (!a.scratch || !a.counters)) return B2_ERR_ARG;
-  const int b_stage = a.n_pad * BKS * 2;
+  const int b_stage = 2 * a.n_pad * BKS * 2;
   int stages = (200 * 1024) / (A_STAGE + b_stage);
   a.stages = stages > 8 ? 8 : stages;
   if (a.stages < 2) return B2_ERR_ARG;
