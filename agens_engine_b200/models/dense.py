@@ -128,8 +128,17 @@ class DenseModel:
         lins = [self.lm_head] + [d[lin] for d in self.layers[:1] for lin in LINEARS]
         need = max(lib.b2_wq_gemv_scratch_floats(x.n, x.k, x.ks, r, M_GEMV) for x in lins for r in (2, x.rb))
         panels = max(x.n_panels() for x in lins)
+        keep = self.ws.mm_min_rows
         self.ws = L.GemvWorkspace(self.dev, floats=max(need, 1 << 16), panels=max(panels, 1 << 10))
+        self.ws.mm_min_rows = keep
         return self
+
+    def set_linear_path(self, mm_min_rows: Optional[int]):
+        """Token rows from which the small-m linears run on the tcgen05 GEMM instead of the GEMV (None: the default of
+        ops.linear).  The two kernels round differently, so a deployment that wants every row to be independent of the
+        batch it travels in pins one path: 1 = tensor-core GEMM for every step, 33 = GEMV for every step."""
+        self.ws.mm_min_rows = mm_min_rows
+        self._graphs.clear()
 
     # ------------------------------------------------------------------------------------------------ sessions
     def new_seq(self, seq: int):

@@ -121,6 +121,7 @@ class GemvWorkspace:
         self.counters = torch.zeros(panels, dtype=torch.int32, device=device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.x16 = None
+        self.mm_min_rows = None      # overrides MM_MIN_ROWS for the launches that use this workspace
 
     def x16_buffer(self, n_pad: int, k: int) -> torch.Tensor:
         if self.x16 is None or self.x16.numel() < n_pad * k:
@@ -146,7 +147,7 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
     ``MM_MIN_ROWS - 1`` rows go to the tensor-core GEMM (:func:`mm`), which takes the same arguments."""
     lib = _lib.cuda_lib()
     m = x.shape[0]
-    if m >= MM_MIN_ROWS and tp is None:
+    if m >= (ws.mm_min_rows or MM_MIN_ROWS) and tp is None:
         return mm(lin, x, ws, epi=epi, pro=pro, ss_in=ss_in, ss_parts=ss_parts, norm_w=norm_w, eps=eps, resid=resid, out=out,
                   ss_out=ss_out, amax_val=amax_val, amax_idx=amax_idx, n_valid=n_valid, yf=yf)
     assert x.dtype == torch.bfloat16 and x.shape[1] == lin.k and x.stride(1) == 1

@@ -70,6 +70,7 @@ class EngineStats:
     prefill_chunks: int = 0
     tokens_out: int = 0
     tokens_prefilled: int = 0
+    tokens_reused: int = 0
     evictions: int = 0
     rejected: int = 0
     peak_batch: int = 0
@@ -81,10 +82,17 @@ class Engine:
 
     def __init__(self, model: DenseModel, emit: Callable[[int, List[int], bool, Optional[str]], bool],
                  sources_factory: Optional[Callable[[], Sequence[DraftSource]]] = None, max_drafts: int = 0,
-                 max_batch: Optional[int] = None, think_tokens: Optional[tuple] = None, reserve_ahead: int = 16):
+                 max_batch: Optional[int] = None, think_tokens: Optional[tuple] = None, reserve_ahead: int = 16,
+                 keep_sequences: bool = False, prefix_chunk: int = 64, prefix_budget_bytes: int = 1 << 40,
+                 invariant: bool = True):
         self.m, self.emit = model, emit
         self.max_batch = min(max_batch or model.max_seqs, model.max_seqs, M_GEMV)
         self.max_drafts = max_drafts
+        if invariant and getattr(model, "world", 1) == 1:
+            # batch-invariant serving (the reference's server mode): every step uses the same linear kernel whatever the
+            # number of rows, so a request's tokens do not depend on what else is running
+            rows_cap = self.max_batch * (1 + max_drafts)
+            model.set_linear_path(None if rows_cap <= 8 else 1)
         self.spec = SpecDecoder(model, list(sources_factory()) if sources_factory else [], max_drafts=max_drafts)
         self.think = think_tokens                      # (start id, end id) for budget / guard
         self.reserve_ahead = reserve_ahead
@@ -97,6 +105,14 @@ class Engine:
         self._thread: Optional[threading.Thread] = None
         self._rid = 0
         self._lock = threading.Lock()
+        # Finished sequences stay resident (or parked on the host) so that the next turn of a conversation, or another
+        # request with the same prompt prefix, skips the prefill of what is already in the KV cache.
+        self.keep_sequences = keep_sequences
+        self.kept: Dict[int, dict] = {}                # handle -> {slot | parked, tokens, session, t_last}
+        self.by_session: Dict[str, int] = {}
+        self._next_handle = 1
+        self.prefix = host.PrefixCache(prefix_budget_bytes, prefix_chunk) if keep_sequences else None
+        self.prefix_chunk = prefix_chunk
 
     # ------------------------------------------------------------------------------------------------ submission
     def submit(self, prompt: Sequence[int], sampling: Optional[dict] = None, rid: Optional[int] = None, session: str = "") -> int:
@@ -172,9 +188,12 @@ class Engine:
                 self.stats.rejected += 1
                 self.emit(r.rid, [], True, "prompt does not fit the context window" if r.prompt else "empty prompt")
                 continue
-            if not self.free_slots or len(self.active) >= self.max_batch:
+            if len(self.active) >= self.max_batch or (not self.free_slots and not self._drop_kept(exclude_session=r.session)):
                 keep.append(r); continue
             items = [self._demand(a) for a in self.active.values()] + [self._demand(r)]
+            while self.kept and (not host.kv_safe(self.m.free_pages(), items) or self._pages(len(r.prompt) + 1) > self.m.free_pages()):
+                if not self._drop_kept(exclude_session=r.session):
+                    break
             if self.active and not host.kv_safe(self.m.free_pages(), items):
                 keep.append(r); continue
             if not self.active and self._pages(len(r.prompt) + len(r.out) + 1) > self.m.free_pages():
@@ -195,7 +214,8 @@ class Engine:
                 self.active[r.slot] = r
                 continue
             r.state, r.done_prompt, r.chunk_index = PREFILL, 0, 0
-            self.m.new_seq(r.slot)
+            if not self._reuse_kept(r):
+                self.m.new_seq(r.slot)
             if self.think and r.sampling.get("reasoning_budget") is not None:
                 r.budget = host.ReasoningBudget(int(r.sampling["reasoning_budget"]), float(r.sampling.get("reasoning_soft", 0.0)),
                                                 r.prompt, self.think[0], self.think[1])
@@ -207,11 +227,109 @@ class Engine:
             self.stats.peak_batch = max(self.stats.peak_batch, len(self.active))
         self.waiting = keep
 
+    # ---- kept sequences: conversations and prompt-prefix reuse ------------------------------------------------------
+    def _keep(self, r: Request):
+        """The finished request's sequence stays in its slot, findable by session id and by token prefix."""
+        n = self.m.seq_len_host[r.slot]
+        toks = (r.prompt + r.out)[:n]
+        h = self._next_handle
+        self._next_handle += 1
+        if r.session and r.session in self.by_session:
+            self._forget(self.by_session[r.session])
+        self.kept[h] = {"slot": r.slot, "parked": None, "tokens": toks, "session": r.session, "t_last": time.monotonic()}
+        if r.session:
+            self.by_session[r.session] = h
+        # one entry per chunk boundary (the cache matches whole chunks); the bytes are booked on the longest one
+        top = n // self.prefix_chunk * self.prefix_chunk
+        for c in range(self.prefix_chunk, top + 1, self.prefix_chunk):
+            _, evicted = self.prefix.insert(toks[:c], h, self.m.cfg.kv_bytes_per_token() * n if c == top else 0)
+            for e in evicted:
+                if e != h:
+                    self._forget(e)
+
+    def _forget(self, h: int):
+        k = self.kept.pop(h, None)
+        if k is None:
+            return
+        if k["session"] and self.by_session.get(k["session"]) == h:
+            self.by_session.pop(k["session"])
+        if k["slot"] is not None:
+            self.m.free_seq(k["slot"])
+            self.free_slots.append(k["slot"])
+
+    def _drop_kept(self, exclude_session: str = "") -> bool:
+        """Gives up the least recently used kept sequence: one that belongs to a conversation is parked on the host
+        (its slot and pages are freed, the next turn brings it back), an anonymous one is dropped.  Snapshots go before
+        conversations, as in the reference's eviction order (serve.rs:616-639)."""
+        cands = [(0 if not k["session"] else 1, h, time.monotonic() - k["t_last"], 0) for h, k in self.kept.items()
+                 if k["slot"] is not None and not (exclude_session and k["session"] == exclude_session)]
+        if not cands:
+            return False
+        i = host.pick_victim(cands, hold_s=0.0, allow_protected=True)
+        if i < 0:
+            return False
+        h = cands[i][1]
+        k = self.kept[h]
+        if k["session"]:
+            k["parked"] = self.m.park(k["slot"])
+            self.free_slots.append(k["slot"])
+            k["slot"] = None
+        else:
+            self._forget(h)
+        return True
+
+    def _reuse_kept(self, r: Request) -> bool:
+        """Starts ``r`` from a kept sequence when one shares a long enough token prefix: the conversation's own
+        sequence is taken over, any other match is forked (full pages shared, copy-on-write by construction: the
+        child is cut at a page boundary).  Returns True when the slot now holds a sequence."""
+        if not self.keep_sequences:
+            return False
+        page = self.m.cfg.page_size
+        limit = len(r.prompt) - 1                                     # the last prompt token must be fed to get logits
+        h = self.by_session.get(r.session) if r.session else None
+        if h is not None:
+            k = self.kept[h]
+            n = 0
+            for a, b in zip(k["tokens"], r.prompt[:limit]):
+                if a != b:
+                    break
+                n += 1
+            n = n // page * page
+            if n >= page:
+                self.kept.pop(h); self.by_session.pop(r.session)
+                if k["slot"] is None:
+                    self.m.unpark(r.slot, k["parked"])
+                else:                                                  # the request moves into the kept sequence's slot
+                    self.spec.samp.pop(r.slot, None)
+                    self.free_slots.append(r.slot)
+                    r.slot = k["slot"]
+                    self.spec.samp[r.slot] = r.state_of_sampling()
+                self.m.truncate(r.slot, n)
+                r.done_prompt = n
+                self.stats.tokens_reused += n
+                return True
+        n, h = self.prefix.lookup(r.prompt[:limit])
+        k = self.kept.get(h) if n >= self.prefix_chunk else None
+        if k is None or k["slot"] is None:
+            return False
+        n = min(n, len(k["tokens"])) // page * page
+        try:
+            self.m.fork(k["slot"], r.slot)
+        except RuntimeError:
+            return False
+        self.m.truncate(r.slot, n)
+        k["t_last"] = time.monotonic()
+        r.done_prompt = n
+        self.stats.tokens_reused += n
+        return True
+
     # ---- eviction ------------------------------------------------------------------------------------------------
     def _evict_for(self, needy: Request) -> bool:
         """Preempts the most recently submitted other sequence and re-queues it at the head of the line (a decoding
         victim's KV rows wait in pinned host memory and come back bit for bit; a prefilling victim starts over).  False
         if nobody can go."""
+        if self._drop_kept():
+            return True
         others = [r for r in self.active.values() if r is not needy]
         if not others:
             return False
@@ -376,7 +494,14 @@ class Engine:
         r.t_last = time.monotonic()
         self.stats.tokens_out += len(out)
         gone = self.emit(r.rid, out, finished, None)
-        if finished or gone:
+        if finished and not gone and self.keep_sequences and r.slot in self.active and r.state == DECODE:
+            for src in self.spec.sources:
+                src.end(r.slot)
+            self.spec.hist.pop(r.slot, None); self.spec.samp.pop(r.slot, None)
+            self.active.pop(r.slot)
+            self._keep(r)
+            r.state = DONE
+        elif finished or gone:
             self._finish(r, silent=True)
 
     def _rewrite_tail(self, r: Request, n_step: int, keep: int, tok: int):

@@ -36,8 +36,9 @@ class Collector:
         return False
 
 
-def _alone(ow, prompt, n_new, sampling=None):
+def _alone(ow, prompt, n_new, sampling=None, path=None):
     m = DenseModel.from_oracle(ow, max_seqs=1, max_ctx=512, prefill_chunk=128)
+    m.set_linear_path(path)         # the engine pins the tensor-core path when a step can exceed eight rows
     return SpecDecoder(m, [], max_drafts=0).generate(0, prompt, n_new, sampling)
 
 
@@ -45,10 +46,11 @@ def test_engine_batches_match_single_runs(tiny):
     cfg, ow = tiny
     torch.manual_seed(11)
     prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (5, 300, 47, 130, 9, 64)]
-    want = [_alone(ow, p, 24) for p in prompts]
     samp = {"temperature": 0.9, "top_k": 50, "top_p": 0.9, "seed": 99, "max_new_tokens": 24}
-    want_s = _alone(ow, prompts[2], 24, SamplingState(0.9, 50, 0.9, 0.0, 99))
     for spec in (False, True):
+        path = 1 if spec else None          # 4 sequences x (1 + 3 drafts) rows: tensor-core path for every step
+        want = [_alone(ow, p, 24, path=path) for p in prompts]
+        want_s = _alone(ow, prompts[2], 24, SamplingState(0.9, 50, 0.9, 0.0, 99), path=path)
         m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512, prefill_chunk=128)
         col = Collector()
         drafter = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512) if spec else None
@@ -121,3 +123,35 @@ def test_engine_behind_openai_server(tiny, tmp_path):
         assert st == 200 and json.loads(text)["usage"]["completion_tokens"] == 8
     finally:
         eng.stop()
+
+
+def test_engine_keeps_sequences_for_conversations_and_prefix_reuse(tiny):
+    cfg, ow = tiny
+    torch.manual_seed(13)
+    m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512, prefill_chunk=128)
+    col = Collector()
+    eng = Engine(m, col, max_batch=2, keep_sequences=True, prefix_chunk=64)
+    q = torch.randint(0, cfg.vocab, (100,)).tolist()
+    solo = _alone(ow, q, 16)
+    a = eng.submit(q, {"max_new_tokens": 16})
+    eng.run_until_idle(5000)
+    assert col.toks[a] == solo and eng.stats.tokens_reused == 0 and len(eng.kept) == 1
+    # the same prompt again: forked from the kept sequence at a chunk boundary, same tokens, less prefill
+    b = eng.submit(q, {"max_new_tokens": 16})
+    eng.run_until_idle(5000)
+    assert eng.stats.tokens_reused == 64 and col.toks[b] == solo
+    # a conversation: the second turn extends the first turn's tokens and takes its sequence over
+    c = eng.submit(q[:70], {"max_new_tokens": 10}, session="conv")
+    eng.run_until_idle(5000)
+    turn2 = q[:70] + col.toks[c] + torch.randint(0, cfg.vocab, (25,)).tolist()
+    before = eng.stats.tokens_reused
+    d = eng.submit(turn2, {"max_new_tokens": 10}, session="conv")
+    eng.run_until_idle(5000)
+    assert eng.stats.tokens_reused - before >= 64 and len(col.toks[d]) == 10 and not col.err
+    # slots run out: kept sequences are given up (conversations parked on the host) and everything still completes
+    rs = [eng.submit(torch.randint(0, cfg.vocab, (40 + i,)).tolist(), {"max_new_tokens": 6}) for i in range(6)]
+    eng.run_until_idle(20000)
+    assert eng.idle() and all(len(col.toks[r]) == 6 for r in rs) and not col.err
+    e = eng.submit(turn2 + col.toks[d] + [5, 6, 7, 8, 9, 10, 11, 12, 13], {"max_new_tokens": 4}, session="conv")
+    eng.run_until_idle(5000)
+    assert len(col.toks[e]) == 4 and not col.err

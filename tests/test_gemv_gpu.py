@@ -29,6 +29,7 @@ def test_gemv_matches_fp64(bits, group, ks):
     n, k = 160, 1024
     ql, lin = _mk(n, k, bits, group, ks=ks)
     ws = L.GemvWorkspace(DEV)
+    ws.mm_min_rows = 33          # these tests exercise the GEMV at every row count
     for m in (1, 3, 8, 13, 32):
         x = (torch.randn(m, k) * 1.5).to(torch.bfloat16).to(DEV)
         y = L.gemv(lin, x, ws, epi=_lib.EPI_F32)
@@ -63,6 +64,7 @@ def test_rows_do_not_depend_on_batch():
     for bits in (2, 3, 4):
         ql, lin = _mk(128, 2048, bits, 128, seed=bits, ks=2)
         ws = L.GemvWorkspace(DEV)
+        ws.mm_min_rows = 33          # these tests exercise the GEMV at every row count
         x = torch.randn(16, 2048).to(torch.bfloat16).to(DEV)
         y16 = L.gemv(lin, x, ws, epi=_lib.EPI_F32)
         y8 = L.gemv(lin, x[:8].contiguous(), ws, epi=_lib.EPI_F32)
@@ -79,6 +81,7 @@ def test_rows_do_not_depend_on_batch():
 def test_gemv_is_deterministic():
     ql, lin = _mk(256, 4096, 3, 128, seed=9, ks=4)
     ws = L.GemvWorkspace(DEV)
+    ws.mm_min_rows = 33          # these tests exercise the GEMV at every row count
     x = torch.randn(4, 4096).to(torch.bfloat16).to(DEV)
     y0 = L.gemv(lin, x, ws, epi=_lib.EPI_F32)
     for _ in range(20):
@@ -91,6 +94,7 @@ def test_norm_prologue_and_residual_epilogue():
     ql, lin = _mk(n, d, 4, 128, seed=1)
     qlo, lino = _mk(d, n, 4, 128, seed=2, ks=1)
     ws = L.GemvWorkspace(DEV)
+    ws.mm_min_rows = 33          # these tests exercise the GEMV at every row count
     m = 3
     h = torch.randn(m, d).to(torch.bfloat16).to(DEV)
     nw = (1 + 0.1 * torch.randn(d)).to(torch.bfloat16).to(DEV)
