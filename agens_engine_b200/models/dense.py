@@ -10,6 +10,7 @@ only per-step input is the token produced by the previous step, handled on the d
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -49,6 +50,7 @@ class DenseModel:
         self.tier = None                               # HostKvTier once enable_host_tier() was called
         self._tiered_groups: Dict[int, tuple] = {}     # this step's sequences with pages on the host
         self.prefill_split = 256                       # KV split size of prefill attention
+        self.prefill_mm = os.environ.get("B200E_PREFILL_MM", "1") == "1"
         self._alloc_buffers()
 
     # ------------------------------------------------------------------------------------------------ weights
@@ -363,7 +365,11 @@ class DenseModel:
 
     # ------------------------------------------------------------------------------------------------ prefill
     def _linear_big(self, lin: L.WqLinear, x: torch.Tensor) -> torch.Tensor:
-        """bf16 [T, n] = x @ dequant(W)^T for T > 32 rows."""
+        """bf16 [T, n] = x @ dequant(W)^T for a prefill chunk.  Up to 256 rows run on the mixed-bit tensor-core GEMM
+        (weights dequantised inside the kernel, one pass over the packed weights); longer chunks dequantise to a bf16
+        buffer first and use the plain bf16 GEMM."""
+        if x.shape[0] <= 256 and self.prefill_mm:
+            return L.mm(lin, x.contiguous(), self.ws)
         from ..ops import gemm as G
         return G.wq_linear(lin, x, self)
 

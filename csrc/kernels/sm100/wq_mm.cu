@@ -24,7 +24,7 @@ struct WqMmArgs {
   const uint8_t* wq; int n, k, m;
   int bits, group;
   int ks;                     // k slices: b2_wq_mm_ks(n, k)
-  int n_pad;                  // token rows of the fp16 activation buffer: 16, 32, 64, 128 or 256
+  int n_pad;                  // token rows of the fp16 activation buffer: 32, 64, 128 or 256
   int stages;
   int epi;
   bf16* y; long ldy;
@@ -155,7 +155,10 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
   const int kb0 = (nbat * slice) / a.ks, kb1 = (nbat * (slice + 1)) / a.ks;      // 128-k batches of this slice
   const int nkb = kb1 - kb0;
   const int npan = a.n / 32;
-  const uint32_t tmem_cols = a.n_pad < 32 ? 32u : (uint32_t)a.n_pad;
+  // One accumulator for every token count: splitting the k steps over several TMEM regions measured no faster and
+  // would make a row's summation order depend on how many rows travel with it.
+  const int nacc = 1;
+  const uint32_t tmem_cols = (uint32_t)(nacc * a.n_pad);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init_m(smem_u32(&full_bar[i]), 1 + kDequantWarps); mbar_init_m(smem_u32(&empty_bar[i]), 1); }
@@ -200,8 +203,10 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
         for (int kh = 0; kh < 2; ++kh) {
           const uint64_t da = desc_sw128(sa + kh * A_SUB), db = desc_sw128(sb + kh * b_sub);
 #pragma unroll
-          for (int k = 0; k < BKS / 16; ++k)
-            if (!(a.dbg & 8)) umma_f16(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb | kh | k) ? 1u : 0u);
+          for (int k = 0; k < BKS / 16; ++k) {
+            const int q = kh * 4 + k, acc = q % nacc;
+            if (!(a.dbg & 8)) umma_f16(tmem_base + (uint32_t)(acc * a.n_pad), da + 2 * k, db + 2 * k, idesc, (kb || q >= nacc) ? 1u : 0u);
+          }
         }
         umma_commit_m(smem_u32(&empty_bar[s]));
       }
@@ -237,7 +242,7 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
 #pragma unroll
     for (int j = 0; j < 4; ++j) joff[j] = (uint32_t)((((2 * j + (t >> 1)) ^ g) << 4) + ((t & 1) << 3));
     // Register ring of raw FM words, kPrefetch stages deep: enough loads in flight per warp to cover DRAM latency.
-    constexpr int kPrefetch = 4;
+    constexpr int kPrefetch = 6;
     RawW ringw[kPrefetch];
 #pragma unroll
     for (int i = 0; i < kPrefetch; ++i)
@@ -247,13 +252,12 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
 #pragma unroll
      for (int pi = 0; pi < kPrefetch; ++pi) {
       const int kb = kset + 2 * (ibase + pi);
-      if (kb >= nkb || !ok) break;
+      if (kb < nkb && ok) {
       const RawW cur = ringw[pi];
       if (kb + 2 * kPrefetch < nkb) ringw[pi] = load_raw(kb + 2 * kPrefetch);
       const int s = kb % S;
-      if (kb >= S) {
-        if (!mbar_wait_m(smem_u32(&empty_bar[s]), ((kb / S) - 1) & 1)) { atomicExch(&s_failed, 1); ok = false; break; }
-      }
+      if (kb >= S && !mbar_wait_m(smem_u32(&empty_bar[s]), ((kb / S) - 1) & 1)) { atomicExch(&s_failed, 1); ok = false; }
+      if (ok) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
       // (scale, scale) and (-zero * scale) x 2 of rows g and g + 8, formed in fp16 (one rounding of the product, as
@@ -295,9 +299,11 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
           }
           ic0 = q0 ? 1.f / 16.f : 1.f; ic1 = q0 ? 1.f / 64.f : 1.f / 4.f;
         }
-        // code = (1024 + c code) / c - 1024 / c (exact), weight = code * scale - zero * scale
-        const uint32_t m0h = h2_bits(ic0, ic0), a0h = h2_bits(-1024.f * ic0, -1024.f * ic0);
-        const uint32_t m1h = h2_bits(ic1, ic1), a1h = h2_bits(-1024.f * ic1, -1024.f * ic1);
+        // code = (1024 + c code) / c - 1024 / c (exact), weight = code * scale - zero * scale.  fp16 bit patterns of
+        // (1 / c, -1024 / c): c = 1: (1, -1024); 4: (0.25, -256); 16: (0.0625, -64); 64: (0.015625, -16)
+        const uint32_t m0h = ic0 == 1.f ? 0x3C003C00u : 0x2C002C00u, a0h = ic0 == 1.f ? 0xE400E400u : 0xD400D400u;
+        const uint32_t m1h = ic1 == 0.25f ? 0x34003400u : (ic1 == 1.f / 16.f ? 0x2C002C00u : 0x24002400u);
+        const uint32_t a1h = ic1 == 0.25f ? 0xDC00DC00u : (ic1 == 1.f / 16.f ? 0xD400D400u : 0xCC00CC00u);
         r0 = hfma2_u(hfma2_u(r0, m0h, a0h), sc0, bi0);
         r2 = hfma2_u(hfma2_u(r2, m1h, a1h), sc0, bi0);
         r1 = hfma2_u(hfma2_u(r1, m0h, a0h), sc1, bi1);
@@ -312,6 +318,8 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
       if (!(a.dbg & 2)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive_m(smem_u32(&full_bar[s]));
+      }
+      }
      }
     }
 
@@ -332,12 +340,19 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
       if (a.ks > 1) {
         if (good) {
           for (int c0 = 0; c0 < a.m; c0 += 32) {
-            uint32_t r[32];
-            tmem_ld32_m(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float acc[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+            for (int ai = 0; ai < nacc; ++ai) {
+              uint32_t r[32];
+              tmem_ld32_m(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(ai * a.n_pad + c0), r);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int i = 0; i < 32; ++i) acc[i] += __uint_as_float(r[i]);
+            }
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              if (c0 + i < a.m) my_part[(size_t)(c0 + i) * BM + rit] = __uint_as_float(r[i]);
+              if (c0 + i < a.m) my_part[(size_t)(c0 + i) * BM + rit] = acc[i];
           }
           __threadfence();
         }
@@ -360,11 +375,15 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
               v[i] = sum;
             }
           } else {
-            uint32_t r[32];
-            tmem_ld32_m(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c0, r);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+            for (int i = 0; i < 32; ++i) v[i] = 0.f;
+            for (int ai = 0; ai < nacc; ++ai) {
+              uint32_t r[32];
+              tmem_ld32_m(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)(ai * a.n_pad + c0), r);
+              asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] += __uint_as_float(r[i]);
+            }
           }
 #pragma unroll 1
           for (int i = 0; i < 32; ++i) {
@@ -488,7 +507,7 @@ B2_API int b2_wq_mm_ks(int n, int k) {
   }
   return best;
 }
-B2_API int b2_wq_mm_npad(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256))); }
+B2_API int b2_wq_mm_npad(int m) { return m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)); }
 B2_API long b2_wq_mm_scratch_floats(int n, int k, int n_pad) {
   const long tiles = (n + BM - 1) / BM;
   return tiles * b2_wq_mm_ks(n, k) * (long)n_pad * BM;
