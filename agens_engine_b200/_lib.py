@@ -177,6 +177,7 @@ def _declare(lib: C.CDLL):
         "b2_rmsnorm": ([vp, l, vp, l, vp, l, vp, f, i, i, vp, l, vp], i),
         "b2_sumsq": ([vp, l, i, i, vp, vp], i),
         "b2_rope_kvstore": ([vp, l, i, i, i, i, vp, vp, vp, vp, vp, i, vp, i, i, vp, l, vp, vp], i),
+        "b2_rope_kvstore_m": ([vp, l, i, i, i, i, vp, vp, vp, vp, vp, vp, i, vp, i, i, vp, l, vp, vp], i),
         "b2_swiglu_interleaved": ([vp, l, i, i, vp, l, vp], i),
         "b2_argmax_final": ([vp, vp, i, i, i, vp, vp, vp], i),
         "b2_argmax_rows": ([vp, l, i, i, vp, vp], i),

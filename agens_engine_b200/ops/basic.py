@@ -67,6 +67,42 @@ def rope_kvstore(qkv: torch.Tensor, hq: int, hkv: int, hd: int, inv_freq: torch.
     return status
 
 
+def mrope_pair_axis(head_dim: int, sections, interleaved: bool = True, device="cpu") -> torch.Tensor:
+    """uint8 [head_dim / 2]: which of the (time, height, width) positions drives each rotary frequency pair.
+    ``sections`` = pairs per axis; interleaved: t, h, w, t, h, w, ... while an axis still has pairs left (the layout of
+    the reference's text model, rope.cu:62-108), else three contiguous blocks."""
+    half = head_dim // 2
+    assert sum(sections) == half
+    out = []
+    if interleaved:
+        left = list(sections)
+        a = 0
+        while len(out) < half:
+            if left[a] > 0:
+                out.append(a); left[a] -= 1
+            a = (a + 1) % 3
+    else:
+        for a, n in enumerate(sections):
+            out += [a] * n
+    return torch.tensor(out, dtype=torch.uint8, device=device)
+
+
+def rope_kvstore_m(qkv: torch.Tensor, hq: int, hkv: int, hd: int, inv_freq: torch.Tensor, tok_pos: torch.Tensor,
+                   rope_pos3: torch.Tensor, pair_axis: torch.Tensor, tok_seq: torch.Tensor, block_table: torch.Tensor,
+                   kv_pool: torch.Tensor, q_out: torch.Tensor, status: Optional[torch.Tensor] = None):
+    """RoPE + KV store with multi-axis positions ``rope_pos3`` int32 [3, n] (time, height, width)."""
+    lib = _lib.cuda_lib()
+    n = qkv.shape[0]
+    status = _status(qkv.device) if status is None else status
+    assert rope_pos3.shape == (3, n) and rope_pos3.is_contiguous() and pair_axis.numel() == hd // 2
+    with torch.cuda.device(qkv.device):
+        check(lib.b2_rope_kvstore_m(ptr(qkv), qkv.stride(0), n, hq, hkv, hd, ptr(inv_freq), ptr(tok_pos), ptr(rope_pos3),
+                                    ptr(pair_axis), ptr(tok_seq), ptr(block_table), block_table.stride(0), ptr(kv_pool),
+                                    kv_pool.shape[3], kv_pool.shape[0], ptr(q_out), q_out.stride(0), ptr(status),
+                                    current_stream()), "b2_rope_kvstore_m")
+    return status
+
+
 def swiglu_interleaved(gu: torch.Tensor) -> torch.Tensor:
     lib = _lib.cuda_lib()
     n, f2 = gu.shape

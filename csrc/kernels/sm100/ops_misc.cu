@@ -113,7 +113,8 @@ __global__ void rope_kvstore_kernel(bf16* __restrict__ qkv, long ld, int n_tok, 
                                     const float* __restrict__ inv_freq, const int* __restrict__ tok_pos,
                                     const int* __restrict__ rope_pos, const int* __restrict__ tok_seq, const int* __restrict__ block_table, int bt_ld,
                                     bf16* __restrict__ kv_pool, int page_size, int n_pages, bf16* __restrict__ q_out,
-                                    long ldq, int* __restrict__ status) {
+                                    long ldq, int* __restrict__ status, const int* __restrict__ rope_pos3,
+                                    const unsigned char* __restrict__ pair_axis) {
   pdl_wait();
   pdl_launch_dependents();
   const int warps_per_block = blockDim.x >> 5;
@@ -145,8 +146,12 @@ __global__ void rope_kvstore_kernel(bf16* __restrict__ qkv, long ld, int n_tok, 
     const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(src + i);
     const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(src + i + half);
     float s0, c0, s1, c1;
-    sincosf((float)rpos * inv_freq[i], &s0, &c0);
-    sincosf((float)rpos * inv_freq[i + 1], &s1, &c1);
+    // multi-axis rotary (image tokens): the position of frequency pair i comes from axis pair_axis[i] of
+    // rope_pos3 [3][n_tok] (time, height, width); text tokens carry the same value on all three axes
+    const int p0 = rope_pos3 ? rope_pos3[(size_t)pair_axis[i] * n_tok + tok] : rpos;
+    const int p1 = rope_pos3 ? rope_pos3[(size_t)pair_axis[i + 1] * n_tok + tok] : rpos;
+    sincosf((float)p0 * inv_freq[i], &s0, &c0);
+    sincosf((float)p1 * inv_freq[i + 1], &s1, &c1);
     const float x0 = __low2float(lo), x1 = __high2float(lo), y0 = __low2float(hi), y1 = __high2float(hi);
     *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(x0 * c0 - y0 * s0, x1 * c1 - y1 * s1);
     *reinterpret_cast<__nv_bfloat162*>(dst + i + half) = __floats2bfloat162_rn(y0 * c0 + x0 * s0, y1 * c1 + x1 * s1);
@@ -302,7 +307,20 @@ B2_API int b2_rope_kvstore(bf16* qkv, long ld, int n_tok, int hq, int hkv, int h
   if (hd % 4 || hd > 256 || n_tok <= 0) return B2_ERR_ARG;
   const int warps = n_tok * (hq + 2 * hkv);
   return launch_pdl(rope_kvstore_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, qkv, ld, n_tok, hq, hkv, hd, inv_freq,
-                    tok_pos, rope_pos, tok_seq, block_table, bt_ld, kv_pool, page_size, n_pages, q_out, ldq, status);
+                    tok_pos, rope_pos, tok_seq, block_table, bt_ld, kv_pool, page_size, n_pages, q_out, ldq, status,
+                    (const int*)nullptr, (const unsigned char*)nullptr);
+}
+
+// Same with multi-axis rotary positions: rope_pos3 [3][n_tok], pair_axis [hd / 2] (axis 0..2 of every frequency pair).
+B2_API int b2_rope_kvstore_m(bf16* qkv, long ld, int n_tok, int hq, int hkv, int hd, const float* inv_freq, const int* tok_pos,
+                             const int* rope_pos3, const unsigned char* pair_axis, const int* tok_seq, const int* block_table,
+                             int bt_ld, bf16* kv_pool, int page_size, int n_pages, bf16* q_out, long ldq, int* status,
+                             cudaStream_t st) {
+  if (hd % 4 || hd > 256 || n_tok <= 0 || !rope_pos3 || !pair_axis) return B2_ERR_ARG;
+  const int warps = n_tok * (hq + 2 * hkv);
+  return launch_pdl(rope_kvstore_kernel, dim3((warps + 7) / 8), dim3(256), 0, st, qkv, ld, n_tok, hq, hkv, hd, inv_freq,
+                    tok_pos, (const int*)nullptr, tok_seq, block_table, bt_ld, kv_pool, page_size, n_pages, q_out, ldq, status,
+                    rope_pos3, pair_axis);
 }
 
 B2_API int b2_swiglu_interleaved(const bf16* gu, long ldg, int n_tok, int f, bf16* act, long lda, cudaStream_t st) {

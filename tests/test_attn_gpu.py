@@ -127,3 +127,34 @@ def test_rmsnorm_embed_swiglu():
     g = gu.reshape(n, 32, 2, 8)[:, :, 0].reshape(n, 256).float()
     u = gu.reshape(n, 32, 2, 8)[:, :, 1].reshape(n, 256).float()
     assert (act.float() - torch.nn.functional.silu(g) * u).abs().max() < 0.03
+
+
+def test_multi_axis_rope_matches_reference():
+    """Frequency pair i rotates by the position of its axis (time / height / width); text rows equal plain RoPE."""
+    from agens_engine_b200.ops import basic
+    torch.manual_seed(5)
+    dev = "cuda:0"
+    n, hq, hkv, hd = 9, 4, 2, 64
+    qkv = torch.randn(n, (hq + 2 * hkv) * hd, device=dev).to(torch.bfloat16)
+    inv = basic.rope_inv_freq(hd, 1e6, dev)
+    axis = basic.mrope_pair_axis(hd, [11, 11, 10], True, dev)
+    assert axis[:7].tolist() == [0, 1, 2, 0, 1, 2, 0] and int((axis == 2).sum()) == 10
+    pos3 = torch.randint(0, 50, (3, n), dtype=torch.int32, device=dev)
+    pos3[:, :3] = pos3[0, :3]                                   # text rows: same value on every axis
+    tok_pos = torch.arange(n, dtype=torch.int32, device=dev)
+    seq = torch.zeros(n, dtype=torch.int32, device=dev)
+    bt = torch.arange(4, dtype=torch.int32, device=dev)[None, :]
+    pool = torch.zeros(4, 2, hkv, 16, hd, dtype=torch.bfloat16, device=dev)
+    q = torch.empty(n, hq * hd, dtype=torch.bfloat16, device=dev)
+    basic.rope_kvstore_m(qkv.clone(), hq, hkv, hd, inv, tok_pos, pos3.contiguous(), axis, seq, bt, pool, q)
+    half = hd // 2
+    pp = pos3[axis.long()].T.float()                             # [n, half]: position per pair
+    ang = pp * inv[None, :]
+    x = qkv[:, :hq * hd].float().view(n, hq, hd)
+    ref = torch.cat([x[..., :half] * torch.cos(ang)[:, None] - x[..., half:] * torch.sin(ang)[:, None],
+                     x[..., half:] * torch.cos(ang)[:, None] + x[..., :half] * torch.sin(ang)[:, None]], -1)
+    assert (q.float().view(n, hq, hd) - ref).abs().max() < 0.02
+    q1 = torch.empty_like(q)
+    pool1 = torch.zeros_like(pool)
+    basic.rope_kvstore(qkv.clone(), hq, hkv, hd, inv, tok_pos, seq, bt, pool1, q1, rope_pos=pos3[0].contiguous())
+    assert torch.equal(q1[:3], q[:3]) and torch.equal(pool1[0, 0, :, :3], pool[0, 0, :, :3])
