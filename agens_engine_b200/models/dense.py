@@ -242,6 +242,47 @@ class DenseModel:
         self.seq_len_host[seq] = n
         self.seq_len[seq] = n
 
+    def save_session(self, seq: int, path: str, tokens: Optional[List[int]] = None):
+        """Writes the KV rows (and optionally the token history) of ``seq`` to a safetensors file so that a conversation
+        survives a restart of the engine (reference: session blob, m1_model.cu snapshot / restore, serve.rs:616-760).
+        The sequence stays where it is."""
+        from ..utils import checkpoint as K
+        n = self.seq_len_host[seq]
+        used = (n + self.cfg.page_size - 1) // self.cfg.page_size
+        idx = torch.tensor(self.seq_pages[seq][:used], dtype=torch.long, device=self.dev)
+        kv = torch.stack([layer.index_select(0, idx) for layer in self.kv]).cpu()
+        meta = {"format": "b200e-session-1", "len": str(n), "n_layers": str(self.cfg.n_layers), "n_kv_heads": str(self.cfg.n_kv_heads),
+                "head_dim": str(self.cfg.head_dim), "page_size": str(self.cfg.page_size)}
+        t = {"kv": kv, "len": torch.tensor([n], dtype=torch.int32)}
+        if tokens is not None:
+            t["tokens"] = torch.tensor(list(tokens), dtype=torch.int32)
+        K.write_safetensors(path, t, metadata=meta)
+
+    def load_session(self, seq: int, path: str) -> List[int]:
+        """Restores a file written by :meth:`save_session` into the free slot ``seq``; returns the stored tokens."""
+        from ..utils import checkpoint as K
+        f = K.SafeTensorsFile(path)
+        kv = f.tensor("kv").clone()
+        toks = f.tensor("tokens").tolist() if "tokens" in f.keys() else []
+        n = int(f.tensor("len")[0])
+        f.close()
+        want = (self.cfg.n_layers, (n + self.cfg.page_size - 1) // self.cfg.page_size, 2, self.cfg.n_kv_heads, self.cfg.page_size, self.cfg.head_dim)
+        if tuple(kv.shape) != want:
+            raise ValueError(f"session file does not match this model: {tuple(kv.shape)} vs {want}")
+        self.unpark(seq, {"len": n, "kv": kv.pin_memory()})
+        return toks
+
+    def recover(self):
+        """After a device-side error status (bounded wait expired, bounds check): drop every sequence, clear the status
+        words and the self-resetting counters, forget captured graphs.  Weights stay loaded (reference: ak_m1_recover)."""
+        torch.cuda.synchronize(self.dev)
+        for s in list(self.seq_pages):
+            self.free_seq(s)
+        self.status.zero_()
+        self.ws.status.zero_()
+        self.ws.counters.zero_()
+        self._graphs.clear()
+
     # ------------------------------------------------------------------------------------------------ small-m forward
     def _layers_small(self, m: int, n_groups: int):
         """Layers of one step for m <= 32 token rows already described by tok_pos / tok_seq / grp_*; h_a and ss_a

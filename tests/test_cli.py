@@ -52,3 +52,17 @@ def test_cli_gates_gpu(capsys):
     assert rc == 0, out
     rc, out = _run(capsys, ["load"] + base)
     assert rc == 0 and json.loads(out)["tp"] == 1
+
+
+def test_compare_tools(tmp_path):
+    import torch
+    from agens_engine_b200.tools import compare as T
+    a = torch.randn(4, 100)
+    torch.save(a, tmp_path / "a.pt"); torch.save(a + 1e-4 * torch.randn(4, 100), tmp_path / "b.pt")
+    rep = T.compare_logits(str(tmp_path / "a.pt"), str(tmp_path / "b.pt"))
+    assert rep["top1_agreement"] == 1.0 and rep["mean_kl"] < 1e-6
+    (tmp_path / "x.json").write_text(json.dumps([1, 2, 3, 4]))
+    (tmp_path / "y.json").write_text(json.dumps({"tokens": [1, 2, 9, 4]}))
+    rep = T.compare_tokens(str(tmp_path / "x.json"), str(tmp_path / "y.json"))
+    assert not rep["equal"] and rep["first_difference"] == 2 and rep["agreement"] == 0.75
+    assert T.main(["tokens", str(tmp_path / "x.json"), str(tmp_path / "x.json")]) == 0

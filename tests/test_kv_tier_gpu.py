@@ -48,3 +48,31 @@ def test_tiered_kv_is_bit_identical():
     assert torch.equal(a, b)
     m1.free_seq(0)
     assert m1.free_pages() == m1.n_pages and 0 not in tier.blocks
+
+
+def test_session_file_round_trip_and_recover(tmp_path):
+    cfg = C.oracle_tiny()
+    ow = O.random_weights(cfg, seed=0)
+    torch.manual_seed(22)
+    prompt = torch.randint(0, cfg.vocab, (50,))
+    m = DenseModel.from_oracle(ow, max_seqs=2, max_ctx=256)
+    m.new_seq(0)
+    first, _ = m.prefill(0, prompt)
+    path = str(tmp_path / "session.safetensors")
+    m.save_session(0, path, tokens=prompt.tolist() + [first])
+    ref, tok = [], first
+    for _ in range(10):
+        out, _ = m.forward_rows([tok], [0]); tok = int(out[0]); ref.append(tok)
+    # a fresh engine instance resumes the conversation from the file
+    m2 = DenseModel.from_oracle(ow, max_seqs=2, max_ctx=256)
+    toks = m2.load_session(1, path)
+    assert toks == prompt.tolist() + [first] and m2.seq_len_host[1] == 50
+    got, tok = [], toks[-1]
+    for _ in range(10):
+        out, _ = m2.forward_rows([tok], [1]); tok = int(out[0]); got.append(tok)
+    assert got == ref
+    m2.status.fill_(3)
+    m2.recover()
+    assert int(m2.status.item()) == 0 and m2.free_pages() == m2.n_pages and not m2.seq_pages
+    m2.new_seq(0)
+    assert m2.prefill(0, prompt)[0] == first
