@@ -17,7 +17,7 @@ import torch
 import torch.distributed as dist
 
 _FORWARDED = ("new_seq", "free_seq", "reserve", "truncate", "fork", "forward_rows", "prefill",
-              "decode_setup", "decode_steps")
+              "decode_setup", "decode_steps", "set_linear_path", "recover")
 
 
 class TpDriver:

@@ -126,6 +126,19 @@ class TpDenseModel(DenseModel):
             from ..ops import basic
             basic.sumsq(out, ss_out)
             return 1
+        m = x.shape[0]
+        if m >= (self.ws.mm_min_rows or L.MM_MIN_ROWS):
+            # More rows than the GEMV family serves well: partial rows from the tensor-core GEMM, summed over the ranks by
+            # the push all-reduce kernel (rank order, bounded waits), then residual add and the next norm's statistic.
+            part = L.mm(lin, x, self.ws, epi=_lib.EPI_F32)
+            rows_per = max(1, self._gather_inbox.slot_stride // lin.n)
+            for r0 in range(0, m, rows_per):
+                r1 = min(m, r0 + rows_per)
+                part[r0:r1] = self._gather.all_reduce(part[r0:r1].reshape(-1)).view(r1 - r0, lin.n)
+            out.copy_((part + resid.float()).to(torch.bfloat16))
+            from ..ops import basic
+            basic.sumsq(out, ss_out)
+            return 1
         prev = (site - 1) % self.n_sites
         tp = self.inbox.tp_push(site, prev, skip_push=(site == self.skip_push_site))
         L.gemv(lin, x, self.ws, epi=EPI_TP_RESID, resid=resid, out=out, ss_out=ss_out, tp=tp)
@@ -144,9 +157,10 @@ class TpDenseModel(DenseModel):
     def _combine_argmax(self, m: int, standalone: bool = False):
         lib = _lib.cuda_lib()
         self.out_ids[:m].add_(self.idx_off[:m])
-        if standalone and not self.use_nccl_decode:
-            # The static argmax slot is re-armed by the first row-parallel site of the next small-m pass; a prefill tail
-            # is not followed by one, so it exchanges the winners through the rotating gather inbox instead.
+        if (standalone or m >= (self.ws.mm_min_rows or L.MM_MIN_ROWS)) and not self.use_nccl_decode:
+            # The static argmax slot is re-armed by the first fused row-parallel site of the next small-m pass; a prefill
+            # tail, and steps on the tensor-core path (whose row-parallel linears do not use the static sites), are not
+            # followed by one, so they exchange the winners through the rotating gather inbox instead.
             n = (2 * m + 3) // 4 * 4
             x = torch.zeros(n, dtype=torch.float32, device=self.dev)
             x[:m] = self.out_val[:m]

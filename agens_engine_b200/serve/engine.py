@@ -88,7 +88,7 @@ class Engine:
         self.m, self.emit = model, emit
         self.max_batch = min(max_batch or model.max_seqs, model.max_seqs, M_GEMV)
         self.max_drafts = max_drafts
-        if invariant and getattr(model, "world", 1) == 1:
+        if invariant:
             # batch-invariant serving (the reference's server mode): every step uses the same linear kernel whatever the
             # number of rows, so a request's tokens do not depend on what else is running
             rows_cap = self.max_batch * (1 + max_drafts)

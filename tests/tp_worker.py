@@ -125,6 +125,17 @@ def main():
             together = serve(reqs)
             alone = [serve([r])[0] for r in reqs]
             assert together == alone, (together, alone)
+            # more than eight rows per step: the tensor-core GEMM + push all-reduce path, pinned for every step
+            def serve16(reqs):
+                got = {}
+                eng = Engine(drv, lambda rid, t, f, e: got.setdefault(rid, []).extend(t) or False, max_batch=4, max_drafts=3)
+                rids = [eng.submit(p, s) for p, s in reqs]
+                eng.run_until_idle(5000)
+                return [got[r] for r in rids]
+            t16 = serve16(reqs)
+            a16 = [serve16([r])[0] for r in reqs]
+            assert t16 == a16 and all(len(t) == 12 for t in t16), (t16, a16)
+            drv.set_linear_path(None)
             assert all(len(t) == 12 for t in together) and together[3] != together[0]
             blob = None
             drv.new_seq(0); drv.prefill(0, torch.tensor(prompts[0], dtype=torch.int32))
