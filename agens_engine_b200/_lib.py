@@ -129,6 +129,7 @@ class AttnDecodeArgs(C.Structure):
         ("n_tok", C.c_int),
         ("status", C.c_void_p),
         ("split_lo", C.c_int), ("split_hi", C.c_int), ("phase", C.c_int),
+        ("shared_kv", C.c_int),
     ]
 
 

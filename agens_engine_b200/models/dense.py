@@ -478,7 +478,8 @@ class DenseModel:
             basic.rope_kvstore(qkv, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, pos, seqv, self.block_table,
                                self.kv[li], q, status=self.status)
             if tiered:
-                a = self.tier.attend(li, q, pg0, pgc, pos, seqv, {seq: (0, pg0.numel())}, self.prefill_split, p_splits, p_o, p_ml, p_out)
+                a = self.tier.attend(li, q, pg0, pgc, pos, seqv, {seq: (0, pg0.numel())}, self.prefill_split, p_splits, p_o, p_ml, p_out,
+                                     shared_kv=True)
             else:
                 a = A.attn_prefill(q, self.kv[li], self.block_table, seq, pos0, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
                                    status=self.status, split_keys=self.prefill_split)

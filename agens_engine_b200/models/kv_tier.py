@@ -71,12 +71,12 @@ class HostKvTier:
 
     # ------------------------------------------------------------------------------------------------ attention
     def attend(self, layer: int, q, grp_tok0, grp_cnt, tok_pos, tok_seq, tiered_groups: Dict[int, tuple], split_keys: int,
-               max_splits: int, part_o, part_ml, out, tree_mask=None):
+               max_splits: int, part_o, part_ml, out, tree_mask=None, shared_kv: bool = False):
         """Attention of one layer for a step in which the sequences of ``tiered_groups`` (seq -> (first group, number
         of groups)) have pages on the host.  Resident splits first, then the staged batches, then one merge."""
         m, cfg = self.m, self.m.cfg
         common = dict(hq=cfg.n_heads, hkv=cfg.n_kv_heads, hd=cfg.head_dim, split_keys=split_keys, max_splits=max_splits,
-                      part_o=part_o, part_ml=part_ml, status=m.status, out=out, tree_mask=tree_mask)
+                      part_o=part_o, part_ml=part_ml, status=m.status, out=out, tree_mask=tree_mask, shared_kv=shared_kv)
         main = torch.cuda.current_stream(m.dev)
         A.attn_decode(q, m.kv[layer], m.block_table, grp_tok0, grp_cnt, tok_pos, tok_seq, phase=1, **common)
         spb = self.B * cfg.page_size // split_keys               # splits per batch

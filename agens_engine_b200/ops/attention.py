@@ -18,7 +18,7 @@ def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tenso
                 split_keys: int, max_splits: int, part_o: Optional[torch.Tensor] = None,
                 part_ml: Optional[torch.Tensor] = None, tree_mask: Optional[torch.Tensor] = None,
                 status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                split_range: Optional[tuple] = None, phase: int = 0) -> torch.Tensor:
+                split_range: Optional[tuple] = None, phase: int = 0, shared_kv: bool = False) -> torch.Tensor:
     """q: bf16 [n_tok, hq*hd] (RoPE applied); kv_pool: bf16 [pages, 2, hkv, 16, hd].  Returns bf16 [n_tok, hq*hd].
     ``split_range=(lo, hi)`` restricts the launch to those KV splits and ``phase`` selects the split kernel (1), the
     merge (2) or both (0): the pieces of a tiered-KV step."""
@@ -47,6 +47,7 @@ def attn_decode(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tenso
     a.status = ptr(status)
     a.split_lo, a.split_hi = split_range if split_range else (0, 0)
     a.phase = phase
+    a.shared_kv = 1 if shared_kv else 0     # CTA-shared K/V ring: same arithmetic per row, fewer loads for many-row groups
     with torch.cuda.device(dev):
         check(lib.b2_attn_decode(C.byref(a), hd, current_stream()), "b2_attn_decode")
     return out
@@ -68,4 +69,5 @@ def attn_prefill(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tens
     T = q.shape[0]
     g0, gc, pos, seqv = prefill_groups(T, pos0, seq, q.device)
     max_splits = (pos0 + T + split_keys - 1) // split_keys
-    return attn_decode(q, kv_pool, block_table, g0, gc, pos, seqv, hq, hkv, hd, split_keys, max_splits, status=status)
+    return attn_decode(q, kv_pool, block_table, g0, gc, pos, seqv, hq, hkv, hd, split_keys, max_splits, status=status,
+                       shared_kv=True)

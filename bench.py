@@ -112,11 +112,17 @@ def main():
                                        max_ctx=args.prompt + warmup + 2 * args.steps + 64, prefill_chunk=256)
     g = torch.Generator().manual_seed(1234)
     firsts = []
+    pre0, pre1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    pre0.record()
     for s in range(args.batch):
         prompt = torch.randint(0, cfg.vocab, (args.prompt,), generator=g)
         model.new_seq(s)
         first, _ = model.prefill(s, prompt)
         firsts.append(first)
+    pre1.record()
+    torch.cuda.synchronize()
+    prefill_ms = pre0.elapsed_time(pre1)        # untimed for the headline; reported as time to first token of the prompt
     seqs = list(range(args.batch))
     total_steps = warmup + 2 * args.steps
     model.decode_setup(seqs, firsts, total_steps)
@@ -177,6 +183,8 @@ def main():
             "e2e": {"value": round(toks / (e2e_ms / 1e3), 2), "unit": "tok/s", "h2d_bytes_per_step": 4 * args.batch,
                     "d2h_bytes_per_step": 4 * args.batch},
             "gpu_launches": model.launches_per_step(args.batch) * args.steps,
+            "prefill": {"tokens": args.prompt * args.batch, "ms": round(prefill_ms, 1),
+                        "tok_s": round(args.prompt * args.batch / (prefill_ms / 1e3), 1), "note": "first call includes one-time set-up"},
             "clocks": clocks, "device_status": status, "impl": "ours",
         }
         if args.layers:

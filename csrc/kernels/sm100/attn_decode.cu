@@ -35,6 +35,9 @@ struct AttnDecodeArgs {
   // resident on the GPU, page batches staged from pinned host memory -- land in their own split slots and are merged
   // once, in split order, so the result is bit-identical to an all-resident run.
   int split_lo, split_hi, phase;
+  // 1: the four warps of a CTA take the four 16-row tiles of one (group, kv head, split) and share one K/V ring in
+  // shared memory (prefill chunks and verify blocks, where a group has many rows); 0: every warp is its own item.
+  int shared_kv;
 };
 
 namespace {
@@ -63,7 +66,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 
 }  // namespace
 
-template <int HD>
+template <int HD, bool SHARED>
 __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a) {
   constexpr int KS = HD / 16;          // k-steps of QK^T
   constexpr int NTO = HD / 8;          // n-tiles of O
@@ -78,17 +81,19 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
 
   const int gq = a.hq / a.hkv;
   // decode the work item
-  long item = (long)blockIdx.x * 4 + warp;
   const int s_lo = a.split_hi > 0 ? a.split_lo : 0;
   const int s_n = a.split_hi > 0 ? a.split_hi - a.split_lo : a.max_splits;
-  const int split = s_lo + (int)(item % s_n); item /= s_n;
   const int mt_max = (8 * gq + 15) / 16;             // tiles needed for the largest group (8 tokens)
-  const int mtile = (int)(item % mt_max); item /= mt_max;
+  long item = SHARED ? (long)blockIdx.x : (long)blockIdx.x * 4 + warp;
+  const int split = s_lo + (int)(item % s_n); item /= s_n;
+  int mtile;
+  if (SHARED) mtile = warp; else { mtile = (int)(item % mt_max); item /= mt_max; }
   const int kvh = (int)(item % a.hkv); item /= a.hkv;
   const int grp = (int)item;
-  if (grp >= a.n_groups) return;
+  if (grp >= a.n_groups) return;                      // uniform over the CTA when SHARED
   const int tok0 = a.grp_tok0[grp], cnt = a.grp_cnt[grp];
-  if (mtile * 16 >= cnt * gq) return;
+  const bool tile_ok = mtile * 16 < cnt * gq;
+  if (!SHARED && !tile_ok) return;
   const int seq = a.tok_seq[tok0];
   const int pos_first = a.tok_pos[tok0];
   const int kv_len = a.tok_pos[tok0 + cnt - 1] + 1;
@@ -105,14 +110,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
   for (int i = 0; i < 2; ++i) {
     const int R = mtile * 16 + g + 8 * i;
     const int tl = R / gq;
-    rvalid[i] = tl < cnt;
+    rvalid[i] = tile_ok && tl < cnt;
     rtok[i] = tok0 + (rvalid[i] ? tl : 0);
     rhead[i] = kvh * gq + (R % gq);
     rpos[i] = rvalid[i] ? a.tok_pos[rtok[i]] : -1;
     rmask[i] = (a.tree_mask && rvalid[i]) ? a.tree_mask[rtok[i]] : 0xffffffffu;
   }
 
-  uint8_t* wsm = smem + (size_t)warp * kStages * 2 * PAGE_B;
+  uint8_t* wsm = smem + (SHARED ? (size_t)0 : (size_t)warp * kStages * 2 * PAGE_B);
   const uint32_t wsm_u = smem_u32(wsm);
   const int* bt = a.block_table + (size_t)seq * a.bt_ld;
   if (bt[k_begin / kPage] == -2) return;   // split lives in the host tier: a staged launch fills its slot
@@ -125,7 +130,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
     const uint8_t* vp = reinterpret_cast<const uint8_t*>(a.kv_pool) + (((size_t)page * 2 + 1) * a.hkv + kvh) * PAGE_B;
     const uint32_t ks = wsm_u + stage * 2 * PAGE_B, vs = ks + PAGE_B;
 #pragma unroll
-    for (int c = lane; c < kPage * CPR; c += 32) {
+    for (int c = SHARED ? (int)threadIdx.x : lane; c < kPage * CPR; c += SHARED ? 128 : 32) {
       const int row = c / CPR, cc = c % CPR;
       const uint32_t off = row * ROWB + ((cc ^ (row & 7)) << 4);
       cp_async16(ks + off, kp + (size_t)c * 16);
@@ -168,7 +173,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
     if (pi + kStages - 1 < n_pg) issue_page(pi + kStages - 1);
     cp_async_commit();
     cp_async_wait<kStages - 1>();
-    __syncwarp();
+    if (SHARED) __syncthreads(); else __syncwarp();
     const int stage = pi % kStages;
     const uint32_t ks_u = wsm_u + stage * 2 * PAGE_B, vs_u = ks_u + PAGE_B;
     float s[2][4];
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
       mma_bf16_16816(o[2 * nn], pa, b[0], b[1]);
       mma_bf16_16816(o[2 * nn + 1], pa, b[2], b[3]);
     }
-    __syncwarp();
+    if (SHARED) __syncthreads(); else __syncwarp();
   }
   cp_async_wait<0>();
 
@@ -319,6 +324,7 @@ __global__ void attn_merge_kernel(const AttnDecodeArgs a) {
 using namespace b2;
 
 B2_API int b2_attn_decode_smem_bytes(int hd) { return 4 * kStages * 2 * kPage * hd * 2; }
+static int attn_shared_smem_bytes(int hd) { return kStages * 2 * kPage * hd * 2; }
 
 // Launches the split kernel and the merge kernel.  `max_groups_tiles` is not needed: the grid covers
 // n_groups x hkv x tiles(8 tokens) x max_splits warp items.
@@ -330,10 +336,11 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* args, int hd, cudaStream_t st) {
   const int mt_max = (8 * gq + 15) / 16;
   if (a.split_hi > 0 && (a.split_lo < 0 || a.split_hi <= a.split_lo || a.split_hi > a.max_splits)) return B2_ERR_ARG;
   const int s_n = a.split_hi > 0 ? a.split_hi - a.split_lo : a.max_splits;
-  const long items = (long)a.n_groups * a.hkv * mt_max * s_n;
+  const bool shared = a.shared_kv != 0 && mt_max <= 4;     // four warps = at most four row tiles per group
+  const long items = shared ? (long)a.n_groups * a.hkv * s_n : (long)a.n_groups * a.hkv * mt_max * s_n;
   const bool run_split = a.phase == 0 || (a.phase & 1), run_merge = a.phase == 0 || (a.phase & 2);
-  const int grid = (int)((items + 3) / 4);
-  const size_t smem = (size_t)b2_attn_decode_smem_bytes(hd);
+  const int grid = shared ? (int)items : (int)((items + 3) / 4);
+  const size_t smem = shared ? (size_t)attn_shared_smem_bytes(hd) : (size_t)b2_attn_decode_smem_bytes(hd);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid); cfg.blockDim = dim3(128); cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
@@ -341,14 +348,20 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* args, int hd, cudaStream_t st) {
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
   cudaError_t e = cudaSuccess;
-  static bool attr128 = false, attr64 = false;
+  static bool attr_set = false;
+  if (!attr_set) {
+    const int big = b2_attn_decode_smem_bytes(128);
+    cudaFuncSetAttribute(attn_decode_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attn_decode_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attn_decode_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    cudaFuncSetAttribute(attn_decode_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, big);
+    attr_set = true;
+  }
   if (!run_split) {
   } else if (hd == 128) {
-    if (!attr128) { cudaFuncSetAttribute(attn_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr128 = true; }
-    e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<128>, a);
+    e = shared ? cudaLaunchKernelEx(&cfg, attn_decode_kernel<128, true>, a) : cudaLaunchKernelEx(&cfg, attn_decode_kernel<128, false>, a);
   } else {
-    if (!attr64) { cudaFuncSetAttribute(attn_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); attr64 = true; }
-    e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<64>, a);
+    e = shared ? cudaLaunchKernelEx(&cfg, attn_decode_kernel<64, true>, a) : cudaLaunchKernelEx(&cfg, attn_decode_kernel<64, false>, a);
   }
   if (e != cudaSuccess) return B2_ERR_LAUNCH;
   if (!run_merge) return B2_OK;

@@ -158,3 +158,22 @@ def test_multi_axis_rope_matches_reference():
     pool1 = torch.zeros_like(pool)
     basic.rope_kvstore(qkv.clone(), hq, hkv, hd, inv, tok_pos, seq, bt, pool1, q1, rope_pos=pos3[0].contiguous())
     assert torch.equal(q1[:3], q[:3]) and torch.equal(pool1[0, 0, :, :3], pool[0, 0, :, :3])
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(16, 2, 128), (4, 2, 64)])
+def test_shared_kv_ring_is_bit_identical(hq, hkv, hd):
+    """The CTA-shared K/V ring (prefill, verify blocks) gives exactly the rows of the per-warp kernel."""
+    from agens_engine_b200.ops import attention as A
+    torch.manual_seed(6)
+    dev = "cuda:0"
+    T, pos0, n_pages = 77, 130, 32
+    pool = torch.randn(n_pages, 2, hkv, 16, hd, device=dev).to(torch.bfloat16)
+    bt = torch.randperm(n_pages, device=dev).to(torch.int32)[None, :]
+    q = torch.randn(T, hq * hd, device=dev).to(torch.bfloat16)
+    g0, gc, pos, seqv = A.prefill_groups(T, pos0, 0, dev)
+    splits = (pos0 + T + 63) // 64
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    a = A.attn_decode(q, pool, bt, g0, gc, pos, seqv, hq, hkv, hd, 64, splits, status=st, shared_kv=False)
+    b = A.attn_decode(q, pool, bt, g0, gc, pos, seqv, hq, hkv, hd, 64, splits, status=st, shared_kv=True)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0 and torch.equal(a, b)
