@@ -414,6 +414,14 @@ class DenseModel:
         from ..ops import gemm as G
         return G.wq_linear(lin, x, self)
 
+    def _prefill_split_for(self, kv_len: int) -> int:
+        """KV split size of a prefill chunk: the base size, doubled until at most 64 splits cover the context (keeps the
+        partial-result buffers bounded at long context)."""
+        s = self.prefill_split
+        while (kv_len + s - 1) // s > 64:
+            s *= 2
+        return s
+
     def prefill(self, seq: int, ids: torch.Tensor, want_logits: bool = False, image_rows: Optional[torch.Tensor] = None,
                 image_pad_id: Optional[int] = None):
         """Chunked prefill of ``ids`` (1-D int tensor) appended to ``seq``; returns the greedy next token (int).
@@ -482,7 +490,7 @@ class DenseModel:
                                      shared_kv=True)
             else:
                 a = A.attn_prefill(q, self.kv[li], self.block_table, seq, pos0, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
-                                   status=self.status, split_keys=self.prefill_split)
+                                   status=self.status, split_keys=self._prefill_split_for(pos0 + T))
             o = self._reduce_rows(self._linear_big(d["o"], a))
             x, h = basic.rmsnorm(o, d["ln2"], cfg.rms_eps, resid=h)
             gu = self._linear_big(d["gate_up"], x)

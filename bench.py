@@ -82,6 +82,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (the result is then not the named config)")
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--prefill-chunk", type=int, default=2048)
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
@@ -105,11 +106,11 @@ def main():
     if world > 1:
         from agens_engine_b200.parallel.tp_model import TpDenseModel
         model = TpDenseModel.random_init(cfg, dev, seed=0, rank=rank, world=world, max_seqs=args.batch,
-                                         max_ctx=args.prompt + warmup + 2 * args.steps + 64)
+                                         max_ctx=args.prompt + warmup + 2 * args.steps + 64, prefill_chunk=args.prefill_chunk)
     else:
         from agens_engine_b200.models.dense import DenseModel
         model = DenseModel.random_init(cfg, dev, seed=0, max_seqs=args.batch,
-                                       max_ctx=args.prompt + warmup + 2 * args.steps + 64, prefill_chunk=256)
+                                       max_ctx=args.prompt + warmup + 2 * args.steps + 64, prefill_chunk=args.prefill_chunk)
     g = torch.Generator().manual_seed(1234)
     firsts = []
     pre0, pre1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
