@@ -231,9 +231,52 @@ def profile_mm(args):
     print("profile_mm done", int(ws.status.item()))
 
 
+def _attn_case(ctx: int, rows: int, dev, hq=64, hkv=8, hd=128):
+    from .ops import attention as A
+    n_pages = (ctx + rows + 15) // 16 + 1
+    pool = torch.randn(n_pages, 2, hkv, 16, hd, device=dev).to(torch.bfloat16)
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev)[None, :]
+    q = torch.randn(rows, hq * hd, device=dev).to(torch.bfloat16)
+    g0, gc, pos, seqv = A.prefill_groups(rows, ctx, 0, dev)
+    return A, pool, bt, q, g0, gc, pos, seqv
+
+
+def bench_attn(args):
+    """Paged attention of the 32B shape (64 q / 8 kv heads x 128): one decode row, an 8-row verify block and a 256-row
+    prefill chunk (per-warp and CTA-shared K/V ring) at several context lengths; CUDA events, L2 flushed."""
+    dev = "cuda:0"
+    pk = peaks()
+    flush = L2Flusher(dev)
+    for ctx in ([2560] if args.small else [2560, 8192, 32768]):
+        for rows, split, shared in ((1, 64, False), (8, 64, False), (256, 256, False), (256, 256, True)):
+            A, pool, bt, q, g0, gc, pos, seqv = _attn_case(ctx, rows, dev)
+            splits = (ctx + rows + split - 1) // split
+            po = torch.empty(rows, 64, splits, 128, dtype=torch.float32, device=dev)
+            pm = torch.empty(rows, 64, splits, 2, dtype=torch.float32, device=dev)
+            out = torch.empty(rows, 64 * 128, dtype=torch.bfloat16, device=dev)
+            fn = lambda: A.attn_decode(q, pool, bt, g0, gc, pos, seqv, 64, 8, 128, split, splits, part_o=po, part_ml=pm, out=out,
+                                       shared_kv=shared)
+            med, _ = time_cuda(fn, iters=10, warmup=3, flush=flush)
+            kv_bytes = 2 * 8 * 128 * 2 * (ctx + rows)
+            print(json.dumps(dict(ctx=ctx, rows=rows, split_keys=split, shared_kv=shared, us=round(med, 1),
+                                  kv_gbs=round(kv_bytes / med / 1e3, 1), frac_hbm_single_read=round(kv_bytes / med / 1e3 / pk["hbm_gbs"], 3),
+                                  tflops=round(4.0 * rows * 64 * 128 * (ctx + rows / 2) / med / 1e6, 1))), flush=True)
+    print(json.dumps({"peaks": pk, "timing": "CUDA events, median of 10, L2 flushed; split kernel + merge kernel"}))
+
+
+def profile_attn(args):
+    """A few plain launches (256-row prefill chunk at an 8K context, CTA-shared ring) for a profiler capture."""
+    dev = "cuda:0"
+    A, pool, bt, q, g0, gc, pos, seqv = _attn_case(8192, 256, dev)
+    for _ in range(3):
+        A.attn_decode(q, pool, bt, g0, gc, pos, seqv, 64, 8, 128, 256, (8192 + 256 + 255) // 256, shared_kv=True)
+    torch.cuda.synchronize()
+    print("profile_attn done")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm"])
+    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--ks", type=int, default=0)
     ap.add_argument("--m", type=int, default=1)
@@ -251,6 +294,10 @@ def main(argv=None):
         bench_mm(args)
     elif args.what == "profile_mm":
         profile_mm(args)
+    elif args.what == "attn":
+        bench_attn(args)
+    elif args.what == "profile_attn":
+        profile_attn(args)
     else:
         raise SystemExit(f"{args.what}: not available yet")
 
