@@ -129,10 +129,13 @@ class DenseModel:
         lib = _lib.cuda_lib()
         lins = [self.lm_head] + [d[lin] for d in self.layers[:1] for lin in LINEARS]
         need = max(lib.b2_wq_gemv_scratch_floats(x.n, x.k, x.ks, r, M_GEMV) for x in lins for r in (2, x.rb))
+        # the tensor-core path's split-k partials at its largest row count, so that the scratch never moves afterwards
+        need = max(need, max(lib.b2_wq_mm_scratch_floats(x.n, x.k, 256) for x in lins))
         panels = max(x.n_panels() for x in lins)
         keep = self.ws.mm_min_rows
         self.ws = L.GemvWorkspace(self.dev, floats=max(need, 1 << 16), panels=max(panels, 1 << 10))
         self.ws.mm_min_rows = keep
+        self.ws.x16_buffer(32, 128)          # allocate the staging buffer now, outside any graph capture
         return self
 
     def set_linear_path(self, mm_min_rows: Optional[int]):

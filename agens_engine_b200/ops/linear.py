@@ -124,8 +124,10 @@ class GemvWorkspace:
         self.mm_min_rows = None      # overrides MM_MIN_ROWS for the launches that use this workspace
 
     def x16_buffer(self, n_pad: int, k: int) -> torch.Tensor:
+        """fp16 activation staging of the tensor-core path.  Sized once for 256 rows x 32768 inputs so that its address
+        stays valid inside captured CUDA graphs; only a wider linear makes it grow (which invalidates such graphs)."""
         if self.x16 is None or self.x16.numel() < n_pad * k:
-            self.x16 = torch.empty(max(n_pad * k, 32 * 25600), dtype=torch.float16, device=self.scratch.device)
+            self.x16 = torch.empty(max(n_pad * k, 256 * 32768), dtype=torch.float16, device=self.scratch.device)
         return self.x16
 
     def ensure_scratch(self, floats: int):

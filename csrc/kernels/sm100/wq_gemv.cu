@@ -688,7 +688,11 @@ B2_API int b2_wq_gemv_vworkers(int n, int k, int ks, int rb) {
   const long U = nitems * (k / 128 / ks);
   long V = (long)(kVirtualCtas / ks) * kGemvWarps;
   if (V < 1) V = 1;
-  if (V > U) V = U;
+  // Small matrices: a worker owns at least kMinUnits (item, batch) units, so an item is cut into fewer fragments and
+  // the hand-off (scratch round trip + ordered sum by the last arriver) stays short.  Shape-only, like everything here.
+  static const long kMinUnits = [] { const char* e = getenv("B200E_GEMV_MIN_UNITS"); return e ? atol(e) : 4L; }();
+  if (V > U / kMinUnits) V = U / kMinUnits;
+  if (V < 1) V = 1;
   return (int)V;
 }
 B2_API int b2_wq_gemv_fmax(int n, int k, int ks, int rb) {
