@@ -326,7 +326,8 @@ def cmd_serve(ns):
         D.launch([a for a in sys.argv], cfg.tp)
     if cfg.mode == "personal":
         cfg.max_batch = 1
-    m, rank, world, ctrl = build_model(cfg)
+    # slots beyond the running batch hold finished conversations and prompt-prefix snapshots
+    m, rank, world, ctrl = build_model(cfg, max_seqs=max(cfg.max_batch, 1) + max(0, min(cfg.max_convs, 64)))
     if rank == 0:
         print("config: " + json.dumps(dataclasses.asdict(cfg)), flush=True)
     if world > 1 and rank > 0:
@@ -364,8 +365,13 @@ def cmd_serve(ns):
     eos = gen_cfg.get("eos_token_id", [])
     srv = Server(tok_path, model_name=cfg.served_model_name, generation_config=gen_cfg,
                  eos_token_ids=eos if isinstance(eos, list) else [eos], max_tokens_default=cfg.max_tokens_default)
+    # ids the tokenizer does not know (padding rows of the embedding) are never produced
+    tj = json.load(open(tok_path))
+    n_tok = 1 + max([max(tj["model"]["vocab"].values(), default=0)] + [int(t["id"]) for t in tj.get("added_tokens", [])])
+    full = m.full_cfg if world > 1 else m.cfg
+    full.vocab_valid = min(full.vocab_valid or full.vocab, n_tok)
     eng = Engine(model, lambda *a: False, sources_factory=(lambda: sources) if sources else None,
-                 max_drafts=cfg.draft_depth if sources else 0, max_batch=cfg.max_batch)
+                 max_drafts=cfg.draft_depth if sources else 0, max_batch=cfg.max_batch, keep_sequences=world == 1)
     attach_to_server(eng, srv, context_length=m.max_ctx)
     eng.start()
     port = srv.start(cfg.host, cfg.port)

@@ -252,10 +252,36 @@ static size_t complete_utf8_prefix(const std::string& s) {
   }
   return n;
 }
+// Replaces every byte that is not part of a well-formed UTF-8 sequence by U+FFFD (what a lossy decode does), so that
+// the text can always travel inside JSON.  A model may emit byte tokens in any order.
+static std::string sanitize_utf8(const std::string& s) {
+  std::string out;
+  out.reserve(s.size());
+  size_t i = 0;
+  while (i < s.size()) {
+    const unsigned char c = (unsigned char)s[i];
+    int need = c < 0x80 ? 0 : ((c & 0xE0) == 0xC0 && c >= 0xC2 ? 1 : ((c & 0xF0) == 0xE0 ? 2 : ((c & 0xF8) == 0xF0 && c <= 0xF4 ? 3 : -1)));
+    bool ok = need >= 0 && i + (size_t)need < s.size();
+    if (ok)
+      for (int j = 1; j <= need; ++j)
+        if (((unsigned char)s[i + j] & 0xC0) != 0x80) { ok = false; break; }
+    if (ok && need == 2) {
+      const unsigned char c1 = (unsigned char)s[i + 1];
+      if ((c == 0xE0 && c1 < 0xA0) || (c == 0xED && c1 >= 0xA0)) ok = false;      // overlong, surrogates
+    }
+    if (ok && need == 3) {
+      const unsigned char c1 = (unsigned char)s[i + 1];
+      if ((c == 0xF0 && c1 < 0x90) || (c == 0xF4 && c1 >= 0x90)) ok = false;
+    }
+    if (ok) { out.append(s, i, (size_t)need + 1); i += (size_t)need + 1; }
+    else { out += "\xEF\xBF\xBD"; ++i; }
+  }
+  return out;
+}
 std::string Detokenizer::push(const std::vector<int>& ids) {
   for (int id : ids) { if (skip_special_ && tk_->is_special(id)) continue; pending_ += tk_->token_bytes(id); }
   const size_t k = complete_utf8_prefix(pending_);
-  std::string out = pending_.substr(0, k);
+  std::string out = sanitize_utf8(pending_.substr(0, k));
   pending_.erase(0, k);
   return out;
 }

@@ -66,3 +66,54 @@ def test_compare_tools(tmp_path):
     rep = T.compare_tokens(str(tmp_path / "x.json"), str(tmp_path / "y.json"))
     assert not rep["equal"] and rep["first_difference"] == 2 and rep["agreement"] == 0.75
     assert T.main(["tokens", str(tmp_path / "x.json"), str(tmp_path / "x.json")]) == 0
+
+
+@pytest.mark.gpu
+def test_cli_serve_over_http(tmp_path):
+    """`serve` end to end: the process loads a model, listens, answers OpenAI requests (plain and streamed)."""
+    import os
+    import subprocess
+    import sys
+    import time
+    import urllib.request
+    from tests.fixtures import tiny_tokenizer_json
+    tok = tmp_path / "tokenizer.json"
+    tok.write_text(tiny_tokenizer_json())
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    log = open(tmp_path / "serve.log", "w")
+    p = subprocess.Popen([sys.executable, "-u", "-m", "agens_engine_b200", "serve", "--random", "oracle-tiny", "--tokenizer", str(tok),
+                          "--port", "0", "--wctx", "512", "--max-batch", "4", "--spec-copy", "1", "--served-model-name", "tiny"],
+                         cwd=root, stdout=log, stderr=subprocess.STDOUT)
+    try:
+        port = None
+        for _ in range(240):
+            time.sleep(0.5)
+            txt = open(tmp_path / "serve.log").read()
+            if "serving tiny on http://" in txt:
+                port = int(txt.split("serving tiny on http://127.0.0.1:")[1].split()[0])
+                break
+            assert p.poll() is None, txt[-2000:]
+        assert port, open(tmp_path / "serve.log").read()[-2000:]
+
+        def post(path, body):
+            req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=json.dumps(body).encode(),
+                                         headers={"Content-Type": "application/json"})
+            with urllib.request.urlopen(req, timeout=60) as r:
+                return r.status, r.read().decode()
+
+        st, txt = post("/v1/chat/completions", {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
+                                                "max_tokens": 10, "temperature": 0})
+        assert st == 200 and json.loads(txt)["usage"]["completion_tokens"] == 10
+        st, txt2 = post("/v1/chat/completions", {"model": "tiny", "messages": [{"role": "user", "content": "hello there"}],
+                                                 "max_tokens": 10, "temperature": 0})
+        assert json.loads(txt2)["choices"][0]["message"] == json.loads(txt)["choices"][0]["message"]
+        st, sse = post("/v1/completions", {"model": "tiny", "prompt": "in the", "max_tokens": 6, "stream": True})
+        assert st == 200 and sse.strip().endswith("data: [DONE]") and sse.count("data: ") >= 3
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=10) as r:
+            assert "tiny" in r.read().decode()
+    finally:
+        p.terminate()
+        try:
+            p.wait(timeout=20)
+        except subprocess.TimeoutExpired:
+            p.kill()

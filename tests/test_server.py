@@ -191,3 +191,17 @@ def test_engine_callback_backend_and_socket(tok_path, tok_text):
     text = "".join(e["choices"][0]["delta"].get("content", "") for e in events if e["choices"])
     assert text == "hello world" and payload.decode().endswith("data: [DONE]\n\n")
     assert seen["prompt"] == tk.encode(S.render_chat([{"role": "user", "content": "hi"}]))
+
+
+def test_detokenizer_never_emits_invalid_utf8():
+    """Byte tokens in an order that is not UTF-8 (a model may produce them) come out as U+FFFD, never as raw bytes."""
+    import json as _json
+    from tests.fixtures import bytes_to_unicode, tiny_tokenizer_json
+    tj = tiny_tokenizer_json()
+    vocab, b2u = _json.loads(tj)["model"]["vocab"], bytes_to_unicode()
+    tk = S.Tokenizer(tj)
+    ids = [vocab[b2u[b]] for b in (0xB5, ord("a"), 0xE2, ord("b"), 0xC3, 0xA9, 0xF0, 0x9F)]
+    pieces = tk.stream_decode(ids, 1)
+    text = "".join(pieces)
+    assert text == "�a�bé�"
+    assert tk.stream_decode(tk.encode("héllo ✓ wörld"), 2)[-1] == "" and "".join(tk.stream_decode(tk.encode("héllo ✓ wörld"), 2)) == "héllo ✓ wörld"
