@@ -28,7 +28,7 @@ def reference_arm(args):
     print(json.dumps({
         "impl": "reference",
         "unavailable": "reference is a Rust/CUDA project (no setup.py/pyproject; cargo and rustc absent, crates need "
-                       "the network): `pip install --target baseline/_ref /root/reference` fails with 'not installable'",
+                       "the network): `pip install --target baseline/_ref <reference>` fails with 'not installable'",
     }))
     return 0
 

@@ -1,5 +1,5 @@
 """End-to-end gates on the GPU: the engine on the CPU-oracle plumbing config reproduces the oracle's greedy tokens
-and logits; decode rows are batch invariant (reference gates: m1 x2 identical, m1-batch, m1-spec; SURVEY of
+and logits; decode rows are batch invariant (reference gates: m1 x2 identical, m1-batch, m1-spec;
 crates/agens-cli/src/m1.rs:159-289, batch.rs)."""
 import pytest
 import torch
