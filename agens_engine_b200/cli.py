@@ -102,8 +102,10 @@ def build_model(cfg: EngineConfig, **kw):
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
         ctrl = D.control_group()
         if cfg.random is None:
-            raise SystemExit("tensor-parallel loading of checkpoints goes through --random or the Python API (from_oracle)")
-        m = TpDenseModel.random_init(_named_config(cfg.random), f"cuda:{local}", cfg.seed, rank, world, **kw)
+            from .utils import checkpoint as K
+            m = K.load_model(cfg.model_dir, f"cuda:{local}", rank=rank, world=world, **kw)
+        else:
+            m = TpDenseModel.random_init(_named_config(cfg.random), f"cuda:{local}", cfg.seed, rank, world, **kw)
         return m, rank, world, ctrl
     from .models.dense import DenseModel
     dev = f"cuda:{cfg.device}"

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes as C
 import hashlib
+import dataclasses
 import json
 import os
 import struct
@@ -203,11 +204,21 @@ def _get_linear(files, wm, name: str, n: int, k: int, fmt: dict) -> quant.QuantL
     return quant.QuantLinear(n, k, bits, group, codes, scale, zero)
 
 
-def load_model(dir_: str, device="cuda:0", **kw):
-    """Validates the directory, then builds a :class:`DenseModel` (q/k/v and gate/up merged, weights repacked to FM)."""
+@dataclasses.dataclass
+class CheckpointWeights:
+    """Quantised weights of a checkpoint in the merged form the models take (q/k/v as one ``qkv`` linear, gate/up
+    interleaved), all on the CPU; the same fields :class:`models.oracle.OracleWeights` offers to ``from_oracle``."""
+    cfg: object
+    embed: torch.Tensor
+    layers: list
+    final_norm: torch.Tensor
+    quant: dict
+
+
+def read_weights(dir_: str) -> CheckpointWeights:
+    """Validates the directory and reads every tensor (reference: m1::load weight loop with gate+up merge,
+    crates/agens-cli/src/m1.rs:452-1066)."""
     from ..models.config import ModelConfig
-    from ..models.dense import DenseModel
-    from ..ops import linear as L
     rep = validate(dir_)
     if not rep["ok"]:
         raise ValueError("invalid checkpoint: " + "; ".join(rep["errors"][:5]))
@@ -221,9 +232,9 @@ def load_model(dir_: str, device="cuda:0", **kw):
     files = {fn: SafeTensorsFile(os.path.join(dir_, fn)) for fn in set(wm.values())}
     fm = rep["linears"]
     cfg.group = next(iter(fm.values())).get("group", 128)
-    m = DenseModel(cfg, device, **kw)
     cat = lambda qs: quant.QuantLinear(sum(q.n for q in qs), qs[0].k, qs[0].bits, qs[0].group, torch.cat([q.codes for q in qs]),
                                        torch.cat([q.scale for q in qs]), torch.cat([q.zero for q in qs]))
+    layers, qd = [], {}
     for l in range(cfg.n_layers):
         p = f"model.layers.{l}."
         g = lambda nm, n, k: _get_linear(files, wm, p + nm, n, k, fm[p + nm])
@@ -233,19 +244,31 @@ def load_model(dir_: str, device="cuda:0", **kw):
         gate, up = g("mlp.gate_proj", cfg.ffn, cfg.d_model), g("mlp.up_proj", cfg.ffn, cfg.d_model)
         if gate.bits != up.bits:
             raise ValueError(f"layer {l}: gate/up use different bit widths")
-        gu = quant.QuantLinear(2 * cfg.ffn, cfg.d_model, gate.bits, gate.group,
-                               quant.interleave_gate_up(gate.codes, up.codes), quant.interleave_gate_up(gate.scale, up.scale),
-                               quant.interleave_gate_up(gate.zero, up.zero))
-        d = {"qkv": L.WqLinear.from_quant(cat([q, kk, v]), m.dev), "o": L.WqLinear.from_quant(g("self_attn.o_proj", cfg.d_model, cfg.q_dim), m.dev),
-             "gate_up": L.WqLinear.from_quant(gu, m.dev), "down": L.WqLinear.from_quant(g("mlp.down_proj", cfg.d_model, cfg.ffn), m.dev)}
-        T = lambda nm: files[wm[p + nm]].tensor(p + nm).clone().to(m.dev)
-        d["ln1"], d["ln2"] = T("input_layernorm.weight"), T("post_attention_layernorm.weight")
+        qd[f"{l}.qkv"] = cat([q, kk, v])
+        qd[f"{l}.o"] = g("self_attn.o_proj", cfg.d_model, cfg.q_dim)
+        qd[f"{l}.gate_up"] = quant.QuantLinear(2 * cfg.ffn, cfg.d_model, gate.bits, gate.group,
+                                               quant.interleave_gate_up(gate.codes, up.codes),
+                                               quant.interleave_gate_up(gate.scale, up.scale),
+                                               quant.interleave_gate_up(gate.zero, up.zero))
+        qd[f"{l}.down"] = g("mlp.down_proj", cfg.d_model, cfg.ffn)
+        T = lambda nm: files[wm[p + nm]].tensor(p + nm).clone()
+        layers.append({"ln1": T("input_layernorm.weight"), "ln2": T("post_attention_layernorm.weight")})
         for lin in ("qkv", "o", "gate_up", "down"):
-            cfg.bits[f"{l}.{lin}"] = d[lin].bits
-        m.layers.append(d)
-    m.embed = files[wm["model.embed_tokens.weight"]].tensor("model.embed_tokens.weight").clone().to(m.dev)
-    m.final_norm = files[wm["model.norm.weight"]].tensor("model.norm.weight").clone().to(m.dev)
-    m.lm_head = L.WqLinear.from_quant(_get_linear(files, wm, "lm_head", cfg.vocab, cfg.d_model, fm["lm_head"]), m.dev)
+            cfg.bits[f"{l}.{lin}"] = qd[f"{l}.{lin}"].bits
+    embed = files[wm["model.embed_tokens.weight"]].tensor("model.embed_tokens.weight").clone()
+    final_norm = files[wm["model.norm.weight"]].tensor("model.norm.weight").clone()
+    qd["lm_head"] = _get_linear(files, wm, "lm_head", cfg.vocab, cfg.d_model, fm["lm_head"])
+    cfg.lm_head_bits = qd["lm_head"].bits
     for f in files.values():
         f.close()
-    return m.finalize()
+    return CheckpointWeights(cfg, embed, layers, final_norm, qd)
+
+
+def load_model(dir_: str, device="cuda:0", rank: int = 0, world: int = 1, **kw):
+    """Builds a :class:`DenseModel` (or this rank's :class:`TpDenseModel` shard) from a checkpoint directory."""
+    w = read_weights(dir_)
+    if world > 1:
+        from ..parallel.tp_model import TpDenseModel
+        return TpDenseModel.from_oracle(w, device, rank, world, **kw)
+    from ..models.dense import DenseModel
+    return DenseModel.from_oracle(w, device, **kw)

@@ -86,6 +86,20 @@ def main():
         allt = [None] * world
         dist.all_gather_object(allt, toks.tolist())
         assert all(t == allt[0] for t in allt)          # every rank produced the same tokens
+        # the same shards loaded from a checkpoint directory give the same tokens
+        import tempfile
+        from agens_engine_b200.utils import checkpoint as K
+        box = [tempfile.mkdtemp() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        if rank == 0:
+            K.save_oracle(box[0], ow, shards=2)
+        dist.barrier()
+        c = K.load_model(box[0], dev, rank=rank, world=world, max_seqs=1, max_ctx=256)
+        c.new_seq(0)
+        assert c.generate_greedy(0, prompt, 16).tolist() == toks.tolist()
+        torch.cuda.synchronize()
+        dist.barrier()
+        c.close()
         # fused path vs the NCCL baseline path: same tokens
         b = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=1, max_ctx=256, use_nccl_decode=True)
         b.new_seq(0)
