@@ -199,8 +199,9 @@ def _get_linear(files, wm, name: str, n: int, k: int, fmt: dict) -> quant.QuantL
         raise NotImplementedError("bf16 linears are quantised at load by the caller")
     bits, group = fmt["bits"], fmt["group"]
     codes = quant.unpack_stream(T(".weight_packed"), bits, k)
-    scale = T(".weight_scale").to(torch.float16)
-    zero = T(".weight_zero_point") if fmt["asymmetric"] else torch.full_like(scale, float(1 << (bits - 1)))
+    # copies: the mapped file may be closed before the weights are packed for the device
+    scale = T(".weight_scale").to(torch.float16).clone()
+    zero = T(".weight_zero_point").clone() if fmt["asymmetric"] else torch.full_like(scale, float(1 << (bits - 1)))
     return quant.QuantLinear(n, k, bits, group, codes, scale, zero)
 
 
