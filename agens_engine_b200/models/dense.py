@@ -102,8 +102,11 @@ class DenseModel:
                    for _ in range(cfg.n_layers)]
         self.block_table = torch.full((self.max_seqs, self.pages_per_seq), -1, dtype=torch.int32, device=dev)
         self.seq_len = i32(self.max_seqs)
-        self.ids, self.last_ids, self.out_ids = i32(M), i32(M), i32(M)
-        self.tok_pos, self.tok_seq, self.grp_tok0, self.grp_cnt = i32(M), i32(M), i32(M), i32(M)
+        # the per-step row description lives in one buffer so that an eager step uploads it with a single copy
+        self._rowbuf = i32(5, M)
+        self._rowbuf_host = torch.zeros(5, M, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(5, M, dtype=torch.int32)
+        self.ids, self.tok_pos, self.tok_seq, self.grp_tok0, self.grp_cnt = (self._rowbuf[i] for i in range(5))
+        self.last_ids, self.out_ids = i32(M), i32(M)
         self.h_a, self.h_b = bf(M, cfg.d_model), bf(M, cfg.d_model)
         parts = max(cfg.d_model // 32, 1)
         self.ss_a = torch.zeros(parts, L.SS_LD, dtype=torch.float32, device=dev)
@@ -188,6 +191,8 @@ class DenseModel:
     def truncate(self, seq: int, n_tokens: int):
         """Roll a sequence back to ``n_tokens`` (rejected speculative rows); pages past the end are released.  A forked
         sequence must not be rolled back below its fork point (its earlier pages are shared)."""
+        if n_tokens == self.seq_len_host[seq]:
+            return
         self.seq_len_host[seq] = n_tokens
         self.seq_len[seq] = n_tokens
         keep = (n_tokens + self.cfg.page_size - 1) // self.cfg.page_size
@@ -361,9 +366,11 @@ class DenseModel:
             pos.append(nxt[s]); nxt[s] += 1
         for s, n in nxt.items():
             self.reserve(s, n)
-        t = lambda x: torch.tensor(x, dtype=torch.int32, device=self.dev)
-        self.ids[:m] = t(ids); self.tok_pos[:m] = t(pos); self.tok_seq[:m] = t(seqs)
-        self.grp_tok0[:len(g0)] = t(g0); self.grp_cnt[:len(g0)] = t(gc)
+        hb = self._rowbuf_host
+        hb[0, :m] = torch.tensor(ids, dtype=torch.int32); hb[1, :m] = torch.tensor(pos, dtype=torch.int32)
+        hb[2, :m] = torch.tensor(seqs, dtype=torch.int32)
+        hb[3, :len(g0)] = torch.tensor(g0, dtype=torch.int32); hb[4, :len(g0)] = torch.tensor(gc, dtype=torch.int32)
+        self._rowbuf.copy_(hb)                     # blocking copy from pinned memory: the host buffer is reused next step
         self._tiered_groups = {}
         if self.tier is not None:
             for gi, i in enumerate(g0):
@@ -376,9 +383,11 @@ class DenseModel:
         else:
             self._rows_body(m, len(g0), want_logits)
         self._tiered_groups = {}
-        for s, n in nxt.items():
-            self.seq_len_host[s] = n
-            self.seq_len[s] = n
+        touched = sorted(set(seqs))
+        for s in touched:
+            self.seq_len_host[s] = nxt[s]
+        self.seq_len[torch.tensor(touched, dtype=torch.long, device=self.dev)] = \
+            torch.tensor([nxt[s] for s in touched], dtype=torch.int32, device=self.dev)
         if self.tier is not None:
             for s in set(seqs):
                 self.tier.maybe_offload(s)

@@ -219,12 +219,11 @@ class SpecDecoder:
     def _sample(self, logits: torch.Tensor, seqs: List[int], positions: List[int]) -> torch.Tensor:
         dev = logits.device
         st = [self.samp[s] for s in seqs]
-        f = lambda xs: torch.tensor(xs, dtype=torch.float32, device=dev)
-        seed = torch.tensor([x.seed & 0x7FFFFFFFFFFFFFFF for x in st], dtype=torch.int64, device=dev)
-        return basic.sample_rows(logits, f([x.temperature for x in st]),
-                                 torch.tensor([x.top_k for x in st], dtype=torch.int32, device=dev),
-                                 f([x.top_p for x in st]), f([x.min_p for x in st]), seed,
-                                 torch.tensor(positions, dtype=torch.int32, device=dev), n_valid=self.t.vocab_valid_full())
+        # three uploads per step: the float parameters, the integer parameters, the seeds
+        f = torch.tensor([[x.temperature for x in st], [x.top_p for x in st], [x.min_p for x in st]], dtype=torch.float32).to(dev)
+        i = torch.tensor([[x.top_k for x in st], list(positions)], dtype=torch.int32).to(dev)
+        seed = torch.tensor([x.seed & 0x7FFFFFFFFFFFFFFF for x in st], dtype=torch.int64).to(dev)
+        return basic.sample_rows(logits, f[0], i[0], f[1], f[2], seed, i[1], n_valid=self.t.vocab_valid_full())
 
     def step(self, seqs: Sequence[int], forced_drafts: Optional[Dict[int, List[int]]] = None) -> Dict[int, List[int]]:
         """One verify step for every sequence of ``seqs``; returns the tokens each of them emitted (at least one).
