@@ -274,9 +274,22 @@ def profile_attn(args):
     print("profile_attn done")
 
 
+def profile_gemm(args):
+    """Three plain launches of the bf16 tcgen05 GEMM (gate/up shape, 2048 rows) for a profiler capture."""
+    from .ops import gemm as G
+    dev = "cuda:0"
+    a = torch.randn(2048, 5120, device=dev).to(torch.bfloat16)
+    b = (torch.randn(51200, 5120, device=dev) * 0.02).to(torch.bfloat16)
+    out = torch.empty(2048, 51200, dtype=torch.bfloat16, device=dev)
+    for _ in range(3):
+        G.gemm_bf16(a, b, out=out)
+    torch.cuda.synchronize()
+    print("profile_gemm done")
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn"])
+    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_gemm"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--ks", type=int, default=0)
     ap.add_argument("--m", type=int, default=1)
@@ -298,6 +311,8 @@ def main(argv=None):
         bench_attn(args)
     elif args.what == "profile_attn":
         profile_attn(args)
+    elif args.what == "profile_gemm":
+        profile_gemm(args)
     else:
         raise SystemExit(f"{args.what}: not available yet")
 
