@@ -111,7 +111,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // 1024-byte aligned base of the ring (the swizzle pattern is anchored at 1024-byte boundaries)
   const uint32_t ring = (smem_u32(smem_g) + 1023u) & ~1023u;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  // Tile order: groups of up to 16 row tiles sweep the column tiles together, row tile fastest, so that CTAs resident at
+  // the same time share B tiles (weights) and the group's A rows stay in L2; B is then read from DRAM about once per
+  // group instead of once per row tile.
+  const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+  constexpr int kGroupM = 16;
+  const int per_group = kGroupM * tiles_n;
+  const int grp = (int)blockIdx.x / per_group;
+  const int gm = min(kGroupM, tiles_m - grp * kGroupM);
+  const int in_grp = (int)blockIdx.x - grp * per_group;
+  const int tile_m = grp * kGroupM + in_grp % gm, tile_n = in_grp / gm;
   const int nkb = (g.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -274,7 +283,7 @@ B2_API int b2_gemm_bf16(const bf16* A, long lda, const bf16* B, long ldb, int M,
     attr = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((N + BN - 1) / BN, (M + BM - 1) / BM, 1);
+  cfg.gridDim = dim3(((N + BN - 1) / BN) * ((M + BM - 1) / BM), 1, 1);
   cfg.blockDim = dim3(kGemmThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
