@@ -43,7 +43,7 @@ struct AttnDecodeArgs {
 namespace {
 
 constexpr int kPage = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 3;      // 96 KB per 4-warp CTA: two CTAs per SM (registers allow two as well)
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
