@@ -103,9 +103,12 @@ class DenseModel:
         self.block_table = torch.full((self.max_seqs, self.pages_per_seq), -1, dtype=torch.int32, device=dev)
         self.seq_len = i32(self.max_seqs)
         # the per-step row description lives in one buffer so that an eager step uploads it with a single copy
-        self._rowbuf = i32(5, M)
-        self._rowbuf_host = torch.zeros(5, M, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(5, M, dtype=torch.int32)
-        self.ids, self.tok_pos, self.tok_seq, self.grp_tok0, self.grp_cnt = (self._rowbuf[i] for i in range(5))
+        self._rowbuf = i32(6, M)
+        self._rowbuf_host = torch.zeros(6, M, dtype=torch.int32).pin_memory() if dev.type == "cuda" else torch.zeros(6, M, dtype=torch.int32)
+        self.ids, self.tok_pos, self.tok_seq, self.grp_tok0, self.grp_cnt, self.rope_pos = (self._rowbuf[i] for i in range(6))
+        # rotary position = KV position + delta: after an image the text positions run behind the token count
+        self.rope_delta: Dict[int, int] = {}
+        self._use_rope_pos = False
         self.last_ids, self.out_ids = i32(M), i32(M)
         self.h_a, self.h_b = bf(M, cfg.d_model), bf(M, cfg.d_model)
         parts = max(cfg.d_model // 32, 1)
@@ -167,6 +170,7 @@ class DenseModel:
         if self.tier is not None:
             self.tier.drop(seq)
         self.pool.free_seq(self._aid.pop(seq))
+        self.rope_delta.pop(seq, None)
         self.seq_pages.pop(seq)
         self.seq_len_host.pop(seq)
         self.block_table[seq].fill_(-1)
@@ -302,7 +306,8 @@ class DenseModel:
             L.gemv(d["qkv"], h_a, ws, pro=PRO_NORM, ss_in=self.ss_a, ss_parts=parts_a, norm_w=d["ln1"], eps=cfg.rms_eps,
                    out=self.qkv[:m])
             basic.rope_kvstore(self.qkv[:m], cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, self.tok_pos,
-                               self.tok_seq, self.block_table, self.kv[li], self.q[:m], status=self.status)
+                               self.tok_seq, self.block_table, self.kv[li], self.q[:m], status=self.status,
+                               rope_pos=self.rope_pos if self._use_rope_pos else None)
             if self._tiered_groups:
                 self.tier.attend(li, self.q[:m], self.grp_tok0[:n_groups], self.grp_cnt[:n_groups], self.tok_pos, self.tok_seq,
                                  self._tiered_groups, self.split_keys, self.max_splits, self.part_o, self.part_ml, self.attn[:m])
@@ -370,6 +375,9 @@ class DenseModel:
         hb[0, :m] = torch.tensor(ids, dtype=torch.int32); hb[1, :m] = torch.tensor(pos, dtype=torch.int32)
         hb[2, :m] = torch.tensor(seqs, dtype=torch.int32)
         hb[3, :len(g0)] = torch.tensor(g0, dtype=torch.int32); hb[4, :len(g0)] = torch.tensor(gc, dtype=torch.int32)
+        self._use_rope_pos = any(self.rope_delta.get(s, 0) for s in seqs)
+        if self._use_rope_pos:
+            hb[5, :m] = torch.tensor([p + self.rope_delta.get(s, 0) for p, s in zip(pos, seqs)], dtype=torch.int32)
         self._rowbuf.copy_(hb)                     # blocking copy from pinned memory: the host buffer is reused next step
         self._tiered_groups = {}
         if self.tier is not None:
@@ -378,7 +386,7 @@ class DenseModel:
                 if self.tier.n_host_pages(s):
                     first, cnt = self._tiered_groups.get(s, (gi, 0))
                     self._tiered_groups[s] = (first, cnt + 1)
-        if self.row_graphs and not self._tiered_groups:
+        if self.row_graphs and not self._tiered_groups and not self._use_rope_pos:
             self._rows_graph(m, len(g0), want_logits).replay()
         else:
             self._rows_body(m, len(g0), want_logits)
@@ -435,13 +443,24 @@ class DenseModel:
         return s
 
     def prefill(self, seq: int, ids: torch.Tensor, want_logits: bool = False, image_rows: Optional[torch.Tensor] = None,
-                image_pad_id: Optional[int] = None):
+                image_pad_id: Optional[int] = None, rope_pos3: Optional[torch.Tensor] = None,
+                pair_axis: Optional[torch.Tensor] = None, rope_next: Optional[int] = None):
         """Chunked prefill of ``ids`` (1-D int tensor) appended to ``seq``; returns the greedy next token (int).
         ``image_rows`` (bf16 [n, d_model], from the vision encoder) replace the embedding rows of the ``image_pad_id``
         tokens, in order (reference: m1_model.cu:2821-2834)."""
         cfg = self.cfg
         ids = ids.to(device=self.dev, dtype=torch.int32)
         T = ids.numel()
+        # multi-axis rotary positions (int32 [3, T], serve.vision.mrope_positions) with the axis of every frequency pair;
+        # rope_next = the running position after the prompt: later tokens rotate by KV position + (rope_next - length)
+        self._rope3 = None
+        if rope_pos3 is not None:
+            assert self.seq_len_host[seq] == 0 and pair_axis is not None and tuple(rope_pos3.shape) == (3, T)
+            assert all(min(self.prefill_chunk, T - c0) > 8 for c0 in range(0, T, self.prefill_chunk)), \
+                "chunks with multi-axis positions go through the large-m path"
+            self._rope3 = (rope_pos3.to(self.dev, torch.int32).contiguous(), pair_axis.to(self.dev))
+            if rope_next is not None:
+                self.rope_delta[seq] = int(rope_next) - T
         self._sub_rows = self._sub_index = None
         if image_rows is not None:
             is_img = ids == image_pad_id
@@ -463,6 +482,7 @@ class DenseModel:
             if self.tier is not None:
                 self.tier.maybe_offload(seq)
         self._sub_rows = self._sub_index = None
+        self._rope3 = None
         return last
 
     def _prefill_chunk(self, seq: int, ids: torch.Tensor, pos0: int, final: bool, want_logits: bool):
@@ -495,8 +515,14 @@ class DenseModel:
             else:
                 x, h = basic.rmsnorm(delta, d["ln1"], cfg.rms_eps, resid=h)
             qkv = self._linear_big(d["qkv"], x)
-            basic.rope_kvstore(qkv, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, pos, seqv, self.block_table,
-                               self.kv[li], q, status=self.status)
+            if getattr(self, "_rope3", None) is not None:
+                r3 = self._rope3[0][:, self._sub_slice[0]:self._sub_slice[1]].contiguous()
+                basic.rope_kvstore_m(qkv, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, pos, r3, self._rope3[1], seqv,
+                                     self.block_table, self.kv[li], q, status=self.status)
+            else:
+                rp = pos + self.rope_delta[seq] if self.rope_delta.get(seq, 0) else None
+                basic.rope_kvstore(qkv, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, self.inv_freq, pos, seqv, self.block_table,
+                                   self.kv[li], q, status=self.status, rope_pos=rp)
             if tiered:
                 a = self.tier.attend(li, q, pg0, pgc, pos, seqv, {seq: (0, pg0.numel())}, self.prefill_split, p_splits, p_o, p_ml, p_out,
                                      shared_kv=True)

@@ -52,3 +52,34 @@ def test_image_rows_replace_placeholder_embeddings():
     m.new_seq(1)
     _, c = m.prefill(1, ids, want_logits=True)
     assert not torch.equal(a, c)
+
+
+def test_prefill_with_multi_axis_positions_and_rope_delta():
+    from agens_engine_b200.ops import basic
+    cfg = C.oracle_tiny()
+    ow = O.random_weights(cfg, seed=0)
+    torch.manual_seed(1)
+    PAD = 7
+    ids = torch.randint(8, cfg.vocab, (40,))
+    ids[4:16] = PAD                                               # one image: merged grid 3 x 4
+    rows = (torch.randn(12, cfg.d_model) * 0.02).to(torch.bfloat16)
+    axis = basic.mrope_pair_axis(cfg.head_dim, [11, 11, 10], True)
+    pos3, nxt = V.mrope_positions(ids.tolist(), PAD, [(3, 4)])
+    assert nxt == 40 - 12 + 4                                     # the image advances the running position by max(3, 4)
+
+    def run(p3, nx):
+        m = DenseModel.from_oracle(ow, max_seqs=1, max_ctx=256, prefill_chunk=64)
+        m.new_seq(0)
+        tok, lg = m.prefill(0, ids, want_logits=True, image_rows=rows, image_pad_id=PAD,
+                            rope_pos3=None if p3 is None else torch.from_numpy(p3), pair_axis=axis, rope_next=nx)
+        out, lg2 = m.forward_rows([tok], [0], want_logits=True)
+        return lg, lg2[0], m
+
+    plain, plain2, _ = run(None, None)
+    import numpy as np
+    same_axes = np.tile(np.arange(40, dtype=np.int32), (3, 1))
+    a, a2, _ = run(same_axes, 40)                                 # every axis = token index: identical to plain RoPE
+    assert torch.equal(a, plain) and torch.equal(a2, plain2)
+    b, b2, m = run(pos3, nxt)
+    assert not torch.equal(b, plain) and m.rope_delta[0] == nxt - 40
+    assert not torch.equal(b2, plain2)                            # the decode row rotates by its KV position + delta
