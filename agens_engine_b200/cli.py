@@ -323,9 +323,15 @@ def cmd_serve(ns):
     from .serve.server import Server
     from .spec import CopyLookupSource, ModelSource, MtpSource
     cfg = EngineConfig.resolve(ns)
+    children = []
     if cfg.tp > 1 and "RANK" not in os.environ:
         from .parallel import driver as D
-        D.launch([a for a in sys.argv], cfg.tp)
+        children = D.launch(["-m", "agens_engine_b200"] + sys.argv[1:], cfg.tp)   # the other ranks run the same command line
+    import signal
+
+    def _on_term(signum, frame):           # a plain kill still releases the followers and the peer mappings
+        raise KeyboardInterrupt
+    signal.signal(signal.SIGTERM, _on_term)
     if cfg.mode == "personal":
         cfg.max_batch = 1
     # slots beyond the running batch hold finished conversations and prompt-prefix snapshots
@@ -389,6 +395,11 @@ def cmd_serve(ns):
         if world > 1:
             model.shutdown()
             _finish(m, world)
+        for c in children:                 # the ranks this process started: wait, then stop exactly those processes
+            try:
+                c.wait(timeout=20)
+            except Exception:
+                c.terminate()
     return 0
 
 

@@ -33,3 +33,44 @@ def test_tp2_model_matches_single_gpu():
 
 def test_tp2_engine_leader_follower_and_sampling():
     _run("engine")
+
+
+def test_tp2_serve_over_http(tmp_path):
+    """`serve --tp 2`: rank 0 starts the other rank, schedules, answers over HTTP; a SIGTERM shuts both ranks down."""
+    import json
+    import time
+    import urllib.request
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from tests.fixtures import tiny_tokenizer_json
+    tok = tmp_path / "tokenizer.json"
+    tok.write_text(tiny_tokenizer_json())
+    root = os.path.dirname(HERE)
+    log = open(tmp_path / "serve.log", "w")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env.pop("RANK", None); env.pop("WORLD_SIZE", None)
+    p = subprocess.Popen([sys.executable, "-u", "-m", "agens_engine_b200", "serve", "--random", "oracle-tiny", "--tokenizer", str(tok),
+                          "--port", "0", "--wctx", "512", "--max-batch", "2", "--max-convs", "0", "--tp", "2",
+                          "--served-model-name", "tiny"], cwd=root, stdout=log, stderr=subprocess.STDOUT, env=env)
+    try:
+        port = None
+        for _ in range(360):
+            time.sleep(0.5)
+            txt = open(tmp_path / "serve.log").read()
+            if "serving tiny on http://" in txt:
+                port = int(txt.split("serving tiny on http://127.0.0.1:")[1].split()[0])
+                break
+            assert p.poll() is None, txt[-3000:]
+        assert port, open(tmp_path / "serve.log").read()[-3000:]
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/v1/completions", headers={"Content-Type": "application/json"},
+                                     data=json.dumps({"model": "tiny", "prompt": "hello there and", "max_tokens": 8, "temperature": 0}).encode())
+        with urllib.request.urlopen(req, timeout=120) as r:
+            body = json.loads(r.read().decode())
+        assert body["usage"]["completion_tokens"] == 8
+    finally:
+        p.terminate()
+        try:
+            p.wait(timeout=60)
+        except subprocess.TimeoutExpired:
+            p.kill()
+    assert "Traceback" not in open(tmp_path / "serve.log").read()
