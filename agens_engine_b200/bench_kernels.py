@@ -265,11 +265,14 @@ def bench_attn(args):
 
 
 def profile_attn(args):
-    """A few plain launches (256-row prefill chunk at an 8K context, CTA-shared ring) for a profiler capture."""
+    """A few plain launches for a profiler capture: by default a 256-row prefill chunk at an 8K context (CTA-shared
+    ring); ``--rows 1 --ctx 32768`` is one decode row over 134 MB of K/V (64-key splits, per-warp ring)."""
     dev = "cuda:0"
-    A, pool, bt, q, g0, gc, pos, seqv = _attn_case(8192, 256, dev)
+    rows, ctx = args.rows, args.ctx
+    split = 256 if rows >= 8 else 64
+    A, pool, bt, q, g0, gc, pos, seqv = _attn_case(ctx, rows, dev)
     for _ in range(3):
-        A.attn_decode(q, pool, bt, g0, gc, pos, seqv, 64, 8, 128, 256, (8192 + 256 + 255) // 256, shared_kv=True)
+        A.attn_decode(q, pool, bt, g0, gc, pos, seqv, 64, 8, 128, split, (ctx + rows + split - 1) // split, shared_kv=rows >= 8)
     torch.cuda.synchronize()
     print("profile_attn done")
 
@@ -294,6 +297,8 @@ def main(argv=None):
     ap.add_argument("--ks", type=int, default=0)
     ap.add_argument("--m", type=int, default=1)
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--rows", type=int, default=256)
+    ap.add_argument("--ctx", type=int, default=8192)
     args = ap.parse_args(argv)
     if args.what == "gemv":
         bench_gemv(args)

@@ -48,6 +48,7 @@ class EngineConfig:
     tokenizer: Optional[str] = None
     profile: Optional[str] = None
     row_graphs: int = 1
+    vision: int = 0
 
     @staticmethod
     def resolve(ns: argparse.Namespace) -> "EngineConfig":
@@ -378,8 +379,20 @@ def cmd_serve(ns):
     n_tok = 1 + max([max(tj["model"]["vocab"].values(), default=0)] + [int(t["id"]) for t in tj.get("added_tokens", [])])
     full = m.full_cfg if world > 1 else m.cfg
     full.vocab_valid = min(full.vocab_valid or full.vocab, n_tok)
+    front = None
+    if cfg.vision and world == 1:
+        # image input: the tower's weights are random-init here (a loader for tower tensors of a checkpoint is not part
+        # of this build); the placeholder id comes from the tokenizer's added tokens
+        from .models.vision import VisionConfig, VisionTower
+        from .serve.vision import VisionFrontEnd
+        pad = [int(t["id"]) for t in tj.get("added_tokens", []) if t.get("content") == "<|image_pad|>"]
+        if not pad:
+            raise SystemExit("--vision 1 needs an <|image_pad|> token in the tokenizer")
+        vc = VisionConfig(out_dim=full.d_model) if full.d_model >= 2048 else \
+            VisionConfig(depth=2, d_model=288, n_heads=4, mlp=608, out_dim=full.d_model, pos_grid=12)
+        front = VisionFrontEnd(VisionTower.random_init(vc, m.dev, seed=cfg.seed + 2), pad[0], full.head_dim)
     eng = Engine(model, lambda *a: False, sources_factory=(lambda: sources) if sources else None,
-                 max_drafts=cfg.draft_depth if sources else 0, max_batch=cfg.max_batch, keep_sequences=world == 1)
+                 max_drafts=cfg.draft_depth if sources else 0, max_batch=cfg.max_batch, keep_sequences=world == 1, vision=front)
     attach_to_server(eng, srv, context_length=m.max_ctx)
     eng.start()
     port = srv.start(cfg.host, cfg.port)
@@ -433,6 +446,7 @@ def main(argv=None) -> int:
     p.add_argument("--host"); p.add_argument("--port", type=int); p.add_argument("--served-model-name")
     p.add_argument("--spec-copy", type=int); p.add_argument("--spec-drafter"); p.add_argument("--mtp")
     p.add_argument("--max-tokens-default", type=int); p.add_argument("--think-guard"); p.add_argument("--tokenizer")
+    p.add_argument("--vision", type=int)
     p.set_defaults(fn=cmd_serve)
     ns = ap.parse_args(argv)
     return int(ns.fn(ns) or 0)

@@ -238,13 +238,16 @@ class DenseModel:
         for l, kv in enumerate(self.kv):
             host_kv[l].copy_(kv.index_select(0, idx), non_blocking=True)
         torch.cuda.current_stream(self.dev).synchronize()
+        delta = self.rope_delta.get(seq, 0)
         self.free_seq(seq)
-        return {"len": n, "kv": host_kv}
+        return {"len": n, "kv": host_kv, "rope_delta": delta}
 
     def unpark(self, seq: int, blob: Dict[str, object]):
         """Restores a parked sequence into the (free) slot ``seq``."""
         self.new_seq(seq)
         n = int(blob["len"])
+        if blob.get("rope_delta"):
+            self.rope_delta[seq] = int(blob["rope_delta"])
         self.reserve(seq, n)
         used = (n + self.cfg.page_size - 1) // self.cfg.page_size
         idx = torch.tensor(self.seq_pages[seq][:used], dtype=torch.long, device=self.dev)
@@ -456,8 +459,6 @@ class DenseModel:
         self._rope3 = None
         if rope_pos3 is not None:
             assert self.seq_len_host[seq] == 0 and pair_axis is not None and tuple(rope_pos3.shape) == (3, T)
-            assert all(min(self.prefill_chunk, T - c0) > 8 for c0 in range(0, T, self.prefill_chunk)), \
-                "chunks with multi-axis positions go through the large-m path"
             self._rope3 = (rope_pos3.to(self.dev, torch.int32).contiguous(), pair_axis.to(self.dev))
             if rope_next is not None:
                 self.rope_delta[seq] = int(rope_next) - T
@@ -468,13 +469,17 @@ class DenseModel:
             self._sub_rows = image_rows.to(self.dev, torch.bfloat16).contiguous()
             self._sub_index = torch.where(is_img, torch.cumsum(is_img.to(torch.int32), 0, dtype=torch.int32) - 1,
                                           torch.full_like(ids, -1)).contiguous()
-            assert self.prefill_chunk > 8 and all(min(self.prefill_chunk, T - c0) > 8 for c0 in range(0, T, self.prefill_chunk)), \
-                "chunks with image rows go through the large-m path"
         start = self.seq_len_host[seq]
         self.reserve(seq, start + T)
         last = None
-        for c0 in range(0, T, self.prefill_chunk):
-            c1 = min(T, c0 + self.prefill_chunk)
+        cuts = list(range(0, T, self.prefill_chunk)) + [T]
+        if self._rope3 is not None or self._sub_rows is not None:
+            # image rows and multi-axis positions exist in the large-m path only (more than 8 rows per chunk): a short
+            # tail borrows 16 rows from the chunk before it
+            assert T > 8 and self.prefill_chunk > 24, "prompts with images need more than 8 tokens"
+            if len(cuts) > 2 and T - cuts[-2] <= 8:
+                cuts[-2] -= 16
+        for c0, c1 in zip(cuts[:-1], cuts[1:]):
             self._sub_slice = (c0, c1)
             last = self._prefill_chunk(seq, ids[c0:c1], start + c0, final=(c1 == T), want_logits=want_logits)
             self.seq_len_host[seq] = start + c1

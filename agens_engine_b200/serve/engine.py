@@ -44,6 +44,8 @@ class Request:
     evictions: int = 0
     parked: Optional[dict] = None         # KV rows in pinned host memory while preempted
     parked_hist: Optional[List[int]] = None
+    images: Optional[List[str]] = None    # data: URLs of the request's image parts, in prompt order
+    mm: Optional[dict] = None             # serve.vision.VisionFrontEnd.prepare(): encoder rows, positions
 
     @property
     def max_new(self) -> int:
@@ -74,6 +76,7 @@ class EngineStats:
     evictions: int = 0
     rejected: int = 0
     peak_batch: int = 0
+    images_encoded: int = 0
 
 
 class Engine:
@@ -84,8 +87,9 @@ class Engine:
                  sources_factory: Optional[Callable[[], Sequence[DraftSource]]] = None, max_drafts: int = 0,
                  max_batch: Optional[int] = None, think_tokens: Optional[tuple] = None, reserve_ahead: int = 16,
                  keep_sequences: bool = False, prefix_chunk: int = 64, prefix_budget_bytes: int = 1 << 40,
-                 invariant: bool = True):
+                 invariant: bool = True, vision=None):
         self.m, self.emit = model, emit
+        self.vision = vision                           # serve.vision.VisionFrontEnd, or None: requests with images fail
         self.max_batch = min(max_batch or model.max_seqs, model.max_seqs, M_GEMV)
         self.max_drafts = max_drafts
         if invariant:
@@ -115,12 +119,15 @@ class Engine:
         self.prefix_chunk = prefix_chunk
 
     # ------------------------------------------------------------------------------------------------ submission
-    def submit(self, prompt: Sequence[int], sampling: Optional[dict] = None, rid: Optional[int] = None, session: str = "") -> int:
+    def submit(self, prompt: Sequence[int], sampling: Optional[dict] = None, rid: Optional[int] = None, session: str = "",
+               images: Optional[Sequence[str]] = None) -> int:
+        """``images``: one ``data:`` URL per image placeholder of the prompt (one placeholder token each, expanded here)."""
         with self._lock:
             if rid is None:
                 self._rid += 1
                 rid = self._rid
-        r = Request(rid, list(prompt), dict(sampling or {}), session, t_submit=time.monotonic())
+        r = Request(rid, list(prompt), dict(sampling or {}), session, t_submit=time.monotonic(),
+                    images=list(images) if images else None)
         self.inbox.put(r)
         return rid
 
@@ -155,9 +162,12 @@ class Engine:
         """One scheduler iteration; returns False when there was nothing to do."""
         while True:
             try:
-                self.waiting.append(self.inbox.get_nowait())
+                r = self.inbox.get_nowait()
             except queue.Empty:
                 break
+            if r.images and not self._prepare_images(r):
+                continue
+            self.waiting.append(r)
         self._admit()
         did = False
         pre = [r for r in self.active.values() if r.state == PREFILL]
@@ -167,6 +177,20 @@ class Engine:
         if dec:
             self._decode(dec); did = True
         return did
+
+    def _prepare_images(self, r: Request) -> bool:
+        """Decodes and encodes the request's images on this (the engine's) thread and expands the prompt."""
+        try:
+            if self.vision is None:
+                raise ValueError("this model does not accept images")
+            r.mm = self.vision.prepare(r.prompt, r.images)
+        except (ValueError, RuntimeError) as e:
+            self.stats.rejected += 1
+            self.emit(r.rid, [], True, f"image input: {e}")
+            return False
+        r.prompt = list(r.mm["ids"])
+        self.stats.images_encoded += len(r.images)
+        return True
 
     # ---- admission -----------------------------------------------------------------------------------------------
     def _pages(self, n_tokens: int) -> int:
@@ -214,7 +238,7 @@ class Engine:
                 self.active[r.slot] = r
                 continue
             r.state, r.done_prompt, r.chunk_index = PREFILL, 0, 0
-            if not self._reuse_kept(r):
+            if r.mm is not None or not self._reuse_kept(r):      # image rows are not in the token-keyed prefix cache
                 self.m.new_seq(r.slot)
             if self.think and r.sampling.get("reasoning_budget") is not None:
                 r.budget = host.ReasoningBudget(int(r.sampling["reasoning_budget"]), float(r.sampling.get("reasoning_soft", 0.0)),
@@ -372,11 +396,17 @@ class Engine:
                               self.stats.prefill_chunks)
         r = pre[i if 0 <= i < len(pre) else 0]
         n = min(self.m.prefill_chunk, len(r.prompt) - r.done_prompt)
+        if r.mm is not None:
+            n = len(r.prompt)                             # the model chunks a prompt with images itself
         chunk = torch.tensor(r.prompt[r.done_prompt:r.done_prompt + n], dtype=torch.int32)
         final = r.done_prompt + n == len(r.prompt)
         sampled = self.spec.samp[r.slot].temperature > 0 or r.needs_logit_edits()
+        kw = {}
+        if r.mm is not None:
+            kw = dict(image_rows=r.mm["rows"], image_pad_id=r.mm["pad_id"], rope_pos3=r.mm["pos3"], pair_axis=r.mm["pair_axis"],
+                      rope_next=r.mm["rope_next"])
         try:
-            res = self._with_room(r, lambda: self.m.prefill(r.slot, chunk, want_logits=final and sampled))
+            res = self._with_room(r, lambda: self.m.prefill(r.slot, chunk, want_logits=final and sampled, **kw))
         except RuntimeError as e:
             self._finish(r, error=str(e)); return
         r.done_prompt += n
@@ -494,7 +524,7 @@ class Engine:
         r.t_last = time.monotonic()
         self.stats.tokens_out += len(out)
         gone = self.emit(r.rid, out, finished, None)
-        if finished and not gone and self.keep_sequences and r.slot in self.active and r.state == DECODE:
+        if finished and not gone and self.keep_sequences and r.mm is None and r.slot in self.active and r.state == DECODE:
             for src in self.spec.sources:
                 src.end(r.slot)
             self.spec.hist.pop(r.slot, None); self.spec.samp.pop(r.slot, None)
@@ -524,7 +554,12 @@ class Engine:
 
 # ---------------------------------------------------------------------------------------------------------------------
 def attach_to_server(engine: Engine, server, context_length: Optional[int] = None):
-    """Makes ``engine`` the backend of an OpenAI front end (:class:`agens_engine_b200.serve.server.Server`)."""
+    """Makes ``engine`` the backend of an OpenAI front end (:class:`agens_engine_b200.serve.server.Server`).  The
+    server passes the request's image URLs inside the sampling object (key ``images``)."""
     engine.emit = lambda rid, toks, fin, err: server.push(rid, toks, fin, err)
-    server.use_engine(lambda rid, prompt, sampling, session: engine.submit(prompt, sampling, rid=rid, session=session),
-                      context_length or engine.m.max_ctx)
+
+    def generate(rid, prompt, sampling, session):
+        images = sampling.pop("images", None) if isinstance(sampling, dict) else None
+        engine.submit(prompt, sampling, rid=rid, session=session, images=images)
+
+    server.use_engine(generate, context_length or engine.m.max_ctx, supports_images=engine.vision is not None)

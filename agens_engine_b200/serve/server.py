@@ -19,7 +19,7 @@ def _h():
         sig = {
             "b2h_server_new": ([cp, cp, i], vp), "b2h_server_free": ([vp], None),
             "b2h_server_use_mock": ([vp, ip, i, i, i], None), "b2h_server_mock_calls": ([vp], vp),
-            "b2h_server_use_callback": ([vp, _GEN_FN, vp, i], None),
+            "b2h_server_use_callback": ([vp, _GEN_FN, vp, i], None), "b2h_server_set_images": ([vp, i], i),
             "b2h_stream_push": ([vp, C.c_longlong, ip, i, i, cp], i), "b2h_stream_cancelled": ([vp, C.c_longlong], i),
             "b2h_server_handle": ([vp, cp, cp, cp, cp, ip], vp),
             "b2h_server_start": ([vp, cp, i], i), "b2h_server_stop": ([vp], None),
@@ -104,13 +104,16 @@ class Server:
     def mock_calls(self) -> list:
         return json.loads(_take(_h().b2h_server_mock_calls(self._s)))
 
-    def use_engine(self, generate: Callable[[int, List[int], dict, str], None], context_length: int = 262144):
+    def use_engine(self, generate: Callable[[int, List[int], dict, str], None], context_length: int = 262144,
+                   supports_images: bool = False):
         """``generate(req_id, prompt_ids, sampling, session_id)`` must return at once; the engine later calls
-        :meth:`push` with each step's tokens."""
+        :meth:`push` with each step's tokens.  With ``supports_images`` chat requests may carry ``image_url`` parts
+        (base64 ``data:`` URLs); they arrive as ``sampling["images"]``, one per ``<|image_pad|>`` token of the prompt."""
         def tramp(_user, req_id, prompt, n, sampling, session):
             generate(req_id, [prompt[i] for i in range(n)], json.loads(sampling.decode()), session.decode())
         self._cb = _GEN_FN(tramp)
         _h().b2h_server_use_callback(self._s, self._cb, None, context_length)
+        _h().b2h_server_set_images(self._s, int(supports_images))
 
     def push(self, req_id: int, ids: Sequence[int], finished: bool = False, error: Optional[str] = None) -> bool:
         """Returns True when the client is gone (stop generating)."""

@@ -164,3 +164,40 @@ def load_url(url: str) -> bytes:
 def image_key(data: bytes) -> int:
     """Prefix-cache salt of an image: the first 8 bytes of its SHA-256."""
     return int.from_bytes(hashlib.sha256(data).digest()[:8], "little")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+class VisionFrontEnd:
+    """Turns the ``image_url`` parts of a chat request into what the model's prefill takes: the prompt with every image
+    placeholder expanded to one token per merged patch, the encoder's rows for those tokens, multi-axis rotary
+    positions and the running position after the prompt (reference: crates/agens-cli/src/mm.rs ``encode`` /
+    ``prefill_prompt_with`` and crates/agens-server/src/vision.rs).  Runs on the engine thread: the tower launches
+    kernels on the model's device."""
+
+    def __init__(self, tower, pad_id: int, head_dim: int, sections: Sequence[int] = (24, 20, 20), interleaved: bool = True,
+                 max_images: int = 16):
+        from ..ops import basic
+        self.tower, self.pad_id, self.max_images = tower, int(pad_id), max_images
+        sections = list(sections)
+        if sum(sections) != head_dim // 2:                     # scale the split to this head size, keeping the shares
+            half = head_dim // 2
+            sections = [half * s // sum(sections) for s in sections]
+            sections[0] += half - sum(sections)
+        self.pair_axis = basic.mrope_pair_axis(head_dim, sections, interleaved)
+
+    def prepare(self, prompt: Sequence[int], urls: Sequence[str]) -> dict:
+        import torch
+        if len(urls) > self.max_images:
+            raise ValueError(f"at most {self.max_images} images per request")
+        rows, counts, grids, keys = [], [], [], []
+        for u in urls:
+            data = load_url(u)
+            patches, (gh, gw) = preprocess(decode_image(data))
+            rows.append(self.tower.encode(torch.from_numpy(patches), (gh, gw)))
+            counts.append(gh * gw // 4)
+            grids.append((gh // 2, gw // 2))
+            keys.append(image_key(data))
+        ids = expand_placeholders(list(prompt), self.pad_id, counts)
+        pos3, nxt = mrope_positions(ids, self.pad_id, grids)
+        return {"ids": ids, "rows": torch.cat(rows, 0), "pos3": torch.from_numpy(pos3), "pair_axis": self.pair_axis,
+                "rope_next": int(nxt), "pad_id": self.pad_id, "keys": keys}

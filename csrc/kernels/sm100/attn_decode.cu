@@ -273,50 +273,107 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
   }
 }
 
-// Combine the splits of every (token, q head) in split order.  One warp per (token, head); the scalar pass over the
-// (max, sum) pairs runs lane-parallel, the accumulation over splits keeps eight loads in flight and adds in order.
-template <int HD>
+// Combine the splits of every (token, q head).  Splits are taken in blocks of eight; block b belongs to lane set
+// b % 8, every set adds its blocks' splits in ascending order, and the eight sets are added in set order at the end.
+// WPI = 1: one warp per (token, head) keeps the eight sets in registers (prefill chunks, large batches).
+// WPI = 8: eight warps per (token, head), one set each, joined through shared memory (decode and verify steps, where
+// the items are few and the chain of dependent loads is what costs).  Both run the same additions in the same order,
+// so a row's bits do not depend on which variant merged it.
+template <int HD, int WPI>
 __global__ void attn_merge_kernel(const AttnDecodeArgs a) {
   pdl_wait();
   pdl_launch_dependents();
-  const int wid = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (wid >= a.n_tok * a.hq) return;
-  const int tok = wid / a.hq, head = wid - tok * a.hq;
-  const int ns = (a.tok_pos[tok] + a.split_keys) / a.split_keys;   // ceil((pos + 1) / split_keys)
-  const float* po = a.part_o + ((size_t)tok * a.hq + head) * a.max_splits * HD;
-  const float2* pm = reinterpret_cast<const float2*>(a.part_ml + ((size_t)tok * a.hq + head) * a.max_splits * 2);
-  float M = -INFINITY;
-  for (int s = lane; s < ns; s += 32) M = fmaxf(M, pm[s].x);
-  M = warp_max(M);
   constexpr int PER = HD / 32;
-  float acc[PER];
+  constexpr int SETS = 8;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int item = WPI == 1 ? blockIdx.x * (blockDim.x >> 5) + warp : blockIdx.x;
+  const bool live = item < a.n_tok * a.hq;
+  __shared__ float part[WPI == 1 ? 1 : SETS][HD + 32];
+  float acc[WPI == 1 ? SETS : 1][PER], L[WPI == 1 ? SETS : 1];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) acc[i] = 0.f;
-  float L = 0.f;
-  for (int s0 = 0; s0 < ns; s0 += 8) {
-    float2 ml[8];
-    float pv[8][PER];
+  for (int w = 0; w < (WPI == 1 ? SETS : 1); ++w) {
+    L[w] = 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int s = s0 + j;
-      ml[j] = s < ns ? pm[s] : make_float2(-INFINITY, 0.f);
+    for (int i = 0; i < PER; ++i) acc[w][i] = 0.f;
+  }
+  int tok = 0, head = 0;
+  if (live) {
+    tok = item / a.hq; head = item - tok * a.hq;
+    const int ns = (a.tok_pos[tok] + a.split_keys) / a.split_keys;   // ceil((pos + 1) / split_keys)
+    const float* po = a.part_o + ((size_t)tok * a.hq + head) * a.max_splits * HD;
+    const float2* pm = reinterpret_cast<const float2*>(a.part_ml + ((size_t)tok * a.hq + head) * a.max_splits * 2);
+    float M = -INFINITY;
+    for (int s = lane; s < ns; s += 32) M = fmaxf(M, pm[s].x);
+    M = warp_max(M);
+    const int b0 = WPI == 1 ? 0 : warp, bstep = WPI == 1 ? 1 : SETS;
+    for (int blk = b0; blk * 8 < ns; blk += bstep) {
+      const int s0 = blk * 8;
+      float2 ml[8];
+      float pv[8][PER];
 #pragma unroll
-      for (int i = 0; i < PER; ++i) pv[j][i] = s < ns ? po[(size_t)s * HD + lane * PER + i] : 0.f;
-    }
+      for (int j = 0; j < 8; ++j) {
+        const int s = s0 + j;
+        ml[j] = s < ns ? pm[s] : make_float2(-INFINITY, 0.f);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (ml[j].x == -INFINITY) continue;
-      const float w = exp2f(ml[j].x - M);
-      L += ml[j].y * w;
+        for (int i = 0; i < PER; ++i) pv[j][i] = s < ns ? po[(size_t)s * HD + lane * PER + i] : 0.f;
+      }
+      if (WPI == 1) {
 #pragma unroll
-      for (int i = 0; i < PER; ++i) acc[i] += pv[j][i] * w;
+        for (int w = 0; w < SETS; ++w) {
+          if ((blk & (SETS - 1)) != w) continue;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (ml[j].x == -INFINITY) continue;
+            const float wt = exp2f(ml[j].x - M);
+            L[w] = fmaf(ml[j].y, wt, L[w]);
+#pragma unroll
+            for (int i = 0; i < PER; ++i) acc[w][i] = fmaf(pv[j][i], wt, acc[w][i]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (ml[j].x == -INFINITY) continue;
+          const float wt = exp2f(ml[j].x - M);
+          L[0] = fmaf(ml[j].y, wt, L[0]);
+#pragma unroll
+          for (int i = 0; i < PER; ++i) acc[0][i] = fmaf(pv[j][i], wt, acc[0][i]);
+        }
+      }
     }
   }
-  const float inv = L > 0.f ? 1.f / L : 0.f;
+  float o[PER], Ls;
+  if (WPI == 1) {
+    if (!live) return;
+    Ls = L[0];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) o[i] = acc[0][i];
+#pragma unroll
+    for (int w = 1; w < SETS; ++w) {
+      Ls = __fadd_rn(Ls, L[w]);
+#pragma unroll
+      for (int i = 0; i < PER; ++i) o[i] = __fadd_rn(o[i], acc[w][i]);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < PER; ++i) part[warp][lane * PER + i] = acc[0][i];
+    if (lane == 0) part[warp][HD] = L[0];
+    __syncthreads();
+    if (warp != 0 || !live) return;
+    Ls = part[0][HD];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) o[i] = part[0][lane * PER + i];
+#pragma unroll
+    for (int w = 1; w < SETS; ++w) {
+      Ls = __fadd_rn(Ls, part[w][HD]);
+#pragma unroll
+      for (int i = 0; i < PER; ++i) o[i] = __fadd_rn(o[i], part[w][lane * PER + i]);
+    }
+  }
+  const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
   bf16* out = a.out + (size_t)tok * a.ldo + (size_t)head * HD + lane * PER;
 #pragma unroll
-  for (int i = 0; i < PER; ++i) out[i] = __float2bfloat16_rn(acc[i] * inv);
+  for (int i = 0; i < PER; ++i) out[i] = __float2bfloat16_rn(__fmul_rn(o[i], inv));
 }
 
 }  // namespace b2
@@ -365,8 +422,10 @@ B2_API int b2_attn_decode(const AttnDecodeArgs* args, int hd, cudaStream_t st) {
   }
   if (e != cudaSuccess) return B2_ERR_LAUNCH;
   if (!run_merge) return B2_OK;
-  cfg.gridDim = dim3((a.n_tok * a.hq + 7) / 8); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0;
-  if (hd == 128) e = cudaLaunchKernelEx(&cfg, attn_merge_kernel<128>, a);
-  else e = cudaLaunchKernelEx(&cfg, attn_merge_kernel<64>, a);
+  const int merge_items = a.n_tok * a.hq;
+  const bool wide = merge_items <= 148 * 8;               // few items: eight warps per item shorten the load chain
+  cfg.gridDim = dim3(wide ? merge_items : (merge_items + 7) / 8); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0;
+  if (hd == 128) e = wide ? cudaLaunchKernelEx(&cfg, attn_merge_kernel<128, 8>, a) : cudaLaunchKernelEx(&cfg, attn_merge_kernel<128, 1>, a);
+  else e = wide ? cudaLaunchKernelEx(&cfg, attn_merge_kernel<64, 8>, a) : cudaLaunchKernelEx(&cfg, attn_merge_kernel<64, 1>, a);
   return e == cudaSuccess ? B2_OK : B2_ERR_LAUNCH;
 }

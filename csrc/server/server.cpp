@@ -101,6 +101,8 @@ class CallbackBackend : public Backend {
   GenerateFn fn = nullptr;
   void* user = nullptr;
   int ctx = 262144;
+  bool images = false;
+  bool supports_images() const override { return images; }
   std::mutex mu;
   std::map<long long, std::shared_ptr<TokenStream>> streams;
   void generate(const GenRequest& r, std::shared_ptr<TokenStream> s) override {
@@ -390,6 +392,7 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
   const Json* ms = body.find("messages");
   if (!ms || !ms->is_array() || ms->size() == 0) return error_response(400, "messages must be a non-empty array");
   std::vector<ChatMessage> msgs;
+  Json image_urls = Json::array();
   for (auto& m : ms->items()) {
     ChatMessage cm;
     cm.role = m.get_string("role", "");
@@ -406,6 +409,7 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
             const Json* iu = part.find("image_url");
             const std::string url = iu ? iu->get_string("url", "") : "";
             if (url.compare(0, 5, "data:") != 0) return error_response(400, "only base64 data: URLs are accepted for images");
+            image_urls.push_back(url);
             cm.content += "<|vision_start|><|image_pad|><|vision_end|>";
           } else return error_response(400, "unsupported content part type: " + type);
         }
@@ -424,6 +428,7 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
   Json sampling;
   if (std::string e = build_sampling(sv, body, true, sampling); !e.empty()) return error_response(400, e);
   if (auto rb = body.find("reasoning_budget"); rb && rb->is_number()) sampling.set("reasoning_budget", rb->as_int());
+  if (image_urls.size()) sampling.set("images", image_urls);      // one per placeholder, in prompt order
   const std::vector<int> ids = sv.tok.encode(prompt);
   if ((long long)ids.size() >= sv.backend->context_length()) return error_response(400, "the prompt is longer than the model's context length");
   const std::string session = !session_hdr.empty() ? session_hdr : body.get_string("session_id", "");
@@ -570,6 +575,12 @@ B2H_API char* b2h_server_mock_calls(void* s) {
   Json a = Json::array();
   if (m) { std::lock_guard<std::mutex> l(m->mu); for (auto& c : m->calls) { Json o = Json::object(), p = Json::array(); for (int t : c.prompt) p.push_back(t); o.set("prompt", p); o.set("sampling", c.sampling); o.set("session_id", c.session_id); a.push_back(o); } }
   return dup_cstr(a.dump());
+}
+B2H_API int b2h_server_set_images(void* s, int on) {
+  auto b = std::dynamic_pointer_cast<CallbackBackend>(static_cast<Server*>(s)->backend);
+  if (!b) return -1;
+  b->images = on != 0;
+  return 0;
 }
 B2H_API void b2h_server_use_callback(void* s, GenerateFn fn, void* user, int context_length) {
   auto b = std::make_shared<CallbackBackend>();

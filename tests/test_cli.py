@@ -82,7 +82,8 @@ def test_cli_serve_over_http(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     log = open(tmp_path / "serve.log", "w")
     p = subprocess.Popen([sys.executable, "-u", "-m", "agens_engine_b200", "serve", "--random", "oracle-tiny", "--tokenizer", str(tok),
-                          "--port", "0", "--wctx", "512", "--max-batch", "4", "--spec-copy", "1", "--served-model-name", "tiny"],
+                          "--port", "0", "--wctx", "512", "--max-batch", "4", "--spec-copy", "1", "--served-model-name", "tiny",
+                          "--vision", "1"],
                          cwd=root, stdout=log, stderr=subprocess.STDOUT)
     try:
         port = None
@@ -111,6 +112,15 @@ def test_cli_serve_over_http(tmp_path):
         assert st == 200 and sse.strip().endswith("data: [DONE]") and sse.count("data: ") >= 3
         with urllib.request.urlopen(f"http://127.0.0.1:{port}/v1/models", timeout=10) as r:
             assert "tiny" in r.read().decode()
+        # an image part: decoded, encoded by the vision tower and prefilled with its rows (PPM payload, 96 x 64 pixels)
+        import base64
+        ppm = b"P6\n96 64\n255\n" + bytes((i * 7) % 256 for i in range(64 * 96 * 3))
+        url = "data:image/x-portable-pixmap;base64," + base64.b64encode(ppm).decode()
+        msg = {"role": "user", "content": [{"type": "text", "text": "describe "}, {"type": "image_url", "image_url": {"url": url}}]}
+        st, txt3 = post("/v1/chat/completions", {"model": "tiny", "messages": [msg], "max_tokens": 6, "temperature": 0})
+        assert st == 200 and json.loads(txt3)["usage"]["completion_tokens"] == 6
+        st, txt4 = post("/v1/chat/completions", {"model": "tiny", "messages": [msg], "max_tokens": 6, "temperature": 0})
+        assert json.loads(txt4)["choices"][0]["message"] == json.loads(txt3)["choices"][0]["message"]
     finally:
         p.terminate()
         try:

@@ -155,3 +155,47 @@ def test_engine_keeps_sequences_for_conversations_and_prefix_reuse(tiny):
     e = eng.submit(turn2 + col.toks[d] + [5, 6, 7, 8, 9, 10, 11, 12, 13], {"max_new_tokens": 4}, session="conv")
     eng.run_until_idle(5000)
     assert len(col.toks[e]) == 4 and not col.err
+
+
+def test_engine_serves_a_request_with_images(tiny):
+    """A request with an image part: the engine decodes the data URL, runs the vision tower, expands the placeholder,
+    prefills with the encoder rows and multi-axis positions and decodes with the rotary delta; its tokens equal the
+    direct model calls, also while a text request shares the batch (reference: crates/agens-cli/src/mm.rs)."""
+    import base64
+    import numpy as np
+    from agens_engine_b200.models.vision import VisionConfig, VisionTower
+    from agens_engine_b200.serve import vision as V
+    cfg, ow = tiny
+    tower = VisionTower.random_init(VisionConfig(depth=2, d_model=288, n_heads=4, mlp=608, out_dim=cfg.d_model, pos_grid=12), seed=1)
+    PAD = 7
+    fe = V.VisionFrontEnd(tower, PAD, cfg.head_dim)
+    img = np.random.default_rng(0).integers(0, 256, size=(70, 100, 3), dtype=np.uint8)
+    url = "data:image/x-portable-pixmap;base64," + base64.b64encode(b"P6\n100 70\n255\n" + img.tobytes()).decode()
+    prompt = [20, 21, 22, PAD, 30, 31, 32, 33, 34]
+    mm = fe.prepare(prompt, [url])
+    assert len(mm["ids"]) == len(prompt) - 1 + 6 and mm["rows"].shape == (6, cfg.d_model)      # 64 x 96 pixels: merged grid 2 x 3
+    m = DenseModel.from_oracle(ow, max_seqs=1, max_ctx=512, prefill_chunk=128)
+    m.new_seq(0)
+    tok, _ = m.prefill(0, torch.tensor(mm["ids"]), image_rows=mm["rows"], image_pad_id=PAD, rope_pos3=mm["pos3"],
+                       pair_axis=mm["pair_axis"], rope_next=mm["rope_next"])
+    ref = [tok]
+    for _ in range(7):
+        out, _ = m.forward_rows([ref[-1]], [0])
+        ref.append(int(out[0]))
+    assert m.rope_delta[0] == mm["rope_next"] - len(mm["ids"]) != 0
+
+    col = Collector()
+    eng = Engine(DenseModel.from_oracle(ow, max_seqs=2, max_ctx=512, prefill_chunk=128), col, max_batch=2, vision=fe)
+    a = eng.submit(prompt, {"max_new_tokens": 8, "ignore_eos": True}, images=[url])
+    b = eng.submit(list(range(40, 60)), {"max_new_tokens": 8, "ignore_eos": True})
+    eng.run_until_idle()
+    assert col.toks[a] == ref and len(col.toks[b]) == 8 and not col.err
+    assert col.toks[b] == _alone(ow, list(range(40, 60)), 8)
+    assert eng.stats.images_encoded == 1
+
+    col2 = Collector()
+    eng2 = Engine(DenseModel.from_oracle(ow, max_seqs=1, max_ctx=512, prefill_chunk=128), col2)
+    c = eng2.submit(prompt, {"max_new_tokens": 4}, images=[url])
+    d = eng2.submit(prompt, {"max_new_tokens": 4}, images=["data:image/png;base64,AAAA"])
+    eng2.run_until_idle()
+    assert "images" in col2.err[c] and col2.done[c] and col2.done[d]

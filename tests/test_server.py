@@ -205,3 +205,28 @@ def test_detokenizer_never_emits_invalid_utf8():
     text = "".join(pieces)
     assert text == "�a�bé�"
     assert tk.stream_decode(tk.encode("héllo ✓ wörld"), 2)[-1] == "" and "".join(tk.stream_decode(tk.encode("héllo ✓ wörld"), 2)) == "héllo ✓ wörld"
+
+
+def test_image_parts_reach_the_engine_callback(tok_path, tok_text):
+    """image_url parts: refused unless the backend takes images; otherwise one placeholder in the prompt per image and
+    the URLs, in order, under sampling["images"] (reference: crates/agens-server/src/openai.rs content-part handling)."""
+    sv = S.Server(tok_path, model_name="m")
+    seen = {}
+
+    def generate(req_id, prompt, sampling, session):
+        seen["sampling"] = sampling
+        sv.push(req_id, [], finished=True)
+
+    url = "data:image/png;base64,AAAA"
+    body = {"messages": [{"role": "user", "content": [{"type": "text", "text": "what is "}, {"type": "image_url", "image_url": {"url": url}},
+                                                     {"type": "image_url", "image_url": {"url": url + "BB"}}]}], "max_tokens": 4}
+    sv.use_engine(generate, context_length=4096)
+    status, resp = sv.handle("POST", "/v1/chat/completions", body)
+    assert status == 400 and "images" in json.loads(resp)["error"]["message"]
+    sv.use_engine(generate, context_length=4096, supports_images=True)
+    status, resp = sv.handle("POST", "/v1/chat/completions", body)
+    assert status == 200
+    assert seen["sampling"]["images"] == [url, url + "BB"]
+    body["messages"][0]["content"][1]["image_url"]["url"] = "http://example.com/x.png"
+    status, resp = sv.handle("POST", "/v1/chat/completions", body)
+    assert status == 400
