@@ -127,3 +127,28 @@ def test_cli_serve_over_http(tmp_path):
             p.wait(timeout=20)
         except subprocess.TimeoutExpired:
             p.kill()
+
+
+def test_deploy_entry_and_launcher_command_lines(tmp_path, capsys):
+    """Container entry point and host launcher (reference: scripts/agens-entry.sh, scripts/agens-run.sh)."""
+    from agens_engine_b200.deploy import entry, run
+    a = entry.serve_argv(["--profile", "48gb", "--model", "/m", "--drafter", "/d", "--mtp", "/h", "--images", "on", "--tp", "4",
+                          "--", "--max-batch", "8"])
+    assert a == ["serve", "--model-dir", "/m", "--host", "0.0.0.0", "--port", "30000", "--profile", "48gb", "--vision", "1",
+                 "--spec-drafter", "/d", "--mtp", "/h", "--tp", "4", "--max-batch", "8"]
+    assert entry.serve_argv([])[:3] == ["serve", "--model-dir", "/model"] and "--tp" not in entry.serve_argv([])
+    for bad in (["--profile", "7gb"], ["--images", "maybe"], ["--tp", "3"], ["--model"]):
+        with pytest.raises(SystemExit):
+            entry.serve_argv(bad)
+    # the flags the entry point emits are flags `serve` knows
+    from agens_engine_b200 import cli
+    with pytest.raises(SystemExit) as e:
+        cli.main(a + ["--help"])
+    assert e.value.code == 0
+    capsys.readouterr()
+    d = run.docker_argv(["--model", str(tmp_path), "--tp", "2", "--gpu", "0,1", "--port", "8000", "--dry-run", "--", "--wctx", "4096"])
+    assert d[:2] == ["echo", "docker"] and "--ipc=host" in d and f"{tmp_path}:/model:ro" in d and d[-3:] == ["--", "--wctx", "4096"]
+    assert d[d.index("-p") + 1] == "8000:30000" and d[d.index("--tp") + 1] == "2"
+    with pytest.raises(SystemExit):
+        run.docker_argv(["--model", str(tmp_path), "--tp", "4", "--gpu", "0"])
+    assert run.main(["--model", str(tmp_path), "--dry-run"]) == 0 and "docker run" in capsys.readouterr().out
