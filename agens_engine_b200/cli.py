@@ -372,8 +372,16 @@ def cmd_serve(ns):
     if cfg.model_dir and os.path.exists(os.path.join(cfg.model_dir, "generation_config.json")):
         gen_cfg = json.load(open(os.path.join(cfg.model_dir, "generation_config.json")))
     eos = gen_cfg.get("eos_token_id", [])
+    # the checkpoint's own chat template, when it ships one (else the built-in ChatML renderer)
+    tcfg_path = os.path.join(os.path.dirname(tok_path), "tokenizer_config.json")
+    tcfg = json.load(open(tcfg_path)) if os.path.exists(tcfg_path) else {}
+    special = lambda v: v.get("content", "") if isinstance(v, dict) else (v or "")
+    template = tcfg.get("chat_template") or ""
+    if isinstance(template, list):                       # named templates: take the default one
+        template = next((t.get("template", "") for t in template if t.get("name") == "default"), "")
     srv = Server(tok_path, model_name=cfg.served_model_name, generation_config=gen_cfg,
-                 eos_token_ids=eos if isinstance(eos, list) else [eos], max_tokens_default=cfg.max_tokens_default)
+                 eos_token_ids=eos if isinstance(eos, list) else [eos], max_tokens_default=cfg.max_tokens_default,
+                 chat_template=template, bos_token=special(tcfg.get("bos_token")), eos_token=special(tcfg.get("eos_token")))
     # ids the tokenizer does not know (padding rows of the embedding) are never produced
     tj = json.load(open(tok_path))
     n_tok = 1 + max([max(tj["model"]["vocab"].values(), default=0)] + [int(t["id"]) for t in tj.get("added_tokens", [])])

@@ -27,7 +27,7 @@ def _h():
             "b2h_tok_decode": ([vp, ip, i, i], vp), "b2h_detok_new": ([vp, i], vp), "b2h_detok_free": ([vp], None),
             "b2h_detok_push": ([vp, ip, i], vp), "b2h_detok_finish": ([vp], vp),
             "b2h_render_chat": ([cp, cp, i, i, i], vp), "b2h_parse_output": ([cp, cp, i, i], vp),
-            "b2h_free_str": ([vp], None),
+            "b2h_free_str": ([vp], None), "b2h_render_template": ([cp, cp, cp, i], vp),
         }
         for name, (args, res) in sig.items():
             fn = getattr(h, name)
@@ -83,15 +83,27 @@ def render_chat(messages: list, tools: Optional[list] = None, add_generation_pro
                                       int(add_generation_prompt), int(enable_thinking), int(continue_final)))
 
 
+def render_template(source: str, **context) -> str:
+    """Renders a Jinja chat template (the subset that chat templates use) with ``context`` as its variables."""
+    err = C.create_string_buffer(512)
+    p = _h().b2h_render_template(source.encode(), json.dumps(context).encode(), err, 512)
+    if not p:
+        raise ValueError(err.value.decode(errors="replace"))
+    return _take(p)
+
+
 def parse_output(text: str, tools: Optional[list] = None, starts_in_reasoning: bool = False, chunk: int = 0) -> dict:
     return json.loads(_take(_h().b2h_parse_output(text.encode(), json.dumps(tools or []).encode(), int(starts_in_reasoning), chunk)))
 
 
 class Server:
     def __init__(self, tokenizer_json: str, model_name: str = "b200-engine", generation_config: Optional[dict] = None,
-                 eos_token_ids: Sequence[int] = (), max_tokens_default: int = 32768):
+                 eos_token_ids: Sequence[int] = (), max_tokens_default: int = 32768, chat_template: str = "",
+                 bos_token: str = "", eos_token: str = ""):
+        """``chat_template``: Jinja source (``tokenizer_config.json``); empty selects the built-in ChatML renderer."""
         cfg = {"tokenizer_json": tokenizer_json, "model_name": model_name, "generation_config": generation_config or {},
-               "eos_token_ids": list(eos_token_ids), "max_tokens_default": max_tokens_default}
+               "eos_token_ids": list(eos_token_ids), "max_tokens_default": max_tokens_default, "chat_template": chat_template,
+               "bos_token": bos_token, "eos_token": eos_token}
         err = C.create_string_buffer(256)
         self._s = _h().b2h_server_new(json.dumps(cfg).encode(), err, 256)
         if not self._s:

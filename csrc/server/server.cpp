@@ -124,6 +124,8 @@ struct Server {
   Json gen_defaults = Json::object();      // generation_config.json: temperature, top_k, top_p
   std::vector<int> eos_ids;
   long long max_tokens_default = 32768;
+  std::string chat_template;               // Jinja source from tokenizer_config.json; empty = the built-in ChatML renderer
+  std::string bos_token, eos_token;
   std::shared_ptr<Backend> backend;
   std::atomic<long long> next_req{1}, n_requests{0}, n_prompt_tokens{0}, n_completion_tokens{0}, n_errors{0};
   int listen_fd = -1;
@@ -424,7 +426,47 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
   if (body.get_string("reasoning_effort", "") == "none") enable_thinking = false;
   const bool cont = body.get_bool("continue_final_message", false);
   const Json tools = body.find("tools") && body.at("tools").is_array() && body.get_string("tool_choice", "auto") != "none" ? body.at("tools") : Json::array();
-  const std::string prompt = render_chatml(msgs, tools, !cont, enable_thinking, cont);
+  std::string prompt;
+  if (sv.chat_template.empty()) prompt = render_chatml(msgs, tools, !cont, enable_thinking, cont);
+  else {
+    // the checkpoint's own template: messages as the template families expect them (tool-call arguments as objects)
+    Json jm = Json::array();
+    for (auto& m : msgs) {
+      Json o = Json::object();
+      o.set("role", m.role); o.set("content", m.content);
+      if (!m.reasoning.empty()) o.set("reasoning_content", m.reasoning);
+      if (m.tool_calls.is_array() && m.tool_calls.size()) {
+        Json calls = Json::array();
+        for (auto& tc : m.tool_calls.items()) {
+          Json call = tc;
+          if (const Json* fn = tc.find("function"); fn && fn->is_object()) {
+            Json f = *fn;
+            if (const Json* a = fn->find("arguments"); a && a->is_string()) { try { f.set("arguments", Json::parse(a->as_string())); } catch (const std::exception&) {} }
+            call.set("function", f);
+          }
+          calls.push_back(call);
+        }
+        o.set("tool_calls", calls);
+      }
+      if (!m.tool_call_id.empty()) o.set("tool_call_id", m.tool_call_id);
+      jm.push_back(o);
+    }
+    Json ctx = Json::object();
+    ctx.set("messages", jm);
+    if (tools.size()) ctx.set("tools", tools);
+    ctx.set("add_generation_prompt", !cont);
+    ctx.set("enable_thinking", enable_thinking);
+    ctx.set("bos_token", sv.bos_token); ctx.set("eos_token", sv.eos_token);
+    if (auto k = body.find("chat_template_kwargs"); k && k->is_object()) for (auto& kv : k->members()) ctx.set(kv.first, kv.second);
+    try { prompt = render_jinja(sv.chat_template, ctx); }
+    catch (const std::exception& e) { return error_response(400, std::string("chat template: ") + e.what()); }
+    if (cont && !msgs.empty()) {
+      // continue_final_message: cut the rendering after the last message's content (the turn stays open)
+      const std::string& last = msgs.back().content;
+      const size_t at = last.empty() ? std::string::npos : prompt.rfind(last);
+      if (at != std::string::npos) prompt.resize(at + last.size());
+    }
+  }
   Json sampling;
   if (std::string e = build_sampling(sv, body, true, sampling); !e.empty()) return error_response(400, e);
   if (auto rb = body.find("reasoning_budget"); rb && rb->is_number()) sampling.set("reasoning_budget", rb->as_int());
@@ -559,6 +601,9 @@ B2H_API void* b2h_server_new(const char* config_json, char* err, int err_cap) {
     if (auto g = c.find("generation_config"); g && g->is_object()) sv->gen_defaults = *g;
     if (auto e = c.find("eos_token_ids"); e && e->is_array()) for (auto& v : e->items()) sv->eos_ids.push_back((int)v.as_int());
     sv->max_tokens_default = c.get_int("max_tokens_default", 32768);
+    sv->chat_template = c.get_string("chat_template", "");
+    sv->bos_token = c.get_string("bos_token", "");
+    sv->eos_token = c.get_string("eos_token", "");
     sv->backend = std::make_shared<MockBackend>();
     return sv;
   } catch (const std::exception& e) { if (err) snprintf(err, err_cap, "%s", e.what()); return nullptr; }
@@ -668,6 +713,15 @@ B2H_API char* b2h_render_chat(const char* messages_json, const char* tools_json,
   } catch (const std::exception& e) { return dup_cstr(std::string("ERROR: ") + e.what()); }
 }
 // Parses text in chunks of `chunk` bytes (0 = at once); returns {"content", "reasoning", "tool_calls": [{name, arguments}]}.
+// Renders a Jinja chat template with a JSON object of variables.  On failure returns null and writes the message to err.
+B2H_API char* b2h_render_template(const char* source, const char* context_json, char* err, int err_cap) {
+  try {
+    return dup_cstr(render_jinja(source, Json::parse(context_json)));
+  } catch (const std::exception& e) {
+    if (err && err_cap > 0) { std::strncpy(err, e.what(), (size_t)err_cap - 1); err[err_cap - 1] = 0; }
+    return nullptr;
+  }
+}
 B2H_API char* b2h_parse_output(const char* text, const char* tools_json, int starts_in_reasoning, int chunk) {
   Json tools = tools_json && *tools_json ? Json::parse(tools_json) : Json::array();
   std::string t = text, content, reasoning;

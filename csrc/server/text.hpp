@@ -51,6 +51,9 @@ struct ChatMessage { std::string role, content, reasoning; Json tool_calls; std:
 std::string render_chatml(const std::vector<ChatMessage>& msgs, const Json& tools, bool add_generation_prompt,
                           bool enable_thinking, bool continue_final);
 
+// Renders a Jinja chat template (the subset in jinja.cpp) with the variables of `context`; throws std::runtime_error.
+std::string render_jinja(const std::string& source, const Json& context);
+
 // Splits generated text into reasoning and content around <think> ... </think>.
 class ReasoningParser {
  public:
