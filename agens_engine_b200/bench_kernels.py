@@ -85,6 +85,7 @@ def bench_gemv(args):
     dev = "cuda:0"
     pk = peaks()
     ws = L.GemvWorkspace(dev, floats=16 << 20)
+    ws.mm_min_rows = 33                      # times the GEMV family itself; above 8 rows its activation staging only fits small k slices
     shapes = [("qkv", 10240, 5120), ("o", 5120, 8192), ("gate_up", 51200, 5120), ("down", 5120, 25600),
               ("lm_head", 151936, 5120)]
     if args.small:

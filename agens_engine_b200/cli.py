@@ -355,7 +355,7 @@ def cmd_serve(ns):
     if cfg.mtp and world == 1:
         from .models.mtp import MtpHead
         sources.append(MtpSource(MtpHead.random_init_for(m), depth=min(cfg.draft_depth, 2)))
-    if cfg.spec_drafter and world == 1:
+    if cfg.spec_drafter:                                  # under --tp the drafter lives beside the leader, unsharded
         from .models.dense import DenseModel
         dcfg = _named_config(cfg.spec_drafter) if not os.path.isdir(cfg.spec_drafter) else None
         if dcfg is None:

@@ -149,6 +149,16 @@ def main():
             t16 = serve16(reqs)
             a16 = [serve16([r])[0] for r in reqs]
             assert t16 == a16 and all(len(t) == 12 for t in t16), (t16, a16)
+            # a companion drafter beside the leader (a plain single-GPU model on rank 0): same tokens, drafts accepted
+            from agens_engine_b200.spec import CopyLookupSource, ModelSource
+            drafter = DenseModel.from_oracle(ow, dev, max_seqs=4, max_ctx=256)
+            got = {}
+            eng = Engine(drv, lambda rid, t, f, e: got.setdefault(rid, []).extend(t) or False, max_batch=4, max_drafts=3,
+                         sources_factory=lambda: [CopyLookupSource(), ModelSource(drafter, 3)])
+            rids = [eng.submit(p, s) for p, s in reqs]
+            eng.run_until_idle(5000)
+            assert [got[r] for r in rids] == t16, ([got[r] for r in rids], t16)
+            assert eng.spec.stats.accepted > 0
             drv.set_linear_path(None)
             assert all(len(t) == 12 for t in together) and together[3] != together[0]
             blob = None
