@@ -278,6 +278,42 @@ def profile_attn(args):
     print("profile_attn done")
 
 
+def profile_misc(args):
+    """Plain launches of the small kernels of a step on 32B shapes, for a profiler capture: RoPE + paged KV store of a
+    2048-row chunk, RMSNorm of 2048 x 5120, the sampler on 32 rows of a 151936-entry vocabulary, and two blocks of the
+    vision tower (full width) on a 448 x 448 image."""
+    from .models.vision import VisionConfig, VisionTower
+    from .ops import basic as B
+    from .serve import vision as V
+    import numpy as np
+    dev = "cuda:0"
+    hq, hkv, hd, n = 64, 8, 128, 2048
+    qkv = torch.randn(n, (hq + 2 * hkv) * hd, device=dev).to(torch.bfloat16)
+    inv_freq = (1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float32) / hd))).to(dev)
+    pos = torch.arange(n, dtype=torch.int32, device=dev)
+    seq = torch.zeros(n, dtype=torch.int32, device=dev)
+    n_pages = n // 16 + 1
+    bt = torch.arange(n_pages, dtype=torch.int32, device=dev)[None, :].contiguous()
+    pool = torch.zeros(n_pages, 2, hkv, 16, hd, dtype=torch.bfloat16, device=dev)
+    q_out = torch.empty(n, hq * hd, dtype=torch.bfloat16, device=dev)
+    x = torch.randn(n, 5120, device=dev).to(torch.bfloat16)
+    w = torch.ones(5120, dtype=torch.bfloat16, device=dev)
+    logits = torch.randn(32, 151936, device=dev)
+    temp = torch.full((32,), 0.7, device=dev); top_p = torch.full((32,), 0.9, device=dev)
+    top_k = torch.full((32,), 50, dtype=torch.int32, device=dev)
+    seed = torch.arange(32, dtype=torch.int64, device=dev); position = torch.arange(32, dtype=torch.int32, device=dev)
+    tower = VisionTower.random_init(VisionConfig(depth=2, out_dim=5120), dev, seed=0)
+    img = np.random.default_rng(0).integers(0, 256, size=(448, 448, 3), dtype=np.uint8)
+    patches, grid = V.preprocess(img)
+    for _ in range(2):
+        B.rope_kvstore(qkv, hq, hkv, hd, inv_freq, pos, seq, bt, pool, q_out)
+        B.rmsnorm(x, w, 1e-6)
+        B.sample_rows(logits, temp, top_k, top_p, None, seed, position)
+        tower.encode(torch.from_numpy(patches), grid)
+    torch.cuda.synchronize()
+    print("profile_misc done")
+
+
 def profile_gemm(args):
     """Three plain launches of the bf16 tcgen05 GEMM (gate/up shape, 2048 rows) for a profiler capture."""
     from .ops import gemm as G
@@ -293,7 +329,7 @@ def profile_gemm(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_gemm"])
+    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_gemm", "profile_misc"])
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--ks", type=int, default=0)
     ap.add_argument("--m", type=int, default=1)
@@ -319,6 +355,8 @@ def main(argv=None):
         profile_attn(args)
     elif args.what == "profile_gemm":
         profile_gemm(args)
+    elif args.what == "profile_misc":
+        profile_misc(args)
     else:
         raise SystemExit(f"{args.what}: not available yet")
 
