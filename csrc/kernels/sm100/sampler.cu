@@ -60,6 +60,35 @@ __device__ float block_reduce_sum(float v, float* sh) {
   __syncthreads();
   return s;
 }
+// Probability masses are fixed point (exp of a non-positive number times 2^31, so one mass fits 32 bits): integer sums
+// do not depend on the order of the additions, so every threshold of the sampler is exactly reproducible.  A histogram
+// bin is a (low, high) pair of 32-bit words: 32-bit shared-memory integer atomics are single instructions, where float
+// and 64-bit ones are compare-and-swap loops; the carry into the high word is a second, rare, atomic.
+__device__ __forceinline__ unsigned long long mass_of(float xv, float mx, float inv_t) {
+  return (unsigned long long)(__expf((xv - mx) * inv_t) * 2147483648.f);
+}
+struct Hist { uint32_t lo[256], hi[256]; };
+__device__ __forceinline__ void hist_add(Hist& h, uint32_t dig, unsigned long long v) {
+  const uint32_t lo = (uint32_t)v;
+  uint32_t hi = (uint32_t)(v >> 32);
+  if (lo) { const uint32_t old = atomicAdd(&h.lo[dig], lo); hi += (old + lo < old) ? 1u : 0u; }
+  if (hi) atomicAdd(&h.hi[dig], hi);
+}
+__device__ __forceinline__ unsigned long long hist_get(const Hist& h, int d) { return ((unsigned long long)h.hi[d] << 32) | h.lo[d]; }
+__device__ __forceinline__ unsigned long long warp_sum_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ unsigned long long block_reduce_sum_u64(unsigned long long v, unsigned long long* sh) {
+  v = warp_sum_u64(v);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
+  __syncthreads();
+  unsigned long long s = 0;
+  for (int i = 0; i < kThreads / 32; ++i) s += sh[i];
+  __syncthreads();
+  return s;
+}
 __device__ float block_reduce_max(float v, float* sh) {
   v = warp_max(v);
   if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
@@ -70,28 +99,67 @@ __device__ float block_reduce_max(float v, float* sh) {
   return s;
 }
 
+// One pass over a row: f(value, index, valid) for every element, the same number of calls on every thread (so f may
+// use warp-wide primitives), with eight elements per thread in flight (two 16-byte loads) where the row allows it:
+// with one element per iteration a pass is bound by the latency of its loads, not by bandwidth.
+template <typename F>
+__device__ __forceinline__ void scan_row(const float* x, int n, F f) {
+  const int n4 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 ? n >> 2 : 0;
+  const float4* x4 = reinterpret_cast<const float4*>(x);
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int base = 0; base < n4; base += 2 * kThreads) {
+    const int i0 = base + (int)threadIdx.x, i1 = i0 + kThreads;
+    const bool v0 = i0 < n4, v1 = i1 < n4;
+    const float4 a = v0 ? x4[i0] : zero;
+    const float4 b = v1 ? x4[i1] : zero;
+    f(a.x, 4 * i0, v0); f(a.y, 4 * i0 + 1, v0); f(a.z, 4 * i0 + 2, v0); f(a.w, 4 * i0 + 3, v0);
+    f(b.x, 4 * i1, v1); f(b.y, 4 * i1 + 1, v1); f(b.z, 4 * i1 + 2, v1); f(b.w, 4 * i1 + 3, v1);
+  }
+  for (int base = 4 * n4; base < n; base += kThreads) {
+    const int i = base + (int)threadIdx.x;
+    f(i < n ? x[i] : 0.f, i, i < n);
+  }
+}
+
 // Radix descent: finds the largest key prefix such that the mass of all elements with a strictly larger key is
 // <= target (mass = probability or count).  On return *above = mass strictly above the final key, *at = mass of
 // elements equal to the final key.  `keep_min`: elements with key < keep_min are ignored.
 template <bool COUNT>
-__device__ uint32_t radix_descend(const float* x, int n, float mx, float inv_t, uint32_t keep_min, float target, float* hist,
-                                  float* above_out, float* at_out) {
+__device__ uint32_t radix_descend(const float* x, int n, float mx, float inv_t, uint32_t keep_min, unsigned long long target,
+                                  Hist& hist, unsigned long long* above_out, unsigned long long* at_out) {
   uint32_t prefix = 0, mask = 0;
-  float above = 0.f, at = 0.f;
+  unsigned long long above = 0, at = 0;
   for (int shift = 24; shift >= 0; shift -= 8) {
-    for (int i = threadIdx.x; i < 256; i += kThreads) hist[i] = 0.f;
+    for (int i = threadIdx.x; i < 256; i += kThreads) { hist.lo[i] = 0; hist.hi[i] = 0; }
     __syncthreads();
-    for (int i = threadIdx.x; i < n; i += kThreads) {
-      const uint32_t k = key_of(x[i]);
-      if (k >= keep_min && (k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], COUNT ? 1.f : __expf((x[i] - mx) * inv_t));
-    }
+    // Logits crowd into a few digits at the upper levels, where one shared-memory atomic per element would serialise
+    // the warp: lanes that share a digit with at least seven others are summed in registers first and their leader
+    // adds once; the rest add for themselves.
+    const int lane = threadIdx.x & 31;
+    scan_row(x, n, [&](float xv, int, bool valid) {
+      const uint32_t k = key_of(xv);
+      const bool on = valid && k >= keep_min && (k & mask) == prefix;
+      const uint32_t dig = on ? (k >> shift) & 255u : 0xFFFFFFFFu;
+      const unsigned long long v = !on ? 0ull : (COUNT ? 1ull : mass_of(xv, mx, inv_t));
+      const unsigned peers = __match_any_sync(0xffffffffu, dig);
+      const bool big = on && __popc(peers) >= 8;
+      unsigned pending = __ballot_sync(0xffffffffu, big);
+      while (pending) {
+        const int leader = __ffs(pending) - 1;
+        const unsigned grp = __shfl_sync(0xffffffffu, peers, leader);
+        const unsigned long long sum = COUNT ? (unsigned long long)__popc(grp) : warp_sum_u64(((grp >> lane) & 1u) ? v : 0ull);
+        if (lane == leader) hist_add(hist, dig, sum);
+        pending &= ~grp;
+      }
+      if (on && !big) hist_add(hist, dig, v);
+    });
     __syncthreads();
     // walk digits from high to low until the running mass passes the target (every thread does the same walk)
     int d = 255;
-    float run = above;
-    for (; d > 0; --d) { if (run + hist[d] > target) break; run += hist[d]; }
+    unsigned long long run = above;
+    for (; d > 0; --d) { const unsigned long long hd = hist_get(hist, d); if (run + hd > target) break; run += hd; }
     above = run;
-    at = hist[d];
+    at = hist_get(hist, d);
     prefix |= (uint32_t)d << shift;
     mask |= 255u << shift;
     __syncthreads();
@@ -103,28 +171,26 @@ __device__ uint32_t radix_descend(const float* x, int n, float mx, float inv_t, 
 
 }  // namespace
 
-// Note on determinism: shared-memory float atomics are order dependent in the last bits; thresholds that decide token
-// identity are therefore taken on counts (exact) or compared with a margin-free walk whose only ambiguity is between
-// equal keys, which the index rule resolves.  The probability-mass histograms feed only the top-p cut and the final
-// walk; both compare against masses accumulated in the same pass, so a different summation order can move the draw
-// only when u falls within one ulp-scale sliver of a bin boundary.
+// Determinism: counts and fixed-point masses are integers, so every histogram, threshold and the final walk are
+// independent of the order in which threads add; equal keys are ordered by token index.
 __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const SampleArgs a) {
   __shared__ float sh[kThreads / 32];
-  __shared__ float hist[256];
+  __shared__ unsigned long long sh64[kThreads / 32];
+  __shared__ Hist hist;
   pdl_wait();
   pdl_launch_dependents();
   const int row = blockIdx.x;
   const float* x = a.logits + (size_t)row * a.ld;
   const int n = a.vocab;
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < n; i += kThreads) mx = fmaxf(mx, x[i]);
+  scan_row(x, n, [&](float xv, int, bool valid) { if (valid) mx = fmaxf(mx, xv); });
   mx = block_reduce_max(mx, sh);
   const float T = a.temperature ? a.temperature[row] : 0.f;
   const int topk = a.top_k ? a.top_k[row] : 0;
   if (T <= 0.f || topk == 1) {
     // greedy: lowest index among the maxima
     int best = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += kThreads) if (x[i] == mx) best = min(best, i);
+    scan_row(x, n, [&](float xv, int i, bool valid) { if (valid && xv == mx) best = min(best, i); });
     __shared__ int sbest[kThreads / 32];
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
@@ -140,34 +206,36 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const SampleArgs 
   if (minp > 0.f) keep_min = max(keep_min, key_of(mx + T * __logf(minp)));
   // top-k: key of the k-th largest logit (ties at the threshold are all kept; the index rule orders them)
   if (topk > 1 && topk < n) {
-    float above, at;
-    const uint32_t kth = radix_descend<true>(x, n, mx, inv_t, 0u, (float)topk - 0.5f, hist, &above, &at);
+    unsigned long long above, at;
+    const uint32_t kth = radix_descend<true>(x, n, mx, inv_t, 0u, (unsigned long long)(topk - 1), hist, &above, &at);
     keep_min = max(keep_min, kth);
   }
   // top-p over what is left: smallest descending prefix whose mass reaches top_p * Z
   const float topp = a.top_p ? a.top_p[row] : 1.f;
   if (topp < 1.f) {
-    float z = 0.f;
-    for (int i = threadIdx.x; i < n; i += kThreads) if (key_of(x[i]) >= keep_min) z += __expf((x[i] - mx) * inv_t);
-    z = block_reduce_sum(z, sh);
-    float above, at;
-    const uint32_t cut = radix_descend<false>(x, n, mx, inv_t, keep_min, topp * z, hist, &above, &at);
+    unsigned long long z = 0;
+    scan_row(x, n, [&](float xv, int, bool valid) { if (valid && key_of(xv) >= keep_min) z += mass_of(xv, mx, inv_t); });
+    z = block_reduce_sum_u64(z, sh64);
+    unsigned long long above, at;
+    const uint32_t cut = radix_descend<false>(x, n, mx, inv_t, keep_min, (unsigned long long)((double)topp * (double)z), hist, &above, &at);
     keep_min = max(keep_min, cut);
   }
   // draw
-  float z = 0.f;
-  for (int i = threadIdx.x; i < n; i += kThreads) if (key_of(x[i]) >= keep_min) z += __expf((x[i] - mx) * inv_t);
-  z = block_reduce_sum(z, sh);
+  unsigned long long z = 0;
+  scan_row(x, n, [&](float xv, int, bool valid) { if (valid && key_of(xv) >= keep_min) z += mass_of(xv, mx, inv_t); });
+  z = block_reduce_sum_u64(z, sh64);                         // at least 2^31: the maximum always survives the filters
   const uint32_t r = philox_first(a.seed ? a.seed[row] : 0ull, (unsigned long long)(a.position ? a.position[row] : 0));
-  const float u = ((float)(r >> 8) + 0.5f) * (1.0f / 16777216.0f);
-  const float target = fminf(u * z, z * (1.f - 1e-7f));
-  float above, at;
+  const double u = ((double)(r >> 8) + 0.5) * (1.0 / 16777216.0);
+  unsigned long long target = (unsigned long long)(u * (double)z);
+  if (z > 0 && target >= z) target = z - 1;
+  unsigned long long above, at;
   const uint32_t key = radix_descend<false>(x, n, mx, inv_t, keep_min, target, hist, &above, &at);
   // among the tokens that share the final key, walk by ascending index: the `want`-th of them wins
-  const float w = __expf((__uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key) - mx) * inv_t);
-  const int rank = w > 0.f ? (int)fminf(floorf(fmaxf(target - above, 0.f) / w), 1e9f) : 0;
+  const unsigned long long w = mass_of(__uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key), mx, inv_t);
+  const unsigned long long rank64 = w > 0 && target > above ? (target - above) / w : 0ull;
+  const int rank = (int)(rank64 > 1000000000ull ? 1000000000ull : rank64);
   float cnt = 0.f;
-  for (int i = threadIdx.x; i < n; i += kThreads) cnt += key_of(x[i]) == key ? 1.f : 0.f;
+  scan_row(x, n, [&](float xv, int, bool valid) { cnt += valid && key_of(xv) == key ? 1.f : 0.f; });
   cnt = block_reduce_sum(cnt, sh);                          // exact: integers below 2^24
   const int want = min(rank, max((int)cnt - 1, 0));
   if ((int)cnt == 0) {                                       // rounding pushed the walk past the last bin: take the mode
@@ -180,7 +248,7 @@ __global__ void __launch_bounds__(kThreads) sample_rows_kernel(const SampleArgs 
     return;
   }
   if ((int)cnt == 1) {                                       // the usual case: one token owns the key
-    for (int i = threadIdx.x; i < n; i += kThreads) if (key_of(x[i]) == key) a.out[row] = i;
+    scan_row(x, n, [&](float xv, int i, bool valid) { if (valid && key_of(xv) == key) a.out[row] = i; });
     return;
   }
   // smallest index I with (number of equal-key tokens at index <= I) == want + 1, by bisection over the index range
