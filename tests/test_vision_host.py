@@ -90,3 +90,37 @@ def test_placeholders_positions_and_decoders():
     assert V.load_url(url) == png and V.image_key(png) == V.image_key(png)
     with pytest.raises(ValueError):
         V.decode_image(b"\xff\xd8\xff\xe0")
+
+
+def test_front_end_expands_placeholders_and_positions_with_a_stub_tower():
+    """VisionFrontEnd.prepare on the CPU with a stand-in encoder: one placeholder per image becomes one token per merged
+    patch, rows and multi-axis positions line up, bad inputs raise ValueError (reference: crates/agens-cli/src/mm.rs)."""
+    import base64
+    import torch
+
+    class StubTower:
+        def encode(self, patches, grid):
+            gh, gw = grid
+            assert patches.shape == (gh * gw, 1536)
+            return torch.full((gh * gw // 4, 32), float(gh * 100 + gw), dtype=torch.bfloat16)
+
+    PAD = 9
+    fe = V.VisionFrontEnd(StubTower(), PAD, head_dim=64)
+    assert fe.pair_axis.numel() == 32
+
+    def ppm(w, h):
+        return "data:image/x-portable-pixmap;base64," + base64.b64encode(b"P6\n%d %d\n255\n" % (w, h) + bytes(w * h * 3)).decode()
+
+    prompt = [1, 2, PAD, 3, PAD, 4]
+    mm = fe.prepare(prompt, [ppm(96, 64), ppm(64, 128)])          # merged grids 2 x 3 and 4 x 2
+    assert mm["ids"] == [1, 2] + [PAD] * 6 + [3] + [PAD] * 8 + [4]
+    assert mm["rows"].shape == (14, 32) and float(mm["rows"][0, 0]) == 406.0 and float(mm["rows"][6, 0]) == 804.0
+    assert tuple(mm["pos3"].shape) == (3, len(mm["ids"])) and len(mm["keys"]) == 2 and mm["keys"][0] != mm["keys"][1]
+    # text advances all axes together; an image advances the running position by max(grid)
+    assert mm["pos3"][:, 1].tolist() == [1, 1, 1] and mm["rope_next"] == len(mm["ids"]) - 6 - 8 + 3 + 4
+    with pytest.raises(ValueError):
+        fe.prepare(prompt, [ppm(96, 64)])                            # two placeholders, one image
+    with pytest.raises(ValueError):
+        fe.prepare([1, PAD], ["http://example.com/a.png"])
+    with pytest.raises(ValueError):
+        fe.prepare([1, PAD], ["data:image/jpeg;base64," + base64.b64encode(b"\xff\xd8\xff\xe0").decode()])
