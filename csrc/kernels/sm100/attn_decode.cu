@@ -43,7 +43,8 @@ struct AttnDecodeArgs {
 namespace {
 
 constexpr int kPage = 16;
-constexpr int kStages = 3;      // 96 KB per 4-warp CTA: two CTAs per SM (registers allow two as well)
+constexpr int kStages = 3;      // CTA-shared ring (prefill chunks, verify blocks): 24 KB per CTA
+constexpr int kStagesWarp = 2;  // per-warp rings (decode): 64 KB per 4-warp CTA, three CTAs per SM (registers allow three)
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -117,13 +118,14 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
     rmask[i] = (a.tree_mask && rvalid[i]) ? a.tree_mask[rtok[i]] : 0xffffffffu;
   }
 
-  uint8_t* wsm = smem + (SHARED ? (size_t)0 : (size_t)warp * kStages * 2 * PAGE_B);
+  constexpr int ST = SHARED ? kStages : kStagesWarp;
+  uint8_t* wsm = smem + (SHARED ? (size_t)0 : (size_t)warp * ST * 2 * PAGE_B);
   const uint32_t wsm_u = smem_u32(wsm);
   const int* bt = a.block_table + (size_t)seq * a.bt_ld;
   if (bt[k_begin / kPage] == -2) return;   // split lives in the host tier: a staged launch fills its slot
 
   auto issue_page = [&](int pi) {
-    const int stage = pi % kStages;
+    const int stage = pi % ST;
     int page = bt[(k_begin / kPage) + pi];
     if (page < 0 || page >= a.n_pages) { atomicExch(a.status, (int)B2_ERR_BOUNDS); page = 0; }
     const uint8_t* kp = reinterpret_cast<const uint8_t*>(a.kv_pool) + (((size_t)page * 2 + 0) * a.hkv + kvh) * PAGE_B;
@@ -140,7 +142,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
 
   // prefetch
 #pragma unroll
-  for (int pi = 0; pi < kStages - 1; ++pi) {
+  for (int pi = 0; pi < ST - 1; ++pi) {
     if (pi < n_pg) issue_page(pi);
     cp_async_commit();
   }
@@ -170,11 +172,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(const AttnDecodeArgs a
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
 
   for (int pi = 0; pi < n_pg; ++pi) {
-    if (pi + kStages - 1 < n_pg) issue_page(pi + kStages - 1);
+    if (pi + ST - 1 < n_pg) issue_page(pi + ST - 1);
     cp_async_commit();
-    cp_async_wait<kStages - 1>();
+    cp_async_wait<ST - 1>();
     if (SHARED) __syncthreads(); else __syncwarp();
-    const int stage = pi % kStages;
+    const int stage = pi % ST;
     const uint32_t ks_u = wsm_u + stage * 2 * PAGE_B, vs_u = ks_u + PAGE_B;
     float s[2][4];
 #pragma unroll
@@ -380,7 +382,7 @@ __global__ void attn_merge_kernel(const AttnDecodeArgs a) {
 
 using namespace b2;
 
-B2_API int b2_attn_decode_smem_bytes(int hd) { return 4 * kStages * 2 * kPage * hd * 2; }
+B2_API int b2_attn_decode_smem_bytes(int hd) { return 4 * kStagesWarp * 2 * kPage * hd * 2; }
 static int attn_shared_smem_bytes(int hd) { return kStages * 2 * kPage * hd * 2; }
 
 // Launches the split kernel and the merge kernel.  `max_groups_tiles` is not needed: the grid covers
