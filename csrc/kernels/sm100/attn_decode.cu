@@ -44,7 +44,7 @@ namespace {
 
 constexpr int kPage = 16;
 constexpr int kStages = 3;      // CTA-shared ring (prefill chunks, verify blocks): 24 KB per CTA
-constexpr int kStagesWarp = 2;  // per-warp rings (decode): 64 KB per 4-warp CTA, three CTAs per SM (registers allow three)
+constexpr int kStagesWarp = 2;  // per-warp rings (decode): 64 KB per 4-warp CTA; two CTAs per SM at 178 registers
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
