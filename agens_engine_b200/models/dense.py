@@ -51,6 +51,9 @@ class DenseModel:
         self._tiered_groups: Dict[int, tuple] = {}     # this step's sequences with pages on the host
         self.prefill_split = 256                       # KV split size of prefill attention
         self.prefill_mm = os.environ.get("B200E_PREFILL_MM", "1") == "1"
+        # steps of up to eight rows run as ONE persistent kernel (ops/step.py) unless switched off
+        self.use_step = os.environ.get("B200E_STEP", "1") == "1"
+        self.step = None
         self._alloc_buffers()
 
     # ------------------------------------------------------------------------------------------------ weights
@@ -142,7 +145,24 @@ class DenseModel:
         self.ws = L.GemvWorkspace(self.dev, floats=max(need, 1 << 16), panels=max(panels, 1 << 10))
         self.ws.mm_min_rows = keep
         self.ws.x16_buffer(32, 128)          # allocate the staging buffer now, outside any graph capture
+        self._open_step()
         return self
+
+    def _open_step(self):
+        """Build the descriptor table of the persistent step kernel (head_dim 128, 16-token pages, CUDA device)."""
+        if self.step is not None:
+            self.step.close()
+            self.step = None
+        if not self.use_step or self.dev.type != "cuda" or self.cfg.head_dim != 128 or self.cfg.page_size != 16:
+            return
+        from ..ops.step import StepRunner
+        self.step = StepRunner(self)
+
+    def _step_ok(self, m: int) -> bool:
+        """The persistent kernel takes this step: it is built, the rows fit, and the deployment has not pinned the
+        tensor-core family for small steps."""
+        return (self.step is not None and self.use_step and m <= 8 and m < (self.ws.mm_min_rows or L.MM_MIN_ROWS)
+                and not self._tiered_groups)
 
     def set_linear_path(self, mm_min_rows: Optional[int]):
         """Token rows from which the small-m linears run on the tcgen05 GEMM instead of the GEMV (None: the default of
@@ -296,6 +316,8 @@ class DenseModel:
         self.status.zero_()
         self.ws.status.zero_()
         self.ws.counters.zero_()
+        if self.step is not None:
+            self.step.reset_sync()
         self._graphs.clear()
 
     # ------------------------------------------------------------------------------------------------ small-m forward
@@ -405,6 +427,9 @@ class DenseModel:
         return self.out_ids[:m].clone(), (self._full_logits(m) if want_logits else None)
 
     def _rows_body(self, m: int, n_groups: int, want_logits: bool):
+        if self._step_ok(m):
+            self.step.launch(m, n_groups, want_logits)
+            return
         basic.embed(self.ids[:m], self.embed, self.ss_a, status=self.status, out=self.h_a[:m])
         parts = self._layers_small(m, n_groups)
         self._head_small(m, parts, want_logits)
@@ -551,6 +576,9 @@ class DenseModel:
     def _decode_body(self, seqs: List[int]):
         """One decode step for ``seqs`` (one row each): the token of the previous step is the input."""
         m = len(seqs)
+        if self._step_ok(m):
+            self.step.launch(m, m, False, decode=True)
+            return
         lib = _lib.cuda_lib()
         check(lib.b2_decode_step_prep(m, ptr(self.last_ids), ptr(self.ids), ptr(self.seq_len), ptr(self.tok_pos),
                                       ptr(self.tok_seq), ptr(self._slot_seq), current_stream()), "b2_decode_step_prep")
@@ -629,5 +657,8 @@ class DenseModel:
             self.seq_len_host[s] += 1
 
     def launches_per_step(self, batch: int = 1) -> int:
-        """Kernels of this package launched by one decode step (prep, embed, 7 per layer, lm_head, argmax)."""
+        """Kernels of this package launched by one decode step: one persistent kernel, or (per-op path) prep, embed,
+        7 per layer, lm_head, argmax."""
+        if self._step_ok(batch):
+            return 1
         return 2 + 7 * self.cfg.n_layers + 2

@@ -203,6 +203,9 @@ class TpDenseModel(DenseModel):
     def close(self):
         """Releases the peer mappings (collective: every rank calls it, with nothing in flight)."""
         self._graphs.clear()
+        if self.step is not None:
+            self.step.close()
+            self.step = None
         if self._gather_inbox is not None:
             self._gather_inbox.close()
             self._gather = self._gather_inbox = None
@@ -211,5 +214,9 @@ class TpDenseModel(DenseModel):
     def weight_bytes(self) -> int:
         return super().weight_bytes()
 
+    def _step_ok(self, m: int) -> bool:
+        return not self.use_nccl_decode and super()._step_ok(m)
+
     def launches_per_step(self, batch: int = 1) -> int:
-        return super().launches_per_step(batch) + 1
+        n = super().launches_per_step(batch)
+        return n if n == 1 else n + 1

@@ -25,12 +25,19 @@ BASELINE_TOK_S = 315.0   # reference README.md:290 (2 x cc 9.0 GPUs, tp2, MTP sp
 
 
 def reference_arm(args):
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "reference is a Rust/CUDA project (no setup.py/pyproject; cargo and rustc absent, crates need "
-                       "the network): `pip install --target baseline/_ref <reference>` fails with 'not installable'",
-    }))
-    return 0
+    """The reference's own kernel library (built unmodified by baseline/build_reference.py) on the same linear shapes;
+    nothing of this package runs on that path."""
+    sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline"))
+    try:
+        import reference_arm as R
+    except Exception as e:          # the driver expects one JSON line and exit code 0 whatever happens here
+        print(json.dumps({"impl": "reference", "unavailable": f"baseline/reference_arm.py could not be imported: {e}"}))
+        return 0
+    try:
+        return R.run(args)
+    except Exception as e:
+        print(json.dumps({"impl": "reference", "unavailable": f"reference arm failed: {type(e).__name__}: {e}"[:300]}))
+        return 0
 
 
 class ClockSampler:
