@@ -79,12 +79,17 @@ def build(verbose: bool = False, ptxas_info: bool = False, jobs: int | None = No
     hdig = _headers_digest()
     nvcc = _nvcc()
     inc = ["-I", str(CSRC)]
+    # extra defines for measurement builds (e.g. B200E_NVCC_DEFS="-DB2_STEP_TRACE"); production builds leave it unset
     nv_flags = NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_info else [])
+    extra = os.environ.get("B200E_NVCC_DEFS", "").split()
     tasks = []
     for s in cu:
         rel = s.relative_to(CSRC)
         obj = OBJDIR / "cuda" / rel.with_suffix(".o")
-        tasks.append(([nvcc, *nv_flags, *inc, "-c", str(s), "-o", str(obj)], obj, _stamp(s, nv_flags, hdig)))
+        text = s.read_text(errors="ignore")
+        # a measurement define only rebuilds the sources that mention it
+        flags = nv_flags + [d for d in extra if d[2:].split("=")[0] in text]
+        tasks.append(([nvcc, *flags, *inc, "-c", str(s), "-o", str(obj)], obj, _stamp(s, flags, hdig)))
     for s in cpp:
         rel = s.relative_to(CSRC)
         obj = OBJDIR / "host" / rel.with_suffix(".o")

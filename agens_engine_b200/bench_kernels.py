@@ -327,9 +327,32 @@ def profile_gemm(args):
     print("profile_gemm done")
 
 
+def profile_step(args):
+    """Small case for an ncu capture of the persistent decode-step kernel: a 4-layer cut of the 32B model (0.95 GB of
+    weights per step, far more than L2), a 512-token context, a few one-row decode steps."""
+    from .models import config as C
+    from .models.dense import DenseModel
+    cfg = C.scaled(C.dense_32b(seed=0), args.layers or 4)
+    m = DenseModel.random_init(cfg, "cuda:0", seed=0, max_seqs=1, max_ctx=args.ctx + 64, prefill_chunk=512)
+    m.new_seq(0)
+    first, _ = m.prefill(0, torch.randint(0, cfg.vocab, (args.ctx,), generator=torch.Generator().manual_seed(1)))
+    m.decode_setup([0], [first], 8)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    m._decode_body([0])
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(4):
+        m._decode_body([0])
+    e1.record()
+    torch.cuda.synchronize()
+    print(json.dumps({"what": "profile_step", "layers": cfg.n_layers, "ctx": args.ctx, "us_per_step": e0.elapsed_time(e1) * 250.0,
+                      "weight_bytes": m.weight_bytes(), "status": int(m.status.item())}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_gemm", "profile_misc"])
+    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_gemm", "profile_misc", "profile_step"])
+    ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--ks", type=int, default=0)
     ap.add_argument("--m", type=int, default=1)
@@ -357,6 +380,8 @@ def main(argv=None):
         profile_gemm(args)
     elif args.what == "profile_misc":
         profile_misc(args)
+    elif args.what == "profile_step":
+        profile_step(args)
     else:
         raise SystemExit(f"{args.what}: not available yet")
 

@@ -51,8 +51,10 @@ class DenseModel:
         self._tiered_groups: Dict[int, tuple] = {}     # this step's sequences with pages on the host
         self.prefill_split = 256                       # KV split size of prefill attention
         self.prefill_mm = os.environ.get("B200E_PREFILL_MM", "1") == "1"
-        # steps of up to eight rows run as ONE persistent kernel (ops/step.py) unless switched off
-        self.use_step = os.environ.get("B200E_STEP", "1") == "1"
+        # Steps of up to eight rows can run as ONE persistent kernel (ops/step.py) when B200E_STEP=1 (or after
+        # `enable_step()`): it keeps a second copy of the weights in its own layout, and on the 32B shapes the per-op
+        # path is still the faster one, so it is opt-in.
+        self.use_step = os.environ.get("B200E_STEP", "0") == "1"
         self.step = None
         self._alloc_buffers()
 
@@ -113,6 +115,7 @@ class DenseModel:
         self.rope_delta: Dict[int, int] = {}
         self._use_rope_pos = False
         self.last_ids, self.out_ids = i32(M), i32(M)
+        self._slot_seq = i32(M)              # decode slots -> sequence ids (fixed address: captured graphs read it)
         self.h_a, self.h_b = bf(M, cfg.d_model), bf(M, cfg.d_model)
         parts = max(cfg.d_model // 32, 1)
         self.ss_a = torch.zeros(parts, L.SS_LD, dtype=torch.float32, device=dev)
@@ -128,9 +131,13 @@ class DenseModel:
         self.amax_idx = torch.empty(lm_panels, L.SS_LD, dtype=torch.int32, device=dev)
         self.logits = torch.empty(M, self.lm_rows, dtype=torch.float32, device=dev)
         self.out_val = torch.empty(M, dtype=torch.float32, device=dev)
-        self.status = i32(1)
+        # status words of every kernel family this model launches, side by side so that one small copy reads them all:
+        # [0] model kernels (bounds checks, step kernel waits), [1] GEMV / GEMM waits, [2], [3] tensor-parallel inboxes
+        self._status_all = i32(4)
+        self.status = self._status_all[0:1]
         self.inv_freq = basic.rope_inv_freq(cfg.head_dim, cfg.rope_theta, dev)
-        self.ws = L.GemvWorkspace(dev, floats=max(4 << 20, 2 * cfg.d_model * 64 * M), panels=max(1 << 16, lm_panels))
+        self.ws = L.GemvWorkspace(dev, floats=max(4 << 20, 2 * cfg.d_model * 64 * M), panels=max(1 << 16, lm_panels),
+                                  status=self._status_all[1:2])
         self._deq_tmp = None
 
     def finalize(self):
@@ -142,7 +149,7 @@ class DenseModel:
         need = max(need, max(lib.b2_wq_mm_scratch_floats(x.n, x.k, 256) for x in lins))
         panels = max(x.n_panels() for x in lins)
         keep = self.ws.mm_min_rows
-        self.ws = L.GemvWorkspace(self.dev, floats=max(need, 1 << 16), panels=max(panels, 1 << 10))
+        self.ws = L.GemvWorkspace(self.dev, floats=max(need, 1 << 16), panels=max(panels, 1 << 10), status=self._status_all[1:2])
         self.ws.mm_min_rows = keep
         self.ws.x16_buffer(32, 128)          # allocate the staging buffer now, outside any graph capture
         self._open_step()
@@ -157,6 +164,15 @@ class DenseModel:
             return
         from ..ops.step import StepRunner
         self.step = StepRunner(self)
+
+    def enable_step(self, on: bool = True):
+        """Switches small steps (up to eight rows) to the persistent step kernel, building its weight copies on first
+        use.  Under tensor parallelism every rank calls it (it opens the exchange region collectively)."""
+        self.use_step = on
+        if on and self.step is None:
+            self._open_step()
+        self._graphs.clear()
+        return self.step is not None
 
     def _step_ok(self, m: int) -> bool:
         """The persistent kernel takes this step: it is built, the rows fit, and the deployment has not pinned the
@@ -217,6 +233,8 @@ class DenseModel:
         sequence must not be rolled back below its fork point (its earlier pages are shared)."""
         if n_tokens == self.seq_len_host[seq]:
             return
+        if self.tier is not None and n_tokens < self.tier.n_host_pages(seq) * self.cfg.page_size:
+            raise RuntimeError(f"truncate: sequence {seq} cannot be rolled back into pages that moved to the host tier")
         self.seq_len_host[seq] = n_tokens
         self.seq_len[seq] = n_tokens
         keep = (n_tokens + self.cfg.page_size - 1) // self.cfg.page_size
@@ -246,12 +264,19 @@ class DenseModel:
         self.seq_len_host[dst] = self.seq_len_host[src]
         self.seq_len[dst] = self.seq_len_host[src]
 
+    def _resident_or_raise(self, seq: int, used: int, what: str):
+        """Pages that live in the host tier carry a negative marker in the page list; gathering them by index would be
+        an out-of-range access on the device, so such calls are refused on the host."""
+        if any(p < 0 for p in self.seq_pages[seq][:used]):
+            raise RuntimeError(f"{what}: sequence {seq} has KV pages in the host tier; bring them back or drop the sequence")
+
     def park(self, seq: int) -> Dict[str, object]:
         """Moves a sequence's KV rows to pinned host memory and frees its slot and pages.  :meth:`unpark` brings it
         back bit for bit, so a preempted or idle conversation resumes without recomputation (reference: park/unpark of
         conversations, serve.rs:616-760, and the host KV tier of m1_model.cu:1818-1905)."""
         n = self.seq_len_host[seq]
         used = (n + self.cfg.page_size - 1) // self.cfg.page_size
+        self._resident_or_raise(seq, used, "park")
         idx = torch.tensor(self.seq_pages[seq][:used], dtype=torch.long, device=self.dev)
         shape = (self.cfg.n_layers, used) + tuple(self.kv[0].shape[1:])
         host_kv = torch.empty(shape, dtype=torch.bfloat16, pin_memory=True)
@@ -284,6 +309,7 @@ class DenseModel:
         from ..utils import checkpoint as K
         n = self.seq_len_host[seq]
         used = (n + self.cfg.page_size - 1) // self.cfg.page_size
+        self._resident_or_raise(seq, used, "save_session")
         idx = torch.tensor(self.seq_pages[seq][:used], dtype=torch.long, device=self.dev)
         kv = torch.stack([layer.index_select(0, idx) for layer in self.kv]).cpu()
         meta = {"format": "b200e-session-1", "len": str(n), "n_layers": str(self.cfg.n_layers), "n_kv_heads": str(self.cfg.n_kv_heads),
@@ -307,14 +333,19 @@ class DenseModel:
         self.unpark(seq, {"len": n, "kv": kv.pin_memory()})
         return toks
 
+    def device_status(self) -> int:
+        """First non-zero status word of the kernels this model launched since the last clear (0: all fine).  One
+        16-byte device-to-host copy; the serving loop calls it once per step before it delivers tokens."""
+        st = self._status_all.cpu().tolist()
+        return next((x for x in st if x), 0)
+
     def recover(self):
         """After a device-side error status (bounded wait expired, bounds check): drop every sequence, clear the status
         words and the self-resetting counters, forget captured graphs.  Weights stay loaded (reference: ak_m1_recover)."""
         torch.cuda.synchronize(self.dev)
         for s in list(self.seq_pages):
             self.free_seq(s)
-        self.status.zero_()
-        self.ws.status.zero_()
+        self._status_all.zero_()
         self.ws.counters.zero_()
         if self.step is not None:
             self.step.reset_sync()
@@ -591,7 +622,7 @@ class DenseModel:
         """Prepare device state for ``n_steps`` graph-replayed decode steps of ``seqs``."""
         m = len(seqs)
         t = lambda x: torch.tensor(x, dtype=torch.int32, device=self.dev)
-        self._slot_seq = t(seqs)
+        self._slot_seq[:m] = t(seqs)
         self.last_ids[:m] = t(first_tokens)
         self.grp_tok0[:m] = torch.arange(m, dtype=torch.int32, device=self.dev)
         self.grp_cnt[:m] = 1

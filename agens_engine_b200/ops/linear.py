@@ -116,10 +116,11 @@ class GemvWorkspace:
     """Split-k scratch, self-resetting item counters and the status word shared by the GEMV / GEMM launches of one
     stream, plus the fp16 activation staging buffer of the tensor-core path (grown on first use)."""
 
-    def __init__(self, device, floats: int = 4 << 20, panels: int = 1 << 16):
+    def __init__(self, device, floats: int = 4 << 20, panels: int = 1 << 16, status: Optional[torch.Tensor] = None):
         self.scratch = torch.empty(floats, dtype=torch.float32, device=device)
         self.counters = torch.zeros(panels, dtype=torch.int32, device=device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        # the status word may live inside a block of status words that the owner reads with one copy
+        self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=device)
         self.x16 = None
         self.mm_min_rows = None      # overrides MM_MIN_ROWS for the launches that use this workspace
 

@@ -31,7 +31,7 @@ class StepLinear(C.Structure):
 class StepLayer(C.Structure):
     _fields_ = [
         ("qkv", StepLinear), ("o", StepLinear), ("gate_up", StepLinear), ("down", StepLinear),
-        ("ln1", C.c_void_p), ("ln2", C.c_void_p), ("kv_pool", C.c_void_p),
+        ("ln1", C.c_void_p), ("ln2", C.c_void_p), ("kv_pool", C.c_void_p), ("pad", C.c_void_p),
     ]
 
 
@@ -62,6 +62,7 @@ class StepArgs(C.Structure):
         ("xreg", C.c_void_p * MAX_TP),
         ("x_off", C.c_long * 2), ("x_amax", C.c_long),
         ("skip_push", C.c_int),
+        ("trace", C.c_void_p),
     ]
 
 
@@ -78,16 +79,30 @@ def _lib_step():
         _lib.declare_optional(lib, "b2_step_smem_bytes", [], i)
         _lib.declare_optional(lib, "b2_step_grid", [C.POINTER(i)], i)
         _lib.declare_optional(lib, "b2_step_launch", [C.POINTER(StepArgs), i, vp], i)
+        _lib.declare_optional(lib, "b2_wq_fm_to_fi", [vp, i, i, i, i, vp, vp], i)
         if lib.b2_step_args_bytes() != C.sizeof(StepArgs) or lib.b2_step_layer_bytes() != C.sizeof(StepLayer):
             raise RuntimeError("ops/step.py and step_kernel.cuh disagree about the argument structures")
         _declared = True
     return lib
 
 
-def step_linear(lin, ncta: int) -> StepLinear:
+def to_fi(lin) -> torch.Tensor:
+    """The linear's weights in the integer-MMA layout of the step kernel (``wq_tools.cu``: FI), converted on the
+    device from the FM buffer.  Same size as the FM buffer: a model that runs both the step kernel and the per-op /
+    prefill kernels holds its quantised weights twice (the reference's dual-layout mode does the same for its W4H
+    copies, kernels/src/w4h.cu:957-968)."""
+    lib = _lib_step()
+    fi = torch.empty_like(lin.wq)
+    with torch.cuda.device(lin.wq.device):
+        check(lib.b2_wq_fm_to_fi(ptr(lin.wq), lin.n, lin.k, lin.bits, lin.group, ptr(fi), current_stream()), "b2_wq_fm_to_fi")
+    return fi
+
+
+def step_linear(lin, ncta: int, wq: Optional[torch.Tensor] = None) -> StepLinear:
     lib = _lib_step()
     out = StepLinear()
-    check(lib.b2_step_linear(ptr(lin.wq), lin.n, lin.k, lin.bits, lin.group, ncta, C.byref(out)), "b2_step_linear")
+    check(lib.b2_step_linear(ptr(lin.wq if wq is None else wq), lin.n, lin.k, lin.bits, lin.group, ncta, C.byref(out)),
+          "b2_step_linear")
     return out
 
 
@@ -109,15 +124,17 @@ class StepRunner:
         L = len(model.layers)
         table = (StepLayer * max(L, 1))()
         need = 0
-        self._lins = []
+        self._fi = []                     # FI copies of every linear (kept alive here)
         for l, d in enumerate(model.layers):
             for name in ("qkv", "o", "gate_up", "down"):
-                sl = step_linear(d[name], self.ncta)
+                self._fi.append(to_fi(d[name]))
+                sl = step_linear(d[name], self.ncta, self._fi[-1])
                 setattr(table[l], name, sl)
                 need = max(need, lib.b2_step_part_floats(C.byref(sl), MAX_ROWS))
             table[l].ln1, table[l].ln2 = ptr(d["ln1"]), ptr(d["ln2"])
             table[l].kv_pool = ptr(model.kv[l])
-        self.lm = step_linear(model.lm_head, self.ncta)
+        self._fi.append(to_fi(model.lm_head))
+        self.lm = step_linear(model.lm_head, self.ncta, self._fi[-1])
         need = max(need, lib.b2_step_part_floats(C.byref(self.lm), MAX_ROWS))
         raw = bytes(table)
         self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
@@ -136,6 +153,7 @@ class StepRunner:
         if self.world > 1:
             self._open_region()
         self.launches = 0
+        self.trace = None            # int64 CUDA tensor; only a library built with -DB2_STEP_TRACE writes to it
 
     def _open_region(self):
         """Exchange region of this rank, mapped by every peer: [counter | o_proj partials | down partials | argmax]."""
@@ -199,6 +217,7 @@ class StepRunner:
             a.x_off[0], a.x_off[1] = self.x_off
             a.x_amax = self.x_amax
         a.skip_push = 1 if self.skip_push else 0
+        a.trace = ptr(self.trace)
         return a
 
     def launch(self, m: int, n_groups: int, want_logits: bool = False, decode: bool = False):

@@ -23,7 +23,7 @@ SENTINEL = 0x80000000   # -0.0f: "not written yet"
 
 class SymmetricInbox:
     def __init__(self, rank: int, world: int, slot_floats: int, n_slots: int, device, group=None,
-                 timeout_s: float = 2.0):
+                 timeout_s: float = 2.0, status: Optional[torch.Tensor] = None):
         """``slot_floats``: floats per source rank in one slot (multiple of 4); the region holds
         ``n_slots * world * slot_floats`` floats."""
         assert slot_floats % 4 == 0 and world <= _lib.K_MAX_TP
@@ -56,7 +56,7 @@ class SymmetricInbox:
                     check(lib.b2_ipc_open(handles[r], C.byref(p)), "b2_ipc_open")
                 self.ptrs.append(p.value)
                 self._opened.append(p.value)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = status if status is not None else torch.zeros(1, dtype=torch.int32, device=self.device)
         if world > 1:
             dist.barrier(group=group)   # every region is armed before anyone pushes
 

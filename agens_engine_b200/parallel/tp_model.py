@@ -43,12 +43,13 @@ class TpDenseModel(DenseModel):
         self.use_nccl_decode = use_nccl_decode
         super().__init__(local_config(cfg, world), device, lm_rows=_pad32(self.vocab_shard), **kw)
         n_sites = 2 * cfg.n_layers + 1
-        self.inbox = SymmetricInbox(rank, world, M_GEMV * cfg.d_model, n_sites, self.dev)
+        self.inbox = SymmetricInbox(rank, world, M_GEMV * cfg.d_model, n_sites, self.dev, status=self._status_all[2:3])
         self.n_sites = n_sites
         self.idx_off = torch.full((M_GEMV,), rank * self.vocab_shard, dtype=torch.int32, device=self.dev)
         self.skip_push_site = -1     # test hook: the call site whose push this rank drops
         from .comm import PushComm
-        self._gather_inbox = SymmetricInbox(rank, world, 8 * self.lm_rows, 3, self.dev)     # logits / winners exchange
+        self._gather_inbox = SymmetricInbox(rank, world, 8 * self.lm_rows, 3, self.dev,
+                                            status=self._status_all[3:4])                       # logits / winners exchange
         self._gather = PushComm(self._gather_inbox)
 
     # ------------------------------------------------------------------------------------------------ weights
@@ -199,6 +200,15 @@ class TpDenseModel(DenseModel):
 
     def vocab_valid_full(self) -> int:
         return self.full_cfg.vocab_valid or self.full_cfg.vocab
+
+    def recover(self):
+        """As the single-GPU recovery, plus re-arming this rank's collective inboxes.  Every rank calls it (the driver
+        forwards the call), with a host-side barrier before anyone launches again."""
+        super().recover()
+        self.inbox.rearm_all()
+        if self._gather_inbox is not None:
+            self._gather_inbox.rearm_all()
+        torch.cuda.synchronize(self.dev)
 
     def close(self):
         """Releases the peer mappings (collective: every rank calls it, with nothing in flight)."""

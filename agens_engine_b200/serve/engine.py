@@ -77,6 +77,7 @@ class EngineStats:
     rejected: int = 0
     peak_batch: int = 0
     images_encoded: int = 0
+    device_errors: int = 0
 
 
 class Engine:
@@ -115,6 +116,7 @@ class Engine:
         self.kept: Dict[int, dict] = {}                # handle -> {slot | parked, tokens, session, t_last}
         self.by_session: Dict[str, int] = {}
         self._next_handle = 1
+        self._prefix_budget = prefix_budget_bytes
         self.prefix = host.PrefixCache(prefix_budget_bytes, prefix_chunk) if keep_sequences else None
         self.prefix_chunk = prefix_chunk
 
@@ -143,11 +145,55 @@ class Engine:
     def run(self):
         torch.cuda.set_device(self.m.dev)
         while not self._stop.is_set():
-            if not self.step():
-                try:
-                    self.waiting.append(self.inbox.get(timeout=0.02))
-                except queue.Empty:
-                    pass
+            try:
+                if not self.step():
+                    try:
+                        self._intake(self.inbox.get(timeout=0.02))
+                    except queue.Empty:
+                        pass
+            except Exception as e:      # a failed step must not take the engine thread (and every open request) with it
+                self._fail_all(f"engine step failed: {type(e).__name__}: {e}")
+
+    def _intake(self, r: Request):
+        """Every request enters through here, whichever wait delivered it: images are decoded and encoded first."""
+        if r.images and not self._prepare_images(r):
+            return
+        self.waiting.append(r)
+
+    def _fail_all(self, why: str):
+        """Ends every running request with an error and puts the model back into a usable state (device status words
+        cleared, sequences dropped, collective inboxes re-armed; under tensor parallelism the followers do the same)."""
+        for r in list(self.active.values()):
+            try:
+                self.emit(r.rid, [], True, why)
+            except Exception:
+                pass
+            r.state = DONE
+        self.active.clear()
+        self.spec.hist.clear(); self.spec.samp.clear()
+        for src in self.spec.sources:
+            reset = getattr(src, "reset", None)
+            if reset:
+                reset()
+        self.kept.clear(); self.by_session.clear()
+        if self.prefix is not None:
+            self.prefix = host.PrefixCache(self._prefix_budget, self.prefix_chunk)
+        try:
+            self.m.recover()
+        except Exception:
+            pass
+        self.free_slots = list(range(self.m.max_seqs - 1, -1, -1))
+        self.stats.device_errors += 1
+
+    def _check_device(self) -> bool:
+        """Reads the device status words once per step (one small copy); a bounded wait that ran out or a bounds check
+        that fired means this step's tokens cannot be trusted: nothing of it is delivered."""
+        st = self.m.device_status()
+        if st == 0:
+            return True
+        from .._lib import STATUS_NAMES
+        self._fail_all(f"device reported: {STATUS_NAMES.get(st, st)}")
+        return False
 
     def idle(self) -> bool:
         return not self.waiting and not self.active and self.inbox.empty()
@@ -165,9 +211,7 @@ class Engine:
                 r = self.inbox.get_nowait()
             except queue.Empty:
                 break
-            if r.images and not self._prepare_images(r):
-                continue
-            self.waiting.append(r)
+            self._intake(r)
         self._admit()
         did = False
         pre = [r for r in self.active.values() if r.state == PREFILL]
@@ -229,7 +273,15 @@ class Engine:
             r.slot = self.free_slots.pop()
             self.spec.samp[r.slot] = r.state_of_sampling()
             if r.parked is not None:                     # preempted earlier: bring its KV rows back and go on decoding
-                self.m.unpark(r.slot, r.parked)
+                try:
+                    self.m.unpark(r.slot, r.parked)
+                except RuntimeError:                     # no room after all: give the slot back and wait in line
+                    if r.slot in self.m.seq_pages:
+                        self.m.free_seq(r.slot)
+                    self.spec.samp.pop(r.slot, None)
+                    self.free_slots.append(r.slot)
+                    r.slot = -1
+                    keep.append(r); continue
                 self.spec.hist[r.slot] = r.parked_hist
                 for s in self.spec.sources:
                     s.begin(r.slot, r.parked_hist)
@@ -322,7 +374,12 @@ class Engine:
             if n >= page:
                 self.kept.pop(h); self.by_session.pop(r.session)
                 if k["slot"] is None:
-                    self.m.unpark(r.slot, k["parked"])
+                    try:
+                        self.m.unpark(r.slot, k["parked"])
+                    except RuntimeError:                               # pool exhausted: start this turn from scratch
+                        if r.slot in self.m.seq_pages:
+                            self.m.free_seq(r.slot)
+                        return False
                 else:                                                  # the request moves into the kept sequence's slot
                     self.spec.samp.pop(r.slot, None)
                     self.free_slots.append(r.slot)
@@ -409,6 +466,8 @@ class Engine:
             res = self._with_room(r, lambda: self.m.prefill(r.slot, chunk, want_logits=final and sampled, **kw))
         except RuntimeError as e:
             self._finish(r, error=str(e)); return
+        if final and not self._check_device():
+            return
         r.done_prompt += n
         r.chunk_index += 1
         self.stats.prefill_chunks += 1
@@ -465,23 +524,37 @@ class Engine:
             for r in fast:
                 self._finish(r, error=str(e))
             return
+        if not self._check_device():
+            return
         self.stats.steps += 1
         for r in fast:
-            if r.slot in res:
+            if r.slot in res and self.active.get(r.slot) is r and r.state == DECODE:
                 self._deliver(r, res[r.slot])
 
     def _decode_plain(self, rows: List[Request]):
         """One token per sequence with logit edits / forced tokens (no speculation: the edits depend on every token)."""
         m = self.m
-        ids = [self.spec.hist[r.slot][-1] for r in rows]
-        slots = [r.slot for r in rows]
-        pos = [m.seq_len_host[s] + 1 for s in slots]
+        live: List[Request] = []
+
+        def run():
+            # an eviction between two attempts may have parked one of the rows: ask only for those still decoding
+            live[:] = [r for r in rows if self.active.get(r.slot) is r and r.state == DECODE]
+            if not live:
+                return None, None
+            return m.forward_rows([self.spec.hist[r.slot][-1] for r in live], [r.slot for r in live], want_logits=True)
+
         try:
-            _, logits = self._with_room(rows[0], lambda: m.forward_rows(ids, slots, want_logits=True))
+            _, logits = self._with_room(rows[0], run)
         except RuntimeError as e:
             for r in rows:
-                self._finish(r, error=str(e))
+                if self.active.get(r.slot) is r:
+                    self._finish(r, error=str(e))
             return
+        rows = list(live)
+        if not rows or not self._check_device():
+            return
+        slots = [r.slot for r in rows]
+        pos = [m.seq_len_host[s] for s in slots]
         self._edit_logits(logits, rows)
         forced: Dict[int, int] = {}
         for i, r in enumerate(rows):

@@ -7,13 +7,13 @@
 // the tensor-parallel all-reduce into its push kernels (kernels/src/tp_ar.cu:160-227).  On a 148-SM part a step of
 // the 32B model is bound by the ~450 kernel boundaries, not by the weights, so here the boundaries disappear:
 //
-//   * one CTA of 16 warps per SM stays resident for the whole step; phases are separated by grid barriers (one
+//   * one CTA of 15 worker warps and one producer warp per SM stays resident for the whole step; phases are separated by grid barriers (one
 //     release-add and a bounded acquire-poll per CTA), tensor-parallel phases by the same barrier across GPUs
 //     (release-adds into every peer's counter over NVLink);
 //   * every warp streams its statically known share of ALL the step's weights through a private cp.async.bulk ring
 //     whose producer runs ahead across phase boundaries: while a barrier or the attention phase is in progress the
 //     next linear's weights are already in flight or in shared memory;
-//   * a linear is cut by contiguous block ranges over the CTAs (stream-k); the 16 warps of a CTA share one row panel
+//   * a linear is cut by contiguous block ranges over the CTAs (stream-k); the worker warps of a CTA share one row panel
 //     at a time and combine their k ranges through shared memory; a panel cut by a CTA boundary leaves one partial per
 //     fragment in global memory.  The consumer ("finalize") stage adds the fragments in a fixed order and applies
 //     what the reference does in separate kernels: RoPE + KV store, the split merge of attention, residual add,
@@ -31,30 +31,52 @@
 namespace b2 {
 namespace {
 
-constexpr int kRingBytes = 7168;           // weight bytes in flight per warp
 constexpr int kRingBars = 16;              // units in flight per warp
-constexpr int kRedTok = 20;                // floats between the token rows of a warp's partial tile (conflict-free)
-constexpr int kRedWarp = kStepMaxRows * kRedTok;
-constexpr int kAttnWarps = 6;              // warps of a CTA that run attention items (two 8 KB K/V stages each)
+constexpr int kAttnWarps = 3;              // warps of a CTA that run attention items
+constexpr int kAttnStages = 2;             // 8 KB K/V page stages per attention warp
 constexpr int kPage = 16;
 
-constexpr int SM_RING = 0;
-constexpr int SM_BARS = SM_RING + kStepWarps * kRingBytes;
-constexpr int SM_MISC = SM_BARS + kStepWarps * kRingBars * 8;
+// Shared memory of a CTA: [mbarriers | misc | work area | weight rings].  The work area (staged activations, group
+// scalars, partial tiles; attention's K/V stages alias it) grows with the number of token rows, and the weight rings
+// take everything that is left: a one-row decode step keeps about 11 KB of weights in flight per warp, an eight-row
+// step 7 KB.  Ring depth changes no arithmetic.
+constexpr int SM_TOTAL = 227328;
+constexpr int SM_BARS = 0;
+constexpr int SM_MISC = 2048;
 constexpr int SM_MISC_BYTES = 2048;
 constexpr int SM_WORK = SM_MISC + SM_MISC_BYTES;
-constexpr int SM_XS_BYTES = kStepMaxRows * (kStepSliceK + 16) * 2;
-constexpr int SM_GSUM = SM_WORK + SM_XS_BYTES;
-constexpr int SM_GSUM_BYTES = (kStepSliceK / 128) * 2 * kStepMaxRows * 8;
-constexpr int SM_RED = SM_GSUM + SM_GSUM_BYTES;
-constexpr int SM_RED_BYTES = 2 * kStepWarps * kRedWarp * 4;
-constexpr int SM_TOTAL = SM_RED + SM_RED_BYTES;
-static_assert(kAttnWarps * 2 * 2 * kPage * 128 * 2 <= SM_TOTAL - SM_WORK, "attention stages alias the GEMV work area");
+constexpr int kMaxBatches = kStepSliceK / 128;
+constexpr int SM_GSUM_BYTES = kMaxBatches * 2 * kStepMaxRows * 8;
+constexpr int kAttnBytes = kAttnWarps * kAttnStages * 2 * kPage * 128 * 2;
+static_assert(kStepWarps * kRingBars * 8 <= SM_MISC, "mbarriers");
 static_assert(SM_TOTAL <= 227 * 1024, "shared memory of one CTA");
 
+struct Lay {
+  int xs_stride;      // bytes of staged activations per 128-k batch: one or two token sets x four steps x 256 B
+  int gsum, tiles;    // byte offsets
+  int ring, ring_w;   // offset of the rings and bytes per warp
+};
+__host__ __device__ __forceinline__ Lay make_lay(int rows) {
+  Lay l;
+  l.xs_stride = rows > 4 ? 2048 : 1024;
+  l.gsum = SM_WORK + kMaxBatches * l.xs_stride;
+  l.tiles = l.gsum + SM_GSUM_BYTES;
+  int end = l.tiles + kStepWarps * 2 * rows * 32 * 4;       // head and tail tile of every worker warp
+  if (end < SM_WORK + kAttnBytes) end = SM_WORK + kAttnBytes;
+  l.ring = (end + 127) & ~127;
+  l.ring_w = ((SM_TOTAL - l.ring) / kStepWarps) & ~63;
+  return l;
+}
+static_assert(SM_WORK + kMaxBatches * 2048 + SM_GSUM_BYTES + kStepWarps * 2 * kStepMaxRows * 32 * 4 + kStepWarps * 2304 * 3 <= SM_TOTAL,
+              "an eight-row step still has three blocks per warp in flight");
+
 // misc area (floats): [0,8) inv_rms, [8,136) per-warp sums, [136,264) argmax values, [264,392) argmax indices,
-// [392,424) row description (ids, pos, seq, rope position)
-constexpr int MI_WSUM = 8, MI_AV = 136, MI_AI = 264, MI_ROW = 392;
+// [392,424) row description (ids, pos, seq, rope position), [424,456) ring progress published to the producer warp,
+// [456,486) panel index of every partial tile
+constexpr int MI_WSUM = 8, MI_AV = 136, MI_AI = 264, MI_ROW = 392, MI_PUB = 424, MI_TILE = 456;   // MI_PUB: 2 words per worker warp
+
+// Barrier over the worker warps (the producer warp never takes part in a CTA barrier).
+__device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStepThreads) : "memory"); }
 
 __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
   unsigned v;
@@ -98,15 +120,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 // ---------------------------------------------------------------------------------------------------- barriers
 struct SyncState {
   unsigned local_target, cross_target;   // arrival counts the next barrier waits for (thread 0 of every CTA)
+  unsigned ev;                           // trace builds: next stamp index
 };
+#ifdef B2_STEP_TRACE
+#define B2_STAMP(a, ss) do { if ((a).trace && blockIdx.x == 0) (a).trace[(ss).ev++] = globaltimer_ns(); } while (0)
+#else
+#define B2_STAMP(a, ss) do { } while (0)
+#endif
 
 // Grid barrier.  Every CTA adds one to the counter with release semantics after its threads met at bar.sync, then
 // polls with acquire loads until all CTAs of this epoch arrived.  The poll is bounded: on expiry (or when another
 // wait already failed) the status word is set and the kernel runs to its end without waiting again.
 __device__ __forceinline__ void grid_sync(const StepArgs& a, SyncState& ss) {
-  __syncthreads();
+  workers_sync();
   if (threadIdx.x == 0) {
     ss.local_target += gridDim.x;
+    B2_STAMP(a, ss);
     __threadfence();
     red_release_gpu(a.sync, 1u);
     if (ld_volatile_i32(a.status) == 0) {
@@ -119,17 +148,19 @@ __device__ __forceinline__ void grid_sync(const StepArgs& a, SyncState& ss) {
         }
       }
     }
+    B2_STAMP(a, ss);
   }
-  __syncthreads();
+  workers_sync();
 }
 
 // The same barrier over all CTAs of all tensor-parallel ranks: one release-add into every rank's counter (word 0 of
 // its exchange region), then a poll of the own counter.  With one rank it is the grid barrier.
 __device__ __forceinline__ void cross_sync(const StepArgs& a, SyncState& ss) {
   if (a.tp_size <= 1) { grid_sync(a, ss); return; }
-  __syncthreads();
+  workers_sync();
   if (threadIdx.x == 0) {
     ss.cross_target += gridDim.x * (unsigned)a.tp_size;
+    B2_STAMP(a, ss);
     __threadfence_system();
     if (!a.skip_push)
       for (int r = 0; r < a.tp_size; ++r) red_release_sys(reinterpret_cast<unsigned*>(a.xreg[r]), 1u);
@@ -144,8 +175,9 @@ __device__ __forceinline__ void cross_sync(const StepArgs& a, SyncState& ss) {
         }
       }
     }
+    B2_STAMP(a, ss);
   }
-  __syncthreads();
+  workers_sync();
 }
 
 // ---------------------------------------------------------------------------------------------------- work split
@@ -191,95 +223,186 @@ __device__ __forceinline__ void split_phase(Phase& ph, int cta) {
   ph.hi = (unsigned)((B * (unsigned)(ph.ci + 1)) / (unsigned)L.cps);
 }
 
-// Producer cursor of one warp (held by lane 0): walks the warp's units of every remaining linear of the step in the
-// order the consumer will use them.  Warp w of a CTA takes row block (w & 1) of the batches b_lo + (w >> 1) + 8 i of
-// every panel segment of the CTA's range.
+// Block range of worker warp w inside its CTA's range: the CTA's blocks are cut into kStepWarps contiguous pieces
+// (stream-k at warp level), so the warps of a CTA carry the same number of blocks (+-1) and never wait for one another
+// inside a phase.  A piece may start and end in the middle of a panel: the warp leaves at most two partial tiles
+// (head and tail) in shared memory; panels that lie completely inside its piece are finished by the warp alone.
+__device__ __forceinline__ void warp_range(const Phase& ph, int warp, unsigned& wlo, unsigned& whi) {
+  const unsigned nblk = ph.hi - ph.lo;
+  wlo = ph.lo + (unsigned)(((unsigned long long)nblk * (unsigned)warp) / kStepWarps);
+  whi = ph.lo + (unsigned)(((unsigned long long)nblk * (unsigned)(warp + 1)) / kStepWarps);
+}
+
+// Producer cursor of one ring (one lane of the producer warp): the blocks of that worker warp, for every remaining
+// linear of the step, in the order the worker consumes them.
 struct Cursor {
   int phase, n_phases;
   Phase ph;
-  unsigned p;
-  int b, b_hi;
+  unsigned blk, whi;
 };
 
 __device__ __forceinline__ void cursor_settle(Cursor& c, const StepArgs& a, int cta, int warp, bool fresh) {
-  // `fresh`: c.ph was just loaded for c.phase and no segment is selected yet
+  // `fresh`: c.ph was just loaded for c.phase and the warp's range is not selected yet
   while (c.phase < c.n_phases) {
     if (fresh) {
-      if (!c.ph.active || c.ph.lo >= c.ph.hi) {
-        ++c.phase;
-        if (c.phase < c.n_phases) { load_linear(a, c.phase, c.ph.lin); split_phase(c.ph, cta); }
-        continue;
-      }
-      c.p = c.ph.lo / (unsigned)c.ph.nbs;
-      const int b_lo = (int)(c.ph.lo - c.p * (unsigned)c.ph.nbs);
-      c.b_hi = (int)min(c.ph.hi - c.p * (unsigned)c.ph.nbs, (unsigned)c.ph.nbs);
-      c.b = b_lo + (warp >> 1);
+      c.blk = c.whi = 0;
+      if (c.ph.active && c.ph.lo < c.ph.hi) warp_range(c.ph, warp, c.blk, c.whi);
       fresh = false;
     }
-    if (c.b < c.b_hi) return;
-    ++c.p;
-    if (c.p * (unsigned)c.ph.nbs >= c.ph.hi) {
-      ++c.phase;
-      if (c.phase < c.n_phases) { load_linear(a, c.phase, c.ph.lin); split_phase(c.ph, cta); }
-      fresh = true;
-      continue;
-    }
-    c.b_hi = (int)min(c.ph.hi - c.p * (unsigned)c.ph.nbs, (unsigned)c.ph.nbs);
-    c.b = warp >> 1;
+    if (c.blk < c.whi) return;
+    ++c.phase;
+    if (c.phase < c.n_phases) { load_linear(a, c.phase, c.ph.lin); split_phase(c.ph, cta); }
+    fresh = true;
   }
 }
 
+// Consumer side of one warp's weight ring.  The producer warp fills it; the consumer publishes how many units it
+// has finished and how many ring bytes that released.
 struct WRing {
-  uint32_t base_u, bars_u;
+  uint32_t bars_u;
   uint8_t* base;
-  unsigned pidx, cidx;     // units issued (lane 0) / consumed (all lanes)
-  int ppos, pfree;         // producer byte position and free bytes (lane 0)
-  int cpos;                // consumer byte position (all lanes)
+  unsigned cidx;           // units consumed
+  unsigned cbytes;         // ring bytes released (wrap skips included)
+  int cpos;                // byte position of the next unit
+  volatile unsigned* pub;  // [0] units consumed, [1] bytes released, as read by the producer warp
 };
 
-// Lane 0: issue bulk copies while the ring has room.
-__device__ __forceinline__ void pump(WRing& r, Cursor& c, const StepArgs& a, int cta, int warp) {
-  while (c.phase < c.n_phases) {
-    const StepLinear& L = c.ph.lin;
-    const int usz = L.wbatch + L.szb;
-    if (r.pidx - r.cidx >= (unsigned)kRingBars) break;
-    int pos = r.ppos, need = usz;
-    if (pos + usz > kRingBytes) { need += kRingBytes - pos; pos = 0; }
-    if (r.pfree < need) break;
-    r.pfree -= need;
-    const uint32_t bar = r.bars_u + (r.pidx % kRingBars) * 8;
-    mbar_expect_tx(bar, (uint32_t)usz);
-    const uint8_t* blkp = L.wq + ((size_t)c.p * L.nbat + (size_t)(c.ph.bs0 + c.b)) * L.blk;
-    const int rb = warp & 1;
-    bulk_g2s(r.base_u + pos, blkp + rb * L.wbatch, (uint32_t)L.wbatch, bar);
-    bulk_g2s(r.base_u + pos + L.wbatch, blkp + 2 * L.wbatch + rb * L.szb, (uint32_t)L.szb, bar);
-    r.ppos = pos + usz;
-    ++r.pidx;
-    c.b += 8;
-    cursor_settle(c, a, cta, warp, false);
+// The last warp of a CTA: lane i feeds the ring of worker warp i with bulk copies, for every linear of the step in
+// order, as far ahead as the ring has room (across phase boundaries: while the workers sit in a barrier, a finalize
+// stage or attention, the next linear's weights are already on their way).  One (32-row x 128-k) block = one
+// contiguous copy.  The warp takes part in no
+// barrier and ends when everything is issued (or when a failed wait set the status word).
+__device__ __forceinline__ void producer_loop(const StepArgs& a, uint8_t* smem, int cta, const Lay& lay) {
+  const int kRingBytes = lay.ring_w;
+  const int lane = threadIdx.x & 31;
+  const bool owner = lane < kStepWarps;
+  Cursor c;
+  c.n_phases = 4 * a.n_layers + 1;
+  c.phase = owner ? 0 : c.n_phases;
+  c.blk = 0; c.whi = 0;
+  unsigned pidx = 0, pbytes = 0;
+  int ppos = 0;
+  const uint32_t base_u = smem_u32(smem + lay.ring) + (owner ? lane : 0) * kRingBytes;
+  const uint32_t bars_u = smem_u32(smem + SM_BARS) + (owner ? lane : 0) * kRingBars * 8;
+  volatile unsigned* pub = reinterpret_cast<volatile unsigned*>(smem + SM_MISC) + MI_PUB + 2 * (owner ? lane : 0);
+  if (owner) {
+    load_linear(a, 0, c.ph.lin);
+    split_phase(c.ph, cta);
+    cursor_settle(c, a, cta, lane, true);
+  }
+  unsigned idle = 0;
+  while (__any_sync(0xffffffffu, c.phase < c.n_phases)) {
+    bool issued = false;
+    if (c.phase < c.n_phases) {
+      const StepLinear& L = c.ph.lin;
+      const int usz = L.blk;
+      int pos = ppos, need = usz;
+      if (pos + usz > kRingBytes) { need += kRingBytes - pos; pos = 0; }
+      const unsigned cidx = pub[0], cby = pub[1];
+      if (pidx - cidx < (unsigned)kRingBars && (unsigned)kRingBytes - (pbytes - cby) >= (unsigned)need) {
+        const uint32_t bar = bars_u + (pidx % kRingBars) * 8;
+        mbar_expect_tx(bar, (uint32_t)usz);
+        const unsigned pp = c.blk / (unsigned)c.ph.nbs, bb = c.blk - pp * (unsigned)c.ph.nbs;
+        bulk_g2s(base_u + pos, L.wq + ((size_t)pp * L.nbat + (size_t)(c.ph.bs0 + bb)) * L.blk, (uint32_t)usz, bar);
+        ppos = pos + usz;
+        pbytes += (unsigned)need;
+        ++pidx;
+        ++c.blk;
+        cursor_settle(c, a, cta, lane, false);
+        issued = true;
+      }
+    }
+    if (__any_sync(0xffffffffu, issued)) { idle = 0; continue; }
+    if ((++idle & 15u) == 0u && ld_volatile_i32(a.status) != 0) break;     // a worker gave up: stop feeding
+    __nanosleep(64);
+  }
+}
+
+// D(16x8, s32) += A(16x32, u8, row) * B(32x8, s8, col)
+__device__ __forceinline__ void mma_u8s8_16832(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// A registers of integer-MMA step s (32 k) of a batch from the FI layout (wq_tools.cu, fi_pos): register r holds four
+// codes of row g + 8 (r & 1), k = 32 s + 16 (r >> 1) + 4 t + byte.
+template <int BITS, int GROUP>
+__device__ __forceinline__ void extract8(const WFrag<BITS, GROUP>& f, int s, uint32_t (&a)[4]) {
+  if (BITS == 4) {
+    const uint32_t w0 = u4_get(f.lo[s >> 1], 2 * (s & 1)), w1 = u4_get(f.lo[s >> 1], 2 * (s & 1) + 1);
+    a[0] = w0 & 0x0F0F0F0Fu;
+    a[1] = w1 & 0x0F0F0F0Fu;
+    a[2] = (w0 >> 4) & 0x0F0F0F0Fu;
+    a[3] = (w1 >> 4) & 0x0F0F0F0Fu;
+  } else {
+    const uint32_t w = u4_get(f.lo[0], s);
+    a[0] = w & 0x03030303u;
+    a[1] = (w >> 2) & 0x03030303u;
+    a[2] = (w >> 4) & 0x03030303u;
+    a[3] = (w >> 6) & 0x03030303u;
+    if (BITS == 3) {
+      // the third bit of register r sits at bit 8 byte + 4 (s & 1) + r of the high-plane word; one shift puts it on bit 2
+      const uint32_t h = (s >> 1) ? f.hi.y : f.hi.x;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int q = 4 * (s & 1) + r;
+        const uint32_t hs = q <= 2 ? (h << (2 - q)) : (h >> (q - 2));
+        a[r] = lop3_and_or(hs, 0x04040404u, a[r]);
+      }
+    }
+  }
+}
+
+// y += s_w * (s_x * acc - z_w * s_x * sum_x) for rows g, g + 8 and tokens t (acc0) and t + 4 (acc1) of one group;
+// acc = 128 * (hi-limb sum) + (lo-limb sum), exact in int32.
+__device__ __forceinline__ void gemv_scale(float (&y)[4], const int (&acc0)[4], const int (&acc1)[4], const uint32_t (&sz)[2],
+                                           float2 q0, float2 q1, bool two_sets) {
+  const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&sz[0]));
+  const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&sz[1]));
+  y[0] = fmaf(s0.x, fmaf(-s0.y, q0.y, (float)(acc0[0] * 128 + acc0[1]) * q0.x), y[0]);
+  y[1] = fmaf(s1.x, fmaf(-s1.y, q0.y, (float)(acc0[2] * 128 + acc0[3]) * q0.x), y[1]);
+  if (two_sets) {
+    y[2] = fmaf(s0.x, fmaf(-s0.y, q1.y, (float)(acc1[0] * 128 + acc1[1]) * q1.x), y[2]);
+    y[3] = fmaf(s1.x, fmaf(-s1.y, q1.y, (float)(acc1[2] * 128 + acc1[3]) * q1.x), y[3]);
   }
 }
 
 // ---------------------------------------------------------------------------------------------------- GEMV phase
-// One linear: stage this CTA's activation slice (optionally RMS-normalised) as fp16(x / c) with the per-group sums,
-// then walk the panel segments of the CTA's block range.  Partial rows go to `a.part` (tp_off < 0) or into every
-// rank's exchange region at float offset tp_off.
+// One linear.  The CTA stages its activation slice as 15-bit fixed point per (token, quantisation group): two signed
+// 8-bit limbs (x = 128 hi + lo) in the B-operand order of mma.m16n8k32, columns (2 tok, 2 tok + 1) = (hi, lo) of
+// token tok, plus per group the scale amax / 16383 and the integer sum of the group (zero points).  Codes are the
+// unsigned A operand, so a group's dot product is exact in int32; scale and zero point are applied in fp32 per
+// group: y += s_w * (s_x * acc - z_w * s_x * sum_x).  Then the CTA walks the panel segments of its block range.
+// Partial rows go to `a.part` (tp_off < 0) or into every rank's exchange region at float offset tp_off.
 template <int BITS, int GROUP>
-__device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, uint8_t* smem, WRing& ring, Cursor& cur,
+__device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, uint8_t* smem, const Lay& lay, WRing& ring,
                                           const bf16* x, long ldx, const bf16* norm_w, long tp_off, bool& failed) {
   constexpr int GPB = 128 / GROUP;
+  constexpr int SPG = 4 / GPB;               // integer-MMA steps per quantisation group
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int cta = blockIdx.x;
   const int R = a.n_rows;
   const StepLinear& L = ph.lin;
   const int nbs = ph.nbs;
-  const int XST = nbs * 128 + 16;
-  __half* xs = reinterpret_cast<__half*>(smem + SM_WORK);
-  float2* gsum = reinterpret_cast<float2*>(smem + SM_GSUM);
+  const int kRingBytes = lay.ring_w;
+  const int xstride = lay.xs_stride;
+  uint8_t* xs8 = smem + SM_WORK;                                       // [batch][token set][step][column][t][half][4]
+  float2* gsum = reinterpret_cast<float2*>(smem + lay.gsum);          // [group][token] (s_x, s_x * sum_x)
   float* misc = reinterpret_cast<float*>(smem + SM_MISC);
   float* inv_rms = misc;
   float* wsum = misc + MI_WSUM;
+#ifdef B2_STEP_TRACE
+  long long tc_wait = 0, tc_comp = 0, tc_pump = 0, tc_red = 0, tc_units = 0;
+  const long long tc_begin = clock64();
+#define B2_TC(var, t0) var += clock64() - (t0)
+#define B2_T0(name) const long long name = clock64()
+#else
+#define B2_TC(var, t0) do { } while (0)
+#define B2_T0(name) do { } while (0)
+#endif
 
   if (norm_w) {
     const int nv = L.k >> 3;
@@ -294,14 +417,14 @@ __device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, ui
       s = warp_sum(s);
       if (lane == 0) wsum[tok * kStepWarps + warp] = s;
     }
-    __syncthreads();
+    workers_sync();
     if (tid < R) {
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < kStepWarps; ++w) s += wsum[tid * kStepWarps + w];
       inv_rms[tid] = rsqrtf(s / (float)L.k + a.eps);
     }
-    __syncthreads();
+    workers_sync();
   }
   if (ph.active && nbs > 0) {
     const int nvec = nbs * 16;
@@ -310,12 +433,13 @@ __device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, ui
       for (int v0 = 0; v0 < nvec; v0 += kStepThreads) {
         const int v = v0 + tid;
         const bool act = v < nvec;
-        float ssum = 0.f, xsum = 0.f;
+        float f[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = 0.f;
         if (act) {
           const int k = k0 + v * 8;
           const uint4 raw = __ldcg(reinterpret_cast<const uint4*>(x + (size_t)tok * ldx + k));
           const bf16* xb = reinterpret_cast<const bf16*>(&raw);
-          float f[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) f[i] = __bfloat162float(xb[i]);
           if (norm_w) {
@@ -325,137 +449,225 @@ __device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, ui
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[i] = bf16_round(f[i] * ir * __bfloat162float(wb[i]));
           }
-          __align__(16) __half h[8];
+        }
+        float amax = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float cinv, c;
-            slot_scale<BITS>((v * 8 + i) & 127, cinv, c);
-            h[i] = __float2half_rn(f[i] * cinv);
-            const float hf = __half2float(h[i]);
-            ssum += hf;
-            xsum += hf * c;
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+        for (int o = GROUP / 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float inv = amax > 0.f ? 16383.f / amax : 0.f;
+        int xi[8], isum = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { xi[i] = __float2int_rn(f[i] * inv); isum += xi[i]; }
+#pragma unroll
+        for (int o = GROUP / 16; o > 0; o >>= 1) isum += __shfl_xor_sync(0xffffffffu, isum, o);
+        if (act) {
+          uint32_t hi[2], lo[2];
+#pragma unroll
+          for (int w = 0; w < 2; ++w) {
+            hi[w] = 0u; lo[w] = 0u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int q = xi[4 * w + j];
+              hi[w] |= ((uint32_t)(q >> 7) & 0xFFu) << (8 * j);
+              lo[w] |= ((uint32_t)q & 0x7Fu) << (8 * j);
+            }
           }
-          *reinterpret_cast<uint4*>(xs + (size_t)tok * XST + v * 8) = *reinterpret_cast<const uint4*>(h);
+          const int b = v >> 4, kb = (v * 8) & 127;
+          const int s = kb >> 5, half = (kb >> 4) & 1, t0 = (kb & 15) >> 2;       // eight consecutive k: t0 and t0 + 1
+          const int col = 2 * (tok & 3);
+          uint8_t* base = xs8 + (size_t)b * xstride + (tok >> 2) * 1024 + s * 256 + half * 4;
+          *reinterpret_cast<uint32_t*>(base + (col * 4 + t0) * 8) = hi[0];
+          *reinterpret_cast<uint32_t*>(base + (col * 4 + t0 + 1) * 8) = hi[1];
+          *reinterpret_cast<uint32_t*>(base + ((col + 1) * 4 + t0) * 8) = lo[0];
+          *reinterpret_cast<uint32_t*>(base + ((col + 1) * 4 + t0 + 1) * 8) = lo[1];
+          if ((lane % (GROUP / 8)) == 0) {
+            const float sx = amax * (1.f / 16383.f);
+            gsum[((v * 8) / GROUP) * kStepMaxRows + tok] = make_float2(sx, sx * (float)isum);
+          }
         }
-#pragma unroll
-        for (int o = GROUP / 16; o > 0; o >>= 1) {
-          ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
-          xsum += __shfl_xor_sync(0xffffffffu, xsum, o);
-        }
-        if (act && (lane % (GROUP / 8)) == 0) gsum[((v * 8) / GROUP) * kStepMaxRows + tok] = make_float2(1024.f * ssum, xsum);
       }
     }
   }
-  __syncthreads();
+  workers_sync();
   if (!ph.active) return;
+#ifdef B2_STEP_TRACE
+  const long long tc_staged = clock64();
+#endif
 
   const unsigned Bsl = (unsigned)L.npan * (unsigned)nbs;
   const int nslots = L.ks * L.fmax;
-  unsigned blk = ph.lo;
-  int seg = 0;
-  const int usz = L.wbatch + L.szb;
-  while (blk < ph.hi) {
+  const bool two_sets = R > 4;
+  const int tokc = g >> 1;                    // token whose (hi, lo) columns this lane feeds as B operand
+  const int usz = L.blk;
+  float* tiles = reinterpret_cast<float*>(smem + lay.tiles);               // [warp][head | tail][token][32 rows]
+  unsigned* tile_panel = reinterpret_cast<unsigned*>(misc + MI_TILE);   // [warp][head | tail] panel of the tile, or none
+  const int tile_f = R * 32;
+  if (lane < 2) tile_panel[warp * 2 + lane] = 0xffffffffu;
+  __syncwarp();
+
+  // Stores one finished (32 rows x R tokens) panel sum of this CTA into its fragment slot; the CTA that holds the
+  // panel's last block also zeroes the slots that no fragment uses.
+  auto store_panel = [&](unsigned p, int row, int tok, float val) {
+    const unsigned first_owner = (((p * (unsigned)nbs) + 1u) * (unsigned)L.cps - 1u) / Bsl;
+    const int f = ph.ci - (int)first_owner;
+    const int f_end = ((p + 1u) * (unsigned)nbs <= ph.hi) ? L.fmax : f + 1;
+    const size_t col = (size_t)p * 32 + row;
+    for (int ff = f; ff < f_end; ++ff) {
+      const float v = ff == f ? val : 0.f;
+      const size_t off = ((size_t)(ph.slice * L.fmax + ff) * R + tok) * L.n + col;
+      if (tp_off < 0) {
+        a.part[off] = v;
+      } else {
+        const size_t roff = (size_t)tp_off + (size_t)a.tp_rank * nslots * R * L.n + off;
+        for (int d = 0; d < a.tp_size; ++d) a.xreg[d][roff] = v;
+      }
+    }
+  };
+
+  unsigned blk, whi;
+  warp_range(ph, warp, blk, whi);
+  int n_tiles = 0;
+  while (blk < whi) {
     const unsigned p = blk / (unsigned)nbs;
-    const int b_lo = (int)(blk - p * (unsigned)nbs);
-    const int b_hi = (int)min(ph.hi - p * (unsigned)nbs, (unsigned)nbs);
-    float y[4] = {0.f, 0.f, 0.f, 0.f};
+    const int b0 = (int)(blk - p * (unsigned)nbs);
+    const int b1 = (int)min(whi - p * (unsigned)nbs, (unsigned)nbs);
+    float y[2][4];                            // [row block][row g tok t, row g+8 tok t, row g tok t+4, row g+8 tok t+4]
+#pragma unroll
+    for (int r = 0; r < 2; ++r)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[r][i] = 0.f;
 #pragma unroll 1
-    for (int b = b_lo + (warp >> 1); b < b_hi; b += 8) {
+    for (int b = b0; b < b1; ++b) {
       int freed = usz;
       if (ring.cpos + usz > kRingBytes) { freed += kRingBytes - ring.cpos; ring.cpos = 0; }
+      B2_T0(tw0);
       if (!failed) {
         if (!mbar_wait_bounded(ring.bars_u + (ring.cidx % kRingBars) * 8, (ring.cidx / kRingBars) & 1u)) {
           atomicExch(a.status, (int)B2_ERR_TIMEOUT);
           failed = true;
         }
       }
+      B2_TC(tc_wait, tw0);
+      B2_T0(tc0);
       if (!failed) {
         const uint8_t* stg = ring.base + ring.cpos;
-        WFrag<BITS, GROUP> cf;
-        load_frag_smem<BITS, GROUP>(cf, stg, stg + L.wbatch, lane);
-        const __half* xrow = xs + b * 128 + t * 4;
+        const uint8_t* xb = xs8 + (size_t)b * xstride + (g * 4 + t) * 8;
+        // B operands of the batch's four steps (both row blocks use them) and the groups' activation scalars
+        uint2 bv[4], bw[4];
+#pragma unroll
+        for (int s4 = 0; s4 < 4; ++s4) {
+          bv[s4] = make_uint2(0u, 0u); bw[s4] = make_uint2(0u, 0u);
+          if (tokc < R) bv[s4] = *reinterpret_cast<const uint2*>(xb + s4 * 256);
+          if (two_sets && tokc + 4 < R) bw[s4] = *reinterpret_cast<const uint2*>(xb + 1024 + s4 * 256);
+        }
+        // both row blocks step by step: two (four with more than four rows) independent integer-MMA chains in flight
+        WFrag<BITS, GROUP> c0, c1;
+        load_frag_smem<BITS, GROUP>(c0, stg, stg + 2 * L.wbatch, lane);
+        load_frag_smem<BITS, GROUP>(c1, stg + L.wbatch, stg + 2 * L.wbatch + L.szb, lane);
 #pragma unroll
         for (int gg = 0; gg < GPB; ++gg) {
-          const int gi = b * GPB + gg;
-          const float2 q0 = gsum[gi * kStepMaxRows + 2 * t];
-          const float2 q1 = gsum[gi * kStepMaxRows + 2 * t + 1];
-          float acc[4] = {-q0.x, -q1.x, -q0.x, -q1.x};
+          const float2 q0 = gsum[(b * GPB + gg) * kStepMaxRows + t];
+          const float2 q1 = two_sets ? gsum[(b * GPB + gg) * kStepMaxRows + t + 4] : make_float2(0.f, 0.f);
+          int a00[4] = {0, 0, 0, 0}, a01[4] = {0, 0, 0, 0}, a10[4] = {0, 0, 0, 0}, a11[4] = {0, 0, 0, 0};
 #pragma unroll
-          for (int s8 = 0; s8 < 8 / GPB; ++s8) {
-            const int s = gg * (8 / GPB) + s8;
-            uint2 bv = make_uint2(0u, 0u);
-            if (g < R) bv = *reinterpret_cast<const uint2*>(xrow + (size_t)g * XST + s * 16);
-            uint32_t af[4];
-            extract<BITS, GROUP>(cf, s, af);
-            mma_f16_16816(acc, af, bv.x, bv.y);
+          for (int s8 = 0; s8 < SPG; ++s8) {
+            const int s4 = gg * SPG + s8;
+            uint32_t af0[4], af1[4];
+            extract8<BITS, GROUP>(c0, s4, af0);
+            extract8<BITS, GROUP>(c1, s4, af1);
+            mma_u8s8_16832(a00, af0, bv[s4].x, bv[s4].y);
+            mma_u8s8_16832(a10, af1, bv[s4].x, bv[s4].y);
+            if (two_sets) {
+              mma_u8s8_16832(a01, af0, bw[s4].x, bw[s4].y);
+              mma_u8s8_16832(a11, af1, bw[s4].x, bw[s4].y);
+            }
           }
-          const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&cf.sz[gg][0]));
-          const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&cf.sz[gg][1]));
-          y[0] = fmaf(s0.x, fmaf(-s0.y, q0.y, acc[0]), y[0]);
-          y[1] = fmaf(s0.x, fmaf(-s0.y, q1.y, acc[1]), y[1]);
-          y[2] = fmaf(s1.x, fmaf(-s1.y, q0.y, acc[2]), y[2]);
-          y[3] = fmaf(s1.x, fmaf(-s1.y, q1.y, acc[3]), y[3]);
+          gemv_scale(y[0], a00, a01, c0.sz[gg], q0, q1, two_sets);
+          gemv_scale(y[1], a10, a11, c1.sz[gg], q0, q1, two_sets);
         }
       }
       __syncwarp();
+      B2_TC(tc_comp, tc0);
+      B2_T0(tp0);
       ++ring.cidx;
       ring.cpos += usz;
-      if (lane == 0) {
-        ring.pfree += freed;
-        if (!failed) pump(ring, cur, a, cta, warp);
+      ring.cbytes += (unsigned)freed;
+      if (lane == 0) {                      // the stage is free again: tell the producer warp
+        __threadfence_block();
+        ring.pub[1] = ring.cbytes;
+        ring.pub[0] = ring.cidx;
       }
+      B2_TC(tc_pump, tp0);
+#ifdef B2_STEP_TRACE
+      ++tc_units;
+#endif
     }
-    // the 16 warps' tiles of this segment meet in shared memory; eight warps carry each 16-row block
-    float* red = reinterpret_cast<float*>(smem + SM_RED) + (seg & 1) * kStepWarps * kRedWarp;
-    {
-      float* mine = red + warp * kRedWarp;
-      mine[(2 * t) * kRedTok + g] = y[0];
-      mine[(2 * t + 1) * kRedTok + g] = y[1];
-      mine[(2 * t) * kRedTok + g + 8] = y[2];
-      mine[(2 * t + 1) * kRedTok + g + 8] = y[3];
-    }
-    __syncthreads();
-    if (tid < 256) {
-      const int row = tid & 31, tok = tid >> 5;
-      if (tok < R) {
-        const int rb = row >> 4, r16 = row & 15;
-        float s = 0.f;
+    // the warp's sum over [b0, b1) of panel p: final for this CTA when the piece covers the whole panel, else a tile
+    if (b0 == 0 && b1 == nbs) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s += red[(2 * j + rb) * kRedWarp + tok * kRedTok + r16];
-        // fragment index of this CTA inside the panel = CTAs since the one that owns the panel's first block
-        const unsigned first_owner = (((p * (unsigned)nbs) + 1u) * (unsigned)L.cps - 1u) / Bsl;
-        const int f = ph.ci - (int)first_owner;
-        const int f_end = (b_hi == nbs) ? L.fmax : f + 1;     // the last fragment also zeroes the unused slots
-        const size_t col = (size_t)p * 32 + row;
-        for (int ff = f; ff < f_end; ++ff) {
-          const float val = ff == f ? s : 0.f;
-          const size_t off = ((size_t)(ph.slice * L.fmax + ff) * R + tok) * L.n + col;
-          if (tp_off < 0) {
-            a.part[off] = val;
-          } else {
-            const size_t roff = (size_t)tp_off + (size_t)a.tp_rank * nslots * R * L.n + off;
-            for (int d = 0; d < a.tp_size; ++d) a.xreg[d][roff] = val;
-          }
-        }
+      for (int rb = 0; rb < 2; ++rb) {
+        if (t < R) { store_panel(p, rb * 16 + g, t, y[rb][0]); store_panel(p, rb * 16 + g + 8, t, y[rb][1]); }
+        if (two_sets && t + 4 < R) { store_panel(p, rb * 16 + g, t + 4, y[rb][2]); store_panel(p, rb * 16 + g + 8, t + 4, y[rb][3]); }
       }
+    } else {
+      float* mine = tiles + (size_t)(warp * 2 + n_tiles) * tile_f;
+#pragma unroll
+      for (int rb = 0; rb < 2; ++rb) {
+        if (t < R) { mine[t * 32 + rb * 16 + g] = y[rb][0]; mine[t * 32 + rb * 16 + g + 8] = y[rb][1]; }
+        if (two_sets && t + 4 < R) { mine[(t + 4) * 32 + rb * 16 + g] = y[rb][2]; mine[(t + 4) * 32 + rb * 16 + g + 8] = y[rb][3]; }
+      }
+      if (lane == 0) tile_panel[warp * 2 + n_tiles] = p;
+      ++n_tiles;
     }
-    blk = p * (unsigned)nbs + (unsigned)b_hi;
-    ++seg;
+    blk = p * (unsigned)nbs + (unsigned)b1;
   }
+  B2_T0(tr0);
+  workers_sync();
+  // Partial tiles of one panel come from consecutive warps (tail of one, heads of the next ones): one pass over the
+  // tiles in (warp, head / tail) order adds each panel's tiles in k order and stores the sum when the panel changes.
+  if (tid < 256) {
+    const int row = tid & 31, tok = tid >> 5;
+    if (tok < R) {
+      unsigned cur_p = 0xffffffffu;
+      float s = 0.f;
+      for (int i = 0; i < 2 * kStepWarps; ++i) {
+        const unsigned tp = tile_panel[i];
+        if (tp == 0xffffffffu) continue;
+        if (tp != cur_p) {
+          if (cur_p != 0xffffffffu) store_panel(cur_p, row, tok, s);
+          cur_p = tp; s = 0.f;
+        }
+        s += tiles[(size_t)i * tile_f + tok * 32 + row];
+      }
+      if (cur_p != 0xffffffffu) store_panel(cur_p, row, tok, s);
+    }
+  }
+  workers_sync();          // tiles and activations are reused by the next phase
+  B2_TC(tc_red, tr0);
+#ifdef B2_STEP_TRACE
+  if (a.trace && blockIdx.x == 0 && lane == 0) {
+    unsigned long long* tr = a.trace + 4096 + ((size_t)a.trace[4095] * kStepWarps + warp) * 8;
+    tr[0] = tc_staged - tc_begin; tr[1] = tc_wait; tr[2] = tc_comp; tr[3] = tc_pump; tr[4] = tc_red; tr[5] = tc_units;
+    tr[6] = clock64() - tc_begin;
+  }
+  workers_sync();
+  if (a.trace && blockIdx.x == 0 && tid == 0) a.trace[4095] += 1;
+#endif
 }
 
-__device__ __forceinline__ void gemv_phase(const StepArgs& a, int phase, uint8_t* smem, WRing& ring, Cursor& cur,
+__device__ __forceinline__ void gemv_phase(const StepArgs& a, int phase, uint8_t* smem, const Lay& lay, WRing& ring,
                                            const bf16* x, long ldx, const bf16* norm_w, long tp_off, bool& failed) {
   Phase ph;
   load_linear(a, phase, ph.lin);
   split_phase(ph, blockIdx.x);
   switch (ph.lin.bits * 1000 + ph.lin.group) {
-    case 4128: gemv_body<4, 128>(a, ph, smem, ring, cur, x, ldx, norm_w, tp_off, failed); break;
-    case 4064: gemv_body<4, 64>(a, ph, smem, ring, cur, x, ldx, norm_w, tp_off, failed); break;
-    case 3128: gemv_body<3, 128>(a, ph, smem, ring, cur, x, ldx, norm_w, tp_off, failed); break;
-    case 3064: gemv_body<3, 64>(a, ph, smem, ring, cur, x, ldx, norm_w, tp_off, failed); break;
-    case 2128: gemv_body<2, 128>(a, ph, smem, ring, cur, x, ldx, norm_w, tp_off, failed); break;
-    default: gemv_body<2, 64>(a, ph, smem, ring, cur, x, ldx, norm_w, tp_off, failed); break;
+    case 4128: gemv_body<4, 128>(a, ph, smem, lay, ring, x, ldx, norm_w, tp_off, failed); break;
+    case 4064: gemv_body<4, 64>(a, ph, smem, lay, ring, x, ldx, norm_w, tp_off, failed); break;
+    case 3128: gemv_body<3, 128>(a, ph, smem, lay, ring, x, ldx, norm_w, tp_off, failed); break;
+    case 3064: gemv_body<3, 64>(a, ph, smem, lay, ring, x, ldx, norm_w, tp_off, failed); break;
+    case 2128: gemv_body<2, 128>(a, ph, smem, lay, ring, x, ldx, norm_w, tp_off, failed); break;
+    default: gemv_body<2, 64>(a, ph, smem, lay, ring, x, ldx, norm_w, tp_off, failed); break;
   }
 }
 
@@ -574,7 +786,7 @@ __device__ __forceinline__ void fin_swiglu(const StepArgs& a, const StepLinear* 
 // attn_decode_kernel<128, false> (attn_decode.cu) with a two-stage K/V ring in this warp's shared memory.
 __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool, long item, uint8_t* wsm, const int* row_pos,
                                        const int* row_seq) {
-  constexpr int HD = 128, KS = HD / 16, NTO = HD / 8, ROWB = HD * 2, CPR = ROWB / 16, PAGE_B = kPage * ROWB, ST = 2;
+  constexpr int HD = 128, KS = HD / 16, NTO = HD / 8, ROWB = HD * 2, CPR = ROWB / 16, PAGE_B = kPage * ROWB, ST = kAttnStages;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int gq = a.hq / a.hkv;
@@ -624,8 +836,11 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
       cp_async16(vs + off, vp + (size_t)c * 16);
     }
   };
-  if (0 < n_pg) issue_page(0);
-  cp_async_commit();
+#pragma unroll
+  for (int pi = 0; pi < ST - 1; ++pi) {
+    if (pi < n_pg) issue_page(pi);
+    cp_async_commit();
+  }
 
   uint32_t qa[KS][4];
 #pragma unroll
@@ -650,9 +865,9 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
 
   for (int pi = 0; pi < n_pg; ++pi) {
-    if (pi + 1 < n_pg) issue_page(pi + 1);
+    if (pi + ST - 1 < n_pg) issue_page(pi + ST - 1);
     cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<ST - 1>();
     __syncwarp();
     const int stage = pi % ST;
     const uint32_t ks_u = wsm_u + stage * 2 * PAGE_B, vs_u = ks_u + PAGE_B;
@@ -763,7 +978,7 @@ __device__ __forceinline__ void attn_phase(const StepArgs& a, const bf16* kv_poo
   const int n_sp = min(a.max_splits, max_pos / a.split_keys + 1);
   const long per_grp = (long)a.hkv * mt_max;
   const long items = (long)a.n_groups * per_grp * n_sp;
-  uint8_t* wsm = smem + SM_WORK + (size_t)warp * 2 * 2 * kPage * 128 * 2;
+  uint8_t* wsm = smem + SM_WORK + (size_t)warp * kAttnStages * 2 * kPage * 128 * 2;
   for (long it = (long)warp * gridDim.x + blockIdx.x; it < items; it += (long)gridDim.x * kAttnWarps) {
     // item order: split fastest, so that the items of one (group, head) spread over the CTAs
     const long outer = it / n_sp;
@@ -772,60 +987,46 @@ __device__ __forceinline__ void attn_phase(const StepArgs& a, const bf16* kv_poo
   }
 }
 
-// Merge of the attention splits of every (row, q head); the order of additions of attn_merge_kernel<128, 1>.
+// Merge of the attention splits of every (row, q head): one warp per item, lane = four output dimensions; the
+// splits are added in ascending order and their loads do not depend on one another, so they are all in flight at once.
 __device__ __forceinline__ void fin_merge(const StepArgs& a, const int* row_pos) {
-  constexpr int HD = 128, PER = HD / 32, SETS = 8;
+  constexpr int HD = 128;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int items = a.n_rows * a.hq;
   for (int item = warp * gridDim.x + blockIdx.x; item < items; item += gridDim.x * kStepWarps) {
     const int tok = item / a.hq, head = item - tok * a.hq;
     const int ns = (row_pos[tok] + a.split_keys) / a.split_keys;
-    const float* po = a.part_o + ((size_t)tok * a.hq + head) * a.max_splits * HD;
+    const float* po = a.part_o + ((size_t)tok * a.hq + head) * a.max_splits * HD + lane * 4;
     const float2* pm = reinterpret_cast<const float2*>(a.part_ml + ((size_t)tok * a.hq + head) * a.max_splits * 2);
     float M = -INFINITY;
     for (int s = lane; s < ns; s += 32) M = fmaxf(M, __ldcg(pm + s).x);
     M = warp_max(M);
-    float acc[SETS][PER], Lw[SETS];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float Ls = 0.f;
+    for (int s0 = 0; s0 < ns; s0 += 8) {
+      float2 ml[8];
+      float4 pv[8];
 #pragma unroll
-    for (int w = 0; w < SETS; ++w) {
-      Lw[w] = 0.f;
+      for (int j = 0; j < 8; ++j) {
+        const int sidx = min(s0 + j, ns - 1);
+        ml[j] = __ldcg(pm + sidx);
+        pv[j] = __ldcg(reinterpret_cast<const float4*>(po + (size_t)sidx * HD));
+      }
 #pragma unroll
-      for (int i = 0; i < PER; ++i) acc[w][i] = 0.f;
-    }
-    for (int blk = 0; blk * 8 < ns; ++blk) {
-      const int s0 = blk * 8;
-#pragma unroll
-      for (int w = 0; w < SETS; ++w) {
-        if ((blk & (SETS - 1)) != w) continue;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int s = s0 + j;
-          if (s >= ns) continue;
-          const float2 ml = __ldcg(pm + s);
-          if (ml.x == -INFINITY) continue;
-          const float4 pv = __ldcg(reinterpret_cast<const float4*>(po + (size_t)s * HD + lane * PER));
-          const float wt = exp2f(ml.x - M);
-          Lw[w] = fmaf(ml.y, wt, Lw[w]);
-          acc[w][0] = fmaf(pv.x, wt, acc[w][0]);
-          acc[w][1] = fmaf(pv.y, wt, acc[w][1]);
-          acc[w][2] = fmaf(pv.z, wt, acc[w][2]);
-          acc[w][3] = fmaf(pv.w, wt, acc[w][3]);
-        }
+      for (int j = 0; j < 8; ++j) {
+        if (s0 + j >= ns || ml[j].x == -INFINITY) continue;
+        const float wt = exp2f(ml[j].x - M);
+        Ls = fmaf(ml[j].y, wt, Ls);
+        acc.x = fmaf(pv[j].x, wt, acc.x);
+        acc.y = fmaf(pv[j].y, wt, acc.y);
+        acc.z = fmaf(pv[j].z, wt, acc.z);
+        acc.w = fmaf(pv[j].w, wt, acc.w);
       }
     }
-    float o[PER], Ls = Lw[0];
-#pragma unroll
-    for (int i = 0; i < PER; ++i) o[i] = acc[0][i];
-#pragma unroll
-    for (int w = 1; w < SETS; ++w) {
-      Ls = __fadd_rn(Ls, Lw[w]);
-#pragma unroll
-      for (int i = 0; i < PER; ++i) o[i] = __fadd_rn(o[i], acc[w][i]);
-    }
     const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
-    bf16* out = a.attn + (size_t)tok * a.hq * HD + (size_t)head * HD + lane * PER;
-    *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(__fmul_rn(o[0], inv), __fmul_rn(o[1], inv));
-    *reinterpret_cast<__nv_bfloat162*>(out + 2) = __floats2bfloat162_rn(__fmul_rn(o[2], inv), __fmul_rn(o[3], inv));
+    bf16* out = a.attn + (size_t)tok * a.hq * HD + (size_t)head * HD + lane * 4;
+    *reinterpret_cast<__nv_bfloat162*>(out) = __floats2bfloat162_rn(__fmul_rn(acc.x, inv), __fmul_rn(acc.y, inv));
+    *reinterpret_cast<__nv_bfloat162*>(out + 2) = __floats2bfloat162_rn(__fmul_rn(acc.z, inv), __fmul_rn(acc.w, inv));
   }
 }
 
@@ -853,7 +1054,7 @@ __device__ __forceinline__ void fin_argmax_cta(const StepArgs& a, uint8_t* smem)
     }
     if (lane == 0) { sv[warp * kStepMaxRows + tok] = best; si[warp * kStepMaxRows + tok] = bi; }
   }
-  __syncthreads();
+  workers_sync();
   if (threadIdx.x < R) {
     const int tok = threadIdx.x;
     float best = sv[tok];
@@ -888,7 +1089,7 @@ __device__ __forceinline__ void argmax_over_ctas(const StepArgs& a, int tok, flo
 
 }  // namespace
 
-__global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepArgs a) {
+__global__ void __launch_bounds__(kStepBlock, 1) step_kernel(const StepArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int cta = blockIdx.x;
@@ -898,21 +1099,31 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepArgs a)
   int* row_seq = row_ids + 16;
   int* row_rope = row_ids + 24;
 
-  WRing ring;
-  ring.base = smem + SM_RING + (size_t)warp * kRingBytes;
-  ring.base_u = smem_u32(ring.base);
-  ring.bars_u = smem_u32(smem + SM_BARS) + warp * kRingBars * 8;
-  ring.pidx = ring.cidx = 0;
-  ring.ppos = ring.cpos = 0;
-  ring.pfree = kRingBytes;
-  if (lane == 0) {
+  if (warp < kStepWarps && lane == 0) {
+    const uint32_t bars = smem_u32(smem + SM_BARS) + warp * kRingBars * 8;
 #pragma unroll
-    for (int i = 0; i < kRingBars; ++i) mbar_init(ring.bars_u + i * 8, 1);
+    for (int i = 0; i < kRingBars; ++i) mbar_init(bars + i * 8, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    volatile unsigned* pub = reinterpret_cast<volatile unsigned*>(misc) + MI_PUB + 2 * warp;
+    pub[0] = 0u; pub[1] = 0u;
   }
+  __syncthreads();          // the only CTA-wide barrier: rings are initialised before the producer warp starts
+  const Lay lay = make_lay(a.n_rows);
+  if (warp == kStepWarps) {
+    producer_loop(a, smem, cta, lay);     // weights do not depend on anything: start streaming at once
+    return;
+  }
+
+  WRing ring;
+  ring.base = smem + lay.ring + (size_t)warp * lay.ring_w;
+  ring.bars_u = smem_u32(smem + SM_BARS) + warp * kRingBars * 8;
+  ring.cidx = 0; ring.cbytes = 0; ring.cpos = 0;
+  ring.pub = reinterpret_cast<volatile unsigned*>(misc) + MI_PUB + 2 * warp;
   SyncState ss;
   ss.local_target = a.sync[1];
   ss.cross_target = a.sync[2];
+  ss.ev = 0;
+  B2_STAMP(a, ss);
   if (tid < kStepMaxRows) {
     int id = 0, pos = 0, seq = 0, rp = 0;
     if (tid < a.n_rows) {
@@ -929,19 +1140,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepArgs a)
     }
     row_ids[tid] = id; row_pos[tid] = pos; row_seq[tid] = seq; row_rope[tid] = rp;
   }
-  __syncthreads();
-
-  Cursor cur;
-  cur.n_phases = 4 * a.n_layers + 1;
-  cur.phase = 0;
-  cur.p = 0; cur.b = 0; cur.b_hi = 0;
-  if (lane == 0) {
-    load_linear(a, 0, cur.ph.lin);
-    split_phase(cur.ph, cta);
-    cursor_settle(cur, a, cta, warp, true);
-    pump(ring, cur, a, cta, warp);     // weights do not depend on anything: start streaming at once
-  }
-  __syncwarp();
+  workers_sync();
   bool failed = false;
 
   fin_embed(a, row_ids);
@@ -950,7 +1149,7 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepArgs a)
   const bool tp = a.tp_size > 1;
   for (int l = 0; l < a.n_layers; ++l) {
     const StepLayer* ly = a.layers + l;
-    gemv_phase(a, 4 * l, smem, ring, cur, a.h, d, ly->ln1, -1, failed);
+    gemv_phase(a, 4 * l, smem, lay, ring, a.h, d, ly->ln1, -1, failed);
     grid_sync(a, ss);
     fin_qkv(a, ly, row_pos, row_seq, row_rope);
     grid_sync(a, ss);
@@ -958,20 +1157,20 @@ __global__ void __launch_bounds__(kStepThreads, 1) step_kernel(const StepArgs a)
     grid_sync(a, ss);
     fin_merge(a, row_pos);
     grid_sync(a, ss);
-    gemv_phase(a, 4 * l + 1, smem, ring, cur, a.attn, (long)a.hq * 128, nullptr, tp ? a.x_off[0] : -1, failed);
+    gemv_phase(a, 4 * l + 1, smem, lay, ring, a.attn, (long)a.hq * 128, nullptr, tp ? a.x_off[0] : -1, failed);
     cross_sync(a, ss);
     fin_resid(a, &ly->o, tp ? a.x_off[0] : -1);
     grid_sync(a, ss);
-    gemv_phase(a, 4 * l + 2, smem, ring, cur, a.h, d, ly->ln2, -1, failed);
+    gemv_phase(a, 4 * l + 2, smem, lay, ring, a.h, d, ly->ln2, -1, failed);
     grid_sync(a, ss);
     fin_swiglu(a, &ly->gate_up);
     grid_sync(a, ss);
-    gemv_phase(a, 4 * l + 3, smem, ring, cur, a.act, (long)a.ffn, nullptr, tp ? a.x_off[1] : -1, failed);
+    gemv_phase(a, 4 * l + 3, smem, lay, ring, a.act, (long)a.ffn, nullptr, tp ? a.x_off[1] : -1, failed);
     cross_sync(a, ss);
     fin_resid(a, &ly->down, tp ? a.x_off[1] : -1);
     grid_sync(a, ss);
   }
-  gemv_phase(a, 4 * a.n_layers, smem, ring, cur, a.h, d, a.final_norm, -1, failed);
+  gemv_phase(a, 4 * a.n_layers, smem, lay, ring, a.h, d, a.final_norm, -1, failed);
   grid_sync(a, ss);
   fin_argmax_cta(a, smem);
   grid_sync(a, ss);
@@ -1066,7 +1265,7 @@ B2_API int b2_step_grid(int* ncta) {
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
   if (cudaFuncSetAttribute(step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SM_TOTAL) != cudaSuccess) return B2_ERR_LAUNCH;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, step_kernel, kStepThreads, SM_TOTAL) != cudaSuccess) return B2_ERR_LAUNCH;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, step_kernel, kStepBlock, SM_TOTAL) != cudaSuccess) return B2_ERR_LAUNCH;
   if (occ < 1 || !coop || sms < 1) return B2_ERR_LAUNCH;
   *ncta = sms;
   return B2_OK;
@@ -1088,7 +1287,7 @@ B2_API int b2_step_launch(const StepArgs* args, int ncta, cudaStream_t stream) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)ncta, 1, 1);
-  cfg.blockDim = dim3(kStepThreads, 1, 1);
+  cfg.blockDim = dim3(kStepBlock, 1, 1);
   cfg.dynamicSmemBytes = SM_TOTAL;
   cfg.stream = stream;
   cudaLaunchAttribute at[1];

@@ -5,8 +5,9 @@
 
 namespace b2 {
 
-constexpr int kStepWarps = 16;
-constexpr int kStepThreads = kStepWarps * 32;
+constexpr int kStepWarps = 15;           // worker warps of a CTA
+constexpr int kStepThreads = kStepWarps * 32;     // worker threads
+constexpr int kStepBlock = kStepThreads + 32;    // plus the producer warp that feeds the workers' weight rings
 constexpr int kStepMaxRows = 8;          // token rows of one step (the n dimension of one mma tile)
 constexpr int kStepSliceK = 5120;        // most inputs of a linear that one CTA stages (k slice)
 constexpr int kStepMaxTp = 8;
@@ -27,7 +28,9 @@ struct StepLayer {
   const bf16* ln1;
   const bf16* ln2;
   bf16* kv_pool;           // [page][2][kv_head][16][128]
+  void* pad;               // keeps every element of the device array 16-byte aligned (the linears are read as uint4)
 };
+static_assert(sizeof(StepLayer) % 16 == 0, "StepLayer array elements must stay 16-byte aligned");
 
 struct StepArgs {
   const StepLayer* layers;   // device array [n_layers]
@@ -77,6 +80,7 @@ struct StepArgs {
   long x_off[2];             // float offsets of the two alternating partial areas (o_proj, down_proj)
   long x_amax;               // float offset of the argmax candidates [rank][8][2]
   int skip_push;             // test hook: this rank does not signal its peers (their bounded wait runs out)
+  unsigned long long* trace; // builds with -DB2_STEP_TRACE only: CTA 0 stamps %globaltimer at every barrier (arrive, leave)
 };
 
 }  // namespace b2

@@ -119,6 +119,51 @@ __global__ void wq_repack_kernel(const int32_t* __restrict__ packed, const void*
   }
 }
 
+
+// ---- FI layout ("fragment-major, integer"): the same blocks, records and (scale, zero) pairs as FM, but the codes of
+// a lane are laid out for mma.m16n8k32 with 8-bit operands: one AND (plus one shift for every other register) turns a
+// 32-bit word into four codes of ONE row as four bytes, i.e. one A register of the integer MMA.  For step s (32 k) of
+// a 128-k batch, lane (g, t) holds registers r = 0..3: row g + 8 (r & 1), k = 32 s + 16 (r >> 1) + 4 t + byte.
+//   4 bits: chunk s >> 1, word 2 (s & 1) + (r & 1), bit 8 byte + 4 (r >> 1)
+//   2 bits: word s, bit 8 byte + 2 r;   3 bits: low plane as 2 bits, high bit in word s >> 1 at bit 8 byte + 4 (s & 1) + r
+// The persistent decode-step kernel (step_kernel.cu) consumes this layout; everything else reads FM.
+__device__ __forceinline__ FmPos fi_pos(int r, int k, int bits, int group, int nbat) {
+  const int panel = r >> 5, rbp = (r >> 4) & 1, rr = r & 15, g = rr & 7, rh = rr >> 3;
+  const int batch = k >> 7, kb = k & 127;
+  const int s = kb >> 5, kl = kb & 31, half = kl >> 4, t = (kl >> 2) & 3, j = kl & 3;
+  const int reg = rh + 2 * half;
+  FmPos p;
+  p.rec = ((size_t)panel * nbat + batch) * fm_block(bits, group) + (size_t)rbp * fm_w_batch(bits);
+  p.lane = g * 4 + t;
+  p.hword = 0; p.hbit = 0;
+  if (bits == 4) {
+    p.rec += (size_t)(s >> 1) * 512;
+    p.word = 2 * (s & 1) + (reg & 1);
+    p.bit = 8 * j + 4 * (reg >> 1);
+  } else {
+    p.word = s;
+    p.bit = 8 * j + 2 * reg;
+    p.hword = s >> 1;
+    p.hbit = 8 * j + 4 * (s & 1) + reg;
+  }
+  return p;
+}
+
+// FM -> FI: one thread per code (a one-time conversion when a model opens the step kernel).
+__global__ void wq_fm_to_fi_kernel(const uint8_t* __restrict__ fm, int n, int k, int bits, int group, uint8_t* __restrict__ fi) {
+  const long total = (long)n * k;
+  const int nbat = k >> 7;
+  for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(idx / k), c = (int)(idx - (long)r * k);
+    const unsigned code = fm_load_code(fm, fm_pos(r, c, bits, group, nbat), bits);
+    fm_store_code(fi, fi_pos(r, c, bits, group, nbat), bits, code);
+    if (c % group == 0) {
+      const size_t off = fm_sz_off(r, c / group, bits, group, nbat);
+      *reinterpret_cast<uint32_t*>(fi + off) = *reinterpret_cast<const uint32_t*>(fm + off);
+    }
+  }
+}
+
 __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
   x += 0x9E3779B97F4A7C15ull;
   x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -205,5 +250,13 @@ B2_API int b2_wq_random(uint8_t* wq, int n, int k, int bits, int group, float st
   if (!fm_ok(n, k, bits, group)) return B2_ERR_ARG;
   if (cudaMemsetAsync(wq, 0, fm_bytes(n, k, bits, group), stream) != cudaSuccess) return B2_ERR_LAUNCH;
   wq_random_kernel<<<grid_for((long)n * (k / group), 128), 128, 0, stream>>>(wq, n, k, bits, group, stddev, seed);
+  return cudaGetLastError() == cudaSuccess ? B2_OK : B2_ERR_LAUNCH;
+}
+
+// FM -> FI (the integer-MMA layout of the decode-step kernel); `fi` has b2_wq_bytes(n, k, bits, group) bytes.
+B2_API int b2_wq_fm_to_fi(const uint8_t* fm, int n, int k, int bits, int group, uint8_t* fi, cudaStream_t stream) {
+  if (!fm_ok(n, k, bits, group) || !fm || !fi) return B2_ERR_ARG;
+  if (cudaMemsetAsync(fi, 0, fm_bytes(n, k, bits, group), stream) != cudaSuccess) return B2_ERR_LAUNCH;
+  wq_fm_to_fi_kernel<<<grid_for((long)n * k, 256), 256, 0, stream>>>(fm, n, k, bits, group, fi);
   return cudaGetLastError() == cudaSuccess ? B2_OK : B2_ERR_LAUNCH;
 }

@@ -31,6 +31,14 @@ def test_tp2_model_matches_single_gpu():
     _run("model")
 
 
+def test_tp2_step_kernel_fused_all_reduce():
+    _run("step")
+
+
+def test_tp4_step_kernel_fused_all_reduce():
+    _run("step", n=4)
+
+
 def test_tp2_engine_leader_follower_and_sampling():
     _run("engine")
 

@@ -113,6 +113,72 @@ def main():
         m._graphs.clear(); b._graphs.clear()
         m.close(); b.close()
         print(f"rank {rank}: closed", flush=True)
+    elif what == "step":
+        # the persistent step kernel under tensor parallelism: row-parallel partials cross NVLink inside the kernel and
+        # every rank adds all ranks' fragments in rank order; ranks agree bit for bit and match one GPU within tolerance
+        bits = {"0.qkv": 4, "0.o": 3, "0.gate_up": 2, "0.down": 4, "1.qkv": 2, "1.o": 4, "1.gate_up": 3, "1.down": 2}
+        cfg = C.ModelConfig("step-tp", 2, 512, 8, 4, 128, 1024, 2048, rope_theta=1e6, group=128, bits=bits, lm_head_bits=4)
+        ow = O.random_weights(cfg, seed=3)
+        torch.manual_seed(0)
+        prompt = torch.randint(0, cfg.vocab, (48,))
+        cont = torch.randint(0, cfg.vocab, (4,)).tolist()
+        m = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=2, max_ctx=256)
+        assert m.enable_step() and m.step.world == world
+        m.new_seq(0)
+        m.prefill(0, prompt)
+        rows = []
+        for t in cont:
+            _, lg = m.forward_rows([t], [0], want_logits=True)
+            rows.append(lg[0])
+        # the same four tokens as one verify block of a second sequence: bit-identical rows
+        m.new_seq(1)
+        m.prefill(1, prompt)
+        _, blk = m.forward_rows(cont, [1] * 4, want_logits=True)
+        for i in range(4):
+            assert torch.equal(blk[i], rows[i]), i
+        lg = torch.stack(rows)
+        assert m.device_status() == 0
+        assert m.step.launches >= 5
+        allr = [torch.empty_like(lg) for _ in range(world)]
+        dist.all_gather(allr, lg)
+        assert all(torch.equal(allr[0], x) for x in allr)          # rank-ordered sums: identical bits on every rank
+        if rank == 0:
+            r = DenseModel.from_oracle(ow, dev, max_seqs=1, max_ctx=256)
+            r.new_seq(0)
+            r.prefill(0, prompt)
+            ref = torch.stack([r.forward_rows([t], [0], want_logits=True)[1][0] for t in cont])
+            err = (lg - ref).abs().max().item()
+            assert err < 0.02 * ref.abs().max().item(), err
+        # greedy decode through the graph-replayed step: every rank produces the same tokens
+        m.truncate(0, 48)
+        first = int(lg[0].argmax())
+        m.decode_setup([0], [first], 8)
+        toks = m.decode_steps(8)[:, 0].tolist()
+        allt = [None] * world
+        dist.all_gather_object(allt, toks)
+        assert all(t == allt[0] for t in allt), allt
+        assert m.device_status() == 0
+        # a rank that does not signal: every rank's bounded barrier wait runs out, the status word says so, nothing
+        # hangs; after a host-side agreement the counters are reset and the next step is fine again
+        m.step.timeout_ns = int(0.3e9)
+        m.step.skip_push = rank == world - 1
+        m.forward_rows([cont[0]], [0])
+        torch.cuda.synchronize()
+        assert m.device_status() == _lib.B2_ERR_TIMEOUT
+        m.step.skip_push = False
+        dist.barrier()
+        m.recover()
+        torch.cuda.synchronize()
+        dist.barrier()
+        m.new_seq(0)
+        m.prefill(0, prompt)
+        _, again = m.forward_rows([cont[0]], [0], want_logits=True)
+        assert m.device_status() == 0
+        assert torch.equal(again[0], rows[0])
+        torch.cuda.synchronize()
+        dist.barrier()
+        m._graphs.clear()
+        m.close()
     elif what == "engine":
         # rank 0 schedules, the others follow; batched requests equal their solo runs, greedy and sampled
         from agens_engine_b200.parallel import driver as D
