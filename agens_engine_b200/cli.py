@@ -86,36 +86,89 @@ def _named_config(name: str):
     raise SystemExit(f"unknown architecture {name!r}")
 
 
+def _model_config(cfg: EngineConfig):
+    if cfg.model_dir:
+        from .models.config import ModelConfig
+        return ModelConfig.from_json(os.path.join(cfg.model_dir, "config.json"))
+    if cfg.random:
+        return _named_config(cfg.random)
+    raise SystemExit("give --model-dir DIR or --random NAME")
+
+
 def build_model(cfg: EngineConfig, **kw):
-    """Builds the (possibly tensor-parallel) model of this rank.  Returns ``(model, rank, world, ctrl_group)``."""
+    """Builds the (possibly tensor-parallel) model of this rank.  Returns ``(model, rank, world, ctrl_group)``.
+
+    With ``--budget-gib`` the load is planned first (``serve/budget.py``): the KV pool gets the pages the plan grants,
+    the context is clamped to what the pool plus the host tier can hold, the host tier is switched on when the plan
+    says so, every rank takes the minimum, the process's allocator is capped at the budget, and the plan is printed.
+    Reference: crates/agens-cli/src/m1.rs:905-974, plan.rs:182-241, tp.rs:77-90."""
     import torch
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     kw.setdefault("max_seqs", max(cfg.max_batch, 1))
     kw.setdefault("max_ctx", cfg.wctx)
     kw.setdefault("prefill_chunk", cfg.prefill_chunk)
     kw.setdefault("split_keys", cfg.split_keys)
+    ctrl = None
+    local = int(os.environ.get("LOCAL_RANK", rank)) if world > 1 else cfg.device
+    dev = f"cuda:{local}"
     if world > 1:
         import torch.distributed as dist
         from .parallel import driver as D
-        from .parallel.tp_model import TpDenseModel
-        local = int(os.environ.get("LOCAL_RANK", rank))
         torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        dist.init_process_group("nccl", device_id=torch.device(dev))
         ctrl = D.control_group()
+    dep = ledger = None
+    if cfg.budget_gib > 0:
+        from .serve import budget as B
+        mc = _model_config(cfg)
+        free, _total = torch.cuda.mem_get_info(local)
+        dep = B.plan_deployment(mc, cfg.budget_gib, kw["max_ctx"], cfg.max_batch, kw["max_seqs"], kw["prefill_chunk"], tp=world,
+                                gpu_free_gib=free / B.GiB, dual_layout=os.environ.get("B200E_STEP", "0") == "1")
+        if world > 1:
+            import torch.distributed as dist
+
+            def all_min(v):
+                t = torch.tensor(v, dtype=torch.int64)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN, group=ctrl)
+                return t.tolist()
+            dep = B.agree_min(dep, all_min)
+        if rank == 0:
+            for line in dep.lines:
+                print(line, flush=True)
+        if not dep.fits or dep.n_pages <= 0:
+            raise SystemExit(f"plan: weights and scratch do not fit {cfg.budget_gib} GiB per GPU")
+        kw["n_pages"] = dep.n_pages
+        kw["max_ctx"] = max(dep.max_ctx, mc.page_size)
+        B.cap_process(dep.budget_bytes, local)
+        ledger = B.BudgetLedger(dep.budget_bytes)
+    if world > 1:
+        from .parallel.tp_model import TpDenseModel
         if cfg.random is None:
             from .utils import checkpoint as K
-            m = K.load_model(cfg.model_dir, f"cuda:{local}", rank=rank, world=world, **kw)
+            m = K.load_model(cfg.model_dir, dev, rank=rank, world=world, **kw)
         else:
-            m = TpDenseModel.random_init(_named_config(cfg.random), f"cuda:{local}", cfg.seed, rank, world, **kw)
-        return m, rank, world, ctrl
-    from .models.dense import DenseModel
-    dev = f"cuda:{cfg.device}"
-    if cfg.model_dir:
+            m = TpDenseModel.random_init(_named_config(cfg.random), dev, cfg.seed, rank, world, **kw)
+    elif cfg.model_dir:
         from .utils import checkpoint as K
-        return K.load_model(cfg.model_dir, dev, **kw), 0, 1, None
-    if cfg.random:
-        return DenseModel.random_init(_named_config(cfg.random), dev, seed=cfg.seed, **kw), 0, 1, None
-    raise SystemExit("give --model-dir DIR or --random NAME")
+        m = K.load_model(cfg.model_dir, dev, **kw)
+    elif cfg.random:
+        from .models.dense import DenseModel
+        m = DenseModel.random_init(_named_config(cfg.random), dev, seed=cfg.seed, **kw)
+    else:
+        raise SystemExit("give --model-dir DIR or --random NAME")
+    if dep is not None:
+        # book what the load took and hold the deployment to it from here on
+        torch.cuda.synchronize(m.dev)
+        ledger.book("weights, KV pool and buffers (allocator)", torch.cuda.memory_allocated(m.dev))
+        m.budget, m.deployment = ledger, dep
+        tier_on = dep.host_tier and os.environ.get("B200E_KV_TIER", "host") != "off" and world == 1
+        if tier_on:
+            m.enable_host_tier(max(dep.resident_window_tokens, 16 * 256))
+        if rank == 0:
+            for line in ledger.report():
+                print(line, flush=True)
+            print(f"plan: context per conversation {kw['max_ctx']} tokens, host tier {'on' if tier_on else 'off'}", flush=True)
+    return m, rank, world, ctrl
 
 
 def _hash(tokens: List[int]) -> str:
@@ -347,7 +400,7 @@ def cmd_serve(ns):
     model = m
     if world > 1:
         from .parallel import driver as D
-        model = D.TpDriver(m, ctrl)
+        model = D.TpDriver(m, ctrl, children=children)
     m.row_graphs = bool(cfg.row_graphs) and world == 1
     sources = []
     if cfg.spec_copy:
@@ -405,9 +458,12 @@ def cmd_serve(ns):
     eng.start()
     port = srv.start(cfg.host, cfg.port)
     print(f"serving {cfg.served_model_name} on http://{cfg.host}:{port} (tp {world}, max batch {eng.max_batch})", flush=True)
+    rc = 0
     try:
-        while True:
-            time.sleep(3600)
+        while eng.fatal is None:
+            time.sleep(0.5)
+        print(f"serve: {eng.fatal}", flush=True)
+        rc = 3                           # a follower is gone: same exit code as the reference's leader
     except KeyboardInterrupt:
         pass
     finally:
@@ -421,7 +477,7 @@ def cmd_serve(ns):
                 c.wait(timeout=20)
             except Exception:
                 c.terminate()
-    return 0
+    return rc
 
 
 # ---------------------------------------------------------------------------------------------------------------------

@@ -246,7 +246,7 @@ class DenseModel:
 
     def fork(self, src: int, dst: int):
         """``dst`` becomes a copy of ``src`` that shares its full KV pages; only a partial last page is copied
-        (reference: fork_row / COW pages, m1_model.cu:1694-1716 and the beam scheduler of bv_engine.cu)."""
+        (reference: fork_row / COW pages, m1_model.cu:1638-1716)."""
         assert dst not in self.seq_pages and 0 <= dst < self.max_seqs
         self.pool.set_len(self._aid[src], self.seq_len_host[src])
         child, cs, cd = self.pool.fork(self._aid[src])

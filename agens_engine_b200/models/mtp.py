@@ -4,8 +4,8 @@ lm_head and drafts from the target's own hidden state.
 Input of MTP position ``i`` is ``fc([norm_e(E[t_{i+1}]) ; norm_h(h_i)])`` where ``h_i`` is the target's last-layer
 residual stream at position ``i`` and ``t_{i+1}`` the token that follows; the layer's output goes through the shared
 final norm and lm_head and predicts ``t_{i+2}``.  Deeper drafts feed the layer's own output back as ``h``.
-Reference: ``crates/agens-dense/src/lib.rs:4305`` (``mtp_draft``, ``mtp_absorb``) and the MTP weights handled by
-``tools/volundr_mtp_export.py``.
+Reference: ``kernels/m1/m1_mtp.cu`` (head forward :565-687, context entries :11, :768) and the MTP checkpoint reader
+``crates/agens-cli/src/spec.rs:306-370`` (``upload_mtp``, ``mtp.*`` tensor names).
 """
 from __future__ import annotations
 

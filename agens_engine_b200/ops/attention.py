@@ -1,4 +1,4 @@
-"""Launchers of the paged attention kernels (``csrc/kernels/sm100/attn_decode.cu``, ``attn_prefill.cu``)."""
+"""Launchers of the paged attention kernels (``csrc/kernels/sm100/attn_decode.cu``: decode, verify and chunked prefill)."""
 from __future__ import annotations
 
 import ctypes as C

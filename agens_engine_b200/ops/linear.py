@@ -137,7 +137,11 @@ class GemvWorkspace:
 
 
 MM_MIN_ROWS = int(os.environ.get("B200E_MM_MIN_ROWS", "9"))     # token rows from which the tcgen05 GEMM takes over
-TRACE_BUFFER = None      # measurement aid: int64 CUDA tensor [CTAs * 8 warps * 8] that receives the kernel's phase stamps
+# Measurement aids.  Only a library built with B200E_NVCC_DEFS=-DB2_MEASURE reads these fields; the production kernels
+# have the modes compiled out, so a stray environment variable cannot change results.
+TRACE_BUFFER = None      # int64 CUDA tensor [CTAs * 8 warps * 8] that receives the GEMV's phase stamps
+GEMV_DEBUG = int(os.environ.get("B200E_GEMV_DEBUG", "0"))
+MM_DBG = int(os.environ.get("B200E_MM_DBG", "0"))
 
 
 def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STORE,
@@ -191,7 +195,7 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
         raise RuntimeError(f"GEMV workspace too small: need {need} floats, {lin.n_panels()} counters")
     a.scratch, a.counters = ptr(ws.scratch), ptr(ws.counters)
     a.status = ptr(ws.status)
-    a.debug = int(os.environ.get("B200E_GEMV_DEBUG", "0"))
+    a.debug = GEMV_DEBUG
     a.trace = ptr(TRACE_BUFFER)
     if tp is not None:
         a.tp = tp
@@ -240,7 +244,7 @@ def mm(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STOR
         raise RuntimeError("workspace has too few counters")
     a.scratch, a.counters, a.status = ptr(ws.scratch), ptr(ws.counters), ptr(ws.status)
     x16 = ws.x16_buffer(n_pad, lin.k)
-    a.dbg = int(os.environ.get("B200E_MM_DBG", "0"))
+    a.dbg = MM_DBG
     norm = pro == PRO_NORM
     with torch.cuda.device(dev):
         check(lib.b2_wq_mm(C.byref(a), ptr(x), x.stride(0), ptr(ss_in) if norm else 0, ss_parts if norm else 0, SS_LD,

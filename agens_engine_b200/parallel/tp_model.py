@@ -6,7 +6,8 @@ replicated.  On the decode path the two row-parallel linears of a layer run as O
 pushes its partial into every rank's inbox over NVLink, sums all ranks in rank order, adds the residual and leaves the
 next norm's statistics (``EPI_TP_RESID`` in ``wq_gemv.cu``) -- no NCCL call and no separate all-reduce launch.  The
 lm_head produces per-rank (value, index) winners that are exchanged and merged by ``b2_comm_argmax_combine``.
-Prefill chunks use NCCL all-reduce on the row-parallel outputs (the baseline path) for now.
+Prefill chunks reduce their row-parallel outputs with the two-shot push kernels (reduce-scatter + all-gather over the
+same symmetric memory); NCCL is used by the ``use_nccl_decode`` baseline only.
 """
 from __future__ import annotations
 
@@ -51,6 +52,7 @@ class TpDenseModel(DenseModel):
         self._gather_inbox = SymmetricInbox(rank, world, 8 * self.lm_rows, 3, self.dev,
                                             status=self._status_all[3:4])                       # logits / winners exchange
         self._gather = PushComm(self._gather_inbox)
+        self._prefill_inbox = self._prefill_comm = None      # opened by the first prefill chunk (collective)
 
     # ------------------------------------------------------------------------------------------------ weights
     @staticmethod
@@ -146,9 +148,34 @@ class TpDenseModel(DenseModel):
         return lin.n_panels()
 
     def _reduce_rows(self, x: torch.Tensor) -> torch.Tensor:
-        y = x.float()
-        dist.all_reduce(y)
-        return y.to(torch.bfloat16)
+        """Sum of a row-parallel partial [rows, n] over the ranks for prefill-size chunks, with the engine's own bounded
+        push kernels and no library collective: two-shot (reduce-scatter, then all-gather) so that every rank moves
+        2 (N - 1) / N of the chunk over NVLink instead of (N - 1) times the chunk.  Sums are taken in rank order, so
+        every rank holds the same bits.  ``use_nccl_decode`` keeps the library all-reduce as the baseline."""
+        if self.use_nccl_decode:
+            y = x.float()
+            dist.all_reduce(y)
+            return y.to(torch.bfloat16)
+        w = self.world
+        if self._prefill_comm is None:
+            from .comm import PushComm
+            self._prefill_inbox = SymmetricInbox(self.rank, w, 1 << 20, 3, self.dev, status=self._status_all[3:4])
+            self._prefill_comm = PushComm(self._prefill_inbox)
+        pc, per = self._prefill_comm, self._prefill_inbox.slot_stride
+        flat = x.float().reshape(-1)
+        n = flat.numel()
+        out = torch.empty_like(flat)
+        step = w * per
+        for o in range(0, n, step):
+            m = min(step, n - o)
+            shard = (m + w - 1) // w
+            shard = (shard + 3) // 4 * 4
+            buf = torch.zeros(w * shard, dtype=torch.float32, device=self.dev)
+            buf[:m] = flat[o:o + m]
+            mine = pc.reduce_scatter(buf.view(w, shard))
+            full = pc.all_gather(mine)
+            out[o:o + m] = full.reshape(-1)[:m]
+        return out.view_as(x).to(torch.bfloat16)
 
     def _lm_valid(self) -> int:
         valid = self.full_cfg.vocab_valid or self.full_cfg.vocab
@@ -206,8 +233,10 @@ class TpDenseModel(DenseModel):
         forwards the call), with a host-side barrier before anyone launches again."""
         super().recover()
         self.inbox.rearm_all()
-        if self._gather_inbox is not None:
-            self._gather_inbox.rearm_all()
+        for ib, pc in ((self._gather_inbox, self._gather), (self._prefill_inbox, self._prefill_comm)):
+            if ib is not None:
+                ib.rearm_all()
+                pc.calls, pc.prev_n = 0, 0
         torch.cuda.synchronize(self.dev)
 
     def close(self):
@@ -219,6 +248,9 @@ class TpDenseModel(DenseModel):
         if self._gather_inbox is not None:
             self._gather_inbox.close()
             self._gather = self._gather_inbox = None
+        if self._prefill_inbox is not None:
+            self._prefill_inbox.close()
+            self._prefill_inbox = self._prefill_comm = None
         self.inbox.close()
 
     def weight_bytes(self) -> int:

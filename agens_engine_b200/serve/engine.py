@@ -2,7 +2,7 @@
 (or speculative verify) steps, samples on the device, applies reasoning budget / think guard, and streams tokens to
 whoever submitted the request.
 
-Plays the role of the reference's continuous loop (``crates/agens-cli/src/serve.rs:860-2770``): admission by the
+Plays the role of the reference's continuous loop (``crates/agens-cli/src/serve.rs:1028-1700`` ``run_loop``): admission by the
 banker's check (``kv_safe``), shortest-remaining-prefill first with a fairness turn (``pick_prefill``), eviction of the
 cheapest victim when the pool runs dry (``pick_victim``; the victim is re-queued and recomputed), one rule for sampling
 so that speculation does not change tokens.  The loop itself is a thread of this process; the model calls go to the
@@ -107,6 +107,7 @@ class Engine:
         self.free_slots = list(range(model.max_seqs - 1, -1, -1))
         self.stats = EngineStats()
         self._stop = threading.Event()
+        self.fatal: Optional[BaseException] = None      # set when the loop had to stop for good
         self._thread: Optional[threading.Thread] = None
         self._rid = 0
         self._lock = threading.Lock()
@@ -152,6 +153,12 @@ class Engine:
                     except queue.Empty:
                         pass
             except Exception as e:      # a failed step must not take the engine thread (and every open request) with it
+                if getattr(e, "fatal", False):          # e.g. a tensor-parallel follower is gone: nothing to recover to
+                    self.fatal = e
+                    for r in list(self.active.values()) + list(self.waiting):
+                        self.emit(r.rid, [], True, f"engine stopped: {e}")
+                    self.active.clear(); self.waiting.clear()
+                    return
                 self._fail_all(f"engine step failed: {type(e).__name__}: {e}")
 
     def _intake(self, r: Request):

@@ -7,7 +7,7 @@ row ``j``.  The emitted tokens are therefore exactly what plain decoding would h
 (the sampler's draw depends only on seed, position and logits).  Rejected rows are rolled back by truncating the
 sequence; their KV entries are overwritten by the next block.
 
-Draft sources, in the reference's cascade order (``crates/agens-dense/src/lib.rs:4191-4349``): copy-lookup over the
+Draft sources, in the reference's cascade order (``crates/agens-cli/src/spec.rs:44-130``, ``lookup.rs``): copy-lookup over the
 sequence's own tokens, the MTP head, the companion drafter model.  Acceptance: ``kernels/m1/m1_model.cu:476-579``.
 """
 from __future__ import annotations

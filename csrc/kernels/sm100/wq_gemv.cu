@@ -68,7 +68,11 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
   const unsigned U = (unsigned)nitems * (unsigned)nb;          // host checks U * V < 2^32
   auto range_lo = [&](int v) -> unsigned { return ((unsigned)v * U) / (unsigned)V; };
 
+#ifdef B2_MEASURE   // measurement builds only (B200E_NVCC_DEFS=-DB2_MEASURE): phase stamps and the bandwidth-probe mode
   unsigned long long* tr = a.trace ? a.trace + ((size_t)blockIdx.x * kGemvWarps + warp) * 8 : nullptr;
+#else
+  unsigned long long* tr = nullptr;
+#endif
   auto stamp = [&](int i) { if (tr && lane == 0) tr[i] = globaltimer_ns(); };
   stamp(0);
   if (lane == 0) {
@@ -212,6 +216,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
       }
       if (first_wait) { stamp(4); first_wait = false; }
       const uint8_t* stg = ring + slot * R::STAGE;
+#ifdef B2_MEASURE
       if (a.debug == 1) {   // measurement aid: stream the weights, skip the arithmetic
         y[0][0][0] += (float)stg[lane];
         __syncwarp();
@@ -221,6 +226,7 @@ __global__ void __launch_bounds__(kGemvThreads) wq_gemv_kernel(const WqGemvArgs 
         }
         continue;
       }
+#endif
       WFrag<BITS, GROUP> cf[RB];
 #pragma unroll
       for (int r = 0; r < RB; ++r)

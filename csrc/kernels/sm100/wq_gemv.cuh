@@ -54,9 +54,9 @@ struct WqGemvArgs {
   float* amax_val; int* amax_idx; int n_valid;   // EPI_ARGMAX: rows >= n_valid never win
   float* scratch; unsigned* counters;   // split-k partials [item][ks][m][16*rb] and self-resetting panel counters
   int* status;           // device status word (B2_ERR_TIMEOUT when a bounded wait ran out)
-  int debug;             // 0 normal; 1 = stream weights without arithmetic (bandwidth probe, results meaningless)
+  int debug;             // read by -DB2_MEASURE builds only: 1 = stream weights without arithmetic (bandwidth probe)
   TpPush tp;
-  unsigned long long* trace;   // measurement aid: [CTA][warp][8] globaltimer stamps of the kernel's phases (null: off)
+  unsigned long long* trace;   // read by -DB2_MEASURE builds only: [CTA][warp][8] globaltimer stamps of the kernel's phases
 };
 
 }  // namespace b2

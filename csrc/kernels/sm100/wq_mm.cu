@@ -18,6 +18,14 @@
 
 #include "common.cuh"
 
+// The `dbg` bits of the argument block switch parts of the kernel off for measurements (results are then meaningless);
+// production builds compile them out: only -DB2_MEASURE builds read the field.
+#ifdef B2_MEASURE
+#define B2_DBG(a, bit) ((a).dbg & (bit))
+#else
+#define B2_DBG(a, bit) 0
+#endif
+
 namespace b2 {
 
 struct WqMmArgs {
@@ -184,7 +192,7 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
         const int s = kb % S;
         if (kb >= S && !mbar_wait_m(smem_u32(&empty_bar[s]), ((kb / S) - 1) & 1)) { atomicExch(&s_failed, 1); break; }
         const uint32_t bar = smem_u32(&full_bar[s]);
-        if (a.dbg & 16) { mbar_arrive_m(bar); continue; }
+        if (B2_DBG(a, 16)) { mbar_arrive_m(bar); continue; }
         mbar_expect_tx_m(bar, (uint32_t)b_stage);
         tma_load_2d_m(ring + s * stage_bytes + A_STAGE, &map_x, (kb0 + kb) * 128, 0, bar);
         tma_load_2d_m(ring + s * stage_bytes + A_STAGE + b_sub, &map_x, (kb0 + kb) * 128 + BKS, 0, bar);
@@ -205,7 +213,7 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
 #pragma unroll
           for (int k = 0; k < BKS / 16; ++k) {
             const int q = kh * 4 + k, acc = q % nacc;
-            if (!(a.dbg & 8)) umma_f16(tmem_base + (uint32_t)(acc * a.n_pad), da + 2 * k, db + 2 * k, idesc, (kb || q >= nacc) ? 1u : 0u);
+            if (!B2_DBG(a, 8)) umma_f16(tmem_base + (uint32_t)(acc * a.n_pad), da + 2 * k, db + 2 * k, idesc, (kb || q >= nacc) ? 1u : 0u);
           }
         }
         umma_commit_m(smem_u32(&empty_bar[s]));
@@ -226,7 +234,7 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
       RawW r;
       const uint8_t* blk = pbase + (size_t)(kb0 + kb) * BLK;
       r.lo1 = make_uint4(0u, 0u, 0u, 0u); r.hi = make_uint2(0u, 0u); r.sz[2] = r.sz[3] = 0u;
-      if (a.dbg & 1) { r.lo0 = r.lo1 = make_uint4(kb, kb, kb, kb); r.sz[0] = r.sz[1] = r.sz[2] = r.sz[3] = 0x3C003C00u; return r; }
+      if (B2_DBG(a, 1)) { r.lo0 = r.lo1 = make_uint4(kb, kb, kb, kb); r.sz[0] = r.sz[1] = r.sz[2] = r.sz[3] = 0x3C003C00u; return r; }
       r.lo0 = ld_nc_v4(blk + rbk * W_BATCH + lane * 16);
       if (BITS == 4) r.lo1 = ld_nc_v4(blk + rbk * W_BATCH + 512 + lane * 16);
       if (BITS == 3) r.hi = ld_nc_v2(blk + rbk * W_BATCH + 512 + lane * 8);
@@ -309,13 +317,13 @@ __global__ void __launch_bounds__(kMmThreads, 1) wq_mm_kernel(const __grid_const
         r1 = hfma2_u(hfma2_u(r1, m0h, a0h), sc1, bi1);
         r3 = hfma2_u(hfma2_u(r3, m1h, a1h), sc1, bi1);
         const uint32_t off = joff[j];
-        if (!(a.dbg & 4)) {
+        if (!B2_DBG(a, 4)) {
           asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(sa + off), "r"(r0), "r"(r2) : "memory");
           asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(sa + 1024u + off), "r"(r1), "r"(r3) : "memory");
         }
       }
       }
-      if (!(a.dbg & 2)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
+      if (!B2_DBG(a, 2)) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy writes -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive_m(smem_u32(&full_bar[s]));
       }

@@ -5,7 +5,8 @@
 // reserve; what is left becomes the paged KV pool; if the pool cannot hold the wanted context, KV pages are tiered to
 // pinned host memory (capped by the pinnable host RAM) and the context is clamped rather than the load failing; ranks
 // take the minimum.  Differences: pages of 16 tokens instead of rows, every layer is dense attention, and the cap is
-// enforced by an arena that refuses past the budget (the GPUs are shared, so no ballast allocation).
+// enforced on the host by the loader's budget ledger (serve/budget.py: every device allocation of a deployment is
+// booked against the budget and refused past it) instead of a ballast allocation: the GPUs are shared.
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
