@@ -142,33 +142,44 @@ def _rows(ql: quant.QuantLinear, lo: int, hi: int) -> quant.QuantLinear:
     return quant.QuantLinear(hi - lo, ql.k, ql.bits, ql.group, ql.codes[lo:hi], ql.scale[lo:hi], ql.zero[lo:hi])
 
 
-def save_oracle(dir_: str, ow, shards: int = 1, symmetric: bool = False, sums: bool = True):
-    """Writes oracle weights (``models/oracle.py``) as a checkpoint directory with separate q/k/v and gate/up tensors."""
+def save_oracle(dir_: str, ow, shards: int = 1, symmetric: bool = False, sums: bool = True, root: str = "model.",
+                bf16_linears: tuple = (), tied: bool = False, extra: Optional[Dict[str, torch.Tensor]] = None):
+    """Writes oracle weights (``models/oracle.py``) as a checkpoint directory with separate q/k/v and gate/up tensors.
+    ``root``: name prefix of the text model (``model.`` or ``model.language_model.``); ``bf16_linears``: suffixes such
+    as ``"self_attn.o_proj"`` written as dequantised bf16 ``weight`` tensors; ``tied``: no lm_head tensor and
+    ``tie_word_embeddings`` set; ``extra``: further tensors stored as they are."""
     cfg = ow.cfg
     os.makedirs(dir_, exist_ok=True)
     hf = {"architectures": ["DenseGQAForCausalLM"], "num_hidden_layers": cfg.n_layers, "hidden_size": cfg.d_model,
           "num_attention_heads": cfg.n_heads, "num_key_value_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
           "intermediate_size": cfg.ffn, "vocab_size": cfg.vocab, "rope_theta": cfg.rope_theta, "rms_norm_eps": cfg.rms_eps,
-          "tie_word_embeddings": False, "torch_dtype": "bfloat16",
+          "tie_word_embeddings": bool(tied), "torch_dtype": "bfloat16",
           "quantization_config": {"format": "pack-quantized", "group_size": cfg.group, "symmetric": symmetric}}
     json.dump(hf, open(os.path.join(dir_, "config.json"), "w"), indent=1)
-    t: Dict[str, torch.Tensor] = {"model.embed_tokens.weight": ow.embed, "model.norm.weight": ow.final_norm}
+    t: Dict[str, torch.Tensor] = {root + "embed_tokens.weight": ow.embed, root + "norm.weight": ow.final_norm}
+    def put(out, name, ql, symmetric):
+        if any(name.endswith(sfx) for sfx in bf16_linears):
+            out[name + ".weight"] = ql.dequant().to(torch.bfloat16)
+        else:
+            _put_linear(out, name, ql, symmetric)
     for l, lay in enumerate(ow.layers):
-        p = f"model.layers.{l}."
+        p = f"{root}layers.{l}."
         t[p + "input_layernorm.weight"], t[p + "post_attention_layernorm.weight"] = lay["ln1"], lay["ln2"]
         qkv = ow.quant[f"{l}.qkv"]
-        _put_linear(t, p + "self_attn.q_proj", _rows(qkv, 0, cfg.q_dim), symmetric)
-        _put_linear(t, p + "self_attn.k_proj", _rows(qkv, cfg.q_dim, cfg.q_dim + cfg.kv_dim), symmetric)
-        _put_linear(t, p + "self_attn.v_proj", _rows(qkv, cfg.q_dim + cfg.kv_dim, cfg.q_dim + 2 * cfg.kv_dim), symmetric)
-        _put_linear(t, p + "self_attn.o_proj", ow.quant[f"{l}.o"], symmetric)
+        put(t, p + "self_attn.q_proj", _rows(qkv, 0, cfg.q_dim), symmetric)
+        put(t, p + "self_attn.k_proj", _rows(qkv, cfg.q_dim, cfg.q_dim + cfg.kv_dim), symmetric)
+        put(t, p + "self_attn.v_proj", _rows(qkv, cfg.q_dim + cfg.kv_dim, cfg.q_dim + 2 * cfg.kv_dim), symmetric)
+        put(t, p + "self_attn.o_proj", ow.quant[f"{l}.o"], symmetric)
         gu = ow.quant[f"{l}.gate_up"]
         gi = torch.arange(cfg.ffn * 2).reshape(cfg.ffn // 8, 2, 8)
         g_rows, u_rows = gi[:, 0].reshape(-1), gi[:, 1].reshape(-1)
         sel = lambda idx: quant.QuantLinear(len(idx), gu.k, gu.bits, gu.group, gu.codes[idx], gu.scale[idx], gu.zero[idx])
-        _put_linear(t, p + "mlp.gate_proj", sel(g_rows), symmetric)
-        _put_linear(t, p + "mlp.up_proj", sel(u_rows), symmetric)
-        _put_linear(t, p + "mlp.down_proj", ow.quant[f"{l}.down"], symmetric)
-    _put_linear(t, "lm_head", ow.quant["lm_head"], symmetric)
+        put(t, p + "mlp.gate_proj", sel(g_rows), symmetric)
+        put(t, p + "mlp.up_proj", sel(u_rows), symmetric)
+        put(t, p + "mlp.down_proj", ow.quant[f"{l}.down"], symmetric)
+    if not tied:
+        put(t, "lm_head", ow.quant["lm_head"], symmetric)
+    t.update(extra or {})
     names = list(t)
     if shards <= 1:
         write_safetensors(os.path.join(dir_, "model.safetensors"), t, {"format": "pt"})
@@ -191,12 +202,16 @@ def save_oracle(dir_: str, ow, shards: int = 1, symmetric: bool = False, sums: b
                 f.write(f"{hashlib.sha256(open(os.path.join(dir_, fn), 'rb').read()).hexdigest()}  {fn}\n")
 
 
+BF16_LOAD_BITS = 4     # bf16 linears (and a tied lm_head) are quantised at load: asymmetric, group 128, this many bits
+
+
 def _get_linear(files, wm, name: str, n: int, k: int, fmt: dict) -> quant.QuantLinear:
     def T(suffix):
         full = name + suffix
         return files[wm[full]].tensor(full)
     if fmt["format"] == "bf16":
-        raise NotImplementedError("bf16 linears are quantised at load by the caller")
+        # the kernels of this engine take quantised linears only: a bf16 linear is quantised here, once, at load
+        return quant.quantize(T(".weight").float(), BF16_LOAD_BITS, 128)
     bits, group = fmt["bits"], fmt["group"]
     codes = quant.unpack_stream(T(".weight_packed"), bits, k)
     # copies: the mapped file may be closed before the weights are packed for the device
@@ -214,11 +229,11 @@ class CheckpointWeights:
     layers: list
     final_norm: torch.Tensor
     quant: dict
+    unexpected: list = dataclasses.field(default_factory=list)     # text-model tensors the loader had no use for
 
 
-def read_weights(dir_: str) -> CheckpointWeights:
-    """Validates the directory and reads every tensor (reference: m1::load weight loop with gate+up merge,
-    crates/agens-cli/src/m1.rs:452-1066)."""
+def _open(dir_: str):
+    """Validates the directory; returns (report, config, weight map, open shard files)."""
     from ..models.config import ModelConfig
     rep = validate(dir_)
     if not rep["ok"]:
@@ -231,20 +246,30 @@ def read_weights(dir_: str) -> CheckpointWeights:
         f0 = SafeTensorsFile(os.path.join(dir_, "model.safetensors"))
         wm = {k: "model.safetensors" for k in f0.keys()}
     files = {fn: SafeTensorsFile(os.path.join(dir_, fn)) for fn in set(wm.values())}
-    fm = rep["linears"]
-    cfg.group = next(iter(fm.values())).get("group", 128)
+    groups = [f.get("group", 128) for f in rep["linears"].values()]
+    cfg.group = max(set(groups), key=groups.count) if groups else 128      # linears carry their own group size
+    hf = json.load(open(os.path.join(dir_, "config.json")))
+    return rep, cfg, wm, files, bool(hf.get("tie_word_embeddings", False))
+
+
+def read_weights(dir_: str) -> CheckpointWeights:
+    """Validates the directory and reads every tensor to the CPU in expanded form (reference: m1::load weight loop with
+    gate+up merge, crates/agens-cli/src/m1.rs:452-1066).  Meant for tests and small models: :func:`load_model` streams
+    the packed tensors to the device instead."""
+    rep, cfg, wm, files, tied = _open(dir_)
+    fm, root = rep["linears"], rep.get("root", "model.")
     cat = lambda qs: quant.QuantLinear(sum(q.n for q in qs), qs[0].k, qs[0].bits, qs[0].group, torch.cat([q.codes for q in qs]),
                                        torch.cat([q.scale for q in qs]), torch.cat([q.zero for q in qs]))
     layers, qd = [], {}
     for l in range(cfg.n_layers):
-        p = f"model.layers.{l}."
+        p = f"{root}layers.{l}."
         g = lambda nm, n, k: _get_linear(files, wm, p + nm, n, k, fm[p + nm])
         q, kk, v = g("self_attn.q_proj", cfg.q_dim, cfg.d_model), g("self_attn.k_proj", cfg.kv_dim, cfg.d_model), g("self_attn.v_proj", cfg.kv_dim, cfg.d_model)
-        if not (q.bits == kk.bits == v.bits):
-            raise ValueError(f"layer {l}: q/k/v use different bit widths; they share one fused kernel launch")
+        if not (q.bits == kk.bits == v.bits and q.group == kk.group == v.group):
+            raise ValueError(f"layer {l}: q/k/v use different bit widths or group sizes; they share one fused kernel launch")
         gate, up = g("mlp.gate_proj", cfg.ffn, cfg.d_model), g("mlp.up_proj", cfg.ffn, cfg.d_model)
-        if gate.bits != up.bits:
-            raise ValueError(f"layer {l}: gate/up use different bit widths")
+        if gate.bits != up.bits or gate.group != up.group:
+            raise ValueError(f"layer {l}: gate/up use different bit widths or group sizes")
         qd[f"{l}.qkv"] = cat([q, kk, v])
         qd[f"{l}.o"] = g("self_attn.o_proj", cfg.d_model, cfg.q_dim)
         qd[f"{l}.gate_up"] = quant.QuantLinear(2 * cfg.ffn, cfg.d_model, gate.bits, gate.group,
@@ -256,20 +281,131 @@ def read_weights(dir_: str) -> CheckpointWeights:
         layers.append({"ln1": T("input_layernorm.weight"), "ln2": T("post_attention_layernorm.weight")})
         for lin in ("qkv", "o", "gate_up", "down"):
             cfg.bits[f"{l}.{lin}"] = qd[f"{l}.{lin}"].bits
-    embed = files[wm["model.embed_tokens.weight"]].tensor("model.embed_tokens.weight").clone()
-    final_norm = files[wm["model.norm.weight"]].tensor("model.norm.weight").clone()
-    qd["lm_head"] = _get_linear(files, wm, "lm_head", cfg.vocab, cfg.d_model, fm["lm_head"])
+    embed = files[wm[root + "embed_tokens.weight"]].tensor(root + "embed_tokens.weight").clone()
+    final_norm = files[wm[root + "norm.weight"]].tensor(root + "norm.weight").clone()
+    if tied:
+        qd["lm_head"] = quant.quantize(embed.float(), BF16_LOAD_BITS, 128)       # tied head: the embedding, quantised once
+    else:
+        qd["lm_head"] = _get_linear(files, wm, "lm_head", cfg.vocab, cfg.d_model, fm["lm_head"])
     cfg.lm_head_bits = qd["lm_head"].bits
     for f in files.values():
         f.close()
-    return CheckpointWeights(cfg, embed, layers, final_norm, qd)
+    return CheckpointWeights(cfg, embed, layers, final_norm, qd, list(rep.get("unexpected", [])))
+
+
+# ---- streaming load: packed tensors go to the device as they are and are repacked there ------------------------------
+
+def _device_linear(parts, device, rows=None, kcut=None, interleave=False):
+    """One engine linear from checkpoint linears that share k, bits and group.  ``parts``: list of (packed int32 [n, w],
+    scale [n, g], zero or None, n, k, bits, group) views into the mapped files.  ``rows``: per-part row ranges (a
+    column-parallel shard), ``kcut``: (k0, k1) input range (a row-parallel shard; word- and group-aligned).  The bit
+    streams are only sliced and concatenated; the device kernel ``b2_wq_repack`` turns them into the kernel layout, so no
+    code is ever expanded on the host (reference: crates/agens-cuda/src/lib.rs:163-214, kernels/src/w4_gemv.cu:441)."""
+    from ..ops import linear as L
+    _, _, _, _, k, bits, group = parts[0]
+    packs, scales, zeros = [], [], []
+    for i, (pk, sc, zp, n, _k, _b, _g) in enumerate(parts):
+        lo, hi = rows[i] if rows is not None else (0, n)
+        pk, sc = pk[lo:hi], sc[lo:hi]
+        zp = None if zp is None else zp[lo:hi]
+        if kcut is not None:
+            k0, k1 = kcut
+            assert (k0 * bits) % 32 == 0 and (k1 * bits) % 32 == 0 and k0 % group == 0 and k1 % group == 0
+            pk = pk[:, k0 * bits // 32:k1 * bits // 32]
+            sc = sc[:, k0 // group:k1 // group]
+            zp = None if zp is None else zp[:, k0 // group:k1 // group]
+        packs.append(pk.to(device)); scales.append(sc.to(device)); zeros.append(None if zp is None else zp.to(device))
+    if any(z is None for z in zeros) and not all(z is None for z in zeros):
+        zeros = [z if z is not None else torch.full_like(s_, float(1 << (bits - 1)), dtype=torch.float16) for z, s_ in zip(zeros, scales)]
+    pk = torch.cat(packs) if len(packs) > 1 else packs[0]
+    sc = torch.cat(scales) if len(scales) > 1 else scales[0]
+    zp = None if zeros[0] is None else (torch.cat(zeros) if len(zeros) > 1 else zeros[0])
+    if interleave:                      # gate rows and up rows in blocks of eight (see quant.interleave_gate_up)
+        f = pk.shape[0] // 2
+        idx = torch.arange(2 * f, device=device).reshape(2, f // 8, 8).permute(1, 0, 2).reshape(-1)
+        pk, sc = pk[idx], sc[idx]
+        zp = None if zp is None else zp[idx]
+    kk = k if kcut is None else kcut[1] - kcut[0]
+    return L.WqLinear.from_checkpoint(pk.contiguous(), sc.contiguous(), None if zp is None else zp.contiguous(),
+                                      pk.shape[0], kk, bits, group, device)
 
 
 def load_model(dir_: str, device="cuda:0", rank: int = 0, world: int = 1, **kw):
-    """Builds a :class:`DenseModel` (or this rank's :class:`TpDenseModel` shard) from a checkpoint directory."""
-    w = read_weights(dir_)
+    """Builds a :class:`DenseModel` (or this rank's :class:`TpDenseModel` shard) from a checkpoint directory.
+
+    Quantised linears stream from the memory-mapped shards to the device in their packed form and are repacked there;
+    peak host memory is the page cache of one tensor.  bf16 linears and a tied lm_head are quantised at load
+    (asymmetric 4 bits, group 128) because the decode kernels take quantised weights only."""
+    from ..models.config import LINEARS
+    from ..models.dense import DenseModel
+    from ..ops import linear as L
+    rep, cfg, wm, files, tied = _open(dir_)
+    fm, root = rep["linears"], rep.get("root", "model.")
+    dev = torch.device(device)
     if world > 1:
         from ..parallel.tp_model import TpDenseModel
-        return TpDenseModel.from_oracle(w, device, rank, world, **kw)
-    from ..models.dense import DenseModel
-    return DenseModel.from_oracle(w, device, **kw)
+        m = TpDenseModel(cfg, dev, rank, world, **kw)
+        lc = m.cfg
+    else:
+        m = DenseModel(cfg, dev, **kw)
+        lc = cfg
+    hd = cfg.head_dim
+    hq, hkv, f = lc.n_heads, lc.n_kv_heads, lc.ffn
+
+    def part(name, n, k):
+        fmt = fm[name]
+        if fmt["format"] == "bf16":
+            ql = quant.quantize(files[wm[name + ".weight"]].tensor(name + ".weight").float(), BF16_LOAD_BITS, 128)
+            return (quant.pack_stream(ql.codes, ql.bits), ql.scale, ql.zero, n, k, ql.bits, ql.group)
+        T = lambda suf: files[wm[name + suf]].tensor(name + suf)
+        zp = T(".weight_zero_point") if fmt["asymmetric"] else None
+        return (T(".weight_packed"), T(".weight_scale"), zp, n, k, fmt["bits"], fmt["group"])
+
+    for l in range(cfg.n_layers):
+        p = f"{root}layers.{l}."
+        q, kk, v = part(p + "self_attn.q_proj", cfg.q_dim, cfg.d_model), part(p + "self_attn.k_proj", cfg.kv_dim, cfg.d_model), \
+            part(p + "self_attn.v_proj", cfg.kv_dim, cfg.d_model)
+        if not (q[5] == kk[5] == v[5] and q[6] == kk[6] == v[6]):
+            raise ValueError(f"layer {l}: q/k/v use different bit widths or group sizes; they share one fused kernel launch")
+        gate, up = part(p + "mlp.gate_proj", cfg.ffn, cfg.d_model), part(p + "mlp.up_proj", cfg.ffn, cfg.d_model)
+        if gate[5] != up[5] or gate[6] != up[6]:
+            raise ValueError(f"layer {l}: gate/up use different bit widths or group sizes")
+        d = {
+            "qkv": _device_linear([q, kk, v], dev, rows=[(rank * hq * hd, (rank + 1) * hq * hd), (rank * hkv * hd, (rank + 1) * hkv * hd),
+                                                        (rank * hkv * hd, (rank + 1) * hkv * hd)]),
+            "o": _device_linear([part(p + "self_attn.o_proj", cfg.d_model, cfg.q_dim)], dev, kcut=(rank * hq * hd, (rank + 1) * hq * hd)),
+            "gate_up": _device_linear([gate, up], dev, rows=[(rank * f, (rank + 1) * f)] * 2, interleave=True),
+            "down": _device_linear([part(p + "mlp.down_proj", cfg.d_model, cfg.ffn)], dev, kcut=(rank * f, (rank + 1) * f)),
+        }
+        T = lambda nm: files[wm[p + nm]].tensor(p + nm).to(dev)
+        d["ln1"], d["ln2"] = T("input_layernorm.weight"), T("post_attention_layernorm.weight")
+        m.layers.append(d)
+        for lin in LINEARS:
+            cfg.bits[f"{l}.{lin}"] = d[lin].bits
+    embed_cpu = files[wm[root + "embed_tokens.weight"]].tensor(root + "embed_tokens.weight")
+    m.embed = embed_cpu.to(dev)
+    m.final_norm = files[wm[root + "norm.weight"]].tensor(root + "norm.weight").to(dev)
+    # lm_head: vocabulary shard of this rank, padded with zero rows to whole panels
+    if tied:
+        ql = quant.quantize(embed_cpu.float(), BF16_LOAD_BITS, 128)
+        lm = (quant.pack_stream(ql.codes, ql.bits), ql.scale, ql.zero, cfg.vocab, cfg.d_model, ql.bits, ql.group)
+    else:
+        lm = part("lm_head", cfg.vocab, cfg.d_model)
+    if world > 1:
+        lo, hi = rank * m.vocab_shard, min(cfg.vocab, (rank + 1) * m.vocab_shard)
+    else:
+        lo, hi = 0, cfg.vocab
+    head = _device_linear([lm], dev, rows=[(lo, hi)])
+    pad = m.lm_rows - (hi - lo)
+    if pad:
+        zq = quant.QuantLinear(pad, cfg.d_model, head.bits, head.group, torch.zeros(pad, cfg.d_model, dtype=torch.uint8),
+                               torch.zeros(pad, cfg.d_model // head.group, dtype=torch.float16),
+                               torch.zeros(pad, cfg.d_model // head.group, dtype=torch.float16))
+        padl = L.WqLinear.from_quant(zq, dev)
+        head = L.WqLinear(m.lm_rows, cfg.d_model, head.bits, head.group, torch.cat([head.wq, padl.wq]), head.ks, L.choose_rb(m.lm_rows))
+    m.lm_head = head
+    cfg.lm_head_bits = head.bits
+    m.unexpected_tensors = list(rep.get("unexpected", []))
+    for fl in files.values():
+        fl.close()
+    return m.finalize()

@@ -17,6 +17,7 @@
 #include <cstring>
 #include <fstream>
 #include <map>
+#include <set>
 #include <sstream>
 #include <string>
 #include <thread>
@@ -283,25 +284,51 @@ static Json validate_dir(const std::string& dir) {
     if (it->second.dtype != dtype || it->second.shape != shape) fail(name + ": expected " + dtype + " of the manifest shape");
   };
   Json linears = Json::object();
+  Json unexpected = Json::array();
+  std::string root = "model.";
+  // Text-model tensors live under `model.` (plain decoders) or `model.language_model.` (checkpoints that also carry a
+  // vision tower; the reference's manifest uses that prefix: crates/agens-core/src/weights.rs:35-107).
+  if (tensors.count("model.language_model.embed_tokens.weight")) root = "model.language_model.";
+  std::set<std::string> used;
+  auto expect_at = [&](const std::string& name, const std::string& dtype, std::vector<long long> shape) {
+    used.insert(name);
+    expect(name, dtype, shape);
+  };
+  auto linear_at = [&](const std::string& name, long long n, long long k) {
+    std::string err;
+    Json fmt = linear_format(tensors, name, n, k, err);
+    if (!err.empty()) { fail(err); return; }
+    linears.set(name, fmt);
+    for (const char* suf : {".weight", ".weight_packed", ".weight_scale", ".weight_zero_point"})
+      if (tensors.count(name + suf)) used.insert(name + suf);
+  };
   if (errors.size() == 0) {
-    expect("model.embed_tokens.weight", "BF16", {vocab, d});
-    expect("model.norm.weight", "BF16", {d});
+    expect_at(root + "embed_tokens.weight", "BF16", {vocab, d});
+    expect_at(root + "norm.weight", "BF16", {d});
     const std::pair<const char*, std::pair<long long, long long>> lin[] = {
         {"self_attn.q_proj", {hq * hd, d}}, {"self_attn.k_proj", {hkv * hd, d}}, {"self_attn.v_proj", {hkv * hd, d}},
         {"self_attn.o_proj", {d, hq * hd}}, {"mlp.gate_proj", {ffn, d}}, {"mlp.up_proj", {ffn, d}}, {"mlp.down_proj", {d, ffn}}};
     for (long long l = 0; l < L; ++l) {
-      const std::string p = "model.layers." + std::to_string(l) + ".";
-      expect(p + "input_layernorm.weight", "BF16", {d});
-      expect(p + "post_attention_layernorm.weight", "BF16", {d});
-      for (auto& e : lin) {
-        std::string err;
-        Json fmt = linear_format(tensors, p + e.first, e.second.first, e.second.second, err);
-        if (!err.empty()) fail(err); else linears.set(p + e.first, fmt);
+      const std::string p = root + "layers." + std::to_string(l) + ".";
+      expect_at(p + "input_layernorm.weight", "BF16", {d});
+      expect_at(p + "post_attention_layernorm.weight", "BF16", {d});
+      // a q_proj with twice the rows carries an output gate (the reference's hybrid attention layers): the dense
+      // family has no such gate, so say what it is instead of "bad shape"
+      auto qp = tensors.find(p + "self_attn.q_proj.weight_packed");
+      if (qp == tensors.end()) qp = tensors.find(p + "self_attn.q_proj.weight");
+      if (qp != tensors.end() && qp->second.shape.size() == 2 && qp->second.shape[0] == 2 * hq * hd) {
+        fail(p + "self_attn.q_proj has 2 x n_heads x head_dim rows (gated attention output): not a dense GQA layer");
+        continue;
       }
+      for (auto& e : lin) linear_at(p + e.first, e.second.first, e.second.second);
     }
-    std::string err;
     const bool tied = cfg.get_bool("tie_word_embeddings", false);
-    if (!tied) { Json fmt = linear_format(tensors, "lm_head", vocab, d, err); if (!err.empty()) fail(err); else linears.set("lm_head", fmt); }
+    if (!tied) linear_at("lm_head", vocab, d);
+    for (auto& kv : tensors) {
+      if (used.count(kv.first)) continue;
+      const bool text = kv.first.rfind(root, 0) == 0 || kv.first.rfind("lm_head", 0) == 0;
+      if (text) unexpected.push_back(kv.first);       // reported, not fatal (reference: weights.rs leftover report)
+    }
   }
   rep.set("ok", errors.size() == 0);
   rep.set("errors", errors);
@@ -309,6 +336,8 @@ static Json validate_dir(const std::string& dir) {
   rep.set("shards", (long long)shards.size());
   rep.set("bytes", total_bytes);
   rep.set("linears", linears);
+  rep.set("root", root);
+  rep.set("unexpected", unexpected);
   return rep;
 }
 

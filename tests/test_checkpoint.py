@@ -95,3 +95,58 @@ def test_symmetric_reference_container(tmp_path):
     packed = f.tensor("model.layers.0.self_attn.o_proj.weight_packed")
     codes = quant.unpack_stream(packed, 4, cfg.q_dim)
     assert torch.equal(codes, ow.quant["0.o"].codes)
+
+
+def test_reference_tensor_names_and_leftover_report(tmp_path):
+    """Checkpoints that carry a vision tower name the text model ``model.language_model.*``; tensors of the text model
+    that the loader has no use for (here: q_norm) are reported, not fatal."""
+    d = str(tmp_path / "lm")
+    cfg = C.oracle_tiny()
+    ow = O.random_weights(cfg, seed=2)
+    extra = {"model.language_model.layers.0.self_attn.q_norm.weight": torch.ones(cfg.head_dim, dtype=torch.bfloat16),
+             "model.visual.patch_embed.proj.weight": torch.zeros(4, 4, dtype=torch.bfloat16)}
+    K.save_oracle(d, ow, root="model.language_model.", extra=extra)
+    rep = K.validate(d)
+    assert rep["ok"], rep["errors"]
+    assert rep["root"] == "model.language_model."
+    assert rep["unexpected"] == ["model.language_model.layers.0.self_attn.q_norm.weight"]     # the vision tensor is not text
+    w = K.read_weights(d)
+    assert w.unexpected == rep["unexpected"]
+    for k, ql in ow.quant.items():
+        assert torch.equal(w.quant[k].codes, ql.codes), k
+    assert torch.equal(w.embed, ow.embed)
+
+
+def test_bf16_linears_and_tied_head_are_quantised_at_load(tmp_path):
+    d = str(tmp_path / "bf")
+    cfg = C.oracle_tiny()
+    ow = O.random_weights(cfg, seed=3)
+    K.save_oracle(d, ow, bf16_linears=("self_attn.o_proj",), tied=True)
+    rep = K.validate(d)
+    assert rep["ok"], rep["errors"]
+    assert rep["linears"]["model.layers.0.self_attn.o_proj"]["format"] == "bf16" and "lm_head" not in rep["linears"]
+    w = K.read_weights(d)
+    o = w.quant["0.o"]
+    assert o.bits == K.BF16_LOAD_BITS and o.group == 128
+    ref = ow.quant["0.o"].dequant().to(torch.bfloat16).float()
+    err = (o.dequant() - ref).abs().max().item()
+    assert err <= 0.6 * float(o.scale.float().max())                       # within half a quantisation step
+    head = w.quant["lm_head"]
+    assert head.n == cfg.vocab and head.bits == K.BF16_LOAD_BITS
+    assert (head.dequant() - ow.embed.float()).abs().max().item() <= 0.6 * float(head.scale.float().max())
+
+
+def test_gated_q_proj_is_named_as_such(tmp_path):
+    d = str(tmp_path / "gated")
+    cfg = C.oracle_tiny()
+    ow = O.random_weights(cfg, seed=4)
+    K.save_oracle(d, ow, sums=False)
+    f = K.SafeTensorsFile(os.path.join(d, "model.safetensors"))
+    t = {k: f.tensor(k).clone() for k in f.keys()}
+    f.close()
+    for suf in (".weight_packed", ".weight_scale", ".weight_zero_point"):
+        n = "model.layers.0.self_attn.q_proj" + suf
+        t[n] = torch.cat([t[n], t[n]])
+    K.write_safetensors(os.path.join(d, "model.safetensors"), t, {"format": "pt"})
+    rep = K.validate(d)
+    assert not rep["ok"] and any("gated attention" in e for e in rep["errors"])
