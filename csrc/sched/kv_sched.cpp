@@ -142,70 +142,118 @@ static int pick_prefill(const long* remaining, const double* age_s, int n, long 
 }
 
 // ------------------------------------------------------------------------------------------------ copy-from-context drafter
+// Proposes the tokens that followed the longest earlier occurrence of the text's current ending (behavioural contract:
+// crates/agens-cli/src/lookup.rs: suffixes of 2..64 tokens, the 24 most recent places that end in the same two tokens
+// are examined, the most recent one wins among equally long matches, at most 7 tokens are proposed; a running mean of
+// accepted drafts per match-length class decides between this source and the model drafter).
+//
+// Data structure: every position p >= 1 carries a link to the previous position that ends the same token pair, and a
+// hash map holds the newest position per pair.  The candidates of a query are the chain behind the newest entry, in
+// recency order; appending is O(1) per token and cutting the text back just unlinks the removed positions.
 class CopyLookup {
  public:
-  static constexpr int kMaxDraft = 7, kCandidates = 24, kMaxMatch = 64, kBuckets = 6;
+  static constexpr int kMaxDraft = 7, kProbe = 24, kLongest = 64, kClasses = 6;
+
   CopyLookup() {
-    const double prior[kBuckets] = {0.6, 1.0, 1.8, 2.6, 3.6, 4.6};
-    for (int i = 0; i < kBuckets; ++i) lk_[i] = {prior[i], 4.0};
-    dr_ = {2.0, 4.0};
+    static const double start_mean[kClasses] = {0.6, 1.0, 1.8, 2.6, 3.6, 4.6};
+    for (int c = 0; c < kClasses; ++c) by_class_[c] = Ema{start_mean[c], 4.0};
+    model_ = Ema{2.0, 4.0};
   }
-  void extend(const int* toks, int n) { hist_.insert(hist_.end(), toks, toks + n); }
-  void truncate(int n) { if (n < (int)hist_.size()) { hist_.resize(n); reindex(); } }
-  int size() const { return (int)hist_.size(); }
-  // Proposes up to 7 tokens that followed the longest earlier occurrence of the current suffix.  Returns the count
-  // (0 = use the other draft source); *match_len receives the matched suffix length.
+
+  void extend(const int* toks, int n) {
+    for (int i = 0; i < n; ++i) text_.push_back(toks[i]);
+  }
+
+  void truncate(int n) {
+    if (n >= (int)text_.size()) return;
+    while (linked_ > std::max(n, 1)) unlink_last();
+    text_.resize(n);
+  }
+
+  int size() const { return (int)text_.size(); }
+
   int propose(int* out, int* match_len, bool copy_only) {
-    index_up_to((int)hist_.size() - 1);
-    pending_lookup_ = false;
-    const int n = (int)hist_.size();
+    awaiting_copy_ = false;
+    const int n = (int)text_.size();
+    // the pair that ends the text is the query: it must not be among the candidates, so linking stops one short
+    while (linked_ < n - 1) link_next();
     if (n < 3) return 0;
-    const uint64_t key = bigram(hist_[n - 2], hist_[n - 1]);
-    auto it = idx_.find(key);
-    if (it == idx_.end()) return 0;
-    const std::vector<int>& pos = it->second;
-    int best_len = 0, best_p = -1, seen = 0;
-    for (int i = (int)pos.size() - 1; i >= 0 && seen < kCandidates; --i, ++seen) {
-      const int p = pos[i];              // bigram ends at p (p < n - 1)
-      int m = 2;
-      while (m < kMaxMatch && p - m >= 0 && hist_[p - m] == hist_[n - 1 - m]) ++m;
-      if (m > best_len && p + 1 < n) { best_len = m; best_p = p; }
+    auto head = newest_.find(pair_key(text_[n - 2], text_[n - 1]));
+    if (head == newest_.end()) return 0;
+    int win_len = 0, win_at = -1;
+    int at = head->second;
+    for (int probes = 0; at > 0 && probes < kProbe; ++probes, at = back_[at]) {
+      const int len = common_suffix(at, n - 1);
+      if (len > win_len) { win_len = len; win_at = at; }
     }
-    if (best_p < 0) return 0;
-    const int b = bucket(best_len);
-    if (!copy_only && lk_[b].v <= dr_.v) return 0;           // the other source is expected to do better
+    if (win_at < 0) return 0;
+    const int cls = length_class(win_len);
+    if (!copy_only && by_class_[cls].mean <= model_.mean) return 0;       // the model drafter is expected to do better
     int cnt = 0;
-    for (int q = best_p + 1; q < n && cnt < kMaxDraft; ++q) out[cnt++] = hist_[q];
-    *match_len = best_len;
-    pending_lookup_ = cnt > 0;
-    pending_bucket_ = b;
+    for (int q = win_at + 1; q < n && cnt < kMaxDraft; ++q) out[cnt++] = text_[q];
+    *match_len = win_len;
+    awaiting_copy_ = cnt > 0;
+    awaiting_class_ = cls;
     return cnt;
   }
-  // Outcome of the verified step: `accepted` drafts were kept.
+
+  // Outcome of the verified step: `accepted` drafts were kept; the mean of the source that made the proposal moves.
   void record(int accepted) {
-    Mean& m = pending_lookup_ ? lk_[pending_bucket_] : dr_;
-    m.n += 1.0;
-    const double w = std::max(1.0 / m.n, 0.03);
-    m.v += w * (accepted - m.v);
-    pending_lookup_ = false;
+    Ema& e = awaiting_copy_ ? by_class_[awaiting_class_] : model_;
+    e.count += 1.0;
+    e.mean += std::max(1.0 / e.count, 0.03) * ((double)accepted - e.mean);
+    awaiting_copy_ = false;
   }
-  double mean_lookup(int b) const { return lk_[b].v; }
-  double mean_drafter() const { return dr_.v; }
+
+  double mean_lookup(int c) const { return by_class_[c].mean; }
+  double mean_drafter() const { return model_.mean; }
+
  private:
-  struct Mean { double v, n; };
-  static uint64_t bigram(int a, int b) { return ((uint64_t)(uint32_t)a << 32) | (uint32_t)b; }
-  static int bucket(int m) { const int th[kBuckets] = {2, 3, 4, 6, 10, 16}; int b = 0; for (int i = 0; i < kBuckets; ++i) if (m >= th[i]) b = i; return b; }
-  void index_up_to(int end) {   // positions p in [1, end): bigram (p-1, p); the last position is the query itself
-    for (int p = std::max(indexed_, 1); p < end; ++p) idx_[bigram(hist_[p - 1], hist_[p])].push_back(p);
-    indexed_ = std::max(indexed_, end);
+  struct Ema { double mean, count; };
+
+  static uint64_t pair_key(int a, int b) { return ((uint64_t)(uint32_t)a << 32) | (uint32_t)b; }
+
+  static int length_class(int len) {
+    static const int at_least[kClasses] = {2, 3, 4, 6, 10, 16};
+    int c = 0;
+    while (c + 1 < kClasses && len >= at_least[c + 1]) ++c;
+    return c;
   }
-  void reindex() { idx_.clear(); indexed_ = 0; }
-  std::vector<int> hist_;
-  std::unordered_map<uint64_t, std::vector<int>> idx_;
-  int indexed_ = 0;
-  Mean lk_[kBuckets], dr_;
-  bool pending_lookup_ = false;
-  int pending_bucket_ = 0;
+
+  // Tokens shared by the text ending at position a and the text ending at position b (a < b), at most kLongest.
+  int common_suffix(int a, int b) const {
+    int len = 0;
+    while (len < kLongest && a - len >= 0 && text_[a - len] == text_[b - len]) ++len;
+    return len;
+  }
+
+  void link_next() {                       // position p = linked_ (or 1 at the start) gets its link
+    const int p = std::max(linked_, 1);
+    if ((int)back_.size() <= p) back_.resize(p + 1, 0);
+    int& slot = newest_[pair_key(text_[p - 1], text_[p])];          // 0 = no earlier place (position 0 ends no pair)
+    back_[p] = slot;
+    slot = p;
+    linked_ = p + 1;
+  }
+
+  void unlink_last() {
+    const int p = linked_ - 1;
+    if (p >= 1) {
+      auto it = newest_.find(pair_key(text_[p - 1], text_[p]));
+      if (it != newest_.end() && it->second == p) {
+        if (back_[p] > 0) it->second = back_[p]; else newest_.erase(it);
+      }
+    }
+    linked_ = p;
+  }
+
+  std::vector<int> text_;
+  std::vector<int> back_;                              // back_[p]: previous position ending the same pair, 0 = none
+  std::unordered_map<uint64_t, int> newest_;
+  int linked_ = 0;                                     // positions below this carry their link
+  Ema by_class_[kClasses], model_;
+  bool awaiting_copy_ = false;
+  int awaiting_class_ = 0;
 };
 
 // ------------------------------------------------------------------------------------------------ prefix cache

@@ -6,13 +6,17 @@
 //           maximum) or temperature -> top-k (ties by index) -> top-p (smallest prefix whose mass reaches p) -> min-p
 //           (p >= min_p * p_max) -> one draw from the renormalised prefix.
 //   RNG     splitmix64(seed) seeds xorshift64*; one 53-bit uniform per sampled token.
-// The implementation keeps a candidate list instead of a dense probability vector, so a draw costs O(vocab) once for
-// the filter plus O(k log k) for the kept candidates.
+// Implementation: the edits touch few ids, so they are collected as a sparse patch list and applied to a working copy
+// of the row; candidates are ordered by ONE 64-bit key per id (order-preserving image of the logit in the high half, the
+// inverted index in the low half), so "logit descending, index ascending" is a plain integer order and top-k is an
+// nth_element over integers; probabilities are formed once, in that order, and one cumulative walk applies top-p,
+// min-p and the draw.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
 #include <deque>
+#include <functional>
 #include <limits>
 #include <string>
 #include <unordered_map>
@@ -55,42 +59,56 @@ struct SamplingParams {
   }
 };
 
-// Reasoning budget: after n thinking tokens without a closing tag, force the closing tag and forbid reopening.
+// Reasoning budget: a thinking block that runs for `limit` tokens without its closing tag gets the tag forced, and the
+// block may not be reopened afterwards; from 80 % of the limit an optional bias nudges the model towards closing.
+// The block is either not open, open since output index `since_`, or over (closed by the model or by force).
 class ReasoningBudget {
  public:
-  ReasoningBudget(int n, double soft, const int* prompt, int n_prompt, int start, int end)
-      : start_(start), end_(end), n_(n), soft_(soft) {
-    const int lo = std::max(0, n_prompt - 16);
-    int last_start = -1;
-    for (int i = lo; i < n_prompt; ++i) if (prompt[i] == start) last_start = i;
-    if (last_start >= 0) {
-      bool ended = false;
-      for (int i = last_start + 1; i < n_prompt; ++i) if (prompt[i] == end) ended = true;
-      if (!ended) open_at_ = 0;
+  ReasoningBudget(int limit, double nudge, const int* prompt, int n_prompt, int open_tok, int close_tok)
+      : open_tok_(open_tok), close_tok_(close_tok), limit_(limit), nudge_(nudge) {
+    // a prompt that ends inside a thinking block (opening tag among its last 16 tokens, no closing tag after it)
+    // starts the count at the first produced token
+    int opened = -1;
+    for (int i = n_prompt - 1; i >= 0 && i >= n_prompt - 16; --i)
+      if (prompt[i] == open_tok) { opened = i; break; }
+    if (opened >= 0 && std::find(prompt + opened + 1, prompt + n_prompt, close_tok) == prompt + n_prompt) {
+      phase_ = Phase::Thinking;
+      since_ = 0;
     }
   }
+
   void accept(long long out_index, int tok) {
-    if (tok == start_) { if (open_at_ < 0 && !closed_) open_at_ = out_index + 1; }
-    else if (tok == end_ && open_at_ >= 0) { open_at_ = -1; closed_ = true; }
+    if (phase_ == Phase::Outside && tok == open_tok_) { phase_ = Phase::Thinking; since_ = out_index + 1; }
+    else if (phase_ == Phase::Thinking && tok == close_tok_) phase_ = Phase::Over;
   }
-  // 0: nothing; 1: force *tok; 2: add *delta to logit of *tok (-inf masks)
+
+  // 0: nothing; 1: force *tok; 2: add *delta to the logit of *tok (-inf masks it)
   int act(long long produced, int* tok, float* delta) {
-    if (closed_) {
-      if (forced_) { *tok = start_; *delta = -std::numeric_limits<float>::infinity(); return 2; }
-      return 0;
+    switch (phase_) {
+      case Phase::Outside:
+      case Phase::Over:
+        return 0;
+      case Phase::OverForced:                 // the block was cut short: the opening tag stays masked
+        *tok = open_tok_;
+        *delta = -std::numeric_limits<float>::infinity();
+        return 2;
+      case Phase::Thinking: {
+        const long long spent = produced - since_;
+        if (spent >= limit_) { phase_ = Phase::OverForced; *tok = close_tok_; return 1; }
+        if (nudge_ != 0.0 && (double)spent >= 0.8 * (double)limit_) { *tok = close_tok_; *delta = (float)nudge_; return 2; }
+        return 0;
+      }
     }
-    if (open_at_ < 0) return 0;
-    const long long k = produced - open_at_;
-    if (k >= n_) { forced_ = closed_ = true; open_at_ = -1; *tok = end_; return 1; }
-    if (soft_ != 0.0 && (double)k >= 0.8 * n_) { *tok = end_; *delta = (float)soft_; return 2; }
     return 0;
   }
+
  private:
-  int start_, end_;
-  long long n_;
-  double soft_;
-  long long open_at_ = -1;
-  bool closed_ = false, forced_ = false;
+  enum class Phase { Outside, Thinking, Over, OverForced };
+  int open_tok_, close_tok_;
+  long long limit_;
+  double nudge_;
+  Phase phase_ = Phase::Outside;
+  long long since_ = 0;
 };
 
 // Thinking-block repetition guard: an n-gram seen k times among the n-grams ending in the last w thinking tokens.
@@ -141,85 +159,120 @@ class ThinkGuard {
   long long seen_ = 0, fired_ = -1;
 };
 
+// splitmix64 finaliser: spreads small or correlated seeds over the whole 64-bit state space
+static inline uint64_t splitmix64(uint64_t x) {
+  x += 0x9e3779b97f4a7c15ull;
+  x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+  x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+  return x ^ (x >> 31);
+}
+
+// xorshift64* generator; one 53-bit uniform in [0, 1) per call
+struct Xorshift64Star {
+  uint64_t state = 1;
+  double next() {
+    state ^= state >> 12; state ^= state << 25; state ^= state >> 27;
+    return (double)((state * 0x2545f4914f6cdd1dull) >> 11) * (1.0 / 9007199254740992.0);
+  }
+};
+
+// float -> uint32 such that the integer order equals the float order (finite values and infinities)
+static inline uint32_t ordered_bits(float v) {
+  v += 0.0f;                      // -0.0 and +0.0 compare equal as floats: give them one image
+  uint32_t u;
+  std::memcpy(&u, &v, 4);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
 class Sampler {
  public:
   Sampler(const SamplingParams& p, uint64_t request_id) : p_(p) {
-    uint64_t seed = p.has_seed ? p.seed : (0x1234567ull ^ (request_id * 0x9e3779b97f4a7c15ull));
-    uint64_t z = seed + 0x9e3779b97f4a7c15ull;                 // splitmix64: small seeds must not correlate
-    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
-    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
-    z ^= z >> 31;
-    rng_ = z | 1;
+    const uint64_t seed = p.has_seed ? p.seed : (0x1234567ull ^ (request_id * 0x9e3779b97f4a7c15ull));
+    rng_.state = splitmix64(seed) | 1;
   }
-  double uniform() {                                             // xorshift64*
-    rng_ ^= rng_ >> 12; rng_ ^= rng_ << 25; rng_ ^= rng_ >> 27;
-    return (double)((rng_ * 0x2545f4914f6cdd1dull) >> 11) / (double)(1ull << 53);
-  }
-  void accept(int tok) { ++counts_[tok]; ++produced_; }
+  double uniform() { return rng_.next(); }
+  void accept(int tok) { ++seen_[tok]; ++produced_; }
   long long produced() const { return produced_; }
+
+  // Greedy requests whose logits would not be edited can take the device's argmax: no logits row is needed.
   bool needs_logits(int vocab_valid) const {
-    if (!p_.greedy() || !p_.logit_bias.empty() || p_.repetition_penalty != 1.0 || p_.frequency_penalty != 0.0 ||
-        p_.presence_penalty != 0.0) return true;
-    if (produced_ < p_.min_new_tokens && !p_.stop_ids.empty()) return true;
-    for (int t : p_.suppress) if (t < vocab_valid) return true;
-    return false;
+    const bool edits = !p_.logit_bias.empty() || p_.repetition_penalty != 1.0 || p_.frequency_penalty != 0.0 ||
+                       p_.presence_penalty != 0.0 || (produced_ < p_.min_new_tokens && !p_.stop_ids.empty()) ||
+                       std::any_of(p_.suppress.begin(), p_.suppress.end(), [&](int t) { return t < vocab_valid; });
+    return edits || !p_.greedy();
   }
+
   int sample(const float* logits, int n, const std::pair<int, float>* extra, int n_extra) {
-    x_.assign(logits, logits + n);
-    auto in = [&](int t) { return t >= 0 && t < n; };
-    for (int i = 0; i < n_extra; ++i) if (in(extra[i].first)) x_[extra[i].first] += extra[i].second;
-    for (auto& b : p_.logit_bias) if (in(b.first)) x_[b.first] += b.second;
-    for (int t : p_.suppress) if (in(t)) x_[t] = -INFINITY;
-    for (auto& kv : counts_) {
-      if (!in(kv.first)) continue;
-      float& v = x_[kv.first];
-      if (p_.repetition_penalty != 1.0) { const float r = (float)p_.repetition_penalty; v = v > 0.f ? v / r : v * r; }
-      v -= (float)p_.frequency_penalty * (float)kv.second + (kv.second > 0 ? (float)p_.presence_penalty : 0.f);
+    row_.assign(logits, logits + n);
+    apply_edits(n, extra, n_extra);
+    if (p_.greedy()) return (int)(std::max_element(row_.begin(), row_.end()) - row_.begin());   // first index of the maximum
+
+    // candidates in (logit descending, index ascending) order = descending order of one integer key per id
+    keys_.clear();
+    for (int i = 0; i < n; ++i)
+      if (std::isfinite(row_[i])) keys_.push_back(((uint64_t)ordered_bits(row_[i]) << 32) | (uint32_t)(0xFFFFFFFFu - (uint32_t)i));
+    if (keys_.empty()) return 0;
+    size_t m = keys_.size();
+    if (p_.top_k > 0 && (size_t)p_.top_k < m) {
+      m = (size_t)p_.top_k;
+      std::nth_element(keys_.begin(), keys_.begin() + (m - 1), keys_.end(), std::greater<uint64_t>());
+      keys_.resize(m);
     }
-    if (produced_ < p_.min_new_tokens) for (int t : p_.stop_ids) if (in(t)) x_[t] = -INFINITY;
-    if (p_.greedy()) {
-      int best = 0;
-      for (int i = 1; i < n; ++i) if (x_[i] > x_[best]) best = i;
-      return best;
-    }
-    idx_.clear();
-    for (int i = 0; i < n; ++i) if (std::isfinite(x_[i])) idx_.push_back(i);
-    if (idx_.empty()) return 0;
-    auto by_logit = [&](int a, int b) { return x_[a] > x_[b] || (x_[a] == x_[b] && a < b); };
-    size_t k = p_.top_k > 0 ? std::min<size_t>((size_t)p_.top_k, idx_.size()) : idx_.size();
-    if (k < idx_.size()) { std::nth_element(idx_.begin(), idx_.begin() + (k - 1), idx_.end(), by_logit); idx_.resize(k); }
-    std::sort(idx_.begin(), idx_.end(), by_logit);
-    const float t = (float)p_.temperature;
-    const float mx = x_[idx_[0]] / t;
-    pr_.resize(idx_.size());
-    double z = 0;
-    for (size_t j = 0; j < idx_.size(); ++j) { pr_[j] = std::exp((double)(x_[idx_[j]] / t - mx)); z += pr_[j]; }
-    for (auto& v : pr_) v /= z;
-    size_t keep = pr_.size();
+    std::sort(keys_.begin(), keys_.end(), std::greater<uint64_t>());
+    auto id_of = [](uint64_t key) { return (int)(0xFFFFFFFFu - (uint32_t)key); };
+
+    // probabilities of the ordered candidates at the request's temperature
+    const float temp = (float)p_.temperature;
+    const float top = row_[id_of(keys_[0])] / temp;
+    prob_.resize(m);
+    double total = 0.0;
+    for (size_t j = 0; j < m; ++j) { prob_[j] = std::exp((double)(row_[id_of(keys_[j])] / temp - top)); total += prob_[j]; }
+    for (size_t j = 0; j < m; ++j) prob_[j] /= total;
+
+    // nucleus: the shortest prefix whose mass reaches top_p; min-p: candidates at least min_p times as likely as the first
+    size_t cut = m;
     if (p_.top_p < 1.0) {
-      double c = 0;
-      for (size_t j = 0; j < pr_.size(); ++j) { c += pr_[j]; if (c >= p_.top_p) { keep = j + 1; break; } }
+      double mass = 0.0;
+      for (size_t j = 0; j < m; ++j) { mass += prob_[j]; if (mass >= p_.top_p) { cut = j + 1; break; } }
     }
     if (p_.min_p > 0.0) {
-      const double thr = pr_[0] * p_.min_p;
-      size_t cnt = 0;
-      while (cnt < pr_.size() && pr_[cnt] >= thr) ++cnt;
-      keep = std::min(keep, std::max<size_t>(cnt, 1));
+      const double floor_p = prob_[0] * p_.min_p;
+      size_t alive = 0;
+      while (alive < m && prob_[alive] >= floor_p) ++alive;
+      cut = std::min(cut, std::max<size_t>(alive, 1));
     }
-    double zz = 0;
-    for (size_t j = 0; j < keep; ++j) zz += pr_[j];
-    double u = uniform() * zz;
-    for (size_t j = 0; j < keep; ++j) { u -= pr_[j]; if (u <= 0.0) return idx_[j]; }
-    return idx_[keep - 1];
+    double kept = 0.0;
+    for (size_t j = 0; j < cut; ++j) kept += prob_[j];
+    double ticket = uniform() * kept;
+    for (size_t j = 0; j < cut; ++j) { ticket -= prob_[j]; if (ticket <= 0.0) return id_of(keys_[j]); }
+    return id_of(keys_[cut - 1]);
   }
+
  private:
+  // extra bias -> logit_bias -> suppressed ids -> repetition / frequency / presence -> stop ids below min_new_tokens
+  void apply_edits(int n, const std::pair<int, float>* extra, int n_extra) {
+    auto valid = [n](int t) { return t >= 0 && t < n; };
+    for (int i = 0; i < n_extra; ++i) if (valid(extra[i].first)) row_[extra[i].first] += extra[i].second;
+    for (const auto& b : p_.logit_bias) if (valid(b.first)) row_[b.first] += b.second;
+    for (int t : p_.suppress) if (valid(t)) row_[t] = -INFINITY;
+    const float rep = (float)p_.repetition_penalty;
+    for (const auto& sc : seen_) {
+      if (!valid(sc.first)) continue;
+      float v = row_[sc.first];
+      if (p_.repetition_penalty != 1.0) v = v > 0.f ? v / rep : v * rep;
+      v -= (float)p_.frequency_penalty * (float)sc.second + (sc.second > 0 ? (float)p_.presence_penalty : 0.f);
+      row_[sc.first] = v;
+    }
+    if (produced_ < p_.min_new_tokens) for (int t : p_.stop_ids) if (valid(t)) row_[t] = -INFINITY;
+  }
+
   SamplingParams p_;
-  uint64_t rng_;
-  std::unordered_map<int, int> counts_;
+  Xorshift64Star rng_;
+  std::unordered_map<int, int> seen_;      // produced token -> count
   long long produced_ = 0;
-  std::vector<float> x_;
-  std::vector<int> idx_;
-  std::vector<double> pr_;
+  std::vector<float> row_;
+  std::vector<uint64_t> keys_;
+  std::vector<double> prob_;
 };
 
 }  // namespace b2

@@ -722,12 +722,29 @@ B2H_API char* b2h_render_template(const char* source, const char* context_json, 
     return nullptr;
   }
 }
+static char* parse_output_with(const char* text, const char* tools_json, int starts_in_reasoning, int chunk,
+                               const std::string& think_open, const std::string& think_close,
+                               const std::string& call_open, const std::string& call_close);
 B2H_API char* b2h_parse_output(const char* text, const char* tools_json, int starts_in_reasoning, int chunk) {
+  return parse_output_with(text, tools_json, starts_in_reasoning, chunk, "<think>", "</think>", "<tool_call>", "</tool_call>");
+}
+// The same with the tags of another template family (the reference model writes <|think|>, <|/think|>, <|call|>, <|/call|>).
+B2H_API char* b2h_parse_output_tags(const char* text, const char* tools_json, int starts_in_reasoning, int chunk,
+                                    const char* think_open, const char* think_close, const char* call_open, const char* call_close) {
+  return parse_output_with(text, tools_json, starts_in_reasoning, chunk, think_open, think_close, call_open, call_close);
+}
+static char* parse_output_with(const char* text, const char* tools_json, int starts_in_reasoning, int chunk,
+                               const std::string& think_open, const std::string& think_close,
+                               const std::string& call_open, const std::string& call_close) {
   Json tools = tools_json && *tools_json ? Json::parse(tools_json) : Json::array();
   std::string t = text, content, reasoning;
   std::vector<ToolCall> calls;
-  ReasoningParser rp(starts_in_reasoning != 0, true);
-  ToolStreamParser tp(tools);
+  ReasoningParser rp(starts_in_reasoning != 0, true, think_open, think_close);
+  ToolStreamParser tp(tools, call_open, call_close);
+  if (call_open != "<tool_call>") {          // the other template family: its parsers' conventions
+    rp.set_interrupt(call_open);
+    tp.content_before_calls_only(true);
+  }
   auto feed = [&](const std::string& piece, bool last) {
     auto ro = rp.push(piece);
     if (last) { auto f = rp.finish(); ro.content += f.content; ro.reasoning += f.reasoning; }

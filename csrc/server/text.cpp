@@ -398,6 +398,16 @@ ReasoningParser::Out ReasoningParser::push(const std::string& delta) {
       stripped_open_ = true;
     }
     const size_t cl = buf_.find(close_);
+    // a tool call that starts inside an unclosed thinking block ends the block: the call is content
+    const size_t brk = interrupt_.empty() ? std::string::npos : buf_.find(interrupt_);
+    if (brk != std::string::npos && (cl == std::string::npos || brk < cl)) {
+      std::string r = buf_.substr(0, brk);
+      buf_.erase(0, brk);
+      in_ = false;
+      if (stream_) o.reasoning += r; else { held_reasoning_ += r; o.reasoning += held_reasoning_; held_reasoning_.clear(); }
+      stripped_open_ = true;
+      continue;
+    }
     if (cl != std::string::npos) {
       std::string r = buf_.substr(0, cl);
       buf_.erase(0, cl + close_.size());
@@ -407,7 +417,7 @@ ReasoningParser::Out ReasoningParser::push(const std::string& delta) {
       stripped_open_ = true;
       continue;
     }
-    const size_t keep = partial_suffix(buf_, close_);
+    const size_t keep = std::max(partial_suffix(buf_, close_), interrupt_.empty() ? (size_t)0 : partial_suffix(buf_, interrupt_));
     std::string r = buf_.substr(0, buf_.size() - keep);
     buf_.erase(0, buf_.size() - keep);
     if (stream_) o.reasoning += r; else held_reasoning_ += r;
@@ -471,17 +481,20 @@ static bool parse_function_block(const std::string& body, const Json& tools, Too
   out.arguments_json = args.dump_python();
   return true;
 }
-ToolParse parse_tool_calls(const std::string& text, const Json& tools) {
+ToolParse parse_tool_calls(const std::string& text, const Json& tools) { return parse_tool_calls(text, tools, "<tool_call>", "</tool_call>"); }
+
+ToolParse parse_tool_calls(const std::string& text, const Json& tools, const std::string& call_open, const std::string& call_close) {
   ToolParse r;
   size_t pos = 0;
+  const size_t lo = call_open.size(), lc = call_close.size();
   while (pos < text.size()) {
-    const size_t a = text.find("<tool_call>", pos), b = text.find("<function=", pos);
+    const size_t a = text.find(call_open, pos), b = text.find("<function=", pos);
     const size_t s = std::min(a, b);
     if (s == std::string::npos) { r.content += text.substr(pos); break; }
     r.content += text.substr(pos, s - pos);
     if (s == a) {
-      size_t e = text.find("</tool_call>", s);
-      const std::string body = text.substr(s + 11, (e == std::string::npos ? text.size() : e) - s - 11);
+      size_t e = text.find(call_close, s);
+      const std::string body = text.substr(s + lo, (e == std::string::npos ? text.size() : e) - s - lo);
       const size_t fb = body.find("<function=");
       ToolCall tc;
       bool ok = false;
@@ -498,8 +511,8 @@ ToolParse parse_tool_calls(const std::string& text, const Json& tools) {
           ok = !tc.name.empty();
         } catch (...) { ok = false; }
       }
-      if (ok) r.calls.push_back(tc); else r.content += text.substr(s, (e == std::string::npos ? text.size() : e + 12) - s);
-      pos = e == std::string::npos ? text.size() : e + 12;
+      if (ok) r.calls.push_back(tc); else r.content += text.substr(s, (e == std::string::npos ? text.size() : e + lc) - s);
+      pos = e == std::string::npos ? text.size() : e + lc;
     } else {
       size_t e = text.find("</function>", s);
       ToolCall tc;
@@ -513,30 +526,44 @@ ToolParse parse_tool_calls(const std::string& text, const Json& tools) {
 
 ToolParse ToolStreamParser::push(const std::string& delta) {
   ToolParse out;
-  buf_ += delta;
+  if (content_before_calls_only_ && saw_call_ && buf_.empty()) {
+    // in this mode text after a finished call is not content, but a further call still is a call
+    tail_ += delta;
+    buf_.swap(tail_);
+  } else {
+    buf_ += delta;
+  }
   while (true) {
-    const size_t a = buf_.find("<tool_call>"), b = buf_.find("<function=");
+    const size_t a = buf_.find(call_open_), b = buf_.find("<function=");
     const size_t s = std::min(a, b);
+    const bool drop = content_before_calls_only_ && saw_call_;
     if (s == std::string::npos) {
       // emit everything except a tail that may still grow into a tag
-      const size_t keep = std::max(partial_suffix(buf_, "<tool_call>"), partial_suffix(buf_, "<function="));
-      out.content += buf_.substr(0, buf_.size() - keep);
+      const size_t keep = std::max(partial_suffix(buf_, call_open_), partial_suffix(buf_, "<function="));
+      if (!drop) out.content += buf_.substr(0, buf_.size() - keep);
       buf_.erase(0, buf_.size() - keep);
       return out;
     }
-    out.content += buf_.substr(0, s);
+    if (!drop) out.content += buf_.substr(0, s);
     buf_.erase(0, s);
-    const std::string close = (s == a) ? "</tool_call>" : "</function>";
+    const std::string close = (s == a) ? call_close_ : "</function>";
     const size_t e = buf_.find(close);
     if (e == std::string::npos) return out;   // the call is still being generated
-    ToolParse one = parse_tool_calls(buf_.substr(0, e + close.size()), tools_);
+    ToolParse one = parse_tool_calls(buf_.substr(0, e + close.size()), tools_, call_open_, call_close_);
     for (auto& c : one.calls) out.calls.push_back(c);
+    if (!one.calls.empty()) saw_call_ = true;
     out.content += one.content;
     buf_.erase(0, e + close.size());
   }
 }
 ToolParse ToolStreamParser::finish() {
-  ToolParse out = parse_tool_calls(buf_, tools_);
+  ToolParse out = parse_tool_calls(buf_, tools_, call_open_, call_close_);
+  if (content_before_calls_only_) {
+    // an unfinished call at the end of the output is neither a call nor content
+    const size_t a = buf_.find(call_open_), b = buf_.find("<function=");
+    const size_t st = std::min(a, b);
+    if (st != std::string::npos && out.calls.empty()) out.content = buf_.substr(0, st);
+  }
   buf_.clear();
   return out;
 }

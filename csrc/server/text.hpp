@@ -63,9 +63,12 @@ class ReasoningParser {
   Out parse_all(const std::string& text) const;
   Out push(const std::string& delta);
   Out finish();
+  // A tag that ends an unclosed thinking block when it shows up inside it (the tool-call opener): the model went
+  // straight from thinking to a call.  Empty = off.
+  void set_interrupt(std::string tag) { interrupt_ = std::move(tag); }
  private:
   bool in_, stream_;
-  std::string open_, close_, buf_, held_reasoning_;
+  std::string open_, close_, interrupt_, buf_, held_reasoning_;
   bool stripped_open_ = false, strip_nl_ = false;
 };
 
@@ -75,16 +78,24 @@ struct ToolCall { std::string name, arguments_json; };
 // <function=NAME><parameter=KEY>VALUE</parameter>...</function> (typed by the tool's JSON schema).
 struct ToolParse { std::string content; std::vector<ToolCall> calls; };
 ToolParse parse_tool_calls(const std::string& text, const Json& tools);
+// The same with the call wrapper of another template family (e.g. "<|call|>" ... "<|/call|>").
+ToolParse parse_tool_calls(const std::string& text, const Json& tools, const std::string& call_open, const std::string& call_close);
 
 class ToolStreamParser {
  public:
-  explicit ToolStreamParser(Json tools) : tools_(std::move(tools)) {}
+  explicit ToolStreamParser(Json tools, std::string call_open = "<tool_call>", std::string call_close = "</tool_call>")
+      : tools_(std::move(tools)), call_open_(std::move(call_open)), call_close_(std::move(call_close)) {}
   // Feeds generated text; returns content that is certainly not part of a call, and calls completed so far.
   ToolParse push(const std::string& delta);
   ToolParse finish();
+  // Content is what precedes the first call only: text after a call and an unfinished call at the end are dropped
+  // (the reference's tool-call detector reports `normal_text` that way).
+  void content_before_calls_only(bool on) { content_before_calls_only_ = on; }
  private:
   Json tools_;
-  std::string buf_;
+  std::string call_open_, call_close_;
+  std::string buf_, tail_;
+  bool content_before_calls_only_ = false, saw_call_ = false;
 };
 
 }  // namespace b2
