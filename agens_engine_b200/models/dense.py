@@ -23,6 +23,8 @@ from ..ops import linear as L
 from .config import LINEARS, ModelConfig
 
 M_GEMV = 32          # most token rows the GEMV family takes in one launch
+M_ROWS = 128         # most token rows of one step (64 decode rows or 128 verify rows, as the reference's batched engine,
+                     # kernels/m1/m1_model.cu:203-212); beyond M_GEMV rows the linears run on the tensor-core GEMM
 
 
 class DenseModel:
@@ -102,7 +104,8 @@ class DenseModel:
         cfg, dev = self.cfg, self.dev
         i32 = lambda *s: torch.zeros(*s, dtype=torch.int32, device=dev)
         bf = lambda *s: torch.zeros(*s, dtype=torch.bfloat16, device=dev)
-        M = M_GEMV
+        # rows of one step: eight per sequence slot (a verify group), at least M_GEMV, at most M_ROWS
+        M = self.max_rows = min(M_ROWS, max(M_GEMV, 8 * self.max_seqs))
         self.kv = [torch.zeros(self.n_pages, 2, cfg.n_kv_heads, cfg.page_size, cfg.head_dim, dtype=torch.bfloat16, device=dev)
                    for _ in range(cfg.n_layers)]
         self.block_table = torch.full((self.max_seqs, self.pages_per_seq), -1, dtype=torch.int32, device=dev)
@@ -416,7 +419,7 @@ class DenseModel:
         """Eager step over explicit rows: ``ids[i]`` is appended to sequence ``seqs[i]`` (rows of one sequence must be
         adjacent: they form a verify group).  Returns the argmax token of every row (and fp32 logits on request)."""
         m = len(ids)
-        assert 1 <= m <= M_GEMV
+        assert 1 <= m <= self.max_rows
         pos, g0, gc = [], [], []
         nxt = dict(self.seq_len_host)
         for i, s in enumerate(seqs):

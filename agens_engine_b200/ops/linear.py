@@ -16,7 +16,7 @@ from .._lib import (EPI_ARGMAX, EPI_F32, EPI_RESID, EPI_STORE, EPI_SWIGLU, EPI_T
                     check, current_stream, ptr)
 from ..utils import quant
 
-SS_LD = 64   # token stride of partial-sum-of-squares / argmax-partial buffers
+SS_LD = 128  # token stride of partial-sum-of-squares / argmax-partial buffers = most token rows of one step
 
 
 def fm_bytes(n: int, k: int, bits: int, group: int) -> int:

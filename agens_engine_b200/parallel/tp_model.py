@@ -21,7 +21,7 @@ import torch.distributed as dist
 from .. import _lib
 from .._lib import EPI_TP_RESID, check, current_stream, ptr
 from ..models.config import LINEARS, ModelConfig
-from ..models.dense import M_GEMV, DenseModel
+from ..models.dense import M_GEMV, M_ROWS, DenseModel
 from ..ops import linear as L
 from ..utils import quant
 from .symm import SymmetricInbox
@@ -46,7 +46,7 @@ class TpDenseModel(DenseModel):
         n_sites = 2 * cfg.n_layers + 1
         self.inbox = SymmetricInbox(rank, world, M_GEMV * cfg.d_model, n_sites, self.dev, status=self._status_all[2:3])
         self.n_sites = n_sites
-        self.idx_off = torch.full((M_GEMV,), rank * self.vocab_shard, dtype=torch.int32, device=self.dev)
+        self.idx_off = torch.full((self.max_rows,), rank * self.vocab_shard, dtype=torch.int32, device=self.dev)
         self.skip_push_site = -1     # test hook: the call site whose push this rank drops
         from .comm import PushComm
         self._gather_inbox = SymmetricInbox(rank, world, 8 * self.lm_rows, 3, self.dev,

@@ -18,7 +18,7 @@ from typing import Callable, Dict, List, Optional, Sequence
 
 import torch
 
-from ..models.dense import DenseModel, M_GEMV
+from ..models.dense import DenseModel, M_ROWS
 from ..ops import basic
 from ..spec import DraftSource, SamplingState, SpecDecoder
 from . import host
@@ -78,6 +78,25 @@ class EngineStats:
     peak_batch: int = 0
     images_encoded: int = 0
     device_errors: int = 0
+    # step timing (host clock around a scheduler iteration that did work, device included: every step ends with a
+    # read of its tokens), as the reference's per-step statistics (crates/agens-cli/src/serve.rs:149-166)
+    last_step_ms: float = 0.0
+    decode_ms_sum: float = 0.0
+    prefill_ms_sum: float = 0.0
+    rows_sum: int = 0
+
+    def prometheus(self, model=None) -> str:
+        g = [("b200e_scheduler_steps_total", self.steps), ("b200e_prefill_chunks_total", self.prefill_chunks),
+             ("b200e_tokens_prefilled_total", self.tokens_prefilled), ("b200e_tokens_reused_total", self.tokens_reused),
+             ("b200e_evictions_total", self.evictions), ("b200e_rejected_total", self.rejected),
+             ("b200e_device_errors_total", self.device_errors), ("b200e_peak_batch", self.peak_batch),
+             ("b200e_last_step_ms", round(self.last_step_ms, 3)),
+             ("b200e_decode_step_ms_avg", round(self.decode_ms_sum / max(self.steps, 1), 3)),
+             ("b200e_prefill_chunk_ms_avg", round(self.prefill_ms_sum / max(self.prefill_chunks, 1), 3)),
+             ("b200e_rows_per_step_avg", round(self.rows_sum / max(self.steps, 1), 2))]
+        if model is not None:
+            g.append(("b200e_kv_pages_free", model.free_pages()))
+        return "".join(f"{k} {v}\n" for k, v in g)
 
 
 class Engine:
@@ -91,7 +110,8 @@ class Engine:
                  invariant: bool = True, vision=None):
         self.m, self.emit = model, emit
         self.vision = vision                           # serve.vision.VisionFrontEnd, or None: requests with images fail
-        self.max_batch = min(max_batch or model.max_seqs, model.max_seqs, M_GEMV)
+        self.max_batch = min(max_batch or model.max_seqs, model.max_seqs, M_ROWS // 2)
+        self.max_rows = min(M_ROWS, getattr(model, "max_rows", M_ROWS))
         self.max_drafts = max_drafts
         if invariant:
             # batch-invariant serving (the reference's server mode): every step uses the same linear kernel whatever the
@@ -106,6 +126,11 @@ class Engine:
         self.active: Dict[int, Request] = {}           # slot -> request
         self.free_slots = list(range(model.max_seqs - 1, -1, -1))
         self.stats = EngineStats()
+        self.on_stats: Optional[Callable[[EngineStats], None]] = None      # called every few steps (metrics export)
+        import os as _os
+        w = _os.environ.get("B200E_PROFILE_STEPS", "")
+        self._prof = tuple(int(x) for x in w.split(":")) if w.count(":") == 1 and all(x.isdigit() for x in w.split(":")) else None
+        self._prof_on = False
         self._stop = threading.Event()
         self.fatal: Optional[BaseException] = None      # set when the loop had to stop for good
         self._thread: Optional[threading.Thread] = None
@@ -221,13 +246,52 @@ class Engine:
             self._intake(r)
         self._admit()
         did = False
+        self._profile_window()
         pre = [r for r in self.active.values() if r.state == PREFILL]
         if pre:
-            self._prefill_one(pre); did = True
+            t0 = time.perf_counter()
+            torch.cuda.nvtx.range_push("prefill chunk")
+            try:
+                self._prefill_one(pre)
+            finally:
+                torch.cuda.nvtx.range_pop()
+            self.stats.last_step_ms = (time.perf_counter() - t0) * 1e3
+            self.stats.prefill_ms_sum += self.stats.last_step_ms
+            did = True
         dec = [r for r in self.active.values() if r.state == DECODE]
         if dec:
-            self._decode(dec); did = True
+            t0 = time.perf_counter()
+            torch.cuda.nvtx.range_push(f"decode step ({len(dec)} sequences)")
+            steps0 = self.stats.steps
+            try:
+                self._decode(dec)
+            finally:
+                torch.cuda.nvtx.range_pop()
+            self.stats.last_step_ms = (time.perf_counter() - t0) * 1e3
+            if self.stats.steps > steps0:
+                self.stats.decode_ms_sum += self.stats.last_step_ms
+                self.stats.rows_sum += len(dec)
+            did = True
+        if did and self.on_stats is not None and (self.stats.steps + self.stats.prefill_chunks) % 16 == 0:
+            self.on_stats(self.stats)
         return did
+
+    def _profile_window(self):
+        """B200E_PROFILE_STEPS=a:b opens a profiler capture range at scheduler step a and closes it at step b, so that a
+        profiler started with capture-range control records exactly those steps (reference: the profiler window of
+        kernels/m1/m1_model.cu:3872-3873)."""
+        if self._prof is None:
+            return
+        a, b = self._prof
+        n = self.stats.steps
+        if not self._prof_on and a <= n < b:
+            torch.cuda.synchronize(self.m.dev)
+            torch.cuda.cudart().cudaProfilerStart()
+            self._prof_on = True
+        elif self._prof_on and n >= b:
+            torch.cuda.synchronize(self.m.dev)
+            torch.cuda.cudart().cudaProfilerStop()
+            self._prof_on, self._prof = False, None
 
     def _prepare_images(self, r: Request) -> bool:
         """Decodes and encodes the request's images on this (the engine's) thread and expands the prompt."""
@@ -522,7 +586,7 @@ class Engine:
         if not fast:
             return
         # verify rows of all sequences must fit one launch
-        per = max(1, min(1 + self.max_drafts, M_GEMV // len(fast)))
+        per = max(1, min(1 + self.max_drafts, self.max_rows // len(fast)))
         self.spec.max_drafts = per - 1
         slots = [r.slot for r in fast]
         try:
@@ -637,6 +701,7 @@ def attach_to_server(engine: Engine, server, context_length: Optional[int] = Non
     """Makes ``engine`` the backend of an OpenAI front end (:class:`agens_engine_b200.serve.server.Server`).  The
     server passes the request's image URLs inside the sampling object (key ``images``)."""
     engine.emit = lambda rid, toks, fin, err: server.push(rid, toks, fin, err)
+    engine.on_stats = lambda st: server.set_metrics(st.prometheus(engine.m))
 
     def generate(rid, prompt, sampling, session):
         images = sampling.pop("images", None) if isinstance(sampling, dict) else None

@@ -20,6 +20,7 @@ def _h():
             "b2h_server_new": ([cp, cp, i], vp), "b2h_server_free": ([vp], None),
             "b2h_server_use_mock": ([vp, ip, i, i, i], None), "b2h_server_mock_calls": ([vp], vp),
             "b2h_server_use_callback": ([vp, _GEN_FN, vp, i], None), "b2h_server_set_images": ([vp, i], i),
+            "b2h_server_set_metrics": ([vp, C.c_char_p], None),
             "b2h_stream_push": ([vp, C.c_longlong, ip, i, i, cp], i), "b2h_stream_cancelled": ([vp, C.c_longlong], i),
             "b2h_server_handle": ([vp, cp, cp, cp, cp, ip], vp),
             "b2h_server_start": ([vp, cp, i], i), "b2h_server_stop": ([vp], None),
@@ -126,6 +127,10 @@ class Server:
         self._cb = _GEN_FN(tramp)
         _h().b2h_server_use_callback(self._s, self._cb, None, context_length)
         _h().b2h_server_set_images(self._s, int(supports_images))
+
+    def set_metrics(self, text: str):
+        """Engine-side gauges shown by ``/metrics`` after the request counters (Prometheus text format)."""
+        _h().b2h_server_set_metrics(self._s, text.encode())
 
     def push(self, req_id: int, ids: Sequence[int], finished: bool = False, error: Optional[str] = None) -> bool:
         """Returns True when the client is gone (stop generating)."""

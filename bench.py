@@ -40,6 +40,151 @@ def reference_arm(args):
         return 0
 
 
+def _open(args, max_seqs, max_ctx, prefill_chunk):
+    """Model of this rank (TP when launched by torchrun) with random-init weights of the named architecture."""
+    import torch
+    import torch.distributed as dist
+    from agens_engine_b200.models import config as C
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+    cfg = C.dense_32b(seed=0)
+    if args.layers:
+        cfg = C.scaled(cfg, args.layers)
+    kw = dict(max_seqs=max_seqs, max_ctx=max_ctx, prefill_chunk=prefill_chunk)
+    if world > 1:
+        from agens_engine_b200.parallel.tp_model import TpDenseModel
+        m = TpDenseModel.random_init(cfg, dev, seed=0, rank=rank, world=world, **kw)
+    else:
+        from agens_engine_b200.models.dense import DenseModel
+        m = DenseModel.random_init(cfg, dev, seed=0, **kw)
+    return m, cfg, rank, world, dev
+
+
+def other_modes(args):
+    """Secondary measurements named by the benchmark configs: time to first token at long context, and aggregate
+    throughput of the serving loop (sampled requests; with the companion drafter in `spec` mode).  Device work is
+    bracketed by synchronisation on both sides; multi-GPU numbers are the maximum over ranks."""
+    import torch
+    import torch.distributed as dist
+    if args.mode == "ttft":
+        chunk = max(args.prefill_chunk, 2048)
+        m, cfg, rank, world, dev = _open(args, 1, args.ctx + 64, chunk)
+        g = torch.Generator().manual_seed(99)
+        # a short warm-up prompt first (lazy module loads, attribute calls), on its own sequence slot
+        m.new_seq(0)
+        m.prefill(0, torch.randint(0, cfg.vocab, (min(4096, args.ctx),), generator=g))
+        m.free_seq(0)
+        times = []
+        for rep in range(max(1, args.steps if args.steps < 8 else 1)):
+            prompt = torch.randint(0, cfg.vocab, (args.ctx,), generator=g)
+            m.new_seq(0)
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            first, _ = m.prefill(0, prompt)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times.append(float(t[0]) / 1e3)
+            m.free_seq(0)
+        times.sort()
+        if rank == 0:
+            p50 = times[len(times) // 2]
+            print(json.dumps({"metric": "ttft_p50_s", "value": round(p50, 3), "unit": "s", "higher_is_better": False, "n_gpus": world,
+                              "ctx": args.ctx, "prefill_chunk": chunk, "prefill_tok_s": round(args.ctx / p50, 1), "repeats": len(times),
+                              "dtype": "bf16", "data": "synthetic", "device_status": m.device_status(),
+                              "config": {"model": cfg.name, "parallelism": f"tp{world}", "kv": "all resident (no host tier)"},
+                              "timing": "CUDA events around prefill() of the whole prompt incl. the first token's lm_head; max over ranks"}))
+        if world > 1:
+            m.close(); dist.barrier(); dist.destroy_process_group()
+        return 0
+    # ---- serve / spec: the engine loop -------------------------------------------------------------------------------
+    from agens_engine_b200.serve.engine import Engine
+    C_, P, N = args.concurrency, args.prompt, args.new_tokens
+    spec = args.mode == "spec"
+    depth = args.draft_depth if spec else 0
+    m, cfg, rank, world, dev = _open(args, C_, P + N + 64, max(args.prefill_chunk, 2048))
+    ctrl = None
+    model = m
+    if world > 1:
+        from agens_engine_b200.parallel import driver as D
+        ctrl = D.control_group()
+        if rank > 0:
+            D.follow(m, ctrl)
+            torch.cuda.synchronize(); m.close(); dist.barrier(); dist.destroy_process_group()
+            return 0
+        model = D.TpDriver(m, ctrl)
+    sources = None
+    if spec:
+        from agens_engine_b200.models import config as MC
+        from agens_engine_b200.models.dense import DenseModel
+        from agens_engine_b200.spec import CopyLookupSource, ModelSource
+        drafter = DenseModel.random_init(MC.drafter_0p6b(), dev, seed=1, max_seqs=C_, max_ctx=P + N + 64, prefill_chunk=2048)
+        drafter.row_graphs = True
+        sources = lambda: [CopyLookupSource(), ModelSource(drafter, depth)]
+    first_at, count, t0 = {}, {}, [0.0]
+
+    def emit(rid, toks, finished, err):
+        if toks and rid not in first_at:
+            first_at[rid] = time.perf_counter() - t0[0]
+        count[rid] = count.get(rid, 0) + len(toks)
+        return False
+    eng = Engine(model, emit, sources_factory=sources, max_drafts=depth, max_batch=C_)
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab, (P,), generator=g).tolist() for _ in range(C_)]
+
+    def samp(i):
+        s = {"max_new_tokens": N, "seed": 100 + i, "ignore_eos": True}
+        if spec:
+            if i % 2:
+                s.update(temperature=0.8)
+            else:
+                s.update(temperature=0.0)
+        else:
+            s.update(temperature=0.7, top_p=0.9)
+        return s
+    eng.submit(prompts[0][:64], {"max_new_tokens": 4})
+    eng.run_until_idle()
+    first_at.clear(); count.clear()
+    steps0 = eng.stats.steps
+    torch.cuda.synchronize()
+    t0[0] = time.perf_counter()
+    rids = [eng.submit(p, samp(i)) for i, p in enumerate(prompts)]
+    eng.run_until_idle()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0[0]
+    total = sum(count.get(r, 0) for r in rids)
+    ttft = sorted(first_at.get(r, wall) for r in rids)
+    decode_start = ttft[-1]
+    out = {"metric": "serve_aggregate_tok_s" if not spec else "spec_aggregate_tok_s", "value": round(total / wall, 1), "unit": "tok/s",
+           "higher_is_better": True, "n_gpus": world, "dtype": "bf16", "data": "synthetic",
+           "decode_phase_tok_s": round((total - C_) / max(wall - decode_start, 1e-9), 1),
+           "ttft_p50_s": round(ttft[len(ttft) // 2], 3), "wall_s": round(wall, 2), "output_tokens": total,
+           "scheduler_steps": eng.stats.steps - steps0, "device_status": m.device_status(),
+           "config": {"model": cfg.name, "parallelism": f"tp{world}", "concurrency": C_, "prompt": P, "new_tokens": N,
+                      "sampling": "half greedy, half temperature 0.8, seeded" if spec else "temperature 0.7, top-p 0.9, seeded"},
+           "timing": "wall clock around submit .. idle on the scheduling rank, device synchronised on both sides"}
+    if spec:
+        st = eng.spec.stats
+        out["draft_depth"] = depth
+        out["accepted_per_step"] = round(st.accepted / max(st.steps, 1), 3)
+        out["spec_steps"] = st.steps
+    print(json.dumps(out))
+    if world > 1:
+        model.shutdown()
+        torch.cuda.synchronize(); m.close(); dist.barrier(); dist.destroy_process_group()
+    return 0
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only query)."""
 
@@ -90,9 +235,22 @@ def main():
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prefill-chunk", type=int, default=2048)
+    ap.add_argument("--mode", default="decode", choices=["decode", "ttft", "serve", "spec"],
+                    help="decode: the headline metric (default).  ttft: time to first token of one --ctx token prompt.  "
+                         "serve: C concurrent sampled requests through the engine loop (benchmark config 3).  "
+                         "spec: the same loop with the 0.6B drafter, half greedy / half sampled (benchmark config 5)")
+    ap.add_argument("--ctx", type=int, default=131072, help="ttft mode: prompt length")
+    ap.add_argument("--concurrency", type=int, default=16)
+    ap.add_argument("--new-tokens", type=int, default=1024)
+    ap.add_argument("--draft-depth", type=int, default=4)
+    ap.add_argument("--step-kernel", type=int, default=-1, help="1 / 0: force the persistent step kernel on / off (default: B200E_STEP)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.step_kernel >= 0:
+        os.environ["B200E_STEP"] = str(args.step_kernel)
+    if args.mode != "decode":
+        return other_modes(args)
 
     import torch
     import torch.distributed as dist

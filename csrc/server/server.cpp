@@ -128,6 +128,8 @@ struct Server {
   std::string bos_token, eos_token;
   std::shared_ptr<Backend> backend;
   std::atomic<long long> next_req{1}, n_requests{0}, n_prompt_tokens{0}, n_completion_tokens{0}, n_errors{0};
+  std::mutex extra_mu;
+  std::string extra_metrics;               // engine-side gauges (scheduler steps, step times, KV pages), set by the engine
   int listen_fd = -1;
   std::thread accept_thread;
   std::atomic<bool> stopping{false};
@@ -501,6 +503,7 @@ static HttpResponse route(Server& sv, const std::string& method, const std::stri
     std::ostringstream o;
     o << "b200e_requests_total " << sv.n_requests << "\nb200e_prompt_tokens_total " << sv.n_prompt_tokens
       << "\nb200e_completion_tokens_total " << sv.n_completion_tokens << "\nb200e_errors_total " << sv.n_errors << "\n";
+    { std::lock_guard<std::mutex> l(sv.extra_mu); o << sv.extra_metrics; }
     r.body = o.str();
     return r;
   }
@@ -620,6 +623,12 @@ B2H_API char* b2h_server_mock_calls(void* s) {
   Json a = Json::array();
   if (m) { std::lock_guard<std::mutex> l(m->mu); for (auto& c : m->calls) { Json o = Json::object(), p = Json::array(); for (int t : c.prompt) p.push_back(t); o.set("prompt", p); o.set("sampling", c.sampling); o.set("session_id", c.session_id); a.push_back(o); } }
   return dup_cstr(a.dump());
+}
+// Replaces the engine-side part of /metrics (Prometheus text lines, newline terminated).
+B2H_API void b2h_server_set_metrics(void* s, const char* text) {
+  auto sv = static_cast<Server*>(s);
+  std::lock_guard<std::mutex> l(sv->extra_mu);
+  sv->extra_metrics = text ? text : "";
 }
 B2H_API int b2h_server_set_images(void* s, int on) {
   auto b = std::dynamic_pointer_cast<CallbackBackend>(static_cast<Server*>(s)->backend);
