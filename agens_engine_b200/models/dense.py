@@ -53,10 +53,14 @@ class DenseModel:
         self._tiered_groups: Dict[int, tuple] = {}     # this step's sequences with pages on the host
         self.prefill_split = 256                       # KV split size of prefill attention
         self.prefill_mm = os.environ.get("B200E_PREFILL_MM", "1") == "1"
-        # Steps of up to eight rows can run as ONE persistent kernel (ops/step.py) when B200E_STEP=1 (or after
-        # `enable_step()`): it keeps a second copy of the weights in its own layout, and on the 32B shapes the per-op
-        # path is still the faster one, so it is opt-in.
-        self.use_step = os.environ.get("B200E_STEP", "0") == "1"
+        # Steps of up to eight rows can run as ONE persistent kernel (ops/step.py).  Measured on the 32B model (one
+        # GPU): 13.2 ms against 30.9 ms for eight rows, 10.4 against 12.1 ms for four, 9.3 against 9.1 ms for two, 9.7
+        # against 8.1 ms for one.  Mode "auto" (default) therefore uses it for three to eight rows, "on" (B200E_STEP=1,
+        # or a serving loop that pins one kernel family) for every step of up to eight rows, "off" never.  It keeps a
+        # second copy of the quantised weights in its own layout, built on first use.
+        env = os.environ.get("B200E_STEP", "auto")
+        self.step_mode = {"1": "on", "0": "off"}.get(env, "auto")
+        self.use_step = self.step_mode != "off"
         self.step = None
         self._alloc_buffers()
 
@@ -163,32 +167,42 @@ class DenseModel:
         if self.step is not None:
             self.step.close()
             self.step = None
-        if not self.use_step or self.dev.type != "cuda" or self.cfg.head_dim != 128 or self.cfg.page_size != 16:
-            return
+        if self.step_mode != "on" or not self._step_possible():
+            return                       # "auto" builds on first use (see _step_ok)
         from ..ops.step import StepRunner
         self.step = StepRunner(self)
 
-    def enable_step(self, on: bool = True):
-        """Switches small steps (up to eight rows) to the persistent step kernel, building its weight copies on first
-        use.  Under tensor parallelism every rank calls it (it opens the exchange region collectively)."""
-        self.use_step = on
-        if on and self.step is None:
-            self._open_step()
+    def _step_possible(self) -> bool:
+        return self.dev.type == "cuda" and self.cfg.head_dim == 128 and self.cfg.page_size == 16 and bool(self.layers)
+
+    def enable_step(self, on=True):
+        """``True`` / "on": every step of up to eight rows runs on the persistent step kernel (its weight copies are
+        built now); "auto": three to eight rows; ``False`` / "off": never.  Under tensor parallelism every rank calls it
+        (it opens the exchange region collectively).  Returns whether the kernel is available."""
+        mode = {True: "on", False: "off"}.get(on, on)
+        assert mode in ("on", "off", "auto")
+        self.step_mode = mode
+        self.use_step = mode != "off"
+        if mode == "on" and self.step is None and self._step_possible():
+            from ..ops.step import StepRunner
+            self.step = StepRunner(self)
         self._graphs.clear()
-        return self.step is not None
+        return self.step is not None or (mode == "auto" and self._step_possible())
 
     def _step_ok(self, m: int) -> bool:
-        """The persistent kernel takes this step: it is built, the rows fit, and the deployment has not pinned the
-        tensor-core family for small steps."""
-        return (self.step is not None and self.use_step and m <= 8 and m < (self.ws.mm_min_rows or L.MM_MIN_ROWS)
-                and not self._tiered_groups)
-
-    def set_linear_path(self, mm_min_rows: Optional[int]):
-        """Token rows from which the small-m linears run on the tcgen05 GEMM instead of the GEMV (None: the default of
-        ops.linear).  The two kernels round differently, so a deployment that wants every row to be independent of the
-        batch it travels in pins one path: 1 = tensor-core GEMM for every step, 33 = GEMV for every step."""
-        self.ws.mm_min_rows = mm_min_rows
-        self._graphs.clear()
+        """The persistent kernel takes this step: the mode wants it for this many rows, the deployment has not pinned
+        the tensor-core family for small steps, no KV is tiered, and the kernel is (or can now be) built."""
+        if self.step_mode == "off" or m > 8 or (self.step_mode == "auto" and m < 3):
+            return False
+        if m >= (self.ws.mm_min_rows or L.MM_MIN_ROWS) or self._tiered_groups:
+            return False
+        if self.step is None:
+            # "auto" on one GPU builds lazily; tensor-parallel models build through enable_step (a collective)
+            if getattr(self, "world", 1) > 1 or not self._step_possible() or torch.cuda.is_current_stream_capturing():
+                return False
+            from ..ops.step import StepRunner
+            self.step = StepRunner(self)
+        return True
 
     # ------------------------------------------------------------------------------------------------ sessions
     def new_seq(self, seq: int):
