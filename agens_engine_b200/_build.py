@@ -60,6 +60,24 @@ def _stamp(src: Path, flags, hdig: str) -> str:
     return h.hexdigest()
 
 
+def _text_with_includes(src: Path, seen=None) -> str:
+    """The source's text followed by the text of the headers of this tree that it includes (quoted includes)."""
+    import re
+    seen = seen if seen is not None else set()
+    if src in seen or not src.exists():
+        return ""
+    seen.add(src)
+    text = src.read_text(errors="ignore")
+    out = [text]
+    for inc in re.findall(r'#include\s+"([^"]+)"', text):
+        for base in (src.parent, CSRC):
+            h = (base / inc).resolve()
+            if h.exists():
+                out.append(_text_with_includes(h, seen))
+                break
+    return "\n".join(out)
+
+
 def _compile(cmd, obj: Path, stamp: str, verbose: bool, force: bool = False):
     stamp_file = obj.with_suffix(obj.suffix + ".stamp")
     if not force and obj.exists() and stamp_file.exists() and stamp_file.read_text() == stamp:
@@ -86,8 +104,8 @@ def build(verbose: bool = False, ptxas_info: bool = False, jobs: int | None = No
     for s in cu:
         rel = s.relative_to(CSRC)
         obj = OBJDIR / "cuda" / rel.with_suffix(".o")
-        text = s.read_text(errors="ignore")
-        # a measurement define only rebuilds the sources that mention it
+        text = _text_with_includes(s)
+        # a measurement define only rebuilds the sources that mention it (themselves or through their own headers)
         flags = nv_flags + [d for d in extra if d[2:].split("=")[0] in text]
         tasks.append(([nvcc, *flags, *inc, "-c", str(s), "-o", str(obj)], obj, _stamp(s, flags, hdig)))
     for s in cpp:

@@ -23,6 +23,7 @@ from ..ops import linear as L
 from .config import LINEARS, ModelConfig
 
 M_GEMV = 32          # most token rows the GEMV family takes in one launch
+STEP_ROWS = 16       # most token rows the persistent step kernel takes (ops/step.py)
 M_ROWS = 128         # most token rows of one step (64 decode rows or 128 verify rows, as the reference's batched engine,
                      # kernels/m1/m1_model.cu:203-212); beyond M_GEMV rows the linears run on the tensor-core GEMM
 
@@ -53,7 +54,7 @@ class DenseModel:
         self._tiered_groups: Dict[int, tuple] = {}     # this step's sequences with pages on the host
         self.prefill_split = 256                       # KV split size of prefill attention
         self.prefill_mm = os.environ.get("B200E_PREFILL_MM", "1") == "1"
-        # Steps of up to eight rows can run as ONE persistent kernel (ops/step.py).  Measured on the 32B model (one
+        # Steps of up to sixteen rows can run as ONE persistent kernel (ops/step.py).  Measured on the 32B model (one
         # GPU): 13.2 ms against 30.9 ms for eight rows, 10.4 against 12.1 ms for four, 9.3 against 9.1 ms for two, 9.7
         # against 8.1 ms for one.  Mode "auto" (default) therefore uses it for three to eight rows, "on" (B200E_STEP=1,
         # or a serving loop that pins one kernel family) for every step of up to eight rows, "off" never.  It keeps a
@@ -61,6 +62,7 @@ class DenseModel:
         env = os.environ.get("B200E_STEP", "auto")
         self.step_mode = {"1": "on", "0": "off"}.get(env, "auto")
         self.use_step = self.step_mode != "off"
+        self.step_uniform = False      # every step (1..16 rows) on the work split of the 9..16-row class: rows comparable bit for bit
         self.step = None
         self._alloc_buffers()
 
@@ -170,38 +172,46 @@ class DenseModel:
         if self.step_mode != "on" or not self._step_possible():
             return                       # "auto" builds on first use (see _step_ok)
         from ..ops.step import StepRunner
-        self.step = StepRunner(self)
+        self.step = StepRunner(self, uniform=self.step_uniform)
 
     def _step_possible(self) -> bool:
         return self.dev.type == "cuda" and self.cfg.head_dim == 128 and self.cfg.page_size == 16 and bool(self.layers)
 
-    def enable_step(self, on=True):
-        """``True`` / "on": every step of up to eight rows runs on the persistent step kernel (its weight copies are
-        built now); "auto": three to eight rows; ``False`` / "off": never.  Under tensor parallelism every rank calls it
-        (it opens the exchange region collectively).  Returns whether the kernel is available."""
+    def enable_step(self, on=True, uniform: Optional[bool] = None):
+        """``True`` / "on": every step of up to sixteen rows runs on the persistent step kernel (its weight copies are
+        built now); "auto": three to sixteen rows; ``False`` / "off": never.  ``uniform``: steps of one to eight rows use
+        the work split of the nine-to-sixteen-row class too, so that a row gives the same bits in a step of any size
+        (batch-invariant serving with up to sixteen rows per step); otherwise rows are bit-comparable within 1..8 and
+        within 9..16.  Under tensor parallelism every rank calls it (it opens the exchange region collectively).
+        Returns whether the kernel is available."""
         mode = {True: "on", False: "off"}.get(on, on)
         assert mode in ("on", "off", "auto")
         self.step_mode = mode
         self.use_step = mode != "off"
+        if uniform is not None and bool(uniform) != self.step_uniform:
+            self.step_uniform = bool(uniform)
+            if self.step is not None:
+                self.step.close()
+                self.step = None
         if mode == "on" and self.step is None and self._step_possible():
             from ..ops.step import StepRunner
-            self.step = StepRunner(self)
+            self.step = StepRunner(self, uniform=self.step_uniform)
         self._graphs.clear()
         return self.step is not None or (mode == "auto" and self._step_possible())
 
     def _step_ok(self, m: int) -> bool:
         """The persistent kernel takes this step: the mode wants it for this many rows, the deployment has not pinned
         the tensor-core family for small steps, no KV is tiered, and the kernel is (or can now be) built."""
-        if self.step_mode == "off" or m > 8 or (self.step_mode == "auto" and m < 3):
+        if self.step_mode == "off" or m > STEP_ROWS or (self.step_mode == "auto" and m < 3):
             return False
-        if m >= (self.ws.mm_min_rows or L.MM_MIN_ROWS) or self._tiered_groups:
+        if (self.ws.mm_min_rows and m >= self.ws.mm_min_rows) or self._tiered_groups:
             return False
         if self.step is None:
             # "auto" on one GPU builds lazily; tensor-parallel models build through enable_step (a collective)
             if getattr(self, "world", 1) > 1 or not self._step_possible() or torch.cuda.is_current_stream_capturing():
                 return False
             from ..ops.step import StepRunner
-            self.step = StepRunner(self)
+            self.step = StepRunner(self, uniform=self.step_uniform)
         return True
 
     # ------------------------------------------------------------------------------------------------ sessions

@@ -1,6 +1,6 @@
 """Launcher of the persistent decode-step kernel (``csrc/kernels/sm100/step_kernel.cu``).
 
-One cooperative launch runs a whole decode or verify step (up to eight token rows) of a dense model: every layer,
+One cooperative launch runs a whole decode or verify step (up to sixteen token rows) of a dense model: every layer,
 the lm_head and the argmax, on one GPU or as one rank of a tensor-parallel group.  Python only assembles the argument
 block; the table of per-layer weight descriptors lives in device memory and is built once.
 """
@@ -14,8 +14,11 @@ import torch
 from .. import _lib
 from .._lib import check, current_stream, ptr
 
-MAX_ROWS = 8
+MAX_ROWS = 16          # rows of one step
+SMALL_ROWS = 8         # steps of up to this many rows stage k slices of SLICE_K inputs, larger steps half of that
+SLICE_K = 5120
 MAX_TP = 8
+N_WARPS = 15
 
 
 class StepLinear(C.Structure):
@@ -42,7 +45,7 @@ class StepArgs(C.Structure):
         ("final_norm", C.c_void_p), ("embed", C.c_void_p),
         ("vocab", C.c_int), ("d_model", C.c_int), ("hq", C.c_int), ("hkv", C.c_int), ("ffn", C.c_int),
         ("eps", C.c_float), ("lm_valid", C.c_int), ("lm_offset", C.c_int),
-        ("n_rows", C.c_int),
+        ("n_rows", C.c_int), ("slice_k", C.c_int),
         ("ids", C.c_void_p), ("tok_pos", C.c_void_p), ("tok_seq", C.c_void_p),
         ("rope_pos", C.c_void_p),
         ("grp_tok0", C.c_void_p), ("grp_cnt", C.c_void_p), ("n_groups", C.c_int),
@@ -51,7 +54,8 @@ class StepArgs(C.Structure):
         ("inv_freq", C.c_void_p),
         ("split_keys", C.c_int), ("max_splits", C.c_int), ("scale_log2", C.c_float),
         ("slot_seq", C.c_void_p), ("last_ids", C.c_void_p), ("seq_len", C.c_void_p),
-        ("part", C.c_void_p), ("h", C.c_void_p), ("q", C.c_void_p), ("attn", C.c_void_p), ("act", C.c_void_p),
+        ("part", C.c_void_p), ("tile_scratch", C.c_void_p), ("xq", C.c_void_p), ("xg", C.c_void_p), ("psq", C.c_void_p),
+        ("h", C.c_void_p), ("q", C.c_void_p), ("attn", C.c_void_p), ("act", C.c_void_p),
         ("part_o", C.c_void_p), ("part_ml", C.c_void_p),
         ("amax_val", C.c_void_p), ("amax_idx", C.c_void_p),
         ("logits", C.c_void_p), ("ld_logits", C.c_long),
@@ -74,7 +78,7 @@ def _lib_step():
     lib = _lib.cuda_lib()
     if not _declared:
         vp, i = C.c_void_p, C.c_int
-        _lib.declare_optional(lib, "b2_step_linear", [vp, i, i, i, i, i, C.POINTER(StepLinear)], i)
+        _lib.declare_optional(lib, "b2_step_linear", [vp, i, i, i, i, i, i, C.POINTER(StepLinear)], i)
         _lib.declare_optional(lib, "b2_step_part_floats", [C.POINTER(StepLinear), i], C.c_long)
         _lib.declare_optional(lib, "b2_step_smem_bytes", [], i)
         _lib.declare_optional(lib, "b2_step_grid", [C.POINTER(i)], i)
@@ -98,49 +102,83 @@ def to_fi(lin) -> torch.Tensor:
     return fi
 
 
-def step_linear(lin, ncta: int, wq: Optional[torch.Tensor] = None) -> StepLinear:
+def step_linear(lin, ncta: int, wq: Optional[torch.Tensor] = None, slice_k: int = SLICE_K) -> StepLinear:
     lib = _lib_step()
     out = StepLinear()
-    check(lib.b2_step_linear(ptr(lin.wq if wq is None else wq), lin.n, lin.k, lin.bits, lin.group, ncta, C.byref(out)),
+    check(lib.b2_step_linear(ptr(lin.wq if wq is None else wq), lin.n, lin.k, lin.bits, lin.group, ncta, slice_k, C.byref(out)),
           "b2_step_linear")
     return out
+
+
+class _Geometry:
+    """Descriptor table of every linear for one k slice: steps of up to SMALL_ROWS rows use the table cut for SLICE_K,
+    larger steps the one cut for half of it.  Both tables point at the same weights."""
+
+    def __init__(self, runner, slice_k: int, rows: int):
+        lib = _lib_step()
+        model = runner.model
+        L = len(model.layers)
+        self.slice_k, self.rows = slice_k, rows
+        table = (StepLayer * max(L, 1))()
+        need = 0
+        i = 0
+        for l, d in enumerate(model.layers):
+            for name in ("qkv", "o", "gate_up", "down"):
+                sl = step_linear(d[name], runner.ncta, runner._fi[i], slice_k)
+                i += 1
+                setattr(table[l], name, sl)
+                need = max(need, lib.b2_step_part_floats(C.byref(sl), rows))
+            table[l].ln1, table[l].ln2 = ptr(d["ln1"]), ptr(d["ln2"])
+            table[l].kv_pool = ptr(model.kv[l])
+        self.lm = step_linear(model.lm_head, runner.ncta, runner._fi[i], slice_k)
+        self.part_floats = max(need, lib.b2_step_part_floats(C.byref(self.lm), rows))
+        self.table = torch.frombuffer(bytearray(bytes(table)), dtype=torch.uint8).to(model.dev)
+        self.host = table                 # geometry of the row-parallel linears (exchange-region sizing)
+
+    def exchange_floats(self, world: int, d_model: int):
+        if not len(self.host) or not self.table.numel():
+            return 0, 0
+        so, sd = self.host[0].o, self.host[0].down
+        return world * so.ks * so.fmax * self.rows * d_model, world * sd.ks * sd.fmax * self.rows * d_model
 
 
 class StepRunner:
     """Owns the descriptor table and the workspaces of the step kernel for one model instance."""
 
-    def __init__(self, model, timeout_s: float = 2.0):
+    def __init__(self, model, timeout_s: float = 2.0, max_rows: int = MAX_ROWS, uniform: bool = False):
         lib = _lib_step()
         self.model = model
         cfg, dev = model.cfg, model.dev
         if cfg.head_dim != 128 or cfg.page_size != 16:
             raise ValueError("the step kernel is built for head_dim 128 and 16-token pages")
+        if not 1 <= max_rows <= MAX_ROWS:
+            raise ValueError(f"the step kernel runs 1..{MAX_ROWS} rows")
         n = C.c_int(0)
         with torch.cuda.device(dev):
             check(lib.b2_step_grid(C.byref(n)), "b2_step_grid")
         self.ncta = n.value
+        self.max_rows = max_rows
         self.world = getattr(model, "world", 1)
         self.rank = getattr(model, "rank", 0)
-        L = len(model.layers)
-        table = (StepLayer * max(L, 1))()
-        need = 0
-        self._fi = []                     # FI copies of every linear (kept alive here)
-        for l, d in enumerate(model.layers):
-            for name in ("qkv", "o", "gate_up", "down"):
-                self._fi.append(to_fi(d[name]))
-                sl = step_linear(d[name], self.ncta, self._fi[-1])
-                setattr(table[l], name, sl)
-                need = max(need, lib.b2_step_part_floats(C.byref(sl), MAX_ROWS))
-            table[l].ln1, table[l].ln2 = ptr(d["ln1"]), ptr(d["ln2"])
-            table[l].kv_pool = ptr(model.kv[l])
+        # FI copies of every linear (kept alive here), in table order
+        self._fi = [to_fi(d[name]) for d in model.layers for name in ("qkv", "o", "gate_up", "down")]
         self._fi.append(to_fi(model.lm_head))
-        self.lm = step_linear(model.lm_head, self.ncta, self._fi[-1])
-        need = max(need, lib.b2_step_part_floats(C.byref(self.lm), MAX_ROWS))
-        raw = bytes(table)
-        self.table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(dev)
-        self._table_host = table          # geometry of the row-parallel linears (exchange-region sizing)
+        # uniform: one work split (that of the large class) for every step, so that rows are bit-comparable across sizes
+        self.uniform = uniform and max_rows > SMALL_ROWS
+        if self.uniform:
+            self.geo = [_Geometry(self, SLICE_K // 2, max_rows)] * 2
+        else:
+            self.geo = [_Geometry(self, SLICE_K, min(max_rows, SMALL_ROWS))]
+            if max_rows > SMALL_ROWS:
+                self.geo.append(_Geometry(self, SLICE_K // 2, max_rows))
         f32 = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
-        self.part = f32(max(need, 1024))
+        self.part = f32(max(max(g.part_floats for g in self.geo), 1024))
+        self.tile_scratch = f32(self.ncta * N_WARPS * 2 * MAX_ROWS * 32) if max_rows > SMALL_ROWS else None
+        # staged activations of the widest linear input (fixed-point limbs, group scalars) and the rows' sums of squares
+        kmax = max([cfg.d_model, cfg.q_dim, cfg.ffn] + [d[name].k for d in model.layers[:1] for name in ("qkv", "o", "gate_up", "down")])
+        self.xq = torch.zeros((kmax // 128) * 4096, dtype=torch.uint8, device=dev)
+        self.xg = f32((kmax // 64) * 16 * 2).zero_()
+        self.psq = f32(MAX_ROWS * (cfg.d_model // 128)).zero_()
         self.amax_val = f32(self.ncta, MAX_ROWS)
         self.amax_idx = torch.empty(self.ncta, MAX_ROWS, dtype=torch.int32, device=dev)
         self.sync = torch.zeros(64, dtype=torch.int32, device=dev)
@@ -161,13 +199,8 @@ class StepRunner:
         from ..parallel.symm import SymmetricInbox
         m, w = self.model, self.world
         d = m.cfg.d_model
-        if len(m.layers):
-            so = self._table_host[0].o
-            sd = self._table_host[0].down
-            n_o = w * so.ks * so.fmax * MAX_ROWS * d
-            n_d = w * sd.ks * sd.fmax * MAX_ROWS * d
-        else:
-            n_o = n_d = 0
+        n_o = max(g.exchange_floats(w, d)[0] for g in self.geo) if len(m.layers) else 0
+        n_d = max(g.exchange_floats(w, d)[1] for g in self.geo) if len(m.layers) else 0
         head = 64
         self.x_off = (head, head + n_o)
         self.x_amax = head + n_o + n_d
@@ -184,8 +217,12 @@ class StepRunner:
     def _args(self, m: int, n_groups: int, want_logits: bool, decode: bool) -> StepArgs:
         md, cfg = self.model, self.model.cfg
         a = StepArgs()
-        a.layers, a.n_layers = ptr(self.table), len(md.layers)
-        a.lm_head = self.lm
+        geo = self.geo[1 if m > SMALL_ROWS else 0]
+        a.layers, a.n_layers = ptr(geo.table), len(md.layers)
+        a.lm_head = geo.lm
+        a.slice_k = geo.slice_k
+        a.tile_scratch = ptr(self.tile_scratch)
+        a.xq, a.xg, a.psq = ptr(self.xq), ptr(self.xg), ptr(self.psq)
         a.final_norm, a.embed = ptr(md.final_norm), ptr(md.embed)
         a.vocab, a.d_model, a.hq, a.hkv, a.ffn = md.embed.shape[0], cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.ffn
         a.eps = cfg.rms_eps
@@ -223,7 +260,7 @@ class StepRunner:
     def launch(self, m: int, n_groups: int, want_logits: bool = False, decode: bool = False):
         """One step on the current stream (capturable).  ``decode``: rows come from ``last_ids`` / ``seq_len`` of the
         model's decode slots and both advance on the device."""
-        assert 1 <= m <= MAX_ROWS
+        assert 1 <= m <= self.max_rows
         lib = _lib_step()
         a = self._args(m, n_groups, want_logits, decode)
         with torch.cuda.device(self.model.dev):

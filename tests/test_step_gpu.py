@@ -27,7 +27,7 @@ def pair(request):
     fused = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512)
     assert fused.enable_step(), "the step kernel must be available on a CUDA device"
     plain = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512)
-    plain.use_step = False
+    plain.enable_step(False)
     return cfg, ow, fused, plain
 
 
@@ -96,6 +96,58 @@ def test_verify_block_equals_single_rows_and_batch_invariance(pair):
     m.truncate(0, 40); m.truncate(1, 23)
     _, ab = m.forward_rows([cont[0], cont[1], cont[2]], [0, 1, 2], want_logits=True)
     assert torch.equal(ab[0], a[0]) and torch.equal(ab[1], b[0])
+    assert int(m.status.item()) == 0
+
+
+@pytest.mark.parametrize("per_seq", [3, 4])
+def test_nine_to_sixteen_rows_match_per_op_path(pair, per_seq):
+    """Steps of 12 and 16 rows (four conversations, verify blocks of 3 or 4 rows each): the large-step instance of the
+    kernel (four token sets, half k slices, partial tiles in global memory) against the per-op path."""
+    cfg, ow, fused, plain = pair
+    torch.manual_seed(6)
+    prompts = [torch.randint(0, cfg.vocab, (17 + 9 * i,)) for i in range(4)]
+    toks = torch.randint(0, cfg.vocab, (4 * per_seq,)).tolist()
+    seqs = [s for s in range(4) for _ in range(per_seq)]
+    outs = []
+    for m in (fused, plain):
+        _reset(m)
+        for s, p in enumerate(prompts):
+            m.new_seq(s)
+            m.prefill(s, p)
+        before = m.step.launches if m.step is not None else 0
+        ids, lg = m.forward_rows(toks, seqs, want_logits=True)
+        outs.append(lg.cpu())
+        assert int(m.status.item()) == 0
+        if m is fused:
+            assert m.step.launches == before + 1
+    scale = outs[1].abs().max().item()
+    err = (outs[0] - outs[1]).abs().max().item()
+    assert err < 0.02 * scale, (err, scale)
+    assert (outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean().item() >= 0.8
+
+
+def test_uniform_split_makes_rows_bit_identical_across_step_sizes():
+    """With the uniform work split a row of a 12-row step equals the same row run alone (and in a 3-row step)."""
+    cfg = small_cfg(128)
+    ow = O.random_weights(cfg, seed=3)
+    m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512)
+    assert m.enable_step("on", uniform=True)
+    torch.manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab, (21 + 5 * i,)) for i in range(3)]
+    for s, p in enumerate(prompts):
+        m.new_seq(s)
+        m.prefill(s, p)
+    toks = torch.randint(0, cfg.vocab, (12,)).tolist()
+    seqs = [s for s in range(3) for _ in range(4)]
+    _, big = m.forward_rows(toks, seqs, want_logits=True)
+    big = big.clone()
+    for s, p in enumerate(prompts):
+        m.truncate(s, len(p))
+    _, small = m.forward_rows(toks[:3], [0, 0, 0], want_logits=True)
+    assert torch.equal(small[:3], big[:3])
+    m.truncate(0, len(prompts[0]))
+    _, one = m.forward_rows([toks[4]], [1], want_logits=True)
+    assert torch.equal(one[0], big[4])
     assert int(m.status.item()) == 0
 
 
