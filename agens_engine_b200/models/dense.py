@@ -55,10 +55,10 @@ class DenseModel:
         self.prefill_split = 256                       # KV split size of prefill attention
         self.prefill_mm = os.environ.get("B200E_PREFILL_MM", "1") == "1"
         # Steps of up to sixteen rows can run as ONE persistent kernel (ops/step.py).  Measured on the 32B model (one
-        # GPU): 13.2 ms against 30.9 ms for eight rows, 10.4 against 12.1 ms for four, 9.3 against 9.1 ms for two, 9.7
-        # against 8.1 ms for one.  Mode "auto" (default) therefore uses it for three to eight rows, "on" (B200E_STEP=1,
-        # or a serving loop that pins one kernel family) for every step of up to eight rows, "off" never.  It keeps a
-        # second copy of the quantised weights in its own layout, built on first use.
+        # GPU, ms per step, step kernel against per-op path): sixteen rows 14.9 / 21.1, twelve 13.7 / 20.0, eight
+        # 11.4 / 30.9, four 10.2 / 12.1, one 9.5 / 7.8.  Mode "auto" (default) therefore uses it for three to sixteen
+        # rows, "on" (B200E_STEP=1, or a serving loop that pins one kernel family) for every step of up to sixteen rows,
+        # "off" never.  It keeps a second copy of the quantised weights in its own layout, built on first use.
         env = os.environ.get("B200E_STEP", "auto")
         self.step_mode = {"1": "on", "0": "off"}.get(env, "auto")
         self.use_step = self.step_mode != "off"
@@ -213,6 +213,13 @@ class DenseModel:
             from ..ops.step import StepRunner
             self.step = StepRunner(self, uniform=self.step_uniform)
         return True
+
+    def set_linear_path(self, mm_min_rows: Optional[int]):
+        """Token rows from which the small-m linears run on the tcgen05 GEMM instead of the GEMV (None: the default of
+        ops.linear).  The two kernels round differently, so a deployment that wants every row to be independent of the
+        batch it travels in pins one path: 1 = tensor-core GEMM for every step, 33 = GEMV for every step."""
+        self.ws.mm_min_rows = mm_min_rows
+        self._graphs.clear()
 
     # ------------------------------------------------------------------------------------------------ sessions
     def new_seq(self, seq: int):

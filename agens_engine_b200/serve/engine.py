@@ -117,11 +117,15 @@ class Engine:
             # batch-invariant serving (the reference's server mode): every step uses the same linear kernel whatever the
             # number of rows, so a request's tokens do not depend on what else is running
             rows_cap = self.max_batch * (1 + max_drafts)
-            model.set_linear_path(None if rows_cap <= 8 else 1)
-            if rows_cap <= 8 and getattr(model, "step_mode", "off") != "off":
-                # up to eight rows per step: ONE kernel family for every step is the persistent step kernel
-                # (2.3 times the per-op path at eight rows, 0.83 times at one row on the 32B model)
-                model.enable_step("on")
+            can_step = getattr(model, "step_mode", "off") != "off" and getattr(model, "_step_possible", lambda: False)()
+            step_rows = 16 if can_step else 0
+            model.set_linear_path(None if rows_cap <= max(8, step_rows) else 1)
+            if rows_cap <= step_rows:
+                # up to sixteen rows per step: ONE kernel family for every step is the persistent step kernel (on the
+                # 32B model 2.7 times the per-op path at eight rows, 1.4 times at sixteen, 0.8 times at one row); beyond
+                # eight rows every step uses the work split of the large steps, so that a row's bits do not depend on
+                # how many rows share its step
+                model.enable_step("on", uniform=rows_cap > 8)
         self.spec = SpecDecoder(model, list(sources_factory()) if sources_factory else [], max_drafts=max_drafts)
         self.think = think_tokens                      # (start id, end id) for budget / guard
         self.reserve_ahead = reserve_ahead

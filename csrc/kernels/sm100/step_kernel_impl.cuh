@@ -641,6 +641,7 @@ __device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, ui
   unsigned blk, whi;
   warp_range(ph, warp, blk, whi);
   int n_tiles = 0;
+  B2_T0(tl0);
   while (blk < whi) {
     const unsigned p = blk / (unsigned)nbs;
     const int b0 = (int)(blk - p * (unsigned)nbs);
@@ -744,15 +745,19 @@ __device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, ui
     blk = p * (unsigned)nbs + (unsigned)b1;
   }
   B2_T0(tr0);
+#ifdef B2_STEP_TRACE
+  const long long tc_loop = tr0 - tl0, tc_pre = tl0 - tc_staged;
+#endif
   workers_sync();
   reduce_tiles(a, ec, tiles, tiles_global);
   workers_sync();          // tiles and activations are reused by the next phase
   B2_TC(tc_red, tr0);
 #ifdef B2_STEP_TRACE
   if (a.trace && blockIdx.x == 0 && lane == 0) {
+    const long long tc_total = clock64() - tc_begin;
     unsigned long long* tr = a.trace + 4096 + ((size_t)a.trace[4095] * kStepWarps + warp) * 8;
-    tr[0] = tc_staged - tc_begin; tr[1] = tc_wait; tr[2] = tc_comp; tr[3] = tc_pump; tr[4] = tc_red; tr[5] = tc_units;
-    tr[6] = clock64() - tc_begin;
+    tr[0] = tc_staged - tc_begin; tr[1] = tc_wait; tr[2] = tc_comp; tr[3] = tc_pump; tr[4] = tc_red; tr[5] = tc_loop;
+    tr[6] = tc_total; tr[7] = tc_pre;
   }
   workers_sync();
   if (a.trace && blockIdx.x == 0 && tid == 0) a.trace[4095] += 1;

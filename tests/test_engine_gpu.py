@@ -36,9 +36,10 @@ class Collector:
         return False
 
 
-def _alone(ow, prompt, n_new, sampling=None, path=None):
+def _alone(ow, prompt, n_new, sampling=None, path=None, uniform=False):
     m = DenseModel.from_oracle(ow, max_seqs=1, max_ctx=512, prefill_chunk=128)
-    m.set_linear_path(path)         # the engine pins the tensor-core path when a step can exceed eight rows
+    m.set_linear_path(path)         # the engine pins the tensor-core path when a step can exceed sixteen rows,
+    m.enable_step("on", uniform=uniform)   # and the persistent step kernel (one work split beyond eight rows) up to there
     return SpecDecoder(m, [], max_drafts=0).generate(0, prompt, n_new, sampling)
 
 
@@ -48,9 +49,11 @@ def test_engine_batches_match_single_runs(tiny):
     prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (5, 300, 47, 130, 9, 64)]
     samp = {"temperature": 0.9, "top_k": 50, "top_p": 0.9, "seed": 99, "max_new_tokens": 24}
     for spec in (False, True):
-        path = 1 if spec else None          # 4 sequences x (1 + 3 drafts) rows: tensor-core path for every step
-        want = [_alone(ow, p, 24, path=path) for p in prompts]
-        want_s = _alone(ow, prompts[2], 24, SamplingState(0.9, 50, 0.9, 0.0, 99), path=path)
+        # 4 sequences x (1 + 3 drafts) = 16 rows: the step kernel with the uniform work split for every step where the
+        # model allows it (head_dim 128), else the tensor-core path for every step
+        path = 1 if (spec and cfg.head_dim != 128) else None
+        want = [_alone(ow, p, 24, path=path, uniform=spec) for p in prompts]
+        want_s = _alone(ow, prompts[2], 24, SamplingState(0.9, 50, 0.9, 0.0, 99), path=path, uniform=spec)
         m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512, prefill_chunk=128)
         col = Collector()
         drafter = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512) if spec else None
