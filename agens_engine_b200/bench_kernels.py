@@ -329,23 +329,28 @@ def profile_gemm(args):
 
 def profile_step(args):
     """Small case for an ncu capture of the persistent decode-step kernel: a 4-layer cut of the 32B model (0.95 GB of
-    weights per step, far more than L2), a 512-token context, a few one-row decode steps."""
+    weights per step, far more than L2), ``--m`` conversations at a ``--ctx``-token context, a few decode steps."""
     from .models import config as C
     from .models.dense import DenseModel
     cfg = C.scaled(C.dense_32b(seed=0), args.layers or 4)
-    m = DenseModel.random_init(cfg, "cuda:0", seed=0, max_seqs=1, max_ctx=args.ctx + 64, prefill_chunk=512)
-    m.new_seq(0)
-    first, _ = m.prefill(0, torch.randint(0, cfg.vocab, (args.ctx,), generator=torch.Generator().manual_seed(1)))
-    m.decode_setup([0], [first], 8)
+    B = max(1, args.m)
+    m = DenseModel.random_init(cfg, "cuda:0", seed=0, max_seqs=B, max_ctx=args.ctx + 64, prefill_chunk=512)
+    m.enable_step("on")
+    firsts = []
+    for s in range(B):
+        m.new_seq(s)
+        firsts.append(m.prefill(s, torch.randint(0, cfg.vocab, (args.ctx,), generator=torch.Generator().manual_seed(1 + s)))[0])
+    seqs = list(range(B))
+    m.decode_setup(seqs, firsts, 8)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    m._decode_body([0])
+    m._decode_body(seqs)
     torch.cuda.synchronize()
     e0.record()
     for _ in range(4):
-        m._decode_body([0])
+        m._decode_body(seqs)
     e1.record()
     torch.cuda.synchronize()
-    print(json.dumps({"what": "profile_step", "layers": cfg.n_layers, "ctx": args.ctx, "us_per_step": e0.elapsed_time(e1) * 250.0,
+    print(json.dumps({"what": "profile_step", "layers": cfg.n_layers, "ctx": args.ctx, "rows": B, "us_per_step": e0.elapsed_time(e1) * 250.0,
                       "weight_bytes": m.weight_bytes(), "status": int(m.status.item())}))
 
 
