@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import Optional
 
 import torch
@@ -62,11 +63,44 @@ def prefill_groups(T: int, pos0: int, seq: int, dev):
     return g0, gc, pos, seqv
 
 
-def attn_prefill(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tensor, seq: int, pos0: int, hq: int,
-                 hkv: int, hd: int, status: Optional[torch.Tensor] = None, split_keys: int = 256) -> torch.Tensor:
-    """Causal attention of a prefill chunk (``q``: bf16 ``[T, hq*hd]`` at positions ``pos0 .. pos0+T-1`` of ``seq``)
-    over the paged KV cache, which already holds the chunk's own K/V."""
+PREFILL_TC_MIN_TOKENS = 64          # chunks from this size run the tcgen05 kernel (head_dim 128, group size dividing 128)
+
+
+def attn_prefill_tc(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tensor, seq: int, pos0: int, hq: int,
+                    hkv: int, status: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of a prefill chunk on the tcgen05 tensor cores (``csrc/kernels/sm100/attn_prefill_tc.cu``):
+    128-row query tiles (128 / group-size tokens x the heads of one KV group), S and the per-block output in TMEM."""
+    lib = _lib.cuda_lib()
+    if not getattr(lib, "_pf_tc_declared", False):
+        vp, i = C.c_void_p, C.c_int
+        lib.b2_attn_prefill_tc.argtypes = [vp, vp, vp, i, vp, i, i, i, i, i, C.c_float, vp, vp]
+        lib.b2_attn_prefill_tc.restype = i
+        lib._pf_tc_declared = True
     T = q.shape[0]
+    assert q.is_contiguous() and q.shape[1] == hq * 128
+    status = torch.zeros(1, dtype=torch.int32, device=q.device) if status is None else status
+    if out is None:
+        out = torch.empty(T, hq * 128, dtype=torch.bfloat16, device=q.device)
+    row = block_table[seq]
+    with torch.cuda.device(q.device):
+        check(lib.b2_attn_prefill_tc(ptr(q), ptr(kv_pool), ptr(row), row.numel(), ptr(out), T, pos0, hq, hkv, kv_pool.shape[0],
+                                     1.0 / math.sqrt(128.0), ptr(status), current_stream()), "b2_attn_prefill_tc")
+    return out
+
+
+def attn_prefill(q: torch.Tensor, kv_pool: torch.Tensor, block_table: torch.Tensor, seq: int, pos0: int, hq: int,
+                 hkv: int, hd: int, status: Optional[torch.Tensor] = None, split_keys: int = 256,
+                 tensor_core: Optional[bool] = None) -> torch.Tensor:
+    """Causal attention of a prefill chunk (``q``: bf16 ``[T, hq*hd]`` at positions ``pos0 .. pos0+T-1`` of ``seq``)
+    over the paged KV cache, which already holds the chunk's own K/V.  Chunks of at least PREFILL_TC_MIN_TOKENS rows
+    with head_dim 128 run the tcgen05 kernel (``tensor_core`` forces the choice), the rest the split-KV kernel."""
+    T = q.shape[0]
+    gq = hq // hkv
+    can_tc = hd == 128 and 128 % gq == 0 and q.is_contiguous() and block_table.stride(1) == 1
+    if tensor_core is None:
+        tensor_core = T >= PREFILL_TC_MIN_TOKENS and os.environ.get("B200E_PREFILL_ATTN_TC", "1") == "1"
+    if tensor_core and can_tc:
+        return attn_prefill_tc(q, kv_pool, block_table, seq, pos0, hq, hkv, status=status)
     g0, gc, pos, seqv = prefill_groups(T, pos0, seq, q.device)
     max_splits = (pos0 + T + split_keys - 1) // split_keys
     return attn_decode(q, kv_pool, block_table, g0, gc, pos, seqv, hq, hkv, hd, split_keys, max_splits, status=status,
