@@ -262,6 +262,20 @@ def bench_attn(args):
             print(json.dumps(dict(ctx=ctx, rows=rows, split_keys=split, shared_kv=shared, us=round(med, 1),
                                   kv_gbs=round(kv_bytes / med / 1e3, 1), frac_hbm_single_read=round(kv_bytes / med / 1e3 / pk["hbm_gbs"], 3),
                                   tflops=round(4.0 * rows * 64 * 128 * (ctx + rows / 2) / med / 1e6, 1))), flush=True)
+    # prefill chunks on the tcgen05 kernel against the split-KV kernel (CTA-shared ring), same inputs
+    for ctx, rows in ([(2560, 2048)] if args.small else [(0, 2048), (8192, 2048), (32768, 2048), (131072 - 2048, 2048), (8192, 256)]):
+        A, pool, bt, q, g0, gc, pos, seqv = _attn_case(ctx, rows, dev)
+        out = torch.empty(rows, 64 * 128, dtype=torch.bfloat16, device=dev)
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+        fl = 4.0 * rows * 64 * 128 * (ctx + rows / 2)
+        med, _ = time_cuda(lambda: A.attn_prefill_tc(q, pool, bt, 0, ctx, 64, 8, status=st, out=out), iters=5, warmup=3, flush=flush)
+        rec = dict(kernel="attn_prefill_tc", ctx=ctx, rows=rows, us=round(med, 1), tflops=round(fl / med / 1e6, 1),
+                   frac_bf16_peak=round(fl / med / 1e6 / pk["bf16_tflops"], 3), status=int(st.item()))
+        if ctx <= 32768:
+            med2, _ = time_cuda(lambda: A.attn_prefill(q, pool, bt, 0, ctx, 64, 8, 128, split_keys=256 if ctx < 16384 else 1024,
+                                                       tensor_core=False), iters=3, warmup=1, flush=flush)
+            rec.update(split_kv_us=round(med2, 1), split_kv_tflops=round(fl / med2 / 1e6, 1))
+        print(json.dumps(rec), flush=True)
     print(json.dumps({"peaks": pk, "timing": "CUDA events, median of 10, L2 flushed; split kernel + merge kernel"}))
 
 

@@ -81,8 +81,7 @@ __device__ __forceinline__ void pf_mma(uint32_t tmem_d, uint64_t adesc, uint64_t
 __device__ __forceinline__ void pf_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+__device__ __forceinline__ void pf_tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -91,10 +90,8 @@ __device__ __forceinline__ void pf_tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+__device__ __forceinline__ void pf_tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // 16-byte asynchronous copy; `valid` false writes zeros (source size 0) without touching the source.
 __device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;
@@ -106,6 +103,12 @@ __device__ __forceinline__ void pf_ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
 }
 __device__ __forceinline__ void pf_stsm_x4(uint32_t addr, const uint32_t (&r)[4]) {
   asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+}
+// 2^x on the special-function unit; 2^-inf = 0
+__device__ __forceinline__ float pf_ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ uint32_t pf_pack(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -166,27 +169,34 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
     pf_cp16(dst, src, ok);
   }
 
-  // K (which = 0) or V (which = 1) of block j into shared memory; keys past kv_len are zero-filled
-  auto load_block = [&](int j, int which) {
+  // Pages of block j that this thread's copies touch (keys 8 i + tid / 16, i = 0..7: page i / 2 of the block's four).
+  int pages[4];
+  auto find_pages = [&](int j) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = i * kPfThreads + tid;
-      const int key = e >> 4, c = e & 15;
-      const int kpos = j * BK + key;
-      const bool ok = kpos < kv_len;
+    for (int g = 0; g < 4; ++g) {
+      const int pi = j * 4 + g;
       int page = 0;
-      if (ok) {
-        const int pi = kpos >> 4;
+      if (pi * 16 < kv_len) {
         page = pi < a.bt_len ? __ldg(a.bt + pi) : -1;
         if (page < 0 || page >= a.n_pages) { atomicExch(a.status, (int)B2_ERR_BOUNDS); page = 0; }
       }
-      const bf16* src = a.kv_pool + ((((size_t)page * 2 + which) * a.hkv + kvh) * 16 + (kpos & 15)) * HD + c * 8;
-      const uint32_t dst = which == 0 ? base + SM_K + (c >> 3) * 8192 + key * 128 + (((c & 7) ^ (key & 7)) << 4)
-                                      : base + SM_VR + key * 256 + ((c ^ (key & 7)) << 4);
+      pages[g] = page;
+    }
+  };
+  // K (which = 0) or V (which = 1) of block j (whose pages find_pages looked up); keys past kv_len are zero-filled
+  const int ld_key = tid >> 4, ld_c = tid & 15;
+  auto load_block = [&](int j, int which) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int key = i * 8 + ld_key;
+      const bool ok = j * BK + key < kv_len;
+      const bf16* src = a.kv_pool + ((((size_t)pages[i >> 1] * 2 + which) * a.hkv + kvh) * 16 + (key & 15)) * HD + ld_c * 8;
+      const uint32_t dst = which == 0 ? base + SM_K + (ld_c >> 3) * 8192 + key * 128 + (((ld_c & 7) ^ (key & 7)) << 4)
+                                      : base + SM_VR + key * 256 + ((ld_c ^ (key & 7)) << 4);
       pf_cp16(dst, src, ok);
     }
   };
-  if (n_blocks > 0) { load_block(0, 0); load_block(0, 1); }
+  if (n_blocks > 0) { find_pages(0); load_block(0, 0); load_block(0, 1); }
   asm volatile("cp.async.commit_group;" ::: "memory");
 
   float o[HD];
@@ -230,7 +240,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
       pf_commit(smem_u32(&bar_s));
     }
     // V(j + 1) may overwrite the raw V buffer now (everyone is past the transpose)
-    if (j + 1 < n_blocks) load_block(j + 1, 1);
+    if (j + 1 < n_blocks) { find_pages(j + 1); load_block(j + 1, 1); }
     // C. wait for S; then K(j + 1) may overwrite K
     if (!failed && !pf_mbar_wait(smem_u32(&bar_s), par)) { failed = true; atomicExch(&s_failed, 1); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -241,13 +251,12 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
     {
       float s[BK];
       {
-        float v[32];
-        pf_tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + 0u, v);
+        uint32_t r0[32], r1[32];
+        pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 0u, r0);
+        pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 32u, r1);
+        pf_tmem_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[i] = v[i] * a.scale_log2;
-        pf_tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + 32u, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[32 + i] = v[i] * a.scale_log2;
+        for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]) * a.scale_log2; s[32 + i] = __uint_as_float(r1[i]) * a.scale_log2; }
       }
       const int kb = j * BK;
       if (!row_valid || kb + BK - 1 > limit) {
@@ -258,14 +267,14 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
       float mx = m_run;
 #pragma unroll
       for (int i = 0; i < BK; ++i) mx = fmaxf(mx, s[i]);
-      corr = (mx == -INFINITY) ? 1.f : exp2f(m_run - mx);
+      const float mref = (mx == -INFINITY) ? 0.f : mx;      // a fully masked row: every p = 2^-inf = 0
+      corr = pf_ex2(m_run - mref);
       m_run = mx;
       float sum = 0.f;
       uint32_t pk[BK / 2];
 #pragma unroll
       for (int i = 0; i < BK; i += 2) {
-        const float p0 = (s[i] == -INFINITY) ? 0.f : exp2f(s[i] - mx);
-        const float p1 = (s[i + 1] == -INFINITY) ? 0.f : exp2f(s[i + 1] - mx);
+        const float p0 = pf_ex2(s[i] - mref), p1 = pf_ex2(s[i + 1] - mref);
         sum += p0 + p1;
         pk[i >> 1] = pf_pack(p0, p1);
       }
@@ -291,11 +300,16 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
     if (!failed && !pf_mbar_wait(smem_u32(&bar_o), par)) { failed = true; atomicExch(&s_failed, 1); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-    for (int c0 = 0; c0 < HD; c0 += 32) {
-      float v[32];
-      pf_tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + 64u + (uint32_t)c0, v);
+    for (int c0 = 0; c0 < HD; c0 += 64) {
+      uint32_t r0[32], r1[32];
+      pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 64u + (uint32_t)c0, r0);
+      pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 96u + (uint32_t)c0, r1);
+      pf_tmem_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, v[i]);
+      for (int i = 0; i < 32; ++i) {
+        o[c0 + i] = fmaf(o[c0 + i], corr, __uint_as_float(r0[i]));
+        o[c0 + 32 + i] = fmaf(o[c0 + 32 + i], corr, __uint_as_float(r1[i]));
+      }
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
