@@ -292,6 +292,20 @@ def profile_attn(args):
     print("profile_attn done")
 
 
+def profile_attn_tc(args):
+    """A few plain launches of the tcgen05 prefill attention for a profiler capture: a ``--rows``-token chunk (default
+    256 -> use 2048) of the 32B head layout at a ``--ctx``-token context (K/V of 8K tokens: 268 MB per layer pool)."""
+    dev = "cuda:0"
+    rows, ctx = args.rows, args.ctx
+    A, pool, bt, q, g0, gc, pos, seqv = _attn_case(ctx, rows, dev)
+    out = torch.empty(rows, 64 * 128, dtype=torch.bfloat16, device=dev)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    for _ in range(3):
+        A.attn_prefill_tc(q, pool, bt, 0, ctx, 64, 8, status=st, out=out)
+    torch.cuda.synchronize()
+    print("profile_attn_tc done, status", int(st.item()))
+
+
 def profile_misc(args):
     """Plain launches of the small kernels of a step on 32B shapes, for a profiler capture: RoPE + paged KV store of a
     2048-row chunk, RMSNorm of 2048 x 5120, the sampler on 32 rows of a 151936-entry vocabulary, and two blocks of the
@@ -370,7 +384,7 @@ def profile_step(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_gemm", "profile_misc", "profile_step"])
+    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_attn_tc", "profile_gemm", "profile_misc", "profile_step"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--ks", type=int, default=0)
@@ -395,6 +409,8 @@ def main(argv=None):
         bench_attn(args)
     elif args.what == "profile_attn":
         profile_attn(args)
+    elif args.what == "profile_attn_tc":
+        profile_attn_tc(args)
     elif args.what == "profile_gemm":
         profile_gemm(args)
     elif args.what == "profile_misc":

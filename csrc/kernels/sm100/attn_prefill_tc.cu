@@ -8,12 +8,14 @@
 //   S (128 x 64, fp32, TMEM)   = Q (smem, K-major, 128-byte swizzle)  x  K_blk^T (smem, K-major)      8 MMAs of k = 16
 //   P = exp2(S * scale - m)    thread = row: tcgen05.ld of its 64 scores, online max / sum, bf16 P row written to
 //                              shared memory in the swizzled A-operand layout
-//   O_blk (128 x 128, TMEM)    = P (smem)  x  V_blk (smem as V^T, K-major)                              4 MMAs of k = 16
+//   O_blk (128 x 128, TMEM)    = P (smem)  x  V_blk (smem as loaded, MN-major B operand)                4 MMAs of k = 16
 //   O = O * exp2(m_old - m) + O_blk      in registers (128 fp32 per thread)
 //
-// K and V pages arrive with cp.async (16-token pages are contiguous 4 KB, so a block is four pages); V is transposed
-// through ldmatrix.trans / stmatrix into the K-major layout the B operand wants.  While the tensor core works on one
-// CTA's MMAs the other resident CTA of the SM (96 KB of shared memory and 256 TMEM columns each) runs its softmax.
+// K and V pages arrive with cp.async (16-token pages are contiguous 4 KB, so a block is four pages) straight into the
+// swizzled operand layout; V needs no transpose because the B operand of P V is taken MN-major.  S is double-buffered
+// in TMEM and K in shared memory: S(j + 1) is issued right behind P V(j), so the tensor core computes it while the
+// threads fold O_blk(j) into O.  While one CTA runs its softmax the other resident CTA of the SM (96 KB of shared
+// memory and 256 TMEM columns each) has the tensor core.
 // Every wait on the tensor core is bounded; expiry sets the status word and the CTA leaves through the normal exit
 // (TMEM is released).
 #include "common.cuh"
@@ -24,12 +26,11 @@ namespace {
 constexpr int HD = 128;
 constexpr int BK = 64;                 // keys per block
 constexpr int kPfThreads = 128;
-constexpr int kPfTmemCols = 256;       // S at column 0 (64 columns), O_blk at column 64 (128 columns)
+constexpr int kPfTmemCols = 256;       // S of even / odd blocks at columns 0 / 64 (64 columns each), O_blk at column 128 (128 columns)
 constexpr int SM_Q = 0;                // two 64-dim halves of [128 rows][128 B]
-constexpr int SM_K = 32768;            // two halves of [64 keys][128 B]
-constexpr int SM_VR = SM_K + 16384;    // V as loaded: [64 keys][256 B], 16-byte chunks XOR-swizzled by key
-constexpr int SM_VT = SM_VR + 16384;   // V^T: [128 dims][128 B = 64 keys]
-constexpr int SM_P = SM_VT + 16384;    // P: [128 rows][128 B = 64 keys]
+constexpr int SM_K = 32768;            // two K buffers, each two 64-dim halves of [64 keys][128 B]
+constexpr int SM_V = SM_K + 32768;     // V, same layout as a K buffer
+constexpr int SM_P = SM_V + 16384;     // P: [128 rows][128 B = 64 keys]
 constexpr int SM_PF_BYTES = SM_P + 16384 + 1024;   // + slack for the 1024-byte alignment of the swizzle pattern
 
 struct PfArgs {
@@ -70,9 +71,20 @@ __device__ __forceinline__ uint64_t pf_desc(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;
   return d;
 }
-// D fp32, A / B bf16, both K-major, N / 8 and M / 16.
-__host__ __device__ constexpr uint32_t pf_idesc(int m, int n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+// D fp32, A / B bf16, A K-major, B K-major or (b_mn) MN-major, N / 8 and M / 16.
+__host__ __device__ constexpr uint32_t pf_idesc(int m, int n, bool b_mn = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+// MN-major operand, 128-byte swizzle: 64 elements of the MN dimension are contiguous (128 B); successive k rows are
+// 128 B apart, 8-row groups `sbo` bytes apart, the next 64 MN elements `lbo` bytes away.
+__device__ __forceinline__ uint64_t pf_desc_mn(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)(lbo >> 4) << 16;
+  d |= (uint64_t)(sbo >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
 }
 __device__ __forceinline__ void pf_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
@@ -97,13 +109,6 @@ __device__ __forceinline__ void pf_cp16(uint32_t dst, const void* src, bool vali
   const int n = valid ? 16 : 0;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
-__device__ __forceinline__ void pf_ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void pf_stsm_x4(uint32_t addr, const uint32_t (&r)[4]) {
-  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
-}
 // 2^x on the special-function unit; 2^-inf = 0
 __device__ __forceinline__ float pf_ex2(float x) {
   float y;
@@ -119,11 +124,11 @@ __device__ __forceinline__ uint32_t pf_pack(float a, float b) {
 
 __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const PfArgs a) {
   extern __shared__ __align__(1024) uint8_t pf_smem[];
-  __shared__ __align__(8) uint64_t bar_s, bar_o;
+  __shared__ __align__(8) uint64_t bar_s[2], bar_o;
   __shared__ uint32_t tmem_slot;
   __shared__ int s_failed;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const uint32_t base = (smem_u32(pf_smem) + 1023u) & ~1023u;
   const int gq = a.hq / a.hkv;
   const int tt = 128 / gq;                                   // tokens per tile
@@ -136,7 +141,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
   const int n_blocks = (kv_len + BK - 1) / BK;
 
   if (tid == 0) {
-    pf_mbar_init(smem_u32(&bar_s), 1);
+    pf_mbar_init(smem_u32(&bar_s[0]), 1);
+    pf_mbar_init(smem_u32(&bar_s[1]), 1);
     pf_mbar_init(smem_u32(&bar_o), 1);
     s_failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -149,9 +155,10 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_slot;
+  const uint32_t tmem_row = tmem_base + ((uint32_t)(warp * 32) << 16);     // this warp's 32 TMEM lanes
   pdl_wait();
 
-  // this thread's row: token t of the tile, query head h of the group
+  // this thread's row: token rt of the tile, query head rh of the group
   const int row = tid;
   const int rt = row / gq, rh = row - rt * gq;
   const bool row_valid = rt < n_tok;
@@ -165,13 +172,15 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
     const int t = r / gq, h = r - t * gq;
     const bool ok = t < n_tok;
     const bf16* src = a.q + ((size_t)(tok0 + (ok ? t : 0)) * a.hq + (size_t)kvh * gq + h) * HD + c * 8;
-    const uint32_t dst = base + SM_Q + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-    pf_cp16(dst, src, ok);
+    pf_cp16(base + SM_Q + (c >> 3) * 16384 + r * 128 + (((c & 7) ^ (r & 7)) << 4), src, ok);
   }
 
-  // Pages of block j that this thread's copies touch (keys 8 i + tid / 16, i = 0..7: page i / 2 of the block's four).
-  int pages[4];
-  auto find_pages = [&](int j) {
+  // K (which = 0) or V (which = 1) of block j: 64 keys x 256 B as two 64-dim halves of [64 keys][128 B], 16-byte chunks
+  // swizzled by key (K is the K-major B operand of S = Q K^T, V the MN-major B operand of O = P V).  This thread copies
+  // chunk tid & 15 of keys 8 i + tid / 16; the block's four pages are looked up once; keys past kv_len are zero-filled.
+  const int ld_key = tid >> 4, ld_c = tid & 15;
+  auto load_block = [&](int j, int which, uint32_t dst_base) {
+    int pages[4];
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       const int pi = j * 4 + g;
@@ -182,78 +191,64 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
       }
       pages[g] = page;
     }
-  };
-  // K (which = 0) or V (which = 1) of block j (whose pages find_pages looked up); keys past kv_len are zero-filled
-  const int ld_key = tid >> 4, ld_c = tid & 15;
-  auto load_block = [&](int j, int which) {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int key = i * 8 + ld_key;
       const bool ok = j * BK + key < kv_len;
       const bf16* src = a.kv_pool + ((((size_t)pages[i >> 1] * 2 + which) * a.hkv + kvh) * 16 + (key & 15)) * HD + ld_c * 8;
-      const uint32_t dst = which == 0 ? base + SM_K + (ld_c >> 3) * 8192 + key * 128 + (((ld_c & 7) ^ (key & 7)) << 4)
-                                      : base + SM_VR + key * 256 + ((ld_c ^ (key & 7)) << 4);
-      pf_cp16(dst, src, ok);
+      pf_cp16(dst_base + (ld_c >> 3) * 8192 + key * 128 + (((ld_c & 7) ^ (key & 7)) << 4), src, ok);
     }
   };
-  if (n_blocks > 0) { find_pages(0); load_block(0, 0); load_block(0, 1); }
-  asm volatile("cp.async.commit_group;" ::: "memory");
+  auto commit = [] { asm volatile("cp.async.commit_group;" ::: "memory"); };
+  constexpr uint32_t idesc_s = pf_idesc(128, BK), idesc_o = pf_idesc(128, HD, true);
+  auto issue_s = [&](int j) {               // S(j) = Q K(j)^T into TMEM columns 64 (j & 1)
+    const uint32_t kb = base + SM_K + (j & 1) * 16384;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint64_t dq = pf_desc(base + SM_Q + h * 16384), dk = pf_desc(kb + h * 8192);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) pf_mma(tmem_base + 64u * (j & 1), dq + 2 * k, dk + 2 * k, idesc_s, (h | k) ? 1u : 0u);
+    }
+    pf_commit(smem_u32(&bar_s[j & 1]));
+  };
+
+  // prologue: Q + K(0) | K(1) | V(0) as three copy groups; S(0) is issued as soon as the first has landed
+  if (n_blocks > 0) load_block(0, 0, base + SM_K);
+  commit();
+  if (n_blocks > 1) load_block(1, 0, base + SM_K + 16384);
+  commit();
+  if (n_blocks > 0) load_block(0, 1, base + SM_V);
+  commit();
+  asm volatile("cp.async.wait_group 2;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (tid == 0 && n_blocks > 0) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    issue_s(0);
+  }
 
   float o[HD];
 #pragma unroll
   for (int i = 0; i < HD; ++i) o[i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
-  constexpr uint32_t idesc_s = pf_idesc(128, BK), idesc_o = pf_idesc(128, HD);
   bool failed = false;
 
 #pragma unroll 1
   for (int j = 0; j < n_blocks; ++j) {
-    const uint32_t par = (uint32_t)j & 1u;
-    // A. K(j), V(j) (and Q) have landed; V -> V^T
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    if (__syncthreads_or(failed ? 1 : 0)) break;          // a wait gave up in the previous block: everyone leaves together
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int dc = warp * 4 + (u >> 1), k0 = (u & 1) * 32;              // 8-dim chunk, first key
-      uint32_t r[4];
-      {
-        const int key = k0 + 8 * (lane >> 3) + (lane & 7);
-        pf_ldsm_x4_t(base + SM_VR + key * 256 + ((dc ^ (key & 7)) << 4), r);
-      }
-      {
-        const int d = dc * 8 + (lane & 7), kc = (k0 >> 3) + (lane >> 3);   // row of V^T, 8-key chunk
-        pf_stsm_x4(base + SM_VT + d * 128 + ((kc ^ (d & 7)) << 4), r);
-      }
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    // B. S = Q K^T
-    if (tid == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const uint64_t dq = pf_desc(base + SM_Q + h * 16384), dk = pf_desc(base + SM_K + h * 8192);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) pf_mma(tmem_base, dq + 2 * k, dk + 2 * k, idesc_s, (h | k) ? 1u : 0u);
-      }
-      pf_commit(smem_u32(&bar_s));
-    }
-    // V(j + 1) may overwrite the raw V buffer now (everyone is past the transpose)
-    if (j + 1 < n_blocks) { find_pages(j + 1); load_block(j + 1, 1); }
-    // C. wait for S; then K(j + 1) may overwrite K
-    if (!failed && !pf_mbar_wait(smem_u32(&bar_s), par)) { failed = true; atomicExch(&s_failed, 1); }
+    // 1. S(j) is complete: its K buffer takes K(j + 2)
+    if (!failed && !pf_mbar_wait(smem_u32(&bar_s[j & 1]), (uint32_t)(j >> 1) & 1u)) { failed = true; atomicExch(&s_failed, 1); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (j + 1 < n_blocks) load_block(j + 1, 0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    // D. softmax of this thread's row
-    float corr = 1.f;
+    if (j + 2 < n_blocks) load_block(j + 2, 0, base + SM_K + (j & 1) * 16384);
+    commit();
+    // 2. softmax of this thread's row -> P
+    float corr;
     {
       float s[BK];
       {
         uint32_t r0[32], r1[32];
-        pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 0u, r0);
-        pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 32u, r1);
+        pf_tmem_ld32_issue(tmem_row + 64u * (j & 1), r0);
+        pf_tmem_ld32_issue(tmem_row + 64u * (j & 1) + 32u, r1);
         pf_tmem_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]) * a.scale_log2; s[32 + i] = __uint_as_float(r1[i]) * a.scale_log2; }
@@ -285,25 +280,31 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + ((c ^ (row & 7)) << 4)), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
                      "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
     }
+    // 3. everything but the newest copy group has landed: K(j + 1) and V(j)
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    // E. O_blk = P V
+    if (__syncthreads_or(failed ? 1 : 0)) break;            // a wait gave up: everyone leaves together
+    // 4. O_blk = P V(j); then S(j + 1) right behind it, so that it runs while the threads fold O_blk into O
     if (tid == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint64_t dp = pf_desc(base + SM_P), dv = pf_desc(base + SM_VT);
+      const uint64_t dp = pf_desc(base + SM_P);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) pf_mma(tmem_base + 64u, dp + 2 * k, dv + 2 * k, idesc_o, k ? 1u : 0u);
+      for (int k = 0; k < 4; ++k)
+        pf_mma(tmem_base + 128u, dp + 2 * k, pf_desc_mn(base + SM_V + k * 2048, 8192, 1024), idesc_o, k ? 1u : 0u);
       pf_commit(smem_u32(&bar_o));
+      if (j + 1 < n_blocks) issue_s(j + 1);
     }
-    // F. O = O * corr + O_blk
-    if (!failed && !pf_mbar_wait(smem_u32(&bar_o), par)) { failed = true; atomicExch(&s_failed, 1); }
+    // 5. O = O * corr + O_blk; the V buffer takes V(j + 1)
+    if (!failed && !pf_mbar_wait(smem_u32(&bar_o), (uint32_t)j & 1u)) { failed = true; atomicExch(&s_failed, 1); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (j + 1 < n_blocks) load_block(j + 1, 1, base + SM_V);
+    commit();
 #pragma unroll
     for (int c0 = 0; c0 < HD; c0 += 64) {
       uint32_t r0[32], r1[32];
-      pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 64u + (uint32_t)c0, r0);
-      pf_tmem_ld32_issue(tmem_base + ((uint32_t)(warp * 32) << 16) + 96u + (uint32_t)c0, r1);
+      pf_tmem_ld32_issue(tmem_row + 128u + (uint32_t)c0, r0);
+      pf_tmem_ld32_issue(tmem_row + 160u + (uint32_t)c0, r1);
       pf_tmem_wait();
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
