@@ -244,6 +244,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
     // 2. softmax of this thread's row -> P
     float corr;
     {
+      // raw scores; the softmax scale folds into the exponent: p = 2^(s * scale - m * scale), m = max of the raw scores
       float s[BK];
       {
         uint32_t r0[32], r1[32];
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
         pf_tmem_ld32_issue(tmem_row + 64u * (j & 1) + 32u, r1);
         pf_tmem_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]) * a.scale_log2; s[32 + i] = __uint_as_float(r1[i]) * a.scale_log2; }
+        for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(r0[i]); s[32 + i] = __uint_as_float(r1[i]); }
       }
       const int kb = j * BK;
       if (!row_valid || kb + BK - 1 > limit) {
@@ -259,20 +260,29 @@ __global__ void __launch_bounds__(kPfThreads, 2) attn_prefill_tc_kernel(const Pf
         for (int i = 0; i < BK; ++i)
           if (!row_valid || kb + i > limit) s[i] = -INFINITY;
       }
-      float mx = m_run;
+      // four independent chains for the maximum and for the sum: a warp has only one partner warp on its scheduler
+      float mx4[4] = {m_run, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int i = 0; i < BK; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 0; i < BK; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], s[i + u]);
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float mref = (mx == -INFINITY) ? 0.f : mx;      // a fully masked row: every p = 2^-inf = 0
-      corr = pf_ex2(m_run - mref);
+      const float moff = -mref * a.scale_log2;
+      corr = pf_ex2(fmaf(m_run, a.scale_log2, moff));
       m_run = mx;
-      float sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[BK / 2];
 #pragma unroll
-      for (int i = 0; i < BK; i += 2) {
-        const float p0 = pf_ex2(s[i] - mref), p1 = pf_ex2(s[i + 1] - mref);
-        sum += p0 + p1;
+      for (int i = 0; i < BK; i += 4) {
+        const float p0 = pf_ex2(fmaf(s[i], a.scale_log2, moff)), p1 = pf_ex2(fmaf(s[i + 1], a.scale_log2, moff));
+        const float p2 = pf_ex2(fmaf(s[i + 2], a.scale_log2, moff)), p3 = pf_ex2(fmaf(s[i + 3], a.scale_log2, moff));
+        sum4[0] += p0; sum4[1] += p1; sum4[2] += p2; sum4[3] += p3;
         pk[i >> 1] = pf_pack(p0, p1);
+        pk[(i >> 1) + 1] = pf_pack(p2, p3);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l_run = l_run * corr + sum;
       const uint32_t prow = base + SM_P + row * 128;
 #pragma unroll
