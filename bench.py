@@ -33,11 +33,27 @@ def reference_arm(args):
     except Exception as e:          # the driver expects one JSON line and exit code 0 whatever happens here
         print(json.dumps({"impl": "reference", "unavailable": f"baseline/reference_arm.py could not be imported: {e}"}))
         return 0
+    import threading
+    rank0 = int(os.environ.get("RANK", "0")) == 0
+
+    def give_up(why):
+        # one JSON line from rank 0, exit code 0 on every rank, no teardown (a blocked collective must not hold the job)
+        if rank0:
+            print(json.dumps({"impl": "reference", "unavailable": why[:300]}))
+        sys.stdout.flush()
+        os._exit(0)
+
+    limit = float(os.environ.get("B200E_REF_ARM_LIMIT_S", "900"))
+    timer = threading.Timer(limit, give_up, args=(f"reference arm did not finish within {limit:.0f} s",))
+    timer.daemon = True
+    timer.start()
     try:
-        return R.run(args)
+        rc = R.run(args)
+        timer.cancel()
+        return rc
     except Exception as e:
-        print(json.dumps({"impl": "reference", "unavailable": f"reference arm failed: {type(e).__name__}: {e}"[:300]}))
-        return 0
+        timer.cancel()
+        give_up(f"reference arm failed: {type(e).__name__}: {e}")
 
 
 def _open(args, max_seqs, max_ctx, prefill_chunk):
