@@ -34,6 +34,9 @@ def _h():
         h.b2h_ppm_header.argtypes, h.b2h_ppm_header.restype = [vp, C.c_long, ip, ip], i
         h.b2h_expand_placeholders.argtypes, h.b2h_expand_placeholders.restype = [ip, i, i, ip, i, ip, i], i
         h.b2h_mrope_positions.argtypes, h.b2h_mrope_positions.restype = [ip, i, i, ip, i, ip], i
+        h.b2h_jpeg_info.argtypes, h.b2h_jpeg_info.restype = [vp, C.c_long, ip, ip, ip], i
+        h.b2h_jpeg_decode.argtypes, h.b2h_jpeg_decode.restype = [vp, C.c_long, vp], i
+        h.b2h_jpeg_error.argtypes, h.b2h_jpeg_error.restype = [], C.c_char_p
         _sig = True
     return h
 
@@ -84,8 +87,9 @@ def mrope_positions(ids: Sequence[int], pad_id: int, grids: Sequence[Tuple[int, 
 
 # ---------------------------------------------------------------------------------------------------------------------
 def decode_image(data: bytes) -> np.ndarray:
-    """uint8 [h, w, 3] from a binary PPM or a non-interlaced 8-bit PNG (RGB, RGBA, grey, grey+alpha, palette); alpha is
-    dropped.  JPEG is not decoded here (no decoder in this build): callers get a clear error."""
+    """uint8 [h, w, 3] from a binary PPM, a non-interlaced 8-bit PNG (RGB, RGBA, grey, grey+alpha, palette; alpha is
+    dropped) or a baseline JPEG (``csrc/server/jpeg.cpp``: grey or three components, 1x / 2x sampling factors, restart
+    intervals; progressive and arithmetic-coded files are refused with a message)."""
     if data[:2] == b"P6":
         h, w = C.c_int(), C.c_int()
         buf = (C.c_ubyte * len(data)).from_buffer_copy(data)
@@ -96,8 +100,22 @@ def decode_image(data: bytes) -> np.ndarray:
     if data[:8] == b"\x89PNG\r\n\x1a\n":
         return _decode_png(data)
     if data[:2] == b"\xff\xd8":
-        raise ValueError("JPEG input needs a decoder that this build does not carry; send PNG or PPM")
+        return _decode_jpeg(data)
     raise ValueError("unknown image format")
+
+
+def _decode_jpeg(data: bytes) -> np.ndarray:
+    lib = _h()
+    buf = (C.c_ubyte * len(data)).from_buffer_copy(data)
+    h, w, nc = C.c_int(), C.c_int(), C.c_int()
+    if lib.b2h_jpeg_info(buf, len(data), C.byref(h), C.byref(w), C.byref(nc)) != 0:
+        raise ValueError(lib.b2h_jpeg_error().decode() or "bad JPEG")
+    if h.value * w.value > (1 << 28):
+        raise ValueError("jpeg: image too large")
+    out = np.empty((h.value, w.value, 3), dtype=np.uint8)
+    if lib.b2h_jpeg_decode(buf, len(data), out.ctypes.data_as(C.c_void_p)) != 0:
+        raise ValueError(lib.b2h_jpeg_error().decode() or "bad JPEG")
+    return out
 
 
 def _decode_png(data: bytes) -> np.ndarray:

@@ -1,0 +1,416 @@
+// Baseline JPEG decoder (ITU-T T.81 sequential DCT, Huffman coding, 8-bit samples) for image inputs of chat requests.
+//
+// The reference decodes JPEG data URLs with nvJPEG on the GPU (kernels/oracle/bridge/vision.cpp:204-228) after the
+// server recognised the format (crates/agens-server/src/vision.rs:126-135).  Here the decode runs on the host next to
+// the PNG / PPM readers: one or three components, any 1x / 2x sampling factors (4:4:4, 4:2:2, 4:4:0, 4:2:0), restart
+// intervals, JFIF YCbCr or Adobe RGB colour.  Progressive, arithmetic-coded, 12-bit and CMYK files are refused with a
+// message.  Chroma is upsampled with the triangle filter common decoders use by default, so results stay within a
+// few levels of theirs.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#define B2H_API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+struct Huff {
+  // canonical code tables: for code length l (1..16) the smallest code, the largest code and the index of its first symbol
+  int mincode[17], maxcode[18], valptr[17];
+  uint8_t vals[256];
+  uint8_t look_len[256], look_sym[256];      // codes of up to 8 bits resolved by one table look-up
+  bool present = false;
+};
+
+struct Comp {
+  int id = 0, h = 1, v = 1, tq = 0, td = 0, ta = 0;
+  int bw = 0, bh = 0;                        // blocks per row / column (padded to whole MCUs)
+  int pred = 0;
+  std::vector<uint8_t> plane;                // bw * 8 x bh * 8 samples
+};
+
+struct Dec {
+  const uint8_t* p;
+  const uint8_t* end;
+  std::string err;
+  int W = 0, H = 0, ncomp = 0;
+  bool progressive = false, have_frame = false, adobe = false;
+  int adobe_transform = -1;
+  uint16_t qt[4][64];
+  bool qt_ok[4] = {false, false, false, false};
+  Huff dc[4], ac[4];
+  Comp comp[3];
+  int restart = 0;
+  int hmax = 1, vmax = 1;
+  // bit reader
+  uint32_t acc = 0;
+  int nbits = 0;
+  bool hit_marker = false;
+};
+
+const uint8_t kZigzag[64] = {0,  1,  8,  16, 9,  2,  3,  10, 17, 24, 32, 25, 18, 11, 4,  5,  12, 19, 26, 33, 40, 48,
+                             41, 34, 27, 20, 13, 6,  7,  14, 21, 28, 35, 42, 49, 56, 57, 50, 43, 36, 29, 22, 15, 23,
+                             30, 37, 44, 51, 58, 59, 52, 45, 38, 31, 39, 46, 53, 60, 61, 54, 47, 55, 62, 63};
+
+bool fail(Dec& d, const char* m) {
+  if (d.err.empty()) d.err = m;
+  return false;
+}
+
+int u16(const uint8_t* q) { return (q[0] << 8) | q[1]; }
+
+bool build_huff(Dec& d, Huff& h, const uint8_t* counts, const uint8_t* vals, int nvals) {
+  int code = 0, k = 0;
+  for (int l = 1; l <= 16; ++l) {
+    h.valptr[l] = k;
+    h.mincode[l] = code;
+    k += counts[l - 1];
+    code += counts[l - 1];
+    h.maxcode[l] = counts[l - 1] ? code - 1 : -1;
+    if (code > (1 << l)) return fail(d, "jpeg: bad Huffman table");
+    code <<= 1;
+  }
+  h.maxcode[17] = 0x7fffffff;
+  if (k != nvals || nvals > 256) return fail(d, "jpeg: bad Huffman table");
+  std::memcpy(h.vals, vals, nvals);
+  std::memset(h.look_len, 0, sizeof h.look_len);
+  code = 0;
+  k = 0;
+  for (int l = 1; l <= 8; ++l) {
+    for (int i = 0; i < counts[l - 1]; ++i, ++k, ++code) {
+      const int first = code << (8 - l), n = 1 << (8 - l);
+      for (int j = 0; j < n; ++j) { h.look_len[first + j] = (uint8_t)l; h.look_sym[first + j] = vals[k]; }
+    }
+    code <<= 1;
+  }
+  h.present = true;
+  return true;
+}
+
+// Entropy-coded bytes: 0xFF 0x00 is a data byte 0xFF; any other marker ends the segment (zeros are fed from then on).
+void fill(Dec& d) {
+  while (d.nbits <= 24) {
+    uint32_t b = 0;
+    if (!d.hit_marker && d.p < d.end) {
+      b = *d.p;
+      if (b == 0xFF) {
+        if (d.p + 1 < d.end && d.p[1] == 0x00) {
+          d.p += 2;
+        } else {
+          d.hit_marker = true;
+          b = 0;
+        }
+      } else {
+        ++d.p;
+      }
+    }
+    d.acc |= b << (24 - d.nbits);
+    d.nbits += 8;
+  }
+}
+int get_bits(Dec& d, int n) {
+  if (n == 0) return 0;
+  if (d.nbits < n) fill(d);
+  const int v = (int)(d.acc >> (32 - n));
+  d.acc <<= n;
+  d.nbits -= n;
+  return v;
+}
+int decode_sym(Dec& d, const Huff& h) {
+  if (d.nbits < 16) fill(d);
+  const int top = (int)(d.acc >> 24);
+  if (h.look_len[top]) {
+    const int l = h.look_len[top];
+    d.acc <<= l;
+    d.nbits -= l;
+    return h.look_sym[top];
+  }
+  int code = (int)(d.acc >> 23), l = 9;          // first nine bits
+  for (; l <= 16; ++l) {
+    if (h.maxcode[l] >= 0 && code <= h.maxcode[l] && code >= h.mincode[l]) break;
+    code = (int)(d.acc >> (32 - (l + 1)));
+  }
+  if (l > 16) return -1;
+  d.acc <<= l;
+  d.nbits -= l;
+  return h.vals[h.valptr[l] + code - h.mincode[l]];
+}
+int extend(int v, int n) { return v < (1 << (n - 1)) ? v - (1 << n) + 1 : v; }
+
+// Inverse DCT of one dequantised block (separable, float), level shift and clamp.
+struct IdctTable {
+  float c[8][8];
+  IdctTable() {
+    for (int x = 0; x < 8; ++x)
+      for (int u = 0; u < 8; ++u) c[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979323846f / 16.f);
+  }
+};
+void idct_store(const int* coef, uint8_t* out, int stride) {
+  static const IdctTable table;              // initialised once, thread-safe
+  const float (*c)[8] = table.c;
+  float tmp[64];
+  for (int v = 0; v < 8; ++v)               // rows: over u
+    for (int x = 0; x < 8; ++x) {
+      float s = 0.f;
+      for (int u = 0; u < 8; ++u) s += c[x][u] * (float)coef[v * 8 + u];
+      tmp[v * 8 + x] = s;
+    }
+  for (int x = 0; x < 8; ++x)               // columns: over v
+    for (int y = 0; y < 8; ++y) {
+      float s = 0.f;
+      for (int v = 0; v < 8; ++v) s += c[y][v] * tmp[v * 8 + x];
+      const int q = (int)std::lrintf(s + 128.f);
+      out[y * stride + x] = (uint8_t)std::min(255, std::max(0, q));
+    }
+}
+
+bool decode_block(Dec& d, Comp& cp, uint8_t* out, int stride) {
+  int coef[64];
+  std::memset(coef, 0, sizeof coef);
+  const Huff& hd = d.dc[cp.td];
+  const Huff& ha = d.ac[cp.ta];
+  const uint16_t* q = d.qt[cp.tq];
+  int t = decode_sym(d, hd);
+  if (t < 0 || t > 11) return fail(d, "jpeg: bad DC code");
+  const int diff = t ? extend(get_bits(d, t), t) : 0;
+  cp.pred += diff;
+  coef[0] = cp.pred * q[0];
+  for (int k = 1; k < 64;) {
+    const int rs = decode_sym(d, ha);
+    if (rs < 0) return fail(d, "jpeg: bad AC code");
+    const int r = rs >> 4, s = rs & 15;
+    if (s == 0) {
+      if (r != 15) break;                  // end of block
+      k += 16;
+      continue;
+    }
+    k += r;
+    if (k > 63) return fail(d, "jpeg: coefficient index out of range");
+    coef[kZigzag[k]] = extend(get_bits(d, s), s) * q[k];
+    ++k;
+  }
+  idct_store(coef, out, stride);
+  return true;
+}
+
+bool parse_headers(Dec& d, bool stop_at_frame) {
+  if (d.end - d.p < 4 || d.p[0] != 0xFF || d.p[1] != 0xD8) return fail(d, "jpeg: no SOI marker");
+  d.p += 2;
+  while (d.p + 4 <= d.end) {
+    if (d.p[0] != 0xFF) return fail(d, "jpeg: marker expected");
+    while (d.p + 1 < d.end && d.p[1] == 0xFF) ++d.p;     // fill bytes
+    const int m = d.p[1];
+    d.p += 2;
+    if (m == 0xD9) return fail(d, "jpeg: no scan before EOI");
+    if (m >= 0xD0 && m <= 0xD7) continue;
+    if (d.p + 2 > d.end) break;
+    const int len = u16(d.p);
+    if (len < 2 || d.p + len > d.end) return fail(d, "jpeg: truncated segment");
+    const uint8_t* s = d.p + 2;
+    const uint8_t* se = d.p + len;
+    if (m == 0xC0 || m == 0xC1 || m == 0xC2) {
+      if (se - s < 6) return fail(d, "jpeg: bad frame header");
+      if (s[0] != 8) return fail(d, "jpeg: only 8-bit samples are supported");
+      d.progressive = m == 0xC2;
+      d.H = u16(s + 1);
+      d.W = u16(s + 3);
+      d.ncomp = s[5];
+      if (d.W <= 0 || d.H <= 0) return fail(d, "jpeg: empty image");
+      if (d.ncomp != 1 && d.ncomp != 3) return fail(d, "jpeg: only grey and three-component images are supported");
+      if (se - s < 6 + 3 * d.ncomp) return fail(d, "jpeg: bad frame header");
+      for (int i = 0; i < d.ncomp; ++i) {
+        Comp& c = d.comp[i];
+        c.id = s[6 + 3 * i];
+        c.h = s[7 + 3 * i] >> 4;
+        c.v = s[7 + 3 * i] & 15;
+        c.tq = s[8 + 3 * i] & 3;
+        if (c.h < 1 || c.h > 2 || c.v < 1 || c.v > 2) return fail(d, "jpeg: sampling factors other than 1 and 2 are not supported");
+        d.hmax = std::max(d.hmax, c.h);
+        d.vmax = std::max(d.vmax, c.v);
+      }
+      d.have_frame = true;
+      if (stop_at_frame) return true;
+      if (d.progressive) return fail(d, "jpeg: progressive files are not supported (send baseline JPEG or PNG)");
+    } else if (m == 0xC3 || (m >= 0xC5 && m <= 0xCF && m != 0xC4 && m != 0xC8 && m != 0xCC)) {
+      return fail(d, "jpeg: lossless, hierarchical and arithmetic-coded files are not supported");
+    } else if (m == 0xC4) {
+      while (s < se) {
+        if (se - s < 17) return fail(d, "jpeg: bad Huffman segment");
+        const int tc = s[0] >> 4, th = s[0] & 15;
+        if (tc > 1 || th > 3) return fail(d, "jpeg: bad Huffman table id");
+        int n = 0;
+        for (int i = 0; i < 16; ++i) n += s[1 + i];
+        if (se - s < 17 + n) return fail(d, "jpeg: bad Huffman segment");
+        if (!build_huff(d, tc ? d.ac[th] : d.dc[th], s + 1, s + 17, n)) return false;
+        s += 17 + n;
+      }
+    } else if (m == 0xDB) {
+      while (s < se) {
+        const int pq = s[0] >> 4, tq = s[0] & 15;
+        if (tq > 3) return fail(d, "jpeg: bad quantisation table id");
+        const int need = 1 + (pq ? 128 : 64);
+        if (se - s < need) return fail(d, "jpeg: bad quantisation segment");
+        for (int i = 0; i < 64; ++i) d.qt[tq][i] = pq ? (uint16_t)u16(s + 1 + 2 * i) : s[1 + i];
+        d.qt_ok[tq] = true;
+        s += need;
+      }
+    } else if (m == 0xDD) {
+      if (se - s < 2) return fail(d, "jpeg: bad restart interval");
+      d.restart = u16(s);
+    } else if (m == 0xEE) {
+      if (se - s >= 12 && std::memcmp(s, "Adobe", 5) == 0) { d.adobe = true; d.adobe_transform = s[11]; }
+    } else if (m == 0xDA) {
+      if (!d.have_frame) return fail(d, "jpeg: scan before frame header");
+      const int ns = s[0];
+      if (ns != d.ncomp || se - s < 1 + 2 * ns + 3) return fail(d, "jpeg: only one interleaved scan is supported");
+      for (int i = 0; i < ns; ++i) {
+        const int cid = s[1 + 2 * i];
+        Comp* c = nullptr;
+        for (int j = 0; j < d.ncomp; ++j)
+          if (d.comp[j].id == cid) c = &d.comp[j];
+        if (!c) return fail(d, "jpeg: scan names an unknown component");
+        c->td = s[2 + 2 * i] >> 4;
+        c->ta = s[2 + 2 * i] & 15;
+        if (c->td > 3 || c->ta > 3 || !d.dc[c->td].present || !d.ac[c->ta].present || !d.qt_ok[c->tq])
+          return fail(d, "jpeg: scan uses a table that was not defined");
+      }
+      d.p += len;
+      return true;                          // entropy-coded data follows
+    }
+    d.p += len;
+  }
+  return fail(d, "jpeg: no scan found");
+}
+
+bool decode_scan(Dec& d) {
+  const int mcu_w = 8 * d.hmax, mcu_h = 8 * d.vmax;
+  const int mx = (d.W + mcu_w - 1) / mcu_w, my = (d.H + mcu_h - 1) / mcu_h;
+  for (int i = 0; i < d.ncomp; ++i) {
+    Comp& c = d.comp[i];
+    if (d.ncomp == 1) { c.h = c.v = 1; }
+    c.bw = mx * c.h;
+    c.bh = my * c.v;
+    c.plane.assign((size_t)c.bw * 8 * c.bh * 8, 0);
+    c.pred = 0;
+  }
+  if (d.ncomp == 1) { d.hmax = d.vmax = 1; }
+  const int mx1 = d.ncomp == 1 ? (d.W + 7) / 8 : mx, my1 = d.ncomp == 1 ? (d.H + 7) / 8 : my;
+  if (d.ncomp == 1) {
+    Comp& c = d.comp[0];
+    c.bw = mx1; c.bh = my1;
+    c.plane.assign((size_t)c.bw * 8 * c.bh * 8, 0);
+  }
+  int countdown = d.restart, next_rst = 0;
+  for (int y = 0; y < my1; ++y)
+    for (int x = 0; x < mx1; ++x) {
+      if (d.restart && countdown == 0) {
+        // byte-align, expect RSTn
+        d.acc = 0; d.nbits = 0;
+        if (!d.hit_marker) {
+          while (d.p + 1 < d.end && !(d.p[0] == 0xFF && d.p[1] != 0x00 && d.p[1] != 0xFF)) ++d.p;   // skip padding
+        }
+        if (d.p + 1 < d.end && d.p[0] == 0xFF && d.p[1] == 0xD0 + next_rst) {
+          d.p += 2;
+        } else {
+          return fail(d, "jpeg: restart marker missing");
+        }
+        d.hit_marker = false;
+        next_rst = (next_rst + 1) & 7;
+        countdown = d.restart;
+        for (int i = 0; i < d.ncomp; ++i) d.comp[i].pred = 0;
+      }
+      for (int i = 0; i < d.ncomp; ++i) {
+        Comp& c = d.comp[i];
+        const int stride = c.bw * 8;
+        for (int by = 0; by < c.v; ++by)
+          for (int bx = 0; bx < c.h; ++bx) {
+            uint8_t* out = c.plane.data() + ((size_t)(y * c.v + by) * 8) * stride + (size_t)(x * c.h + bx) * 8;
+            if (!decode_block(d, c, out, stride)) return false;
+          }
+      }
+      if (d.restart) --countdown;
+    }
+  return true;
+}
+
+// Sample of a subsampled plane at full-resolution position (x, y): triangle filter (3/4, 1/4) along each halved axis,
+// edge samples replicated.
+inline float sample_up(const Comp& c, int x, int y, int hs, int vs, int W, int H) {
+  const int stride = c.bw * 8, pw = (W + hs - 1) / hs, ph = (H + vs - 1) / vs;     // the component's own size
+  auto at = [&](int xx, int yy) {
+    xx = std::min(std::max(xx, 0), pw - 1);
+    yy = std::min(std::max(yy, 0), ph - 1);
+    return (float)c.plane[(size_t)yy * stride + xx];
+  };
+  if (hs == 1 && vs == 1) return at(x, y);
+  int x0 = x, x1 = x, y0 = y, y1 = y;
+  float wx = 0.f, wy = 0.f;                  // weight of the second sample
+  if (hs == 2) { x0 = x >> 1; x1 = (x & 1) ? x0 + 1 : x0 - 1; wx = 0.25f; }
+  if (vs == 2) { y0 = y >> 1; y1 = (y & 1) ? y0 + 1 : y0 - 1; wy = 0.25f; }
+  const float a = at(x0, y0) * (1.f - wx) + at(x1, y0) * wx;
+  const float b = at(x0, y1) * (1.f - wx) + at(x1, y1) * wx;
+  return a * (1.f - wy) + b * wy;
+}
+
+inline uint8_t clamp8(float v) { return (uint8_t)std::min(255, std::max(0, (int)std::lrintf(v))); }
+
+void to_rgb(const Dec& d, uint8_t* rgb) {
+  if (d.ncomp == 1) {
+    const Comp& c = d.comp[0];
+    for (int y = 0; y < d.H; ++y)
+      for (int x = 0; x < d.W; ++x) {
+        const uint8_t g = c.plane[(size_t)y * c.bw * 8 + x];
+        uint8_t* o = rgb + ((size_t)y * d.W + x) * 3;
+        o[0] = o[1] = o[2] = g;
+      }
+    return;
+  }
+  // three components: YCbCr unless an Adobe segment says the data is RGB (transform 0)
+  const bool ycc = !(d.adobe && d.adobe_transform == 0);
+  for (int y = 0; y < d.H; ++y)
+    for (int x = 0; x < d.W; ++x) {
+      float v[3];
+      for (int i = 0; i < 3; ++i) {
+        const Comp& c = d.comp[i];
+        v[i] = sample_up(c, x, y, d.hmax / c.h, d.vmax / c.v, d.W, d.H);
+      }
+      uint8_t* o = rgb + ((size_t)y * d.W + x) * 3;
+      if (ycc) {
+        const float Y = v[0], cb = v[1] - 128.f, cr = v[2] - 128.f;
+        o[0] = clamp8(Y + 1.402f * cr);
+        o[1] = clamp8(Y - 0.344136f * cb - 0.714136f * cr);
+        o[2] = clamp8(Y + 1.772f * cb);
+      } else {
+        o[0] = clamp8(v[0]); o[1] = clamp8(v[1]); o[2] = clamp8(v[2]);
+      }
+    }
+}
+
+thread_local std::string g_jpeg_err;
+
+}  // namespace
+
+// Height, width and component count of a JPEG file; 0 on success.
+B2H_API int b2h_jpeg_info(const uint8_t* data, long n, int* h, int* w, int* comps) {
+  Dec d;
+  d.p = data;
+  d.end = data + n;
+  if (!parse_headers(d, true)) { g_jpeg_err = d.err; return 1; }
+  *h = d.H; *w = d.W; *comps = d.ncomp;
+  return 0;
+}
+
+// Decodes into rgb (h * w * 3 bytes, sizes from b2h_jpeg_info); 0 on success, else b2h_jpeg_error() says why.
+B2H_API int b2h_jpeg_decode(const uint8_t* data, long n, uint8_t* rgb) {
+  Dec d;
+  d.p = data;
+  d.end = data + n;
+  if (!parse_headers(d, false) || !decode_scan(d)) { g_jpeg_err = d.err.empty() ? "jpeg: decode failed" : d.err; return 1; }
+  to_rgb(d, rgb);
+  return 0;
+}
+
+B2H_API const char* b2h_jpeg_error() { return g_jpeg_err.c_str(); }
