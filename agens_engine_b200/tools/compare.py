@@ -13,7 +13,12 @@ import torch
 
 
 def compare_logits(a_path: str, b_path: str) -> dict:
-    a, b = torch.load(a_path).double(), torch.load(b_path).double()
+    return logits_report(torch.load(a_path), torch.load(b_path))
+
+
+def logits_report(a: torch.Tensor, b: torch.Tensor) -> dict:
+    """Mean / max KL(a || b) of the softmax rows, top-1 agreement and the largest absolute difference."""
+    a, b = a.detach().double().cpu(), b.detach().double().cpu()
     a, b = a.reshape(-1, a.shape[-1]), b.reshape(-1, b.shape[-1])
     if a.shape != b.shape:
         raise ValueError(f"shapes differ: {tuple(a.shape)} vs {tuple(b.shape)}")

@@ -42,11 +42,16 @@ def test_no_alloc_entry_matches_regular_entry_twice():
         y = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
         status = torch.full((1,), -1, dtype=torch.int32, device=DEV)
         before = torch.cuda.memory_allocated()
+        # the driver's own count of free device memory (sees cudaMalloc by anyone in the process, not only PyTorch's
+        # allocator); checked on the second call, after the first one loaded the kernel image and resolved the symbol
+        free_before = torch.cuda.mem_get_info()[0]
         rc = fn(lin.wq.data_ptr(), n, k, bits, 128, ks, x.data_ptr(), x.stride(0), m, y.data_ptr(), y.stride(0),
                 status.data_ptr(), stream, err)
         torch.cuda.synchronize()
         assert rc == 0, err.value
         assert torch.cuda.memory_allocated() == before
+        if call > 0:
+            assert torch.cuda.mem_get_info()[0] >= free_before, "device memory was taken during the call"
         assert int(status.item()) == 0
         assert torch.allclose(y.float(), ref.float(), rtol=2e-2, atol=1e-3), call
         assert torch.equal(y, ref), call               # same kernel, same schedule: identical bits

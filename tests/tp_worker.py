@@ -86,6 +86,21 @@ def main():
         allt = [None] * world
         dist.all_gather_object(allt, toks.tolist())
         assert all(t == allt[0] for t in allt)          # every rank produced the same tokens
+        # teacher-forced logits gate (the reference's TP check: next-token agreement with one GPU and mean KL,
+        # README.md:267-272): the same 16 continuation tokens through both models, row by row
+        from agens_engine_b200.tools.compare import logits_report
+        forced = toks.tolist()
+        m.truncate(0, len(prompt))
+        rows_tp = torch.stack([m.forward_rows([t], [0], want_logits=True)[1][0] for t in forced])
+        all_rows = [None] * world
+        dist.all_gather_object(all_rows, rows_tp.cpu())
+        assert all(torch.equal(x, all_rows[0]) for x in all_rows)      # replicated logits: bitwise equal on every rank
+        if rank == 0:
+            r.truncate(0, len(prompt))
+            rows_1 = torch.stack([r.forward_rows([t], [0], want_logits=True)[1][0] for t in forced])
+            rep = logits_report(rows_1, rows_tp)
+            assert rep["top1_agreement"] >= 0.9 and rep["mean_kl"] < 2e-2, rep
+            print(f"rank 0: logits gate {rep}", flush=True)
         # the same shards loaded from a checkpoint directory give the same tokens
         import tempfile
         from agens_engine_b200.utils import checkpoint as K
