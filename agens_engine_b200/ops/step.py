@@ -54,7 +54,7 @@ class StepArgs(C.Structure):
         ("inv_freq", C.c_void_p),
         ("split_keys", C.c_int), ("max_splits", C.c_int), ("scale_log2", C.c_float),
         ("slot_seq", C.c_void_p), ("last_ids", C.c_void_p), ("seq_len", C.c_void_p),
-        ("part", C.c_void_p), ("tile_scratch", C.c_void_p), ("xq", C.c_void_p), ("xg", C.c_void_p), ("psq", C.c_void_p),
+        ("part", C.c_void_p), ("tile_scratch", C.c_void_p), ("xq", C.c_void_p), ("xg", C.c_void_p), ("psq", C.c_void_p), ("attn_ctr", C.c_void_p),
         ("h", C.c_void_p), ("q", C.c_void_p), ("attn", C.c_void_p), ("act", C.c_void_p),
         ("part_o", C.c_void_p), ("part_ml", C.c_void_p),
         ("amax_val", C.c_void_p), ("amax_idx", C.c_void_p),
@@ -179,6 +179,7 @@ class StepRunner:
         self.xq = torch.zeros((kmax // 128) * 4096, dtype=torch.uint8, device=dev)
         self.xg = f32((kmax // 64) * 16 * 2).zero_()
         self.psq = f32(MAX_ROWS * (cfg.d_model // 128)).zero_()
+        self.attn_ctr = torch.zeros(max(len(model.layers), 1), dtype=torch.int32, device=dev)
         self.amax_val = f32(self.ncta, MAX_ROWS)
         self.amax_idx = torch.empty(self.ncta, MAX_ROWS, dtype=torch.int32, device=dev)
         self.sync = torch.zeros(64, dtype=torch.int32, device=dev)
@@ -223,6 +224,7 @@ class StepRunner:
         a.slice_k = geo.slice_k
         a.tile_scratch = ptr(self.tile_scratch)
         a.xq, a.xg, a.psq = ptr(self.xq), ptr(self.xg), ptr(self.psq)
+        a.attn_ctr = ptr(self.attn_ctr)
         a.final_norm, a.embed = ptr(md.final_norm), ptr(md.embed)
         a.vocab, a.d_model, a.hq, a.hkv, a.ffn = md.embed.shape[0], cfg.d_model, cfg.n_heads, cfg.n_kv_heads, cfg.ffn
         a.eps = cfg.rms_eps
@@ -270,6 +272,7 @@ class StepRunner:
     def reset_sync(self):
         """After a failed step (status word set): put the barrier counters back to zero on this rank."""
         self.sync.zero_()
+        self.attn_ctr.zero_()
         if self.region is not None:
             lib = _lib.cuda_lib()
             with torch.cuda.device(self.model.dev):

@@ -66,6 +66,7 @@ struct StepArgs {
   uint8_t* xq;               // staged activations of the next linear: [k / 128][token sets * 1024] bytes (fixed-point limbs)
   float2* xg;                // their group scalars: [k / group][4 * token sets] (scale, scale * integer sum)
   float* psq;                // sums of squares of the residual stream: [rows][d_model / 128]
+  int* attn_ctr;             // [n_layers] work counters of the attention stages (zero between launches)
   bf16* h;                   // residual stream [rows][d_model]
   bf16* q;                   // [rows][hq * 128]
   bf16* attn;                // [rows][hq * 128]

@@ -46,11 +46,12 @@ constexpr int SM_BARS = 0;
 constexpr int SM_MISC = 2048;
 constexpr int SM_MISC_BYTES = 3584;
 constexpr int SM_WORK = SM_MISC + SM_MISC_BYTES;
-// Warps of a CTA that run attention items, each with two 8 KB K/V page stages: three for steps of up to four rows,
-// six beyond (the work area is that large anyway, and such steps have more items)
-constexpr int kAttnStages = 2;
-__host__ __device__ __forceinline__ int attn_warps(int rows) { return rows > 4 ? 6 : 3; }
-__host__ __device__ __forceinline__ int attn_bytes(int rows) { return attn_warps(rows) * kAttnStages * 2 * kPage * 128 * 2; }
+// Warps of a CTA that run attention items and their 8 KB K/V page stages: three warps with two stages each for steps
+// of up to four rows; beyond, twelve warps with one stage each (the work area is that large anyway): a page costs a
+// warp about 2 us of dependent tensor-core latency, so more warps in flight beat a deeper pipeline per warp.
+__host__ __device__ __forceinline__ int attn_warps(int rows) { return rows > 4 ? 12 : 3; }
+__host__ __device__ __forceinline__ int attn_stages(int rows) { return rows > 4 ? 1 : 2; }
+__host__ __device__ __forceinline__ int attn_bytes(int rows) { return attn_warps(rows) * attn_stages(rows) * 2 * kPage * 128 * 2; }
 constexpr int kTileFloats = kStepWarps * 2 * kStepMaxRows * 32;      // floats of one CTA's tiles in global memory
 static_assert(kStepWarps * kRingBars * 8 <= SM_MISC, "mbarriers");
 static_assert(SM_TOTAL <= 227 * 1024, "shared memory of one CTA");
@@ -80,8 +81,8 @@ static_assert(SM_WORK + (kStepSliceK / 128) * (2048 + 2 * 8 * 8) + kStepWarps * 
               "an eight-row step still has three blocks per warp in flight");
 static_assert(SM_WORK + (kStepSliceK / 256) * (4096 + 2 * 16 * 8) + kStepWarps * 2560 * 3 + 128 <= SM_TOTAL,
               "a sixteen-row step still has three blocks per warp in flight");
-static_assert(SM_WORK + 6 * kAttnStages * 2 * kPage * 128 * 2 + kStepWarps * 2560 * 3 + 128 <= SM_TOTAL,
-              "six attention warps leave three blocks per warp in flight");
+static_assert(SM_WORK + 12 * 1 * 2 * kPage * 128 * 2 + kStepWarps * 2560 * 3 + 128 <= SM_TOTAL,
+              "twelve attention warps leave three blocks per warp in flight");
 
 // misc area (floats): [0,16) inv_rms, [16,256) per-warp sums, [256,496) argmax values, [496,736) argmax indices,
 // [736,800) row description (ids, pos, seq, rope position), [800,832) ring progress published to the producer warp,
@@ -988,16 +989,36 @@ __device__ __noinline__ void fin_swiglu(const StepArgs& a, const StepLinear* Lg,
   }
 }
 
-// One attention work item (query group, kv head, 16-row tile, kv split) on one warp; the arithmetic of
+// One attention work item (query group, kv head, 16-row tile, run of `spi` consecutive kv splits) on one warp: the
+// pages of the run stream through one pipeline and the query fragments are loaded once, while every split still gets
+// its own partial (accumulators restart at each split boundary), so the partials do not depend on the run length; the arithmetic of
 // attn_decode_kernel<128, false> (attn_decode.cu) with an ST-stage K/V ring in this warp's shared memory.
-template <int ST>
-__device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool, long item, int mt_max, uint8_t* wsm,
-                                          const int* row_pos, const int* row_seq) {
+// LOW8: every group of the step has at most eight (token, head) rows per KV head (plain decode rows with eight query
+// heads per KV head), so rows 8..15 of the MMA tile are padding.  Their query fragments, scores and output
+// accumulators are then not kept (zeros go in, the results are dropped): half the accumulator registers, which is what
+// keeps this stage free of local-memory spills; rows 0..7 see exactly the same MMA operations either way.
+template <bool LOW8>
+__device__ __forceinline__ void mma_rows(float (&d)[LOW8 ? 2 : 4], const uint32_t (&a4)[4], uint32_t b0, uint32_t b1) {
+  if (LOW8) {
+    float t[4] = {d[0], d[1], 0.f, 0.f};
+    mma_bf16_16816(t, a4, b0, b1);
+    d[0] = t[0]; d[1] = t[1];
+  } else {
+    float t[4] = {d[0], d[1], d[LOW8 ? 0 : 2], d[LOW8 ? 1 : 3]};
+    mma_bf16_16816(t, a4, b0, b1);
+    d[0] = t[0]; d[1] = t[1]; d[LOW8 ? 0 : 2] = t[2]; d[LOW8 ? 1 : 3] = t[3];
+  }
+}
+
+template <int ST, bool LOW8>
+__device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool, long item, int split0, int spi, int mt_max,
+                                          uint8_t* wsm, const int* row_pos, const int* row_seq) {
   constexpr int HD = 128, KS = HD / 16, NTO = HD / 8, ROWB = HD * 2, CPR = ROWB / 16, PAGE_B = kPage * ROWB;
+  constexpr int NR = LOW8 ? 1 : 2;           // row halves of the tile that are kept (rows g, g + 8)
+  constexpr int NA = LOW8 ? 2 : 4;           // accumulator registers per n-tile
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   const int gq = a.hq / a.hkv;
-  const int split = (int)(item % a.max_splits); item /= a.max_splits;
   const int mtile = (int)(item % mt_max); item /= mt_max;
   const int kvh = (int)(item % a.hkv); item /= a.hkv;
   const int grp = (int)item;
@@ -1006,16 +1027,17 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
   const int seq = row_seq[tok0];
   const int pos_first = row_pos[tok0];
   const int kv_len = row_pos[tok0 + cnt - 1] + 1;
-  const int k_begin = split * a.split_keys;
+  const int k_begin = split0 * a.split_keys;
   if (k_begin >= kv_len) return;
-  const int k_end = min(kv_len, k_begin + a.split_keys);
+  const int k_end = min(kv_len, k_begin + spi * a.split_keys);
   const int n_pg = (k_end - k_begin + kPage - 1) / kPage;
+  const int pps = a.split_keys / kPage;                      // pages per split
 
-  int rtok[2], rhead[2], rpos[2];
-  bool rvalid[2];
-  unsigned rmask[2];
+  int rtok[NR], rhead[NR], rpos[NR];
+  bool rvalid[NR];
+  unsigned rmask[NR];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < NR; ++i) {
     const int Rr = mtile * 16 + g + 8 * i;
     const int tl = Rr / gq;
     rvalid[i] = tl < cnt;
@@ -1027,9 +1049,13 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
   const uint32_t wsm_u = smem_u32(wsm);
   const int* bt = a.block_table + (size_t)seq * a.bt_ld;
 
+  // page numbers of the whole run up front (at most 16 splits x 4 pages): lane i holds pages i and i + 32, so that the
+  // page loop has no dependent global load in front of its copies
+  const int pg_lo = lane < n_pg ? bt[(k_begin / kPage) + lane] : 0;
+  const int pg_hi = lane + 32 < n_pg ? bt[(k_begin / kPage) + lane + 32] : 0;
   auto issue_page = [&](int pi) {
     const int stage = pi % ST;
-    int page = bt[(k_begin / kPage) + pi];
+    int page = pi < 32 ? __shfl_sync(0xffffffffu, pg_lo, pi) : (pi < 64 ? __shfl_sync(0xffffffffu, pg_hi, pi - 32) : bt[(k_begin / kPage) + pi]);
     if (page < 0 || page >= a.n_pages) { atomicExch(a.status, (int)B2_ERR_BOUNDS); page = 0; }
     const uint8_t* kp = reinterpret_cast<const uint8_t*>(kv_pool) + (((size_t)page * 2 + 0) * a.hkv + kvh) * PAGE_B;
     const uint8_t* vp = reinterpret_cast<const uint8_t*>(kv_pool) + (((size_t)page * 2 + 1) * a.hkv + kvh) * PAGE_B;
@@ -1048,40 +1074,56 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
     cp_async_commit();
   }
 
-  uint32_t qa[KS][4];
+  uint32_t qa[KS][2 * NR];                   // [ks][row half][k half]: A registers (a0, a2) of row g, (a1, a3) of row g + 8
 #pragma unroll
   for (int ks = 0; ks < KS; ++ks) {
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NR; ++i) {
       uint32_t v0 = 0u, v1 = 0u;
       if (rvalid[i]) {
         const bf16* qp = a.q + (size_t)rtok[i] * a.hq * HD + (size_t)rhead[i] * HD + ks * 16 + 2 * t;
         v0 = __ldcg(reinterpret_cast<const unsigned*>(qp));
         v1 = __ldcg(reinterpret_cast<const unsigned*>(qp + 8));
       }
-      qa[ks][i] = v0;
-      qa[ks][2 + i] = v1;
+      qa[ks][2 * i] = v0;
+      qa[ks][2 * i + 1] = v1;
     }
   }
-  float o[NTO][4];
+  float o[NTO][NA];
 #pragma unroll
   for (int n = 0; n < NTO; ++n)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o[n][i] = 0.f;
-  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    for (int i = 0; i < NA; ++i) o[n][i] = 0.f;
+  float mrow[NR], lrow[NR];
+#pragma unroll
+  for (int r = 0; r < NR; ++r) { mrow[r] = -INFINITY; lrow[r] = 0.f; }
 
+#ifdef B2_STEP_TRACE
+  long long ta_issue = 0, ta_wait = 0, ta_comp = 0;
+  const long long ta_begin = clock64();
+#endif
   for (int pi = 0; pi < n_pg; ++pi) {
+#ifdef B2_STEP_TRACE
+    const long long tq0 = clock64();
+#endif
     if (pi + ST - 1 < n_pg) issue_page(pi + ST - 1);
     cp_async_commit();
+#ifdef B2_STEP_TRACE
+    const long long tq1 = clock64();
+#endif
     cp_async_wait<ST - 1>();
     __syncwarp();
+#ifdef B2_STEP_TRACE
+    const long long tq2 = clock64();
+    ta_issue += tq1 - tq0; ta_wait += tq2 - tq1;
+#endif
     const int stage = pi % ST;
     const uint32_t ks_u = wsm_u + stage * 2 * PAGE_B, vs_u = ks_u + PAGE_B;
-    float s[2][4];
+    float s[2][NA];
 #pragma unroll
     for (int n = 0; n < 2; ++n)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
+      for (int i = 0; i < NA; ++i) s[n][i] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < KS; ++ks) {
       uint32_t b[4];
@@ -1089,15 +1131,18 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
       const int key = (j >> 1) * 8 + (lane & 7);
       const int cc = 2 * ks + (j & 1);
       ldsm_x4(ks_u + key * ROWB + ((cc ^ (key & 7)) << 4), b);
-      mma_bf16_16816(s[0], qa[ks], b[0], b[1]);
-      mma_bf16_16816(s[1], qa[ks], b[2], b[3]);
+      const uint32_t a4[4] = {qa[ks][0], LOW8 ? 0u : qa[ks][LOW8 ? 0 : 2], qa[ks][1], LOW8 ? 0u : qa[ks][LOW8 ? 1 : 3]};
+      mma_rows<LOW8>(s[0], a4, b[0], b[1]);
+      mma_rows<LOW8>(s[1], a4, b[2], b[3]);
     }
     const int kb = k_begin + pi * kPage;
-    float mx[2] = {-INFINITY, -INFINITY};
+    float mx[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) mx[r] = -INFINITY;
 #pragma unroll
     for (int n = 0; n < 2; ++n)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < NA; ++i) {
         const int r = i >> 1;
         const int key = kb + n * 8 + 2 * t + (i & 1);
         bool ok = key <= rpos[r];
@@ -1107,13 +1152,14 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
         mx[r] = fmaxf(mx[r], v);
       }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NR; ++r) {
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
       mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
     }
-    float corr[2], psum[2] = {0.f, 0.f};
+    float corr[NR], psum[NR];
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NR; ++r) {
+      psum[r] = 0.f;
       const float mnew = fmaxf(mrow[r], mx[r]);
       corr[r] = (mnew == -INFINITY) ? 1.f : exp2f(mrow[r] - mnew);
       mrow[r] = mnew;
@@ -1121,28 +1167,27 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
 #pragma unroll
     for (int n = 0; n < 2; ++n)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
+      for (int i = 0; i < NA; ++i) {
         const int r = i >> 1;
         const float p = (s[n][i] == -INFINITY) ? 0.f : exp2f(s[n][i] - mrow[r]);
         s[n][i] = p;
         psum[r] += p;
       }
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
+    for (int r = 0; r < NR; ++r) {
       psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 1);
       psum[r] += __shfl_xor_sync(0xffffffffu, psum[r], 2);
       lrow[r] = lrow[r] * corr[r] + psum[r];
     }
 #pragma unroll
-    for (int n = 0; n < NTO; ++n) {
-      o[n][0] *= corr[0]; o[n][1] *= corr[0];
-      o[n][2] *= corr[1]; o[n][3] *= corr[1];
-    }
+    for (int n = 0; n < NTO; ++n)
+#pragma unroll
+      for (int i = 0; i < NA; ++i) o[n][i] *= corr[i >> 1];
     uint32_t pa[4];
     pa[0] = pack_bf16(s[0][0], s[0][1]);
-    pa[1] = pack_bf16(s[0][2], s[0][3]);
+    pa[1] = LOW8 ? 0u : pack_bf16(s[0][LOW8 ? 0 : 2], s[0][LOW8 ? 1 : 3]);
     pa[2] = pack_bf16(s[1][0], s[1][1]);
-    pa[3] = pack_bf16(s[1][2], s[1][3]);
+    pa[3] = LOW8 ? 0u : pack_bf16(s[1][LOW8 ? 0 : 2], s[1][LOW8 ? 1 : 3]);
 #pragma unroll
     for (int nn = 0; nn < NTO / 2; ++nn) {
       uint32_t b[4];
@@ -1150,50 +1195,90 @@ __device__ __forceinline__ void attn_item(const StepArgs& a, const bf16* kv_pool
       const int key = (j & 1) * 8 + (lane & 7);
       const int cc = 2 * nn + (j >> 1);
       ldsm_x4_t(vs_u + key * ROWB + ((cc ^ (key & 7)) << 4), b);
-      mma_bf16_16816(o[2 * nn], pa, b[0], b[1]);
-      mma_bf16_16816(o[2 * nn + 1], pa, b[2], b[3]);
+      mma_rows<LOW8>(o[2 * nn], pa, b[0], b[1]);
+      mma_rows<LOW8>(o[2 * nn + 1], pa, b[2], b[3]);
     }
     __syncwarp();
+    // end of a split (or of the run): its partial goes out and the accumulators restart
+    if ((pi + 1) % pps == 0 || pi + 1 == n_pg) {
+      const int split = split0 + pi / pps;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        if (!rvalid[r]) continue;
+        float* po = a.part_o + (((size_t)rtok[r] * a.hq + rhead[r]) * a.max_splits + split) * HD;
+#pragma unroll
+        for (int n = 0; n < NTO; ++n)
+          *reinterpret_cast<float2*>(po + n * 8 + 2 * t) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
+        if (t == 0) {
+          float* pm = a.part_ml + (((size_t)rtok[r] * a.hq + rhead[r]) * a.max_splits + split) * 2;
+          pm[0] = mrow[r];
+          pm[1] = lrow[r];
+        }
+      }
+#pragma unroll
+      for (int n = 0; n < NTO; ++n)
+#pragma unroll
+        for (int i = 0; i < NA; ++i) o[n][i] = 0.f;
+#pragma unroll
+      for (int r = 0; r < NR; ++r) { mrow[r] = -INFINITY; lrow[r] = 0.f; }
+    }
+#ifdef B2_STEP_TRACE
+    ta_comp += clock64() - tq2;
+#endif
   }
   cp_async_wait<0>();
   __syncwarp();
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (!rvalid[r]) continue;
-    float* po = a.part_o + (((size_t)rtok[r] * a.hq + rhead[r]) * a.max_splits + split) * HD;
-#pragma unroll
-    for (int n = 0; n < NTO; ++n)
-      *reinterpret_cast<float2*>(po + n * 8 + 2 * t) = make_float2(o[n][2 * r], o[n][2 * r + 1]);
-    if (t == 0) {
-      float* pm = a.part_ml + (((size_t)rtok[r] * a.hq + rhead[r]) * a.max_splits + split) * 2;
-      pm[0] = mrow[r];
-      pm[1] = lrow[r];
-    }
+#ifdef B2_STEP_TRACE
+  if (a.trace && blockIdx.x == 0 && lane == 0) {
+    unsigned long long* tr = a.trace + 200000 + (threadIdx.x >> 5) * 8;
+    tr[0] += (unsigned long long)ta_issue; tr[1] += (unsigned long long)ta_wait; tr[2] += (unsigned long long)ta_comp;
+    tr[3] += (unsigned long long)n_pg; tr[4] += 1ull; tr[5] += (unsigned long long)(clock64() - ta_begin);
   }
+#endif
 }
 
-template <int ST>
-__device__ __noinline__ void attn_phase(const StepArgs& a, const bf16* kv_pool, uint8_t* smem, const int* row_pos,
-                                           const int* row_seq) {
+template <int ST, bool LOW8>
+__device__ __noinline__ void attn_phase_v(const StepArgs& a, const bf16* kv_pool, uint8_t* smem, const int* row_pos,
+                                          const int* row_seq, int max_pos, int max_cnt, int* ctr) {
   const int warp = threadIdx.x >> 5;
   const int n_warps = attn_warps(a.n_rows);
   if (warp >= n_warps) return;
   const int gq = a.hq / a.hkv;
-  // splits that any row of this step can reach, and 16-row tiles that the largest group needs (one for decode rows)
-  int max_pos = 0, max_cnt = 1;
-  for (int i = 0; i < a.n_rows; ++i) max_pos = max(max_pos, row_pos[i]);
-  for (int i = 0; i < a.n_groups; ++i) max_cnt = max(max_cnt, a.grp_cnt[i]);
   const int mt_max = (max_cnt * gq + 15) / 16;
   const int n_sp = min(a.max_splits, max_pos / a.split_keys + 1);
   const long per_grp = (long)a.hkv * mt_max;
-  const long items = (long)a.n_groups * per_grp * n_sp;
+  // An item sets up once (row description, page lookups, query fragments: a chain of a few microseconds), so long
+  // contexts give an item a run of consecutive splits: about four items per attention warp of the grid, at most 16 splits.
+  const long slots = (long)gridDim.x * n_warps;
+  const long all_splits = (long)a.n_groups * per_grp * n_sp;
+  int spi = (int)min(16l, max(1l, all_splits / (4 * slots)));
+  const int n_run = (n_sp + spi - 1) / spi;
+  const long items = (long)a.n_groups * per_grp * n_run;
   uint8_t* wsm = smem + SM_WORK + (size_t)warp * ST * 2 * kPage * 128 * 2;
-  for (long it = (long)warp * gridDim.x + blockIdx.x; it < items; it += (long)gridDim.x * n_warps) {
-    // item order: split fastest, so that the items of one (group, head) spread over the CTAs
-    const long outer = it / n_sp;
-    const int split = (int)(it - outer * n_sp);
-    attn_item<ST>(a, kv_pool, outer * a.max_splits + split, mt_max, wsm, row_pos, row_seq);
+  // Items are handed out by a counter (one per layer, back at zero when the kernel ends): which warp computes an item
+  // does not change its result, and a warp that drew short items simply draws more.
+  for (;;) {
+    long it = 0;
+    if ((threadIdx.x & 31) == 0) it = (long)atomicAdd(ctr, 1);
+    it = __shfl_sync(0xffffffffu, it, 0);
+    if (it >= items) break;
+    // item order: run fastest, so that the items of one (group, head) spread over the CTAs
+    const long outer = it / n_run;
+    const int run = (int)(it - outer * n_run);
+    attn_item<ST, LOW8>(a, kv_pool, outer, run * spi, min(spi, n_sp - run * spi), mt_max, wsm, row_pos, row_seq);
   }
+}
+
+template <int ST>
+__device__ __forceinline__ void attn_phase(const StepArgs& a, const bf16* kv_pool, uint8_t* smem, const int* row_pos,
+                                           const int* row_seq, int* ctr) {
+  // splits that any row of this step can reach, and rows of the largest group (one for plain decode rows)
+  int max_pos = 0, max_cnt = 1;
+  for (int i = 0; i < a.n_rows; ++i) max_pos = max(max_pos, row_pos[i]);
+  for (int i = 0; i < a.n_groups; ++i) max_cnt = max(max_cnt, a.grp_cnt[i]);
+  // plain decode rows with at most eight query heads per KV head: the upper half of every 16-row tile is padding
+  if (max_cnt * (a.hq / a.hkv) <= 8) attn_phase_v<ST, true>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
+  else attn_phase_v<ST, false>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
 }
 
 // Merge of the attention splits of every (row, q head): one warp per item, lane = four output dimensions; the
@@ -1372,8 +1457,9 @@ __global__ void __launch_bounds__(kStepBlock, 1) step_kernel(const __grid_consta
     grid_sync(a, ss);
     fin_qkv(a, ly, row_pos, row_seq, row_rope);
     grid_sync(a, ss);
-    attn_phase<kAttnStages>(a, ly->kv_pool, smem, row_pos, row_seq);
+    attn_phase<(NS == 1 ? 2 : 1)>(a, ly->kv_pool, smem, row_pos, row_seq, a.attn_ctr + l);
     grid_sync(a, ss);
+    if (cta == 0 && tid == 0) a.attn_ctr[l] = 0;          // every CTA is past its last draw: ready for the next launch
     fin_merge(a, row_pos, lay, ly->o.group);
     grid_sync(a, ss);
     gemv_phase<NS>(a, 4 * l + 1, lay, &ring, tp ? a.x_off[0] : -1, &failed);
