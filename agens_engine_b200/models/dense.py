@@ -55,8 +55,8 @@ class DenseModel:
         self.prefill_split = 256                       # KV split size of prefill attention
         self.prefill_mm = os.environ.get("B200E_PREFILL_MM", "1") == "1"
         # Steps of up to sixteen rows can run as ONE persistent kernel (ops/step.py).  Measured on the 32B model (one
-        # GPU, ms per step, step kernel against per-op path): sixteen rows 14.9 / 21.1, twelve 13.7 / 20.0, eight
-        # 11.4 / 30.9, four 10.2 / 12.1, one 9.5 / 7.8.  Mode "auto" (default) therefore uses it for three to sixteen
+        # GPU, ms per step, step kernel against per-op path): sixteen rows 14.6 / 21.1, twelve 13.9 / 20.0, eight
+        # 11.8 / 30.9, four 10.5 / 12.1, one 9.9 / 7.8.  Mode "auto" (default) therefore uses it for three to sixteen
         # rows, "on" (B200E_STEP=1, or a serving loop that pins one kernel family) for every step of up to sixteen rows,
         # "off" never.  It keeps a second copy of the quantised weights in its own layout, built on first use.
         env = os.environ.get("B200E_STEP", "auto")

@@ -46,12 +46,12 @@ constexpr int SM_BARS = 0;
 constexpr int SM_MISC = 2048;
 constexpr int SM_MISC_BYTES = 3584;
 constexpr int SM_WORK = SM_MISC + SM_MISC_BYTES;
-// Warps of a CTA that run attention items and their 8 KB K/V page stages: three warps with two stages each for steps
-// of up to four rows; beyond, twelve warps with one stage each (the work area is that large anyway): a page costs a
-// warp about 2 us of dependent tensor-core latency, so more warps in flight beat a deeper pipeline per warp.
-__host__ __device__ __forceinline__ int attn_warps(int rows) { return rows > 4 ? 12 : 3; }
-__host__ __device__ __forceinline__ int attn_stages(int rows) { return rows > 4 ? 1 : 2; }
-__host__ __device__ __forceinline__ int attn_bytes(int rows) { return attn_warps(rows) * attn_stages(rows) * 2 * kPage * 128 * 2; }
+// Warps of a CTA that run attention items and their 8 KB K/V page stages.  Base shape: three warps (six beyond four
+// rows: the work area is that large anyway) with two stages each.  When the step has more split items than base warps
+// in the grid, twice the warps run with one stage each in the same shared memory: a page costs a warp about 2 us of
+// dependent tensor-core latency, so more warps in flight then beat a deeper pipeline per warp.
+__host__ __device__ __forceinline__ int attn_warps(int rows) { return rows > 4 ? 6 : 3; }
+__host__ __device__ __forceinline__ int attn_bytes(int rows) { return attn_warps(rows) * 2 * 2 * kPage * 128 * 2; }
 constexpr int kTileFloats = kStepWarps * 2 * kStepMaxRows * 32;      // floats of one CTA's tiles in global memory
 static_assert(kStepWarps * kRingBars * 8 <= SM_MISC, "mbarriers");
 static_assert(SM_TOTAL <= 227 * 1024, "shared memory of one CTA");
@@ -81,8 +81,8 @@ static_assert(SM_WORK + (kStepSliceK / 128) * (2048 + 2 * 8 * 8) + kStepWarps * 
               "an eight-row step still has three blocks per warp in flight");
 static_assert(SM_WORK + (kStepSliceK / 256) * (4096 + 2 * 16 * 8) + kStepWarps * 2560 * 3 + 128 <= SM_TOTAL,
               "a sixteen-row step still has three blocks per warp in flight");
-static_assert(SM_WORK + 12 * 1 * 2 * kPage * 128 * 2 + kStepWarps * 2560 * 3 + 128 <= SM_TOTAL,
-              "twelve attention warps leave three blocks per warp in flight");
+static_assert(SM_WORK + 6 * 2 * 2 * kPage * 128 * 2 + kStepWarps * 2560 * 3 + 128 <= SM_TOTAL,
+              "the attention stages leave three blocks per warp in flight");
 
 // misc area (floats): [0,16) inv_rms, [16,256) per-warp sums, [256,496) argmax values, [496,736) argmax indices,
 // [736,800) row description (ids, pos, seq, rope position), [800,832) ring progress published to the producer warp,
@@ -1241,7 +1241,7 @@ template <int ST, bool LOW8>
 __device__ __noinline__ void attn_phase_v(const StepArgs& a, const bf16* kv_pool, uint8_t* smem, const int* row_pos,
                                           const int* row_seq, int max_pos, int max_cnt, int* ctr) {
   const int warp = threadIdx.x >> 5;
-  const int n_warps = attn_warps(a.n_rows);
+  const int n_warps = attn_warps(a.n_rows) * (ST == 1 ? 2 : 1);
   if (warp >= n_warps) return;
   const int gq = a.hq / a.hkv;
   const int mt_max = (max_cnt * gq + 15) / 16;
@@ -1269,16 +1269,24 @@ __device__ __noinline__ void attn_phase_v(const StepArgs& a, const bf16* kv_pool
   }
 }
 
-template <int ST>
 __device__ __forceinline__ void attn_phase(const StepArgs& a, const bf16* kv_pool, uint8_t* smem, const int* row_pos,
                                            const int* row_seq, int* ctr) {
   // splits that any row of this step can reach, and rows of the largest group (one for plain decode rows)
   int max_pos = 0, max_cnt = 1;
   for (int i = 0; i < a.n_rows; ++i) max_pos = max(max_pos, row_pos[i]);
   for (int i = 0; i < a.n_groups; ++i) max_cnt = max(max_cnt, a.grp_cnt[i]);
+  const int gq = a.hq / a.hkv;
+  const long all_splits = (long)a.n_groups * a.hkv * ((max_cnt * gq + 15) / 16) * min(a.max_splits, max_pos / a.split_keys + 1);
+  const bool wide = all_splits > (long)gridDim.x * attn_warps(a.n_rows);      // more items than base warps: one stage, twice the warps
   // plain decode rows with at most eight query heads per KV head: the upper half of every 16-row tile is padding
-  if (max_cnt * (a.hq / a.hkv) <= 8) attn_phase_v<ST, true>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
-  else attn_phase_v<ST, false>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
+  const bool low8 = max_cnt * gq <= 8;
+  if (wide) {
+    if (low8) attn_phase_v<1, true>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
+    else attn_phase_v<1, false>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
+  } else {
+    if (low8) attn_phase_v<2, true>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
+    else attn_phase_v<2, false>(a, kv_pool, smem, row_pos, row_seq, max_pos, max_cnt, ctr);
+  }
 }
 
 // Merge of the attention splits of every (row, q head): one warp per item, lane = four output dimensions; the
@@ -1457,7 +1465,7 @@ __global__ void __launch_bounds__(kStepBlock, 1) step_kernel(const __grid_consta
     grid_sync(a, ss);
     fin_qkv(a, ly, row_pos, row_seq, row_rope);
     grid_sync(a, ss);
-    attn_phase<(NS == 1 ? 2 : 1)>(a, ly->kv_pool, smem, row_pos, row_seq, a.attn_ctr + l);
+    attn_phase(a, ly->kv_pool, smem, row_pos, row_seq, a.attn_ctr + l);
     grid_sync(a, ss);
     if (cta == 0 && tid == 0) a.attn_ctr[l] = 0;          // every CTA is past its last draw: ready for the next launch
     fin_merge(a, row_pos, lay, ly->o.group);
