@@ -123,7 +123,7 @@ def build_model(cfg: EngineConfig, **kw):
         mc = _model_config(cfg)
         free, _total = torch.cuda.mem_get_info(local)
         dep = B.plan_deployment(mc, cfg.budget_gib, kw["max_ctx"], cfg.max_batch, kw["max_seqs"], kw["prefill_chunk"], tp=world,
-                                gpu_free_gib=free / B.GiB, dual_layout=os.environ.get("B200E_STEP", "0") == "1")
+                                gpu_free_gib=free / B.GiB, dual_layout=os.environ.get("B200E_STEP", "auto") != "0")
         if world > 1:
             import torch.distributed as dist
 

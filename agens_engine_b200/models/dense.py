@@ -211,7 +211,16 @@ class DenseModel:
             if getattr(self, "world", 1) > 1 or not self._step_possible() or torch.cuda.is_current_stream_capturing():
                 return False
             from ..ops.step import StepRunner
-            self.step = StepRunner(self, uniform=self.step_uniform)
+            try:
+                self.step = StepRunner(self, uniform=self.step_uniform)
+            except (RuntimeError, MemoryError) as e:
+                # the second weight layout did not fit (a capped allocator, a nearly full GPU): stay on the per-op kernels
+                self.step = None
+                self.step_mode = "off"
+                self.use_step = False
+                import warnings
+                warnings.warn(f"persistent step kernel disabled: {e}")
+                return False
         return True
 
     def set_linear_path(self, mm_min_rows: Optional[int]):

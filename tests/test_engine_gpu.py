@@ -202,3 +202,27 @@ def test_engine_serves_a_request_with_images(tiny):
     d = eng2.submit(prompt, {"max_new_tokens": 4}, images=["data:image/png;base64,AAAA"])
     eng2.run_until_idle()
     assert "images" in col2.err[c] and col2.done[c] and col2.done[d]
+
+
+def test_budgeted_build_stays_under_the_cap_and_clamps_the_context():
+    """`build_model` with a per-GPU budget: the KV pool and the context come from the plan, the allocator is capped at the
+    budget, and a conversation longer than the clamped context fails with an error instead of taking more memory."""
+    from agens_engine_b200 import cli
+    free, total = torch.cuda.mem_get_info(0)
+    cfg = cli.EngineConfig(random="dense-32b-2l", budget_gib=6.0, wctx=262144, max_batch=2, prefill_chunk=256)
+    try:
+        m, rank, world, ctrl = cli.build_model(cfg)
+        assert rank == 0 and world == 1 and ctrl is None
+        assert m.deployment.fits and m.max_ctx <= 262144
+        assert torch.cuda.memory_allocated(0) <= m.deployment.budget_bytes
+        assert m.budget.used <= m.budget.budget
+        m.new_seq(0)
+        toks = torch.randint(0, m.cfg.vocab, (300,))
+        first, _ = m.prefill(0, toks)
+        assert 0 <= int(first) < m.cfg.vocab
+        with pytest.raises(RuntimeError):
+            m.reserve(0, m.max_ctx + 64)               # past the planned context: refused on the host
+        with pytest.raises(Exception):
+            torch.empty(int(m.deployment.budget_bytes), dtype=torch.uint8, device="cuda:0")   # past the cap: refused
+    finally:
+        torch.cuda.set_per_process_memory_fraction(1.0, 0)
