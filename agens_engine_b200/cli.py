@@ -108,6 +108,10 @@ def build_model(cfg: EngineConfig, **kw):
     kw.setdefault("max_ctx", cfg.wctx)
     kw.setdefault("prefill_chunk", cfg.prefill_chunk)
     kw.setdefault("split_keys", cfg.split_keys)
+    # long contexts: at most 1024 attention splits per (row, head), so that the split partials stay near 1 GB at 256K
+    want = (kw["max_ctx"] + 1023) // 1024
+    while kw["split_keys"] < want:
+        kw["split_keys"] *= 2
     ctrl = None
     local = int(os.environ.get("LOCAL_RANK", rank)) if world > 1 else cfg.device
     dev = f"cuda:{local}"
@@ -123,7 +127,8 @@ def build_model(cfg: EngineConfig, **kw):
         mc = _model_config(cfg)
         free, _total = torch.cuda.mem_get_info(local)
         dep = B.plan_deployment(mc, cfg.budget_gib, kw["max_ctx"], cfg.max_batch, kw["max_seqs"], kw["prefill_chunk"], tp=world,
-                                gpu_free_gib=free / B.GiB, dual_layout=os.environ.get("B200E_STEP", "auto") != "0")
+                                gpu_free_gib=free / B.GiB, dual_layout=os.environ.get("B200E_STEP", "auto") != "0",
+                                split_keys=kw["split_keys"])
         if world > 1:
             import torch.distributed as dist
 

@@ -93,7 +93,11 @@ class DenseModel:
             d["ln1"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
             d["ln2"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
             m.layers.append(d)
-        m.embed = (torch.randn(cfg.vocab, cfg.d_model, device=m.dev, generator=g) * 0.02).to(torch.bfloat16)
+        # in row chunks: the fp32 intermediate of the whole table would be a 3 GB transient on the 32B vocabulary
+        m.embed = torch.empty(cfg.vocab, cfg.d_model, dtype=torch.bfloat16, device=m.dev)
+        for r0 in range(0, cfg.vocab, 16384):
+            r1 = min(cfg.vocab, r0 + 16384)
+            m.embed[r0:r1] = (torch.randn(r1 - r0, cfg.d_model, device=m.dev, generator=g) * 0.02).to(torch.bfloat16)
         m.final_norm = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
         m.lm_head = L.WqLinear.random(cfg.vocab, cfg.d_model, cfg.lm_head_bits, cfg.group, m.dev, seed=seed * 1000003 + 999983)
         return m.finalize()

@@ -88,7 +88,7 @@ class Deployment:
 
 def plan_deployment(cfg, budget_gib: float, wctx: int, max_batch: int, sessions: int, prefill_chunk: int, tp: int = 1,
                     gpu_free_gib: Optional[float] = None, host_avail_gib: float = -1.0, allow_host_tier: bool = True,
-                    weights_bytes: Optional[int] = None, dual_layout: bool = False) -> Deployment:
+                    weights_bytes: Optional[int] = None, dual_layout: bool = False, split_keys: int = 64) -> Deployment:
     """Runs the planner for one rank of a ``tp``-way deployment of the architecture ``cfg`` (the full model's config).
     ``weights_bytes``: measured bytes when the weights are already on the device, else the architecture's estimate
     plus 0.6 GiB of CUDA context; ``dual_layout`` doubles the quantised linears (the step kernel's second layout)."""
@@ -100,7 +100,8 @@ def plan_deployment(cfg, budget_gib: float, wctx: int, max_batch: int, sessions:
                weights_bytes=int(weights_bytes), kv_bytes_per_token=int(cfg.kv_bytes_per_token(tp)), page_size=cfg.page_size,
                max_batch=int(max_batch), sessions=int(sessions), prefill_chunk=int(prefill_chunk), d_model=cfg.d_model, ffn=cfg.ffn,
                q_dim=cfg.q_dim, kv_dim=cfg.kv_dim, vocab=cfg.vocab, n_heads=cfg.n_heads, head_dim=cfg.head_dim, tp=int(tp),
-               wctx=int(wctx), host_avail_gib=float(host_avail_gib), allow_host_tier=bool(allow_host_tier))
+               wctx=int(wctx), host_avail_gib=float(host_avail_gib), allow_host_tier=bool(allow_host_tier),
+               split_keys=int(split_keys))
     if "error" in p:
         raise ValueError(p["error"])
     ps = cfg.page_size

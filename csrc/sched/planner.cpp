@@ -38,7 +38,7 @@ struct PlanIn {
   double host_headroom_gib = 8;
   bool allow_host_tier = true;
   int resident_window_pages = 0;    // pages of a tiered conversation that always stay on the GPU (0 = auto)
-  int max_splits_bytes_tokens = 32; // token rows the decode attention partial buffers are sized for
+  int split_keys = 64;              // keys per attention split: the partial buffers hold wctx / split_keys splits per (row, head)
 };
 
 static PlanIn parse_in(const Json& j) {
@@ -65,6 +65,7 @@ static PlanIn parse_in(const Json& j) {
   p.host_headroom_gib = j.get_double("host_headroom_gib", 8);
   p.allow_host_tier = j.get_bool("allow_host_tier", true);
   p.resident_window_pages = (int)j.get_int("resident_window_pages", 0);
+  p.split_keys = std::max(16, (int)j.get_int("split_keys", 64));
   return p;
 }
 
@@ -102,7 +103,11 @@ static Json scratch_items(const PlanIn& p) {
   const long long shard_ffn = p.ffn / p.tp, shard_q = p.q_dim / p.tp, shard_kv = p.kv_dim / p.tp;
   it.set("prefill_activations", (long long)(T * (2ll * p.d_model + shard_q + 2 * shard_kv + shard_q + 3ll * shard_ffn) * 2));
   it.set("dequant_tile", (long long)std::max<long long>((long long)p.d_model * 2 * shard_ffn * 2, 64ll << 20));
-  it.set("attention_partials", (long long)p.max_splits_bytes_tokens * (p.n_heads / p.tp) * 4096ll / 64 * (p.head_dim + 2) * 4);
+  // split partials of the decode / verify attention: [rows][heads][splits][head_dim + (max, sum)] fp32, rows = eight per
+  // sequence slot between 32 and 128, splits = wanted context / keys per split
+  const long long rows = std::min(128, std::max(32, 8 * p.max_batch));
+  const long long splits = (p.wctx + p.split_keys - 1) / p.split_keys;
+  it.set("attention_partials", (long long)(rows * (p.n_heads / p.tp) * splits * (p.head_dim + 2) * 4));
   it.set("gemv_scratch", (long long)(64ll << 20));
   it.set("logits", (long long)32 * (p.vocab / p.tp) * 4);
   it.set("tp_inboxes", (long long)(p.tp > 1 ? 129ll * p.tp * 32 * p.d_model * 4 : 0));
