@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Builds the reference's kernel library, unmodified, for the reference arm of bench.py.
 
-    python baseline/build_reference.py [path to the reference checkout]
+    python baseline/build_reference.py PATH_TO_THE_REFERENCE_CHECKOUT      (or set AGENS_REFERENCE_DIR)
 
 The reference is a Rust workspace plus a CUDA/CMake project; it has no setup.py / pyproject.toml, so `pip install
 --target baseline/_ref <reference>` answers "not installable", and cargo / rustc are not available offline.  Its kernel
@@ -19,7 +19,12 @@ HERE = Path(__file__).resolve().parent
 
 
 def main() -> int:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+    where = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("AGENS_REFERENCE_DIR")
+    if not where:
+        print("usage: python baseline/build_reference.py PATH_TO_THE_REFERENCE_CHECKOUT", file=sys.stderr)
+        return 2
+    ref = Path(where)
     src = ref / "kernels"
     if not (src / "CMakeLists.txt").exists():
         print(f"{src} has no CMakeLists.txt", file=sys.stderr)

@@ -44,7 +44,7 @@ def unavailable(why: str):
 
 def run(args) -> int:
     if not LIB.exists():
-        return unavailable("baseline/_ref/libagens_kernels_py.so is missing: run `python baseline/build_reference.py` "
+        return unavailable("baseline/_ref/libagens_kernels_py.so is missing: run `python baseline/build_reference.py REFERENCE_DIR` "
                            "(CMake + nvcc build of the reference's kernels for sm_100)")
     import torch
     import torch.distributed as dist
