@@ -88,7 +88,8 @@ static_assert(SM_WORK + 6 * 2 * 2 * kPage * 128 * 2 + kStepWarps * 2560 * 3 + 12
 // [736,800) row description (ids, pos, seq, rope position), [800,832) ring progress published to the producer warp,
 // [832,862) panel index of every partial tile
 constexpr int MI_WSUM = 16, MI_AV = 256, MI_AI = 496, MI_ROW = 736, MI_PUB = 800, MI_TILE = 832;   // MI_PUB: 2 words per worker warp
-static_assert((MI_TILE + 2 * kStepWarps) * 4 <= SM_MISC_BYTES, "misc area");
+constexpr int MI_DESC = 864;               // [864,896): two 64-byte slots for the next linears' descriptors (16-byte aligned)
+static_assert(MI_TILE + 2 * kStepWarps <= MI_DESC && (MI_DESC + 32) * 4 <= SM_MISC_BYTES && (MI_DESC * 4) % 16 == 0, "misc area");
 
 // Barrier over the worker warps (the producer warp never takes part in a CTA barrier).
 __device__ __forceinline__ void workers_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kStepThreads) : "memory"); }
@@ -205,10 +206,13 @@ struct Phase {
 };
 
 // Field-wise copy of a StepLinear from global memory (four 16-byte loads; keeps the copy in registers).
+__device__ __forceinline__ void decode_linear(uint4 a0, uint4 a1, uint4 a2, uint4 a3, StepLinear& L);
 __device__ __forceinline__ void fetch_linear(const StepLinear* src, StepLinear& L) {
   static_assert(sizeof(StepLinear) == 64, "StepLinear is read as four 16-byte words");
   const uint4* s4 = reinterpret_cast<const uint4*>(src);
-  const uint4 a0 = __ldg(s4), a1 = __ldg(s4 + 1), a2 = __ldg(s4 + 2), a3 = __ldg(s4 + 3);
+  decode_linear(__ldg(s4), __ldg(s4 + 1), __ldg(s4 + 2), __ldg(s4 + 3), L);
+}
+__device__ __forceinline__ void decode_linear(uint4 a0, uint4 a1, uint4 a2, uint4 a3, StepLinear& L) {
   L.wq = reinterpret_cast<const uint8_t*>(((unsigned long long)a0.y << 32) | (unsigned long long)a0.x);
   L.n = (int)a0.z; L.k = (int)a0.w;
   L.bits = (int)a1.x; L.group = (int)a1.y; L.npan = (int)a1.z; L.nbat = (int)a1.w;
@@ -216,12 +220,14 @@ __device__ __forceinline__ void fetch_linear(const StepLinear* src, StepLinear& 
   L.cps = (int)a3.x; L.fmax = (int)a3.y; L.pad = 0;
 }
 
-__device__ __forceinline__ void load_linear(const StepArgs& a, int phase, StepLinear& L) {
-  if (phase >= 4 * a.n_layers) { L = a.lm_head; return; }
+__device__ __forceinline__ const StepLinear* linear_of(const StepArgs& a, int phase) {
   const StepLayer* ly = a.layers + (phase >> 2);
   const int j = phase & 3;
-  const StepLinear* src = j == 0 ? &ly->qkv : (j == 1 ? &ly->o : (j == 2 ? &ly->gate_up : &ly->down));
-  fetch_linear(src, L);
+  return j == 0 ? &ly->qkv : (j == 1 ? &ly->o : (j == 2 ? &ly->gate_up : &ly->down));
+}
+__device__ __forceinline__ void load_linear(const StepArgs& a, int phase, StepLinear& L) {
+  if (phase >= 4 * a.n_layers) { L = a.lm_head; return; }
+  fetch_linear(linear_of(a, phase), L);
 }
 
 __device__ __forceinline__ void split_phase(Phase& ph, int cta) {
@@ -463,25 +469,22 @@ __device__ __noinline__ void quant_store(const StepArgs& a, int xstride, int gst
   }
 }
 
-// 1 / rms of every row of the step from the per-batch sums of squares (fixed order), into shared memory.
-__device__ __noinline__ void row_scales(const StepArgs& a) {
-  extern __shared__ __align__(128) uint8_t smem[];
-  float* inv_rms = reinterpret_cast<float*>(smem + SM_MISC);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nb = a.d_model >> 7;
-  for (int tok = warp; tok < a.n_rows; tok += kStepWarps) {
-    float s = 0.f;
-    for (int b = lane; b < nb; b += 32) s += __ldcg(a.psq + (size_t)tok * nb + b);
-    s = warp_sum(s);
-    if (lane == 0) inv_rms[tok] = rsqrtf(s / (float)a.d_model + a.eps);
-  }
-  workers_sync();
-}
-
 // Stage 1 of a linear: the CTA's k slice of the staged activations and of their group scalars, global -> shared.
-__device__ __noinline__ void copy_staged(const StepArgs& a, const Phase& ph, Lay lay) {
+__device__ __noinline__ void copy_staged(const StepArgs& a, const Phase& ph, Lay lay, bool want_scales) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int tid = threadIdx.x;
+  if (want_scales) {
+    // 1 / rms of every row from the per-batch sums of squares (fixed order), for the finalize stage after this linear
+    float* inv_rms = reinterpret_cast<float*>(smem + SM_MISC);
+    const int warp = tid >> 5, lane = tid & 31;
+    const int nb = a.d_model >> 7;
+    for (int tok = warp; tok < a.n_rows; tok += kStepWarps) {
+      float s = 0.f;
+      for (int b = lane; b < nb; b += 32) s += __ldcg(a.psq + (size_t)tok * nb + b);
+      s = warp_sum(s);
+      if (lane == 0) inv_rms[tok] = rsqrtf(s / (float)a.d_model + a.eps);
+    }
+  }
   if (ph.active && ph.nbs > 0) {
     const int gpb = 128 / ph.lin.group;
     const uint4* src = reinterpret_cast<const uint4*>(a.xq + (size_t)ph.bs0 * lay.xs_stride);
@@ -592,7 +595,7 @@ __device__ __noinline__ void reduce_tiles(const StepArgs& a, const EmitCtx& ec, 
 
 template <int BITS, int GROUP, int NS>
 __device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, uint8_t* smem, const Lay& lay, WRing& ring,
-                                          long tp_off, bool& failed) {
+                                          long tp_off, bool& failed, bool want_scales) {
   constexpr int GPB = 128 / GROUP;
   constexpr int SPG = 4 / GPB;               // integer-MMA steps per quantisation group
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -617,7 +620,7 @@ __device__ __forceinline__ void gemv_body(const StepArgs& a, const Phase& ph, ui
 #define B2_T0(name) do { } while (0)
 #endif
 
-  copy_staged(a, ph, lay);
+  copy_staged(a, ph, lay, want_scales);
   if (!ph.active) return;
 #ifdef B2_STEP_TRACE
   const long long tc_staged = clock64();
@@ -773,9 +776,23 @@ __device__ __noinline__ void gemv_phase(const StepArgs& a, int phase, Lay lay, W
   WRing ring = *ring_io;
   bool failed = *failed_io;
   Phase ph;
-  load_linear(a, phase, ph.lin);
+  // The descriptor of this linear was copied to shared memory during the previous phase (its global load would sit in
+  // front of everything else here); the first phase and the lm_head (kernel parameter) read theirs directly.  The
+  // input is RMS-normed for qkv, gate / up and the lm_head: their finalize stages need the rows' 1 / rms.
+  const bool want_scales = (phase & 1) == 0;
+  uint4* dslot = reinterpret_cast<uint4*>(reinterpret_cast<float*>(smem + SM_MISC) + MI_DESC);
+  if (phase == 0 || phase >= 4 * a.n_layers) {
+    load_linear(a, phase, ph.lin);
+  } else {
+    const uint4* d4 = dslot + 4 * (phase & 1);
+    decode_linear(d4[0], d4[1], d4[2], d4[3], ph.lin);
+  }
+  if (threadIdx.x < 4 && phase + 1 < 4 * a.n_layers) {
+    cp_async16(smem_u32(dslot + 4 * ((phase + 1) & 1) + threadIdx.x), reinterpret_cast<const uint4*>(linear_of(a, phase + 1)) + threadIdx.x);
+    cp_async_commit();
+  }
   split_phase(ph, blockIdx.x);
-#define B2_STEP_BODY(B, G) gemv_body<B, G, NS>(a, ph, smem, lay, ring, tp_off, failed)
+#define B2_STEP_BODY(B, G) gemv_body<B, G, NS>(a, ph, smem, lay, ring, tp_off, failed, want_scales)
   switch (ph.lin.bits * 1000 + ph.lin.group) {
     case 4128: B2_STEP_BODY(4, 128); break;
     case 4064: B2_STEP_BODY(4, 64); break;
@@ -785,6 +802,7 @@ __device__ __noinline__ void gemv_phase(const StepArgs& a, int phase, Lay lay, W
     default: B2_STEP_BODY(2, 64); break;
   }
 #undef B2_STEP_BODY
+  if (threadIdx.x < 4) cp_async_wait<0>();      // the next descriptor has landed long ago; the stages' barriers publish it
   *ring_io = ring;
   *failed_io = failed;
 }
@@ -876,7 +894,6 @@ __device__ __noinline__ void fin_qkv(const StepArgs& a, const StepLayer* ly, con
   const StepLinear& L = ly->qkv;
   StepLinear Lc;
   fetch_linear(&L, Lc);
-  row_scales(a);
   bf16* kv_pool = ly->kv_pool;
   const int heads = a.hq + 2 * a.hkv;
   const int items = a.n_rows * heads;
@@ -964,7 +981,6 @@ __device__ __noinline__ void fin_swiglu(const StepArgs& a, const StepLinear* Lg,
   const float* inv_rms = reinterpret_cast<const float*>(smem + SM_MISC);
   StepLinear L;
   fetch_linear(Lg, L);
-  row_scales(a);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int f = L.n >> 1, R = a.n_rows;
   const int nb = f >> 7;
@@ -1345,7 +1361,6 @@ __device__ __noinline__ void fin_argmax_cta(const StepArgs& a, uint8_t* smem) {
   int* si = reinterpret_cast<int*>(misc + MI_AI);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int R = a.n_rows;
-  row_scales(a);
   const float* inv_rms = misc;
   for (int tok = 0; tok < R; ++tok) {
     float best = -INFINITY;
