@@ -37,6 +37,11 @@ def _h():
         h.b2h_jpeg_info.argtypes, h.b2h_jpeg_info.restype = [vp, C.c_long, ip, ip, ip], i
         h.b2h_jpeg_decode.argtypes, h.b2h_jpeg_decode.restype = [vp, C.c_long, vp], i
         h.b2h_jpeg_error.argtypes, h.b2h_jpeg_error.restype = [], C.c_char_p
+        for nm in ("b2h_bmp_info", "b2h_gif_info"):
+            getattr(h, nm).argtypes, getattr(h, nm).restype = [vp, C.c_long, ip, ip], i
+        for nm in ("b2h_bmp_decode", "b2h_gif_decode"):
+            getattr(h, nm).argtypes, getattr(h, nm).restype = [vp, C.c_long, vp], i
+        h.b2h_image_error.argtypes, h.b2h_image_error.restype = [], C.c_char_p
         _sig = True
     return h
 
@@ -89,7 +94,8 @@ def mrope_positions(ids: Sequence[int], pad_id: int, grids: Sequence[Tuple[int, 
 def decode_image(data: bytes) -> np.ndarray:
     """uint8 [h, w, 3] from a binary PPM, a non-interlaced 8-bit PNG (RGB, RGBA, grey, grey+alpha, palette; alpha is
     dropped) or a baseline JPEG (``csrc/server/jpeg.cpp``: grey or three components, 1x / 2x sampling factors, restart
-    intervals; progressive and arithmetic-coded files are refused with a message)."""
+    intervals; progressive and arithmetic-coded files are refused with a message), an uncompressed BMP or the first
+    frame of a GIF (``csrc/server/image_misc.cpp``)."""
     if data[:2] == b"P6":
         h, w = C.c_int(), C.c_int()
         buf = (C.c_ubyte * len(data)).from_buffer_copy(data)
@@ -101,6 +107,10 @@ def decode_image(data: bytes) -> np.ndarray:
         return _decode_png(data)
     if data[:2] == b"\xff\xd8":
         return _decode_jpeg(data)
+    if data[:2] == b"BM":
+        return _decode_simple(data, "bmp")
+    if data[:4] == b"GIF8":
+        return _decode_simple(data, "gif")
     raise ValueError("unknown image format")
 
 
@@ -115,6 +125,20 @@ def _decode_jpeg(data: bytes) -> np.ndarray:
     out = np.empty((h.value, w.value, 3), dtype=np.uint8)
     if lib.b2h_jpeg_decode(buf, len(data), out.ctypes.data_as(C.c_void_p)) != 0:
         raise ValueError(lib.b2h_jpeg_error().decode() or "bad JPEG")
+    return out
+
+
+def _decode_simple(data: bytes, kind: str) -> np.ndarray:
+    """BMP (uncompressed 8 / 24 / 32-bit) and GIF (first frame) through ``csrc/server/image_misc.cpp``."""
+    lib = _h()
+    info, dec = (lib.b2h_bmp_info, lib.b2h_bmp_decode) if kind == "bmp" else (lib.b2h_gif_info, lib.b2h_gif_decode)
+    buf = (C.c_ubyte * len(data)).from_buffer_copy(data)
+    h, w = C.c_int(), C.c_int()
+    if info(buf, len(data), C.byref(h), C.byref(w)) != 0:
+        raise ValueError(lib.b2h_image_error().decode() or f"bad {kind}")
+    out = np.empty((h.value, w.value, 3), dtype=np.uint8)
+    if dec(buf, len(data), out.ctypes.data_as(C.c_void_p)) != 0:
+        raise ValueError(lib.b2h_image_error().decode() or f"bad {kind}")
     return out
 
 
