@@ -32,6 +32,8 @@ class Json {
   Json(unsigned v) : t_(Int), i_(v) {}
   Json(unsigned long v) : t_(Int), i_((long long)v) {}
   Json(double v) : t_(Double), d_(v) {}
+  // An integer beyond 64 bits that only survives as a double: written with all its digits, as an integer
+  static Json big_integer(double v) { Json j(v); j.int_like_ = true; return j; }
   Json(const char* s) : t_(String), s_(s) {}
   Json(std::string s) : t_(String), s_(std::move(s)) {}
   static Json array() { Json j; j.t_ = Array; return j; }
@@ -104,6 +106,7 @@ class Json {
   bool b_ = false;
   long long i_ = 0;
   double d_ = 0;
+  bool int_like_ = false;
   std::string s_;
   Arr a_;
   Obj o_;
@@ -264,14 +267,37 @@ class Json {
       case Double: {
         if (std::isnan(d_)) { out += "NaN"; break; }
         if (std::isinf(d_)) { out += d_ > 0 ? "Infinity" : "-Infinity"; break; }
+        if (int_like_) { char ib[64]; snprintf(ib, sizeof ib, "%.0f", d_); out += ib; break; }
+        // Python's repr(float): the shortest digits that round-trip, fixed notation for decimal exponents in
+        // [-4, 16), else d.ddde+XX with at least two exponent digits
         char b[40];
-        // shortest representation that round-trips, as Python's repr(float)
-        for (int prec = 1; prec <= 17; ++prec) {
-          snprintf(b, sizeof b, "%.*g", prec, d_);
+        int prec = 1;
+        for (; prec <= 17; ++prec) {
+          snprintf(b, sizeof b, "%.*e", prec - 1, d_);
           if (std::strtod(b, nullptr) == d_) break;
         }
-        std::string s = b;
-        if (s.find_first_of(".eEn") == std::string::npos) s += ".0";
+        std::string m = b;                       // [-]d[.ddd]e[+-]XX
+        const size_t epos = m.find('e');
+        const int e10 = std::atoi(m.c_str() + epos + 1);
+        std::string digits;
+        bool neg = false;
+        for (size_t i = 0; i < epos; ++i) { if (m[i] == '-') neg = true; else if (m[i] != '.') digits.push_back(m[i]); }
+        std::string s = neg ? "-" : "";
+        if (e10 >= -4 && e10 < 16) {
+          if (e10 < 0) {
+            s += "0." + std::string((size_t)(-e10 - 1), '0') + digits;
+          } else if ((int)digits.size() <= e10 + 1) {
+            s += digits + std::string((size_t)(e10 + 1 - (int)digits.size()), '0') + ".0";
+          } else {
+            s += digits.substr(0, (size_t)e10 + 1) + "." + digits.substr((size_t)e10 + 1);
+          }
+        } else {
+          s += digits.substr(0, 1);
+          if (digits.size() > 1) s += "." + digits.substr(1);
+          char eb[16];
+          snprintf(eb, sizeof eb, "e%c%02d", e10 < 0 ? '-' : '+', e10 < 0 ? -e10 : e10);
+          s += eb;
+        }
         out += s;
         break;
       }

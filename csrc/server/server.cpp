@@ -746,11 +746,12 @@ static char* parse_output_with(const char* text, const char* tools_json, int sta
                                const std::string& think_open, const std::string& think_close,
                                const std::string& call_open, const std::string& call_close) {
   Json tools = tools_json && *tools_json ? Json::parse(tools_json) : Json::array();
+  const bool with_calls = !tools.is_null();      // "null": the request carries no tools (or tool_choice none): calls stay text
   std::string t = text, content, reasoning;
   std::vector<ToolCall> calls;
   ReasoningParser rp(starts_in_reasoning != 0, true, think_open, think_close);
-  ToolStreamParser tp(tools, call_open, call_close);
-  if (call_open != "<tool_call>") {          // the other template family: its parsers' conventions
+  ToolStreamParser tp(with_calls ? tools : Json::array(), call_open, call_close);
+  if (call_open != "<tool_call>" && with_calls) {          // the other template family: its parsers' conventions
     rp.set_interrupt(call_open);
     tp.content_before_calls_only(true);
   }
@@ -758,12 +759,22 @@ static char* parse_output_with(const char* text, const char* tools_json, int sta
     auto ro = rp.push(piece);
     if (last) { auto f = rp.finish(); ro.content += f.content; ro.reasoning += f.reasoning; }
     reasoning += ro.reasoning;
+    if (!with_calls) { content += ro.content; return; }
     auto tr = tp.push(ro.content);
     if (last) { auto f = tp.finish(); tr.content += f.content; for (auto& c : f.calls) tr.calls.push_back(c); }
     content += tr.content;
     for (auto& c : tr.calls) calls.push_back(c);
   };
-  if (chunk <= 0) feed(t, true);
+  // A complete (non-streamed) output that was not forced into reasoning but carries the opening tag somewhere is read
+  // as reasoning up to its first closing tag, the opening tag's text included (parser corpus: think_start_mid).
+  const size_t close_at = t.find(think_close);
+  if (chunk <= 0 && !starts_in_reasoning && !think_open.empty() && close_at != std::string::npos &&
+      t.find(think_open) != std::string::npos && t.compare(0, think_open.size(), think_open) != 0) {
+    reasoning = t.substr(0, close_at);
+    ReasoningParser plain(false, true, "\x01no-open\x01", "\x01no-close\x01");
+    rp = plain;
+    feed(t.substr(close_at + think_close.size()), true);
+  } else if (chunk <= 0) feed(t, true);
   else { for (size_t i = 0; i < t.size(); i += (size_t)chunk) feed(t.substr(i, (size_t)chunk), false); feed("", true); }
   Json o = Json::object(), a = Json::array();
   for (auto& c : calls) { Json j = Json::object(); j.set("name", c.name); j.set("arguments", c.arguments_json); a.push_back(j); }

@@ -441,15 +441,185 @@ static const Json* tool_schema(const Json& tools, const std::string& name) {
   }
   return nullptr;
 }
-static Json typed_value(const std::string& raw, const Json* schema, const std::string& key) {
-  std::string type = "string";
-  if (schema) if (auto props = schema->find("properties")) if (auto p = props->find(key)) {
-    if (auto t = p->find("type")) { if (t->is_string()) type = t->as_string(); else if (t->is_array() && t->size()) type = (*t)[0].as_string(); }
-    else if (p->contains("enum")) type = "string"; else if (p->contains("properties")) type = "object";
+// ---- typing of a parameter's text through the tool's JSON schema
+// The contract (observed on the reference's parser corpus, crates/agens-server/tests/fixtures/parser_corpus.json):
+//   * the text "null" in any letter case is JSON null, whatever the declared type;
+//   * the declared types are the property's "type" (a string or a list) plus the types inside anyOf / oneOf / allOf;
+//   * if "string" is among them the text stays a string; a property without any type information stays a string too;
+//   * an enum without a type yields the enum member whose JSON text equals the value (so "2" becomes 2 for [1, 2]);
+//   * integers follow Python's int(): sign, leading zeros, single underscores between digits;
+//   * numbers follow Python's float(): inf / infinity / nan, exponents, underscores;
+//   * booleans: "true" in any letter case is true, everything else false;
+//   * objects and arrays: JSON first, then a Python literal (single quotes, True / False / None, tuples become lists);
+//   * whatever does not convert stays the text.
+static std::string lower_trim(const std::string& v) {
+  size_t a = 0, b = v.size();
+  while (a < b && std::isspace((unsigned char)v[a])) ++a;
+  while (b > a && std::isspace((unsigned char)v[b - 1])) --b;
+  std::string o = v.substr(a, b - a);
+  for (auto& c : o) c = (char)std::tolower((unsigned char)c);
+  return o;
+}
+static bool strip_underscores(const std::string& v, std::string& out) {       // Python's rule: single, between digits
+  out.clear();
+  for (size_t i = 0; i < v.size(); ++i) {
+    if (v[i] == '_') {
+      if (i == 0 || i + 1 >= v.size() || !std::isdigit((unsigned char)v[i - 1]) || !std::isdigit((unsigned char)v[i + 1])) return false;
+      continue;
+    }
+    out.push_back(v[i]);
   }
-  if (type == "string") return Json(raw);
-  try { return Json::parse(raw); } catch (...) {}
-  if (type == "boolean") { if (raw == "True" || raw == "true") return Json(true); if (raw == "False" || raw == "false") return Json(false); }
+  return true;
+}
+static bool python_int(const std::string& raw, long long& out) {
+  std::string t, v = lower_trim(raw);
+  if (!strip_underscores(v, t) || t.empty()) return false;
+  size_t i = (t[0] == '+' || t[0] == '-') ? 1 : 0;
+  if (i >= t.size() || t.size() - i > 18) return false;
+  for (size_t j = i; j < t.size(); ++j) if (!std::isdigit((unsigned char)t[j])) return false;
+  out = std::strtoll(t.c_str(), nullptr, 10);
+  return true;
+}
+static bool python_float(const std::string& raw, double& out) {
+  std::string t, v = lower_trim(raw);
+  if (!strip_underscores(v, t) || t.empty()) return false;
+  std::string u = t;
+  const bool neg = u[0] == '-';
+  if (u[0] == '+' || u[0] == '-') u.erase(0, 1);
+  if (u == "inf" || u == "infinity") { out = neg ? -INFINITY : INFINITY; return true; }
+  if (u == "nan") { out = NAN; return true; }
+  bool digit = false;
+  for (char c : u) {
+    if (std::isdigit((unsigned char)c)) digit = true;
+    else if (c != '.' && c != 'e' && c != '+' && c != '-') return false;
+  }
+  if (!digit) return false;
+  char* end = nullptr;
+  out = std::strtod(t.c_str(), &end);
+  return end && *end == 0;
+}
+// Python literal (dict / list / tuple / str / numbers / True / False / None) -> Json; throws on anything else.
+struct PyLit {
+  const std::string& s;
+  size_t i = 0;
+  explicit PyLit(const std::string& t) : s(t) {}
+  void ws() { while (i < s.size() && std::isspace((unsigned char)s[i])) ++i; }
+  [[noreturn]] void bad() { throw std::runtime_error("not a Python literal"); }
+  Json value() {
+    ws();
+    if (i >= s.size()) bad();
+    const char c = s[i];
+    if (c == '{') {
+      ++i;
+      Json o = Json::object();
+      ws();
+      if (i < s.size() && s[i] == '}') { ++i; return o; }
+      while (true) {
+        Json k = value();
+        if (!k.is_string()) bad();
+        ws();
+        if (i >= s.size() || s[i] != ':') bad();
+        ++i;
+        o.set(k.as_string(), value());
+        ws();
+        if (i < s.size() && s[i] == ',') { ++i; ws(); if (i < s.size() && s[i] == '}') { ++i; return o; } continue; }
+        if (i < s.size() && s[i] == '}') { ++i; return o; }
+        bad();
+      }
+    }
+    if (c == '[' || c == '(') {
+      const char close = c == '[' ? ']' : ')';
+      ++i;
+      Json a = Json::array();
+      ws();
+      if (i < s.size() && s[i] == close) { ++i; return a; }
+      while (true) {
+        a.push_back(value());
+        ws();
+        if (i < s.size() && s[i] == ',') { ++i; ws(); if (i < s.size() && s[i] == close) { ++i; return a; } continue; }
+        if (i < s.size() && s[i] == close) { ++i; return a; }
+        bad();
+      }
+    }
+    if (c == '\'' || c == '"') {
+      ++i;
+      std::string o;
+      while (i < s.size() && s[i] != c) {
+        if (s[i] == '\\' && i + 1 < s.size()) {
+          const char e = s[i + 1];
+          i += 2;
+          if (e == 'n') o.push_back('\n'); else if (e == 't') o.push_back('\t'); else if (e == 'r') o.push_back('\r');
+          else if (e == '\\' || e == '\'' || e == '"') o.push_back(e); else { o.push_back('\\'); o.push_back(e); }
+          continue;
+        }
+        o.push_back(s[i++]);
+      }
+      if (i >= s.size()) bad();
+      ++i;
+      return Json(o);
+    }
+    size_t j = i;
+    while (j < s.size() && (std::isalnum((unsigned char)s[j]) || s[j] == '_' || s[j] == '.' || s[j] == '+' || s[j] == '-')) ++j;
+    const std::string tok = s.substr(i, j - i);
+    if (tok.empty()) bad();
+    i = j;
+    if (tok == "True") return Json(true);
+    if (tok == "False") return Json(false);
+    if (tok == "None") return Json();
+    long long iv;
+    if (python_int(tok, iv)) return Json((int64_t)iv);
+    double dv;
+    if (python_float(tok, dv)) return Json(dv);
+    bad();
+  }
+  Json parse() { Json v = value(); ws(); if (i != s.size()) bad(); return v; }
+};
+static void collect_types(const Json& p, std::vector<std::string>& types) {
+  if (auto t = p.find("type")) {
+    if (t->is_string()) types.push_back(t->as_string());
+    else if (t->is_array()) for (auto& x : t->items()) if (x.is_string()) types.push_back(x.as_string());
+  }
+  for (const char* key : {"anyOf", "oneOf", "allOf"})
+    if (auto a = p.find(key)) if (a->is_array()) for (auto& m : a->items()) if (m.is_object()) collect_types(m, types);
+  if (types.empty() && p.contains("properties")) types.push_back("object");
+}
+static Json typed_value(const std::string& raw, const Json* schema, const std::string& key) {
+  if (lower_trim(raw) == "null") return Json();
+  const Json* prop = nullptr;
+  if (schema) if (auto props = schema->find("properties")) prop = props->find(key);
+  if (!prop || !prop->is_object()) return Json(raw);
+  std::vector<std::string> types;
+  collect_types(*prop, types);
+  auto has = [&](const char* t) { for (auto& x : types) if (x == t) return true; return false; };
+  auto has_prefix = [&](const char* t) { for (auto& x : types) if (x.rfind(t, 0) == 0) return true; return false; };
+  if (types.empty()) {
+    if (auto en = prop->find("enum")) if (en->is_array()) {
+      const std::string v = lower_trim(raw) == raw ? raw : raw;      // members are compared with the text as written
+      for (auto& m : en->items()) {
+        if (m.is_string() && m.as_string() == v) return m;
+        if (!m.is_string() && m.dump() == lower_trim(raw)) return m;
+      }
+    }
+    return Json(raw);
+  }
+  if (has("string")) return Json(raw);
+  long long iv;
+  if ((has_prefix("int") || has_prefix("uint")) && python_int(raw, iv)) return Json((int64_t)iv);
+  double dv;
+  if ((has("number") || has("float") || has("double")) && python_float(raw, dv)) {
+    // text that reads as an integer stays one: exactly when it fits 64 bits, else with the digits of the nearest double
+    const std::string lt = lower_trim(raw);
+    if (std::isfinite(dv) && lt.find_first_of(".en") == std::string::npos) {
+      if (python_int(raw, iv)) return Json((int64_t)iv);
+      return Json::big_integer(dv);
+    }
+    return Json(dv);
+  }
+  if (has("boolean")) return Json(lower_trim(raw) == "true");
+  if (has("object") || has("array") || has("dict") || has("list") || has("tuple")) {
+    try { return Json::parse(raw); } catch (...) {}
+    try { return PyLit(raw).parse(); } catch (...) {}
+  }
   return Json(raw);
 }
 static std::string strip_nl(std::string v) {
@@ -498,7 +668,14 @@ ToolParse parse_tool_calls(const std::string& text, const Json& tools, const std
       const size_t fb = body.find("<function=");
       ToolCall tc;
       bool ok = false;
+      if (e == std::string::npos && !r.calls.empty()) {
+        // the output ended inside a further call: after a complete call the fragment is neither a call nor content
+        r.unfinished = true;
+        break;
+      }
       if (fb != std::string::npos) {
+        // a block closed by the call tag counts even without its </function>; a lone call that the output cut short is
+        // salvaged with what it has (the value runs to the end of the text)
         size_t fe = body.find("</function>", fb);
         ok = parse_function_block(body.substr(fb + 10, (fe == std::string::npos ? body.size() : fe) - fb - 10), tools, tc);
       } else {
@@ -515,6 +692,7 @@ ToolParse parse_tool_calls(const std::string& text, const Json& tools, const std
       pos = e == std::string::npos ? text.size() : e + lc;
     } else {
       size_t e = text.find("</function>", s);
+      if (e == std::string::npos && !r.calls.empty()) { r.unfinished = true; break; }
       ToolCall tc;
       if (parse_function_block(text.substr(s + 10, (e == std::string::npos ? text.size() : e) - s - 10), tools, tc)) r.calls.push_back(tc);
       pos = e == std::string::npos ? text.size() : e + 11;
@@ -557,6 +735,18 @@ ToolParse ToolStreamParser::push(const std::string& delta) {
   }
 }
 ToolParse ToolStreamParser::finish() {
+  if (saw_call_) {
+    // after a complete call a fragment of a further call at the end of the output is neither a call nor content
+    const size_t a0 = buf_.find(call_open_), b0 = buf_.find("<function=");
+    const size_t st0 = std::min(a0, b0);
+    if (st0 != std::string::npos) {
+      ToolParse cut;
+      if (!content_before_calls_only_) cut.content = buf_.substr(0, st0);
+      cut.unfinished = true;
+      buf_.clear();
+      return cut;
+    }
+  }
   ToolParse out = parse_tool_calls(buf_, tools_, call_open_, call_close_);
   if (content_before_calls_only_) {
     // an unfinished call at the end of the output is neither a call nor content

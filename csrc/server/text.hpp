@@ -76,7 +76,11 @@ struct ToolCall { std::string name, arguments_json; };
 
 // Tool calls in either wire format: <tool_call>{"name": .., "arguments": {..}}</tool_call> (JSON body) or
 // <function=NAME><parameter=KEY>VALUE</parameter>...</function> (typed by the tool's JSON schema).
-struct ToolParse { std::string content; std::vector<ToolCall> calls; };
+struct ToolParse {
+  std::string content;
+  std::vector<ToolCall> calls;
+  bool unfinished = false;      // the text ended inside a call: that call is neither reported nor content
+};
 ToolParse parse_tool_calls(const std::string& text, const Json& tools);
 // The same with the call wrapper of another template family (e.g. "<|call|>" ... "<|/call|>").
 ToolParse parse_tool_calls(const std::string& text, const Json& tools, const std::string& call_open, const std::string& call_close);

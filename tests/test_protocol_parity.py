@@ -23,7 +23,7 @@ def _parse(text, tools, starts_in_reasoning, chunk):
     fn = lib.b2h_parse_output_tags
     fn.restype = C.c_void_p
     fn.argtypes = [C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_char_p, C.c_char_p, C.c_char_p, C.c_char_p]
-    p = fn(text.encode(), json.dumps(tools or []).encode(), 1 if starts_in_reasoning else 0, chunk, *TAGS)
+    p = fn(text.encode(), json.dumps(tools).encode(), 1 if starts_in_reasoning else 0, chunk, *TAGS)
     out = json.loads(C.string_at(p).decode())
     lib.b2h_free_str(C.c_void_p(p))
     return out
