@@ -221,7 +221,12 @@ class Json {
     if (is_float) return Json(std::strtod(num.c_str(), nullptr));
     errno = 0;
     long long v = std::strtoll(num.c_str(), nullptr, 10);
-    if (errno == ERANGE) return Json(std::strtod(num.c_str(), nullptr));
+    if (errno == ERANGE) {
+      // an integer beyond 64 bits: the value survives as a double, the digits as written (Python keeps such integers exact)
+      Json j = Json::big_integer(std::strtod(num.c_str(), nullptr));
+      j.s_ = num;
+      return j;
+    }
     return Json(v);
   }
 
@@ -267,7 +272,13 @@ class Json {
       case Double: {
         if (std::isnan(d_)) { out += "NaN"; break; }
         if (std::isinf(d_)) { out += d_ > 0 ? "Infinity" : "-Infinity"; break; }
-        if (int_like_) { char ib[64]; snprintf(ib, sizeof ib, "%.0f", d_); out += ib; break; }
+        if (int_like_) {
+          if (!s_.empty()) { out += s_; break; }            // parsed from text: the digits as written
+          char ib[64];
+          snprintf(ib, sizeof ib, "%.0f", d_);
+          out += ib;
+          break;
+        }
         // Python's repr(float): the shortest digits that round-trip, fixed notation for decimal exponents in
         // [-4, 16), else d.ddde+XX with at least two exponent digits
         char b[40];

@@ -57,3 +57,31 @@ def test_parser_corpus_replay():
     rate = same / max(total, 1)
     print(f"parser corpus: {same} of {total} checks agree ({rate:.1%}); first differences: {diffs}")
     assert rate >= float(os.environ.get("B200E_PARITY_MIN", "0.9")), diffs
+
+
+def test_template_cases_replay():
+    """The reference's chat template (fixtures/model/chat_template.jinja) rendered by the C++ Jinja interpreter on the
+    51 cases of its template parity test (crates/agens-server/tests/template_parity.rs): every expected prompt must
+    come out byte for byte, and the cases that expect a template error must raise one."""
+    from agens_engine_b200.serve import server as S
+    path = os.path.join(FIX, "template_cases.json")
+    tpl_path = os.path.join(FIX, "model", "chat_template.jinja")
+    if not (os.path.isfile(path) and os.path.isfile(tpl_path)):
+        pytest.skip("template fixtures not present")
+    tpl = open(tpl_path).read()
+    cases = json.load(open(path))["cases"]
+    bad = []
+    for x in cases:
+        ctx = {"messages": x["messages"], "add_generation_prompt": True}
+        if x.get("tools") is not None:
+            ctx["tools"] = x["tools"]
+        ctx.update(x.get("kwargs") or {})
+        try:
+            out, err = S.render_template(tpl, **ctx), None
+        except Exception as e:          # a template that calls raise_exception
+            out, err = None, str(e)
+        ok = (err is not None) if x.get("error") is not None else (out == x["expected"])
+        if not ok:
+            bad.append(x["name"])
+    print(f"template cases: {len(cases) - len(bad)} of {len(cases)} agree; differences: {bad}")
+    assert not bad, bad
