@@ -15,6 +15,7 @@
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
+#include <cctype>
 #include <cstdio>
 #include <cstring>
 #include <ctime>
@@ -224,6 +225,20 @@ struct Emit { std::function<void(const std::string&)> write; std::function<bool(
 
 // Runs one generation to completion.  Streaming responses are written through `emit` as SSE events; the complete
 // response body (JSON or the concatenated event stream) is returned as well.
+static void normalize_schema_types(Json& sc);
+// The request's tools as the output parsers use them: none under tool_choice "none", parameter schemas with their
+// type names in JSON-schema form.
+static Json request_tools(const Json& body) {
+  if (!(body.find("tools") && body.at("tools").is_array()) || body.get_string("tool_choice", "auto") == "none") return Json::array();
+  Json tools = body.at("tools");
+  for (auto& t : tools.items())
+    if (t.is_object())
+      for (auto& kv : t.members())
+        if (kv.first == "function" && kv.second.is_object())
+          for (auto& fk : kv.second.members()) if (fk.first == "parameters") normalize_schema_types(fk.second);
+  return tools;
+}
+
 static HttpResponse run_generation(Server& sv, const Json& body, bool chat, const std::vector<int>& prompt_ids, const Json& sampling,
                                    bool starts_in_reasoning, const std::string& session_id, Emit* emit) {
   const bool stream = body.get_bool("stream", false);
@@ -232,7 +247,7 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
   const bool stream_reasoning = body.get_bool("stream_reasoning", true);
   const bool skip_special = body.get_bool("skip_special_tokens", true);
   const bool no_stop_trim = body.get_bool("no_stop_trim", false);
-  const Json tools = body.find("tools") && body.at("tools").is_array() && body.get_string("tool_choice", "auto") != "none" ? body.at("tools") : Json::array();
+  const Json tools = request_tools(body);
   std::vector<std::string> stops;
   if (auto p = body.find("stop")) { if (p->is_string()) stops.push_back(p->as_string()); else if (p->is_array()) for (auto& s : p->items()) if (s.is_string()) stops.push_back(s.as_string()); }
   std::vector<int> stop_ids;
@@ -390,6 +405,69 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
   return resp;
 }
 
+// Tool parameter schemas may carry database / ORM style type names ("varchar(255)", "int", "list[str]", "map");
+// the template (and the typed argument conversion) sees the JSON-schema name instead
+// (crates/agens-server/src/toolcall.rs:241-375).  Rules: a standard name stays; otherwise the text before "(" is
+// trimmed and lower-cased and looked up: exact aliases first, then family prefixes followed by a digit or bracket.
+static std::string schema_type_name(const std::string& raw) {
+  static const char* kStd[] = {"null", "boolean", "object", "array", "number", "string", "integer"};
+  for (auto t : kStd) if (raw == t) return raw;
+  std::string base = raw.substr(0, raw.find('('));
+  size_t a = 0, b = base.size();
+  while (a < b && std::isspace((unsigned char)base[a])) ++a;
+  while (b > a && std::isspace((unsigned char)base[b - 1])) --b;
+  base = base.substr(a, b - a);
+  for (auto& c : base) c = (char)std::tolower((unsigned char)c);
+  for (auto t : kStd) if (base == t) return base;
+  struct Family { const char* target; std::vector<const char*> exact, prefix; };
+  static const std::vector<Family> kFamilies = {
+      {"string", {"str", "text", "varchar", "char", "enum", "uuid", "date", "datetime", "time", "timestamp", "binary", "blob", "bytea", "bytes", "varbinary"}, {}},
+      {"boolean", {"bool"}, {}},
+      {"integer", {"bigint", "smallint", "tinyint"}, {"int", "uint", "long", "short", "unsigned"}},
+      {"number", {"double", "decimal", "real", "numeric"}, {"num", "float"}},
+      {"array", {"arr", "tuple", "set"}, {"list"}},
+      {"object", {"map"}, {"dict"}},
+  };
+  for (auto& f : kFamilies) for (auto e : f.exact) if (base == e) return f.target;
+  // prefixes in the order integer, number, array, object; within a family in the order listed
+  for (auto& f : kFamilies)
+    for (auto p : f.prefix) {
+      const size_t n = std::strlen(p);
+      if (base == p) return f.target;
+      if (base.size() > n && base.compare(0, n, p) == 0 && std::strchr("0123456789[<( \t", base[n])) return f.target;
+    }
+  return raw;
+}
+
+static void normalize_schema_types(Json& sc) {
+  if (sc.is_array()) { for (auto& it : sc.items()) normalize_schema_types(it); return; }
+  if (!sc.is_object()) return;
+  for (auto& kv : sc.members()) {
+    const std::string& k = kv.first;
+    Json& v = kv.second;
+    if (k == "type") {
+      if (v.is_string()) v = Json(schema_type_name(v.as_string()));
+      else if (v.is_array()) {
+        Json out = Json::array();
+        for (auto& it : v.items()) {
+          Json n = it.is_string() ? Json(schema_type_name(it.as_string())) : it;
+          bool seen = false;
+          for (auto& o : out.items()) if (o.dump() == n.dump()) seen = true;
+          if (!seen) out.push_back(n);
+        }
+        v = out;
+      }
+    } else if (k == "properties" || k == "patternProperties" || k == "$defs" || k == "definitions" || k == "dependentSchemas") {
+      if (v.is_object()) for (auto& m : v.members()) normalize_schema_types(m.second);
+    } else if (k == "anyOf" || k == "oneOf" || k == "allOf" || k == "prefixItems") {
+      if (v.is_array()) for (auto& m : v.items()) normalize_schema_types(m);
+    } else if (k == "items" || k == "additionalProperties" || k == "not" || k == "if" || k == "then" || k == "else" || k == "contains" ||
+               k == "propertyNames" || k == "unevaluatedItems" || k == "unevaluatedProperties") {
+      normalize_schema_types(v);
+    }
+  }
+}
+
 static HttpResponse handle_chat(Server& sv, const Json& body, const std::string& session_hdr, Emit* emit) {
   if (!body.is_object()) return error_response(400, "request body must be a JSON object");
   if (std::string e = reject_unsupported(body, true); !e.empty()) return error_response(400, e);
@@ -401,13 +479,19 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
     ChatMessage cm;
     cm.role = m.get_string("role", "");
     if (cm.role != "system" && cm.role != "user" && cm.role != "assistant" && cm.role != "tool" && cm.role != "developer") return error_response(400, "unknown message role: " + cm.role);
-    if (cm.role == "developer") cm.role = "system";
+    // with a checkpoint template the role goes through as written (the template decides what it accepts); the built-in
+    // ChatML renderer treats "developer" as "system"
+    if (cm.role == "developer" && sv.chat_template.empty()) cm.role = "system";
     if (auto c = m.find("content")) {
       if (c->is_string()) cm.content = c->as_string();
       else if (c->is_array()) {
         for (auto& part : c->items()) {
           const std::string type = part.get_string("type", "");
-          if (type == "text") cm.content += part.get_string("text", "");
+          if (type == "text") {
+            // text parts of a tool result are joined with one space, those of other roles run together
+            if (cm.role == "tool" && !cm.content.empty()) cm.content += " ";
+            cm.content += part.get_string("text", "");
+          }
           else if (type == "image_url") {
             if (!sv.backend->supports_images()) return error_response(400, "this model does not accept images");
             const Json* iu = part.find("image_url");
@@ -425,8 +509,19 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
   }
   bool enable_thinking = true;
   if (auto k = body.find("chat_template_kwargs"); k && k->is_object()) enable_thinking = k->get_bool("enable_thinking", true);
-  if (body.get_string("reasoning_effort", "") == "none") enable_thinking = false;
+  // reasoning effort: top-level "reasoning_effort" or {"reasoning": {"effort": ...}}; "none" switches thinking off, any
+  // other value goes to the template (which knows the values it supports)
+  std::string effort = body.get_string("reasoning_effort", "");
+  if (auto r = body.find("reasoning"); r && r->is_object() && effort.empty()) effort = r->get_string("effort", "");
+  if (effort == "none") { enable_thinking = false; effort.clear(); }
   const bool cont = body.get_bool("continue_final_message", false);
+  // A conversation that ends with an assistant message: with continue_final_message the turn is reopened and its
+  // text continued; without it the text is handed to the model as a user message (request corpus: assistant_last_converted)
+  std::string continue_text;
+  if (!sv.chat_template.empty() && !msgs.empty() && msgs.back().role == "assistant") {
+    if (cont) { continue_text = msgs.back().content; msgs.pop_back(); }
+    else msgs.back().role = "user";
+  }
   const Json tools = body.find("tools") && body.at("tools").is_array() && body.get_string("tool_choice", "auto") != "none" ? body.at("tools") : Json::array();
   std::string prompt;
   if (sv.chat_template.empty()) prompt = render_chatml(msgs, tools, !cont, enable_thinking, cont);
@@ -443,7 +538,10 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
           Json call = tc;
           if (const Json* fn = tc.find("function"); fn && fn->is_object()) {
             Json f = *fn;
-            if (const Json* a = fn->find("arguments"); a && a->is_string()) { try { f.set("arguments", Json::parse(a->as_string())); } catch (const std::exception&) {} }
+            if (const Json* a = fn->find("arguments"); a && a->is_string()) {
+              try { f.set("arguments", Json::parse(a->as_string())); }
+              catch (const std::exception&) { return error_response(400, "Assistant tool call function.arguments must be valid JSON."); }
+            }
             call.set("function", f);
           }
           calls.push_back(call);
@@ -455,15 +553,45 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
     }
     Json ctx = Json::object();
     ctx.set("messages", jm);
-    if (tools.size()) ctx.set("tools", tools);
-    ctx.set("add_generation_prompt", !cont);
+    std::string forced_tool;
+    if (auto tc = body.find("tool_choice"); tc && tc->is_object())
+      if (auto fn = tc->find("function"); fn && fn->is_object()) forced_tool = fn->get_string("name", "");
+    if (tools.size()) {
+      // tools as the reference hands them to its template: the function's fields in the order description, name,
+      // parameters (then whatever else the request carried), the parameter schema as written
+      Json norm = Json::array();
+      for (auto& t : tools.items()) {
+        const Json* fn = t.find("function");
+        if (!fn || !fn->is_object()) { norm.push_back(t); continue; }
+        if (!forced_tool.empty() && fn->get_string("name", "") != forced_tool) continue;   // a named tool_choice lists that tool only
+        Json f = Json::object();
+        f.set("description", fn->find("description") ? *fn->find("description") : Json());
+        f.set("name", fn->find("name") ? *fn->find("name") : Json());
+        Json params = fn->find("parameters") ? *fn->find("parameters") : Json();
+        normalize_schema_types(params);
+        f.set("parameters", params);
+        f.set("strict", fn->find("strict") && fn->at("strict").is_bool() ? fn->at("strict") : Json(false));
+        const Json* defer = t.find("defer_loading");
+        if (defer && !defer->is_null()) f.set("defer_loading", *defer);
+        Json o = Json::object();
+        o.set("type", t.find("type") ? *t.find("type") : Json("function"));
+        o.set("function", f);
+        o.set("defer_loading", defer ? *defer : Json());
+        norm.push_back(o);
+      }
+      ctx.set("tools", norm);
+    }
+    ctx.set("add_generation_prompt", continue_text.empty() ? !cont : true);
     ctx.set("enable_thinking", enable_thinking);
+    if (!effort.empty()) ctx.set("reasoning_effort", effort);
     ctx.set("bos_token", sv.bos_token); ctx.set("eos_token", sv.eos_token);
     if (auto k = body.find("chat_template_kwargs"); k && k->is_object()) for (auto& kv : k->members()) ctx.set(kv.first, kv.second);
     try { prompt = render_jinja(sv.chat_template, ctx); }
     catch (const std::exception& e) { return error_response(400, std::string("chat template: ") + e.what()); }
-    if (cont && !msgs.empty()) {
-      // continue_final_message: cut the rendering after the last message's content (the turn stays open)
+    if (!continue_text.empty()) {
+      prompt += continue_text;               // the reopened assistant turn continues where its text stopped
+    } else if (cont && !msgs.empty()) {
+      // continue_final_message on another role: cut the rendering after the last message's content (the turn stays open)
       const std::string& last = msgs.back().content;
       const size_t at = last.empty() ? std::string::npos : prompt.rfind(last);
       if (at != std::string::npos) prompt.resize(at + last.size());

@@ -226,7 +226,11 @@ def test_server_renders_chat_requests_with_the_checkpoint_template(tmp_path):
     assert status == 200
     want_msgs = json.loads(json.dumps(msgs))
     want_msgs[2]["tool_calls"][0]["function"]["arguments"] = {"city": "Oslo"}
-    want = oracle(CHATML_TOOLS, messages=want_msgs, tools=TOOLS, add_generation_prompt=True)
+    # the template sees the tools in the server's normal form: description, name, parameters, strict, then defer_loading
+    want_tools = [{"type": "function", "function": {"description": t["function"].get("description"), "name": t["function"]["name"],
+                                                    "parameters": t["function"].get("parameters"), "strict": False},
+                   "defer_loading": None} for t in TOOLS]
+    want = oracle(CHATML_TOOLS, messages=want_msgs, tools=want_tools, add_generation_prompt=True)
     assert sv.mock_calls()[-1]["prompt"] == tk.encode(want)
     # a template that refuses the conversation turns into a 400 with its message
     sv2 = S.Server(str(tok), model_name="m", chat_template="{{ raise_exception('no system role') }}")

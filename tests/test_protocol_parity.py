@@ -85,3 +85,64 @@ def test_template_cases_replay():
             bad.append(x["name"])
     print(f"template cases: {len(cases) - len(bad)} of {len(cases)} agree; differences: {bad}")
     assert not bad, bad
+
+
+def test_request_cases_replay(tmp_path):
+    """The reference's request corpus (fixtures/request_cases.json, test crates/agens-server/tests/request_parity.rs):
+    chat-completion bodies with the prompt text and the sampling parameters the engine must receive, or the 400 error
+    the request must get.  Each body goes through the C++ server's chat handler with the reference's template and
+    generation_config and a byte-level tokenizer that carries the template's marker tokens; the mock engine records
+    the prompt ids and the sampling record.  Prompts are compared byte for byte.  Sampling fields are compared with
+    three representation differences allowed: no token cap (null) is this server's default cap, an absent
+    stop-token list is an empty one, and greedy is recorded as top_k 1 rather than temperature 0."""
+    from agens_engine_b200.serve import server as S
+    from tests import fixtures as F
+    path = os.path.join(FIX, "request_cases.json")
+    tpl_path = os.path.join(FIX, "model", "chat_template.jinja")
+    gen_path = os.path.join(FIX, "model", "generation_config.json")
+    if not all(os.path.isfile(p) for p in (path, tpl_path, gen_path)):
+        pytest.skip("request fixtures not present")
+    tj = json.loads(F.tiny_tokenizer_json())
+    nid = max(a["id"] for a in tj["added_tokens"]) + 1
+    for s in ("<|agens_start|>", "<|agens_end|>", "<|think|>", "<|/think|>", "<|call|>", "<|/call|>"):
+        tj["added_tokens"].append({"id": nid, "content": s, "single_word": False, "lstrip": False, "rstrip": False,
+                                   "normalized": False, "special": True})
+        nid += 1
+    tok_json = json.dumps(tj)
+    tok_path = tmp_path / "tokenizer.json"
+    tok_path.write_text(tok_json)
+    srv = S.Server(str(tok_path), model_name="volundr", generation_config=json.load(open(gen_path)),
+                   chat_template=open(tpl_path).read())
+    srv.use_mock([65, 66], step=1, supports_images=True)
+    tk = S.Tokenizer(tok_json)
+    keys = ("temperature", "top_p", "top_k", "min_p", "max_new_tokens", "presence_penalty", "frequency_penalty",
+            "repetition_penalty", "min_new_tokens", "ignore_eos", "stop_token_ids")
+    cases = json.load(open(path))["cases"]
+    bad = []
+    for x in cases:
+        n0 = len(srv.mock_calls())
+        status, body = srv.handle("POST", "/v1/chat/completions", x["body"])
+        calls = srv.mock_calls()
+        if "error" in x:
+            if not (status == 400 and x["error"] in body):
+                bad.append((x["name"], "error", status))
+            continue
+        if len(calls) == n0:
+            bad.append((x["name"], "no engine call", status))
+            continue
+        c = calls[-1]
+        if tk.decode(c["prompt"], skip_special=False) != x["prompt"]:
+            bad.append((x["name"], "prompt"))
+        want, got = dict(x["sampling"]), dict(c["sampling"])
+        if want.get("max_new_tokens") is None:
+            want.pop("max_new_tokens", None), got.pop("max_new_tokens", None)
+        if want.get("stop_token_ids") is None:
+            want["stop_token_ids"] = []
+        if want.get("temperature") == 0.0 and got.get("top_k") == 1:
+            for d in (want, got):
+                d.pop("temperature", None), d.pop("top_k", None)
+        diff = {k: (want.get(k), got.get(k)) for k in keys if want.get(k) != got.get(k)}
+        if diff:
+            bad.append((x["name"], "sampling", diff))
+    print(f"request cases: {len(cases) - len({b[0] for b in bad})} of {len(cases)} agree; differences: {bad}")
+    assert not bad, bad
