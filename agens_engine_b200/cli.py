@@ -412,7 +412,12 @@ def cmd_serve(ns):
         sources.append(CopyLookupSource())
     if cfg.mtp and world == 1:
         from .models.mtp import MtpHead
-        sources.append(MtpSource(MtpHead.random_init_for(m), depth=min(cfg.draft_depth, 2)))
+        if os.path.isdir(cfg.mtp):                        # a head checkpoint (mtp.* tensors); anything else: a random-init head
+            from .utils import checkpoint as K
+            head = K.load_mtp(cfg.mtp, m)
+        else:
+            head = MtpHead.random_init_for(m)
+        sources.append(MtpSource(head, depth=min(cfg.draft_depth, 2)))
     if cfg.spec_drafter:                                  # under --tp the drafter lives beside the leader, unsharded
         from .models.dense import DenseModel
         dcfg = _named_config(cfg.spec_drafter) if not os.path.isdir(cfg.spec_drafter) else None

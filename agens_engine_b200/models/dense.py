@@ -64,6 +64,8 @@ class DenseModel:
         self.use_step = self.step_mode != "off"
         self.step_uniform = False      # every step (1..16 rows) on the work split of the 9..16-row class: rows comparable bit for bit
         self.step = None
+        # prefill hands every chunk's last-layer residual rows to this callable: hidden_sink(first position, bf16 [T, d_model])
+        self.hidden_sink = None
         self._alloc_buffers()
 
     # ------------------------------------------------------------------------------------------------ weights
@@ -593,11 +595,18 @@ class DenseModel:
         self._rope3 = None
         return last
 
+    def _chunk_input(self, ids: torch.Tensor, sub_i: Optional[torch.Tensor]) -> torch.Tensor:
+        """Input rows of the first layer for a prefill chunk of more than eight tokens (bf16 [T, d_model])."""
+        return basic.embed(ids, self.embed, None, sub_rows=self._sub_rows if sub_i is not None else None, sub_index=sub_i,
+                           status=self.status)
+
     def _prefill_chunk(self, seq: int, ids: torch.Tensor, pos0: int, final: bool, want_logits: bool):
         cfg, dev = self.cfg, self.dev
         T = ids.numel()
         if T <= 8:
             out, logits = self.forward_rows(ids.tolist(), [seq] * T, want_logits)
+            if self.hidden_sink is not None:
+                self.hidden_sink(pos0, self.h_a[:T])
             # forward_rows advanced the host length itself; undo so prefill() owns the bookkeeping
             return (int(out[-1]), logits[-1] if logits is not None else None) if final else None
         from ..ops import gemm as G
@@ -606,8 +615,7 @@ class DenseModel:
         sub_i = None
         if getattr(self, "_sub_index", None) is not None:
             sub_i = self._sub_index[self._sub_slice[0]:self._sub_slice[1]].contiguous()
-        h = basic.embed(ids, self.embed, None, sub_rows=self._sub_rows if sub_i is not None else None, sub_index=sub_i,
-                        status=self.status)
+        h = self._chunk_input(ids, sub_i)
         q = torch.empty(T, cfg.q_dim, dtype=torch.bfloat16, device=dev)
         delta = None
         tiered = self.tier is not None and self.tier.n_host_pages(seq) > 0
@@ -642,6 +650,9 @@ class DenseModel:
             gu = self._linear_big(d["gate_up"], x)
             act = basic.swiglu_interleaved(gu)
             delta = self._reduce_rows(self._linear_big(d["down"], act))
+        if self.hidden_sink is not None:
+            # the residual stream after the last layer, every row of the chunk (what an MTP head reads as its context)
+            self.hidden_sink(pos0, (h.float() + delta.float()).to(torch.bfloat16))
         if not final:
             return None
         hl = (h[-1:].float() + delta[-1:].float()).to(torch.bfloat16)

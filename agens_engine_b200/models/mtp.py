@@ -36,6 +36,7 @@ class MtpHead(DenseModel):
         self.norm_e = self.norm_h = None
         self.cat = torch.zeros(M_GEMV, 2 * cfg.d_model, dtype=torch.bfloat16, device=self.dev)
         self.hid_in = torch.zeros(M_GEMV, cfg.d_model, dtype=torch.bfloat16, device=self.dev)
+        self._pair_hidden = None
 
     @staticmethod
     def random_init_for(target: DenseModel, seed: int = 7, **kw) -> "MtpHead":
@@ -73,6 +74,35 @@ class MtpHead(DenseModel):
         basic.sumsq(self.h_a[:m], self.ss_a)
         parts = self._layers_small(m, n_groups)
         self._head_small(m, parts, want_logits)
+
+    # -------------------------------------------------------------------------------------------- prompt positions
+    def _chunk_input(self, ids: torch.Tensor, sub_i) -> torch.Tensor:
+        cfg = self.cfg
+        c0, c1 = self._sub_slice
+        e = basic.embed(ids, self.embed, None, status=self.status)
+        cat = torch.cat([basic.rmsnorm(e, self.norm_e, cfg.rms_eps),
+                         basic.rmsnorm(self._pair_hidden[c0:c1].contiguous(), self.norm_h, cfg.rms_eps)], dim=1)
+        return self._linear_big(self.fc, cat)
+
+    def _prefill_chunk(self, seq: int, ids: torch.Tensor, pos0: int, final: bool, want_logits: bool):
+        if ids.numel() <= M_GEMV:                      # short tail: the row path reads its hidden rows from hid_in
+            c0, c1 = self._sub_slice
+            self.hid_in[:c1 - c0].copy_(self._pair_hidden[c0:c1])
+        return super()._prefill_chunk(seq, ids, pos0, final, want_logits)
+
+    def prefill_pairs(self, seq: int, tokens_after: torch.Tensor, hidden: torch.Tensor):
+        """Context entries for ``T`` committed positions at once (a prefill chunk of the target): ``hidden[i]`` is the
+        target's last-layer residual row of a position and ``tokens_after[i]`` the token that follows it.  Runs the
+        layer through the large-m path (tensor-core linears, prefill attention) and appends T entries to the head's
+        own KV of ``seq``; nothing is drafted.  Reference: kernels/m1/m1_mtp.cu:768 (``materialize`` after every
+        prefill chunk)."""
+        T = int(tokens_after.numel())
+        assert hidden.shape[0] == T
+        self._pair_hidden = hidden
+        try:
+            self.prefill(seq, tokens_after)
+        finally:
+            self._pair_hidden = None
 
     def forward_mtp(self, ids: List[int], hidden: torch.Tensor, seqs: List[int]):
         """Rows ``(ids[i], hidden[i])`` appended to ``seqs[i]``; returns the drafted token of every row.  The layer's

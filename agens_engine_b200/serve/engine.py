@@ -46,6 +46,7 @@ class Request:
     parked_hist: Optional[List[int]] = None
     images: Optional[List[str]] = None    # data: URLs of the request's image parts, in prompt order
     mm: Optional[dict] = None             # serve.vision.VisionFrontEnd.prepare(): encoder rows, positions
+    mtp_sinks: Optional[list] = None      # per-chunk feeders of the MTP heads while the prompt prefills
 
     @property
     def max_new(self) -> int:
@@ -500,6 +501,7 @@ class Engine:
         v.state, v.slot = WAITING, -1
         if v.parked is None:
             v.done_prompt = 0
+            v.mtp_sinks = None
         v.evictions += 1
         self.stats.evictions += 1
         self.waiting.insert(0, v)
@@ -541,10 +543,22 @@ class Engine:
         if r.mm is not None:
             kw = dict(image_rows=r.mm["rows"], image_pad_id=r.mm["pad_id"], rope_pos3=r.mm["pos3"], pair_axis=r.mm["pair_axis"],
                       rope_next=r.mm["rope_next"])
+        # MTP heads get context entries for the prompt positions from the hidden rows of every chunk (single-GPU
+        # models; the sink is made at the request's first chunk and covers the positions a prefix cache did not supply)
+        mtp = self.spec._mtp if self.spec.mtp_prompt and hasattr(self.m, "hidden_sink") and r.mm is None else []
+        if mtp and len(r.prompt) - r.done_prompt > 1 and r.mtp_sinks is None:
+            r.mtp_sinks = [s.prefill_sink(r.slot, r.prompt, start=r.done_prompt) for s in mtp]
+        sinks = r.mtp_sinks
+        if sinks:
+            self.m.hidden_sink = lambda pos0, hid: [f(pos0, hid) for f in sinks]
         try:
             res = self._with_room(r, lambda: self.m.prefill(r.slot, chunk, want_logits=final and sampled, **kw))
         except RuntimeError as e:
+            r.mtp_sinks = None
             self._finish(r, error=str(e)); return
+        finally:
+            if sinks:
+                self.m.hidden_sink = None
         if final and not self._check_device():
             return
         r.done_prompt += n
@@ -561,6 +575,7 @@ class Engine:
         self.spec.hist[r.slot] = list(r.prompt) + [tok]
         for s in self.spec.sources:
             s.begin(r.slot, self.spec.hist[r.slot])
+        r.mtp_sinks = None
         r.state = DECODE
         self._deliver(r, [tok])
 

@@ -125,10 +125,43 @@ class MtpSource(DraftSource):
         self.h, self.depth = head, depth
         self.pending: Dict[int, tuple] = {}
         self.first: Dict[int, int] = {}                 # history index of the token paired with MTP entry 0
+        self._fed: Dict[int, torch.Tensor] = {}         # last prompt position's hidden row, kept until the first token is known
 
     def begin(self, seq, prompt):
-        self.h.new_seq(seq)
+        """``prompt`` = the prompt followed by the first generated token.  When the target's prefill handed over its
+        hidden rows (:meth:`prefill_sink`), the prompt positions already have their entries and only the last prompt
+        position, whose following token is the first generated one, is fed here."""
+        if seq in self._fed:
+            last_h = self._fed.pop(seq)
+            self.absorb(seq, [prompt[-1]], last_h)
+            return
+        self._fresh(seq)
         self.first[seq] = len(prompt)
+
+    def _fresh(self, seq: int):
+        if seq in self.h.seq_pages:                     # a prefill that was given up left its entries behind
+            self.h.free_seq(seq)
+        self.pending.pop(seq, None); self._fed.pop(seq, None)
+        self.h.new_seq(seq)
+
+    def prefill_sink(self, seq: int, prompt: Sequence[int], start: int = 0):
+        """Callable for ``DenseModel.hidden_sink`` during the prefill of ``prompt[start:]`` on ``seq``: every chunk's
+        hidden rows become context entries of the head (an entry pairs the state at a prompt position with the prompt
+        token after it), so that the first draft already attends to the prompt (reference: kernels/m1/m1_mtp.cu:11,
+        :768).  ``start`` > 0: the positions before it came from a prefix cache and have no entries."""
+        self._fresh(seq)
+        self.first[seq] = start + 1
+        P = len(prompt)
+        toks = torch.tensor(list(prompt), dtype=torch.int32, device=self.h.dev)
+
+        def sink(pos0: int, hidden: torch.Tensor):
+            T = hidden.shape[0]
+            n = min(pos0 + T, P - 1) - pos0            # the last prompt position waits for the first generated token
+            if n > 0:
+                self.h.prefill_pairs(seq, toks[pos0 + 1:pos0 + 1 + n], hidden[:n])
+            if pos0 + T == P:
+                self._fed[seq] = hidden[T - 1:T].clone()
+        return sink
 
     def rewind(self, seq, n_hist):
         keep = max(n_hist - self.first[seq], 0)         # entry e pairs the hidden state with history token first + e
@@ -159,7 +192,7 @@ class MtpSource(DraftSource):
         return drafts
 
     def end(self, seq):
-        self.h.free_seq(seq); self.pending.pop(seq, None); self.first.pop(seq, None)
+        self.h.free_seq(seq); self.pending.pop(seq, None); self.first.pop(seq, None); self._fed.pop(seq, None)
 
 
 @dataclasses.dataclass
@@ -193,6 +226,7 @@ class SpecDecoder:
         self.samp: Dict[int, SamplingState] = {}
         self.stats = SpecStats()
         self._mtp = [s for s in self.sources if isinstance(s, MtpSource)]
+        self.mtp_prompt = True      # MTP heads get context entries for the prompt positions (off: entries start at the first generated token)
 
     # -------------------------------------------------------------------------------------------- sequences
     def begin(self, seq: int, prompt: Sequence[int], sampling: Optional[SamplingState] = None) -> int:
@@ -201,7 +235,13 @@ class SpecDecoder:
         t.new_seq(seq)
         self.samp[seq] = sampling or SamplingState()
         sampled = self.samp[seq].temperature > 0
-        first, logits = t.prefill(seq, torch.tensor(list(prompt), dtype=torch.int32), want_logits=sampled)
+        if self._mtp and self.mtp_prompt and len(prompt) > 1:
+            sinks = [mtp.prefill_sink(seq, prompt) for mtp in self._mtp]
+            t.hidden_sink = lambda pos0, hid: [f(pos0, hid) for f in sinks]
+        try:
+            first, logits = t.prefill(seq, torch.tensor(list(prompt), dtype=torch.int32), want_logits=sampled)
+        finally:
+            t.hidden_sink = None
         if sampled:
             first = int(self._sample(logits[None, :], [seq], [len(prompt)])[0])
         self.hist[seq] = list(prompt) + [first]

@@ -409,3 +409,83 @@ def load_model(dir_: str, device="cuda:0", rank: int = 0, world: int = 1, **kw):
     for fl in files.values():
         fl.close()
     return m.finalize()
+
+
+# ---------------------------------------------------------------------------------------------------- MTP head
+MTP_NORMS = ("pre_fc_norm_embedding.weight", "pre_fc_norm_hidden.weight", "norm.weight", "layers.0.input_layernorm.weight",
+             "layers.0.post_attention_layernorm.weight")
+MTP_LINEARS = ("fc.weight", "layers.0.self_attn.q_proj.weight", "layers.0.self_attn.k_proj.weight",
+               "layers.0.self_attn.v_proj.weight", "layers.0.self_attn.o_proj.weight", "layers.0.mlp.gate_proj.weight",
+               "layers.0.mlp.up_proj.weight", "layers.0.mlp.down_proj.weight")
+
+
+def read_mtp(dir_: str, cfg) -> Dict[str, torch.Tensor]:
+    """Reads an MTP head checkpoint: bf16 tensors named ``mtp.*`` in the ``*.safetensors`` files of ``dir_`` (the
+    layout of the reference's exporter; reader: crates/agens-cli/src/spec.rs:306-370).  Returns the tensors by their
+    name without the prefix, on the host, after checking that every tensor the dense-shaped head needs is there, is
+    bf16 and has the shape ``cfg`` implies.  Tensors of other head designs (``q_norm`` / ``k_norm``) are listed under
+    the key ``"_unexpected"`` and ignored."""
+    d, f = cfg.d_model, cfg.ffn
+    want = {"fc.weight": (d, 2 * d), "layers.0.self_attn.q_proj.weight": (cfg.q_dim, d),
+            "layers.0.self_attn.k_proj.weight": (cfg.kv_dim, d), "layers.0.self_attn.v_proj.weight": (cfg.kv_dim, d),
+            "layers.0.self_attn.o_proj.weight": (d, cfg.q_dim), "layers.0.mlp.gate_proj.weight": (f, d),
+            "layers.0.mlp.up_proj.weight": (f, d), "layers.0.mlp.down_proj.weight": (d, f)}
+    want.update({n: (d,) for n in MTP_NORMS})
+    out: Dict[str, torch.Tensor] = {}
+    extra = []
+    names = sorted(x for x in os.listdir(dir_) if x.endswith(".safetensors"))
+    if not names:
+        raise FileNotFoundError(f"mtp {dir_}: no .safetensors file")
+    for fn in names:
+        st = SafeTensorsFile(os.path.join(dir_, fn))
+        for full in st.keys():
+            if not full.startswith("mtp."):
+                continue
+            name = full[4:]
+            if name not in want:
+                extra.append(full)
+                continue
+            info = st.info[full]
+            if info["dtype"] != "BF16":
+                raise ValueError(f"mtp {full}: {info['dtype']} (bf16 expected)")
+            if tuple(info["shape"]) != want[name]:
+                raise ValueError(f"mtp {full}: shape {tuple(info['shape'])}, expected {want[name]}")
+            out[name] = st.tensor(full).clone()
+        st.close()
+    missing = [n for n in want if n not in out]
+    if missing:
+        raise ValueError(f"mtp {dir_}: missing tensors {missing}")
+    out["_unexpected"] = extra
+    return out
+
+
+def load_mtp(dir_: str, target, bits: int = BF16_LOAD_BITS, **kw):
+    """An :class:`~agens_engine_b200.models.mtp.MtpHead` for ``target`` from the ``mtp.*`` tensors of ``dir_``.  The
+    linears are quantised at load (asymmetric, ``bits`` bits, group 128 or the model's group when that is smaller; the
+    reference quantises its head to 4-bit group 128 at load as well, spec.rs:318-340); gate and up are merged row-interleaved as in the main model; embedding and
+    lm_head stay the target's."""
+    from ..models.mtp import MtpHead
+    from ..ops import linear as L
+    t = read_mtp(dir_, target.cfg)
+    dev = target.dev
+    h = MtpHead(target, **kw)
+
+    def lin(*names, interleave=False):
+        if interleave:
+            w = quant.interleave_gate_up(t[names[0]].float(), t[names[1]].float())
+        else:
+            w = torch.cat([t[n].float() for n in names])
+        return L.WqLinear.from_quant(quant.quantize(w, bits, min(128, target.cfg.group)), dev)
+
+    p = "layers.0."
+    h.layers.append({
+        "qkv": lin(p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "self_attn.v_proj.weight"),
+        "o": lin(p + "self_attn.o_proj.weight"),
+        "gate_up": lin(p + "mlp.gate_proj.weight", p + "mlp.up_proj.weight", interleave=True),
+        "down": lin(p + "mlp.down_proj.weight"),
+        "ln1": t[p + "input_layernorm.weight"].to(dev), "ln2": t[p + "post_attention_layernorm.weight"].to(dev)})
+    h.fc = lin("fc.weight")
+    h.norm_e, h.norm_h = t["pre_fc_norm_embedding.weight"].to(dev), t["pre_fc_norm_hidden.weight"].to(dev)
+    h.final_norm = t["norm.weight"].to(dev)
+    h.unexpected_tensors = t["_unexpected"]
+    return h.finalize()

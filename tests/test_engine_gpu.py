@@ -71,6 +71,38 @@ def test_engine_batches_match_single_runs(tiny):
             assert eng.spec.stats.accepted > 0
 
 
+def test_engine_feeds_prompt_positions_to_the_mtp_head(tiny):
+    """With an MTP head as draft source the engine hands every prefill chunk's hidden rows to the head: a request leaves
+    prefill with one head entry per prompt position, and the tokens stay those of a run alone."""
+    from agens_engine_b200.models.mtp import MtpHead
+    from agens_engine_b200.spec import MtpSource
+    cfg, ow = tiny
+    torch.manual_seed(13)
+    prompts = [torch.randint(0, cfg.vocab, (n,)).tolist() for n in (150, 6, 40)]
+    path = 1 if cfg.head_dim != 128 else None
+    want = [_alone(ow, p, 16, path=path, uniform=True) for p in prompts]
+    m = DenseModel.from_oracle(ow, max_seqs=4, max_ctx=512, prefill_chunk=64)
+    head = MtpHead.random_init_for(m)
+    src = MtpSource(head, depth=2)
+    seen = {}
+    begin0 = src.begin
+
+    def begin(seq, hist):                                  # entries of the head when the request enters decoding
+        begin0(seq, hist)
+        seen[len(hist) - 1] = (head.seq_len_host[seq], src.first[seq])
+    src.begin = begin
+    col = Collector()
+    eng = Engine(m, col, sources_factory=lambda: [src], max_drafts=3)
+    rids = [eng.submit(p, {"max_new_tokens": 16}) for p in prompts]
+    eng.run_until_idle(10000)
+    assert eng.idle() and not col.err
+    for rid, w in zip(rids, want):
+        assert col.toks[rid] == w, rid
+    assert seen == {150: (150, 1), 6: (6, 1), 40: (40, 1)}
+    assert eng.spec.stats.by_source.get("mtp", [0, 0])[0] > 0
+    assert m.free_pages() == m.n_pages and head.free_pages() == head.n_pages
+
+
 def test_engine_stops_limits_and_pressure(tiny):
     cfg, ow = tiny
     torch.manual_seed(12)

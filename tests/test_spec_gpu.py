@@ -191,3 +191,91 @@ def test_spec_sources_and_sampling(tiny):
         out += dec.step([0], forced_drafts={0: plain_s[len(out):len(out) + 4]})[0]
     dec.end(0)
     assert out[:n_new] == plain_s and dec.stats.accepted > 0
+
+
+def _seq_kv(model, seq, n):
+    """K and V rows of ``seq`` (layer 0) as [2, kv_heads, n, head_dim] fp32."""
+    ps = model.cfg.page_size
+    pages = model.seq_pages[seq][:(n + ps - 1) // ps]
+    kv = model.kv[0][torch.tensor(pages, device=model.dev)]              # [pages, 2, heads, page, hd]
+    return kv.permute(1, 2, 0, 3, 4).reshape(2, model.cfg.n_kv_heads, -1, model.cfg.head_dim)[:, :, :n].float()
+
+
+def test_mtp_prompt_context_entries(tiny):
+    """The MTP head gets one context entry per prompt position while the target prefills (reference:
+    kernels/m1/m1_mtp.cu:11, :768): the entries written through the large-m path equal those of the row path fed with
+    the same (hidden, next token) pairs, the first draft attends to them, and the decoded tokens stay those of plain
+    decoding."""
+    cfg, ow = tiny
+    torch.manual_seed(11)
+    prompt = torch.randint(0, cfg.vocab, (77,)).tolist()              # chunks of 32, 32 and a 13-row tail
+    n_new = 24
+    plain = _plain(ow, prompt, n_new)
+    m = DenseModel.from_oracle(ow, max_seqs=2, max_ctx=512, prefill_chunk=32)
+    head = MtpHead.random_init_for(m)
+    src = MtpSource(head, depth=2)
+    dec = SpecDecoder(m, [src], max_drafts=4)
+    captured = []
+    first_sink = src.prefill_sink
+
+    def spy(seq, p):                                                   # keeps the hidden rows the sink was given
+        f = first_sink(seq, p)
+        def g(pos0, hid):
+            captured.append((pos0, hid.clone()))
+            f(pos0, hid)
+        return g
+    src.prefill_sink = spy
+    first = dec.begin(0, prompt)
+    P = len(prompt)
+    assert first == plain[0]
+    assert [c[0] for c in captured] == [0, 32, 64] and sum(c[1].shape[0] for c in captured) == P
+    assert head.seq_len_host[0] == P and src.first[0] == 1 and 0 in src.pending
+    big = _seq_kv(head, 0, P)
+    # the same pairs through the row path (eight rows per call) on a second head with the same weights
+    hidden = torch.cat([c[1] for c in captured])
+    toks = prompt[1:] + [first]
+    head2 = MtpHead.random_init_for(m)
+    head2.new_seq(0)
+    for c in range(0, P, 8):
+        e = min(P, c + 8)
+        head2.forward_mtp(toks[c:e], hidden[c:e], [0] * (e - c))
+    small = _seq_kv(head2, 0, P)
+    err = (big - small).abs().max().item()
+    ref = small.abs().max().item()
+    assert err <= 0.03 * ref + 1e-3, (err, ref)
+    # decoding goes on from there and stays exact; the head keeps one entry per committed position
+    out = [first]
+    while len(out) < n_new:
+        out += dec.step([0])[0]
+    assert out[:n_new] == plain
+    assert head.seq_len_host[0] == len(dec.hist[0]) - 1
+    assert dec.stats.by_source.get("mtp", [0, 0])[0] > 0
+    dec.end(0)
+    # without prompt entries (the switch off) the head starts at the first generated token
+    dec = SpecDecoder(m, [MtpSource(MtpHead.random_init_for(m), depth=2)], max_drafts=4)
+    dec.mtp_prompt = False
+    assert dec.generate(0, prompt, n_new) == plain
+
+
+def test_mtp_head_from_checkpoint(tiny, tmp_path):
+    """An MTP head loaded from ``mtp.*`` tensors drafts; speculative output equals plain decoding."""
+    from agens_engine_b200.utils import checkpoint as K
+    cfg, ow = tiny
+    g = torch.Generator().manual_seed(3)
+    d, f = cfg.d_model, cfg.ffn
+    shapes = {"fc.weight": (d, 2 * d), "layers.0.self_attn.q_proj.weight": (cfg.q_dim, d),
+              "layers.0.self_attn.k_proj.weight": (cfg.kv_dim, d), "layers.0.self_attn.v_proj.weight": (cfg.kv_dim, d),
+              "layers.0.self_attn.o_proj.weight": (d, cfg.q_dim), "layers.0.mlp.gate_proj.weight": (f, d),
+              "layers.0.mlp.up_proj.weight": (f, d), "layers.0.mlp.down_proj.weight": (d, f)}
+    t = {"mtp." + n: (torch.randn(*s, generator=g) * 0.05).to(torch.bfloat16) for n, s in shapes.items()}
+    t.update({"mtp." + n: (1.0 + 0.05 * torch.randn(d, generator=g)).to(torch.bfloat16) for n in K.MTP_NORMS})
+    K.write_safetensors(str(tmp_path / "mtp.safetensors"), t)
+    torch.manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab, (40,)).tolist()
+    plain = _plain(ow, prompt, 20)
+    m = DenseModel.from_oracle(ow, max_seqs=2, max_ctx=512)
+    head = K.load_mtp(str(tmp_path), m)
+    assert head.final_norm is not m.final_norm and head.embed is m.embed and head.lm_head is m.lm_head
+    dec = SpecDecoder(m, [MtpSource(head, depth=2)], max_drafts=4)
+    assert dec.generate(0, prompt, 20) == plain
+    assert dec.stats.by_source.get("mtp", [0, 0])[0] > 0
