@@ -118,7 +118,14 @@ class CallbackBackend : public Backend {
 // ------------------------------------------------------------------------------------------------ server state
 struct HttpResponse { int status = 200; std::string content_type = "application/json", body; bool sse = false; };
 
+// Markers of the model's output language: the think block and the tool-call wrapper.  Two families are known: the
+// ChatML one and the reference model's (<|think|> ... <|/think|>, <|call|> ... <|/call|>); the checkpoint's chat template
+// tells which (it writes the markers itself).
+struct TagSet { std::string think_open = "<think>", think_close = "</think>", call_open = "<tool_call>", call_close = "</tool_call>"; };
+
 struct Server {
+  TagSet tags;
+  std::vector<int> think_close_ids;        // token ids of the closing think tag (reasoning token count)
   Tokenizer tok;
   bool has_tok = false;
   std::string model_name = "b200-engine";
@@ -146,10 +153,12 @@ static std::string hex_id(int n) {
   return s;
 }
 
-static HttpResponse error_response(int status, const std::string& msg, const std::string& type = "invalid_request_error") {
-  Json e = Json::object(), o = Json::object();
-  e.set("message", msg); e.set("type", type); e.set("param", Json()); e.set("code", status);
-  o.set("error", e);
+// Error bodies have the reference server's shape (crates/agens-server/src/openai.rs:17-42): a flat object; requests that
+// fail validation are "BadRequestError", those refused while the conversation is converted (template errors, bad
+// tool-call arguments in the history) "BadRequest".
+static HttpResponse error_response(int status, const std::string& msg, const std::string& type = "BadRequestError") {
+  Json o = Json::object();
+  o.set("object", "error"); o.set("message", msg); o.set("type", type); o.set("param", Json()); o.set("code", status);
   HttpResponse r; r.status = status; r.body = o.dump();
   return r;
 }
@@ -240,19 +249,24 @@ static Json request_tools(const Json& body) {
 }
 
 static HttpResponse run_generation(Server& sv, const Json& body, bool chat, const std::vector<int>& prompt_ids, const Json& sampling,
-                                   bool starts_in_reasoning, const std::string& session_id, Emit* emit) {
+                                   bool starts_in_reasoning, const std::string& session_id, Emit* emit, bool thinking = false) {
   const bool stream = body.get_bool("stream", false);
-  const bool include_usage = body.find("stream_options") && body.at("stream_options").get_bool("include_usage", false);
+  const Json* so = body.find("stream_options");
+  const bool include_usage = so && so->is_object() && so->get_bool("include_usage", false);
+  const bool continuous_usage = include_usage && so->get_bool("continuous_usage_stats", false);
   const bool separate_reasoning = body.get_bool("separate_reasoning", true);
   const bool stream_reasoning = body.get_bool("stream_reasoning", true);
   const bool skip_special = body.get_bool("skip_special_tokens", true);
   const bool no_stop_trim = body.get_bool("no_stop_trim", false);
   const Json tools = request_tools(body);
+  const bool tools_active = chat && tools.size() > 0;
+  const TagSet& tg = sv.tags;
   std::vector<std::string> stops;
   if (auto p = body.find("stop")) { if (p->is_string()) stops.push_back(p->as_string()); else if (p->is_array()) for (auto& s : p->items()) if (s.is_string()) stops.push_back(s.as_string()); }
   std::vector<int> stop_ids;
   for (auto& v : sampling.at("stop_token_ids").items()) stop_ids.push_back((int)v.as_int());
   const long long max_new = sampling.get_int("max_new_tokens", sv.max_tokens_default);
+  const long long min_new = sampling.get_int("min_new_tokens", 0);
 
   GenRequest req;
   req.id = sv.next_req++;
@@ -264,17 +278,39 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
   sv.n_prompt_tokens += (long long)prompt_ids.size();
   if (max_new > 0) sv.backend->generate(req, ts); else ts->push(nullptr, 0, true);
 
-  const std::string id = (chat ? "chatcmpl-" : "cmpl-") + hex_id(24);
+  // The wire format is the reference server's (crates/agens-server/src/openai.rs:848-1180): a client-chosen "rid" is the
+  // response id; every choice carries logprobs / matched_stop; usage counts the tokens through the stop token and the
+  // reasoning tokens through the closing think tag.
+  const std::string id = body.find("rid") && body.at("rid").is_string() ? body.at("rid").as_string()
+                                                                          : (chat ? "chatcmpl-" : "cmpl-") + hex_id(24);
   const long long created = (long long)std::time(nullptr);
   Detokenizer detok(&sv.tok, skip_special);
-  ReasoningParser rp(starts_in_reasoning, stream_reasoning);
-  ToolStreamParser tp(tools);
+  ReasoningParser rp(starts_in_reasoning, stream_reasoning, tg.think_open, tg.think_close);
+  ToolStreamParser tp(tools, tg.call_open, tg.call_close);
+  if (tg.think_open != "<think>") rp.keep_newlines_after_close(true);
+  if (tg.call_open != "<tool_call>" && tools_active) { rp.set_interrupt(tg.call_open); tp.content_before_calls_only(true); }
+  // streamed calls of the <function=...> family go out piece by piece (name, then the arguments as parameters complete)
+  ToolDeltaParser dp(tools, tg.call_open, tg.call_close);
+  const bool call_deltas = stream && tools_active && tg.call_open != "<tool_call>";
   std::string text_all, content_all, reasoning_all, sse_all, pending_text;
   std::vector<ToolCall> calls;
   long long n_out = 0, n_reasoning_tokens = 0;
   std::string finish = "length";
-  bool in_reasoning_tokens = starts_in_reasoning;
+  Json matched = Json();                         // stop token id, stop string, or null
+  // reasoning tokens: every token of a request with thinking on, through the closing think tag when one comes
+  bool count_reasoning = (thinking || starts_in_reasoning) && !sv.think_close_ids.empty();
+  bool force_nonempty = false;                   // chat_template_kwargs.force_nonempty_content: reasoning alone becomes the content
+  if (auto k = body.find("chat_template_kwargs"); k && k->is_object()) force_nonempty = k->get_bool("force_nonempty_content", false);
+  std::string whole;                             // non-streaming: the text is parsed once, when it is complete
+  std::string final_text;                        // streamed completions: text of the last step
+  size_t think_match = 0;
 
+  auto usage_json = [&]() {
+    Json u = Json::object();
+    u.set("prompt_tokens", (long long)prompt_ids.size()); u.set("total_tokens", (long long)prompt_ids.size() + n_out);
+    u.set("completion_tokens", n_out); u.set("prompt_tokens_details", Json()); u.set("reasoning_tokens", n_reasoning_tokens);
+    return u;
+  };
   auto send = [&](const Json& chunk) {
     const std::string ev = "data: " + chunk.dump() + "\n\n";
     sse_all += ev;
@@ -285,26 +321,49 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
     c.set("id", id); c.set("object", chat ? "chat.completion.chunk" : "text_completion"); c.set("created", created); c.set("model", sv.model_name);
     return c;
   };
-  auto delta_chunk = [&](const std::string& content, const std::string& reasoning, const Json& tool_delta, const Json& fin) {
-    Json c = base_chunk(), ch = Json::object();
-    ch.set("index", 0);
-    if (chat) {
-      Json d = Json::object();
-      if (!content.empty()) d.set("content", content);
-      if (!reasoning.empty()) d.set("reasoning_content", reasoning);
-      if (!tool_delta.is_null()) d.set("tool_calls", tool_delta);
-      ch.set("delta", d);
-    } else ch.set("text", content);
-    ch.set("finish_reason", fin);
-    Json arr = Json::array(); arr.push_back(ch);
+  auto wrap = [&](Json choice, bool with_usage_key) {
+    Json c = base_chunk(), arr = Json::array();
+    arr.push_back(std::move(choice));
     c.set("choices", arr);
+    if (continuous_usage) c.set("usage", usage_json());
+    else if (with_usage_key) c.set("usage", Json());
+    return c;
+  };
+  auto choice_of = [&](Json delta) {
+    Json ch = Json::object();
+    ch.set("index", 0); ch.set("delta", std::move(delta)); ch.set("logprobs", Json()); ch.set("finish_reason", Json()); ch.set("matched_stop", Json());
+    return ch;
+  };
+  // chat deltas come in the reference's two shapes: the short one (reasoning / plain content) and, once the request has
+  // tools, the long one with every field present
+  auto reasoning_chunk = [&](const std::string& r) { Json d = Json::object(); d.set("reasoning_content", r); return wrap(choice_of(d), false); };
+  auto content_chunk = [&](const std::string& c) {
+    Json d = Json::object();
+    if (tools_active) { d.set("role", Json()); d.set("content", c); d.set("reasoning_content", Json()); d.set("tool_calls", Json()); }
+    else { d.set("reasoning_content", Json()); d.set("content", c); }
+    return wrap(choice_of(d), tools_active);
+  };
+  auto call_chunk = [&](const Json& id_, long long index, const Json& name, const std::string& args) {
+    Json fn = Json::object(), tc = Json::object(), arr = Json::array(), d = Json::object();
+    fn.set("name", name); fn.set("arguments", args);
+    tc.set("id", id_); tc.set("index", index); tc.set("type", "function"); tc.set("function", fn);
+    arr.push_back(tc);
+    d.set("role", Json()); d.set("content", Json()); d.set("reasoning_content", Json()); d.set("tool_calls", arr);
+    return wrap(choice_of(d), true);
+  };
+  auto text_chunk = [&](const std::string& t, const Json& fin, const Json& ms) {      // /v1/completions
+    Json ch = Json::object();
+    ch.set("index", 0); ch.set("text", t); ch.set("logprobs", Json()); ch.set("finish_reason", fin); ch.set("matched_stop", ms);
+    Json c = base_chunk(), arr = Json::array();
+    arr.push_back(ch); c.set("choices", arr);
+    c.set("usage", continuous_usage ? usage_json() : Json());
     return c;
   };
   if (stream && chat) {
-    Json c = base_chunk(), ch = Json::object(), d = Json::object();
-    d.set("role", "assistant"); d.set("content", "");
-    ch.set("index", 0); ch.set("delta", d); ch.set("finish_reason", Json());
-    Json arr = Json::array(); arr.push_back(ch); c.set("choices", arr);
+    Json d = Json::object();
+    d.set("reasoning_content", Json()); d.set("role", "assistant"); d.set("content", "");
+    Json c = base_chunk(), arr = Json::array();
+    arr.push_back(choice_of(d)); c.set("choices", arr);
     send(c);
   }
   // text -> (reasoning, content, tool calls) -> client
@@ -313,71 +372,119 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
     if (chat && separate_reasoning) { ro = rp.push(piece); if (last) { auto f = rp.finish(); ro.content += f.content; ro.reasoning += f.reasoning; } }
     else ro.content = piece;
     reasoning_all += ro.reasoning;
+    if (call_deltas) {
+      if (!ro.reasoning.empty()) send(reasoning_chunk(ro.reasoning));
+      const std::vector<ToolDelta> ds = dp.push(ro.content);
+      std::string plain;                          // the content of one step goes out first, then the call pieces in order
+      for (auto& d : ds) if (d.kind == ToolDelta::Content) plain += d.text;
+      if (!plain.empty()) { content_all += plain; send(content_chunk(plain)); }
+      for (auto& d : ds) {
+        if (d.kind == ToolDelta::Content) continue;
+        if (d.kind == ToolDelta::Start) { send(call_chunk(Json("call_" + hex_id(24)), d.index, Json(d.text), "")); calls.push_back(ToolCall{d.text, ""}); }
+        else { send(call_chunk(Json(), d.index, Json(), d.text)); if (d.index >= 0 && d.index < (int)calls.size()) calls[d.index].arguments_json += d.text; }
+      }
+      return;
+    }
     ToolParse t;
-    if (chat && tools.size()) { t = tp.push(ro.content); if (last) { auto f = tp.finish(); t.content += f.content; for (auto& c : f.calls) t.calls.push_back(c); } }
+    if (tools_active) { t = tp.push(ro.content); if (last) { auto f = tp.finish(); t.content += f.content; for (auto& c : f.calls) t.calls.push_back(c); } }
     else t.content = ro.content;
     content_all += t.content;
-    Json tool_delta;
-    if (!t.calls.empty()) {
-      tool_delta = Json::array();
-      for (auto& c : t.calls) {
-        Json tc = Json::object(), fn = Json::object();
-        tc.set("index", (long long)calls.size()); tc.set("id", "call_" + hex_id(24)); tc.set("type", "function");
-        fn.set("name", c.name); fn.set("arguments", c.arguments_json);
-        tc.set("function", fn);
-        tool_delta.push_back(tc);
-        calls.push_back(c);
-      }
+    if (!stream) { for (auto& c : t.calls) calls.push_back(c); return; }
+    if (!ro.reasoning.empty()) send(reasoning_chunk(ro.reasoning));
+    if (!t.content.empty()) send(chat ? content_chunk(t.content) : text_chunk(t.content, Json(), Json()));
+    for (auto& c : t.calls) {
+      // a call goes out as its header (id, name, empty arguments) followed by its arguments
+      const long long index = (long long)calls.size();
+      send(call_chunk(Json("call_" + hex_id(24)), index, Json(c.name), ""));
+      send(call_chunk(Json(), index, Json(), c.arguments_json));
+      calls.push_back(c);
     }
-    if (stream && (!t.content.empty() || !ro.reasoning.empty() || !tool_delta.is_null())) send(delta_chunk(t.content, ro.reasoning, tool_delta, Json()));
   };
 
   std::vector<int> step_ids;
   bool done = false;
   while (!done && ts->pop(step_ids)) {
+    std::string step_text;                        // one engine step = one event per kind of text
+    size_t step_hold = 0;
+    // reasoning tokens are counted per engine step, before the step is cut at a stop (the reference counts that way):
+    // tokens through the closing think tag
+    for (size_t i = 0; i < step_ids.size() && count_reasoning && n_out + (long long)i < max_new; ++i) {
+      const int tkn = step_ids[i];
+      ++n_reasoning_tokens;
+      think_match = tkn == sv.think_close_ids[think_match] ? think_match + 1 : (tkn == sv.think_close_ids[0] ? 1 : 0);
+      if (think_match == sv.think_close_ids.size()) count_reasoning = false;
+    }
     for (int tkn : step_ids) {
       if (n_out >= max_new) { done = true; break; }
       ++n_out;
-      const bool is_stop_id = std::find(stop_ids.begin(), stop_ids.end(), tkn) != stop_ids.end() && n_out > sampling.get_int("min_new_tokens", 0);
-      if (is_stop_id) { finish = "stop"; done = true; break; }
-      if (in_reasoning_tokens) ++n_reasoning_tokens;
+      const bool is_stop_id = std::find(stop_ids.begin(), stop_ids.end(), tkn) != stop_ids.end() && n_out > min_new;
+      if (is_stop_id) { finish = "stop"; matched = Json((long long)tkn); done = true; break; }
       std::string piece = detok.push({tkn});
       text_all += piece;
-      if (in_reasoning_tokens && text_all.find("</think>") != std::string::npos) in_reasoning_tokens = false;
       pending_text += piece;
       size_t hold = 0;
       const size_t sp = find_stop(pending_text, stops, hold);
       if (sp != std::string::npos) {
         std::string upto = pending_text.substr(0, sp);
-        if (no_stop_trim) for (auto& s : stops) if (pending_text.compare(sp, s.size(), s) == 0) { upto += s; break; }
-        process_text(upto, false);
+        for (auto& s : stops) if (!s.empty() && pending_text.compare(sp, s.size(), s) == 0) { matched = Json(s); if (no_stop_trim) upto += s; break; }
+        step_text += upto;
         pending_text.clear();
         finish = "stop"; done = true; break;
       }
-      const std::string ready = pending_text.substr(0, pending_text.size() - hold);
-      pending_text.erase(0, ready.size());
-      if (!ready.empty()) process_text(ready, false);
+      step_hold = hold;
       if (n_out >= max_new) { done = true; break; }
     }
+    // once per engine step: while the end of the text could still grow into a stop string nothing of it goes out
+    if (step_hold == 0 || finish == "stop") { step_text += pending_text; pending_text.clear(); }     // (a matched stop string left nothing pending)
+    if (!stream) whole += step_text;
+    else if (!chat) {
+      // /v1/completions: one event per engine step; the step that ends the request carries its text and the finish reason
+      content_all += step_text;
+      if (done) final_text = step_text;
+      else if (!step_text.empty()) send(text_chunk(step_text, Json(), Json()));
+    } else if (!step_text.empty()) process_text(step_text, false);
     if (emit && !emit->alive()) { ts->cancel(); done = true; finish = "abort"; }
   }
   ts->cancel();     // the engine stops at its next step once the receiver is gone
   if (auto cb = dynamic_cast<CallbackBackend*>(sv.backend.get())) cb->drop(req.id);
-  if (!ts->error.empty()) { sv.n_errors++; return error_response(500, ts->error, "internal_error"); }
+  if (!ts->error.empty()) { sv.n_errors++; return error_response(500, ts->error, "InternalServerError"); }
   { std::string tail = detok.finish(); if (finish != "stop") pending_text += tail; }
-  process_text(finish == "stop" ? std::string() : pending_text, true);
-  if (!calls.empty()) finish = "tool_calls";
+  if (!stream) {
+    whole += finish == "stop" ? std::string() : pending_text;
+    // with the whole text in hand a think block that closes later keeps a call marker inside it as reasoning
+    if (whole.find(tg.think_close) != std::string::npos) rp.set_interrupt("");
+    process_text(whole, true);
+  } else if (!chat) {
+    if (finish != "stop") { final_text += pending_text; content_all += pending_text; }
+  } else process_text(finish == "stop" ? std::string() : pending_text, true);
+  if (force_nonempty && chat && content_all.empty() && calls.empty() && !reasoning_all.empty()) {
+    if (stream) send(content_chunk(reasoning_all));
+    content_all = reasoning_all;
+    reasoning_all.clear();
+  }
+  // a stop token after at least one call reads as "tool_calls"; the complete response then reports no matched stop
+  const bool by_calls = !calls.empty() && finish == "stop" && matched.is_int();
   sv.n_completion_tokens += n_out;
-
-  Json usage = Json::object();
-  usage.set("prompt_tokens", (long long)prompt_ids.size()); usage.set("completion_tokens", n_out);
-  usage.set("total_tokens", (long long)prompt_ids.size() + n_out);
-  Json det = Json::object(); det.set("reasoning_tokens", n_reasoning_tokens); usage.set("completion_tokens_details", det);
 
   HttpResponse resp;
   if (stream) {
-    send(delta_chunk("", "", Json(), Json(finish)));
-    if (include_usage) { Json c = base_chunk(); c.set("choices", Json::array()); c.set("usage", usage); send(c); }
+    if (chat) {
+      Json d = Json::object(), ch = Json::object();
+      d.set("reasoning_content", Json());
+      ch.set("index", 0); ch.set("delta", d); ch.set("logprobs", Json()); ch.set("finish_reason", by_calls ? "tool_calls" : finish); ch.set("matched_stop", matched);
+      Json c = base_chunk(), arr = Json::array();
+      arr.push_back(ch); c.set("choices", arr);
+      send(c);
+    } else send(text_chunk(final_text, Json(finish), matched));
+    if (include_usage) {
+      Json c = base_chunk(), u = usage_json();
+      if (!chat) {                                // the completions usage event leaves absent details out
+        Json v = Json::object();
+        for (auto& kv : u.members()) if (!kv.second.is_null()) v.set(kv.first, kv.second);
+        u = v;
+      }
+      c.set("choices", Json::array()); c.set("usage", u); send(c);
+    }
     sse_all += "data: [DONE]\n\n";
     if (emit) emit->write("data: [DONE]\n\n");
     resp.sse = true; resp.content_type = "text/event-stream"; resp.body = sse_all;
@@ -389,18 +496,27 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
   if (chat) {
     Json m = Json::object();
     m.set("role", "assistant");
-    m.set("content", content_all.empty() && !calls.empty() ? Json() : Json(content_all));
+    m.set("content", content_all);
     m.set("reasoning_content", reasoning_all.empty() ? Json() : Json(reasoning_all));
     if (!calls.empty()) {
       Json arr = Json::array();
-      for (auto& c : calls) { Json tc = Json::object(), fn = Json::object(); tc.set("id", "call_" + hex_id(24)); tc.set("type", "function"); fn.set("name", c.name); fn.set("arguments", c.arguments_json); tc.set("function", fn); arr.push_back(tc); }
+      long long index = 0;
+      for (auto& c : calls) {
+        Json tc = Json::object(), fn = Json::object();
+        tc.set("id", "call_" + hex_id(24)); tc.set("index", index++); tc.set("type", "function");
+        fn.set("name", c.name); fn.set("arguments", c.arguments_json);
+        tc.set("function", fn); arr.push_back(tc);
+      }
       m.set("tool_calls", arr);
     } else m.set("tool_calls", Json());
     ch.set("message", m);
   } else ch.set("text", content_all);
-  ch.set("finish_reason", finish);
+  ch.set("logprobs", Json());
+  ch.set("finish_reason", by_calls ? "tool_calls" : finish);
+  ch.set("matched_stop", by_calls ? Json() : matched);
   Json arr = Json::array(); arr.push_back(ch);
-  o.set("choices", arr); o.set("usage", usage);
+  o.set("choices", arr); o.set("usage", usage_json());
+  Json meta = Json::object(); meta.set("weight_version", "default"); o.set("metadata", meta);
   resp.body = o.dump();
   return resp;
 }
@@ -523,6 +639,29 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
     else msgs.back().role = "user";
   }
   const Json tools = body.find("tools") && body.at("tools").is_array() && body.get_string("tool_choice", "auto") != "none" ? body.at("tools") : Json::array();
+  {
+    // tool_choice against the tools, and the token cap against the context (openai.rs:671-706 of the reference)
+    const bool has_tools = body.find("tools") && body.at("tools").is_array() && body.at("tools").size() > 0;
+    const Json* tc = body.find("tool_choice");
+    if (tc && tc->is_string() && tc->as_string() == "required" && !has_tools)
+      return error_response(400, "Tools cannot be empty if tool choice is set to required.");
+    if (tc && tc->is_object()) {
+      std::string name;
+      if (auto fn = tc->find("function"); fn && fn->is_object()) name = fn->get_string("name", "");
+      if (!has_tools) return error_response(400, "Tools cannot be empty if tool choice is set to a specific tool.");
+      bool exists = false;
+      for (auto& t : body.at("tools").items())
+        if (auto fn = t.find("function"); fn && fn->is_object() && fn->get_string("name", "") == name) exists = true;
+      if (!exists) return error_response(400, "Tool '" + name + "' not found in tools list.");
+    }
+    long long cap = 0;
+    if (auto p = body.find("max_completion_tokens"); p && p->is_number() && p->as_int() != 0) cap = p->as_int();
+    else if (auto q = body.find("max_tokens"); q && q->is_number()) cap = q->as_int();
+    const long long ctx_len = sv.backend->context_length();
+    if (cap != 0 && cap > ctx_len)
+      return error_response(400, "max_completion_tokens is too large: " + std::to_string(cap) + ".This model supports at most " +
+                                     std::to_string(ctx_len) + " completion tokens.");
+  }
   std::string prompt;
   if (sv.chat_template.empty()) prompt = render_chatml(msgs, tools, !cont, enable_thinking, cont);
   else {
@@ -540,7 +679,8 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
             Json f = *fn;
             if (const Json* a = fn->find("arguments"); a && a->is_string()) {
               try { f.set("arguments", Json::parse(a->as_string())); }
-              catch (const std::exception&) { return error_response(400, "Assistant tool call function.arguments must be valid JSON."); }
+              catch (const std::exception&) { return error_response(400, "Assistant tool call function.arguments must be valid JSON.", "BadRequest"); }
+              if (!f.at("arguments").is_object()) return error_response(400, "Assistant tool call function.arguments must be a JSON object.", "BadRequest");
             }
             call.set("function", f);
           }
@@ -587,7 +727,7 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
     ctx.set("bos_token", sv.bos_token); ctx.set("eos_token", sv.eos_token);
     if (auto k = body.find("chat_template_kwargs"); k && k->is_object()) for (auto& kv : k->members()) ctx.set(kv.first, kv.second);
     try { prompt = render_jinja(sv.chat_template, ctx); }
-    catch (const std::exception& e) { return error_response(400, std::string("chat template: ") + e.what()); }
+    catch (const std::exception& e) { return error_response(400, e.what(), "BadRequest"); }
     if (!continue_text.empty()) {
       prompt += continue_text;               // the reopened assistant turn continues where its text stopped
     } else if (cont && !msgs.empty()) {
@@ -604,7 +744,11 @@ static HttpResponse handle_chat(Server& sv, const Json& body, const std::string&
   const std::vector<int> ids = sv.tok.encode(prompt);
   if ((long long)ids.size() >= sv.backend->context_length()) return error_response(400, "the prompt is longer than the model's context length");
   const std::string session = !session_hdr.empty() ? session_hdr : body.get_string("session_id", "");
-  return run_generation(sv, body, true, ids, sampling, /*starts_in_reasoning=*/false, session, emit);
+  // a template that opens the think block itself leaves the generation inside it
+  const size_t last_open = prompt.rfind(sv.tags.think_open), last_close = prompt.rfind(sv.tags.think_close);
+  const bool in_think = !sv.chat_template.empty() && last_open != std::string::npos &&
+                        (last_close == std::string::npos || last_close < last_open);
+  return run_generation(sv, body, true, ids, sampling, in_think, session, emit, enable_thinking);
 }
 
 static HttpResponse handle_completion(Server& sv, const Json& body, const std::string& session_hdr, Emit* emit) {
@@ -638,7 +782,7 @@ static HttpResponse route(Server& sv, const std::string& method, const std::stri
   auto model_card = [&]() { Json m = Json::object(); m.set("id", sv.model_name); m.set("object", "model"); m.set("created", (long long)std::time(nullptr)); m.set("owned_by", "b200-engine"); m.set("max_model_len", sv.backend->context_length()); m.set("engine_version", "0.1.0"); return m; };
   if (method == "GET" && path == "/v1/models") { Json o = Json::object(), a = Json::array(); a.push_back(model_card()); o.set("object", "list"); o.set("data", a); HttpResponse r; r.body = o.dump(); return r; }
   if (method == "GET" && path.compare(0, 11, "/v1/models/") == 0) {
-    if (path.substr(11) != sv.model_name) return error_response(404, "model not found: " + path.substr(11), "not_found_error");
+    if (path.substr(11) != sv.model_name) return error_response(404, "model not found: " + path.substr(11), "NotFoundError");
     HttpResponse r; r.body = model_card().dump(); return r;
   }
   if (method == "POST" && (path == "/v1/chat/completions" || path == "/v1/completions")) {
@@ -646,7 +790,7 @@ static HttpResponse route(Server& sv, const std::string& method, const std::stri
     try { body = Json::parse(body_text); } catch (const std::exception& e) { return error_response(400, std::string("invalid JSON: ") + e.what()); }
     return path == "/v1/chat/completions" ? handle_chat(sv, body, session_hdr, emit) : handle_completion(sv, body, session_hdr, emit);
   }
-  return error_response(404, "no route for " + method + " " + path, "not_found_error");
+  return error_response(404, "no route for " + method + " " + path, "NotFoundError");
 }
 
 // ------------------------------------------------------------------------------------------------ HTTP/1.1 over sockets
@@ -731,10 +875,19 @@ B2H_API void* b2h_server_new(const char* config_json, char* err, int err_cap) {
     sv->model_name = c.get_string("model_name", "b200-engine");
     if (auto g = c.find("generation_config"); g && g->is_object()) sv->gen_defaults = *g;
     if (auto e = c.find("eos_token_ids"); e && e->is_array()) for (auto& v : e->items()) sv->eos_ids.push_back((int)v.as_int());
+    if (sv->eos_ids.empty()) {                 // generation_config.json names the end-of-sequence ids (one id or a list)
+      if (auto e = sv->gen_defaults.find("eos_token_id")) {
+        if (e->is_int()) sv->eos_ids.push_back((int)e->as_int());
+        else if (e->is_array()) for (auto& v : e->items()) if (v.is_int()) sv->eos_ids.push_back((int)v.as_int());
+      }
+    }
     sv->max_tokens_default = c.get_int("max_tokens_default", 32768);
     sv->chat_template = c.get_string("chat_template", "");
     sv->bos_token = c.get_string("bos_token", "");
     sv->eos_token = c.get_string("eos_token", "");
+    if (sv->chat_template.find("<|think|>") != std::string::npos) { sv->tags.think_open = "<|think|>"; sv->tags.think_close = "<|/think|>"; }
+    if (sv->chat_template.find("<|call|>") != std::string::npos) { sv->tags.call_open = "<|call|>"; sv->tags.call_close = "<|/call|>"; }
+    if (sv->has_tok) sv->think_close_ids = sv->tok.encode(sv->tags.think_close);
     sv->backend = std::make_shared<MockBackend>();
     return sv;
   } catch (const std::exception& e) { if (err) snprintf(err, err_cap, "%s", e.what()); return nullptr; }
@@ -879,6 +1032,7 @@ static char* parse_output_with(const char* text, const char* tools_json, int sta
   std::vector<ToolCall> calls;
   ReasoningParser rp(starts_in_reasoning != 0, true, think_open, think_close);
   ToolStreamParser tp(with_calls ? tools : Json::array(), call_open, call_close);
+  if (think_open != "<think>") rp.keep_newlines_after_close(true);
   if (call_open != "<tool_call>" && with_calls) {          // the other template family: its parsers' conventions
     rp.set_interrupt(call_open);
     tp.content_before_calls_only(true);

@@ -381,6 +381,11 @@ ReasoningParser::Out ReasoningParser::push(const std::string& delta) {
         if (partial_suffix(buf_, open_) && buf_.find_first_not_of(" \n\t") != std::string::npos &&
             buf_.find_first_not_of(" \n\t") + partial_suffix(buf_, open_) == buf_.size()) return o;   // may still become the tag
       }
+      if (stripped_open_ && !buf_.empty() && buf_.size() < open_.size() && open_.compare(0, buf_.size(), buf_) == 0) return o;   // may become an opening tag
+      if (stripped_open_ && !open_.empty() && buf_.compare(0, open_.size(), open_) == 0) {
+        // a later opening tag at the start of a piece of output begins another think block
+        buf_.erase(0, open_.size()); in_ = true; continue;
+      }
       if (strip_nl_) {       // newlines right after the closing tag belong to the block, whichever chunk brings them
         size_t a = buf_.find_first_not_of('\n');
         if (a == std::string::npos) { buf_.clear(); return o; }
@@ -413,7 +418,7 @@ ReasoningParser::Out ReasoningParser::push(const std::string& delta) {
       buf_.erase(0, cl + close_.size());
       in_ = false;
       if (stream_) o.reasoning += r; else { held_reasoning_ += r; o.reasoning += held_reasoning_; held_reasoning_.clear(); }
-      strip_nl_ = true;
+      strip_nl_ = !keep_nl_;
       stripped_open_ = true;
       continue;
     }
@@ -648,7 +653,7 @@ static bool parse_function_block(const std::string& body, const Json& tools, Too
     args.set(key, typed_value(strip_nl(body.substr(kend + 1, stop - kend - 1)), schema, key));
     pos = (vend != std::string::npos && vend == stop) ? vend + 12 : stop;
   }
-  out.arguments_json = args.dump_python();
+  out.arguments_json = args.dump(Json::Style{true, false});
   return true;
 }
 ToolParse parse_tool_calls(const std::string& text, const Json& tools) { return parse_tool_calls(text, tools, "<tool_call>", "</tool_call>"); }
@@ -684,7 +689,7 @@ ToolParse parse_tool_calls(const std::string& text, const Json& tools, const std
           tc.name = j.get_string("name", "");
           const Json* ar = j.find("arguments");
           if (!ar) ar = j.find("parameters");
-          tc.arguments_json = ar ? (ar->is_string() ? ar->as_string() : ar->dump_python()) : "{}";
+          tc.arguments_json = ar ? (ar->is_string() ? ar->as_string() : ar->dump(Json::Style{true, false})) : "{}";
           ok = !tc.name.empty();
         } catch (...) { ok = false; }
       }
@@ -756,6 +761,103 @@ ToolParse ToolStreamParser::finish() {
   }
   buf_.clear();
   return out;
+}
+
+// ---- incremental tool calls ----------------------------------------------------------------------------------------
+static bool is_prefix_of(const std::string& s, const std::string& full) { return s.size() <= full.size() && full.compare(0, s.size(), s) == 0; }
+static bool starts_with(const std::string& s, const std::string& p) { return s.size() >= p.size() && s.compare(0, p.size(), p) == 0; }
+
+std::vector<ToolDelta> ToolDeltaParser::push(const std::string& delta) {
+  std::vector<ToolDelta> out;
+  auto content = [&](const std::string& t) {
+    if (t.empty()) return;
+    if (!out.empty() && out.back().kind == ToolDelta::Content) out.back().text += t; else out.push_back({ToolDelta::Content, -1, t});
+  };
+  auto args = [&](const std::string& t) { out.push_back({ToolDelta::Args, n_calls_ - 1, t}); };
+  auto skip_ws = [&]() { size_t a = buf_.find_first_not_of(" \n\r\t"); buf_.erase(0, a == std::string::npos ? buf_.size() : a); };
+  static const std::string kFn = "<function=", kFnEnd = "</function>", kPar = "<parameter=", kParEnd = "</parameter>";
+  buf_ += delta;
+  while (true) {
+    if (st_ == Outside) {
+      const size_t p = buf_.find(open_);
+      if (p == std::string::npos) {
+        const size_t keep = partial_suffix(buf_, open_);      // may still become the wrapper tag
+        content(buf_.substr(0, buf_.size() - keep));
+        buf_.erase(0, buf_.size() - keep);
+        return out;
+      }
+      content(buf_.substr(0, p));
+      buf_.erase(0, p + open_.size());
+      st_ = WantFunction;
+    } else if (st_ == WantFunction) {
+      skip_ws();
+      if (buf_.empty()) return out;
+      if (starts_with(buf_, kFn)) {
+        const size_t gt = buf_.find('>');
+        if (gt == std::string::npos) return out;
+        const std::string name = buf_.substr(kFn.size(), gt - kFn.size());
+        buf_.erase(0, gt + 1);
+        schema_ = tool_schema(tools_, name);
+        out.push_back({ToolDelta::Start, n_calls_++, name});
+        n_params_ = 0; opened_ = false;
+        st_ = InBody;
+      } else if (starts_with(buf_, close_)) { buf_.erase(0, close_.size()); st_ = Outside; }
+      else if (is_prefix_of(buf_, kFn) || is_prefix_of(buf_, close_)) return out;
+      else {
+        // something else follows the wrapper tag: it is skipped up to a function header or the closing tag, whichever
+        // comes (the reference's detector keeps waiting for a header the same way)
+        const size_t f = buf_.find(kFn), c = buf_.find(close_);
+        if (f == std::string::npos && c == std::string::npos) {
+          const size_t keep = std::max(partial_suffix(buf_, kFn), partial_suffix(buf_, close_));
+          buf_.erase(0, buf_.size() - keep);
+          return out;
+        }
+        buf_.erase(0, std::min(f, c));
+      }
+    } else if (st_ == InBody) {
+      skip_ws();
+      if (buf_.empty()) return out;
+      if (starts_with(buf_, kPar)) {
+        const size_t gt = buf_.find('>');
+        if (gt == std::string::npos) return out;
+        key_ = buf_.substr(kPar.size(), gt - kPar.size());
+        buf_.erase(0, gt + 1);
+        st_ = InValue;
+      } else if (starts_with(buf_, kFnEnd)) {
+        if (!opened_) { args("{"); opened_ = true; }
+        args("}");
+        buf_.erase(0, kFnEnd.size());
+        st_ = AfterFunction;
+      } else if (starts_with(buf_, close_)) { buf_.erase(0, close_.size()); st_ = Outside; }   // no </function>: the object stays open
+      else if (is_prefix_of(buf_, kPar) || is_prefix_of(buf_, kFnEnd) || is_prefix_of(buf_, close_)) return out;
+      else {                                      // stray text inside a call: skipped up to the next tag
+        const size_t lt = buf_.find('<', 1);
+        if (lt == std::string::npos) { buf_.clear(); return out; }
+        buf_.erase(0, lt);
+      }
+    } else if (st_ == InValue) {
+      size_t end = std::string::npos;
+      bool eat = false;
+      const std::string* tags[4] = {&kParEnd, &kPar, &kFnEnd, &close_};
+      for (const std::string* tag : tags) {
+        const size_t p = buf_.find(*tag);
+        if (p < end) { end = p; eat = tag == &kParEnd; }
+      }
+      if (end == std::string::npos) return out;   // the value is reported whole, when its parameter ends
+      const Json v = typed_value(strip_nl(buf_.substr(0, end)), schema_, key_);
+      if (!opened_) { args("{"); opened_ = true; }
+      args(std::string(n_params_ ? ", " : "") + Json(key_).dump(Json::Style{true, false}) + ": " + v.dump(Json::Style{true, false}));
+      ++n_params_;
+      buf_.erase(0, end + (eat ? kParEnd.size() : 0));
+      st_ = InBody;
+    } else {                                      // AfterFunction
+      skip_ws();
+      if (buf_.empty()) return out;
+      if (starts_with(buf_, close_)) { buf_.erase(0, close_.size()); st_ = Outside; }
+      else if (is_prefix_of(buf_, close_)) return out;
+      else st_ = Outside;
+    }
+  }
 }
 
 }  // namespace b2

@@ -66,10 +66,13 @@ class ReasoningParser {
   // A tag that ends an unclosed thinking block when it shows up inside it (the tool-call opener): the model went
   // straight from thinking to a call.  Empty = off.
   void set_interrupt(std::string tag) { interrupt_ = std::move(tag); }
+  // Newlines right after the closing tag: dropped by default (the ChatML family writes "</think>\n\n" before the
+  // answer); the reference model's parsers hand them on as content.
+  void keep_newlines_after_close(bool on) { keep_nl_ = on; }
  private:
   bool in_, stream_;
   std::string open_, close_, interrupt_, buf_, held_reasoning_;
-  bool stripped_open_ = false, strip_nl_ = false;
+  bool stripped_open_ = false, strip_nl_ = false, keep_nl_ = false;
 };
 
 struct ToolCall { std::string name, arguments_json; };
@@ -100,6 +103,34 @@ class ToolStreamParser {
   std::string call_open_, call_close_;
   std::string buf_, tail_;
   bool content_before_calls_only_ = false, saw_call_ = false;
+};
+
+// Streaming view of tool calls in the <function=NAME><parameter=KEY>VALUE</parameter>...</function> format inside a call
+// wrapper: instead of whole calls it reports what a streaming client gets: content, the start of a call (its name), and
+// pieces of the call's arguments object as its parameters complete ("{", "\"key\": value", ", \"key\": value", "}").
+// Behaviour follows the reference's streaming detector (crates/agens-server/src/toolcall.rs, ToolCallStreamParser): a
+// value is reported when its parameter ends (closing tag, the next parameter or the end of the function), the closing
+// brace when </function> arrives, text between and after calls is content, a partial wrapper tag at the end of the
+// output is dropped.
+struct ToolDelta {
+  enum Kind { Content, Start, Args } kind;
+  int index;            // call index (Start / Args)
+  std::string text;     // content, function name, or a piece of the arguments JSON
+};
+class ToolDeltaParser {
+ public:
+  ToolDeltaParser(Json tools, std::string call_open, std::string call_close)
+      : tools_(std::move(tools)), open_(std::move(call_open)), close_(std::move(call_close)) {}
+  std::vector<ToolDelta> push(const std::string& delta);
+  int calls() const { return n_calls_; }
+ private:
+  enum St { Outside, WantFunction, InBody, InValue, AfterFunction };
+  Json tools_;
+  std::string open_, close_, buf_, key_;
+  const Json* schema_ = nullptr;
+  St st_ = Outside;
+  int n_calls_ = 0, n_params_ = 0;
+  bool opened_ = false;
 };
 
 }  // namespace b2

@@ -132,7 +132,7 @@ def test_tool_call_response(tok_path, tok_text):
     tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {"x": {"type": "integer"}}}}}]
     st, body = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "tools": tools})
     r = json.loads(body)["choices"][0]
-    assert r["finish_reason"] == "tool_calls" and r["message"]["content"] is None
+    assert r["finish_reason"] == "tool_calls" and r["message"]["content"] == "" and r["matched_stop"] is None
     tc = r["message"]["tool_calls"][0]
     assert tc["function"] == {"name": "f", "arguments": '{"x": 1}'} and tc["id"].startswith("call_") and len(tc["id"]) == 29
 
@@ -147,7 +147,7 @@ def test_validation_errors_and_routes(tok_path, tok_text):
            ({"messages": [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": "data:image/png;base64,AA"}}]}]}, "images")]
     for body, frag in bad:
         st, text = sv.handle("POST", "/v1/chat/completions", body)
-        assert st == 400 and frag in json.loads(text)["error"]["message"], (body, text)
+        assert st == 400 and frag in json.loads(text)["message"], (body, text)
     assert sv.handle("POST", "/v1/completions", {"prompt": ["a", "b"]})[0] == 400
     assert sv.handle("POST", "/v1/completions", {"prompt": "a", "echo": True})[0] == 400
     assert sv.handle("GET", "/health")[0] == 200 and sv.handle("GET", "/health_generate") == (200, "")
@@ -222,7 +222,7 @@ def test_image_parts_reach_the_engine_callback(tok_path, tok_text):
                                                      {"type": "image_url", "image_url": {"url": url + "BB"}}]}], "max_tokens": 4}
     sv.use_engine(generate, context_length=4096)
     status, resp = sv.handle("POST", "/v1/chat/completions", body)
-    assert status == 400 and "images" in json.loads(resp)["error"]["message"]
+    assert status == 400 and "images" in json.loads(resp)["message"]
     sv.use_engine(generate, context_length=4096, supports_images=True)
     status, resp = sv.handle("POST", "/v1/chat/completions", body)
     assert status == 200
