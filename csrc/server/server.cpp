@@ -174,18 +174,18 @@ static std::string build_sampling(const Server& sv, const Json& body, bool chat,
   if (!num("temperature", temperature) || !num("top_p", top_p) || !num("min_p", min_p) || !num("presence_penalty", pres) ||
       !num("frequency_penalty", freq) || !num("repetition_penalty", rep)) return "sampling parameters must be numbers";
   if (auto p = body.find("top_k"); p && p->is_number()) top_k = p->as_int();
-  if (temperature < 0) return "temperature must be non-negative, got " + Json(temperature).dump();
-  if (top_p <= 0 || top_p > 1) return "top_p must be in (0, 1], got " + Json(top_p).dump();
-  if (min_p < 0 || min_p > 1) return "min_p must be in [0, 1], got " + Json(min_p).dump();
-  if (top_k < -1 || top_k == 0) return "top_k must be -1 (disable) or at least 1, got " + std::to_string(top_k);
-  if (freq < -2 || freq > 2) return "frequency_penalty must be in [-2, 2], got " + Json(freq).dump();
-  if (pres < -2 || pres > 2) return "presence_penalty must be in [-2, 2], got " + Json(pres).dump();
-  if (rep <= 0 || rep > 2) return "repetition_penalty must be in (0, 2], got " + Json(rep).dump();
+  if (temperature < 0) return "temperature must be non-negative, got " + Json(temperature).dump() + ".";
+  if (top_p <= 0 || top_p > 1) return "top_p must be in (0, 1], got " + Json(top_p).dump() + ".";
+  if (min_p < 0 || min_p > 1) return "min_p must be in [0, 1], got " + Json(min_p).dump() + ".";
+  if (top_k < -1 || top_k == 0) return "top_k must be -1 (disable) or at least 1, got " + std::to_string(top_k) + ".";
+  if (freq < -2 || freq > 2) return "frequency_penalty must be in [-2, 2], got " + Json(freq).dump() + ".";
+  if (pres < -2 || pres > 2) return "presence_penalty must be in [-2, 2], got " + Json(pres).dump() + ".";
+  if (rep <= 0 || rep > 2) return "repetition_penalty must be in (0, 2], got " + Json(rep).dump() + ".";
   if (temperature < 1e-6) { temperature = 1.0; top_k = 1; }     // greedy is expressed as top_k = 1
   long long max_new = sv.max_tokens_default;
   if (auto p = body.find("max_completion_tokens"); p && p->is_number()) max_new = p->as_int();
   else if (auto q = body.find("max_tokens"); q && q->is_number()) max_new = q->as_int();
-  if (max_new < 0) return "max_tokens must be at least 0, got " + std::to_string(max_new);
+  if (max_new < 0) return "max_new_tokens must be at least 0, got " + std::to_string(max_new) + ".";
   const long long min_new = body.get_int("min_tokens", 0);
   if (min_new > max_new) return "min_tokens must not exceed max_tokens";
   out.set("temperature", temperature); out.set("top_p", top_p); out.set("top_k", top_k); out.set("min_p", min_p);
@@ -779,7 +779,7 @@ static HttpResponse route(Server& sv, const std::string& method, const std::stri
     r.body = o.str();
     return r;
   }
-  auto model_card = [&]() { Json m = Json::object(); m.set("id", sv.model_name); m.set("object", "model"); m.set("created", (long long)std::time(nullptr)); m.set("owned_by", "b200-engine"); m.set("max_model_len", sv.backend->context_length()); m.set("engine_version", "0.1.0"); return m; };
+  auto model_card = [&]() { Json m = Json::object(); m.set("id", sv.model_name); m.set("object", "model"); m.set("created", (long long)std::time(nullptr)); m.set("engine_version", "0.1.0"); m.set("owned_by", "b200-engine"); m.set("root", sv.model_name); m.set("parent", Json()); m.set("max_model_len", sv.backend->context_length()); return m; };   // the reference's card: id, object, created, version, owned_by, root, parent, max_model_len
   if (method == "GET" && path == "/v1/models") { Json o = Json::object(), a = Json::array(); a.push_back(model_card()); o.set("object", "list"); o.set("data", a); HttpResponse r; r.body = o.dump(); return r; }
   if (method == "GET" && path.compare(0, 11, "/v1/models/") == 0) {
     if (path.substr(11) != sv.model_name) return error_response(404, "model not found: " + path.substr(11), "NotFoundError");
