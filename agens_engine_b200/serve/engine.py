@@ -47,6 +47,7 @@ class Request:
     images: Optional[List[str]] = None    # data: URLs of the request's image parts, in prompt order
     mm: Optional[dict] = None             # serve.vision.VisionFrontEnd.prepare(): encoder rows, positions
     mtp_sinks: Optional[list] = None      # per-chunk feeders of the MTP heads while the prompt prefills
+    pen_state: Optional[dict] = None      # device-side token counts of a request with penalties (_edit_logits)
 
     @property
     def max_new(self) -> int:
@@ -581,21 +582,37 @@ class Engine:
 
     # ---- decode --------------------------------------------------------------------------------------------------
     def _edit_logits(self, logits: torch.Tensor, rows: List[Request]):
-        """Penalties and logit bias, applied in place on the device rows (reference: sampler.rs penalties)."""
+        """Penalties and logit bias, applied in place on the device rows (reference: sampler.rs penalties).  Every
+        request with penalties keeps its token counts on the device (how often each id was generated, which ids occur in
+        prompt or output); a step uploads only the tokens generated since the last one and edits the row with whole-row
+        vector operations."""
         for i, r in enumerate(rows):
             if not r.needs_logit_edits():
                 continue
             s = r.sampling
-            seen = r.prompt + r.out if float(s.get("repetition_penalty", 1)) != 1 else r.out
-            if seen:
-                ids, counts = torch.unique(torch.tensor(seen, device=logits.device), return_counts=True)
-                rep = float(s.get("repetition_penalty", 1))
+            rep = float(s.get("repetition_penalty", 1))
+            pres, freq = float(s.get("presence_penalty", 0)), float(s.get("frequency_penalty", 0))
+            row = logits[i]
+            if rep != 1 or pres != 0 or freq != 0:
+                st = r.pen_state
+                if st is None or st["cnt"].device != row.device or st["cnt"].numel() != row.numel():
+                    st = r.pen_state = {"cnt": torch.zeros(row.numel(), dtype=torch.int32, device=row.device), "n": 0, "seen": None}
+                    if rep != 1:
+                        st["seen"] = torch.zeros(row.numel(), dtype=torch.bool, device=row.device)
+                        if r.prompt:
+                            st["seen"][torch.tensor(r.prompt, dtype=torch.long, device=row.device).clamp_(0, row.numel() - 1)] = True
+                new = r.out[st["n"]:]
+                if new:
+                    t = torch.tensor(new, dtype=torch.long, device=row.device).clamp_(0, row.numel() - 1)
+                    st["cnt"].index_add_(0, t, torch.ones_like(t, dtype=torch.int32))
+                    if st["seen"] is not None:
+                        st["seen"][t] = True
+                    st["n"] = len(r.out)
                 if rep != 1:
-                    v = logits[i, ids]
-                    logits[i, ids] = torch.where(v > 0, v / rep, v * rep)
-                if r.out:
-                    oid, oc = torch.unique(torch.tensor(r.out, device=logits.device), return_counts=True)
-                    logits[i, oid] -= float(s.get("presence_penalty", 0)) + float(s.get("frequency_penalty", 0)) * oc.float()
+                    row.copy_(torch.where(st["seen"], torch.where(row > 0, row / rep, row * rep), row))
+                if pres != 0 or freq != 0:
+                    cnt = st["cnt"]
+                    row.sub_(torch.where(cnt > 0, pres + freq * cnt.float(), torch.zeros_like(row)))
             for k, v in (s.get("logit_bias") or {}).items():
                 if 0 <= int(k) < logits.shape[1]:
                     logits[i, int(k)] += float(v)

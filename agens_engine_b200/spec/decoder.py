@@ -35,6 +35,11 @@ class DraftSource:
         """Drafts continuing ``history`` (whose last element is the next input token)."""
         return []
 
+    def propose_many(self, seqs: Sequence[int], histories: Dict[int, Sequence[int]], max_n: int) -> Dict[int, List[int]]:
+        """Drafts for several sequences of one step.  Sources that run a model override this to batch the sequences
+        into shared forward passes (the reference drafts a batch per call as well: kernels/m1/m1_mtp.cu ``propose_b``)."""
+        return {s: self.propose(s, histories[s], max_n) for s in seqs}
+
     def feedback(self, seq: int, n_proposed: int, n_accepted: int):
         pass
 
@@ -106,6 +111,49 @@ class ModelSource(DraftSource):
         while len(drafts) < min(max_n, self.depth):
             out, _ = m.forward_rows([drafts[-1]], [seq])
             drafts.append(int(out[0]))
+        return drafts
+
+    def propose_many(self, seqs, histories, max_n):
+        """One forward pass per draft position for all sequences together: first the rows every sequence still misses
+        (its last emitted tokens, at most eight per pass), then one row per sequence and position.  A step of sixteen
+        sequences at depth three is three passes instead of forty-eight."""
+        m = self.m
+        seqs = list(seqs)
+        depth = min(max_n, self.depth)
+        if depth <= 0 or not seqs:
+            return {s: [] for s in seqs}
+        missing = {}
+        for s in seqs:
+            h = histories[s]
+            have = m.seq_len_host[s]
+            if have > len(h) - 1:
+                m.truncate(s, len(h) - 1); have = len(h) - 1
+            missing[s] = list(h[have:])
+        last: Dict[int, int] = {}
+        todo = seqs
+        while todo:
+            ids, rows, ends, nxt = [], [], {}, []
+            for s in todo:
+                take = missing[s][:MAX_BLOCK]
+                if len(ids) + len(take) > m.max_rows:
+                    nxt.append(s); continue
+                ids += take; rows += [s] * len(take)
+                missing[s] = missing[s][len(take):]
+                ends[s] = len(ids) - 1
+                if missing[s]:
+                    nxt.append(s)
+            out, _ = m.forward_rows(ids, rows)
+            oh = out.tolist()
+            for s, e in ends.items():
+                last[s] = oh[e]
+            todo = nxt
+        drafts = {s: [last[s]] for s in seqs}
+        for _ in range(depth - 1):
+            for c in range(0, len(seqs), m.max_rows):
+                part = seqs[c:c + m.max_rows]
+                out, _ = m.forward_rows([drafts[s][-1] for s in part], part)
+                for s, tok in zip(part, out.tolist()):
+                    drafts[s].append(tok)
         return drafts
 
     def rewind(self, seq, n_hist):
@@ -191,6 +239,53 @@ class MtpSource(DraftSource):
         self.h.truncate(seq, base)                      # recurrent rows are provisional
         return drafts
 
+    def absorb_many(self, items):
+        """:meth:`absorb` for several sequences of one verify step in shared passes through the head: ``items`` is a
+        list of (sequence, tokens after, hidden rows)."""
+        cap = self.h.cat.shape[0]
+        batch: list = []
+
+        def flush():
+            ids = [t for _, toks, _ in batch for t in toks]
+            rows = [q for q, toks, _ in batch for _ in toks]
+            hid = torch.cat([h[:len(toks)] for _, toks, h in batch])
+            oh = self.h.forward_mtp(ids, hid, rows).tolist()
+            r = 0
+            for q, toks, _ in batch:
+                r += len(toks)
+                self.pending[q] = (oh[r - 1], self.h.h_a[r - 1:r].clone(), self.h.seq_len_host[q])
+
+        n = 0
+        for it in items:
+            k = len(it[1])
+            if k > MAX_BLOCK:
+                self.absorb(*it); continue
+            if n + k > cap:
+                flush(); batch = []; n = 0
+            batch.append(it); n += k
+        if batch:
+            flush()
+
+    def propose_many(self, seqs, histories, max_n):
+        res: Dict[int, List[int]] = {s: [] for s in seqs}
+        live = [s for s in seqs if s in self.pending]
+        if not live:
+            return res
+        pend = {s: self.pending.pop(s) for s in live}
+        hid = {s: pend[s][1] for s in live}
+        for s in live:
+            res[s] = [pend[s][0]]
+        cap = self.h.cat.shape[0]
+        for _ in range(min(max_n, self.depth) - 1):          # deeper drafts: one row per sequence and pass
+            for c in range(0, len(live), cap):
+                part = live[c:c + cap]
+                oh = self.h.forward_mtp([res[s][-1] for s in part], torch.cat([hid[s] for s in part]), part).tolist()
+                for i, s in enumerate(part):
+                    res[s].append(oh[i]); hid[s] = self.h.h_a[i:i + 1].clone()
+        for s in live:
+            self.h.truncate(s, pend[s][2])                  # recurrent rows are provisional
+        return res
+
     def end(self, seq):
         self.h.free_seq(seq); self.pending.pop(seq, None); self.first.pop(seq, None); self._fed.pop(seq, None)
 
@@ -259,11 +354,15 @@ class SpecDecoder:
     def _sample(self, logits: torch.Tensor, seqs: List[int], positions: List[int]) -> torch.Tensor:
         dev = logits.device
         st = [self.samp[s] for s in seqs]
-        # three uploads per step: the float parameters, the integer parameters, the seeds
-        f = torch.tensor([[x.temperature for x in st], [x.top_p for x in st], [x.min_p for x in st]], dtype=torch.float32).to(dev)
-        i = torch.tensor([[x.top_k for x in st], list(positions)], dtype=torch.int32).to(dev)
-        seed = torch.tensor([x.seed & 0x7FFFFFFFFFFFFFFF for x in st], dtype=torch.int64).to(dev)
-        return basic.sample_rows(logits, f[0], i[0], f[1], f[2], seed, i[1], n_valid=self.t.vocab_valid_full())
+        # one upload per step: float parameters as their bit patterns, integer parameters, the seeds as two halves
+        f = torch.tensor([[x.temperature for x in st], [x.top_p for x in st], [x.min_p for x in st]], dtype=torch.float32)
+        seeds = [x.seed & 0x7FFFFFFFFFFFFFFF for x in st]
+        i = torch.tensor([[x.top_k for x in st], list(positions), [v & 0x7FFFFFFF for v in seeds], [(v >> 31) & 0x7FFFFFFF for v in seeds],
+                          [v >> 62 for v in seeds]], dtype=torch.int32)
+        p = torch.cat([f.view(torch.int32), i]).to(dev)
+        fl = p[:3].view(torch.float32)
+        seed = p[5].long() | (p[6].long() << 31) | (p[7].long() << 62)
+        return basic.sample_rows(logits, fl[0], p[3], fl[1], fl[2], seed, p[4], n_valid=self.t.vocab_valid_full())
 
     def step(self, seqs: Sequence[int], forced_drafts: Optional[Dict[int, List[int]]] = None) -> Dict[int, List[int]]:
         """One verify step for every sequence of ``seqs``; returns the tokens each of them emitted (at least one).
@@ -271,18 +370,27 @@ class SpecDecoder:
         t = self.t
         ids, rows_seq, row0, cnt, positions = [], [], [], [], []
         used: Dict[int, tuple] = {}
+        # drafts: the sources are asked in their order; each one drafts for all sequences still without drafts at once
+        drafts_of: Dict[int, List[int]] = {}
+        src_of: Dict[int, DraftSource] = {}
+        if forced_drafts is not None:
+            for s in seqs:
+                if s in forced_drafts:
+                    drafts_of[s] = list(forced_drafts[s])[:self.max_drafts]
+        waiting = [s for s in seqs if s not in drafts_of]
+        if self.max_drafts:
+            for src in self.sources:
+                if not waiting:
+                    break
+                got = src.propose_many(waiting, self.hist, self.max_drafts)
+                for s in waiting:
+                    if got.get(s):
+                        drafts_of[s] = list(got[s]); src_of[s] = src
+                waiting = [s for s in waiting if s not in drafts_of]
         for s in seqs:
             h = self.hist[s]
-            drafts: List[int] = []
-            src_used = None
-            if forced_drafts is not None and s in forced_drafts:
-                drafts = list(forced_drafts[s])[:self.max_drafts]
-            else:
-                for src in self.sources:
-                    drafts = src.propose(s, h, self.max_drafts) if self.max_drafts else []
-                    if drafts:
-                        src_used = src
-                        break
+            drafts = drafts_of.get(s, [])
+            src_used = src_of.get(s)
             room = t.max_ctx - t.seq_len_host[s] - 1
             drafts = drafts[:max(room, 0)]
             used[s] = (src_used, len(drafts))
@@ -298,8 +406,10 @@ class SpecDecoder:
         dev = t.dev
         ti = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
         n_emit, emitted = basic.spec_accept(ti(ids), target, ti(row0), ti(cnt), MAX_BLOCK)
-        n_emit_h, emitted_h = n_emit.cpu().tolist(), emitted.cpu().tolist()
+        both = torch.cat([n_emit.view(-1, 1), emitted], dim=1).cpu().tolist()          # one read-back per step
+        n_emit_h, emitted_h = [r[0] for r in both], [r[1:] for r in both]
         result: Dict[int, List[int]] = {}
+        absorb = []
         for b, s in enumerate(seqs):
             k = n_emit_h[b]
             toks = emitted_h[b][:k]
@@ -311,9 +421,10 @@ class SpecDecoder:
             if src is not None:
                 src.feedback(s, n_prop, k - 1)
                 st = self.stats.by_source.setdefault(src.name, [0, 0]); st[0] += n_prop; st[1] += k - 1
-            for mtp in self._mtp:
-                # committed positions of this block: rows 0 .. k-1; the token after row j is toks[j]
-                mtp.absorb(s, toks, t.h_a[row0[b]:row0[b] + k])
+            # committed positions of this block: rows 0 .. k-1; the token after row j is toks[j]
+            absorb.append((s, toks, t.h_a[row0[b]:row0[b] + k]))
+        for mtp in self._mtp:
+            mtp.absorb_many(absorb)
         return result
 
     def generate(self, seq: int, prompt: Sequence[int], n_new: int, sampling: Optional[SamplingState] = None,
