@@ -201,6 +201,7 @@ def _declare(lib: C.CDLL):
         "b2_sample_rows": ([C.POINTER(SampleArgs), i, vp], i),
         "b2_spec_accept": ([vp, vp, vp, vp, i, vp, vp, i, vp], i),
         "b2_gemm_bf16": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp, vp], i),
+        "b2_bf16_gemv": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp], i),
     }
     for name, (args, res) in sig.items():
         if hasattr(lib, name):

@@ -155,6 +155,32 @@ def bench_gemm(args):
     print(json.dumps({"peaks": pk, "timing": "CUDA events, median of 10, L2 flushed between launches"}))
 
 
+def bench_bf16(args):
+    """bf16 GEMV (linears kept in bf16) on the shapes of the 0.6B drafter and of the 32B model, ``--m`` rows: launches
+    back to back in a CUDA graph over rotating weight copies larger than L2, device time per launch and the fraction of
+    the measured copy bandwidth the weight stream reaches."""
+    dev = "cuda:0"
+    pk = peaks()
+    ws = L.GemvWorkspace(dev, floats=1 << 16)
+    shapes = [("drafter qkv", 4096, 1024), ("drafter gate_up", 6144, 1024), ("drafter down", 1024, 3072), ("32b qkv", 10240, 5120),
+              ("32b o", 5120, 8192), ("32b gate_up", 51200, 5120), ("32b down", 5120, 25600)]
+    for name, n, k in shapes[:4] if args.small else shapes:
+        w = (torch.randn(n, k, device=dev) * 0.02).to(torch.bfloat16)
+        ncopy = max(4, min(64, (512 << 20) // (n * k * 2) + 1))
+        lins = [L.Bf16Linear(n, k, w.clone()) for _ in range(ncopy)]
+        x = torch.randn(args.m, k, device=dev).to(torch.bfloat16)
+        out = torch.empty(args.m, n, dtype=torch.bfloat16, device=dev)
+
+        def launch_all():
+            for ln in lins:
+                L.gemv(ln, x, ws, out=out)
+        us, best = graph_time_us(launch_all, ncopy)
+        gbs = n * k * 2 / us / 1e3
+        print(json.dumps(dict(name=name, n=n, k=k, m=args.m, us=round(us, 2), best_us=round(best, 2), weight_gbs=round(gbs, 1),
+                              frac_of_measured_copy=round(gbs / pk["hbm_gbs"], 3))), flush=True)
+    print(json.dumps({"peaks": pk, "timing": "CUDA graph of back-to-back launches over rotating weight copies (> L2), median of 10"}))
+
+
 def trace_gemv(args):
     """Phase stamps of the GEMV on the 32B shapes (m rows), captured inside a CUDA graph of back-to-back launches over
     rotating weight copies: where the time of one launch goes (start skew, prefetch issue, dependency wait, activation
@@ -384,7 +410,7 @@ def profile_step(args):
 
 def main(argv=None):
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_attn_tc", "profile_gemm", "profile_misc", "profile_step"])
+    ap.add_argument("what", choices=["gemv", "bf16", "attn", "gemm", "profile_gemv", "trace_gemv", "mm", "profile_mm", "profile_attn", "profile_attn_tc", "profile_gemm", "profile_misc", "profile_step"])
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--bits", type=int, default=4)
     ap.add_argument("--ks", type=int, default=0)
@@ -395,6 +421,8 @@ def main(argv=None):
     args = ap.parse_args(argv)
     if args.what == "gemv":
         bench_gemv(args)
+    elif args.what == "bf16":
+        bench_bf16(args)
     elif args.what == "profile_gemv":
         profile_gemv(args)
     elif args.what == "gemm":

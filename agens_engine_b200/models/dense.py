@@ -83,7 +83,9 @@ class DenseModel:
 
     @staticmethod
     def random_init(cfg: ModelConfig, device="cuda:0", seed: int = 0, **kw) -> "DenseModel":
-        """Random-init weights of the named architecture, quantised on the device (no host copy of 32B weights)."""
+        """Random-init weights of the named architecture, quantised on the device (no host copy of 32B weights).
+        ``bf16_linears=True``: the layers' linears are bf16 instead (the benchmark drafter of the reference is bf16)."""
+        bf16_linears = bool(kw.pop("bf16_linears", False))
         m = DenseModel(cfg, device, **kw)
         shapes = cfg.linear_shapes()
         g = torch.Generator(device=m.dev).manual_seed(seed)
@@ -91,6 +93,9 @@ class DenseModel:
             d = {}
             for i, lin in enumerate(LINEARS):
                 n, k = shapes[lin]
+                if bf16_linears:
+                    d[lin] = L.Bf16Linear(n, k, (torch.randn(n, k, device=m.dev, generator=g) * 0.02).to(torch.bfloat16))
+                    continue
                 d[lin] = L.WqLinear.random(n, k, cfg.bits_of(l, lin), cfg.group, m.dev, seed=seed * 1000003 + l * 8 + i)
             d["ln1"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
             d["ln2"] = (1.0 + 0.05 * torch.randn(cfg.d_model, device=m.dev, generator=g)).to(torch.bfloat16)
@@ -158,7 +163,7 @@ class DenseModel:
     def finalize(self):
         """Size the split-k workspace from the loaded linears (call once after the weights are in place)."""
         lib = _lib.cuda_lib()
-        lins = [self.lm_head] + [d[lin] for d in self.layers[:1] for lin in LINEARS]
+        lins = [x for x in [self.lm_head] + [d[lin] for d in self.layers for lin in LINEARS] if isinstance(x, L.WqLinear)]
         need = max(lib.b2_wq_gemv_scratch_floats(x.n, x.k, x.ks, r, M_GEMV) for x in lins for r in (2, x.rb))
         # the tensor-core path's split-k partials at its largest row count, so that the scratch never moves afterwards
         need = max(need, max(lib.b2_wq_mm_scratch_floats(x.n, x.k, 256) for x in lins))
@@ -181,7 +186,9 @@ class DenseModel:
         self.step = StepRunner(self, uniform=self.step_uniform)
 
     def _step_possible(self) -> bool:
-        return self.dev.type == "cuda" and self.cfg.head_dim == 128 and self.cfg.page_size == 16 and bool(self.layers)
+        # (the step kernel reads quantised weights only: a model with bf16 linears stays on the per-op kernels)
+        return self.dev.type == "cuda" and self.cfg.head_dim == 128 and self.cfg.page_size == 16 and bool(self.layers) \
+            and all(isinstance(d[lin], L.WqLinear) for d in self.layers for lin in LINEARS)
 
     def enable_step(self, on=True, uniform: Optional[bool] = None):
         """``True`` / "on": every step of up to sixteen rows runs on the persistent step kernel (its weight copies are

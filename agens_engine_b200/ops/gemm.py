@@ -32,6 +32,8 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, resid: Optional[torch.Tensor] = 
 def wq_linear(lin: L.WqLinear, x: torch.Tensor, owner=None, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``bf16 [T, n] = x @ dequant(W)^T (+ resid)``.  The weight is dequantised FM -> bf16 into a reusable buffer, then
     multiplied by the tcgen05 GEMM.  ``B200E_PLAIN_GEMM=1`` selects the library GEMM instead (same-box baseline)."""
+    if isinstance(lin, L.Bf16Linear):
+        return gemm_bf16(x, lin.w, resid=resid, status=getattr(owner, "status", None))
     tmp = None
     if owner is not None:
         need = lin.n * lin.k

@@ -112,6 +112,84 @@ class WqLinear:
         return ql.dequant()
 
 
+@dataclasses.dataclass
+class Bf16Linear:
+    """A linear kept in bf16 (checkpoint format ``bf16``, reference: crates/agens-core/src/weights.rs:176-187
+    ``LinearFormat::Bf16``; the bf16 drafter): ``w`` is bf16 ``[n, k]`` on the device.  :func:`gemv` and :func:`mm` take
+    it like a quantised linear; up to eight rows run the bf16 GEMV (``csrc/kernels/sm100/bf16_gemv.cu``), more rows the
+    tcgen05 GEMM.  Norm prologue, SwiGLU and the next norm's statistics are separate small kernels on this path."""
+    n: int
+    k: int
+    w: torch.Tensor
+    bits: int = 16
+    group: int = 0
+    ks: int = 1
+    rb: int = 2
+
+    @staticmethod
+    def from_tensor(w: torch.Tensor, device) -> "Bf16Linear":
+        w = w.to(device=device, dtype=torch.bfloat16).contiguous()
+        return Bf16Linear(w.shape[0], w.shape[1], w)
+
+    def n_panels(self) -> int:
+        return 1                 # parts of the sum of squares a residual epilogue leaves (one: a separate pass computes it)
+
+    def nbytes(self) -> int:
+        return self.w.numel() * 2
+
+    def dequant(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return self.w
+
+    def dequant_cpu(self) -> torch.Tensor:
+        return self.w.float().cpu()
+
+
+BF16_GEMV_ROWS = 8
+
+
+def _bf16_linear(lin: Bf16Linear, x: torch.Tensor, *, epi: int, pro: int, norm_w, eps: float, resid, out, ss_out, gemv_rows: int = BF16_GEMV_ROWS):
+    """The contract of :func:`gemv` for a bf16 linear, as separate kernels: RMSNorm (when asked), the product, then
+    SwiGLU or the residual's sum of squares."""
+    from . import basic
+    from . import gemm as G
+    lib = _lib.cuda_lib()
+    m = x.shape[0]
+    assert x.dtype == torch.bfloat16 and x.shape[1] == lin.k and x.stride(1) == 1
+    xin = basic.rmsnorm(x, norm_w, eps) if pro == PRO_NORM else x
+    dev = x.device
+
+    def product(dst_bf16, dst_f32, r):
+        if m <= gemv_rows:
+            d = dst_bf16 if dst_bf16 is not None else dst_f32
+            with torch.cuda.device(dev):
+                check(lib.b2_bf16_gemv(ptr(xin), xin.stride(0), ptr(lin.w), lin.w.stride(0), m, lin.n, lin.k, ptr(dst_bf16), ptr(dst_f32),
+                                       d.stride(0), ptr(r), r.stride(0) if r is not None else 0, current_stream()), "b2_bf16_gemv")
+        else:
+            G.gemm_bf16(xin, lin.w, resid=r, out=dst_bf16 if dst_bf16 is not None else dst_f32)
+
+    if epi in (EPI_STORE, EPI_RESID):
+        if out is None:
+            out = torch.empty(m, lin.n, dtype=torch.bfloat16, device=dev)
+        product(out, None, resid if epi == EPI_RESID else None)
+        if epi == EPI_RESID and ss_out is not None:
+            basic.sumsq(out, ss_out)
+        return out
+    if epi == EPI_SWIGLU:
+        gu = torch.empty(m, lin.n, dtype=torch.bfloat16, device=dev)
+        product(gu, None, None)
+        act = basic.swiglu_interleaved(gu)
+        if out is None:
+            return act
+        out.copy_(act)
+        return out
+    if epi == EPI_F32:
+        if out is None:
+            out = torch.empty(m, lin.n, dtype=torch.float32, device=dev)
+        product(None, out, None)
+        return out
+    raise ValueError("this epilogue is not available for a bf16 linear (the lm_head is quantised at load)")
+
+
 class GemvWorkspace:
     """Split-k scratch, self-resetting item counters and the status word shared by the GEMV / GEMM launches of one
     stream, plus the fp16 activation staging buffer of the tensor-core path (grown on first use)."""
@@ -152,6 +230,12 @@ def gemv(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_ST
          yf: Optional[torch.Tensor] = None, tp: Optional[_lib.TpPush] = None):
     """Launch one GEMV on the current stream.  ``x``: bf16 ``[m, k]`` (``h`` when ``pro == PRO_NORM``).  More than
     ``MM_MIN_ROWS - 1`` rows go to the tensor-core GEMM (:func:`mm`), which takes the same arguments."""
+    if isinstance(lin, Bf16Linear):
+        if tp is not None:
+            raise ValueError("bf16 linears are not sharded: tensor-parallel models quantise them at load")
+        # a workspace pinned to the tensor-core path (one kernel family for every step) pins bf16 linears to the GEMM too
+        rows = BF16_GEMV_ROWS if ws.mm_min_rows is None else min(BF16_GEMV_ROWS, ws.mm_min_rows - 1)
+        return _bf16_linear(lin, x, epi=epi, pro=pro, norm_w=norm_w, eps=eps, resid=resid, out=out, ss_out=ss_out, gemv_rows=rows)
     lib = _lib.cuda_lib()
     m = x.shape[0]
     if m >= (ws.mm_min_rows or MM_MIN_ROWS) and tp is None:
@@ -212,6 +296,8 @@ def mm(lin: WqLinear, x: torch.Tensor, ws: GemvWorkspace, *, epi: int = EPI_STOR
     """Same contract as :func:`gemv` for 1 .. 256 rows on the tcgen05 tensor cores (``csrc/kernels/sm100/wq_mm.cu``):
     the weights are dequantised to fp16 tiles inside the kernel, the activations are staged as fp16 by a small prologue
     kernel that also applies the RMSNorm of ``pro == PRO_NORM``."""
+    if isinstance(lin, Bf16Linear):
+        return _bf16_linear(lin, x, epi=epi, pro=pro, norm_w=norm_w, eps=eps, resid=resid, out=out, ss_out=ss_out, gemv_rows=0)
     lib = _lib.cuda_lib()
     m = x.shape[0]
     assert x.dtype == torch.bfloat16 and x.shape[1] == lin.k and x.stride(1) == 1 and 1 <= m <= 256

@@ -334,8 +334,8 @@ def load_model(dir_: str, device="cuda:0", rank: int = 0, world: int = 1, **kw):
     """Builds a :class:`DenseModel` (or this rank's :class:`TpDenseModel` shard) from a checkpoint directory.
 
     Quantised linears stream from the memory-mapped shards to the device in their packed form and are repacked there;
-    peak host memory is the page cache of one tensor.  bf16 linears and a tied lm_head are quantised at load
-    (asymmetric 4 bits, group 128) because the decode kernels take quantised weights only."""
+    peak host memory is the page cache of one tensor.  bf16 linears stay bf16 on one GPU (see ``keep_bf16`` below);
+    a tied lm_head, and bf16 linears of a tensor-parallel load, are quantised at load (asymmetric 4 bits, group 128)."""
     from ..models.config import LINEARS
     from ..models.dense import DenseModel
     from ..ops import linear as L
@@ -361,8 +361,42 @@ def load_model(dir_: str, device="cuda:0", rank: int = 0, world: int = 1, **kw):
         zp = T(".weight_zero_point") if fmt["asymmetric"] else None
         return (T(".weight_packed"), T(".weight_scale"), zp, n, k, fmt["bits"], fmt["group"])
 
+    # Linears stored as bf16 stay bf16 on one GPU (Bf16Linear: bf16 GEMV / tcgen05 GEMM) when every tensor of the fused
+    # launch is bf16; B200E_BF16_LINEARS=quant, a tensor-parallel load or a mixed group quantises them at load instead.
+    keep_bf16 = world == 1 and os.environ.get("B200E_BF16_LINEARS", "bf16") != "quant"
+
+    def all_bf16(*names):
+        return keep_bf16 and all(fm[n_]["format"] == "bf16" for n_ in names)
+
+    def raw(name):
+        return files[wm[name + ".weight"]].tensor(name + ".weight")
+
     for l in range(cfg.n_layers):
         p = f"{root}layers.{l}."
+        groups = {"qkv": [p + "self_attn.q_proj", p + "self_attn.k_proj", p + "self_attn.v_proj"], "o": [p + "self_attn.o_proj"],
+                  "gate_up": [p + "mlp.gate_proj", p + "mlp.up_proj"], "down": [p + "mlp.down_proj"]}
+        if any(all_bf16(*grp) for grp in groups.values()):
+            d = {}
+            shapes = {"qkv": [(cfg.q_dim, cfg.d_model), (cfg.kv_dim, cfg.d_model), (cfg.kv_dim, cfg.d_model)], "o": [(cfg.d_model, cfg.q_dim)],
+                      "gate_up": [(cfg.ffn, cfg.d_model)] * 2, "down": [(cfg.d_model, cfg.ffn)]}
+            for lin, names in groups.items():
+                if all_bf16(*names):
+                    if lin == "gate_up":
+                        w = quant.interleave_gate_up(raw(names[0]), raw(names[1]))
+                    else:
+                        w = torch.cat([raw(n_) for n_ in names]) if len(names) > 1 else raw(names[0])
+                    d[lin] = L.Bf16Linear.from_tensor(w, dev)
+                else:
+                    parts_ = [part(n_, *shp) for n_, shp in zip(names, shapes[lin])]
+                    if len({(x[5], x[6]) for x in parts_}) != 1:
+                        raise ValueError(f"layer {l}: the tensors of {lin} use different bit widths or group sizes; they share one launch")
+                    d[lin] = _device_linear(parts_, dev, interleave=(lin == "gate_up"))
+            T = lambda nm: files[wm[p + nm]].tensor(p + nm).to(dev)
+            d["ln1"], d["ln2"] = T("input_layernorm.weight"), T("post_attention_layernorm.weight")
+            m.layers.append(d)
+            for lin in LINEARS:
+                cfg.bits[f"{l}.{lin}"] = d[lin].bits
+            continue
         q, kk, v = part(p + "self_attn.q_proj", cfg.q_dim, cfg.d_model), part(p + "self_attn.k_proj", cfg.kv_dim, cfg.d_model), \
             part(p + "self_attn.v_proj", cfg.kv_dim, cfg.d_model)
         if not (q[5] == kk[5] == v[5] and q[6] == kk[6] == v[6]):

@@ -144,7 +144,8 @@ def other_modes(args):
         from agens_engine_b200.models import config as MC
         from agens_engine_b200.models.dense import DenseModel
         from agens_engine_b200.spec import CopyLookupSource, ModelSource
-        drafter = DenseModel.random_init(MC.drafter_0p6b(), dev, seed=1, max_seqs=C_, max_ctx=P + N + 64, prefill_chunk=2048)
+        drafter = DenseModel.random_init(MC.drafter_0p6b(), dev, seed=1, max_seqs=C_, max_ctx=P + N + 64, prefill_chunk=2048,
+                                         bf16_linears=os.environ.get("B200E_DRAFTER_BF16", "1") == "1")   # the reference's drafter is bf16
         drafter.row_graphs = True
         sources = lambda: [CopyLookupSource(), ModelSource(drafter, depth)]
     first_at, count, t0 = {}, {}, [0.0]
