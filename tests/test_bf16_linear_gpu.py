@@ -76,3 +76,31 @@ def test_checkpoint_with_bf16_linears_runs_in_bf16(tmp_path, which, monkeypatch)
     monkeypatch.setenv("B200E_BF16_LINEARS", "quant")
     q = K.load_model(d, "cuda:0", max_seqs=1, max_ctx=256)
     assert all(isinstance(q.layers[0][lin], L.WqLinear) for lin in ("qkv", "o", "gate_up", "down"))
+
+
+def test_bf16_drafter_with_row_graphs_keeps_speculation_exact():
+    """A random-init bf16 model as companion drafter, its steps replayed as CUDA graphs: the emitted tokens are those of
+    plain decoding, and a drafter with the target's own weights in bf16 gets most of its drafts accepted."""
+    from agens_engine_b200.models.dense import DenseModel
+    from agens_engine_b200.spec import ModelSource, SpecDecoder
+    cfg = C.oracle_tiny()
+    ow = O.random_weights(cfg, seed=0)
+    torch.manual_seed(4)
+    prompt = torch.randint(0, cfg.vocab, (30,)).tolist()
+    plain = SpecDecoder(DenseModel.from_oracle(ow, max_seqs=2, max_ctx=512), [], max_drafts=0).generate(0, prompt, 24)
+    target = DenseModel.from_oracle(ow, max_seqs=2, max_ctx=512)
+    drafter = DenseModel.random_init(cfg, "cuda:0", seed=9, max_seqs=2, max_ctx=512, bf16_linears=True)
+    assert all(isinstance(drafter.layers[0][lin], L.Bf16Linear) for lin in ("qkv", "o", "gate_up", "down"))
+    drafter.row_graphs = True
+    dec = SpecDecoder(target, [ModelSource(drafter, depth=3)], max_drafts=3)
+    assert dec.generate(0, prompt, 24) == plain and dec.stats.proposed > 0
+    # the target's weights, dequantised to bf16 linears, as the drafter: nearly every draft is right
+    same = DenseModel.from_oracle(ow, max_seqs=2, max_ctx=512)
+    for l, d in enumerate(same.layers):
+        for lin in ("qkv", "o", "gate_up", "down"):
+            d[lin] = L.Bf16Linear.from_tensor(ow.quant[f"{l}.{lin}"].dequant(), same.dev)
+    same.finalize()
+    same.row_graphs = True
+    dec = SpecDecoder(target, [ModelSource(same, depth=3)], max_drafts=3)
+    assert dec.generate(0, prompt, 24) == plain
+    assert dec.stats.accepted >= 0.7 * dec.stats.proposed, (dec.stats.accepted, dec.stats.proposed)
