@@ -410,11 +410,11 @@ def cmd_serve(ns):
     sources = []
     if cfg.spec_copy:
         sources.append(CopyLookupSource())
-    if cfg.mtp and world == 1:
+    if cfg.mtp:                                           # under --tp the head runs beside the leader, unsharded
         from .models.mtp import MtpHead
         if os.path.isdir(cfg.mtp):                        # a head checkpoint (mtp.* tensors); anything else: a random-init head
             from .utils import checkpoint as K
-            head = K.load_mtp(cfg.mtp, m)
+            head = K.load_mtp(cfg.mtp, m, lm_head_dir=cfg.model_dir)
         else:
             head = MtpHead.random_init_for(m)
         sources.append(MtpSource(head, depth=min(cfg.draft_depth, 2)))

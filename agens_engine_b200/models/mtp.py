@@ -22,15 +22,21 @@ from .dense import DenseModel, M_GEMV
 
 class MtpHead(DenseModel):
     """One-layer model with its own paged KV; ``embed``, ``final_norm`` weights for the head and ``lm_head`` are the
-    target's tensors (shared, not copied)."""
+    target's tensors (shared, not copied).  Beside a tensor-parallel target the head runs unsharded on the leader's GPU
+    (the target's hidden rows are replicated on every rank); the target's lm_head is a vocabulary shard there, so the
+    head carries its own full one (``own_lm_head``; reference: the MTP head under TP, kernels/m1/m1_mtp.cu:503-524)."""
 
     def __init__(self, target: DenseModel, **kw):
-        cfg = scaled(target.cfg, 1)
+        full = getattr(target, "full_cfg", None)
+        cfg = scaled(full or target.cfg, 1)
+        self.own_lm_head = full is not None
         kw.setdefault("max_seqs", target.max_seqs)
         kw.setdefault("max_ctx", target.max_ctx)
         kw.setdefault("split_keys", target.split_keys)
-        super().__init__(cfg, target.dev, lm_rows=target.lm_rows, **kw)
-        self.embed, self.lm_head = target.embed, target.lm_head
+        lm_rows = (cfg.vocab + 31) // 32 * 32 if self.own_lm_head else target.lm_rows
+        super().__init__(cfg, target.dev, lm_rows=lm_rows, **kw)
+        self.embed = target.embed
+        self.lm_head = None if self.own_lm_head else target.lm_head
         self.final_norm = target.final_norm
         self.fc: Optional[L.WqLinear] = None
         self.norm_e = self.norm_h = None
@@ -53,6 +59,8 @@ class MtpHead(DenseModel):
         m.fc = L.WqLinear.random(cfg.d_model, 2 * cfg.d_model, 4, cfg.group, dev, seed=seed * 7919 + 100)
         m.norm_e = (1.0 + 0.05 * torch.randn(cfg.d_model, device=dev, generator=g)).to(torch.bfloat16)
         m.norm_h = (1.0 + 0.05 * torch.randn(cfg.d_model, device=dev, generator=g)).to(torch.bfloat16)
+        if m.own_lm_head:
+            m.lm_head = L.WqLinear.random(m.lm_rows, cfg.d_model, cfg.lm_head_bits, cfg.group, dev, seed=seed * 7919 + 200)
         return m.finalize()
 
     def finalize(self):

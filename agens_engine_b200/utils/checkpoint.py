@@ -493,23 +493,56 @@ def read_mtp(dir_: str, cfg) -> Dict[str, torch.Tensor]:
     return out
 
 
-def load_mtp(dir_: str, target, bits: int = BF16_LOAD_BITS, **kw):
+def load_lm_head(dir_: str, device, rows: Optional[int] = None):
+    """The whole (unsharded) lm_head of the model checkpoint ``dir_`` as an engine linear, padded with zero rows to
+    ``rows``: what a head beside a tensor-parallel target needs (the target itself holds a vocabulary shard)."""
+    from ..ops import linear as L
+    rep, cfg, wm, files, tied = _open(dir_)
+    fm, root = rep["linears"], rep.get("root", "model.")
+    if tied or fm["lm_head"]["format"] == "bf16":
+        name = root + "embed_tokens.weight" if tied else "lm_head.weight"
+        ql = quant.quantize(files[wm[name]].tensor(name).float(), BF16_LOAD_BITS, 128)
+        lm = (quant.pack_stream(ql.codes, ql.bits), ql.scale, ql.zero, cfg.vocab, cfg.d_model, ql.bits, ql.group)
+    else:
+        fmt = fm["lm_head"]
+        T = lambda suf: files[wm["lm_head" + suf]].tensor("lm_head" + suf)
+        lm = (T(".weight_packed"), T(".weight_scale"), T(".weight_zero_point") if fmt["asymmetric"] else None, cfg.vocab, cfg.d_model,
+              fmt["bits"], fmt["group"])
+    head = _device_linear([lm], torch.device(device))
+    rows = rows or (cfg.vocab + 31) // 32 * 32
+    pad = rows - cfg.vocab
+    if pad:
+        zq = quant.QuantLinear(pad, cfg.d_model, head.bits, head.group, torch.zeros(pad, cfg.d_model, dtype=torch.uint8),
+                               torch.zeros(pad, cfg.d_model // head.group, dtype=torch.float16),
+                               torch.zeros(pad, cfg.d_model // head.group, dtype=torch.float16))
+        padl = L.WqLinear.from_quant(zq, device)
+        head = L.WqLinear(rows, cfg.d_model, head.bits, head.group, torch.cat([head.wq, padl.wq]), head.ks, L.choose_rb(rows))
+    for fl in files.values():
+        fl.close()
+    return head
+
+
+def load_mtp(dir_: str, target, bits: int = BF16_LOAD_BITS, lm_head_dir: Optional[str] = None, **kw):
     """An :class:`~agens_engine_b200.models.mtp.MtpHead` for ``target`` from the ``mtp.*`` tensors of ``dir_``.  The
     linears are quantised at load (asymmetric, ``bits`` bits, group 128 or the model's group when that is smaller; the
     reference quantises its head to 4-bit group 128 at load as well, spec.rs:318-340); gate and up are merged row-interleaved as in the main model; embedding and
     lm_head stay the target's."""
     from ..models.mtp import MtpHead
     from ..ops import linear as L
-    t = read_mtp(dir_, target.cfg)
+    t = read_mtp(dir_, getattr(target, "full_cfg", None) or target.cfg)
     dev = target.dev
     h = MtpHead(target, **kw)
+    if h.own_lm_head:          # beside a tensor-parallel target: the whole lm_head comes from the model's checkpoint
+        if not lm_head_dir:
+            raise ValueError("an MTP head beside a tensor-parallel model needs the model checkpoint for its lm_head (lm_head_dir)")
+        h.lm_head = load_lm_head(lm_head_dir, dev, rows=h.lm_rows)
 
     def lin(*names, interleave=False):
         if interleave:
             w = quant.interleave_gate_up(t[names[0]].float(), t[names[1]].float())
         else:
             w = torch.cat([t[n].float() for n in names])
-        return L.WqLinear.from_quant(quant.quantize(w, bits, min(128, target.cfg.group)), dev)
+        return L.WqLinear.from_quant(quant.quantize(w, bits, min(128, h.cfg.group)), dev)
 
     p = "layers.0."
     h.layers.append({

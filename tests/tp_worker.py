@@ -240,6 +240,20 @@ def main():
             eng.run_until_idle(5000)
             assert [got[r] for r in rids] == t16, ([got[r] for r in rids], t16)
             assert eng.spec.stats.accepted > 0
+            # an MTP head beside the leader: unsharded, with its own full lm_head, fed with the leader's replicated hidden
+            # rows (prompt positions included); same tokens again
+            from agens_engine_b200.models.mtp import MtpHead
+            from agens_engine_b200.spec import MtpSource
+            head = MtpHead.random_init_for(m)
+            assert head.own_lm_head and head.lm_head.n >= cfg.vocab and head.cfg.n_heads == cfg.n_heads
+            src = MtpSource(head, depth=2)
+            got = {}
+            eng = Engine(drv, lambda rid, t, f, e: got.setdefault(rid, []).extend(t) or False, max_batch=4, max_drafts=3,
+                         sources_factory=lambda: [src])
+            rids = [eng.submit(p, s) for p, s in reqs]
+            eng.run_until_idle(5000)
+            assert [got[r] for r in rids] == t16, ([got[r] for r in rids], t16)
+            assert eng.spec.stats.by_source.get("mtp", [0, 0])[0] > 0 and head.free_pages() == head.n_pages
             drv.set_linear_path(None)
             assert all(len(t) == 12 for t in together) and together[3] != together[0]
             blob = None
