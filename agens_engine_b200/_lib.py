@@ -194,6 +194,7 @@ def _declare(lib: C.CDLL):
         "b2_comm_all_reduce": ([C.POINTER(CommArgs), vp, vp, l, vp, vp, vp], i),
         "b2_comm_all_gather": ([C.POINTER(CommArgs), vp, l, vp, vp], i),
         "b2_comm_reduce_scatter": ([C.POINTER(CommArgs), vp, l, vp, vp], i),
+        "b2_comm_collect_gather": ([C.POINTER(CommArgs), l, i, i, i, vp, vp], i),
         "b2_comm_barrier": ([C.POINTER(CommArgs), vp], i),
         "b2_comm_argmax_combine": ([C.POINTER(CommArgs), vp, vp, i, vp, vp, vp], i),
         "b2_wq_mm": ([C.POINTER(WqMmArgs), vp, l, vp, i, i, vp, f, vp, vp], i),
@@ -202,6 +203,7 @@ def _declare(lib: C.CDLL):
         "b2_spec_accept": ([vp, vp, vp, vp, i, vp, vp, i, vp], i),
         "b2_gemm_bf16": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp, vp], i),
         "b2_bf16_gemv": ([vp, l, vp, l, i, i, i, vp, vp, l, vp, l, vp], i),
+        "b2_gemm_bf16_push": ([vp, l, vp, l, i, i, i, vp, i, i, l, l, i, vp, vp], i),
     }
     for name, (args, res) in sig.items():
         if hasattr(lib, name):

@@ -549,6 +549,10 @@ class DenseModel:
         from ..ops import gemm as G
         return G.wq_linear(lin, x, self)
 
+    def _row_linear_big(self, lin, x: torch.Tensor) -> torch.Tensor:
+        """A row-parallel linear of a prefill chunk, summed over the tensor-parallel ranks (one GPU: the plain linear)."""
+        return self._reduce_rows(self._linear_big(lin, x))
+
     def _prefill_split_for(self, kv_len: int) -> int:
         """KV split size of a prefill chunk: the base size, doubled until at most 64 splits cover the context (keeps the
         partial-result buffers bounded at long context)."""
@@ -652,11 +656,11 @@ class DenseModel:
             else:
                 a = A.attn_prefill(q, self.kv[li], self.block_table, seq, pos0, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim,
                                    status=self.status, split_keys=self._prefill_split_for(pos0 + T))
-            o = self._reduce_rows(self._linear_big(d["o"], a))
+            o = self._row_linear_big(d["o"], a)
             x, h = basic.rmsnorm(o, d["ln2"], cfg.rms_eps, resid=h)
             gu = self._linear_big(d["gate_up"], x)
             act = basic.swiglu_interleaved(gu)
-            delta = self._reduce_rows(self._linear_big(d["down"], act))
+            delta = self._row_linear_big(d["down"], act)
         if self.hidden_sink is not None:
             # the residual stream after the last layer, every row of the chunk (what an MTP head reads as its context)
             self.hidden_sink(pos0, (h.float() + delta.float()).to(torch.bfloat16))

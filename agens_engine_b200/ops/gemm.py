@@ -29,6 +29,20 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, resid: Optional[torch.Tensor] = 
     return out
 
 
+def dequant_bf16(lin, owner=None) -> torch.Tensor:
+    """The linear's weights as bf16 [n, k]: a bf16 linear's own tensor, else the quantised weights expanded into a
+    buffer that ``owner`` keeps and reuses."""
+    if isinstance(lin, L.Bf16Linear):
+        return lin.w
+    tmp = None
+    if owner is not None:
+        need = lin.n * lin.k
+        if getattr(owner, "_deq_tmp", None) is None or owner._deq_tmp.numel() < need:
+            owner._deq_tmp = torch.empty(need, dtype=torch.bfloat16, device=lin.wq.device)
+        tmp = owner._deq_tmp[:need].view(lin.n, lin.k)
+    return lin.dequant(out=tmp)
+
+
 def wq_linear(lin: L.WqLinear, x: torch.Tensor, owner=None, resid: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``bf16 [T, n] = x @ dequant(W)^T (+ resid)``.  The weight is dequantised FM -> bf16 into a reusable buffer, then
     multiplied by the tcgen05 GEMM.  ``B200E_PLAIN_GEMM=1`` selects the library GEMM instead (same-box baseline)."""

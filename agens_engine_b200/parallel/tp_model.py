@@ -12,6 +12,7 @@ same symmetric memory); NCCL is used by the ``use_nccl_decode`` baseline only.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import dataclasses
 from typing import Optional
 
@@ -53,6 +54,8 @@ class TpDenseModel(DenseModel):
                                             status=self._status_all[3:4])                       # logits / winners exchange
         self._gather = PushComm(self._gather_inbox)
         self._prefill_inbox = self._prefill_comm = None      # opened by the first prefill chunk (collective)
+        self._fused_inbox = self._fused_comm = None          # inbox of the fused GEMM + reduce-scatter (first long chunk)
+        self.fused_prefill = os.environ.get("B200E_TP_FUSED_PREFILL", "1") == "1"
 
     # ------------------------------------------------------------------------------------------------ weights
     @staticmethod
@@ -177,6 +180,28 @@ class TpDenseModel(DenseModel):
             out[o:o + m] = full.reshape(-1)[:m]
         return out.view_as(x).to(torch.bfloat16)
 
+    def _row_linear_big(self, lin, x: torch.Tensor) -> torch.Tensor:
+        """Prefill-size row-parallel linear with the reduce-scatter fused into the GEMM (fused path 1 beyond decode
+        rows): the tcgen05 GEMM's epilogue stores every fp32 partial tile into the inbox of the rank that owns its rows,
+        over NVLink, while the remaining tiles are computed; one more kernel sums each rank's rows in rank order, hands the
+        sums to the peers and collects theirs (``PushComm.gemm_reduce_gather``).  No library collective and no separate
+        pass over the partial product.  Chunks that run on the in-kernel-dequant
+        GEMM (up to 256 rows) and the NCCL baseline keep the unfused route."""
+        T = x.shape[0]
+        w = self.world
+        if self.use_nccl_decode or not self.fused_prefill or (T <= 256 and self.prefill_mm) or T < 32 * w:
+            return self._reduce_rows(self._linear_big(lin, x))
+        if self._fused_comm is None:
+            from .comm import PushComm
+            rows = (self.prefill_chunk + 32 + w - 1) // w
+            self._fused_inbox = SymmetricInbox(self.rank, w, (rows * self.cfg.d_model + 3) // 4 * 4, 6, self.dev, status=self._status_all[3:4])
+            self._fused_comm = PushComm(self._fused_inbox)
+        pc = self._fused_comm
+        if ((T + w - 1) // w) * lin.n > self._fused_inbox.slot_stride:
+            return self._reduce_rows(self._linear_big(lin, x))
+        from ..ops import gemm as G
+        return pc.gemm_reduce_gather(x.contiguous(), G.dequant_bf16(lin, self), status=self.status)
+
     def _lm_valid(self) -> int:
         valid = self.full_cfg.vocab_valid or self.full_cfg.vocab
         lo = self.rank * self.vocab_shard
@@ -233,7 +258,7 @@ class TpDenseModel(DenseModel):
         forwards the call), with a host-side barrier before anyone launches again."""
         super().recover()
         self.inbox.rearm_all()
-        for ib, pc in ((self._gather_inbox, self._gather), (self._prefill_inbox, self._prefill_comm)):
+        for ib, pc in ((self._gather_inbox, self._gather), (self._prefill_inbox, self._prefill_comm), (self._fused_inbox, self._fused_comm)):
             if ib is not None:
                 ib.rearm_all()
                 pc.calls, pc.prev_n = 0, 0
@@ -251,6 +276,9 @@ class TpDenseModel(DenseModel):
         if self._prefill_inbox is not None:
             self._prefill_inbox.close()
             self._prefill_inbox = self._prefill_comm = None
+        if self._fused_inbox is not None:
+            self._fused_inbox.close()
+            self._fused_inbox = self._fused_comm = None
         self.inbox.close()
 
     def weight_bytes(self) -> int:

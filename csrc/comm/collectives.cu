@@ -108,6 +108,62 @@ __global__ void push_collective_kernel(const CommArgs a, const float* __restrict
   if (timed_out) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
 }
 
+// Second half of a row-parallel linear whose GEMM epilogue already stored its fp32 partial tiles into the owners' inboxes
+// (b2_gemm_bf16_push, slot A): sum my rows over the source ranks in rank order, write them as bf16 and push the sums to
+// every peer (slot B); then take the peers' rows from slot B as they arrive.  One launch replaces reduce-scatter
+// combine + all-gather + conversion.  Every unit is re-armed by the thread that read it, so the call needs no clearing
+// pass; the caller rotates over three pairs of slots, so a slot is written again two calls after it was read.
+// Rank r owns rows [r * rows_per, (r + 1) * rows_per) of the [total_rows, n_cols] result.
+__global__ void collect_gather_kernel(const CommArgs a, long slot_b_off, int rows_per, int n_cols, int total_rows,
+                                      bf16* __restrict__ out) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const uint64_t t_start = globaltimer_ns();
+  bool timed_out = false;
+  const long n_shard = (long)rows_per * n_cols;
+  auto valid_units = [&](int r) -> long {
+    long rows = (long)total_rows - (long)r * rows_per;
+    rows = rows < 0 ? 0 : (rows > rows_per ? rows_per : rows);
+    return rows * n_cols >> 2;
+  };
+  auto store_bf16 = [&](long flat, const float4& s) {
+    __nv_bfloat162 o[2] = {__floats2bfloat162_rn(s.x, s.y), __floats2bfloat162_rn(s.z, s.w)};
+    *reinterpret_cast<uint2*>(out + flat) = *reinterpret_cast<const uint2*>(o);
+  };
+  const long stride_t = (long)gridDim.x * blockDim.x, first = (long)blockIdx.x * blockDim.x + threadIdx.x;
+  // ---- my rows: combine the partials of slot A, hand the sums on ----
+  float* mine_a = a.inbox[a.rank] + a.slot_off;
+  for (long i = first, nv = valid_units(a.rank); i < nv; i += stride_t) {
+    const long e = i << 2;
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int src = 0; src < a.size; ++src) {
+      float4 v;
+      float* p = mine_a + (long)src * a.slot_stride + e;
+      if (!wait_unit(p, v, t_start, a.timeout_ns)) timed_out = true;
+      clear_unit(p);
+      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    store_bf16((long)a.rank * n_shard + e, s);
+    const float4 sv = sanitize(s);
+    for (int dst = 0; dst < a.size; ++dst)
+      if (dst != a.rank) st_peer_v4(a.inbox[dst] + slot_b_off + (long)a.rank * a.slot_stride + e, sv);
+  }
+  // ---- the peers' rows from slot B ----
+  float* mine_b = a.inbox[a.rank] + slot_b_off;
+  for (int k = 1; k < a.size; ++k) {
+    const int src = (a.rank + k) % a.size;
+    for (long i = first, nv = valid_units(src); i < nv; i += stride_t) {
+      const long e = i << 2;
+      float4 v;
+      float* p = mine_b + (long)src * a.slot_stride + e;
+      if (!wait_unit(p, v, t_start, a.timeout_ns)) timed_out = true;
+      clear_unit(p);
+      store_bf16((long)src * n_shard + e, v);
+    }
+  }
+  if (timed_out) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
+}
+
 // Vocab-parallel argmax: every rank contributes (best value, best index) per token; all ranks pick the same winner
 // (largest value, lowest index on ties).  One thread per token.
 __global__ void argmax_combine_kernel(const CommArgs a, const float* __restrict__ val, const int* __restrict__ idx, int n_tok,
@@ -180,9 +236,20 @@ B2_API int b2_comm_all_gather(const CommArgs* a, const float* in, long n, float*
 
 // in holds size * n elements; rank r receives the sum over ranks of chunk r.
 B2_API int b2_comm_reduce_scatter(const CommArgs* a, const float* in, long n, float* out, cudaStream_t st) {
-  if (!args_ok(a, n) || !in || !out) return B2_ERR_ARG;
+  if (!args_ok(a, n) || (!in && !a->skip_push) || !out) return B2_ERR_ARG;   // skip_push: wait-and-combine only (the pushes came from a fused GEMM epilogue)
   return launch_pdl_c(push_collective_kernel<2>, dim3(grid_of(n >> 2)), dim3(256), st, *a, in, (const bf16*)nullptr, n, out,
                       (bf16*)nullptr);
+}
+
+// See collect_gather_kernel.  a->slot_off is slot A (the GEMM's partials), slot_b_off slot B (the gathered sums); out is
+// bf16 [total_rows, n_cols] contiguous; rows_per * n_cols <= slot_stride, n_cols % 4 == 0.
+B2_API int b2_comm_collect_gather(const CommArgs* a, long slot_b_off, int rows_per, int n_cols, int total_rows, bf16* out,
+                                  cudaStream_t st) {
+  if (!a || !a->status || !out || a->size < 1 || a->size > kCommMaxRanks || a->rank < 0 || a->rank >= a->size) return B2_ERR_ARG;
+  if (rows_per <= 0 || n_cols <= 0 || (n_cols % 4) || total_rows <= 0 || (long)rows_per * a->size < total_rows) return B2_ERR_ARG;
+  if ((long)rows_per * n_cols > a->slot_stride || (a->slot_off % 4) || (slot_b_off % 4) || (a->slot_stride % 4)) return B2_ERR_ARG;
+  return launch_pdl_c(collect_gather_kernel, dim3(grid_of(((long)rows_per * n_cols) >> 2)), dim3(256), st, *a, slot_b_off, rows_per,
+                      n_cols, total_rows, out);
 }
 
 // Barrier = all-gather of one unit whose result is discarded into the caller's 4 * size float scratch (status reports

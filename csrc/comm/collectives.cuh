@@ -26,6 +26,8 @@ B2_API int b2_comm_all_reduce(const b2::CommArgs* a, const float* in_f32, const 
                               bf16* out_bf16, cudaStream_t st);
 B2_API int b2_comm_all_gather(const b2::CommArgs* a, const float* in, long n_per_rank, float* out, cudaStream_t st);
 B2_API int b2_comm_reduce_scatter(const b2::CommArgs* a, const float* in, long n_per_rank, float* out, cudaStream_t st);
+B2_API int b2_comm_collect_gather(const b2::CommArgs* a, long slot_b_off, int rows_per, int n_cols, int total_rows, bf16* out,
+                                  cudaStream_t st);
 B2_API int b2_comm_barrier(const b2::CommArgs* a, cudaStream_t st);
 B2_API int b2_comm_argmax_combine(const b2::CommArgs* a, const float* val, const int* idx, int n_tok, int* out_idx,
                                   float* out_val, cudaStream_t st);

@@ -97,6 +97,12 @@ struct GemmArgs {
   float* Df;                  // fp32 output (or null), same ldd
   const bf16* R; long ldr;    // optional residual added in fp32 before rounding
   int* status;
+  // Fused reduce-scatter (tensor-parallel row-parallel linears): the fp32 partial tile goes straight into the inbox slot
+  // of the rank that owns its rows (rows_per_rank consecutive rows per rank), over NVLink for a peer, with plain stores,
+  // while the other tiles are still being computed.  push[r] = rank r's inbox + slot + this rank's lane inside the slot.
+  float* push[8];
+  int push_ranks;             // 0: off
+  int rows_per_rank;
 };
 
 }  // namespace
@@ -215,6 +221,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
               }
             }
           }
+          if (g.push_ranks) {
+            const int owner = row / g.rows_per_rank;
+            float* pp = g.push[owner] + (size_t)(row - owner * g.rows_per_rank) * g.N + col;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              if (col + i < g.N) {
+                // + 0.f turns -0.0 into +0.0: the bit pattern of -0.0 marks a unit of the inbox that has not arrived
+                asm volatile("st.volatile.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(pp + i), "f"(v[i] + 0.f), "f"(v[i + 1] + 0.f),
+                             "f"(v[i + 2] + 0.f), "f"(v[i + 3] + 0.f) : "memory");
+              }
+          }
           if (g.Df) {
             float* fp = g.Df + (size_t)row * g.ldd + col;
 #pragma unroll
@@ -268,14 +285,19 @@ static bool make_map(CUtensorMap* m, const void* ptr, long rows, long cols, long
 
 // D (bf16 and/or fp32, leading dimension ldd) = A[M,K] (lda) * B[N,K]^T (ldb) + R (optional bf16 residual, ldr).
 // Pointers must be 16-byte aligned, leading dimensions multiples of 8 elements, N a multiple of 8.
-B2_API int b2_gemm_bf16(const bf16* A, long lda, const bf16* B, long ldb, int M, int N, int K, bf16* D, float* Df, long ldd,
-                        const bf16* R, long ldr, int* status, cudaStream_t st) {
+static int gemm_launch(const bf16* A, long lda, const bf16* B, long ldb, int M, int N, int K, bf16* D, float* Df, long ldd,
+                       const bf16* R, long ldr, int* status, float* const* push, int push_ranks, int rows_per_rank, cudaStream_t st) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % 8) || (N % 8) || (lda % 8) || (ldb % 8) || (ldd % 8) || (R && (ldr % 8))) return B2_ERR_ARG;
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) return B2_ERR_ARG;
-  if ((!D && !Df) || (reinterpret_cast<uintptr_t>(D) & 15) || (reinterpret_cast<uintptr_t>(Df) & 15)) return B2_ERR_ARG;
+  if ((!D && !Df && push_ranks <= 0) || (reinterpret_cast<uintptr_t>(D) & 15) || (reinterpret_cast<uintptr_t>(Df) & 15)) return B2_ERR_ARG;
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, M, K, lda, BM) || !make_map(&mb, B, N, K, ldb, BN)) return B2_ERR_LAUNCH;
-  GemmArgs g{M, N, K, D, ldd, Df, R, ldr, status};
+  GemmArgs g{M, N, K, D, ldd, Df, R, ldr, status, {nullptr}, 0, 0};
+  if (push_ranks > 0) {
+    if (push_ranks > 8 || rows_per_rank <= 0 || (long)rows_per_rank * push_ranks < M) return B2_ERR_ARG;
+    for (int r = 0; r < push_ranks; ++r) g.push[r] = push[r];
+    g.push_ranks = push_ranks; g.rows_per_rank = rows_per_rank;
+  }
   const size_t smem = (size_t)kStagesG * STAGE_BYTES + 1024;
   static bool attr = false;
   if (!attr) {
@@ -293,4 +315,21 @@ B2_API int b2_gemm_bf16(const bf16* A, long lda, const bf16* B, long ldb, int M,
   cfg.attrs = at;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, gemm_tc_kernel, ma, mb, g) == cudaSuccess ? B2_OK : B2_ERR_LAUNCH;
+}
+
+B2_API int b2_gemm_bf16(const bf16* A, long lda, const bf16* B, long ldb, int M, int N, int K, bf16* D, float* Df, long ldd,
+                        const bf16* R, long ldr, int* status, cudaStream_t st) {
+  return gemm_launch(A, lda, B, ldb, M, N, K, D, Df, ldd, R, ldr, status, nullptr, 0, 0, st);
+}
+
+// The same product with the reduce-scatter of a tensor-parallel row-parallel linear fused into the epilogue: every fp32
+// partial tile is stored into the inbox slot (inbox[r] + slot_off + rank * slot_stride) of the rank r that owns its rows
+// (rows_per_rank consecutive rows each; rows_per_rank * N <= slot_stride).  The owners then sum the slots in rank order
+// with the wait-and-combine half of the push reduce-scatter (b2_comm_reduce_scatter with skip_push).
+B2_API int b2_gemm_bf16_push(const bf16* A, long lda, const bf16* B, long ldb, int M, int N, int K, float* const* inbox, int ranks,
+                             int rank, long slot_off, long slot_stride, int rows_per_rank, int* status, cudaStream_t st) {
+  if (ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks || (long)rows_per_rank * N > slot_stride || (N % 4)) return B2_ERR_ARG;
+  float* push[8];
+  for (int r = 0; r < ranks; ++r) push[r] = inbox[r] + slot_off + (long)rank * slot_stride;
+  return gemm_launch(A, lda, B, ldb, M, N, K, nullptr, nullptr, 8, nullptr, 0, status, push, ranks, rows_per_rank, st);
 }

@@ -42,6 +42,44 @@ def main():
         pc.barrier()
         torch.cuda.synchronize()
         inbox.check_status()
+        # GEMM with the reduce-scatter fused into its epilogue (partial tiles stored straight into the owners' inboxes):
+        # every rank's rows equal the sum over ranks of the plain products; several calls rotate the slots; row counts
+        # that do not divide by the rank count or the tile height
+        big = SymmetricInbox(rank, world, 512 * 384, 3, dev, timeout_s=2.0)
+        pg = PushComm(big)
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        for T, N, K_ in ((300, 384, 256), (517, 256, 320), (1000, 384, 128), (64 * world, 128, 64)):
+            xa = torch.randn(T, K_, device=dev, generator=g).to(torch.bfloat16)
+            wb = (torch.randn(N, K_, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+            shard, rows_per = pg.gemm_reduce_scatter(xa, wb)
+            full = pg.all_gather(shard).view(world * rows_per, N)[:T]
+            want = xa.float() @ wb.float().t()
+            dist.all_reduce(want)
+            assert torch.allclose(full, want, rtol=2e-3, atol=2e-3 * want.abs().max().item()), (T, N, K_, (full - want).abs().max().item())
+            fa = [torch.empty_like(full) for _ in range(world)]
+            dist.all_gather(fa, full.contiguous())
+            assert all(torch.equal(fa[0], f) for f in fa)       # rank-ordered sums: identical bits on every rank
+        torch.cuda.synchronize()
+        big.check_status("gemm_reduce_scatter")
+        big.close()
+        # the same linear in two launches: GEMM with the push epilogue, then one combine + gather kernel (bf16 result);
+        # seven calls go around the three slot pairs more than twice
+        six = SymmetricInbox(rank, world, 512 * 384, 6, dev, timeout_s=2.0)
+        ps = PushComm(six)
+        for it, (T, N, K_) in enumerate(((300, 384, 256), (517, 256, 320), (1000, 384, 128), (64 * world, 128, 64), (33, 64, 64),
+                                         (999, 384, 256), (512, 384, 64))):
+            xa = torch.randn(T, K_, device=dev, generator=g).to(torch.bfloat16)
+            wb = (torch.randn(N, K_, device=dev, generator=g) * 0.1).to(torch.bfloat16)
+            got = ps.gemm_reduce_gather(xa, wb)
+            want = xa.float() @ wb.float().t()
+            dist.all_reduce(want)
+            assert got.shape == (T, N) and (got.float() - want).abs().max().item() <= 0.01 * want.abs().max().item() + 1e-3, (it, T, N, K_)
+            fa = [torch.empty_like(got) for _ in range(world)]
+            dist.all_gather(fa, got)
+            assert all(torch.equal(fa[0], f) for f in fa)
+        torch.cuda.synchronize()
+        six.check_status("gemm_reduce_gather")
+        six.close()
         # a lost message: the last rank drops its push; every rank's bounded wait runs out and reports, nothing hangs
         inbox.timeout_ns = int(0.2e9)
         out = pc.all_reduce(torch.ones(64, device=dev), skip_push=(rank == world - 1))
@@ -115,6 +153,25 @@ def main():
         torch.cuda.synchronize()
         dist.barrier()
         c.close()
+        # a long prefill chunk takes the fused GEMM + reduce-scatter for its row-parallel linears: the logits after it
+        # agree with the unfused route (push reduce-scatter of the finished product) and are the same bits on every rank
+        long_prompt = torch.randint(0, cfg.vocab, (700,))
+        lg = {}
+        for fused in (True, False):
+            f = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=1, max_ctx=1024, prefill_chunk=512)
+            f.fused_prefill = fused
+            f.prefill_mm = False                   # the dequantise + bf16 GEMM route for every chunk size
+            f.new_seq(0)
+            _, lg[fused] = f.prefill(0, long_prompt, want_logits=True)
+            assert (f._fused_comm is not None) == fused
+            f.inbox.check_status("tp prefill")
+            torch.cuda.synchronize(); dist.barrier()
+            f.close()
+        err = (lg[True] - lg[False]).abs().max().item()
+        assert err <= 0.02 * lg[False].abs().max().item(), err
+        both = [None] * world
+        dist.all_gather_object(both, lg[True].cpu())
+        assert all(torch.equal(x, both[0]) for x in both)
         # fused path vs the NCCL baseline path: same tokens
         b = TpDenseModel.from_oracle(ow, dev, rank, world, max_seqs=1, max_ctx=256, use_nccl_decode=True)
         b.new_seq(0)
