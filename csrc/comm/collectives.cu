@@ -132,33 +132,50 @@ __global__ void collect_gather_kernel(const CommArgs a, long slot_b_off, int row
   };
   const long stride_t = (long)gridDim.x * blockDim.x, first = (long)blockIdx.x * blockDim.x + threadIdx.x;
   // ---- my rows: combine the partials of slot A, hand the sums on ----
+  // All sources' units are requested before the first one is looked at, so a thread has `size` loads in flight; only a
+  // unit that has not arrived yet is polled.
   float* mine_a = a.inbox[a.rank] + a.slot_off;
   for (long i = first, nv = valid_units(a.rank); i < nv; i += stride_t) {
     const long e = i << 2;
+    float4 v[kCommMaxRanks];
+#pragma unroll
+    for (int src = 0; src < kCommMaxRanks; ++src)
+      if (src < a.size) v[src] = ld_vol_v4(mine_a + (long)src * a.slot_stride + e);
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int src = 0; src < a.size; ++src) {
-      float4 v;
-      float* p = mine_a + (long)src * a.slot_stride + e;
-      if (!wait_unit(p, v, t_start, a.timeout_ns)) timed_out = true;
-      clear_unit(p);
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-    }
+#pragma unroll
+    for (int src = 0; src < kCommMaxRanks; ++src)
+      if (src < a.size) {
+        float* p = mine_a + (long)src * a.slot_stride + e;
+        if (!arrived(v[src]) && !wait_unit(p, v[src], t_start, a.timeout_ns)) timed_out = true;
+        clear_unit(p);
+        s.x += v[src].x; s.y += v[src].y; s.z += v[src].z; s.w += v[src].w;
+      }
     store_bf16((long)a.rank * n_shard + e, s);
     const float4 sv = sanitize(s);
     for (int dst = 0; dst < a.size; ++dst)
       if (dst != a.rank) st_peer_v4(a.inbox[dst] + slot_b_off + (long)a.rank * a.slot_stride + e, sv);
   }
-  // ---- the peers' rows from slot B ----
+  // ---- the peers' rows from slot B: four units of a peer in flight per thread ----
   float* mine_b = a.inbox[a.rank] + slot_b_off;
   for (int k = 1; k < a.size; ++k) {
     const int src = (a.rank + k) % a.size;
-    for (long i = first, nv = valid_units(src); i < nv; i += stride_t) {
-      const long e = i << 2;
-      float4 v;
-      float* p = mine_b + (long)src * a.slot_stride + e;
-      if (!wait_unit(p, v, t_start, a.timeout_ns)) timed_out = true;
-      clear_unit(p);
-      store_bf16((long)src * n_shard + e, v);
+    float* base = mine_b + (long)src * a.slot_stride;
+    const long nv = valid_units(src);
+    for (long i = first; i < nv; i += 4 * stride_t) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (i + u * stride_t < nv) v[u] = ld_vol_v4(base + ((i + u * stride_t) << 2));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long iu = i + u * stride_t;
+        if (iu < nv) {
+          float* p = base + (iu << 2);
+          if (!arrived(v[u]) && !wait_unit(p, v[u], t_start, a.timeout_ns)) timed_out = true;
+          clear_unit(p);
+          store_bf16((long)src * n_shard + (iu << 2), v[u]);
+        }
+      }
     }
   }
   if (timed_out) atomicExch(a.status, (int)B2_ERR_TIMEOUT);
