@@ -230,3 +230,115 @@ def test_image_parts_reach_the_engine_callback(tok_path, tok_text):
     body["messages"][0]["content"][1]["image_url"]["url"] = "http://example.com/x.png"
     status, resp = sv.handle("POST", "/v1/chat/completions", body)
     assert status == 400
+
+
+# ---- the other marker family (<|think|> ... <|/think|>, <|call|> ... <|/call|>) and the wire format, without fixtures ----
+FAMILY_TEMPLATE = (
+    "{% for m in messages %}<|agens_start|>{{ m.role }}\n{{ m.content }}<|agens_end|>\n{% endfor %}"
+    "{% if tools %}<tools>{% for t in tools %}{{ t | tojson }}{% endfor %}</tools> calls look like <|call|>...<|/call|>\n{% endif %}"
+    "<|agens_start|>assistant\n{% if enable_thinking is defined and not enable_thinking %}{% else %}<|think|>\n{% endif %}")
+WEATHER = [{"type": "function", "function": {"name": "get_weather", "description": "weather", "parameters": {
+    "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "int"}}}}}]
+
+
+def _family_server(tok_path, tok_text, reply, step=1, **kw):
+    tk = S.Tokenizer(tok_text)
+    sv = S.Server(tok_path, model_name="m", chat_template=FAMILY_TEMPLATE, eos_token_ids=[tk.encode("<|im_end|>")[0]], **kw)
+    sv.use_mock(tk.encode(reply) + tk.encode("<|im_end|>"), step=step)
+    return sv, tk
+
+
+def _events(body):
+    out = []
+    for line in body.split("\n\n"):
+        if line.startswith("data: {"):
+            out.append(json.loads(line[6:]))
+    return out
+
+
+def test_marker_family_comes_from_the_template_and_generation_starts_in_reasoning(tok_path, tok_text):
+    reply = "plan it\n<|/think|>\n\nThe answer."
+    sv, tk = _family_server(tok_path, tok_text, reply)
+    st, body = sv.handle("POST", "/v1/chat/completions", {"rid": "R1", "messages": [{"role": "user", "content": "hi"}]})
+    r = json.loads(body)
+    assert st == 200 and r["id"] == "R1" and list(r) == ["id", "object", "created", "model", "choices", "usage", "metadata"]
+    ch = r["choices"][0]
+    assert list(ch) == ["index", "message", "logprobs", "finish_reason", "matched_stop"]
+    assert ch["message"] == {"role": "assistant", "content": "\n\nThe answer.", "reasoning_content": "plan it\n", "tool_calls": None}
+    eos = tk.encode("<|im_end|>")[0]
+    assert ch["finish_reason"] == "stop" and ch["matched_stop"] == eos
+    n_out = len(tk.encode(reply)) + 1
+    n_reason = len(tk.encode("plan it\n<|/think|>"))             # tokens through the closing marker (several byte tokens here)
+    assert r["usage"]["completion_tokens"] == n_out and r["usage"]["reasoning_tokens"] == n_reason
+    assert r["usage"]["prompt_tokens_details"] is None and r["metadata"] == {"weight_version": "default"}
+    # thinking off: the template leaves the block closed, nothing is reasoning and no reasoning tokens are counted
+    sv, _ = _family_server(tok_path, tok_text, "Just text.")
+    st, body = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}],
+                                                          "chat_template_kwargs": {"enable_thinking": False}})
+    r = json.loads(body)
+    assert r["choices"][0]["message"]["content"] == "Just text." and r["choices"][0]["message"]["reasoning_content"] is None
+    assert r["usage"]["reasoning_tokens"] == 0
+    # reasoning alone, with force_nonempty_content: it becomes the content
+    sv, _ = _family_server(tok_path, tok_text, "only thoughts")
+    st, body = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}],
+                                                          "chat_template_kwargs": {"force_nonempty_content": True}})
+    msg = json.loads(body)["choices"][0]["message"]
+    assert msg["content"] == "only thoughts" and msg["reasoning_content"] is None
+
+
+def test_streamed_tool_call_goes_out_piece_by_piece(tok_path, tok_text):
+    reply = ("think\n<|/think|>\n\nFirst.\n\n<|call|>\n<function=get_weather>\n<parameter=city>\nHong Kong\n</parameter>\n"
+             "<parameter=days>\n2\n</parameter>\n</function>\n<|/call|>")
+    for step in (1, 5):
+        sv, tk = _family_server(tok_path, tok_text, reply, step=step)
+        body = {"rid": "R2", "messages": [{"role": "user", "content": "weather?"}], "tools": WEATHER, "stream": True,
+                "stream_options": {"include_usage": True}}
+        st, text = sv.handle("POST", "/v1/chat/completions", body)
+        assert st == 200 and text.endswith("data: [DONE]\n\n")
+        ev = _events(text)
+        first = ev[0]["choices"][0]
+        assert first["delta"] == {"reasoning_content": None, "role": "assistant", "content": ""} and "usage" not in ev[0]
+        reasoning = "".join(e["choices"][0]["delta"].get("reasoning_content") or "" for e in ev if e["choices"])
+        content = "".join(e["choices"][0]["delta"].get("content") or "" for e in ev if e["choices"])
+        assert reasoning == "think\n" and content == "\n\nFirst.\n\n"
+        calls = [e["choices"][0]["delta"]["tool_calls"][0] for e in ev if e["choices"] and e["choices"][0]["delta"].get("tool_calls")]
+        assert calls[0]["id"].startswith("call_") and calls[0]["function"] == {"name": "get_weather", "arguments": ""}
+        assert [c["function"]["arguments"] for c in calls[1:]] == ["{", '"city": "Hong Kong"', ', "days": 2', "}"]
+        assert all(c["id"] is None and c["function"]["name"] is None and c["index"] == 0 for c in calls[1:])
+        # content events of a request with tools carry every delta field and a usage key
+        with_content = [e for e in ev if e["choices"] and e["choices"][0]["delta"].get("content")]
+        assert set(with_content[0]["choices"][0]["delta"]) == {"role", "content", "reasoning_content", "tool_calls"} and "usage" in with_content[0]
+        fin = [e for e in ev if e["choices"] and e["choices"][0]["finish_reason"]][-1]["choices"][0]
+        assert fin["finish_reason"] == "tool_calls" and fin["matched_stop"] == tk.encode("<|im_end|>")[0]
+        assert ev[-1]["choices"] == [] and ev[-1]["usage"]["completion_tokens"] == len(tk.encode(reply)) + 1
+    # the complete response of the same output: arguments typed by the (normalised) schema, no matched stop
+    sv, tk = _family_server(tok_path, tok_text, reply)
+    st, text = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "weather?"}], "tools": WEATHER})
+    ch = json.loads(text)["choices"][0]
+    assert ch["finish_reason"] == "tool_calls" and ch["matched_stop"] is None and ch["message"]["content"] == "\n\nFirst.\n\n"
+    tc = ch["message"]["tool_calls"][0]
+    assert tc["index"] == 0 and tc["function"] == {"name": "get_weather", "arguments": '{"city": "Hong Kong", "days": 2}'}
+
+
+def test_stop_strings_errors_and_completion_stream(tok_path, tok_text):
+    sv, tk = _family_server(tok_path, tok_text, "r\n<|/think|>\n\nalpha beta STOP gamma")
+    st, text = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "stop": "STOP"})
+    ch = json.loads(text)["choices"][0]
+    assert ch["message"]["content"] == "\n\nalpha beta " and ch["finish_reason"] == "stop" and ch["matched_stop"] == "STOP"
+    # validation errors: the reference's flat body
+    st, text = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "tool_choice": "required"})
+    assert st == 400 and json.loads(text) == {"object": "error", "message": "Tools cannot be empty if tool choice is set to required.",
+                                               "type": "BadRequestError", "param": None, "code": 400}
+    st, text = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "tools": WEATHER,
+                                                          "tool_choice": {"type": "function", "function": {"name": "nope"}}})
+    assert st == 400 and json.loads(text)["message"] == "Tool 'nope' not found in tools list."
+    st, text = sv.handle("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "x"}], "max_tokens": 10 ** 7})
+    assert st == 400 and "is too large" in json.loads(text)["message"]
+    # /v1/completions stream: one event per step, the last step carries its text and the finish reason
+    sv2 = S.Server(tok_path, model_name="m")
+    sv2.use_mock(tk.encode("one two three"), step=1)
+    st, text = sv2.handle("POST", "/v1/completions", {"prompt": "count", "max_tokens": 3, "stream": True, "stream_options": {"include_usage": True}})
+    ev = _events(text)
+    assert [e["choices"][0]["finish_reason"] for e in ev if e["choices"]] == [None, None, "length"]
+    assert "".join(e["choices"][0]["text"] for e in ev if e["choices"]) == tk.decode(tk.encode("one two three")[:3], skip_special=False)
+    assert ev[-1]["choices"] == [] and "prompt_tokens_details" not in ev[-1]["usage"]
