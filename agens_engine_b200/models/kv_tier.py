@@ -36,6 +36,8 @@ class HostKvTier:
         self.bt_stage = (torch.arange(model.pages_per_seq, dtype=torch.int32, device=model.dev) % batch_pages)[None, :] \
             .expand(model.max_seqs, -1)
         self.blocks: Dict[int, List[torch.Tensor]] = {}        # seq -> pinned [layers, B, 2, hkv, 16, hd] per batch
+        self.ready: Dict[int, List[torch.cuda.Event]] = {}     # seq -> per batch: its device-to-host copies are complete
+        self._free: List[torch.Tensor] = []                    # pinned blocks of ended sequences, reused (no allocation per batch)
         self.bytes_h2d = 0
         self.bytes_d2h = 0
 
@@ -55,19 +57,30 @@ class HostKvTier:
         b = len(self.blocks.setdefault(seq, []))
         lo = b * self.B
         idx = torch.tensor(m.seq_pages[seq][lo:lo + self.B], dtype=torch.long, device=m.dev)
-        blk = torch.empty((m.cfg.n_layers, self.B) + tuple(m.kv[0].shape[1:]), dtype=torch.bfloat16, pin_memory=True)
+        blk = self._free.pop() if self._free else \
+            torch.empty((m.cfg.n_layers, self.B) + tuple(m.kv[0].shape[1:]), dtype=torch.bfloat16, pin_memory=True)
+        main = torch.cuda.current_stream(m.dev)
         for l, kv in enumerate(m.kv):
             blk[l].copy_(kv.index_select(0, idx), non_blocking=True)
-        torch.cuda.current_stream(m.dev).synchronize()          # the pages are reused as soon as they are freed
+        # No host wait: whatever writes the freed pages next is ordered behind these copies on the same stream, and the
+        # side stream that brings the block back waits for this event before it reads the pinned memory.
+        ev = torch.cuda.Event()
+        ev.record(main)
         self.bytes_d2h += blk.numel() * 2
         self.blocks[seq].append(blk)
+        self.ready.setdefault(seq, []).append(ev)
         for i in range(lo, lo + self.B):
             m.pool.evict_page(m._aid[seq], i)
             m.seq_pages[seq][i] = HOST_PAGE
         m.block_table[seq, lo:lo + self.B] = HOST_PAGE
 
     def drop(self, seq: int):
-        self.blocks.pop(seq, None)
+        blks, evs = self.blocks.pop(seq, None), self.ready.pop(seq, None)
+        if blks:
+            for e in evs or ():
+                e.synchronize()                                 # a block is only reused once its copies have landed
+            self.copy_stream.synchronize()                      # ... and nothing is still reading it back
+            self._free.extend(blks)
 
     # ------------------------------------------------------------------------------------------------ attention
     def attend(self, layer: int, q, grp_tok0, grp_cnt, tok_pos, tok_seq, tiered_groups: Dict[int, tuple], split_keys: int,
@@ -87,6 +100,7 @@ class HostKvTier:
                 buf = k % 2
                 with torch.cuda.stream(self.copy_stream):
                     self.copy_stream.wait_event(self.ev_used[buf])           # the launch that last read this buffer
+                    self.copy_stream.wait_event(self.ready[seq][b])          # the block's own device-to-host copies
                     self.stage[buf].copy_(blk[layer], non_blocking=True)
                     self.ev_copied[buf].record(self.copy_stream)
                 self.bytes_h2d += blk[layer].numel() * 2
