@@ -342,6 +342,123 @@ def cmd_batch(ns):
     return 0 if ok else 1
 
 
+def cmd_spec_batch(ns):
+    """Batched speculation gate (reference: m1-spec-batch, crates/agens-cli/src/spec.rs ``run_batch``): several
+    sequences verify their draft blocks in one step; with perfect, corrupted and garbage drafts every sequence emits
+    exactly its plain greedy tokens."""
+    from .spec import SpecDecoder
+    cfg = EngineConfig.resolve(ns)
+    nb = max(2, int(ns.sequences))
+    depth = max(1, min(cfg.draft_depth, 7))
+    m, rank, world, _ = build_model(cfg, max_seqs=nb, max_ctx=max(cfg.wctx, ns.prompt_len + ns.new_tokens + 16))
+    m.row_graphs = bool(cfg.row_graphs)
+    prompts = [_prompt(m.cfg, max(4, ns.prompt_len - 5 * i), cfg.seed + i) for i in range(nb)]
+    plain = [SpecDecoder(m, [], max_drafts=0).generate(0, p, ns.new_tokens) for p in prompts]
+    ok, rep = True, {"plain_hash": _hash([t for p in plain for t in p])}
+    for mode in ("perfect", "corrupt", "garbage"):
+        dec = SpecDecoder(m, [], max_drafts=depth)
+        outs = [[dec.begin(i, p)] for i, p in enumerate(prompts)]
+        while any(len(o) < ns.new_tokens for o in outs):
+            live = [i for i, o in enumerate(outs) if len(o) < ns.new_tokens]
+            forced = {}
+            for i in live:
+                d = plain[i][len(outs[i]):len(outs[i]) + depth]
+                if mode == "corrupt" and len(d) > ns.corrupt:
+                    d = d[:ns.corrupt] + [(d[ns.corrupt] + 1) % m.cfg.vocab] + d[ns.corrupt + 1:]
+                if mode == "garbage":
+                    d = [(t + 7) % m.cfg.vocab for t in d]
+                forced[i] = d
+            for i, toks in dec.step(live, forced_drafts=forced).items():
+                outs[i] += toks
+        for i in range(nb):
+            dec.end(i)
+        same = all(o[:ns.new_tokens] == p for o, p in zip(outs, plain))
+        rep[mode] = {"equal": same, "tokens_per_step": round(dec.stats.tokens_per_step(), 2)}
+        ok &= same
+    print(json.dumps(rep))
+    return 0 if ok else 1
+
+
+def cmd_agent_replay(ns):
+    """Agent-session replay (reference: m2a-demo, crates/agens-cli/src/m1.rs:1417-1514).  ``transcripts`` is a JSON
+    list of sessions, each a list of turns, each turn the full prompt ids of that turn (consecutive turns share a
+    growing prefix).  Mode ``session`` keeps one resident sequence per transcript holding the prefix common to
+    consecutive turns: a turn advances it by the new tokens only, forks it, prefills the rest of the turn's prompt on
+    the fork, generates greedily and frees the fork; nothing is prefilled twice.  Mode ``reprefill`` prefills every
+    turn from scratch.  Both write per turn the time to the first token and the generated tokens to ``out``; ``--check``
+    runs both and reports how far their tokens agree."""
+    import time
+    import torch
+    cfg = EngineConfig.resolve(ns)
+    sessions = json.load(open(ns.transcripts))
+    if ns.max_sessions:
+        sessions = sessions[:ns.max_sessions]
+    longest = max(len(t) for s_ in sessions for t in s_)
+    m, rank, world, _ = build_model(cfg, max_seqs=2, max_ctx=max(cfg.wctx, longest + ns.new_tokens + 16))
+    m.set_linear_path(1)          # one linear kernel family whatever the chunk size, so that both modes see the same numerics
+
+    def generate(seq, first):
+        out, tok = [first], first
+        while len(out) < ns.new_tokens and tok != ns.eos:
+            o, _ = m.forward_rows([tok], [seq]); tok = int(o[0]); out.append(tok)
+        return out
+
+    def run(mode):
+        rows = []
+        for si, turns in enumerate(sessions):
+            if mode == "session":
+                m.new_seq(0)
+            kept: List[int] = []
+            for ti, ids in enumerate(turns):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                if mode == "session":
+                    nxt = turns[ti + 1] if ti + 1 < len(turns) else ids
+                    keep = 0
+                    while keep < min(len(ids), len(nxt)) and ids[keep] == nxt[keep]:
+                        keep += 1
+                    keep = max(len(kept), min(keep, len(ids) - 1))        # the resident prefix only grows; one token stays for the fork
+                    common = 0
+                    while common < min(len(kept), len(ids)) and kept[common] == ids[common]:
+                        common += 1
+                    if common < len(kept):                                  # the conversation was edited: drop what differs
+                        m.truncate(0, common); kept = kept[:common]; keep = max(keep, common)
+                    if keep > len(kept):
+                        m.prefill(0, torch.tensor(ids[len(kept):keep], dtype=torch.int32)); kept = list(ids[:keep])
+                    m.fork(0, 1)
+                    first, _ = m.prefill(1, torch.tensor(ids[len(kept):], dtype=torch.int32))
+                else:
+                    m.new_seq(1)
+                    first, _ = m.prefill(1, torch.tensor(ids, dtype=torch.int32))
+                torch.cuda.synchronize()
+                ttft = time.perf_counter() - t0
+                toks = generate(1, first)
+                m.free_seq(1)
+                rows.append({"session": si, "turn": ti, "prompt_tokens": len(ids), "ttft_s": round(ttft, 4), "tokens": toks})
+            if mode == "session":
+                m.free_seq(0)
+        return rows
+
+    modes = ["session", "reprefill"] if ns.check else [ns.replay_mode]
+    res = {md: run(md) for md in modes}
+    json.dump(res, open(ns.out, "w"))
+    rep = {md: {"turns": len(r), "mean_ttft_s": round(sum(x["ttft_s"] for x in r) / max(len(r), 1), 4)} for md, r in res.items()}
+    ok = True
+    if ns.check:
+        a_, b_ = [x["tokens"] for x in res["session"]], [x["tokens"] for x in res["reprefill"]]
+        # The two modes cut the prompt into different chunks, and chunks of different sizes take different kernels (their
+        # sums run in different orders), so the comparison is an agreement rate, not bit equality: the first generated
+        # token of every turn, and all positions up to the first difference of a turn.
+        first = sum(int(x[0] == y[0]) for x, y in zip(a_, b_)) / max(len(a_), 1)
+        same = sum(next((i for i, (p, q) in enumerate(zip(x, y)) if p != q), min(len(x), len(y))) for x, y in zip(a_, b_))
+        rep["tokens_equal"] = a_ == b_
+        rep["first_token_agreement"] = round(first, 3)
+        rep["agreement_until_first_difference"] = round(same / max(sum(len(x) for x in a_), 1), 3)
+        ok = first >= ns.min_agreement
+    print(json.dumps(rep))
+    return 0 if ok else 1
+
+
 def cmd_session(ns):
     """Session gate: park -> clobber -> unpark restores exactly; a fork continues like its parent."""
     import torch
@@ -516,6 +633,12 @@ def main(argv=None) -> int:
     p = sub.add_parser("kv"); _engine_flags(p); p.add_argument("--save-logits"); p.add_argument("--cmp-logits"); p.set_defaults(fn=cmd_kv)
     p = sub.add_parser("spec"); _engine_flags(p); p.add_argument("--corrupt", type=int, default=2); p.set_defaults(fn=cmd_spec)
     p = sub.add_parser("batch"); _engine_flags(p); p.add_argument("--batch", default="2,4,8"); p.set_defaults(fn=cmd_batch)
+    p = sub.add_parser("spec-batch"); _engine_flags(p); p.add_argument("--corrupt", type=int, default=2)
+    p.add_argument("--sequences", type=int, default=4); p.set_defaults(fn=cmd_spec_batch)
+    p = sub.add_parser("agent-replay"); _engine_flags(p); p.add_argument("transcripts"); p.add_argument("out")
+    p.add_argument("--replay-mode", choices=["session", "reprefill"], default="session"); p.add_argument("--check", action="store_true")
+    p.add_argument("--max-sessions", type=int, default=0); p.add_argument("--eos", type=int, default=-1)
+    p.add_argument("--min-agreement", type=float, default=0.75); p.set_defaults(fn=cmd_agent_replay)
     p = sub.add_parser("serve"); _engine_flags(p)
     p.add_argument("--host"); p.add_argument("--port", type=int); p.add_argument("--served-model-name")
     p.add_argument("--spec-copy", type=int); p.add_argument("--spec-drafter"); p.add_argument("--mtp")

@@ -52,6 +52,32 @@ def test_cli_gates_gpu(capsys):
     assert rc == 0, out
     rc, out = _run(capsys, ["load"] + base)
     assert rc == 0 and json.loads(out)["tp"] == 1
+    rc, out = _run(capsys, ["spec-batch"] + base + ["--sequences", "3", "--draft-depth", "3"])
+    assert rc == 0 and all(json.loads(out)[k]["equal"] for k in ("perfect", "corrupt", "garbage")), out
+    assert json.loads(out)["perfect"]["tokens_per_step"] > 2.5
+
+
+@pytest.mark.gpu
+def test_cli_agent_replay_gpu(capsys, tmp_path):
+    """Agent-session replay: growing multi-turn prompts served from one resident sequence (advance, fork, prefill the
+    rest, generate) agree with prefilling every turn from scratch (first tokens; chunk sizes differ, so not bit for bit)."""
+    import random
+    rnd = random.Random(5)
+    sessions = []
+    for s_ in range(2):
+        ids = [rnd.randrange(1000) for _ in range(40)]
+        turns = []
+        for t in range(4):
+            ids = ids + [rnd.randrange(1000) for _ in range(25 + 7 * t)]       # tool results and the next question
+            turns.append(ids + [rnd.randrange(1000) for _ in range(6)])       # the generation prompt of this turn only
+        sessions.append(turns)
+    (tmp_path / "t.json").write_text(json.dumps(sessions))
+    rc, out = _run(capsys, ["agent-replay", "--random", "oracle-tiny", "--wctx", "512", "--new-tokens", "8", str(tmp_path / "t.json"),
+                            str(tmp_path / "o.json"), "--check"])
+    rep = json.loads(out)
+    assert rc == 0 and rep["first_token_agreement"] >= 0.75 and rep["session"]["turns"] == 8, out
+    rows = json.load(open(tmp_path / "o.json"))["session"]
+    assert all(len(r["tokens"]) == 8 for r in rows)
 
 
 def test_compare_tools(tmp_path):
