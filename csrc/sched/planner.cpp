@@ -110,7 +110,9 @@ static Json scratch_items(const PlanIn& p) {
   it.set("attention_partials", (long long)(rows * (p.n_heads / p.tp) * splits * (p.head_dim + 2) * 4));
   it.set("gemv_scratch", (long long)(64ll << 20));
   it.set("logits", (long long)32 * (p.vocab / p.tp) * 4);
-  it.set("tp_inboxes", (long long)(p.tp > 1 ? 129ll * p.tp * 32 * p.d_model * 4 : 0));
+  // per-step inboxes of the fused decode all-reduce, plus the inbox of the fused GEMM + reduce-scatter of prefill chunks:
+  // six slots of (chunk + 32) rows x d_model fp32 over all source ranks together
+  it.set("tp_inboxes", (long long)(p.tp > 1 ? 129ll * p.tp * 32 * p.d_model * 4 + 6ll * (T + 32 + p.tp) * p.d_model * 4 : 0));
   it.set("runtime_reserve", runtime_reserve(p.max_batch));
   return it;
 }
