@@ -342,3 +342,34 @@ def test_stop_strings_errors_and_completion_stream(tok_path, tok_text):
     assert [e["choices"][0]["finish_reason"] for e in ev if e["choices"]] == [None, None, "length"]
     assert "".join(e["choices"][0]["text"] for e in ev if e["choices"]) == tk.decode(tk.encode("one two three")[:3], skip_special=False)
     assert ev[-1]["choices"] == [] and "prompt_tokens_details" not in ev[-1]["usage"]
+
+
+def test_tools_reach_the_template_in_normal_form(tok_path, tok_text):
+    """Tools as the template sees them: description / name / parameters / strict in that order plus defer_loading,
+    database-style type names rewritten to JSON-schema ones, a named tool_choice listing that tool only."""
+    tpl = "{% for t in tools %}{{ t | tojson }}\n{% endfor %}{{ messages[0].content }}"
+    tk = S.Tokenizer(tok_text)
+    sv = S.Server(tok_path, model_name="m", chat_template=tpl)
+    sv.use_mock(tk.encode("ok"), step=1)
+    tools = [{"type": "function", "function": {"name": "db", "parameters": {"type": "object", "properties": {
+                 "id": {"type": "int"}, "name": {"type": "varchar(255)"}, "price": {"type": "decimal(10,2)"}, "tags": {"type": "list[str]"},
+                 "meta": {"type": "map"}, "flag": {"type": ["bool", "null", "boolean"]}, "u": {"type": "uint8"}, "other": {"type": "widget"},
+                 "nested": {"type": "object", "properties": {"when": {"type": "TIMESTAMP"}}, "items": {"type": "float32"}}}}}},
+             {"type": "function", "function": {"name": "second", "description": "d", "parameters": {"type": "object"}, "strict": True},
+              "defer_loading": True}]
+    body = {"messages": [{"role": "user", "content": "END"}], "tools": tools, "max_tokens": 2}
+    assert sv.handle("POST", "/v1/chat/completions", body)[0] == 200
+    lines = tk.decode(sv.mock_calls()[-1]["prompt"], skip_special=False).split("\n")
+    first, second = json.loads(lines[0]), json.loads(lines[1])
+    assert list(first) == ["type", "function", "defer_loading"] and first["defer_loading"] is None
+    assert list(first["function"]) == ["description", "name", "parameters", "strict"] and first["function"]["strict"] is False
+    props = first["function"]["parameters"]["properties"]
+    assert {k: v["type"] for k, v in props.items() if k != "nested"} == {
+        "id": "integer", "name": "string", "price": "number", "tags": "array", "meta": "object", "flag": ["boolean", "null"],
+        "u": "integer", "other": "widget"}
+    assert props["nested"]["properties"]["when"]["type"] == "string" and props["nested"]["items"]["type"] == "number"
+    assert second["function"]["strict"] is True and second["function"]["defer_loading"] is True and second["defer_loading"] is True
+    # a named tool_choice: only that tool is shown
+    assert sv.handle("POST", "/v1/chat/completions", dict(body, tool_choice={"type": "function", "function": {"name": "second"}}))[0] == 200
+    text = tk.decode(sv.mock_calls()[-1]["prompt"], skip_special=False)
+    assert text.count("\n") == 1 and json.loads(text.split("\n")[0])["function"]["name"] == "second"
