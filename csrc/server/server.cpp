@@ -298,7 +298,8 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
   std::string finish = "length";
   Json matched = Json();                         // stop token id, stop string, or null
   // reasoning tokens: every token of a request with thinking on, through the closing think tag when one comes
-  bool count_reasoning = (thinking || starts_in_reasoning) && !sv.think_close_ids.empty();
+  // (with the built-in ChatML renderer the model opens its think block itself, if at all: counted from the text below)
+  bool count_reasoning = !sv.chat_template.empty() && (thinking || starts_in_reasoning) && !sv.think_close_ids.empty();
   bool force_nonempty = false;                   // chat_template_kwargs.force_nonempty_content: reasoning alone becomes the content
   if (auto k = body.find("chat_template_kwargs"); k && k->is_object()) force_nonempty = k->get_bool("force_nonempty_content", false);
   std::string whole;                             // non-streaming: the text is parsed once, when it is complete
@@ -462,6 +463,8 @@ static HttpResponse run_generation(Server& sv, const Json& body, bool chat, cons
     content_all = reasoning_all;
     reasoning_all.clear();
   }
+  if (sv.chat_template.empty() && chat && !reasoning_all.empty() && sv.has_tok)
+    n_reasoning_tokens = std::min<long long>(n_out, (long long)sv.tok.encode(tg.think_open + reasoning_all).size() + (long long)sv.think_close_ids.size());
   // a stop token after at least one call reads as "tool_calls"; the complete response then reports no matched stop
   const bool by_calls = !calls.empty() && finish == "stop" && matched.is_int();
   sv.n_completion_tokens += n_out;

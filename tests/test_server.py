@@ -101,6 +101,7 @@ def test_chat_completion_non_stream_defaults_and_usage(tok_path, tok_text):
     assert msg["content"] == "hello world" and msg["reasoning_content"] == "hm" and r["choices"][0]["finish_reason"] == "stop"
     assert r["usage"]["prompt_tokens"] == len(tk.encode(S.render_chat([{"role": "user", "content": "hi"}])))
     assert r["usage"]["completion_tokens"] == len(tk.encode("<think>hm</think>\n\nhello world")) + 1
+    assert r["usage"]["reasoning_tokens"] == len(tk.encode("<think>hm")) + len(tk.encode("</think>"))
     call = sv.mock_calls()[0]
     assert call["session_id"] == "abc"                                 # header wins / is forwarded
     s = call["sampling"]
