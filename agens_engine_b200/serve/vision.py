@@ -37,11 +37,12 @@ def _h():
         h.b2h_jpeg_info.argtypes, h.b2h_jpeg_info.restype = [vp, C.c_long, ip, ip, ip], i
         h.b2h_jpeg_decode.argtypes, h.b2h_jpeg_decode.restype = [vp, C.c_long, vp], i
         h.b2h_jpeg_error.argtypes, h.b2h_jpeg_error.restype = [], C.c_char_p
-        for nm in ("b2h_bmp_info", "b2h_gif_info"):
+        for nm in ("b2h_bmp_info", "b2h_gif_info", "b2h_webp_info"):
             getattr(h, nm).argtypes, getattr(h, nm).restype = [vp, C.c_long, ip, ip], i
-        for nm in ("b2h_bmp_decode", "b2h_gif_decode"):
+        for nm in ("b2h_bmp_decode", "b2h_gif_decode", "b2h_webp_decode"):
             getattr(h, nm).argtypes, getattr(h, nm).restype = [vp, C.c_long, vp], i
         h.b2h_image_error.argtypes, h.b2h_image_error.restype = [], C.c_char_p
+        h.b2h_webp_error.argtypes, h.b2h_webp_error.restype = [], C.c_char_p
         _sig = True
     return h
 
@@ -95,7 +96,7 @@ def decode_image(data: bytes) -> np.ndarray:
     """uint8 [h, w, 3] from a binary PPM, a non-interlaced 8-bit PNG (RGB, RGBA, grey, grey+alpha, palette; alpha is
     dropped) or a baseline JPEG (``csrc/server/jpeg.cpp``: grey or three components, 1x / 2x sampling factors, restart
     intervals; progressive and arithmetic-coded files are refused with a message), an uncompressed BMP or the first
-    frame of a GIF (``csrc/server/image_misc.cpp``)."""
+    frame of a GIF (``csrc/server/image_misc.cpp``), or a lossless WebP (``csrc/server/webp.cpp``)."""
     if data[:2] == b"P6":
         h, w = C.c_int(), C.c_int()
         buf = (C.c_ubyte * len(data)).from_buffer_copy(data)
@@ -111,6 +112,8 @@ def decode_image(data: bytes) -> np.ndarray:
         return _decode_simple(data, "bmp")
     if data[:4] == b"GIF8":
         return _decode_simple(data, "gif")
+    if data[:4] == b"RIFF" and data[8:12] == b"WEBP":
+        return _decode_simple(data, "webp")
     raise ValueError("unknown image format")
 
 
@@ -129,16 +132,19 @@ def _decode_jpeg(data: bytes) -> np.ndarray:
 
 
 def _decode_simple(data: bytes, kind: str) -> np.ndarray:
-    """BMP (uncompressed 8 / 24 / 32-bit) and GIF (first frame) through ``csrc/server/image_misc.cpp``."""
+    """BMP (uncompressed 8 / 24 / 32-bit) and GIF (first frame) through ``csrc/server/image_misc.cpp``; lossless WebP
+    through ``csrc/server/webp.cpp`` (lossy WebP is refused with a message)."""
     lib = _h()
-    info, dec = (lib.b2h_bmp_info, lib.b2h_bmp_decode) if kind == "bmp" else (lib.b2h_gif_info, lib.b2h_gif_decode)
+    info, dec, err = {"bmp": (lib.b2h_bmp_info, lib.b2h_bmp_decode, lib.b2h_image_error),
+                      "gif": (lib.b2h_gif_info, lib.b2h_gif_decode, lib.b2h_image_error),
+                      "webp": (lib.b2h_webp_info, lib.b2h_webp_decode, lib.b2h_webp_error)}[kind]
     buf = (C.c_ubyte * len(data)).from_buffer_copy(data)
     h, w = C.c_int(), C.c_int()
     if info(buf, len(data), C.byref(h), C.byref(w)) != 0:
-        raise ValueError(lib.b2h_image_error().decode() or f"bad {kind}")
+        raise ValueError(err().decode() or f"bad {kind}")
     out = np.empty((h.value, w.value, 3), dtype=np.uint8)
     if dec(buf, len(data), out.ctypes.data_as(C.c_void_p)) != 0:
-        raise ValueError(lib.b2h_image_error().decode() or f"bad {kind}")
+        raise ValueError(err().decode() or f"bad {kind}")
     return out
 
 
