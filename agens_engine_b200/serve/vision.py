@@ -94,8 +94,8 @@ def mrope_positions(ids: Sequence[int], pad_id: int, grids: Sequence[Tuple[int, 
 # ---------------------------------------------------------------------------------------------------------------------
 def decode_image(data: bytes) -> np.ndarray:
     """uint8 [h, w, 3] from a binary PPM, a non-interlaced 8-bit PNG (RGB, RGBA, grey, grey+alpha, palette; alpha is
-    dropped) or a baseline JPEG (``csrc/server/jpeg.cpp``: grey or three components, 1x / 2x sampling factors, restart
-    intervals; progressive and arithmetic-coded files are refused with a message), an uncompressed BMP or the first
+    dropped) or a JPEG (``csrc/server/jpeg.cpp``: sequential or progressive, grey or three components, 1x / 2x sampling
+    factors, restart intervals; arithmetic-coded files are refused with a message), an uncompressed BMP or the first
     frame of a GIF (``csrc/server/image_misc.cpp``), or a lossless WebP (``csrc/server/webp.cpp``)."""
     if data[:2] == b"P6":
         h, w = C.c_int(), C.c_int()

@@ -1,9 +1,12 @@
-// Baseline JPEG decoder (ITU-T T.81 sequential DCT, Huffman coding, 8-bit samples) for image inputs of chat requests.
+// JPEG decoder (ITU-T T.81 sequential and progressive DCT, Huffman coding, 8-bit samples) for image inputs of chat requests.
 //
 // The reference decodes JPEG data URLs with nvJPEG on the GPU (kernels/oracle/bridge/vision.cpp:204-228) after the
 // server recognised the format (crates/agens-server/src/vision.rs:126-135).  Here the decode runs on the host next to
 // the PNG / PPM readers: one or three components, any 1x / 2x sampling factors (4:4:4, 4:2:2, 4:4:0, 4:2:0), restart
-// intervals, JFIF YCbCr or Adobe RGB colour.  Progressive, arithmetic-coded, 12-bit and CMYK files are refused with a
+// intervals, JFIF YCbCr or Adobe RGB colour, any number of scans: interleaved or one component per scan, and the
+// progressive mode (spectral selection and successive approximation: DC / AC first and refinement scans with
+// end-of-band runs).  Every scan writes into per-component coefficient buffers; dequantisation and the inverse DCT run
+// once after the last scan.  Arithmetic-coded, lossless, hierarchical, 12-bit and CMYK files are refused with a
 // message.  Chroma is upsampled with the triangle filter common decoders use by default, so results stay within a
 // few levels of theirs.
 #include <algorithm>
@@ -28,7 +31,9 @@ struct Huff {
 struct Comp {
   int id = 0, h = 1, v = 1, tq = 0, td = 0, ta = 0;
   int bw = 0, bh = 0;                        // blocks per row / column (padded to whole MCUs)
+  int nbw = 0, nbh = 0;                      // blocks per row / column that a scan of this component alone visits
   int pred = 0;
+  std::vector<int16_t> coef;                 // bw * bh blocks of 64 coefficients (natural order), filled by the scans
   std::vector<uint8_t> plane;                // bw * 8 x bh * 8 samples
 };
 
@@ -45,6 +50,11 @@ struct Dec {
   Comp comp[3];
   int restart = 0;
   int hmax = 1, vmax = 1;
+  // the scan being decoded
+  Comp* scan_comp[3] = {nullptr, nullptr, nullptr};
+  int scan_n = 0, ss = 0, se = 63, ah = 0, al = 0;
+  int eobrun = 0;
+  bool planes_ready = false;
   // bit reader
   uint32_t acc = 0;
   int nbits = 0;
@@ -167,17 +177,16 @@ void idct_store(const int* coef, uint8_t* out, int stride) {
     }
 }
 
-bool decode_block(Dec& d, Comp& cp, uint8_t* out, int stride) {
-  int coef[64];
-  std::memset(coef, 0, sizeof coef);
+// ---- one block of one scan --------------------------------------------------------------------------------------------
+// Sequential mode: the whole block.  Progressive mode: the DC coefficient (first pass / one refinement bit) or the band
+// ss..se of AC coefficients (first pass with end-of-band runs / refinement with correction bits), T.81 annex G.
+bool block_sequential(Dec& d, Comp& cp, int16_t* c) {
   const Huff& hd = d.dc[cp.td];
   const Huff& ha = d.ac[cp.ta];
-  const uint16_t* q = d.qt[cp.tq];
   int t = decode_sym(d, hd);
   if (t < 0 || t > 11) return fail(d, "jpeg: bad DC code");
-  const int diff = t ? extend(get_bits(d, t), t) : 0;
-  cp.pred += diff;
-  coef[0] = cp.pred * q[0];
+  cp.pred += t ? extend(get_bits(d, t), t) : 0;
+  c[0] = (int16_t)cp.pred;
   for (int k = 1; k < 64;) {
     const int rs = decode_sym(d, ha);
     if (rs < 0) return fail(d, "jpeg: bad AC code");
@@ -189,11 +198,91 @@ bool decode_block(Dec& d, Comp& cp, uint8_t* out, int stride) {
     }
     k += r;
     if (k > 63) return fail(d, "jpeg: coefficient index out of range");
-    coef[kZigzag[k]] = extend(get_bits(d, s), s) * q[k];
+    c[kZigzag[k]] = (int16_t)extend(get_bits(d, s), s);
     ++k;
   }
-  idct_store(coef, out, stride);
   return true;
+}
+
+bool block_dc(Dec& d, Comp& cp, int16_t* c) {
+  if (d.ah == 0) {
+    int t = decode_sym(d, d.dc[cp.td]);
+    if (t < 0 || t > 11) return fail(d, "jpeg: bad DC code");
+    cp.pred += t ? extend(get_bits(d, t), t) : 0;
+    c[0] = (int16_t)(cp.pred * (1 << d.al));
+  } else if (get_bits(d, 1)) {
+    c[0] = (int16_t)(c[0] | (1 << d.al));
+  }
+  return true;
+}
+
+bool block_ac_first(Dec& d, Comp& cp, int16_t* c) {
+  if (d.eobrun > 0) { --d.eobrun; return true; }
+  const Huff& ha = d.ac[cp.ta];
+  for (int k = d.ss; k <= d.se; ++k) {
+    const int rs = decode_sym(d, ha);
+    if (rs < 0) return fail(d, "jpeg: bad AC code");
+    const int r = rs >> 4, s = rs & 15;
+    if (s) {
+      k += r;
+      if (k > d.se) return fail(d, "jpeg: coefficient index out of range");
+      c[kZigzag[k]] = (int16_t)(extend(get_bits(d, s), s) * (1 << d.al));
+    } else if (r == 15) {
+      k += 15;
+    } else {
+      d.eobrun = (1 << r) - 1 + (r ? get_bits(d, r) : 0);      // this block ends the band, and so do the next eobrun blocks
+      break;
+    }
+  }
+  return true;
+}
+
+bool block_ac_refine(Dec& d, Comp& cp, int16_t* c) {
+  const int p1 = 1 << d.al, m1 = -(1 << d.al);
+  const Huff& ha = d.ac[cp.ta];
+  auto correct = [&](int16_t& v) {         // one more bit of precision for a coefficient that is already non-zero
+    if (get_bits(d, 1) && (v & p1) == 0) v = (int16_t)(v + (v >= 0 ? p1 : m1));
+  };
+  int k = d.ss;
+  if (d.eobrun == 0) {
+    for (; k <= d.se; ++k) {
+      const int rs = decode_sym(d, ha);
+      if (rs < 0) return fail(d, "jpeg: bad AC code");
+      int r = rs >> 4, s = rs & 15;
+      if (s) {
+        if (s != 1) return fail(d, "jpeg: bad refinement code");
+        s = get_bits(d, 1) ? p1 : m1;
+      } else if (r != 15) {
+        d.eobrun = (1 << r) + (r ? get_bits(d, r) : 0);
+        break;
+      }
+      // pass over r coefficients that are still zero; the non-zero ones on the way take a correction bit each
+      do {
+        int16_t& v = c[kZigzag[k]];
+        if (v != 0) correct(v);
+        else if (--r < 0) break;
+        ++k;
+      } while (k <= d.se);
+      if (s) {
+        if (k > d.se) return fail(d, "jpeg: coefficient index out of range");
+        c[kZigzag[k]] = (int16_t)s;
+      }
+    }
+  }
+  if (d.eobrun > 0) {
+    for (; k <= d.se; ++k) {
+      int16_t& v = c[kZigzag[k]];
+      if (v != 0) correct(v);
+    }
+    --d.eobrun;
+  }
+  return true;
+}
+
+bool decode_one_block(Dec& d, Comp& cp, int16_t* c) {
+  if (!d.progressive) return block_sequential(d, cp, c);
+  if (d.ss == 0) return block_dc(d, cp, c);
+  return d.ah == 0 ? block_ac_first(d, cp, c) : block_ac_refine(d, cp, c);
 }
 
 bool parse_headers(Dec& d, bool stop_at_frame) {
@@ -233,7 +322,21 @@ bool parse_headers(Dec& d, bool stop_at_frame) {
       }
       d.have_frame = true;
       if (stop_at_frame) return true;
-      if (d.progressive) return fail(d, "jpeg: progressive files are not supported (send baseline JPEG or PNG)");
+      {
+        const int mcu_w = 8 * d.hmax, mcu_h = 8 * d.vmax;
+        const int mx = (d.W + mcu_w - 1) / mcu_w, my = (d.H + mcu_h - 1) / mcu_h;
+        if (d.ncomp == 1) { d.comp[0].h = d.comp[0].v = 1; d.hmax = d.vmax = 1; }
+        for (int i = 0; i < d.ncomp; ++i) {
+          Comp& c = d.comp[i];
+          c.bw = d.ncomp == 1 ? (d.W + 7) / 8 : mx * c.h;
+          c.bh = d.ncomp == 1 ? (d.H + 7) / 8 : my * c.v;
+          // a scan of this component alone covers the component's own size, not the padded one
+          c.nbw = (((long)d.W * c.h + d.hmax - 1) / d.hmax + 7) / 8;
+          c.nbh = (((long)d.H * c.v + d.vmax - 1) / d.vmax + 7) / 8;
+          if ((long long)c.bw * c.bh > (1ll << 22)) return fail(d, "jpeg: image too large");
+          c.coef.assign((size_t)c.bw * c.bh * 64, 0);
+        }
+      }
     } else if (m == 0xC3 || (m >= 0xC5 && m <= 0xCF && m != 0xC4 && m != 0xC8 && m != 0xCC)) {
       return fail(d, "jpeg: lossless, hierarchical and arithmetic-coded files are not supported");
     } else if (m == 0xC4) {
@@ -265,7 +368,12 @@ bool parse_headers(Dec& d, bool stop_at_frame) {
     } else if (m == 0xDA) {
       if (!d.have_frame) return fail(d, "jpeg: scan before frame header");
       const int ns = s[0];
-      if (ns != d.ncomp || se - s < 1 + 2 * ns + 3) return fail(d, "jpeg: only one interleaved scan is supported");
+      if (ns < 1 || ns > d.ncomp || se - s < 1 + 2 * ns + 3) return fail(d, "jpeg: bad scan header");
+      d.scan_n = ns;
+      d.ss = s[1 + 2 * ns]; d.se = s[2 + 2 * ns]; d.ah = s[3 + 2 * ns] >> 4; d.al = s[3 + 2 * ns] & 15;
+      if (!d.progressive) { d.ss = 0; d.se = 63; d.ah = d.al = 0; }
+      else if (d.ss > d.se || d.se > 63 || (d.ss == 0 && d.se != 0) || (d.ss > 0 && ns != 1) || d.al > 13)
+        return fail(d, "jpeg: bad progressive scan parameters");
       for (int i = 0; i < ns; ++i) {
         const int cid = s[1 + 2 * i];
         Comp* c = nullptr;
@@ -274,8 +382,10 @@ bool parse_headers(Dec& d, bool stop_at_frame) {
         if (!c) return fail(d, "jpeg: scan names an unknown component");
         c->td = s[2 + 2 * i] >> 4;
         c->ta = s[2 + 2 * i] & 15;
-        if (c->td > 3 || c->ta > 3 || !d.dc[c->td].present || !d.ac[c->ta].present || !d.qt_ok[c->tq])
+        const bool need_dc = d.ss == 0 && d.ah == 0, need_ac = d.se > 0;
+        if (c->td > 3 || c->ta > 3 || (need_dc && !d.dc[c->td].present) || (need_ac && !d.ac[c->ta].present))
           return fail(d, "jpeg: scan uses a table that was not defined");
+        d.scan_comp[i] = c;
       }
       d.p += len;
       return true;                          // entropy-coded data follows
@@ -285,27 +395,19 @@ bool parse_headers(Dec& d, bool stop_at_frame) {
   return fail(d, "jpeg: no scan found");
 }
 
+// Entropy-coded data of the scan whose header parse_headers() just read.
 bool decode_scan(Dec& d) {
+  for (int i = 0; i < d.scan_n; ++i) d.scan_comp[i]->pred = 0;
+  d.eobrun = 0;
+  d.acc = 0; d.nbits = 0; d.hit_marker = false;
+  const bool single = d.scan_n == 1;
+  Comp& c0 = *d.scan_comp[0];
   const int mcu_w = 8 * d.hmax, mcu_h = 8 * d.vmax;
-  const int mx = (d.W + mcu_w - 1) / mcu_w, my = (d.H + mcu_h - 1) / mcu_h;
-  for (int i = 0; i < d.ncomp; ++i) {
-    Comp& c = d.comp[i];
-    if (d.ncomp == 1) { c.h = c.v = 1; }
-    c.bw = mx * c.h;
-    c.bh = my * c.v;
-    c.plane.assign((size_t)c.bw * 8 * c.bh * 8, 0);
-    c.pred = 0;
-  }
-  if (d.ncomp == 1) { d.hmax = d.vmax = 1; }
-  const int mx1 = d.ncomp == 1 ? (d.W + 7) / 8 : mx, my1 = d.ncomp == 1 ? (d.H + 7) / 8 : my;
-  if (d.ncomp == 1) {
-    Comp& c = d.comp[0];
-    c.bw = mx1; c.bh = my1;
-    c.plane.assign((size_t)c.bw * 8 * c.bh * 8, 0);
-  }
+  // one component: its blocks in raster order; several: MCUs of h x v blocks per component
+  const int nx = single ? c0.nbw : (d.W + mcu_w - 1) / mcu_w, ny = single ? c0.nbh : (d.H + mcu_h - 1) / mcu_h;
   int countdown = d.restart, next_rst = 0;
-  for (int y = 0; y < my1; ++y)
-    for (int x = 0; x < mx1; ++x) {
+  for (int y = 0; y < ny; ++y)
+    for (int x = 0; x < nx; ++x) {
       if (d.restart && countdown == 0) {
         // byte-align, expect RSTn
         d.acc = 0; d.nbits = 0;
@@ -320,20 +422,116 @@ bool decode_scan(Dec& d) {
         d.hit_marker = false;
         next_rst = (next_rst + 1) & 7;
         countdown = d.restart;
-        for (int i = 0; i < d.ncomp; ++i) d.comp[i].pred = 0;
+        for (int i = 0; i < d.scan_n; ++i) d.scan_comp[i]->pred = 0;
+        d.eobrun = 0;
       }
-      for (int i = 0; i < d.ncomp; ++i) {
-        Comp& c = d.comp[i];
-        const int stride = c.bw * 8;
-        for (int by = 0; by < c.v; ++by)
-          for (int bx = 0; bx < c.h; ++bx) {
-            uint8_t* out = c.plane.data() + ((size_t)(y * c.v + by) * 8) * stride + (size_t)(x * c.h + bx) * 8;
-            if (!decode_block(d, c, out, stride)) return false;
-          }
+      if (single) {
+        if (!decode_one_block(d, c0, c0.coef.data() + ((size_t)y * c0.bw + x) * 64)) return false;
+      } else {
+        for (int i = 0; i < d.scan_n; ++i) {
+          Comp& c = *d.scan_comp[i];
+          for (int by = 0; by < c.v; ++by)
+            for (int bx = 0; bx < c.h; ++bx)
+              if (!decode_one_block(d, c, c.coef.data() + ((size_t)(y * c.v + by) * c.bw + (size_t)(x * c.h + bx)) * 64)) return false;
+        }
       }
       if (d.restart) --countdown;
     }
   return true;
+}
+
+// After a scan: the markers and segments up to the next scan header.  Returns false at the end of the image.
+bool next_scan(Dec& d) {
+  // the bit reader stopped in front of a marker (or at the end of the data)
+  while (d.p + 1 < d.end && !(d.p[0] == 0xFF && d.p[1] != 0x00 && d.p[1] != 0xFF && !(d.p[1] >= 0xD0 && d.p[1] <= 0xD7))) ++d.p;
+  while (d.p + 4 <= d.end) {
+    if (d.p[0] != 0xFF) { ++d.p; continue; }
+    const int m = d.p[1];
+    if (m == 0xFF) { ++d.p; continue; }
+    d.p += 2;
+    if (m == 0xD9) return false;
+    if (m == 0x00 || (m >= 0xD0 && m <= 0xD7)) continue;
+    const int len = u16(d.p);
+    if (len < 2 || d.p + len > d.end) return false;         // truncated tail: keep what the earlier scans gave
+    const uint8_t* s = d.p + 2;
+    const uint8_t* se = d.p + len;
+    if (m == 0xC4) {
+      while (s < se) {
+        if (se - s < 17) return fail(d, "jpeg: bad Huffman segment");
+        const int tc = s[0] >> 4, th = s[0] & 15;
+        if (tc > 1 || th > 3) return fail(d, "jpeg: bad Huffman table id");
+        int n = 0;
+        for (int i = 0; i < 16; ++i) n += s[1 + i];
+        if (se - s < 17 + n) return fail(d, "jpeg: bad Huffman segment");
+        if (!build_huff(d, tc ? d.ac[th] : d.dc[th], s + 1, s + 17, n)) return false;
+        s += 17 + n;
+      }
+    } else if (m == 0xDB) {
+      while (s < se) {
+        const int pq = s[0] >> 4, tq = s[0] & 15;
+        const int need = 1 + (pq ? 128 : 64);
+        if (tq > 3 || se - s < need) return fail(d, "jpeg: bad quantisation segment");
+        for (int i = 0; i < 64; ++i) d.qt[tq][i] = pq ? (uint16_t)u16(s + 1 + 2 * i) : s[1 + i];
+        d.qt_ok[tq] = true;
+        s += need;
+      }
+    } else if (m == 0xDD) {
+      if (se - s >= 2) d.restart = u16(s);
+    } else if (m == 0xDA) {
+      const int ns = s[0];
+      if (ns < 1 || ns > d.ncomp || se - s < 1 + 2 * ns + 3) return fail(d, "jpeg: bad scan header");
+      d.scan_n = ns;
+      d.ss = s[1 + 2 * ns]; d.se = s[2 + 2 * ns]; d.ah = s[3 + 2 * ns] >> 4; d.al = s[3 + 2 * ns] & 15;
+      if (!d.progressive) { d.ss = 0; d.se = 63; d.ah = d.al = 0; }
+      else if (d.ss > d.se || d.se > 63 || (d.ss == 0 && d.se != 0) || (d.ss > 0 && ns != 1) || d.al > 13)
+        return fail(d, "jpeg: bad progressive scan parameters");
+      for (int i = 0; i < ns; ++i) {
+        Comp* c = nullptr;
+        for (int j = 0; j < d.ncomp; ++j)
+          if (d.comp[j].id == s[1 + 2 * i]) c = &d.comp[j];
+        if (!c) return fail(d, "jpeg: scan names an unknown component");
+        c->td = s[2 + 2 * i] >> 4;
+        c->ta = s[2 + 2 * i] & 15;
+        const bool need_dc = d.ss == 0 && d.ah == 0, need_ac = d.se > 0;
+        if (c->td > 3 || c->ta > 3 || (need_dc && !d.dc[c->td].present) || (need_ac && !d.ac[c->ta].present))
+          return fail(d, "jpeg: scan uses a table that was not defined");
+        d.scan_comp[i] = c;
+      }
+      d.p += len;
+      return true;
+    }
+    d.p += len;
+  }
+  return false;
+}
+
+// Dequantise and transform every block once all scans are in.
+bool finish_planes(Dec& d) {
+  for (int i = 0; i < d.ncomp; ++i) {
+    Comp& c = d.comp[i];
+    if (!d.qt_ok[c.tq]) return fail(d, "jpeg: a component uses a quantisation table that was not defined");
+    int qnat[64];
+    for (int k = 0; k < 64; ++k) qnat[kZigzag[k]] = d.qt[c.tq][k];
+    c.plane.assign((size_t)c.bw * 8 * c.bh * 8, 0);
+    const int stride = c.bw * 8;
+    int blk[64];
+    for (int by = 0; by < c.bh; ++by)
+      for (int bx = 0; bx < c.bw; ++bx) {
+        const int16_t* src = c.coef.data() + ((size_t)by * c.bw + bx) * 64;
+        for (int k = 0; k < 64; ++k) blk[k] = (int)src[k] * qnat[k];
+        idct_store(blk, c.plane.data() + (size_t)by * 8 * stride + (size_t)bx * 8, stride);
+      }
+  }
+  return true;
+}
+
+// All scans of the image.
+bool decode_image(Dec& d) {
+  do {
+    if (!decode_scan(d)) return false;
+  } while (next_scan(d));
+  if (!d.err.empty()) return false;
+  return finish_planes(d);
 }
 
 // Sample of a subsampled plane at full-resolution position (x, y): triangle filter (3/4, 1/4) along each halved axis,
@@ -408,7 +606,7 @@ B2H_API int b2h_jpeg_decode(const uint8_t* data, long n, uint8_t* rgb) {
   Dec d;
   d.p = data;
   d.end = data + n;
-  if (!parse_headers(d, false) || !decode_scan(d)) { g_jpeg_err = d.err.empty() ? "jpeg: decode failed" : d.err; return 1; }
+  if (!parse_headers(d, false) || !decode_image(d)) { g_jpeg_err = d.err.empty() ? "jpeg: decode failed" : d.err; return 1; }
   to_rgb(d, rgb);
   return 0;
 }
