@@ -43,6 +43,7 @@ def _h():
             getattr(h, nm).argtypes, getattr(h, nm).restype = [vp, C.c_long, vp], i
         h.b2h_image_error.argtypes, h.b2h_image_error.restype = [], C.c_char_p
         h.b2h_webp_error.argtypes, h.b2h_webp_error.restype = [], C.c_char_p
+        h.b2h_png_unfilter.argtypes, h.b2h_png_unfilter.restype = [vp, C.c_long, i, i, i, i, i, vp, i, vp], i
         _sig = True
     return h
 
@@ -93,7 +94,7 @@ def mrope_positions(ids: Sequence[int], pad_id: int, grids: Sequence[Tuple[int, 
 
 # ---------------------------------------------------------------------------------------------------------------------
 def decode_image(data: bytes) -> np.ndarray:
-    """uint8 [h, w, 3] from a binary PPM, a non-interlaced 8-bit PNG (RGB, RGBA, grey, grey+alpha, palette; alpha is
+    """uint8 [h, w, 3] from a binary PPM, a PNG (every colour type and bit depth, interlaced or not; alpha is
     dropped) or a JPEG (``csrc/server/jpeg.cpp``: sequential or progressive, grey or three components, 1x / 2x sampling
     factors, restart intervals; arithmetic-coded files are refused with a message), an uncompressed BMP or the first
     frame of a GIF (``csrc/server/image_misc.cpp``), or a lossless WebP (``csrc/server/webp.cpp``)."""
@@ -149,56 +150,36 @@ def _decode_simple(data: bytes, kind: str) -> np.ndarray:
 
 
 def _decode_png(data: bytes) -> np.ndarray:
-    p, idat, pal = 8, b"", None
+    """PNG: the chunks are read and the IDAT stream inflated here (zlib), the scanlines are reconstructed by
+    ``b2h_png_unfilter`` (``csrc/server/image_misc.cpp``): every filter type, bit depths 1 to 16, every colour type,
+    Adam7 interlacing; alpha is dropped."""
+    p, idat, pal = 8, [], b""
     w = h = depth = ctype = interlace = 0
-    while p < len(data):
+    while p + 8 <= len(data):
         n, kind = struct.unpack(">I4s", data[p:p + 8])
         body = data[p + 8:p + 8 + n]
         if kind == b"IHDR":
-            w, h, depth, ctype, _, _, interlace = struct.unpack(">IIBBBBB", body)
+            w, h, depth, ctype, _, _, interlace = struct.unpack(">IIBBBBB", body[:13])
         elif kind == b"PLTE":
-            pal = np.frombuffer(body, dtype=np.uint8).reshape(-1, 3)
+            pal = bytes(body[:len(body) // 3 * 3])
         elif kind == b"IDAT":
-            idat += body
+            idat.append(body)
         elif kind == b"IEND":
             break
         p += 12 + n
-    if depth != 8 or interlace:
-        raise ValueError("only 8-bit non-interlaced PNG is supported")
-    ch = {0: 1, 2: 3, 3: 1, 4: 2, 6: 4}[ctype]
-    raw = zlib.decompress(idat)
-    stride = w * ch
-    out = np.zeros((h, stride), dtype=np.uint8)
-    prev = np.zeros(stride, dtype=np.int32)
-    for y in range(h):
-        f = raw[y * (stride + 1)]
-        line = np.frombuffer(raw, dtype=np.uint8, count=stride, offset=y * (stride + 1) + 1).astype(np.int32)
-        cur = np.zeros(stride, dtype=np.int32)
-        if f == 0:
-            cur = line
-        elif f == 2:
-            cur = (line + prev) & 255
-        else:
-            for x in range(stride):
-                a = cur[x - ch] if x >= ch else 0
-                b = prev[x]
-                c = prev[x - ch] if x >= ch else 0
-                if f == 1:
-                    pr = a
-                elif f == 3:
-                    pr = (a + b) >> 1
-                else:
-                    pa, pb, pc = abs(b - c), abs(a - c), abs(a + b - 2 * c)
-                    pr = a if pa <= pb and pa <= pc else (b if pb <= pc else c)
-                cur[x] = (line[x] + pr) & 255
-        out[y] = cur
-        prev = cur
-    img = out.reshape(h, w, ch)
-    if ctype == 3:
-        return pal[img[:, :, 0]]
-    if ch == 1 or ch == 2:
-        return np.repeat(img[:, :, :1], 3, axis=2)
-    return img[:, :, :3].copy()
+    if w <= 0 or h <= 0 or ctype not in (0, 2, 3, 4, 6):
+        raise ValueError("bad PNG header")
+    try:
+        raw = zlib.decompress(b"".join(idat))
+    except zlib.error as e:
+        raise ValueError(f"png: {e}")
+    lib = _h()
+    out = np.empty((h, w, 3), dtype=np.uint8)
+    buf = (C.c_ubyte * len(raw)).from_buffer_copy(raw)
+    pbuf = (C.c_ubyte * max(len(pal), 1)).from_buffer_copy(pal or b"\0")
+    if lib.b2h_png_unfilter(buf, len(raw), w, h, depth, ctype, interlace, pbuf, len(pal) // 3, out.ctypes.data_as(C.c_void_p)) != 0:
+        raise ValueError(lib.b2h_image_error().decode() or "bad PNG")
+    return out
 
 
 def load_url(url: str) -> bytes:

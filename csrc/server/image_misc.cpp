@@ -1,10 +1,13 @@
-// BMP and GIF (first frame) readers for image inputs of chat requests, next to the PNG / PPM / JPEG readers.
+// BMP and GIF (first frame) readers and the PNG scanline reconstruction for image inputs of chat requests, next to the
+// PPM / JPEG / WebP readers.
 //
 // The reference accepts these formats through its image crate / nvJPEG path (crates/agens-server/src/vision.rs:126-135);
 // here they are decoded on the host.  BMP: uncompressed 24 / 32-bit and 8-bit palettised, bottom-up or top-down.
 // GIF: the first image of the file (87a / 89a), global or local colour table, interlaced or not, LZW decoded;
 // transparency is ignored (the colour of the index is used), animation frames after the first are not read.
+#include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -209,4 +212,96 @@ B2H_API int b2h_gif_decode(const uint8_t* d, long n, uint8_t* rgb) {
     return 0;                                             // first frame only
   }
   return fail("gif: no image in the file");
+}
+
+// ---- PNG: scanline reconstruction ----------------------------------------------------------------------------------------
+// The inflated IDAT stream (zlib runs in the caller) -> RGB: filter types 0..4, bit depths 1 / 2 / 4 / 8 / 16, colour types
+// grey / RGB / palette / grey+alpha / RGBA (alpha dropped, 16-bit samples keep their high byte), Adam7 interlacing.
+// pal: the PLTE entries (3 bytes each).  Returns 0 on success.
+namespace {
+
+inline int paeth(int a, int b, int c) {
+  const int pa = std::abs(b - c), pb = std::abs(a - c), pc = std::abs(a + b - 2 * c);
+  return pa <= pb && pa <= pc ? a : (pb <= pc ? b : c);
+}
+
+// One sub-image (the whole picture, or one Adam7 pass): pw x ph pixels whose scanlines start at raw; writes pixel (i, j) of
+// it to rgb at (x0 + i * dx, y0 + j * dy).  Returns the bytes consumed, or -1.
+long png_pass(const uint8_t* raw, long n, int pw, int ph, int depth, int ctype, const uint8_t* pal, int npal, uint8_t* rgb, int W,
+              int x0, int y0, int dx, int dy) {
+  static const int kCh[7] = {1, 0, 3, 1, 2, 0, 4};
+  const int ch = kCh[ctype];
+  const int bpp = std::max(1, ch * depth / 8);
+  const long line = ((long)pw * ch * depth + 7) / 8;
+  if (pw == 0 || ph == 0) return 0;
+  if ((line + 1) * ph > n) return -1;
+  std::vector<uint8_t> prev((size_t)line, 0), cur((size_t)line);
+  for (int j = 0; j < ph; ++j) {
+    const uint8_t* src = raw + (size_t)j * (line + 1);
+    const int f = src[0];
+    ++src;
+    for (long i = 0; i < line; ++i) {
+      const int a = i >= bpp ? cur[(size_t)(i - bpp)] : 0, b = prev[(size_t)i], c = i >= bpp ? prev[(size_t)(i - bpp)] : 0;
+      int pr;
+      switch (f) {
+        case 0: pr = 0; break;
+        case 1: pr = a; break;
+        case 2: pr = b; break;
+        case 3: pr = (a + b) >> 1; break;
+        case 4: pr = paeth(a, b, c); break;
+        default: return -1;
+      }
+      cur[(size_t)i] = (uint8_t)(src[i] + pr);
+    }
+    const int maxv = (1 << depth) - 1;
+    for (int i = 0; i < pw; ++i) {
+      auto sample = [&](int k) -> int {       // k-th sample of the pixel, as 8 bits (raw index for palette images)
+        const long s = (long)i * ch + k;
+        if (depth == 8) return cur[(size_t)s];
+        if (depth == 16) return cur[(size_t)(2 * s)];
+        const long bit = s * depth;
+        const int v = (cur[(size_t)(bit >> 3)] >> (8 - depth - (bit & 7))) & maxv;
+        return ctype == 3 ? v : v * 255 / maxv;
+      };
+      uint8_t* o = rgb + ((size_t)(y0 + j * dy) * W + (size_t)(x0 + i * dx)) * 3;
+      if (ctype == 3) {
+        const int idx = sample(0);
+        if (idx < npal) { o[0] = pal[3 * idx]; o[1] = pal[3 * idx + 1]; o[2] = pal[3 * idx + 2]; }
+        else { o[0] = o[1] = o[2] = 0; }
+      } else if (ch <= 2) {
+        o[0] = o[1] = o[2] = (uint8_t)sample(0);
+      } else {
+        o[0] = (uint8_t)sample(0); o[1] = (uint8_t)sample(1); o[2] = (uint8_t)sample(2);
+      }
+    }
+    prev.swap(cur);
+  }
+  return (line + 1) * ph;
+}
+
+}  // namespace
+
+B2H_API int b2h_png_unfilter(const uint8_t* raw, long n, int w, int h, int depth, int ctype, int interlace, const uint8_t* pal,
+                             int npal, uint8_t* rgb) {
+  if (w <= 0 || h <= 0 || (long long)w * h > (1ll << 28)) return fail("png: bad size");
+  const bool depth_ok = (ctype == 0 && (depth == 1 || depth == 2 || depth == 4 || depth == 8 || depth == 16)) ||
+                        (ctype == 3 && (depth == 1 || depth == 2 || depth == 4 || depth == 8)) ||
+                        ((ctype == 2 || ctype == 4 || ctype == 6) && (depth == 8 || depth == 16));
+  if (!depth_ok) return fail("png: bad colour type / bit depth");
+  if (ctype == 3 && (!pal || npal <= 0)) return fail("png: palette image without a palette");
+  if (interlace == 0) {
+    if (png_pass(raw, n, w, h, depth, ctype, pal, npal, rgb, w, 0, 0, 1, 1) < 0) return fail("png: truncated or damaged image data");
+    return 0;
+  }
+  if (interlace != 1) return fail("png: unknown interlace method");
+  static const int kX0[7] = {0, 4, 0, 2, 0, 1, 0}, kY0[7] = {0, 0, 4, 0, 2, 0, 1}, kDx[7] = {8, 8, 4, 4, 2, 2, 1}, kDy[7] = {8, 8, 8, 4, 4, 2, 2};
+  long off = 0;
+  for (int p = 0; p < 7; ++p) {
+    const int pw = (w - kX0[p] + kDx[p] - 1) / kDx[p], ph = (h - kY0[p] + kDy[p] - 1) / kDy[p];
+    if (pw <= 0 || ph <= 0) continue;
+    const long used = png_pass(raw + off, n - off, pw, ph, depth, ctype, pal, npal, rgb, w, kX0[p], kY0[p], kDx[p], kDy[p]);
+    if (used < 0) return fail("png: truncated or damaged image data");
+    off += used;
+  }
+  return 0;
 }

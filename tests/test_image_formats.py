@@ -124,3 +124,112 @@ def test_webp_alpha_container_and_refusals():
     broken = bytearray(data); broken[12 + 8] = 0x00            # the lossless signature byte
     with pytest.raises(ValueError):
         V.decode_image(bytes(broken))
+
+
+# ---- PNG (chunks and zlib in Python, scanlines in csrc/server/image_misc.cpp) -----------------------------------------------
+def _png(arr, mode, **kw):
+    buf = io.BytesIO()
+    PIL.fromarray(arr, mode).save(buf, "PNG", **kw)
+    return buf.getvalue()
+
+
+def test_png_colour_types_and_bit_depths_match_pillow():
+    rng = np.random.default_rng(2)
+    rgb = _img(53, 71, seed=5)
+    rgba = np.concatenate([rgb, rng.integers(0, 256, (53, 71, 1), dtype=np.uint8)], -1)
+    grey = rgb[..., 0].copy()
+    la = np.stack([grey, rgba[..., 3]], -1)
+    for name, data in {"rgb": _png(rgb, "RGB"), "rgba": _png(rgba, "RGBA"), "grey": _png(grey, "L"), "grey+alpha": _png(la, "LA"),
+                       "rgb optimised": _png(rgb, "RGB", optimize=True)}.items():
+        assert np.array_equal(V.decode_image(data), _pil(data)), name
+    # palette images at 8, 4, 2 and 1 bits per pixel
+    for colours, bits in ((200, 8), (16, 4), (4, 2), (2, 1)):
+        pal = rng.integers(0, 256, (colours, 3), dtype=np.uint8)
+        idx = rng.integers(0, colours, (37, 45), dtype=np.uint8)
+        im = PIL.fromarray(idx, "P")
+        im.putpalette(pal.reshape(-1).tolist())
+        buf = io.BytesIO()
+        im.save(buf, "PNG", bits=bits)
+        assert np.array_equal(V.decode_image(buf.getvalue()), pal[idx]), bits
+    # bilevel and 16-bit grey (the high byte is kept)
+    one = rng.integers(0, 2, (19, 27)).astype(np.uint8) * 255
+    buf = io.BytesIO()
+    PIL.fromarray(one, "L").convert("1", dither=0).save(buf, "PNG")
+    assert np.array_equal(V.decode_image(buf.getvalue())[..., 0], one) and np.array_equal(V.decode_image(buf.getvalue()), _pil(buf.getvalue()))
+    g16 = rng.integers(0, 65536, (21, 33)).astype(np.uint16)
+    buf = io.BytesIO()
+    PIL.fromarray(g16).save(buf, "PNG")
+    assert np.array_equal(V.decode_image(buf.getvalue())[..., 1], (g16 >> 8).astype(np.uint8))
+
+
+def test_png_adam7_interlaced_and_every_filter():
+    """Interlaced files (Pillow does not write them): built here pass by pass, each scanline with one of the five filter
+    types, for RGB, RGBA, 16-bit RGB and a 2-bit palette."""
+    import struct
+    import zlib
+    rng = np.random.default_rng(3)
+
+    def chunk(kind, body):
+        return struct.pack(">I", len(body)) + kind + body + struct.pack(">I", zlib.crc32(kind + body))
+
+    def filtered(rows, bpp):            # rows: list of bytes objects; cycles through filter types 0..4
+        out, prev = b"", bytes(len(rows[0])) if rows else b""
+        for j, row in enumerate(rows):
+            f = j % 5
+            enc = bytearray(len(row))
+            for i, v in enumerate(row):
+                a = row[i - bpp] if i >= bpp else 0
+                b = prev[i]
+                c = prev[i - bpp] if i >= bpp else 0
+                if f == 0: pr = 0
+                elif f == 1: pr = a
+                elif f == 2: pr = b
+                elif f == 3: pr = (a + b) >> 1
+                else:
+                    pa, pb, pc = abs(b - c), abs(a - c), abs(a + b - 2 * c)
+                    pr = a if pa <= pb and pa <= pc else (b if pb <= pc else c)
+                enc[i] = (v - pr) & 255
+            out += bytes([f]) + bytes(enc)
+            prev = row
+        return out
+
+    def pack_rows(px, depth):           # px: [h, w, ch] integer samples -> list of scanline bytes
+        rows = []
+        for r in px:
+            flat = r.reshape(-1)
+            if depth == 8:
+                rows.append(bytes(flat.astype(np.uint8)))
+            elif depth == 16:
+                rows.append(flat.astype(">u2").tobytes())
+            else:
+                bits = "".join(format(int(v), f"0{depth}b") for v in flat)
+                bits += "0" * (-len(bits) % 8)
+                rows.append(bytes(int(bits[i:i + 8], 2) for i in range(0, len(bits), 8)))
+        return rows
+
+    passes = [(0, 0, 8, 8), (4, 0, 8, 8), (0, 4, 4, 8), (2, 0, 4, 4), (0, 2, 2, 4), (1, 0, 2, 2), (0, 1, 1, 2)]
+    for w, h in ((23, 17), (3, 2), (8, 8), (1, 1)):
+        for ctype, depth, ch in ((2, 8, 3), (6, 8, 4), (2, 16, 3), (3, 2, 1)):
+            hi = 4 if ctype == 3 else (65536 if depth == 16 else 256)
+            px = rng.integers(0, hi, (h, w, ch))
+            raw = b""
+            for x0, y0, dx, dy in passes:
+                sub = px[y0::dy, x0::dx]
+                if sub.size:
+                    raw += filtered(pack_rows(sub, depth), max(1, ch * depth // 8))
+            pal = rng.integers(0, 256, (4, 3), dtype=np.uint8)
+            data = b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", w, h, depth, ctype, 0, 0, 1))
+            if ctype == 3:
+                data += chunk(b"PLTE", pal.tobytes())
+            data += chunk(b"IDAT", zlib.compress(raw)) + chunk(b"IEND", b"")
+            got = V.decode_image(data)
+            if ctype == 3:
+                want = pal[px[..., 0]]
+            elif depth == 16:
+                want = (px[..., :3] >> 8).astype(np.uint8)
+            else:
+                want = px[..., :3].astype(np.uint8)
+            assert np.array_equal(got, want), (w, h, ctype, depth)
+            assert np.array_equal(got, _pil(data)) or depth == 16          # Pillow reads it the same way (16-bit RGB aside)
+    with pytest.raises(ValueError):
+        V.decode_image(b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", 4, 4, 8, 2, 0, 0, 0)) + chunk(b"IDAT", zlib.compress(b"\0" * 10)) + chunk(b"IEND", b""))
