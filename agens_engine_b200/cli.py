@@ -39,6 +39,7 @@ class EngineConfig:
     spec_copy: int = 0
     spec_drafter: Optional[str] = None
     mtp: Optional[str] = None
+    mtp_vocab: Optional[str] = None       # shortlist of the MTP head's lm_head: a count (first N ids) or a file of uint32 ids
     draft_depth: int = 4
     host: str = "127.0.0.1"
     port: int = 30000
@@ -534,6 +535,12 @@ def cmd_serve(ns):
             head = K.load_mtp(cfg.mtp, m, lm_head_dir=cfg.model_dir)
         else:
             head = MtpHead.random_init_for(m)
+        if cfg.mtp_vocab:                                 # the head's shortlist: the first N ids, or a file of little-endian uint32 ids
+            if os.path.isfile(cfg.mtp_vocab):
+                import numpy as np
+                head.use_shortlist(np.fromfile(cfg.mtp_vocab, dtype="<u4").astype(np.int64).tolist())
+            else:
+                head.use_shortlist(range(min(int(cfg.mtp_vocab), head.cfg.vocab_valid or head.cfg.vocab)))
         sources.append(MtpSource(head, depth=min(cfg.draft_depth, 2)))
     if cfg.spec_drafter:                                  # under --tp the drafter lives beside the leader, unsharded
         from .models.dense import DenseModel
@@ -641,7 +648,7 @@ def main(argv=None) -> int:
     p.add_argument("--min-agreement", type=float, default=0.75); p.set_defaults(fn=cmd_agent_replay)
     p = sub.add_parser("serve"); _engine_flags(p)
     p.add_argument("--host"); p.add_argument("--port", type=int); p.add_argument("--served-model-name")
-    p.add_argument("--spec-copy", type=int); p.add_argument("--spec-drafter"); p.add_argument("--mtp")
+    p.add_argument("--spec-copy", type=int); p.add_argument("--spec-drafter"); p.add_argument("--mtp"); p.add_argument("--mtp-vocab")
     p.add_argument("--max-tokens-default", type=int); p.add_argument("--think-guard"); p.add_argument("--tokenizer")
     p.add_argument("--vision", type=int)
     p.set_defaults(fn=cmd_serve)

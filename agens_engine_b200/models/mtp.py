@@ -43,6 +43,8 @@ class MtpHead(DenseModel):
         self.cat = torch.zeros(M_GEMV, 2 * cfg.d_model, dtype=torch.bfloat16, device=self.dev)
         self.hid_in = torch.zeros(M_GEMV, cfg.d_model, dtype=torch.bfloat16, device=self.dev)
         self._pair_hidden = None
+        self.shortlist = None          # int32 [rows of the shortlist lm_head]: token id of every row (use_shortlist)
+        self._short_n = 0
 
     @staticmethod
     def random_init_for(target: DenseModel, seed: int = 7, **kw) -> "MtpHead":
@@ -62,6 +64,33 @@ class MtpHead(DenseModel):
         if m.own_lm_head:
             m.lm_head = L.WqLinear.random(m.lm_rows, cfg.d_model, cfg.lm_head_bits, cfg.group, dev, seed=seed * 7919 + 200)
         return m.finalize()
+
+    def use_shortlist(self, ids):
+        """Restricts the head's lm_head to the token ids of ``ids`` (the reference's draft shortlist, by default the
+        32768 most frequent ids of its own generations: crates/agens-cli/src/spec.rs:372-386): a chain step then reads
+        that many rows of the head instead of the whole vocabulary.  The rows are taken from the current lm_head,
+        quantised again in its format; a drafted token is always one of ``ids``."""
+        from ..utils import quant
+        full = self.lm_head
+        idx = torch.as_tensor(list(ids), dtype=torch.long, device=self.dev)
+        assert idx.numel() > 0 and int(idx.max()) < (self.cfg.vocab_valid or self.cfg.vocab) and int(idx.min()) >= 0
+        rows = full.dequant().index_select(0, idx).float().cpu()
+        n = int(idx.numel())
+        pad = (-n) % 32
+        if pad:
+            rows = torch.cat([rows, torch.zeros(pad, rows.shape[1])])
+        self.lm_head = L.WqLinear.from_quant(quant.quantize(rows, full.bits, full.group), self.dev)
+        self.lm_rows = n + pad
+        self._short_n = n
+        self.shortlist = torch.cat([idx, torch.zeros(pad, dtype=torch.long, device=self.dev)]).to(torch.int32)
+        return self.finalize()
+
+    def _lm_valid(self) -> int:
+        return self._short_n if self.shortlist is not None else super()._lm_valid()
+
+    def _combine_argmax(self, m: int, standalone: bool = False):
+        if self.shortlist is not None:                   # position in the shortlist -> token id
+            self.out_ids[:m].copy_(self.shortlist.index_select(0, self.out_ids[:m].long()))
 
     def finalize(self):
         super().finalize()

@@ -279,3 +279,41 @@ def test_mtp_head_from_checkpoint(tiny, tmp_path):
     dec = SpecDecoder(m, [MtpSource(head, depth=2)], max_drafts=4)
     assert dec.generate(0, prompt, 20) == plain
     assert dec.stats.by_source.get("mtp", [0, 0])[0] > 0
+
+
+def test_mtp_shortlist_head(tiny):
+    """The MTP head with a shortlist lm_head (reference: the draft shortlist, crates/agens-cli/src/spec.rs:372-386):
+    it reads only the shortlist's rows, every draft is one of the shortlist's ids, the output stays exact."""
+    cfg, ow = tiny
+    torch.manual_seed(21)
+    prompt = torch.randint(0, cfg.vocab, (40,)).tolist()
+    plain = _plain(ow, prompt, 20)
+    m = DenseModel.from_oracle(ow, max_seqs=2, max_ctx=512)
+    head = MtpHead.random_init_for(m)
+    ids = list(range(3, cfg.vocab, 4))[:200]                       # 200 ids, not a multiple of 32
+    head.use_shortlist(ids)
+    assert head.lm_head.n == 224 and head._lm_valid() == 200 and head.lm_head is not m.lm_head
+    seen = []
+    src = MtpSource(head, depth=2)
+    many0 = src.propose_many
+
+    def spy(seqs, hist, max_n):
+        out = many0(seqs, hist, max_n)
+        seen.extend(t for d in out.values() for t in d)
+        return out
+    src.propose_many = spy
+    dec = SpecDecoder(m, [src], max_drafts=4)
+    assert dec.generate(0, prompt, 20) == plain
+    assert seen and set(seen) <= set(ids)
+    # the shortlist rows are the full head's rows: the winner among them is the full head's best shortlist id
+    full = MtpHead.random_init_for(m)
+    h = torch.randn(1, cfg.d_model, device=m.dev).to(torch.bfloat16)
+    for hd in (head, full):
+        hd.new_seq(0)
+    tok = int(prompt[5])
+    a = int(head.forward_mtp([tok], h, [0])[0])
+    full.forward_rows  # (same weights: random_init_for is seeded)
+    full.hid_in[:1].copy_(h)
+    _, logits = full.forward_rows([tok], [0], want_logits=True)
+    best = max(ids, key=lambda t: float(logits[0, t]))
+    assert a == best or abs(float(logits[0, a]) - float(logits[0, best])) < 0.05 * float(logits[0].abs().max())
