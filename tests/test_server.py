@@ -374,3 +374,32 @@ def test_tools_reach_the_template_in_normal_form(tok_path, tok_text):
     assert sv.handle("POST", "/v1/chat/completions", dict(body, tool_choice={"type": "function", "function": {"name": "second"}}))[0] == 200
     text = tk.decode(sv.mock_calls()[-1]["prompt"], skip_special=False)
     assert text.count("\n") == 1 and json.loads(text.split("\n")[0])["function"]["name"] == "second"
+
+
+def test_tokenizer_differential_on_a_trained_bpe():
+    """A byte-level BPE trained here with the `tokenizers` library on mixed-script text (the pre-tokeniser pattern of the
+    dense GQA checkpoints): the C++ tokenizer gives the same ids and the same decoded text on the corpus and on random
+    strings of awkward pieces (contractions in any case, digits of other scripts, emoji, marker tokens, runs of blanks)."""
+    import random
+    tk_lib = pytest.importorskip("tokenizers")
+    from tokenizers import Regex, decoders, models, pre_tokenizers, trainers
+    rnd = random.Random(0)
+    words = ["hello", "world", "the", "quick", "brown", "fox", "naïve", "café", "漢字", "かな", "한국어", "don't", "I'm", "we'll", "THEY'RE", "x=12*345;",
+             "foo_bar", "CamelCase", "1234567", "3.14159", "🙂", "👍🏽", "Ünïcödé", "ß", "Ελληνικά", "русский", "עברית", "العربية", "\t", "\n", "\r\n",
+             "  ", "   ", "!!!", "...", "<|im_start|>", "</s>", "a", "b", "ab", "abc"]
+    corpus = ["".join(rnd.choice(words) + rnd.choice(["", " ", " ", "  ", "\n", ", ", ". "]) for _ in range(rnd.randint(1, 12))) for _ in range(1500)]
+    tok = tk_lib.Tokenizer(models.BPE())
+    pat = "(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\\r\\n\\p{L}\\p{N}]?\\p{L}+|\\p{N}| ?[^\\s\\p{L}\\p{N}]+[\\r\\n]*|\\s*[\\r\\n]+|\\s+(?!\\S)|\\s+"
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pat), behavior="isolated", invert=False),
+                                                 pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    tok.train_from_iterator(corpus, trainers.BpeTrainer(vocab_size=900, special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>"],
+                                                        initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False))
+    mine = S.Tokenizer(tok.to_str())
+    pieces = ["a", "b", " ", "  ", "\n", "'", "'s", "'S", "'Re", "1", "22", "é", "漢", "🙂", "\t", "!", "?", "_", "x", "The", " the", "<|im_start|>",
+              "<|im_end|>", "\r\n", " ", "Ⅷ", "²", "٣"]
+    tests = corpus[:200] + ["".join(rnd.choice(pieces) for _ in range(rnd.randint(0, 40))) for _ in range(600)]
+    for t in tests:
+        want = tok.encode(t, add_special_tokens=False).ids
+        assert mine.encode(t) == want, t
+        assert mine.decode(want, skip_special=False) == tok.decode(want, skip_special_tokens=False), t
