@@ -1,6 +1,6 @@
 """Replays the reference's protocol parity corpus against the C++ server's parsers, when a checkout of the reference's
-fixtures is available: set B200E_REF_FIXTURES to its ``crates/agens-server/tests/fixtures`` directory (the test is
-skipped otherwise).  The corpus holds raw model outputs (real generations, re-rendered agent transcripts, synthetic edge
+fixtures is available: B200E_REF_FIXTURES names its ``crates/agens-server/tests/fixtures`` directory, or the checkout
+sits next to this repository as ``../reference`` (the tests are skipped otherwise).  The corpus holds raw model outputs (real generations, re-rendered agent transcripts, synthetic edge
 cases) with the reasoning / content / tool-call split its parsers produce (reference test:
 crates/agens-server/tests/parser_parity.rs).  Compared here, non-streaming and streamed in 7-byte chunks: the reasoning
 text, the content outside calls, and every call's name and arguments."""
@@ -12,9 +12,19 @@ import pytest
 
 from agens_engine_b200.serve import host as H
 
-FIX = os.environ.get("B200E_REF_FIXTURES", "")
+def _fixtures_dir() -> str:
+    """B200E_REF_FIXTURES, else a checkout of the reference next to this repository (``../reference``) if there is one."""
+    env = os.environ.get("B200E_REF_FIXTURES", "")
+    if env:
+        return env
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    guess = os.path.join(os.path.dirname(here), "reference", "crates", "agens-server", "tests", "fixtures")
+    return guess if os.path.isfile(os.path.join(guess, "parser_corpus.json")) else ""
+
+
+FIX = _fixtures_dir()
 pytestmark = pytest.mark.skipif(not os.path.isfile(os.path.join(FIX, "parser_corpus.json")),
-                                reason="B200E_REF_FIXTURES does not point at the reference's fixtures")
+                                reason="the reference's fixtures are not available (B200E_REF_FIXTURES)")
 TAGS = (b"<|think|>", b"<|/think|>", b"<|call|>", b"<|/call|>")
 
 
