@@ -576,8 +576,8 @@ def cmd_serve(ns):
     full.vocab_valid = min(full.vocab_valid or full.vocab, n_tok)
     front = None
     if cfg.vision and world == 1:
-        # image input: the tower's weights are random-init here (a loader for tower tensors of a checkpoint is not part
-        # of this build); the placeholder id comes from the tokenizer's added tokens
+        # image input: the checkpoint's own tower (model.visual.* tensors) when it has one, else random-init weights of
+        # the reference tower's shape; the placeholder id comes from the tokenizer's added tokens
         from .models.vision import VisionConfig, VisionTower
         from .serve.vision import VisionFrontEnd
         pad = [int(t["id"]) for t in tj.get("added_tokens", []) if t.get("content") == "<|image_pad|>"]
@@ -585,7 +585,13 @@ def cmd_serve(ns):
             raise SystemExit("--vision 1 needs an <|image_pad|> token in the tokenizer")
         vc = VisionConfig(out_dim=full.d_model) if full.d_model >= 2048 else \
             VisionConfig(depth=2, d_model=288, n_heads=4, mlp=608, out_dim=full.d_model, pos_grid=12)
-        front = VisionFrontEnd(VisionTower.random_init(vc, m.dev, seed=cfg.seed + 2), pad[0], full.head_dim)
+        if cfg.model_dir and VisionTower.has_tower(cfg.model_dir):
+            tower = VisionTower.from_checkpoint(cfg.model_dir, m.dev)
+            if tower.cfg.out_dim != full.d_model:
+                raise SystemExit(f"the checkpoint's vision tower feeds {tower.cfg.out_dim}-wide rows into a {full.d_model}-wide model")
+        else:
+            tower = VisionTower.random_init(vc, m.dev, seed=cfg.seed + 2)
+        front = VisionFrontEnd(tower, pad[0], full.head_dim)
     eng = Engine(model, lambda *a: False, sources_factory=(lambda: sources) if sources else None,
                  max_drafts=cfg.draft_depth if sources else 0, max_batch=cfg.max_batch, keep_sequences=world == 1, vision=front)
     attach_to_server(eng, srv, context_length=m.max_ctx)

@@ -144,6 +144,75 @@ class VisionTower:
                 "ln2_w": G(d), "ln2_b": B(d), "fc1_w": W(cfg.mlp, d), "fc1_b": B(cfg.mlp), "fc2_w": W(d, cfg.mlp), "fc2_b": B(d)}.items()})
         return t
 
+    # names of the tower's tensors in a checkpoint (``model.visual.`` + ...), as the reference registers them
+    # (kernels/oracle/bridge/vision.cpp:56-61, :114; loader crates/agens-cli/src/m1.rs:338-360)
+    _TOP = {"patch_embed.proj.weight": "patch_w", "patch_embed.proj.bias": "patch_b", "pos_embed.weight": "pos",
+            "merger.norm.weight": "m_ln_w", "merger.norm.bias": "m_ln_b", "merger.linear_fc1.weight": "m_fc1_w",
+            "merger.linear_fc1.bias": "m_fc1_b", "merger.linear_fc2.weight": "m_fc2_w", "merger.linear_fc2.bias": "m_fc2_b"}
+    _BLOCK = {"norm1.weight": "ln1_w", "norm1.bias": "ln1_b", "attn.qkv.weight": "qkv_w", "attn.qkv.bias": "qkv_b",
+              "attn.proj.weight": "proj_w", "attn.proj.bias": "proj_b", "norm2.weight": "ln2_w", "norm2.bias": "ln2_b",
+              "mlp.linear_fc1.weight": "fc1_w", "mlp.linear_fc1.bias": "fc1_b", "mlp.linear_fc2.weight": "fc2_w",
+              "mlp.linear_fc2.bias": "fc2_b"}
+
+    @staticmethod
+    def has_tower(dir_: str, prefix: str = "model.visual.") -> bool:
+        """Whether the checkpoint directory carries vision tower tensors."""
+        import json
+        import os
+        idx = os.path.join(dir_, "model.safetensors.index.json")
+        if os.path.exists(idx):
+            return any(k.startswith(prefix) for k in json.load(open(idx))["weight_map"])
+        from ..utils.checkpoint import SafeTensorsFile
+        one = os.path.join(dir_, "model.safetensors")
+        return os.path.exists(one) and any(k.startswith(prefix) for k in SafeTensorsFile(one).keys())
+
+    @staticmethod
+    def from_checkpoint(dir_: str, device="cuda:0", n_heads: int = 16, resident: bool = True, prefix: str = "model.visual.",
+                        eps: float = 1e-6) -> "VisionTower":
+        """The checkpoint's own tower: bf16 tensors ``model.visual.*`` of the safetensors shards in ``dir_``.  Sizes come
+        from the tensors (depth = number of blocks, width, MLP width, patch size, position grid, output width); only the
+        head count is not in them.  ``resident=False`` keeps the blocks in pinned host memory and streams them per layer
+        at encode time, as the reference does."""
+        import json
+        import os
+        from ..utils.checkpoint import SafeTensorsFile
+        idx = os.path.join(dir_, "model.safetensors.index.json")
+        if os.path.exists(idx):
+            wm = {k: v for k, v in json.load(open(idx))["weight_map"].items() if k.startswith(prefix)}
+        else:
+            wm = {k: "model.safetensors" for k in SafeTensorsFile(os.path.join(dir_, "model.safetensors")).keys() if k.startswith(prefix)}
+        if not wm:
+            raise ValueError(f"{dir_}: no {prefix}* tensors")
+        files = {fn: SafeTensorsFile(os.path.join(dir_, fn)) for fn in set(wm.values())}
+
+        def get(name):
+            full = prefix + name
+            if full not in wm:
+                raise ValueError(f"vision tower: missing tensor {full}")
+            f = files[wm[full]]
+            if f.info[full]["dtype"] != "BF16":
+                raise ValueError(f"{full}: vision tensors must be bf16 (got {f.info[full]['dtype']})")
+            return f.tensor(full).clone()
+
+        depth = 1 + max(int(k[len(prefix) + 7:].split(".")[0]) for k in wm if k.startswith(prefix + "blocks."))
+        top = {mine: get(name) for name, mine in VisionTower._TOP.items()}
+        d = top["patch_w"].shape[0]
+        top["patch_w"] = top["patch_w"].reshape(d, -1).contiguous()              # [d, channels x (frames x) patch x patch]
+        grid = int(round(math.sqrt(top["pos"].shape[0])))
+        blocks = [{mine: get(f"blocks.{i}.{name}") for name, mine in VisionTower._BLOCK.items()} for i in range(depth)]
+        cfg = VisionConfig(depth=depth, d_model=d, n_heads=n_heads, mlp=blocks[0]["fc1_w"].shape[0], patch_dim=top["patch_w"].shape[1],
+                           out_dim=top["m_fc2_w"].shape[0], pos_grid=grid, eps=eps)
+        if grid * grid != top["pos"].shape[0] or d % n_heads or tuple(top["m_fc1_w"].shape) != (4 * d, 4 * d) or \
+                tuple(blocks[0]["qkv_w"].shape) != (3 * d, d):
+            raise ValueError("vision tower: tensor shapes do not fit together")
+        t = VisionTower(cfg, device, resident)
+        put = (lambda x: x.to(t.dev)) if resident or t.dev.type != "cuda" else (lambda x: x.pin_memory())
+        t.w = {k: v.to(t.dev) for k, v in top.items()}
+        t.blocks = [{k: put(v) for k, v in b.items()} for b in blocks]
+        for f in files.values():
+            f.close()
+        return t
+
     def weight_bytes(self) -> int:
         return sum(v.numel() * 2 for v in self.w.values()) + sum(v.numel() * 2 for b in self.blocks for v in b.values())
 

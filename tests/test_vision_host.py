@@ -1,6 +1,7 @@
 """Host image pipeline against torch's antialiased bicubic and hand-worked cases (reference: vision.rs tests :223 and
 the preprocess contract of kernels/oracle/bridge/vision.cpp:234-256)."""
 import base64
+import json
 import struct
 import zlib
 
@@ -124,3 +125,37 @@ def test_front_end_expands_placeholders_and_positions_with_a_stub_tower():
         fe.prepare([1, PAD], ["http://example.com/a.png"])
     with pytest.raises(ValueError):
         fe.prepare([1, PAD], ["data:image/jpeg;base64," + base64.b64encode(b"\xff\xd8\xff\xe0").decode()])
+
+
+def test_vision_tower_loads_from_checkpoint_tensors(tmp_path):
+    """The tower of a checkpoint (``model.visual.*`` tensors, the reference's names): sizes are read off the tensors and
+    the loaded tower computes what the tower that wrote them computes (fp32 restatement, on the CPU)."""
+    import torch
+    from agens_engine_b200.models.vision import VisionConfig, VisionTower
+    from agens_engine_b200.utils import checkpoint as K
+    cfg = VisionConfig(depth=3, d_model=64, n_heads=4, mlp=160, patch_dim=3 * 2 * 8 * 8, out_dim=96, pos_grid=6)
+    a = VisionTower.random_init(cfg, "cpu", seed=4)
+    back = {v: k for k, v in VisionTower._TOP.items()}
+    tensors = {"model.visual." + back[k]: v.clone() for k, v in a.w.items()}
+    tensors["model.visual.patch_embed.proj.weight"] = a.w["patch_w"].reshape(64, 3, 2, 8, 8).contiguous()     # conv-shaped in the file
+    bback = {v: k for k, v in VisionTower._BLOCK.items()}
+    for i, blk in enumerate(a.blocks):
+        for k, v in blk.items():
+            tensors[f"model.visual.blocks.{i}.{bback[k]}"] = v.clone()
+    tensors["model.norm.weight"] = torch.ones(8, dtype=torch.bfloat16)                    # not a tower tensor
+    items = list(tensors.items())
+    K.write_safetensors(str(tmp_path / "model-00001-of-00002.safetensors"), dict(items[:20]))
+    K.write_safetensors(str(tmp_path / "model-00002-of-00002.safetensors"), dict(items[20:]))
+    wm = {k: "model-00001-of-00002.safetensors" for k, _ in items[:20]}
+    wm.update({k: "model-00002-of-00002.safetensors" for k, _ in items[20:]})
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    assert VisionTower.has_tower(str(tmp_path))
+    b = VisionTower.from_checkpoint(str(tmp_path), "cpu", n_heads=4)
+    assert (b.cfg.depth, b.cfg.d_model, b.cfg.mlp, b.cfg.patch_dim, b.cfg.out_dim, b.cfg.pos_grid) == (3, 64, 160, 384, 96, 6)
+    patches = torch.randn(4 * 6, cfg.patch_dim)
+    assert torch.equal(a.encode_ref(patches, (4, 6)), b.encode_ref(patches, (4, 6)))
+    # an incomplete tower is refused by name
+    wm.pop("model.visual.merger.linear_fc2.bias")
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps({"weight_map": wm}))
+    with pytest.raises(ValueError, match="merger.linear_fc2.bias"):
+        VisionTower.from_checkpoint(str(tmp_path), "cpu", n_heads=4)
