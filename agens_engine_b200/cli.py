@@ -575,7 +575,8 @@ def cmd_serve(ns):
     full = m.full_cfg if world > 1 else m.cfg
     full.vocab_valid = min(full.vocab_valid or full.vocab, n_tok)
     front = None
-    if cfg.vision and world == 1:
+    if cfg.vision:                                        # under --tp the tower runs on the leader; the driver hands the
+        # encoder rows and position tables to the followers with the prefill call (every rank substitutes the same rows)
         # image input: the checkpoint's own tower (model.visual.* tensors) when it has one, else random-init weights of
         # the reference tower's shape; the placeholder id comes from the tokenizer's added tokens
         from .models.vision import VisionConfig, VisionTower

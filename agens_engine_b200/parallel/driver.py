@@ -84,9 +84,13 @@ class TpDriver:
 
 
 def _plain(x):
-    """Tensors become lists so that commands stay small and device free."""
+    """Tensors travel device free: small ones as lists, larger ones (encoder rows of an image, position tables) as their
+    raw bytes, which pickle and broadcast at memory speed."""
     if isinstance(x, torch.Tensor):
-        return ("__tensor__", x.dtype, x.cpu().tolist())
+        t = x.detach().cpu().contiguous()
+        if t.numel() <= 1024:
+            return ("__tensor__", t.dtype, t.tolist())
+        return ("__tensor_bytes__", t.dtype, tuple(t.shape), t.view(torch.uint8).numpy().tobytes())
     if isinstance(x, (list, tuple)):
         return type(x)(_plain(v) for v in x)
     if isinstance(x, dict):
@@ -97,6 +101,8 @@ def _plain(x):
 def _revive(x):
     if isinstance(x, tuple) and len(x) == 3 and x[0] == "__tensor__":
         return torch.tensor(x[2], dtype=x[1])
+    if isinstance(x, tuple) and len(x) == 4 and x[0] == "__tensor_bytes__":
+        return torch.frombuffer(bytearray(x[3]), dtype=torch.uint8).view(x[1]).reshape(x[2])
     if isinstance(x, (list, tuple)):
         return type(x)(_revive(v) for v in x)
     if isinstance(x, dict):

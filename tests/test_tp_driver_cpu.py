@@ -36,6 +36,12 @@ class FakeModel:
     def enable_host_tier(self, window_tokens, batch_pages=256):
         self.calls.append(("enable_host_tier", window_tokens))
 
+    def prefill(self, seq, ids, want_logits=False, image_rows=None, rope_pos3=None, **kw):
+        # what a rank needs of an image prompt: the ids, the encoder rows and the position table, bit for bit
+        self.calls.append(("prefill", seq, tuple(ids.tolist()), str(image_rows.dtype), tuple(image_rows.shape),
+                           float(image_rows.float().sum()), int(rope_pos3.sum())))
+        return 0, None
+
 
 def _rank(rank, world, port, mode, q):
     os.environ.update({"MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "RANK": str(rank), "WORLD_SIZE": str(world)})
@@ -56,6 +62,13 @@ def _rank(rank, world, port, mode, q):
         blob = drv.park(0)
         drv.unpark(1, blob)
         drv.enable_host_tier(4096)
+        if mode == "normal":
+            import torch
+            g = torch.Generator().manual_seed(1)
+            rows = torch.randn(300, 64, generator=g).to(torch.bfloat16)           # large tensors travel as raw bytes
+            pos3 = torch.arange(3 * 40, dtype=torch.int32).reshape(3, 40)
+            drv.prefill(0, torch.arange(40, dtype=torch.int32), image_rows=rows, rope_pos3=pos3)
+            q.put(("leader-prefill", m.calls[-1]))
         if mode == "death":
             time.sleep(1.5)                       # the follower has left by now
             t0 = time.time()
@@ -94,7 +107,7 @@ def _run(mode):
         p.start()
     out = []
     deadline = time.time() + 90
-    want = 3 if mode == "death" else 4
+    want = 3 if mode == "death" else 5
     while len(out) < want and time.time() < deadline:
         try:
             out.append(q.get(timeout=1.0))
@@ -114,9 +127,11 @@ def test_forwarded_calls_and_deterministic_errors():
     leader = [o for o in out if o[0] == "leader"]
     assert ("leader", "caught KV pool exhausted") in leader and ("leader", "done") in leader
     fol = [o for o in out if o[0] == "follower"][0]
-    assert fol[1] == 6                                              # every command was taken, the failing one included
+    assert fol[1] == 7                                              # every command was taken, the failing one included
     names = [c[0] for c in fol[2]]
-    assert names == ["new_seq", "reserve", "forward_rows", "park", "unpark", "enable_host_tier"]
+    assert names == ["new_seq", "reserve", "forward_rows", "park", "unpark", "enable_host_tier", "prefill"]
+    lead = [o for o in out if o[0] == "leader-prefill"][0][1]
+    assert fol[2][-1] == lead and lead[3] == "torch.bfloat16" and lead[4] == (300, 64)   # image rows reach the follower intact
     assert any("KV pool exhausted" in o[1] for o in out if o[0] == "log")
 
 
