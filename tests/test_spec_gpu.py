@@ -312,8 +312,7 @@ def test_mtp_shortlist_head(tiny):
         hd.new_seq(0)
     tok = int(prompt[5])
     a = int(head.forward_mtp([tok], h, [0])[0])
-    full.forward_rows  # (same weights: random_init_for is seeded)
-    full.hid_in[:1].copy_(h)
+    full.hid_in[:1].copy_(h)                               # (same weights: random_init_for is seeded)
     _, logits = full.forward_rows([tok], [0], want_logits=True)
     best = max(ids, key=lambda t: float(logits[0, t]))
     assert a == best or abs(float(logits[0, a]) - float(logits[0, best])) < 0.05 * float(logits[0].abs().max())
