@@ -2,12 +2,11 @@
 //
 // The reference decodes JPEG data URLs with nvJPEG on the GPU (kernels/oracle/bridge/vision.cpp:204-228) after the
 // server recognised the format (crates/agens-server/src/vision.rs:126-135).  Here the decode runs on the host next to
-// the PNG / PPM readers: one or three components, any 1x / 2x sampling factors (4:4:4, 4:2:2, 4:4:0, 4:2:0), restart
+// the PNG / PPM readers: one, three or four (Adobe CMYK / YCCK) components, any 1x / 2x sampling factors (4:4:4, 4:2:2, 4:4:0, 4:2:0), restart
 // intervals, JFIF YCbCr or Adobe RGB colour, any number of scans: interleaved or one component per scan, and the
 // progressive mode (spectral selection and successive approximation: DC / AC first and refinement scans with
 // end-of-band runs).  Every scan writes into per-component coefficient buffers; dequantisation and the inverse DCT run
-// once after the last scan.  Arithmetic-coded, lossless, hierarchical, 12-bit and CMYK files are refused with a
-// message.  Chroma is upsampled with the triangle filter common decoders use by default, so results stay within a
+// once after the last scan.  Arithmetic-coded, lossless, hierarchical and 12-bit files are refused with a message.  Chroma is upsampled with the triangle filter common decoders use by default, so results stay within a
 // few levels of theirs.
 #include <algorithm>
 #include <cmath>
@@ -47,11 +46,11 @@ struct Dec {
   uint16_t qt[4][64];
   bool qt_ok[4] = {false, false, false, false};
   Huff dc[4], ac[4];
-  Comp comp[3];
+  Comp comp[4];
   int restart = 0;
   int hmax = 1, vmax = 1;
   // the scan being decoded
-  Comp* scan_comp[3] = {nullptr, nullptr, nullptr};
+  Comp* scan_comp[4] = {nullptr, nullptr, nullptr, nullptr};
   int scan_n = 0, ss = 0, se = 63, ah = 0, al = 0;
   int eobrun = 0;
   bool planes_ready = false;
@@ -308,7 +307,7 @@ bool parse_headers(Dec& d, bool stop_at_frame) {
       d.W = u16(s + 3);
       d.ncomp = s[5];
       if (d.W <= 0 || d.H <= 0) return fail(d, "jpeg: empty image");
-      if (d.ncomp != 1 && d.ncomp != 3) return fail(d, "jpeg: only grey and three-component images are supported");
+      if (d.ncomp != 1 && d.ncomp != 3 && d.ncomp != 4) return fail(d, "jpeg: only grey, three- and four-component images are supported");
       if (se - s < 6 + 3 * d.ncomp) return fail(d, "jpeg: bad frame header");
       for (int i = 0; i < d.ncomp; ++i) {
         Comp& c = d.comp[i];
@@ -563,6 +562,29 @@ void to_rgb(const Dec& d, uint8_t* rgb) {
         const uint8_t g = c.plane[(size_t)y * c.bw * 8 + x];
         uint8_t* o = rgb + ((size_t)y * d.W + x) * 3;
         o[0] = o[1] = o[2] = g;
+      }
+    return;
+  }
+  if (d.ncomp == 4) {
+    // Adobe CMYK (transform 0) or YCCK (transform 2): the file holds the inverted ink values (255 = no ink); YCCK codes
+    // the three colour inks as YCbCr.  RGB = colour ink value x black value / 255, the conversion common viewers use.
+    const bool ycck = d.adobe && d.adobe_transform == 2;
+    for (int y = 0; y < d.H; ++y)
+      for (int x = 0; x < d.W; ++x) {
+        float v[4];
+        for (int i = 0; i < 4; ++i) {
+          const Comp& c = d.comp[i];
+          v[i] = sample_up(c, x, y, d.hmax / c.h, d.vmax / c.v, d.W, d.H);
+        }
+        if (ycck) {
+          const float Y = v[0], cb = v[1] - 128.f, cr = v[2] - 128.f;
+          v[0] = std::min(255.f, std::max(0.f, Y + 1.402f * cr));
+          v[1] = std::min(255.f, std::max(0.f, Y - 0.344136f * cb - 0.714136f * cr));
+          v[2] = std::min(255.f, std::max(0.f, Y + 1.772f * cb));
+        }
+        if (!d.adobe) { v[0] = 255.f - v[0]; v[1] = 255.f - v[1]; v[2] = 255.f - v[2]; v[3] = 255.f - v[3]; }   // plain CMYK: not inverted
+        uint8_t* o = rgb + ((size_t)y * d.W + x) * 3;
+        for (int i = 0; i < 3; ++i) o[i] = clamp8(v[i] * v[3] / 255.f);
       }
     return;
   }

@@ -106,3 +106,16 @@ def test_truncated_and_garbage_inputs_fail_cleanly():
         except ValueError:
             continue
         assert out.shape[2] == 3            # a truncated scan may still decode (missing data reads as zeros)
+
+
+def test_cmyk_files_match_pillow():
+    """Four-component Adobe files (inverted ink values): converted to RGB as common viewers do; sequential and
+    progressive."""
+    img = PIL.fromarray(_image(60, 90, seed=9)).convert("CMYK")
+    for kw in ({}, {"progressive": True}):
+        buf = io.BytesIO()
+        img.save(buf, "JPEG", quality=92, **kw)
+        data = buf.getvalue()
+        ours, ref = V.decode_image(data), _pil(data)
+        diff = np.abs(ours.astype(np.int32) - ref.astype(np.int32))
+        assert ours.shape == (60, 90, 3) and diff.mean() < 1.0 and diff.max() <= 12, (kw, diff.mean(), diff.max())
