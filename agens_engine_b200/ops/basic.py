@@ -148,9 +148,25 @@ def sample_rows(logits: torch.Tensor, temperature: torch.Tensor, top_k: Optional
 
 
 def spec_accept(ids: torch.Tensor, target: torch.Tensor, row0: torch.Tensor, cnt: torch.Tensor, max_block: int):
-    """Longest-prefix acceptance of verify blocks; returns ``(n_emitted [blocks], emitted [blocks, max_block])``."""
-    lib = _lib.cuda_lib()
+    """Longest-prefix acceptance of verify blocks; returns ``(n_emitted [blocks], emitted [blocks, max_block])``.
+    Block b covers rows ``row0[b] .. row0[b] + cnt[b] - 1`` (the bonus token, then the drafts); ``target[r]`` is the
+    model's own token after row r; draft j + 1 is accepted iff it equals ``target[j]``.  Host tensors take the same rule
+    in plain Python (scheduler tests with a stand-in model)."""
     nb = row0.numel()
+    if ids.device.type == "cpu":
+        n_emit = torch.empty(nb, dtype=torch.int32)
+        emitted = torch.zeros(nb, max_block, dtype=torch.int32)
+        il, tl = ids.tolist(), target.tolist()
+        for b_, (r0, c) in enumerate(zip(row0.tolist(), cnt.tolist())):
+            acc = 0
+            while acc + 1 < c and il[r0 + acc + 1] == tl[r0 + acc]:
+                acc += 1
+            for j in range(acc):
+                emitted[b_, j] = il[r0 + j + 1]
+            emitted[b_, acc] = tl[r0 + acc]
+            n_emit[b_] = acc + 1
+        return n_emit, emitted
+    lib = _lib.cuda_lib()
     n_emit = torch.empty(nb, dtype=torch.int32, device=ids.device)
     emitted = torch.zeros(nb, max_block, dtype=torch.int32, device=ids.device)
     with torch.cuda.device(ids.device):

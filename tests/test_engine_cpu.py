@@ -1,0 +1,199 @@
+"""The serving loop on the CPU with a stand-in model (no kernels): the scheduler, the speculative decoder's bookkeeping and
+the KV policy run exactly as on a GPU, the "model" is a fixed function of everything a sequence was fed.  Any slip in the
+bookkeeping (a token fed twice or not at all, a sequence resumed with the wrong rows, drafts accepted wrongly) changes
+the tokens.  Reference gates: serve-smoke, batch-e2e, session and eviction behaviour of crates/agens-cli/src/serve.rs."""
+import types
+
+import torch
+
+from agens_engine_b200.serve.engine import Engine
+from agens_engine_b200.spec import CopyLookupSource, ModelSource
+
+
+def _next(tokens):
+    return (sum((j % 97 + 1) * v for j, v in enumerate(tokens)) * 31 + 7 * len(tokens)) % 500
+
+
+class FakeModel:
+    def __init__(self, max_seqs=4, max_ctx=256, n_pages=None, page=16, chunk=32, wrong_every=0):
+        self.cfg = types.SimpleNamespace(page_size=page, vocab=500, vocab_valid=0, d_model=8, kv_bytes_per_token=lambda tp=1: 64)
+        self.dev = torch.device("cpu")
+        self.max_seqs, self.max_ctx, self.prefill_chunk, self.max_rows = max_seqs, max_ctx, chunk, 32
+        self.n_pages = n_pages or max_seqs * ((max_ctx + page - 1) // page)
+        self.tokens, self.seq_len_host, self.seq_pages = {}, {}, {}
+        self.hidden_sink = None
+        self.h_a = torch.zeros(32, 8)
+        self.calls = 0
+
+    # ---- pages ----
+    def free_pages(self):
+        return self.n_pages - sum(len(p) for p in self.seq_pages.values())
+
+    def _fit(self, s, n):
+        if n > self.max_ctx:
+            raise RuntimeError("context length exceeds max_ctx")
+        need = (n + self.cfg.page_size - 1) // self.cfg.page_size - len(self.seq_pages[s])
+        if need > self.free_pages():
+            raise RuntimeError("KV pool exhausted")
+        self.seq_pages[s] += [0] * max(need, 0)
+
+    def reserve(self, s, n):
+        self._fit(s, n)
+
+    def new_seq(self, s):
+        assert s not in self.tokens and 0 <= s < self.max_seqs
+        self.tokens[s], self.seq_len_host[s], self.seq_pages[s] = [], 0, []
+
+    def free_seq(self, s):
+        self.tokens.pop(s); self.seq_len_host.pop(s); self.seq_pages.pop(s)
+
+    def truncate(self, s, n):
+        assert n <= len(self.tokens[s])
+        del self.tokens[s][n:]
+        self.seq_len_host[s] = n
+        del self.seq_pages[s][(n + self.cfg.page_size - 1) // self.cfg.page_size:]
+
+    def fork(self, src, dst):
+        self.new_seq(dst)
+        self._fit(dst, len(self.tokens[src]))
+        self.tokens[dst] = list(self.tokens[src])
+        self.seq_len_host[dst] = len(self.tokens[dst])
+
+    def park(self, s):
+        blob = {"len": len(self.tokens[s]), "tokens": list(self.tokens[s])}
+        self.free_seq(s)
+        return blob
+
+    def unpark(self, s, blob):
+        self.new_seq(s)
+        try:
+            self._fit(s, blob["len"])
+        except RuntimeError:
+            self.free_seq(s)
+            raise
+        self.tokens[s] = list(blob["tokens"])
+        self.seq_len_host[s] = blob["len"]
+
+    # ---- forward ----
+    def prefill(self, s, ids, want_logits=False, **kw):
+        ids = ids.tolist()
+        self._fit(s, len(self.tokens[s]) + len(ids))
+        self.tokens[s] += ids
+        self.seq_len_host[s] = len(self.tokens[s])
+        self.calls += 1
+        return _next(self.tokens[s]), None
+
+    def forward_rows(self, ids, seqs, want_logits=False):
+        assert 1 <= len(ids) <= self.max_rows
+        grow = {}
+        for s in seqs:
+            grow[s] = grow.get(s, 0) + 1
+        for s, g in grow.items():
+            self._fit(s, len(self.tokens[s]) + g)
+        out = []
+        for t, s in zip(ids, seqs):
+            self.tokens[s].append(int(t))
+            out.append(_next(self.tokens[s]))
+        for s in grow:
+            self.seq_len_host[s] = len(self.tokens[s])
+        self.calls += 1
+        return torch.tensor(out, dtype=torch.int32), None
+
+    def set_linear_path(self, x): pass
+    def device_status(self): return 0
+    def recover(self): pass
+    def vocab_valid_full(self): return 500
+
+
+def _alone(prompt, n_new, stop=()):
+    toks, out = list(prompt), []
+    while len(out) < n_new:
+        t = _next(toks)
+        if t in stop:
+            break
+        out.append(t); toks.append(t)
+    return out
+
+
+def _serve(model, reqs, **kw):
+    got, done = {}, {}
+
+    def emit(rid, toks, finished, err):
+        got.setdefault(rid, []).extend(toks)
+        if finished:
+            done[rid] = err
+        return False
+    eng = Engine(model, emit, **kw)
+    rids = [eng.submit(p, s) for p, s in reqs]
+    eng.run_until_idle(20000)
+    assert eng.idle()
+    return eng, [got.get(r, []) for r in rids], [done.get(r) for r in rids]
+
+
+def _prompts(n, lo=5, hi=120, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, 500, (int(torch.randint(lo, hi, (1,), generator=g)),), generator=g).tolist() for _ in range(n)]
+
+
+def test_batched_requests_get_the_tokens_of_a_run_alone():
+    prompts = _prompts(9)
+    m = FakeModel(max_seqs=4, max_ctx=256)
+    eng, outs, errs = _serve(m, [(p, {"max_new_tokens": 20}) for p in prompts])
+    assert outs == [_alone(p, 20) for p in prompts] and errs == [None] * 9
+    assert eng.stats.peak_batch == 4 and m.free_pages() == m.n_pages and not m.tokens
+
+
+def test_speculation_with_right_wrong_and_copied_drafts():
+    prompts = [p * 3 for p in _prompts(5, lo=6, hi=20, seed=2)]            # repetitive prompts: copy-lookup finds drafts
+    want = [_alone(p, 30) for p in prompts]
+    # a drafter that computes the same function drafts perfectly; one with another page size of history does not
+    class Drafter(FakeModel):
+        pass
+    good = Drafter(max_seqs=4, max_ctx=256)
+    m = FakeModel(max_seqs=4, max_ctx=256)
+    eng, outs, _ = _serve(m, [(p, {"max_new_tokens": 30}) for p in prompts], sources_factory=lambda: [ModelSource(good, 3)], max_drafts=3)
+    assert outs == want and eng.spec.stats.accepted == eng.spec.stats.proposed > 0
+    assert eng.spec.stats.tokens_per_step() > 3.0 and not good.tokens and not m.tokens
+    bad = Drafter(max_seqs=4, max_ctx=256)
+    bad.forward_rows = lambda ids, seqs, want_logits=False, f=bad.forward_rows: ((f(ids, seqs)[0] + (torch.arange(len(ids)) % 2)).to(torch.int32), None)
+    m = FakeModel(max_seqs=4, max_ctx=256)
+    eng, outs, _ = _serve(m, [(p, {"max_new_tokens": 30}) for p in prompts], sources_factory=lambda: [CopyLookupSource(), ModelSource(bad, 3)],
+                          max_drafts=3)
+    assert outs == want and 0 < eng.spec.stats.accepted < eng.spec.stats.proposed
+
+
+def test_stop_ids_limits_and_context_overflow():
+    p = _prompts(1, seed=5)[0]
+    full = _alone(p, 40)
+    stop = full[7]
+    m = FakeModel(max_seqs=2, max_ctx=256)
+    eng, outs, errs = _serve(m, [(p, {"max_new_tokens": 40, "stop_token_ids": [stop]}), (p, {"max_new_tokens": 3}),
+                                 (list(range(300)), {"max_new_tokens": 4})])
+    assert outs[0] == full[:full.index(stop) + 1] and outs[1] == full[:3]        # the stop token itself is delivered (the server drops it)
+    assert outs[2] == [] and errs[2] and not m.tokens
+
+
+def test_kv_pressure_preempts_and_resumes_exactly():
+    prompts = _prompts(6, lo=40, hi=100, seed=7)
+    m = FakeModel(max_seqs=4, max_ctx=256, n_pages=22)                        # far fewer pages than four full sequences need
+    eng, outs, errs = _serve(m, [(p, {"max_new_tokens": 60}) for p in prompts])
+    assert outs == [_alone(p, 60) for p in prompts] and errs == [None] * 6
+    assert eng.stats.evictions > 0 and m.free_pages() == m.n_pages
+
+
+def test_kept_sequences_reuse_a_conversation_prefix():
+    p1 = _prompts(1, lo=60, hi=61, seed=9)[0]
+    m = FakeModel(max_seqs=4, max_ctx=512)
+    got = {}
+    eng = Engine(m, lambda rid, t, f, e: got.setdefault(rid, []).extend(t) or False, keep_sequences=True)
+    r1 = eng.submit(p1, {"max_new_tokens": 10}, session="conv")
+    eng.run_until_idle(5000)
+    a1 = got[r1]
+    assert a1 == _alone(p1, 10)
+    calls_before = m.calls
+    p2 = p1 + a1 + [11, 12, 13]                                              # the next turn of the same conversation
+    r2 = eng.submit(p2, {"max_new_tokens": 10}, session="conv")
+    eng.run_until_idle(5000)
+    assert got[r2] == _alone(p2, 10)
+    fed = m.calls - calls_before
+    assert fed <= 1 + 10 + 1, fed                                            # the old turn was not prefilled again (one short chunk + decode)
