@@ -179,7 +179,8 @@ class Engine:
             self._thread.join(timeout=30)
 
     def run(self):
-        torch.cuda.set_device(self.m.dev)
+        if self.m.dev.type == "cuda":
+            torch.cuda.set_device(self.m.dev)
         while not self._stop.is_set():
             try:
                 if not self.step():

@@ -197,3 +197,56 @@ def test_kept_sequences_reuse_a_conversation_prefix():
     assert got[r2] == _alone(p2, 10)
     fed = m.calls - calls_before
     assert fed <= 1 + 10 + 1, fed                                            # the old turn was not prefilled again (one short chunk + decode)
+
+
+def test_engine_thread_behind_the_http_front_end(tmp_path):
+    """The OpenAI front end (C++) on top of the engine thread on top of the stand-in model: requests in parallel, plain and
+    streamed, get the text of the tokens a run alone produces; usage counts them."""
+    import json
+    import threading
+    from agens_engine_b200.serve.engine import attach_to_server
+    from agens_engine_b200.serve.server import Server, Tokenizer
+    from tests.fixtures import tiny_tokenizer_json
+    tok = tmp_path / "tokenizer.json"
+    tok.write_text(tiny_tokenizer_json())
+    tk = Tokenizer(tiny_tokenizer_json())
+    srv = Server(str(tok), model_name="fake", eos_token_ids=[])
+
+    class Bytes(FakeModel):                                  # ids the byte-level test tokenizer can print
+        def prefill(self, s, ids, want_logits=False, **kw):
+            t, lg = super().prefill(s, ids, want_logits, **kw)
+            return 65 + t % 26, lg
+
+        def forward_rows(self, ids, seqs, want_logits=False):
+            out, lg = super().forward_rows(ids, seqs, want_logits)
+            return 65 + out % 26, lg
+
+    m = Bytes(max_seqs=4, max_ctx=512)
+    eng = Engine(m, lambda *a: False)
+    attach_to_server(eng, srv)
+    eng.start()
+    try:
+        prompts = ["count to three", "the quick brown fox", "hello", "a b c d e f g"]
+        res = {}
+
+        def call(i, stream):
+            res[(i, stream)] = srv.handle("POST", "/v1/completions", {"prompt": prompts[i], "max_tokens": 9, "temperature": 0, "stream": stream})
+        th = [threading.Thread(target=call, args=(i, st)) for i in range(4) for st in (False, True)]
+        [t.start() for t in th]
+        [t.join(60) for t in th]
+        for i, p in enumerate(prompts):
+            toks, want = tk.encode(p), []
+            while len(want) < 9:
+                want.append(65 + _next(toks) % 26)
+                toks.append(want[-1])
+            text = tk.decode(want, skip_special=False)
+            st, body = res[(i, False)]
+            r = json.loads(body)
+            assert st == 200 and r["choices"][0]["text"] == text and r["usage"]["completion_tokens"] == 9, (i, body)
+            st, body = res[(i, True)]
+            ev = [json.loads(x[6:]) for x in body.split("\n\n") if x.startswith("data: {")]
+            assert st == 200 and "".join(e["choices"][0]["text"] for e in ev if e["choices"]) == text
+        assert "b200e_requests_total 8" in srv.handle("GET", "/metrics")[1]
+    finally:
+        eng.stop()
+    assert not m.tokens
