@@ -19,6 +19,7 @@ MERGE = 2
 FACTOR = PATCH * MERGE
 MIN_PIXELS = 64 * 64
 MAX_PIXELS = 4_194_304
+MAX_DECODE_PIXELS = 1 << 26          # largest image a request may make the host decode (192 MiB of RGB)
 MAX_IMAGES = 16
 _sig = False
 
@@ -124,7 +125,7 @@ def _decode_jpeg(data: bytes) -> np.ndarray:
     h, w, nc = C.c_int(), C.c_int(), C.c_int()
     if lib.b2h_jpeg_info(buf, len(data), C.byref(h), C.byref(w), C.byref(nc)) != 0:
         raise ValueError(lib.b2h_jpeg_error().decode() or "bad JPEG")
-    if h.value * w.value > (1 << 28):
+    if h.value * w.value > MAX_DECODE_PIXELS:
         raise ValueError("jpeg: image too large")
     out = np.empty((h.value, w.value, 3), dtype=np.uint8)
     if lib.b2h_jpeg_decode(buf, len(data), out.ctypes.data_as(C.c_void_p)) != 0:
@@ -143,6 +144,8 @@ def _decode_simple(data: bytes, kind: str) -> np.ndarray:
     h, w = C.c_int(), C.c_int()
     if info(buf, len(data), C.byref(h), C.byref(w)) != 0:
         raise ValueError(err().decode() or f"bad {kind}")
+    if h.value * w.value > MAX_DECODE_PIXELS:
+        raise ValueError(f"{kind}: image too large")
     out = np.empty((h.value, w.value, 3), dtype=np.uint8)
     if dec(buf, len(data), out.ctypes.data_as(C.c_void_p)) != 0:
         raise ValueError(err().decode() or f"bad {kind}")
@@ -167,10 +170,16 @@ def _decode_png(data: bytes) -> np.ndarray:
         elif kind == b"IEND":
             break
         p += 12 + n
-    if w <= 0 or h <= 0 or ctype not in (0, 2, 3, 4, 6):
+    if w <= 0 or h <= 0 or ctype not in (0, 2, 3, 4, 6) or depth not in (1, 2, 4, 8, 16):
         raise ValueError("bad PNG header")
+    if w * h > MAX_DECODE_PIXELS:
+        raise ValueError("png: image too large")
+    # inflate no more than the scanlines can hold (filter bytes and Adam7 row padding included): a small file may
+    # expand a thousandfold
+    limit = h * (1 + (w * 8 * depth + 7) // 8) + 16 * (h + 7) + 64
     try:
-        raw = zlib.decompress(b"".join(idat))
+        z = zlib.decompressobj()
+        raw = z.decompress(b"".join(idat), limit)
     except zlib.error as e:
         raise ValueError(f"png: {e}")
     lib = _h()

@@ -10,8 +10,10 @@
 #include <netinet/in.h>
 #include <netinet/tcp.h>
 #include <sys/socket.h>
+#include <sys/time.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
@@ -26,6 +28,7 @@
 #include <mutex>
 #include <random>
 #include <sstream>
+#include <system_error>
 #include <thread>
 
 #include "text.hpp"
@@ -804,34 +807,88 @@ static bool send_all(int fd, const std::string& s) {
 }
 static const char* status_text(int s) { return s == 200 ? "OK" : s == 400 ? "Bad Request" : s == 404 ? "Not Found" : s == 500 ? "Internal Server Error" : "Error"; }
 
-static void serve_connection(Server* sv, int fd) {
+// Limits of the socket layer: a request head of at most 1 MiB, a body of at most kMaxBody bytes, kIoTimeoutS seconds of
+// silence while a request is being read, and at most kMaxConnections connections being served at once.
+constexpr size_t kMaxBody = 512ull << 20;
+constexpr int kIoTimeoutS = 30;
+constexpr int kMaxConnections = 2048;
+static std::atomic<int> g_connections{0};
+
+static void send_plain(int fd, int status, const std::string& body) {
+  std::ostringstream o;
+  o << "HTTP/1.1 " << status << " " << (status == 413 ? "Payload Too Large" : status == 408 ? "Request Timeout" : status == 503 ? "Service Unavailable" : status_text(status))
+    << "\r\nContent-Type: application/json\r\nContent-Length: " << body.size() << "\r\nConnection: close\r\n\r\n" << body;
+  send_all(fd, o.str());
+}
+
+static void serve_connection_inner(Server* sv, int fd) {
+  timeval tv{kIoTimeoutS, 0};
+  setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof tv);
+  setsockopt(fd, SOL_SOCKET, SO_SNDTIMEO, &tv, sizeof tv);
   std::string buf;
   char tmp[8192];
   size_t hdr_end = std::string::npos;
   while (hdr_end == std::string::npos) {
     ssize_t n = recv(fd, tmp, sizeof tmp, 0);
-    if (n <= 0) { close(fd); return; }
+    if (n <= 0) return;
+    const size_t from = buf.size() < 3 ? 0 : buf.size() - 3;
     buf.append(tmp, (size_t)n);
-    hdr_end = buf.find("\r\n\r\n");
-    if (buf.size() > (1 << 20)) { close(fd); return; }
+    hdr_end = buf.find("\r\n\r\n", from);
+    if (hdr_end == std::string::npos && buf.size() > (1 << 20)) { send_plain(fd, 400, error_response(400, "request head too large").body); return; }
   }
   std::istringstream hs(buf.substr(0, hdr_end));
   std::string method, path, ver, line, session;
   hs >> method >> path >> ver;
   size_t clen = 0;
+  bool expect_continue = false, chunked = false;
   std::getline(hs, line);
   while (std::getline(hs, line)) {
     if (!line.empty() && line.back() == '\r') line.pop_back();
     const size_t c = line.find(':');
     if (c == std::string::npos) continue;
     std::string k = line.substr(0, c), v = line.substr(c + 1);
-    while (!v.empty() && v[0] == ' ') v.erase(0, 1);
-    for (auto& ch : k) ch = (char)tolower(ch);
-    if (k == "content-length") clen = (size_t)std::atoll(v.c_str());
+    while (!v.empty() && (v[0] == ' ' || v[0] == '\t')) v.erase(0, 1);
+    while (!v.empty() && (v.back() == ' ' || v.back() == '\t')) v.pop_back();
+    for (auto& ch : k) ch = (char)tolower((unsigned char)ch);
+    if (k == "content-length") {
+      if (v.empty() || v.size() > 18 || v.find_first_not_of("0123456789") != std::string::npos) { send_plain(fd, 400, error_response(400, "bad Content-Length").body); return; }
+      clen = (size_t)std::strtoull(v.c_str(), nullptr, 10);
+    }
     if (k == "x-session-id") session = v;
+    if (k == "expect") { std::string lv = v; for (auto& ch : lv) ch = (char)tolower((unsigned char)ch); expect_continue = lv == "100-continue"; }
+    if (k == "transfer-encoding") { std::string lv = v; for (auto& ch : lv) ch = (char)tolower((unsigned char)ch); chunked = lv.find("chunked") != std::string::npos; }
   }
+  if (clen > kMaxBody) { send_plain(fd, 413, error_response(413, "request body too large").body); return; }
   std::string body = buf.substr(hdr_end + 4);
-  while (body.size() < clen) { ssize_t n = recv(fd, tmp, sizeof tmp, 0); if (n <= 0) break; body.append(tmp, (size_t)n); }
+  if (expect_continue && body.size() < clen) send_all(fd, "HTTP/1.1 100 Continue\r\n\r\n");
+  if (chunked) {
+    // chunked request body: size line (hex, optional extensions), data, CRLF ... until a zero-size chunk
+    std::string raw = std::move(body);
+    body.clear();
+    size_t p = 0;
+    auto need = [&](size_t upto) {
+      while (raw.size() < upto) { ssize_t n = recv(fd, tmp, sizeof tmp, 0); if (n <= 0) return false; raw.append(tmp, (size_t)n); if (raw.size() > kMaxBody + (1 << 20)) return false; }
+      return true;
+    };
+    for (;;) {
+      size_t eol;
+      while ((eol = raw.find("\r\n", p)) == std::string::npos) { if (raw.size() - p > 64 || !need(raw.size() + 1)) { send_plain(fd, 400, error_response(400, "bad chunked body").body); return; } }
+      const std::string sz = raw.substr(p, eol - p);
+      char* endp = nullptr;
+      const unsigned long long n = std::strtoull(sz.c_str(), &endp, 16);
+      if (endp == sz.c_str() || n > kMaxBody || body.size() + n > kMaxBody) { send_plain(fd, endp == sz.c_str() ? 400 : 413, error_response(400, "bad chunked body").body); return; }
+      p = eol + 2;
+      if (n == 0) break;
+      if (!need(p + n + 2)) { send_plain(fd, 400, error_response(400, "truncated chunked body").body); return; }
+      body.append(raw, p, (size_t)n);
+      p += n + 2;
+    }
+  } else {
+    body.reserve(std::min(clen, (size_t)(64u << 20)));
+    while (body.size() < clen) { ssize_t n = recv(fd, tmp, sizeof tmp, 0); if (n <= 0) break; body.append(tmp, (size_t)n); }
+    if (body.size() < clen) { send_plain(fd, 408, error_response(408, "request body incomplete").body); return; }
+    if (body.size() > clen) body.resize(clen);
+  }
   const size_t q = path.find('?');
   if (q != std::string::npos) path.resize(q);
   bool headers_sent = false, alive = true;
@@ -847,14 +904,26 @@ static void serve_connection(Server* sv, int fd) {
     if (n == 0) alive = false;      // orderly shutdown by the client
     return alive;
   };
-  HttpResponse r = route(*sv, method, path, session, body, &em);
+  HttpResponse r;
+  try {
+    r = route(*sv, method, path, session, body, &em);
+  } catch (const std::exception& e) {                 // a handler's bug must not take the process down
+    r = error_response(500, std::string("internal error: ") + e.what(), "InternalServerError");
+  } catch (...) {
+    r = error_response(500, "internal error", "InternalServerError");
+  }
   if (!(r.sse && headers_sent)) {
     std::ostringstream o;
     o << "HTTP/1.1 " << r.status << " " << status_text(r.status) << "\r\nContent-Type: " << r.content_type << "\r\nContent-Length: " << r.body.size() << "\r\nConnection: close\r\n\r\n";
     send_all(fd, o.str() + r.body);
   }
+}
+
+static void serve_connection(Server* sv, int fd) {
+  serve_connection_inner(sv, fd);
   shutdown(fd, SHUT_RDWR);
   close(fd);
+  --g_connections;
 }
 
 }  // namespace b2
@@ -967,7 +1036,15 @@ B2H_API int b2h_server_start(void* sp, const char* host, int port) {
       if (c < 0) { if (sv->stopping) break; continue; }
       int one = 1;
       setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &one, sizeof one);
-      std::thread(serve_connection, sv, c).detach();
+      if (++g_connections > kMaxConnections) {            // shed load instead of piling up threads
+        send_plain(c, 503, error_response(503, "too many connections").body);
+        close(c);
+        --g_connections;
+        continue;
+      }
+      try {
+        std::thread(serve_connection, sv, c).detach();
+      } catch (const std::system_error&) { close(c); --g_connections; }
     }
   });
   return ntohs(a.sin_port);

@@ -233,3 +233,27 @@ def test_png_adam7_interlaced_and_every_filter():
             assert np.array_equal(got, _pil(data)) or depth == 16          # Pillow reads it the same way (16-bit RGB aside)
     with pytest.raises(ValueError):
         V.decode_image(b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", 4, 4, 8, 2, 0, 0, 0)) + chunk(b"IDAT", zlib.compress(b"\0" * 10)) + chunk(b"IEND", b""))
+
+
+def test_oversized_and_expanding_images_are_refused():
+    """Headers that claim more pixels than a request may make the host decode are refused before any buffer is made,
+    and a PNG's compressed stream is inflated only as far as its scanlines can hold."""
+    import struct
+    import zlib
+    from agens_engine_b200.serve import vision as V
+
+    def chunk(kind, body):
+        return struct.pack(">I", len(body)) + kind + body + struct.pack(">I", zlib.crc32(kind + body))
+    bomb = zlib.compress(b"\0" * (64 << 20), 9)                  # 64 MiB of zeros in about 64 KiB
+    png = b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", 4, 4, 8, 2, 0, 0, 0)) + chunk(b"IDAT", bomb) + chunk(b"IEND", b"")
+    img = V.decode_image(png)                                    # only the first rows are inflated; the rest is ignored
+    assert img.shape == (4, 4, 3) and not img.any()
+    huge = b"\x89PNG\r\n\x1a\n" + chunk(b"IHDR", struct.pack(">IIBBBBB", 60000, 60000, 8, 2, 0, 0, 0)) + chunk(b"IDAT", zlib.compress(b"\0")) + chunk(b"IEND", b"")
+    with pytest.raises(ValueError, match="too large"):
+        V.decode_image(huge)
+    gif = b"GIF89a" + struct.pack("<HH", 16000, 16000) + b"\x00\x00\x00" + b"\x3b"
+    with pytest.raises(ValueError, match="too large"):
+        V.decode_image(gif)
+    bmp = b"BM" + struct.pack("<IHHI", 54, 0, 0, 54) + struct.pack("<IiiHHIIiiII", 40, 30000, 30000, 1, 24, 0, 0, 0, 0, 0, 0)
+    with pytest.raises(ValueError):
+        V.decode_image(bmp)

@@ -403,3 +403,70 @@ def test_tokenizer_differential_on_a_trained_bpe():
         want = tok.encode(t, add_special_tokens=False).ids
         assert mine.encode(t) == want, t
         assert mine.decode(want, skip_special=False) == tok.decode(want, skip_special_tokens=False), t
+
+
+def _raw(port, payload: bytes, half_close: bool = False) -> bytes:
+    s = socket.create_connection(("127.0.0.1", port))
+    s.settimeout(20)
+    s.sendall(payload)
+    if half_close:
+        s.shutdown(socket.SHUT_WR)
+    data = b""
+    while True:
+        chunk = s.recv(65536)
+        if not chunk:
+            break
+        data += chunk
+    s.close()
+    return data
+
+
+def test_socket_layer_limits_and_framing(tok_path, tok_text):
+    """The listener's own framing rules: Content-Length must be a plain number within the body limit, a chunked body is
+    reassembled, ``Expect: 100-continue`` is answered before the body is read, a body that ends early is an error, and
+    none of it disturbs the next request."""
+    tk = S.Tokenizer(tok_text)
+    sv = S.Server(tok_path, model_name="m", eos_token_ids=[])
+    sv.use_mock(tk.encode("ok then"), step=2)
+    port = sv.start()
+    try:
+        body = json.dumps({"prompt": "hi", "max_tokens": 3}).encode()
+        head = b"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\n"
+        ok = _raw(port, head + b"Content-Length: %d\r\n\r\n" % len(body) + body)
+        want = json.loads(ok.partition(b"\r\n\r\n")[2])["choices"][0]["text"]
+        assert ok.startswith(b"HTTP/1.1 200") and want
+        # a body limit and a syntax check on the length
+        big = _raw(port, head + b"Content-Length: 99999999999999\r\n\r\n")
+        assert big.startswith(b"HTTP/1.1 413") and json.loads(big.partition(b"\r\n\r\n")[2])["object"] == "error"
+        for bad in (b"-5", b"12abc", b"", b"1" * 30):
+            r = _raw(port, head + b"Content-Length: " + bad + b"\r\n\r\n" + body)
+            assert r.startswith(b"HTTP/1.1 400"), (bad, r[:80])
+        # chunked transfer encoding, with a chunk extension and the pieces cut mid-token
+        cut = [body[:5], body[5:6], body[6:]]
+        chunked = b"".join(b"%x;ext=1\r\n" % len(c) + c + b"\r\n" for c in cut) + b"0\r\n\r\n"
+        r = _raw(port, head + b"Transfer-Encoding: chunked\r\n\r\n" + chunked)
+        assert r.startswith(b"HTTP/1.1 200") and json.loads(r.partition(b"\r\n\r\n")[2])["choices"][0]["text"] == want
+        r = _raw(port, head + b"Transfer-Encoding: chunked\r\n\r\nzz\r\n")
+        assert r.startswith(b"HTTP/1.1 400")
+        # Expect: 100-continue
+        s = socket.create_connection(("127.0.0.1", port))
+        s.settimeout(20)
+        s.sendall(head + b"Expect: 100-continue\r\nContent-Length: %d\r\n\r\n" % len(body))
+        assert s.recv(64).startswith(b"HTTP/1.1 100 Continue")
+        s.sendall(body)
+        data = b""
+        while True:
+            chunk = s.recv(65536)
+            if not chunk:
+                break
+            data += chunk
+        s.close()
+        assert b"200 OK" in data and want.encode() in data
+        # the client goes away in the middle of the body; extra bytes after the body are not part of it
+        r = _raw(port, head + b"Content-Length: %d\r\n\r\n" % (len(body) + 10) + body, half_close=True)
+        assert r.startswith(b"HTTP/1.1 408")
+        r = _raw(port, head + b"Content-Length: %d\r\n\r\n" % len(body) + body + b"GARBAGE")
+        assert r.startswith(b"HTTP/1.1 200")
+        assert _raw(port, b"\r\n\r\n").startswith(b"HTTP/1.1 404") and _raw(port, b"GET /health HTTP/1.1\r\n\r\n").startswith(b"HTTP/1.1 200")
+    finally:
+        sv.stop()
