@@ -310,7 +310,7 @@ class Engine:
             if self.vision is None:
                 raise ValueError("this model does not accept images")
             r.mm = self.vision.prepare(r.prompt, r.images)
-        except (ValueError, RuntimeError) as e:
+        except Exception as e:                            # untrusted bytes: whatever goes wrong ends this request only
             self.stats.rejected += 1
             self.emit(r.rid, [], True, f"image input: {e}")
             return False

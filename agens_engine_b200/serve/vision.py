@@ -162,6 +162,8 @@ def _decode_png(data: bytes) -> np.ndarray:
         n, kind = struct.unpack(">I4s", data[p:p + 8])
         body = data[p + 8:p + 8 + n]
         if kind == b"IHDR":
+            if len(body) < 13:
+                raise ValueError("png: truncated header")
             w, h, depth, ctype, _, _, interlace = struct.unpack(">IIBBBBB", body[:13])
         elif kind == b"PLTE":
             pal = bytes(body[:len(body) // 3 * 3])
