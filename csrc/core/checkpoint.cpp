@@ -74,8 +74,9 @@ static StFile* st_open(const std::string& path, std::string& err) {
       t.begin = kv.second.at("data_offsets")[0].as_int();
       t.end = kv.second.at("data_offsets")[1].as_int();
       long long n = 1;
-      for (auto d : t.shape) n *= d;
-      if (t.begin < 0 || t.end < t.begin || (size_t)t.end > f->size - f->data_off || dtype_size(t.dtype) == 0 ||
+      bool shape_ok = true;                                // no negative extents, no product beyond 63 bits
+      for (auto d : t.shape) shape_ok = shape_ok && d >= 0 && !__builtin_mul_overflow(n, d, &n);
+      if (!shape_ok || n > (1ll << 56) || t.begin < 0 || t.end < t.begin || (size_t)t.end > f->size - f->data_off || dtype_size(t.dtype) == 0 ||
           n * dtype_size(t.dtype) != t.end - t.begin) {
         err = "tensor " + t.name + ": offsets do not match dtype and shape";
         delete f;

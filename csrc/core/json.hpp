@@ -49,7 +49,13 @@ class Json {
   bool is_object() const { return t_ == Object; }
 
   bool as_bool() const { return b_; }
-  long long as_int() const { return t_ == Double ? (long long)d_ : i_; }
+  long long as_int() const {                                  // a double saturates (the plain cast is undefined out of range)
+    if (t_ != Double) return i_;
+    if (!(d_ == d_)) return 0;
+    if (d_ >= 9.2e18) return 9223372036854775807ll;
+    if (d_ <= -9.2e18) return -9223372036854775807ll - 1;
+    return (long long)d_;
+  }
   double as_double() const { return t_ == Int ? (double)i_ : d_; }
   const std::string& as_string() const { return s_; }
   const Arr& items() const { return a_; }
@@ -59,7 +65,10 @@ class Json {
 
   size_t size() const { return t_ == Array ? a_.size() : (t_ == Object ? o_.size() : 0); }
   void push_back(Json v) { a_.push_back(std::move(v)); }
-  const Json& operator[](size_t i) const { return a_[i]; }
+  const Json& operator[](size_t i) const {
+    if (i >= a_.size()) throw std::runtime_error("JSON array index out of range");
+    return a_[i];
+  }
 
   const Json* find(const std::string& k) const {
     if (t_ != Object) return nullptr;

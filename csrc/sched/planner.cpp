@@ -66,6 +66,29 @@ static PlanIn parse_in(const Json& j) {
   p.allow_host_tier = j.get_bool("allow_host_tier", true);
   p.resident_window_pages = (int)j.get_int("resident_window_pages", 0);
   p.split_keys = std::max(16, (int)j.get_int("split_keys", 64));
+  // sizes the arithmetic below divides by or multiplies together
+  auto in_range = [](long long v, long long lo, long long hi, const char* name) {
+    if (v < lo || v > hi) throw std::runtime_error(std::string("plan: ") + name + " out of range");
+  };
+  in_range(p.tp, 1, 64, "tp");
+  in_range(p.page_size, 1, 1 << 16, "page_size");
+  in_range(p.max_batch, 1, 1 << 16, "max_batch");
+  in_range(p.sessions, 0, 1 << 20, "sessions");
+  in_range(p.prefill_chunk, 1, 1 << 22, "prefill_chunk");
+  in_range(p.d_model, 1, 1 << 20, "d_model");
+  in_range(p.ffn, 1, 1 << 24, "ffn");
+  in_range(p.q_dim, 1, 1 << 24, "q_dim");
+  in_range(p.kv_dim, 1, 1 << 24, "kv_dim");
+  in_range(p.vocab, 1, 1 << 26, "vocab");
+  in_range(p.n_heads, 1, 1 << 16, "n_heads");
+  in_range(p.head_dim, 1, 1 << 16, "head_dim");
+  in_range(p.wctx, 1, 1ll << 32, "wctx");
+  in_range(p.weights_bytes, 0, 1ll << 50, "weights_bytes");
+  in_range(p.kv_bytes_per_token, 0, 1ll << 32, "kv_bytes_per_token");
+  in_range(p.resident_window_pages, 0, 1 << 30, "resident_window_pages");
+  for (double g : {p.budget_gib, p.gpu_free_gib, p.headroom_gib, p.host_headroom_gib})
+    if (!(g == g) || g < -1e6 || g > 1e6) throw std::runtime_error("plan: a GiB figure is out of range");
+  if (!(p.host_avail_gib == p.host_avail_gib) || p.host_avail_gib > 1e6) throw std::runtime_error("plan: host_avail_gib out of range");
   return p;
 }
 

@@ -150,3 +150,38 @@ def test_gated_q_proj_is_named_as_such(tmp_path):
     K.write_safetensors(os.path.join(d, "model.safetensors"), t, {"format": "pt"})
     rep = K.validate(d)
     assert not rep["ok"] and any("gated attention" in e for e in rep["errors"])
+
+
+def test_damaged_safetensors_headers_are_refused(tmp_path):
+    """A header whose offsets, shapes or lengths do not describe the file is refused with a message; nothing is read
+    past the mapping (development runs this reader on mutated files under AddressSanitizer)."""
+    import json
+    import struct
+    from agens_engine_b200.utils.checkpoint import SafeTensorsFile
+    good = {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 16]}}
+
+    def write(header, payload=bytes(16), hlen=None):
+        hj = json.dumps(header).encode() if not isinstance(header, bytes) else header
+        p = tmp_path / "x.safetensors"
+        p.write_bytes(struct.pack("<Q", len(hj) if hlen is None else hlen) + hj + payload)
+        return str(p)
+    assert SafeTensorsFile(write(good)).tensor("a").shape == (2, 2)
+    bad = [
+        {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0]}},                       # one offset only
+        {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": []}},
+        {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [0, 32]}},                   # past the end of the file
+        {"a": {"dtype": "F32", "shape": [2, 2], "data_offsets": [-16, 0]}},
+        {"a": {"dtype": "F32", "shape": [-2, -2], "data_offsets": [0, 16]}},                 # negative extents
+        {"a": {"dtype": "F32", "shape": [4611686018427387904, 4, 1], "data_offsets": [0, 16]}},   # product wraps to 4
+        {"a": {"dtype": "F32", "shape": [9223372036854775807, 9223372036854775807], "data_offsets": [0, 16]}},
+        {"a": {"dtype": "F33", "shape": [2, 2], "data_offsets": [0, 16]}},
+        {"a": {"dtype": "F32", "shape": "2x2", "data_offsets": [0, 16]}},
+        {"a": [1, 2, 3]},
+        b"{\"a\": ",
+    ]
+    for h in bad:
+        with pytest.raises(IOError):
+            SafeTensorsFile(write(h))
+    for hlen in (2**63, 2**64 - 1, 10**6):
+        with pytest.raises(IOError):
+            SafeTensorsFile(write(good, hlen=hlen))
