@@ -141,7 +141,7 @@ struct Server {
   std::atomic<long long> next_req{1}, n_requests{0}, n_prompt_tokens{0}, n_completion_tokens{0}, n_errors{0};
   std::mutex extra_mu;
   std::string extra_metrics;               // engine-side gauges (scheduler steps, step times, KV pages), set by the engine
-  int listen_fd = -1;
+  std::atomic<int> listen_fd{-1};
   std::thread accept_thread;
   std::atomic<bool> stopping{false};
 };
@@ -1032,7 +1032,9 @@ B2H_API int b2h_server_start(void* sp, const char* host, int port) {
   sv->stopping = false;
   sv->accept_thread = std::thread([sv]() {
     while (!sv->stopping) {
-      int c = accept(sv->listen_fd, nullptr, nullptr);
+      const int lfd = sv->listen_fd.load();
+      if (lfd < 0) break;
+      int c = accept(lfd, nullptr, nullptr);
       if (c < 0) { if (sv->stopping) break; continue; }
       int one = 1;
       setsockopt(c, IPPROTO_TCP, TCP_NODELAY, &one, sizeof one);
@@ -1052,7 +1054,8 @@ B2H_API int b2h_server_start(void* sp, const char* host, int port) {
 B2H_API void b2h_server_stop(void* sp) {
   auto sv = static_cast<Server*>(sp);
   sv->stopping = true;
-  if (sv->listen_fd >= 0) { shutdown(sv->listen_fd, SHUT_RDWR); close(sv->listen_fd); sv->listen_fd = -1; }
+  const int lfd = sv->listen_fd.exchange(-1);
+  if (lfd >= 0) { shutdown(lfd, SHUT_RDWR); close(lfd); }
   if (sv->accept_thread.joinable()) sv->accept_thread.join();
 }
 

@@ -65,25 +65,27 @@ static bool is_letter_cp(unsigned c) {
 }
 
 // GPT-2 byte <-> printable code point tables
-static const unsigned* byte_to_cp() {
-  static unsigned tab[256];
-  static bool init = false;
-  if (!init) {
+// Both tables are built once by the initialiser of a function-local static (thread safe: requests reach them from
+// many connection threads at once).
+struct ByteTables {
+  unsigned to_cp[256];
+  int to_byte[512];                                       // code points used by the mapping are below 256 + 68
+  ByteTables() {
     int n = 0;
+    for (int& v : to_byte) v = -1;
     for (int b = 0; b < 256; ++b) {
       const bool keep = (b >= '!' && b <= '~') || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF);
-      tab[b] = keep ? (unsigned)b : 256u + (unsigned)(n++);
+      to_cp[b] = keep ? (unsigned)b : 256u + (unsigned)(n++);
+      to_byte[to_cp[b]] = b;
     }
-    init = true;
   }
-  return tab;
+};
+static const ByteTables& byte_tables() {
+  static const ByteTables t;
+  return t;
 }
-static int cp_to_byte(unsigned cp) {
-  static std::unordered_map<unsigned, int> inv;
-  if (inv.empty()) { const unsigned* t = byte_to_cp(); for (int b = 0; b < 256; ++b) inv[t[b]] = b; }
-  auto it = inv.find(cp);
-  return it == inv.end() ? -1 : it->second;
-}
+static const unsigned* byte_to_cp() { return byte_tables().to_cp; }
+static int cp_to_byte(unsigned cp) { return cp < 512 ? byte_tables().to_byte[cp] : -1; }
 
 // ------------------------------------------------------------------------------------------------ tokenizer
 Tokenizer Tokenizer::from_json(const std::string& text) {

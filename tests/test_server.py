@@ -470,3 +470,27 @@ def test_socket_layer_limits_and_framing(tok_path, tok_text):
         assert _raw(port, b"\r\n\r\n").startswith(b"HTTP/1.1 404") and _raw(port, b"GET /health HTTP/1.1\r\n\r\n").startswith(b"HTTP/1.1 200")
     finally:
         sv.stop()
+
+
+def test_first_requests_of_a_process_may_arrive_together(tok_text, tmp_path):
+    """The tokenizer's byte tables are built on first use; many threads may be the first at once (connection threads
+    of the listener).  Fresh processes, sixteen threads released together, every decode checked."""
+    import subprocess
+    import sys
+    (tmp_path / "tok.json").write_text(tok_text)
+    prog = (
+        "import sys, threading\n"
+        "from agens_engine_b200.serve import server as S\n"
+        "tk = S.Tokenizer(open(sys.argv[1]).read())\n"
+        "ids = list(range(40, 256)) * 4\n"
+        "go, out = threading.Barrier(16), [None] * 16\n"
+        "def run(i):\n"
+        "    go.wait()\n"
+        "    out[i] = (tk.decode(ids, skip_special=False), tk.encode('héllo wörld ✓ ' * 20))\n"
+        "th = [threading.Thread(target=run, args=(i,)) for i in range(16)]\n"
+        "[t.start() for t in th]; [t.join() for t in th]\n"
+        "assert all(o == out[0] for o in out) and out[0][0] and tk.decode(out[0][1], skip_special=False) == 'héllo wörld ✓ ' * 20\n"
+        "print('same')\n")
+    for _ in range(3):
+        r = subprocess.run([sys.executable, "-c", prog, str(tmp_path / "tok.json")], capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0 and r.stdout.strip() == "same", r.stderr[-2000:]
