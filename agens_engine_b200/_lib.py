@@ -50,6 +50,10 @@ def host_lib() -> C.CDLL:
     """Host-only library (no CUDA dependency) for CPU tests of the runtime, scheduler and server code."""
     global _host
     if _host is None:
+        override = os.environ.get("B200E_HOST_LIB", "")       # a sanitizer build of the host sources (tools/sanitize.py)
+        if override:
+            _host = C.CDLL(override)
+            return _host
         _ensure_built()
         path = _LIBDIR / "libagens_b200_host.so"
         if not path.exists():
