@@ -357,7 +357,9 @@ class Engine:
             if r.parked is not None:                     # preempted earlier: bring its KV rows back and go on decoding
                 try:
                     self.m.unpark(r.slot, r.parked)
-                except RuntimeError:                     # no room after all: give the slot back and wait in line
+                except RuntimeError as e:                     # no room after all: give the slot back and wait in line
+                    if getattr(e, "fatal", False):         # nothing to recover to (a follower is gone): the run loop ends
+                        raise
                     if r.slot in self.m.seq_pages:
                         self.m.free_seq(r.slot)
                     self.spec.samp.pop(r.slot, None)
@@ -458,7 +460,9 @@ class Engine:
                 if k["slot"] is None:
                     try:
                         self.m.unpark(r.slot, k["parked"])
-                    except RuntimeError:                               # pool exhausted: start this turn from scratch
+                    except RuntimeError as e:                               # pool exhausted: start this turn from scratch
+                        if getattr(e, "fatal", False):         # nothing to recover to (a follower is gone): the run loop ends
+                            raise
                         if r.slot in self.m.seq_pages:
                             self.m.free_seq(r.slot)
                         return False
@@ -478,7 +482,9 @@ class Engine:
         n = min(n, len(k["tokens"])) // page * page
         try:
             self.m.fork(k["slot"], r.slot)
-        except RuntimeError:
+        except RuntimeError as e:
+            if getattr(e, "fatal", False):         # nothing to recover to (a follower is gone): the run loop ends
+                raise
             return False
         self.m.truncate(r.slot, n)
         k["t_last"] = time.monotonic()
@@ -556,6 +562,8 @@ class Engine:
         try:
             res = self._with_room(r, lambda: self.m.prefill(r.slot, chunk, want_logits=final and sampled, **kw))
         except RuntimeError as e:
+            if getattr(e, "fatal", False):         # nothing to recover to (a follower is gone): the run loop ends
+                raise
             r.mtp_sinks = None
             self._finish(r, error=str(e)); return
         finally:
@@ -633,6 +641,8 @@ class Engine:
         try:
             res = self._with_room(fast[0], lambda: self.spec.step([s for s in slots if s in self.active and self.active[s].state == DECODE]))
         except RuntimeError as e:
+            if getattr(e, "fatal", False):         # nothing to recover to (a follower is gone): the run loop ends
+                raise
             for r in fast:
                 self._finish(r, error=str(e))
             return
@@ -658,6 +668,8 @@ class Engine:
         try:
             _, logits = self._with_room(rows[0], run)
         except RuntimeError as e:
+            if getattr(e, "fatal", False):         # nothing to recover to (a follower is gone): the run loop ends
+                raise
             for r in rows:
                 if self.active.get(r.slot) is r:
                     self._finish(r, error=str(e))

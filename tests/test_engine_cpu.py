@@ -250,3 +250,71 @@ def test_engine_thread_behind_the_http_front_end(tmp_path):
     finally:
         eng.stop()
     assert not m.tokens
+
+
+def test_a_failed_step_ends_open_requests_and_the_engine_keeps_serving():
+    """A step that raises (a device error status, a bounds check) ends every running request with an error, the model is
+    put back into a clean state and the engine thread keeps serving: later requests get exact tokens.  A failure marked
+    fatal (a tensor-parallel follower is gone) ends the engine instead, and waiting requests are told."""
+    import time
+
+    class Flaky(FakeModel):
+        fail_at, fatal = -1, False
+
+        def forward_rows(self, ids, seqs, want_logits=False):
+            if self.calls == self.fail_at:
+                self.fail_at = -1
+                e = (RuntimeError if self.fatal else ValueError)("the step went wrong")
+                e.fatal = self.fatal
+                raise e
+            return super().forward_rows(ids, seqs, want_logits)
+
+        def device_status(self):
+            st, self.status_once = getattr(self, "status_once", 0), 0
+            return st
+
+        def recover(self):
+            for s in list(self.tokens):
+                self.free_seq(s)
+
+    got, done = {}, {}
+
+    def emit(rid, toks, finished, err):
+        got.setdefault(rid, []).extend(toks)
+        if finished:
+            done[rid] = err
+        return False
+    m = Flaky(max_seqs=4, max_ctx=256)
+    eng = Engine(m, emit)
+    eng.start()
+    try:
+        prompts = _prompts(6, lo=10, hi=40, seed=3)
+        m.fail_at = 12                                             # somewhere in the decode steps of the first batch
+        first = [eng.submit(p, {"max_new_tokens": 30}) for p in prompts[:3]]
+        t0 = time.time()
+        while len(done) < 3 and time.time() - t0 < 30:
+            time.sleep(0.01)
+        assert all(done.get(r) and "engine step failed" in done[r] for r in first), done
+        assert not m.tokens and m.free_pages() == m.n_pages
+        later = [eng.submit(p, {"max_new_tokens": 12}) for p in prompts[3:]]
+        t0 = time.time()
+        while len(done) < 6 and time.time() - t0 < 30:
+            time.sleep(0.01)
+        assert [got[r] for r in later] == [_alone(p, 12) for p in prompts[3:]] and all(done[r] is None for r in later)
+        # a device status word (a bounded wait that ran out) is found after the step: same recovery
+        m.status_once = 3
+        more = [eng.submit(p, {"max_new_tokens": 8}) for p in prompts[:2]]
+        t0 = time.time()
+        while len(done) < 8 and time.time() - t0 < 30:
+            time.sleep(0.01)
+        assert any("device reported" in (done.get(r) or "") for r in more) and not m.tokens, done
+        done.pop(more[0]); done.pop(more[1])
+        # a fatal failure: the engine thread ends, open and waiting requests are told why
+        m.fail_at, m.fatal = m.calls + 3, True
+        last = [eng.submit(p, {"max_new_tokens": 30}) for p in prompts[:5]]
+        t0 = time.time()
+        while len(done) < 11 and time.time() - t0 < 30:
+            time.sleep(0.01)
+        assert eng.fatal is not None and all("engine stopped" in (done.get(r) or "") for r in last), done
+    finally:
+        eng.stop()
