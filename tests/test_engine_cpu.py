@@ -318,3 +318,71 @@ def test_a_failed_step_ends_open_requests_and_the_engine_keeps_serving():
         assert eng.fatal is not None and all("engine stopped" in (done.get(r) or "") for r in last), done
     finally:
         eng.stop()
+
+
+def test_random_workloads_keep_every_request_exact_and_leak_nothing():
+    """Seeded random deployments: pool sizes from ample to tight, batch widths, draft sources that are right, wrong or
+    copied, stop ids, clients that go away, kept conversations.  Every request that ends without an error has exactly
+    the tokens of a run alone (up to its stop or limit), and when the engine is idle no page or slot is held."""
+    import random
+    seen = {"evictions": 0, "accepted": 0, "rejected_drafts": 0, "left": 0, "errors": 0}
+    for seed in range(40):
+        rng = random.Random(seed)
+        max_seqs = rng.choice([2, 3, 4, 6])
+        max_ctx = rng.choice([128, 256])
+        page = rng.choice([8, 16])
+        full = max_seqs * ((max_ctx + page - 1) // page)
+        n_pages = rng.choice([full, full // 2, max(full // 3, (max_ctx + page - 1) // page + 2)])
+        m = FakeModel(max_seqs=max_seqs, max_ctx=max_ctx, n_pages=n_pages, page=page, chunk=rng.choice([16, 32, 64]))
+        kw = {}
+        mode = rng.choice(["plain", "good", "bad", "copy"])
+        if mode != "plain":
+            d = FakeModel(max_seqs=max_seqs, max_ctx=max_ctx, page=page)
+            if mode == "bad":
+                d.forward_rows = lambda ids, seqs, want_logits=False, f=d.forward_rows: ((f(ids, seqs)[0] + (torch.arange(len(ids)) % 3 == 1)).to(torch.int32), None)
+            srcs = [CopyLookupSource()] if mode == "copy" else [CopyLookupSource(), ModelSource(d, rng.choice([2, 3]))]
+            kw = dict(sources_factory=lambda srcs=srcs: srcs, max_drafts=rng.choice([2, 3]))
+        keep = rng.random() < 0.4
+        got, done, gone = {}, {}, {}
+
+        def emit(rid, toks, finished, err):
+            got.setdefault(rid, []).extend(toks)
+            if finished:
+                done[rid] = err
+            return rid in gone and len(got[rid]) >= gone[rid]          # True: the client went away
+        eng = Engine(m, emit, keep_sequences=keep, max_batch=rng.choice([2, 4, 8]), **kw)
+        reqs = {}
+        for wave in range(3):
+            for _ in range(rng.randint(1, 5)):
+                base = [rng.randrange(500) for _ in range(rng.randint(3, 12))]
+                prompt = (base * rng.randint(1, 6))[:max_ctx - 40] if rng.random() < 0.5 else [rng.randrange(500) for _ in range(rng.randint(4, max_ctx - 60))]
+                n_new = rng.randint(1, 30)
+                samp = {"max_new_tokens": n_new}
+                alone = _alone(prompt, n_new)
+                stop = None
+                if rng.random() < 0.3 and len(alone) > 2:
+                    stop = alone[rng.randrange(1, len(alone))]
+                    samp["stop_token_ids"] = [stop]
+                rid = eng.submit(prompt, samp, session=f"s{rng.randrange(3)}" if keep and rng.random() < 0.5 else "")
+                if rng.random() < 0.15:
+                    gone[rid] = rng.randint(1, max(1, n_new // 2))
+                want = alone if stop is None else alone[:alone.index(stop) + 1]
+                reqs[rid] = want
+            for _ in range(rng.randint(0, 40)):
+                eng.step()
+        eng.run_until_idle(50000)
+        assert eng.idle(), seed
+        for rid, want in reqs.items():
+            assert rid in done or rid in gone, (seed, rid)              # nobody is told about a request whose client left
+            if rid in done and done[rid] is None and rid not in gone:
+                assert got.get(rid, []) == want, (seed, rid, mode)
+            else:
+                assert got.get(rid, []) == want[:len(got.get(rid, []))], (seed, rid, mode)
+        if not keep:
+            assert not m.tokens and m.free_pages() == m.n_pages, seed
+        seen["evictions"] += eng.stats.evictions
+        seen["accepted"] += eng.spec.stats.accepted
+        seen["rejected_drafts"] += eng.spec.stats.proposed - eng.spec.stats.accepted
+        seen["left"] += len(gone)
+        seen["errors"] += sum(1 for e in done.values() if e)
+    assert seen["evictions"] > 0 and seen["accepted"] > 0 and seen["rejected_drafts"] > 0 and seen["left"] > 0, seen
