@@ -169,7 +169,7 @@ class PageAllocator:
     def pages(self, s: int) -> List[int]:
         buf = (C.c_int * 65536)()
         n = lib().b2h_pages_list(self._h, s, buf, 65536)
-        return list(buf[:n])
+        return list(buf[:max(n, 0)])
 
 
 def kv_safe(avail: int, items: Sequence[Tuple[int, int]]) -> bool:

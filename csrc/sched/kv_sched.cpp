@@ -332,22 +332,31 @@ using namespace b2;
 // ---- C ABI ----
 B2H_API void* b2h_pages_new(int n_pages, int page_size) { return new PageAllocator(n_pages, page_size); }
 B2H_API void b2h_pages_free(void* a) { delete static_cast<PageAllocator*>(a); }
+// An unknown sequence id or page index is the caller's bug; it comes back as kBadId (-1000) instead of an exception
+// crossing the C boundary (which would end the process).
+static constexpr int kBadId = -1000;
+#define B2H_GUARD(expr) try { return (expr); } catch (const std::exception&) { return kBadId; }
 B2H_API int b2h_pages_free_count(void* a) { return static_cast<PageAllocator*>(a)->free_pages(); }
 B2H_API int b2h_pages_new_seq(void* a) { return static_cast<PageAllocator*>(a)->new_seq(); }
-B2H_API int b2h_pages_reserve(void* a, int s, int n_tokens) { return static_cast<PageAllocator*>(a)->reserve(s, n_tokens); }
-B2H_API void b2h_pages_set_len(void* a, int s, int n) { static_cast<PageAllocator*>(a)->set_len(s, n); }
-B2H_API int b2h_pages_len(void* a, int s) { return static_cast<PageAllocator*>(a)->seq_len(s); }
-B2H_API int b2h_pages_truncate(void* a, int s, int n) { return static_cast<PageAllocator*>(a)->truncate(s, n); }
-B2H_API int b2h_pages_evict_page(void* a, int s, int index) { return static_cast<PageAllocator*>(a)->evict_page(s, index); }
-B2H_API int b2h_pages_fork(void* a, int s, int* src, int* dst) { return static_cast<PageAllocator*>(a)->fork(s, src, dst); }
+B2H_API int b2h_pages_reserve(void* a, int s, int n_tokens) { B2H_GUARD(static_cast<PageAllocator*>(a)->reserve(s, n_tokens)) }
+B2H_API void b2h_pages_set_len(void* a, int s, int n) { try { static_cast<PageAllocator*>(a)->set_len(s, n); } catch (const std::exception&) {} }
+B2H_API int b2h_pages_len(void* a, int s) { B2H_GUARD(static_cast<PageAllocator*>(a)->seq_len(s)) }
+B2H_API int b2h_pages_truncate(void* a, int s, int n) { B2H_GUARD(static_cast<PageAllocator*>(a)->truncate(s, n)) }
+B2H_API int b2h_pages_evict_page(void* a, int s, int index) { B2H_GUARD(static_cast<PageAllocator*>(a)->evict_page(s, index)) }
+B2H_API int b2h_pages_fork(void* a, int s, int* src, int* dst) { B2H_GUARD(static_cast<PageAllocator*>(a)->fork(s, src, dst)) }
 B2H_API int b2h_pages_free_seq(void* a, int s) { return static_cast<PageAllocator*>(a)->free_seq(s); }
-B2H_API int b2h_pages_exclusive(void* a, int s) { return static_cast<PageAllocator*>(a)->exclusive_pages(s); }
-B2H_API int b2h_pages_refcount(void* a, int page) { return static_cast<PageAllocator*>(a)->refcount(page); }
+B2H_API int b2h_pages_exclusive(void* a, int s) { B2H_GUARD(static_cast<PageAllocator*>(a)->exclusive_pages(s)) }
+B2H_API int b2h_pages_refcount(void* a, int page) {
+  auto al = static_cast<PageAllocator*>(a);
+  return page >= 0 && page < al->n_pages() ? al->refcount(page) : kBadId;
+}
 B2H_API int b2h_pages_list(void* a, int s, int* out, int cap) {
-  const auto& p = static_cast<PageAllocator*>(a)->pages(s);
-  const int n = std::min<int>((int)p.size(), cap);
-  std::memcpy(out, p.data(), sizeof(int) * n);
-  return (int)p.size();
+  try {
+    const auto& p = static_cast<PageAllocator*>(a)->pages(s);
+    const int n = std::min<int>((int)p.size(), cap);
+    std::memcpy(out, p.data(), sizeof(int) * n);
+    return (int)p.size();
+  } catch (const std::exception&) { return kBadId; }
 }
 
 B2H_API int b2h_kv_safe(long avail, const long* need, const long* hold, int n) {

@@ -164,3 +164,77 @@ def test_planner_gpu_and_host_tier_and_profiles():
     assert pr["flags"]["budget_gib"] == 16 and pr["flags"]["wctx"] == 262148 and pr["flags"]["mode"] == "personal"
     assert H.profile("48gb", 8)["flags"]["tp"] == 8
     assert "error" in H.profile("16gb", 3) and "error" in H.profile("nope")
+
+
+def test_page_allocator_against_a_model_under_random_operations():
+    """Reserve / truncate / fork / free / evict in seeded random order against a plain Python restatement: the same page
+    counts, reference counts that equal the number of holders, free + held = total at every step; unknown ids come back
+    as an error code instead of ending the process."""
+    import random
+    for seed in range(20):
+        rng = random.Random(seed)
+        n_pages, page = rng.choice([8, 24, 64]), rng.choice([4, 16])
+        a = H.PageAllocator(n_pages, page)
+        model = {}                                             # id -> [pages (or -2), len]
+        for _ in range(400):
+            op = rng.random()
+            ids = list(model)
+            if op < 0.2 or not ids:
+                s = a.new_seq()
+                assert s not in model
+                model[s] = [[], 0]
+            elif op < 0.5:
+                s = rng.choice(ids)
+                n = rng.randint(0, page * 10)
+                need = max(0, (n + page - 1) // page - len(model[s][0]))
+                got = a.reserve(s, n)
+                if need > a_free(model, n_pages):
+                    assert got == -1
+                else:
+                    assert got == need
+                    model[s][0] = a.pages(s)
+                    if n > model[s][1] and got >= 0:
+                        model[s][1] = min(n, len(model[s][0]) * page)
+                        a.set_len(s, model[s][1])
+            elif op < 0.65:
+                s = rng.choice(ids)
+                n = rng.randint(0, max(model[s][1], 1))
+                a.truncate(s, n)
+                model[s][1] = min(model[s][1], n)
+                del model[s][0][(n + page - 1) // page:]
+            elif op < 0.8:
+                s = rng.choice(ids)
+                c, src, dst = a.fork(s)
+                partial = model[s][1] % page != 0
+                if any(p < 0 for p in model[s][0]) or (partial and a_free(model, n_pages) == 0):
+                    assert c == -1
+                else:
+                    assert c >= 0 and (src >= 0) == partial
+                    model[c] = [a.pages(c), model[s][1]]
+                    used = (model[s][1] + page - 1) // page
+                    assert len(model[c][0]) == used and model[c][0][:used - (1 if partial else 0)] == model[s][0][:used - (1 if partial else 0)]
+            elif op < 0.9:
+                s = rng.choice(ids)
+                a.free_seq(s)
+                del model[s]
+            else:
+                s = rng.choice(ids)
+                if model[s][0]:
+                    i = rng.randrange(len(model[s][0]))
+                    a.evict_page(s, i)
+                    model[s][0][i] = -2
+            # invariants
+            held = {}
+            for s, (pages, n) in model.items():
+                assert a.pages(s) == pages and a.seq_len(s) == n, (seed, s)
+                for p in pages:
+                    if p >= 0:
+                        held[p] = held.get(p, 0) + 1
+            assert a.free_pages == n_pages - len(held)
+            assert all(a.refcount(p) == c for p, c in held.items())
+        assert a.reserve(10**6, 5) == -1000 and a.seq_len(10**6) == -1000 and a.refcount(-1) == -1000 and a.pages(10**6) == []
+        assert a.fork(10**6)[0] == -1000 and a.truncate(10**6, 0) == -1000 and a.free_seq(10**6) == 0
+
+
+def a_free(model, n_pages):
+    return n_pages - len({p for pages, _ in model.values() for p in pages if p >= 0})
