@@ -82,11 +82,24 @@ static std::vector<Tok> lex_expr(const std::string& src) {
   return out;
 }
 
+// Recursion limits: a template is configuration, but one that nests without end must be refused, not overflow the stack.
+constexpr int kMaxExprDepth = 600;       // three counted frames per level: about 200 nested parentheses, literals or unary operators
+constexpr int kMaxExprTokens = 20000;    // bounds the length of an operator chain (its tree is as deep as it is long)
+constexpr int kMaxBlockDepth = 200;      // nested if / for / macro / set blocks
+constexpr int kMaxEvalDepth = 1000;      // expression evaluation (an operator chain evaluates through its left spine)
+constexpr int kMaxMacroDepth = 100;      // macro calls in flight
+struct DepthGuard {
+  int& d;
+  DepthGuard(int& depth, int limit, const char* what) : d(depth) { if (++d > limit) { --d; throw Error(std::string(what) + " nested too deeply"); } }
+  ~DepthGuard() { --d; }
+};
+
 class ExprParser {
  public:
-  explicit ExprParser(std::vector<Tok> t) : t_(std::move(t)) {}
+  explicit ExprParser(std::vector<Tok> t) : t_(std::move(t)) { if (t_.size() > (size_t)kMaxExprTokens) throw Error("expression too long"); }
   ExprP parse_full() { ExprP e = parse_cond(); if (cur().t != Tok::End) throw Error("unexpected '" + cur().s + "' in expression"); return e; }
   ExprP parse_cond() {
+    DepthGuard g(depth_, kMaxExprDepth, "expression");
     ExprP e = parse_or();
     while (is_id("if")) {
       ++p_;
@@ -107,11 +120,13 @@ class ExprParser {
 
  private:
   std::vector<Tok> t_;
+  int depth_ = 0;
   static ExprP mk(Expr::Kind k) { auto e = std::make_shared<Expr>(); e->kind = k; return e; }
   static ExprP bin(const std::string& op, ExprP a, ExprP b) { auto e = mk(Expr::Bin); e->name = op; e->a = a; e->b = b; return e; }
   ExprP parse_or() { ExprP e = parse_and(); while (is_id("or")) { ++p_; e = bin("or", e, parse_and()); } return e; }
   ExprP parse_and() { ExprP e = parse_not(); while (is_id("and")) { ++p_; e = bin("and", e, parse_not()); } return e; }
   ExprP parse_not() {
+    DepthGuard g(depth_, kMaxExprDepth, "expression");
     if (is_id("not")) { ++p_; auto e = mk(Expr::Not); e->a = parse_not(); return e; }
     return parse_cmp();
   }
@@ -137,6 +152,7 @@ class ExprParser {
     return e;
   }
   ExprP parse_unary() {
+    DepthGuard g(depth_, kMaxExprDepth, "expression");
     if (is_op("-")) { ++p_; auto e = mk(Expr::Neg); e->a = parse_unary(); return e; }
     if (is_op("+")) { ++p_; return parse_unary(); }
     return parse_postfix(parse_primary());
@@ -322,10 +338,12 @@ class TemplateParser {
  private:
   std::vector<Piece> p_;
   size_t i_ = 0;
+  int depth_ = 0;
   static ExprP expr_of(const std::string& s) { return ExprParser(lex_expr(s)).parse_full(); }
 
   // Parses until one of the `stops` keywords opens a statement; *stop receives that statement's text.
   Body parse_body(const std::vector<std::string>& stops, std::string* stop) {
+    DepthGuard g(depth_, kMaxBlockDepth, "blocks");
     Body body;
     while (i_ < p_.size()) {
       const Piece& pc = p_[i_++];
@@ -596,6 +614,7 @@ class Interp {
  private:
   std::vector<std::map<std::string, Val>> scopes_;
   std::map<std::string, NodeP> macros_;
+  int eval_depth_ = 0, macro_depth_ = 0;
 
   Val lookup(const std::string& name) const {
     for (size_t i = scopes_.size(); i-- > 0;) { auto it = scopes_[i].find(name); if (it != scopes_[i].end()) return it->second; }
@@ -696,6 +715,7 @@ class Interp {
   static long long norm_index(long long i, long long n) { return i < 0 ? i + n : i; }
 
   Val eval(const ExprP& ep) {
+    DepthGuard g(eval_depth_, kMaxEvalDepth, "expression evaluation");
     const Expr& e = *ep;
     switch (e.kind) {
       case Expr::Lit: return Val(e.lit);
@@ -1000,6 +1020,7 @@ class Interp {
     const std::string& fn = callee.name;
     if (auto it = macros_.find(fn); it != macros_.end()) {
       const Node& mc = *it->second;
+      DepthGuard g(macro_depth_, kMaxMacroDepth, "macro calls");
       std::vector<Val> a = eval_args(e);
       std::map<std::string, Val> frame;
       for (size_t i = 0; i < mc.params.size(); ++i) {

@@ -236,3 +236,33 @@ def test_server_renders_chat_requests_with_the_checkpoint_template(tmp_path):
     sv2 = S.Server(str(tok), model_name="m", chat_template="{{ raise_exception('no system role') }}")
     status, resp = sv2.handle("POST", "/v1/chat/completions", {"messages": msgs[:2]})
     assert status == 400 and "no system role" in resp
+
+
+def test_templates_that_nest_without_end_are_refused_not_crashed():
+    """Parentheses, unary chains, blocks, operator chains and macro recursion beyond the interpreter's limits raise an
+    error (in a fresh process: before the limits these overflowed the stack)."""
+    import subprocess
+    import sys
+    prog = (
+        "from agens_engine_b200.serve import server as S\n"
+        "cases = ['{{ ' + '(' * 5000 + '1' + ')' * 5000 + ' }}', '{{ ' + '(' * 100000 + '1' + ')' * 100000 + ' }}',\n"
+        "         '{{ ' + 'not ' * 5000 + 'true }}', '{{ ' + '-' * 5000 + '1 }}', '{{ ' + '[' * 5000 + ']' * 5000 + ' }}',\n"
+        "         '{% if true %}' * 50000 + 'x' + '{% endif %}' * 50000, '{% for a in [1] %}' * 3000 + 'x' + '{% endfor %}' * 3000,\n"
+        "         '{{ ' + ' + '.join(['1'] * 9990) + ' }}', '{{ ' + ' ~ '.join([\"'a'\"] * 9990) + ' }}',\n"
+        "         '{% macro f(n) %}{{ f(n + 1) }}{% endmacro %}{{ f(0) }}',\n"
+        "         '{{ 1 if ' * 3000 + 'true' + ' else 2 }}' * 0 + '{{ ' + 'a if b else ' * 3000 + 'c }}']\n"
+        "bad = 0\n"
+        "for c in cases:\n"
+        "    try:\n"
+        "        S.render_template(c, a=1, b=0, c=2)\n"
+        "    except ValueError:\n"
+        "        bad += 1\n"
+        "deep = 1\n"
+        "for _ in range(150):\n"
+        "    deep = [deep]\n"
+        "assert S.render_template('{{ v | tojson }}{{ v }}', v=deep).count('[') == 300\n"
+        "assert S.render_template('{{ ' + ' + '.join(['1'] * 500) + ' }}') == '500'\n"
+        "assert S.render_template('{{ ' + '(' * 100 + '7' + ')' * 100 + ' }}') == '7'\n"
+        "print('refused', bad, 'of', len(cases))\n")
+    r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip() == "refused 11 of 11", (r.returncode, r.stdout, r.stderr[-1500:])
