@@ -14,6 +14,7 @@
 #include <algorithm>
 #include <climits>
 #include <cstring>
+#include <queue>
 
 namespace b2 {
 
@@ -182,15 +183,39 @@ void Tokenizer::bpe(const std::string& piece, std::vector<int>& out) const {
   std::vector<std::string> sym;
   const unsigned* b2c = byte_to_cp();
   for (unsigned char c : piece) { std::string s; append_cp(s, b2c[c]); sym.push_back(s); }
-  while (sym.size() > 1) {
-    int best = INT_MAX; size_t at = 0;
-    for (size_t k = 0; k + 1 < sym.size(); ++k) {
-      auto it = merge_rank_.find(sym[k] + " " + sym[k + 1]);
-      if (it != merge_rank_.end() && it->second < best) { best = it->second; at = k; }
+  // Lowest-ranked pair first, the leftmost one among equals: a heap of candidate pairs over a linked list of symbols
+  // (n log n; a scan per merge took minutes on a hundred thousand spaces).  A popped candidate is stale when either
+  // symbol has been merged since it was pushed, which its recorded lengths show.
+  const int n = (int)sym.size();
+  if (n > 1) {
+    std::vector<int> prev(n), next(n);
+    std::vector<char> alive(n, 1);
+    for (int k = 0; k < n; ++k) { prev[k] = k - 1; next[k] = k + 1 < n ? k + 1 : -1; }
+    struct Cand { int rank, left, right; size_t ll, rl; };
+    auto later = [](const Cand& a, const Cand& b) { return a.rank != b.rank ? a.rank > b.rank : a.left > b.left; };
+    std::priority_queue<Cand, std::vector<Cand>, decltype(later)> heap(later);
+    std::string key;
+    auto push = [&](int l, int r) {
+      if (l < 0 || r < 0) return;
+      key.assign(sym[l]); key.push_back(' '); key.append(sym[r]);
+      auto it = merge_rank_.find(key);
+      if (it != merge_rank_.end()) heap.push(Cand{it->second, l, r, sym[l].size(), sym[r].size()});
+    };
+    for (int k = 0; k + 1 < n; ++k) push(k, k + 1);
+    while (!heap.empty()) {
+      const Cand c = heap.top();
+      heap.pop();
+      if (!alive[c.left] || !alive[c.right] || next[c.left] != c.right || sym[c.left].size() != c.ll || sym[c.right].size() != c.rl) continue;
+      sym[c.left] += sym[c.right];
+      alive[c.right] = 0;
+      next[c.left] = next[c.right];
+      if (next[c.right] >= 0) prev[next[c.right]] = c.left;
+      push(prev[c.left], c.left);
+      push(c.left, next[c.left]);
     }
-    if (best == INT_MAX) break;
-    sym[at] += sym[at + 1];
-    sym.erase(sym.begin() + at + 1);
+    std::vector<std::string> merged;
+    for (int k = 0; k >= 0; k = next[k]) merged.push_back(std::move(sym[k]));
+    sym.swap(merged);
   }
   for (auto& s : sym) {
     auto it = vocab_.find(s);
@@ -512,7 +537,10 @@ struct PyLit {
   explicit PyLit(const std::string& t) : s(t) {}
   void ws() { while (i < s.size() && std::isspace((unsigned char)s[i])) ++i; }
   [[noreturn]] void bad() { throw std::runtime_error("not a Python literal"); }
+  int depth = 0;                                          // as deep as the JSON parser goes; model output decides the text
+  struct Level { int& d; explicit Level(int& x) : d(x) { if (++d > 200) { --d; throw std::runtime_error("literal nested too deeply"); } } ~Level() { --d; } };
   Json value() {
+    Level lv(depth);
     ws();
     if (i >= s.size()) bad();
     const char c = s[i];

@@ -494,3 +494,31 @@ def test_first_requests_of_a_process_may_arrive_together(tok_text, tmp_path):
     for _ in range(3):
         r = subprocess.run([sys.executable, "-c", prog, str(tmp_path / "tok.json")], capture_output=True, text=True, timeout=120)
         assert r.returncode == 0 and r.stdout.strip() == "same", r.stderr[-2000:]
+
+
+def test_long_unbroken_runs_tokenize_in_linear_time_and_like_the_library(tok_text):
+    """A hundred thousand spaces, or one word repeated without a break, is one pre-token; its merges must not cost a
+    scan each (that took minutes).  Same ids as the tokenizers library, within seconds."""
+    import time
+    tokenizers = pytest.importorskip("tokenizers")
+    ref = tokenizers.Tokenizer.from_str(tok_text)
+    mine = S.Tokenizer(tok_text)
+    t0 = time.time()
+    for text in (" " * 100000, "the" * 33000, "ab" * 20000 + " " + "thing" * 9000, "\n" * 50000, "aaaa" * 10000 + "é" * 5000):
+        ids = mine.encode(text)
+        assert ids == ref.encode(text, add_special_tokens=False).ids, text[:12]
+    assert time.time() - t0 < 30
+
+
+def test_deeply_nested_tool_arguments_fall_back_to_text():
+    """Model output decides how deep a parameter's literal nests: beyond the parser's depth the value is kept as text
+    (a hundred thousand brackets used to overflow the stack)."""
+    tools = [{"type": "function", "function": {"name": "f", "parameters": {"type": "object", "properties": {"a": {"type": "array"}, "o": {"type": "object"}}}}}]
+    for lit, key in (("[" * 100000 + "]" * 100000, "a"), ("{'k': " * 100000 + "1" + "}" * 100000, "o"), ("(" * 100000 + "1," + ")" * 100000, "a")):
+        out = S.parse_output(f"<tool_call>\n<function=f>\n<parameter={key}>\n{lit}\n</parameter>\n</function>\n</tool_call>", tools)
+        assert json.loads(out["tool_calls"][0]["arguments"])[key] == lit
+    out = S.parse_output("<tool_call>\n<function=f>\n<parameter=a>\n" + "[" * 40 + "(1, 'x')" + "]" * 40 + "\n</parameter>\n</function>\n</tool_call>", tools)
+    v = json.loads(out["tool_calls"][0]["arguments"])["a"]
+    for _ in range(40):
+        v = v[0]
+    assert v == [1, "x"]
