@@ -714,6 +714,32 @@ class Interp {
 
   static long long norm_index(long long i, long long n) { return i < 0 ? i + n : i; }
 
+  // A chain of names, attributes and subscripts resolved to the stored value itself, without copying the containers on
+  // the way (a template that says messages[i] or message.content inside a loop over the messages would otherwise copy
+  // the whole conversation per access: quadratic in its length).  known = false: not such a chain, evaluate normally;
+  // known = true and nullptr: the chain resolves to undefined.
+  const Json* ref_of(const Expr& e, bool& known) {
+    known = true;
+    switch (e.kind) {
+      case Expr::Name: { Val* v = lookup_ref(e.name); return v && !v->undef ? &v->j : nullptr; }
+      case Expr::Attr: {
+        const Json* o = ref_of(*e.a, known);
+        if (!known || !o) return nullptr;
+        return o->is_object() ? o->find(e.name) : nullptr;
+      }
+      case Expr::Index: {
+        Val k = eval(e.b);                                 // first: evaluating the key may run arbitrary expressions
+        const Json* o = ref_of(*e.a, known);
+        if (!known || !o || k.undef) return nullptr;
+        if (o->is_object()) return k.j.is_string() ? o->find(k.j.as_string()) : nullptr;
+        if (o->is_array() && k.j.is_int()) { const long long n = (long long)o->size(), i = norm_index(k.j.as_int(), n); return i >= 0 && i < n ? &(*o)[(size_t)i] : nullptr; }
+        if (o->is_string()) known = false;                 // characters of a string: the general path
+        return nullptr;
+      }
+      default: known = false; return nullptr;
+    }
+  }
+
   Val eval(const ExprP& ep) {
     DepthGuard g(eval_depth_, kMaxEvalDepth, "expression evaluation");
     const Expr& e = *ep;
@@ -730,12 +756,14 @@ class Interp {
       case Expr::Neg: { Val v = eval(e.a); if (v.undef || !v.j.is_number()) throw Error("cannot negate this value"); return v.j.is_int() ? Val(Json(-v.j.as_int())) : Val(Json(-v.j.as_double())); }
       case Expr::Cond: if (truthy(eval(e.b))) return eval(e.a); return e.c ? eval(e.c) : Val();
       case Expr::Attr: {
+        { bool known; const Json* p = ref_of(e, known); if (known) return p ? Val(*p) : Val(); }
         Val o = eval(e.a);
         if (o.undef) return Val();
         if (o.j.is_object()) { const Json* p = o.j.find(e.name); return p ? Val(*p) : Val(); }
         return Val();
       }
       case Expr::Index: {
+        { bool known; const Json* p = ref_of(e, known); if (known) return p ? Val(*p) : Val(); }
         Val o = eval(e.a), k = eval(e.b);
         if (o.undef || k.undef) return Val();
         if (o.j.is_object()) { if (!k.j.is_string()) return Val(); const Json* p = o.j.find(k.j.as_string()); return p ? Val(*p) : Val(); }
@@ -749,7 +777,13 @@ class Interp {
       }
       case Expr::Slice: return eval_slice(e);
       case Expr::Bin: return eval_bin(e);
-      case Expr::Filter: return apply_filter(e.name, eval(e.a), e);
+      case Expr::Filter: {
+        if ((e.name == "length" || e.name == "count") && e.args.empty() && e.kwargs.empty()) {     // the size of a stored container
+          bool known; const Json* p = ref_of(*e.a, known);
+          if (known && p && (p->is_array() || p->is_object())) return Val(Json((long long)p->size()));
+        }
+        return apply_filter(e.name, eval(e.a), e);
+      }
       case Expr::Test: { const bool r = apply_test(e.name, eval(e.a), e); return Val(Json(e.negated ? !r : r)); }
       case Expr::Call: return eval_call(e);
     }

@@ -266,3 +266,20 @@ def test_templates_that_nest_without_end_are_refused_not_crashed():
         "print('refused', bad, 'of', len(cases))\n")
     r = subprocess.run([sys.executable, "-c", prog], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.strip() == "refused 11 of 11", (r.returncode, r.stdout, r.stderr[-1500:])
+
+
+def test_long_conversations_render_in_linear_time():
+    """A template that subscripts the message list inside its loop over the messages (most chat templates do) must not
+    copy the conversation per access: 4000 messages took seconds, a 1000-message agent transcript a quarter of one."""
+    import time
+    tmpl = ("{% for m in messages %}{% if loop.index0 > 0 and messages[loop.index0 - 1].role == m.role %}!{% endif %}"
+            "<|{{ m.role }}|>{{ m['content'] }}{% if messages | length > 1 and loop.last %}[{{ messages[-1].content | length }}]{% endif %}\n{% endfor %}")
+    def conv(n):
+        return [{"role": "user" if i % 2 == 0 else "assistant", "content": ("message %d " % i) * 40} for i in range(n)]
+    jinja2 = pytest.importorskip("jinja2")
+    want = jinja2.Environment(trim_blocks=True, lstrip_blocks=True).from_string(tmpl).render(messages=conv(50))
+    assert S.render_template(tmpl, messages=conv(50)) == want
+    S.render_template(tmpl, messages=conv(500))
+    t0 = time.time(); S.render_template(tmpl, messages=conv(1000)); t1 = time.time() - t0
+    t0 = time.time(); out = S.render_template(tmpl, messages=conv(8000)); t8 = time.time() - t0
+    assert out.count("<|user|>") == 4000 and t8 < 2.0 and t8 < 40 * max(t1, 0.005), (t1, t8)
