@@ -114,6 +114,7 @@ Tokenizer Tokenizer::from_json(const std::string& text) {
       if (e.get_bool("special", false)) t.special_[id] = true;
     }
     std::sort(t.added_.begin(), t.added_.end(), [](auto& a, auto& b) { return a.first.size() > b.first.size(); });
+    for (auto& a : t.added_) if (!a.first.empty()) t.added_first_[(unsigned char)a.first[0]] = true;
   }
   return t;
 }
@@ -179,6 +180,14 @@ std::vector<std::string> Tokenizer::pretokenize(const std::string& text) const {
 }
 
 void Tokenizer::bpe(const std::string& piece, std::vector<int>& out) const {
+  constexpr size_t kCacheWordBytes = 48, kCacheWords = 1u << 18;
+  const bool cacheable = piece.size() <= kCacheWordBytes;
+  if (cacheable) {
+    std::shared_lock<std::shared_mutex> l(cache_->mu);
+    auto it = cache_->ids.find(piece);
+    if (it != cache_->ids.end()) { out.insert(out.end(), it->second.begin(), it->second.end()); return; }
+  }
+  const size_t out_start = out.size();
   // byte-level symbols
   std::vector<std::string> sym;
   const unsigned* b2c = byte_to_cp();
@@ -223,6 +232,10 @@ void Tokenizer::bpe(const std::string& piece, std::vector<int>& out) const {
     // unknown merged symbol: fall back to its single byte-level characters
     for (size_t i = 0; i < s.size();) { size_t j = i; decode_cp(s, j); auto b = vocab_.find(s.substr(i, j - i)); if (b != vocab_.end()) out.push_back(b->second); i = j; }
   }
+  if (cacheable) {
+    std::unique_lock<std::shared_mutex> l(cache_->mu);
+    if (cache_->ids.size() < kCacheWords) cache_->ids.emplace(piece, std::vector<int>(out.begin() + (long)out_start, out.end()));
+  }
 }
 
 std::vector<int> Tokenizer::encode(const std::string& text) const {
@@ -233,7 +246,7 @@ std::vector<int> Tokenizer::encode(const std::string& text) const {
   };
   while (pos < text.size()) {
     bool hit = false;
-    if (!added_.empty()) {
+    if (added_first_[(unsigned char)text[pos]]) {          // only where an added token can start
       for (auto& a : added_) {
         if (!a.first.empty() && text.compare(pos, a.first.size(), a.first) == 0) {
           flush(pos);

@@ -2,6 +2,9 @@
 // chat template, reasoning splitter and tool-call parsers.  See text.cpp for the behaviour each class keeps.
 #pragma once
 #include <map>
+#include <memory>
+#include <mutex>
+#include <shared_mutex>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -28,8 +31,13 @@ class Tokenizer {
   std::vector<std::string> id_to_tok_;                      // id -> byte-level string (or added-token text)
   std::unordered_map<std::string, int> merge_rank_;         // "a b" -> rank
   std::vector<std::pair<std::string, int>> added_;          // added tokens, longest first
+  bool added_first_[256] = {};                              // bytes an added token starts with
   std::unordered_map<int, bool> special_;
   std::unordered_map<int, bool> is_added_;
+  // ids of pre-tokens seen before (words repeat: most of a prompt is served from here); shared by the threads that
+  // encode through this tokenizer, copies of the tokenizer share it too
+  struct WordCache { std::shared_mutex mu; std::unordered_map<std::string, std::vector<int>> ids; };
+  std::shared_ptr<WordCache> cache_ = std::make_shared<WordCache>();
 };
 
 // Streams text out of a growing id list without ever emitting half a UTF-8 sequence.
