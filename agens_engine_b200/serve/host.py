@@ -3,6 +3,7 @@ page allocator, KV admission policy, copy-lookup drafter, prefix cache, memory p
 implements these in Rust (``crates/agens-cli/src/{sampler,lookup,prefix,plan,profile,serve}.rs``)."""
 from __future__ import annotations
 
+import array
 import ctypes as C
 import json
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -40,6 +41,7 @@ def lib() -> C.CDLL:
             "b2h_prefix_new": ([ll, i], vp), "b2h_prefix_free": ([vp], None),
             "b2h_prefix_lookup": ([vp, ip, i, C.c_ulonglong, llp], i),
             "b2h_prefix_insert": ([vp, ip, i, C.c_ulonglong, ll, ll, llp, i], i),
+            "b2h_prefix_insert_chain": ([vp, ip, i, C.c_ulonglong, ll, ll, llp, i], i),
             "b2h_prefix_ref": ([vp, ll, i], None), "b2h_prefix_used": ([vp], ll), "b2h_prefix_evict_lru": ([vp], ll),
             "b2h_plan": ([C.c_char_p], vp), "b2h_profile": ([C.c_char_p, i], vp), "b2h_free_str": ([vp], None),
             "b2h_host_mem_available": ([], ll),
@@ -52,7 +54,12 @@ def lib() -> C.CDLL:
 
 
 def _ints(xs: Sequence[int]):
-    return (C.c_int * len(xs))(*xs)
+    """A C int array of ``xs`` (through array.array: several times faster than unpacking into the ctypes constructor,
+    which matters for prompts of a hundred thousand tokens)."""
+    if len(xs) < 64:
+        return (C.c_int * len(xs))(*xs)
+    a = array.array("i", xs)
+    return (C.c_int * len(a)).from_buffer(a)
 
 
 def _take_json(p) -> dict:
@@ -222,7 +229,10 @@ class PrefixCache:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            lib().b2h_prefix_free(self._h)
+            try:
+                lib().b2h_prefix_free(self._h)
+            except TypeError:                               # interpreter shutdown: the module globals are gone
+                pass
 
     def lookup(self, toks: Sequence[int], salt: int = 0):
         h = C.c_longlong(-1)
@@ -232,6 +242,13 @@ class PrefixCache:
     def insert(self, toks: Sequence[int], handle: int, nbytes: int, salt: int = 0):
         ev = (C.c_longlong * 64)()
         n = lib().b2h_prefix_insert(self._h, _ints(toks), len(toks), salt, handle, nbytes, ev, 64)
+        return n, list(ev[:max(n, 0)])
+
+    def insert_chain(self, toks: Sequence[int], handle: int, nbytes: int, salt: int = 0):
+        """One entry per chunk boundary of ``toks`` in one pass (the bytes are booked on the longest); returns
+        ``(count, evicted handles)`` like :meth:`insert`."""
+        ev = (C.c_longlong * 256)()
+        n = lib().b2h_prefix_insert_chain(self._h, _ints(toks), len(toks), salt, handle, nbytes, ev, 256)
         return n, list(ev[:max(n, 0)])
 
     def ref(self, handle: int, delta: int):

@@ -290,7 +290,27 @@ class PrefixCache {
   // to `evicted` (caller frees their device/host memory); returns their count, -1 if the snapshot cannot fit.
   int insert(const int* toks, int n, uint64_t salt, long long handle, long long bytes, long long* evicted, int max_evicted) {
     if (n % chunk_ != 0 || bytes > budget_) return -1;
-    const uint64_t k = key_of(toks, n, salt);
+    return insert_key(key_of(toks, n, salt), handle, bytes, evicted, max_evicted);
+  }
+  // One entry per chunk boundary of the first n tokens in a single pass over them (n rounded down to a boundary); the
+  // bytes are booked on the longest entry.  Same result as insert() per boundary, without hashing every prefix from the
+  // start (a 128K-token conversation has 2048 boundaries).  Returns the number of evicted handles, -1 if it cannot fit.
+  int insert_chain(const int* toks, int n, uint64_t salt, long long handle, long long bytes, long long* evicted, int max_evicted) {
+    const int top = n / chunk_ * chunk_;
+    if (bytes > budget_) return -1;
+    uint64_t h = 0x243f6a8885a308d3ull ^ salt;
+    int ne = 0;
+    for (int i = 0; i < top; ++i) {
+      h = mix(h, (uint32_t)toks[i]);
+      if ((i + 1) % chunk_ == 0) {
+        const int r = insert_key(mix(h, (uint64_t)(i + 1)), handle, i + 1 == top ? bytes : 0, evicted + ne, max_evicted - ne);
+        if (r < 0) return -1;
+        ne += r;
+      }
+    }
+    return ne;
+  }
+  int insert_key(uint64_t k, long long handle, long long bytes, long long* evicted, int max_evicted) {
     if (map_.count(k)) return 0;
     int ne = 0;
     while (used_ + bytes > budget_) {
@@ -387,6 +407,9 @@ B2H_API void b2h_prefix_free(void* p) { delete static_cast<PrefixCache*>(p); }
 B2H_API int b2h_prefix_lookup(void* p, const int* toks, int n, unsigned long long salt, long long* handle) { return static_cast<PrefixCache*>(p)->lookup(toks, n, salt, handle); }
 B2H_API int b2h_prefix_insert(void* p, const int* toks, int n, unsigned long long salt, long long handle, long long bytes, long long* evicted, int max_evicted) {
   return static_cast<PrefixCache*>(p)->insert(toks, n, salt, handle, bytes, evicted, max_evicted);
+}
+B2H_API int b2h_prefix_insert_chain(void* p, const int* toks, int n, unsigned long long salt, long long handle, long long bytes, long long* evicted, int max_evicted) {
+  return static_cast<PrefixCache*>(p)->insert_chain(toks, n, salt, handle, bytes, evicted, max_evicted);
 }
 B2H_API void b2h_prefix_ref(void* p, long long handle, int delta) { static_cast<PrefixCache*>(p)->ref(handle, delta); }
 B2H_API long long b2h_prefix_used(void* p) { return static_cast<PrefixCache*>(p)->used(); }

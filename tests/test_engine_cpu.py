@@ -386,3 +386,38 @@ def test_random_workloads_keep_every_request_exact_and_leak_nothing():
         seen["left"] += len(gone)
         seen["errors"] += sum(1 for e in done.values() if e)
     assert seen["evictions"] > 0 and seen["accepted"] > 0 and seen["rejected_drafts"] > 0 and seen["left"] > 0, seen
+
+
+def test_the_scheduler_itself_is_cheap_at_128k_tokens():
+    """A 128K-token conversation through the engine with a stand-in model that costs nothing: admission, chunking, the
+    prefix cache, the copy-lookup index and keeping the sequence for the next turn take well under a second (keeping it
+    alone took 18 s when every chunk boundary was hashed from the start of the prompt)."""
+    import time
+
+    class Free(FakeModel):
+        def prefill(self, s, ids, want_logits=False, **kw):
+            self._fit(s, len(self.tokens[s]) + len(ids))
+            self.tokens[s] += ids.tolist()
+            self.seq_len_host[s] = len(self.tokens[s])
+            return 5, None
+
+        def forward_rows(self, ids, seqs, want_logits=False):
+            for t, s in zip(ids, seqs):
+                self.tokens[s].append(int(t))
+                self.seq_len_host[s] = len(self.tokens[s])
+            for s in set(seqs):
+                self._fit(s, len(self.tokens[s]))
+            return torch.tensor([7] * len(ids), dtype=torch.int32), None
+    m = Free(max_seqs=2, max_ctx=140000, page=16, chunk=8192)
+    got = {}
+    eng = Engine(m, lambda rid, t, f, e: got.setdefault(rid, []).extend(t) or False, sources_factory=lambda: [CopyLookupSource()],
+                 max_drafts=3, keep_sequences=True)
+    prompt = torch.randint(0, 500, (131072,)).tolist()
+    t0 = time.time()
+    r1 = eng.submit(prompt, {"max_new_tokens": 16}, session="a")
+    eng.run_until_idle(100000)
+    t1 = time.time()
+    r2 = eng.submit(prompt + got[r1] + [3, 4, 5], {"max_new_tokens": 16}, session="a")     # the next turn takes the kept sequence over
+    eng.run_until_idle(100000)
+    t2 = time.time()
+    assert len(got[r1]) == 16 and len(got[r2]) == 16 and t1 - t0 < 5.0 and t2 - t1 < 5.0, (t1 - t0, t2 - t1)

@@ -238,3 +238,32 @@ def test_page_allocator_against_a_model_under_random_operations():
 
 def a_free(model, n_pages):
     return n_pages - len({p for pages, _ in model.values() for p in pages if p >= 0})
+
+
+def test_prefix_chain_insert_equals_one_insert_per_boundary():
+    """insert_chain registers every chunk boundary of a token list in one pass; lookups and evictions behave as after one
+    insert() per boundary (which hashed every prefix from its start: 18 s for a 128K-token conversation)."""
+    import random
+    import time
+    rng = random.Random(3)
+    toks = [rng.randrange(50000) for _ in range(1000)]
+    a, b = H.PrefixCache(10_000, 64), H.PrefixCache(10_000, 64)
+    for cache, chained in ((a, False), (b, True)):
+        cache.insert([1] * 128, 7, 6000)                       # an older snapshot that the new one pushes out
+        if chained:
+            n, ev = cache.insert_chain(toks, 9, 5000)
+        else:
+            ev = []
+            top = len(toks) // 64 * 64
+            for c in range(64, top + 1, 64):
+                _, e = cache.insert(toks[:c], 9, 5000 if c == top else 0)
+                ev += e
+        assert ev == [7] and cache.used == 5000
+    for probe in (toks, toks[:700], toks[:64] + [0] * 200, toks[:63], [5] * 300):
+        assert a.lookup(probe) == b.lookup(probe)
+    assert b.lookup(toks) == (960, 9) and b.lookup(toks[:700]) == (640, 9)
+    big = [rng.randrange(50000) for _ in range(131072)]
+    c = H.PrefixCache(1 << 40, 64)
+    t0 = time.time()
+    c.insert_chain(big, 1, 1 << 30)
+    assert c.lookup(big) == (131072, 1) and time.time() - t0 < 2.0
