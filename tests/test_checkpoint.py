@@ -185,3 +185,33 @@ def test_damaged_safetensors_headers_are_refused(tmp_path):
     for hlen in (2**63, 2**64 - 1, 10**6):
         with pytest.raises(IOError):
             SafeTensorsFile(write(good, hlen=hlen))
+
+
+def test_sha256_portable_loop_in_a_process_of_its_own():
+    """B200E_NO_SHA_NI=1 keeps the portable compression function: the same test in a fresh process."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, B200E_NO_SHA_NI="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", __file__, "-q", "-k", "equals_hashlib", "-p", "no:cacheprovider"], env=env,
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "1 passed" in r.stdout, r.stdout[-1500:] + r.stderr[-500:]
+
+
+def test_sha256_equals_hashlib_at_every_length():
+    """Both compression functions (the CPU's SHA extensions where it has them, the portable loop elsewhere) through the
+    streaming interface: every length around the block and padding boundaries, and a few megabytes."""
+    import ctypes as C
+    import hashlib
+    import os
+    from agens_engine_b200 import _lib
+    h = _lib.host_lib()
+    h.b2h_sha256_bytes.restype = C.c_void_p
+    h.b2h_sha256_bytes.argtypes = [C.c_char_p, C.c_longlong]
+    h.b2h_free_str.argtypes = [C.c_void_p]
+    data = os.urandom(3 * 1024 * 1024 + 17)
+    for n in list(range(0, 260)) + [4095, 4096, 4097, 65536 + 55, 65536 + 56, 1 << 20, len(data)]:
+        p = h.b2h_sha256_bytes(data[:n], n)
+        got = C.string_at(p).decode()
+        h.b2h_free_str(p)
+        assert got == hashlib.sha256(data[:n]).hexdigest(), n
