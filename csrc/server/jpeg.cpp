@@ -151,29 +151,58 @@ int extend(int v, int n) { return v < (1 << (n - 1)) ? v - (1 << n) + 1 : v; }
 
 // Inverse DCT of one dequantised block (separable, float), level shift and clamp.
 struct IdctTable {
-  float c[8][8];
+  float c[8][8];                             // c[x][u]
+  float ct[8][8];                            // ct[u][x]: the same numbers with the output index innermost
   IdctTable() {
     for (int x = 0; x < 8; ++x)
-      for (int u = 0; u < 8; ++u) c[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979323846f / 16.f);
+      for (int u = 0; u < 8; ++u) ct[u][x] = c[x][u] = (u == 0 ? std::sqrt(0.125f) : 0.5f) * std::cos((2 * x + 1) * u * 3.14159265358979323846f / 16.f);
   }
 };
-void idct_store(const int* coef, uint8_t* out, int stride) {
+// Sums run over ascending u (then v) as in the plain triple loop, zero coefficients and all-zero rows left out (adding
+// them changes nothing), the output index innermost so that the compiler can use vector registers.  A block with only
+// its DC coefficient (most blocks of a smooth image) is one constant.
+__attribute__((optimize("O3"))) void idct_store(const int* coef, uint8_t* out, int stride) {
   static const IdctTable table;              // initialised once, thread-safe
   const float (*c)[8] = table.c;
+  const float (*ct)[8] = table.ct;
+  unsigned rows = 0;                         // bit v: row v has a non-zero coefficient
+  for (int v = 0; v < 8; ++v) {
+    int any = 0;
+    for (int u = 0; u < 8; ++u) any |= coef[v * 8 + u];
+    if (any) rows |= 1u << v;
+  }
+  bool dc_only = rows <= 1u;
+  if (dc_only) for (int u = 1; u < 8; ++u) dc_only = dc_only && coef[u] == 0;
+  if (dc_only) {
+    const float s = c[0][0] * (c[0][0] * (float)coef[0]);
+    const int q = (int)std::lrintf(s + 128.f);
+    const uint8_t px = (uint8_t)std::min(255, std::max(0, q));
+    for (int y = 0; y < 8; ++y) std::memset(out + y * stride, px, 8);
+    return;
+  }
   float tmp[64];
-  for (int v = 0; v < 8; ++v)               // rows: over u
-    for (int x = 0; x < 8; ++x) {
-      float s = 0.f;
-      for (int u = 0; u < 8; ++u) s += c[x][u] * (float)coef[v * 8 + u];
-      tmp[v * 8 + x] = s;
+  for (int v = 0; v < 8; ++v) {             // rows: over u
+    if (!(rows >> v & 1u)) continue;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int u = 0; u < 8; ++u) {
+      if (coef[v * 8 + u] == 0) continue;
+      const float f = (float)coef[v * 8 + u];
+      for (int x = 0; x < 8; ++x) acc[x] += ct[u][x] * f;
     }
-  for (int x = 0; x < 8; ++x)               // columns: over v
-    for (int y = 0; y < 8; ++y) {
-      float s = 0.f;
-      for (int v = 0; v < 8; ++v) s += c[y][v] * tmp[v * 8 + x];
-      const int q = (int)std::lrintf(s + 128.f);
+    for (int x = 0; x < 8; ++x) tmp[v * 8 + x] = acc[x];
+  }
+  for (int y = 0; y < 8; ++y) {             // columns: over v
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int v = 0; v < 8; ++v) {
+      if (!(rows >> v & 1u)) continue;
+      const float f = c[y][v];
+      for (int x = 0; x < 8; ++x) acc[x] += f * tmp[v * 8 + x];
+    }
+    for (int x = 0; x < 8; ++x) {
+      const int q = (int)std::lrintf(acc[x] + 128.f);
       out[y * stride + x] = (uint8_t)std::min(255, std::max(0, q));
     }
+  }
 }
 
 // ---- one block of one scan --------------------------------------------------------------------------------------------
@@ -554,6 +583,32 @@ inline float sample_up(const Comp& c, int x, int y, int hs, int vs, int W, int H
   return a * (1.f - wy) + b * wy;
 }
 
+// One full-resolution row of a component: the same arithmetic as sample_up() for every x, with the row addresses and
+// weights taken once per row instead of once per pixel.
+__attribute__((optimize("O3"))) void sample_row(const Comp& c, int y, int hs, int vs, int W, int H, float* out) {
+  const int stride = c.bw * 8, pw = (W + hs - 1) / hs, ph = (H + vs - 1) / vs;
+  auto clampi = [](int v, int hi) { return std::min(std::max(v, 0), hi); };
+  if (hs == 1 && vs == 1) {
+    const uint8_t* r = c.plane.data() + (size_t)clampi(y, ph - 1) * stride;
+    for (int x = 0; x < W; ++x) out[x] = (float)r[x];                 // pw == W here
+    return;
+  }
+  int y0 = y, y1 = y;
+  float wy = 0.f;
+  if (vs == 2) { y0 = y >> 1; y1 = (y & 1) ? y0 + 1 : y0 - 1; wy = 0.25f; }
+  const uint8_t* r0 = c.plane.data() + (size_t)clampi(y0, ph - 1) * stride;
+  const uint8_t* r1 = c.plane.data() + (size_t)clampi(y1, ph - 1) * stride;
+  for (int x = 0; x < W; ++x) {
+    int x0 = x, x1 = x;
+    float wx = 0.f;
+    if (hs == 2) { x0 = x >> 1; x1 = (x & 1) ? x0 + 1 : x0 - 1; wx = 0.25f; }
+    x0 = clampi(x0, pw - 1); x1 = clampi(x1, pw - 1);
+    const float a = (float)r0[x0] * (1.f - wx) + (float)r0[x1] * wx;
+    const float b = (float)r1[x0] * (1.f - wx) + (float)r1[x1] * wx;
+    out[x] = a * (1.f - wy) + b * wy;
+  }
+}
+
 inline uint8_t clamp8(float v) { return (uint8_t)std::min(255, std::max(0, (int)std::lrintf(v))); }
 
 void to_rgb(const Dec& d, uint8_t* rgb) {
@@ -592,23 +647,24 @@ void to_rgb(const Dec& d, uint8_t* rgb) {
   }
   // three components: YCbCr unless an Adobe segment says the data is RGB (transform 0)
   const bool ycc = !(d.adobe && d.adobe_transform == 0);
-  for (int y = 0; y < d.H; ++y)
-    for (int x = 0; x < d.W; ++x) {
-      float v[3];
-      for (int i = 0; i < 3; ++i) {
-        const Comp& c = d.comp[i];
-        v[i] = sample_up(c, x, y, d.hmax / c.h, d.vmax / c.v, d.W, d.H);
-      }
-      uint8_t* o = rgb + ((size_t)y * d.W + x) * 3;
-      if (ycc) {
-        const float Y = v[0], cb = v[1] - 128.f, cr = v[2] - 128.f;
+  std::vector<float> rows((size_t)3 * d.W);
+  float* v0 = rows.data();
+  float* v1 = v0 + d.W;
+  float* v2 = v1 + d.W;
+  for (int y = 0; y < d.H; ++y) {
+    for (int i = 0; i < 3; ++i) sample_row(d.comp[i], y, d.hmax / d.comp[i].h, d.vmax / d.comp[i].v, d.W, d.H, v0 + (size_t)i * d.W);
+    uint8_t* o = rgb + (size_t)y * d.W * 3;
+    if (ycc) {
+      for (int x = 0; x < d.W; ++x, o += 3) {
+        const float Y = v0[x], cb = v1[x] - 128.f, cr = v2[x] - 128.f;
         o[0] = clamp8(Y + 1.402f * cr);
         o[1] = clamp8(Y - 0.344136f * cb - 0.714136f * cr);
         o[2] = clamp8(Y + 1.772f * cb);
-      } else {
-        o[0] = clamp8(v[0]); o[1] = clamp8(v[1]); o[2] = clamp8(v[2]);
       }
+    } else {
+      for (int x = 0; x < d.W; ++x, o += 3) { o[0] = clamp8(v0[x]); o[1] = clamp8(v1[x]); o[2] = clamp8(v2[x]); }
     }
+  }
 }
 
 thread_local std::string g_jpeg_err;
