@@ -144,6 +144,7 @@ struct Server {
   std::atomic<int> listen_fd{-1};
   std::thread accept_thread;
   std::atomic<bool> stopping{false};
+  std::atomic<int> live_connections{0};      // connection threads that still use this object
 };
 
 static std::string hex_id(int n) {
@@ -924,6 +925,12 @@ static void serve_connection(Server* sv, int fd) {
   shutdown(fd, SHUT_RDWR);
   close(fd);
   --g_connections;
+  --sv->live_connections;                    // last use of sv by this thread
+}
+
+// Connection threads are detached; the object they serve must outlive them.  Waits (bounded) until none is left.
+static void drain_connections(Server* sv, int seconds) {
+  for (int i = 0; i < seconds * 100 && sv->live_connections.load() > 0; ++i) std::this_thread::sleep_for(std::chrono::milliseconds(10));
 }
 
 }  // namespace b2
@@ -964,7 +971,14 @@ B2H_API void* b2h_server_new(const char* config_json, char* err, int err_cap) {
     return sv;
   } catch (const std::exception& e) { if (err) snprintf(err, err_cap, "%s", e.what()); return nullptr; }
 }
-B2H_API void b2h_server_free(void* s) { delete static_cast<Server*>(s); }
+B2H_API void b2h_server_stop(void* sp);
+B2H_API void b2h_server_free(void* s) {
+  auto sv = static_cast<Server*>(s);
+  if (sv->listen_fd.load() >= 0 || sv->accept_thread.joinable()) b2h_server_stop(s);
+  drain_connections(sv, 30);
+  if (sv->live_connections.load() > 0) return;            // a connection is stuck past every time-out: leak rather than free under it
+  delete sv;
+}
 B2H_API void b2h_server_use_mock(void* s, const int* script, int n, int step, int supports_images) {
   auto m = std::make_shared<MockBackend>();
   m->script.assign(script, script + n); m->step = std::max(1, step); m->images = supports_images != 0;
@@ -1044,9 +1058,10 @@ B2H_API int b2h_server_start(void* sp, const char* host, int port) {
         --g_connections;
         continue;
       }
+      ++sv->live_connections;
       try {
         std::thread(serve_connection, sv, c).detach();
-      } catch (const std::system_error&) { close(c); --g_connections; }
+      } catch (const std::system_error&) { close(c); --g_connections; --sv->live_connections; }
     }
   });
   return ntohs(a.sin_port);
@@ -1057,6 +1072,7 @@ B2H_API void b2h_server_stop(void* sp) {
   const int lfd = sv->listen_fd.exchange(-1);
   if (lfd >= 0) { shutdown(lfd, SHUT_RDWR); close(lfd); }
   if (sv->accept_thread.joinable()) sv->accept_thread.join();
+  drain_connections(sv, 5);                  // requests in flight finish (or their clients time out) before the caller moves on
 }
 
 // ---- text layer exports (tests, Python-side engine glue) ----
