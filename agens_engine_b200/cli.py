@@ -600,6 +600,14 @@ def cmd_serve(ns):
     port = srv.start(cfg.host, cfg.port)
     print(f"serving {cfg.served_model_name} on http://{cfg.host}:{port} (tp {world}, max batch {eng.max_batch})", flush=True)
     rc = 0
+
+    def _terminate(signum, frame):           # `docker stop` sends SIGTERM: leave through the same path as Ctrl-C
+        raise KeyboardInterrupt
+    try:
+        import signal
+        signal.signal(signal.SIGTERM, _terminate)
+    except ValueError:                       # not the main thread (embedded use): the caller owns signal handling
+        pass
     try:
         while eng.fatal is None:
             time.sleep(0.5)
