@@ -58,7 +58,10 @@ def _ints(xs: Sequence[int]):
     which matters for prompts of a hundred thousand tokens)."""
     if len(xs) < 64:
         return (C.c_int * len(xs))(*xs)
-    a = array.array("i", xs)
+    try:
+        a = array.array("i", xs)
+    except (TypeError, OverflowError):                      # elements that are not plain ints: the general constructor
+        return (C.c_int * len(xs))(*xs)
     return (C.c_int * len(a)).from_buffer(a)
 
 
@@ -76,7 +79,10 @@ class Sampler:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            lib().b2h_sampler_free(self._h)
+            try:
+                lib().b2h_sampler_free(self._h)
+            except TypeError:                               # interpreter shutdown: the module globals are gone
+                pass
 
     def sample(self, logits, extra: Sequence[Tuple[int, float]] = ()) -> int:
         import numpy as np
@@ -101,7 +107,10 @@ class ReasoningBudget:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            lib().b2h_budget_free(self._h)
+            try:
+                lib().b2h_budget_free(self._h)
+            except TypeError:                               # interpreter shutdown: the module globals are gone
+                pass
 
     def accept(self, out_index: int, tok: int):
         lib().b2h_budget_accept(self._h, out_index, tok)
@@ -119,7 +128,10 @@ class ThinkGuard:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            lib().b2h_guard_free(self._h)
+            try:
+                lib().b2h_guard_free(self._h)
+            except TypeError:                               # interpreter shutdown: the module globals are gone
+                pass
 
     def filter(self, tok: int, pending: bool = True) -> int:
         return lib().b2h_guard_filter(self._h, tok, 1 if pending else 0)
@@ -136,7 +148,10 @@ class PageAllocator:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            lib().b2h_pages_free(self._h)
+            try:
+                lib().b2h_pages_free(self._h)
+            except TypeError:                               # interpreter shutdown: the module globals are gone
+                pass
 
     free_pages = property(lambda self: lib().b2h_pages_free_count(self._h))
 
@@ -203,7 +218,10 @@ class CopyLookup:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            lib().b2h_lookup_free(self._h)
+            try:
+                lib().b2h_lookup_free(self._h)
+            except TypeError:                               # interpreter shutdown: the module globals are gone
+                pass
 
     def extend(self, toks: Sequence[int]):
         lib().b2h_lookup_extend(self._h, _ints(toks), len(toks))
